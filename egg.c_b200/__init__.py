@@ -1,0 +1,225 @@
+"""egg_c_b200 — ctypes host binding of libegg_b200.so (the C ABI of include/egg_b200.h).
+
+The library is the product; this module only loads it, mirrors `struct egg_config`
+and wraps each entry point so that tests and bench.py read like the reference's
+training loop (full_cuda_train_transformer_adam_mgpu.cu:1506-1688).  There is no
+CPU fallback: a missing or unloadable library raises.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libegg_b200.so")
+
+EGG_OK, EGG_E_INVALID, EGG_E_CUDA, EGG_E_NOMEM, EGG_E_TIMEOUT, EGG_E_NCCL, EGG_E_STATE = 0, -1, -2, -3, -4, -5, -6
+
+EXPORTS = [
+    "egg_config_defaults", "egg_config_validate", "egg_model_bytes", "egg_opt_state_bytes", "egg_ctx_create",
+    "egg_ctx_destroy", "egg_last_error", "egg_sync", "egg_upload_model", "egg_download_model", "egg_upload_opt_state",
+    "egg_download_opt_state", "egg_set_dataset", "egg_eval_chunk", "egg_read_losses", "egg_compute_fitness_pairs",
+    "egg_write_fitness", "egg_read_fitness", "egg_nccl_unique_id", "egg_comm_init", "egg_allgather_fitness",
+    "egg_apply_update", "egg_generation_host", "egg_perturbed_projection", "egg_update_reconstruct",
+]
+
+
+class EggConfig(C.Structure):
+    """struct egg_config (include/egg_b200.h)."""
+    _fields_ = [(n, C.c_int32) for n in (
+        "hidden_dim", "head_dim", "n_layers", "seq_len", "vocab_size", "population_size",
+        "fixed_point", "sigma_shift", "sigma_shift_vector", "shift_attn", "shift_out",
+        "shift_logit", "shift_mlp_up", "shift_mlp_down", "softmax_scale_bit", "rope_scale_bit",
+        "device_mask", "device_gaussian", "host_mask", "use_same_data", "use_muon",
+        "chunk_relative_loss")] + [
+        ("softmax_exp_scale", C.c_double), ("adam_beta1", C.c_float), ("adam_beta2", C.c_float),
+        ("adam_eps", C.c_float), ("adam_weight_decay", C.c_float), ("muon_momentum", C.c_float),
+        ("muon_lr_scale", C.c_float)]
+
+
+class EggError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__("egg_b200 error %d: %s" % (code, msg))
+        self.code = code
+
+
+_lib = None
+
+
+def build(force=False):
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("egg_c_b200_build", os.path.join(_HERE, "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.build(force=force)
+
+
+def lib():
+    """Loads libegg_b200.so; raises if it is missing (there is no fallback path)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise EggError(EGG_E_STATE, "libegg_b200.so is not built (run python egg.c_b200/build.py)")
+        L = C.CDLL(LIB_PATH)
+        P = C.POINTER
+        cfgp = P(EggConfig)
+        vp = C.c_void_p
+        L.egg_config_defaults.argtypes = [cfgp]
+        L.egg_config_defaults.restype = None
+        L.egg_config_validate.argtypes = [cfgp, P(C.c_char_p)]
+        L.egg_model_bytes.argtypes = [cfgp]
+        L.egg_model_bytes.restype = C.c_int64
+        L.egg_opt_state_bytes.argtypes = [cfgp]
+        L.egg_opt_state_bytes.restype = C.c_int64
+        L.egg_ctx_create.argtypes = [cfgp, C.c_int, C.c_int, P(vp)]
+        L.egg_ctx_destroy.argtypes = [vp]
+        L.egg_ctx_destroy.restype = None
+        L.egg_last_error.restype = C.c_char_p
+        L.egg_sync.argtypes = [vp]
+        for f in (L.egg_upload_model, L.egg_download_model, L.egg_upload_opt_state, L.egg_download_opt_state, L.egg_set_dataset):
+            f.argtypes = [vp, vp, C.c_int64]
+        L.egg_eval_chunk.argtypes = [vp, C.c_uint32, C.c_int64, C.c_int, C.c_int]
+        L.egg_read_losses.argtypes = [vp, vp, C.c_int, C.c_int]
+        L.egg_compute_fitness_pairs.argtypes = [vp, C.c_int, C.c_int]
+        L.egg_write_fitness.argtypes = [vp, vp, C.c_int, C.c_int]
+        L.egg_read_fitness.argtypes = [vp, vp, C.c_int, C.c_int]
+        L.egg_nccl_unique_id.argtypes = [vp]
+        L.egg_comm_init.argtypes = [vp, vp, C.c_int, C.c_int]
+        L.egg_allgather_fitness.argtypes = [vp]
+        L.egg_apply_update.argtypes = [vp, C.c_uint32, C.c_float, P(C.c_uint64)]
+        L.egg_generation_host.argtypes = [vp, vp, C.c_int64, C.c_int64, C.c_uint32, C.c_float, vp, P(C.c_uint64)]
+        L.egg_perturbed_projection.argtypes = [vp, vp, vp, vp, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_int,
+                                               C.c_int, C.c_int, C.c_int, C.c_int]
+        L.egg_update_reconstruct.argtypes = [vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint32, vp, C.c_int]
+        _lib = L
+    return _lib
+
+
+def _check(rc):
+    if rc != 0:
+        raise EggError(rc, lib().egg_last_error().decode())
+
+
+def default_config(**kw):
+    cfg = EggConfig()
+    lib().egg_config_defaults(C.byref(cfg))
+    for k, v in kw.items():
+        if not hasattr(cfg, k):
+            raise KeyError(k)
+        setattr(cfg, k, v)
+    return cfg
+
+
+def model_bytes(cfg):
+    return lib().egg_model_bytes(C.byref(cfg))
+
+
+def opt_state_bytes(cfg):
+    return lib().egg_opt_state_bytes(C.byref(cfg))
+
+
+def _ptr(a):
+    if a is None:
+        return None
+    if isinstance(a, int):
+        return C.c_void_p(a)
+    return a.ctypes.data_as(C.c_void_p)
+
+
+class Context:
+    """One egg_ctx: one process, one GPU."""
+
+    def __init__(self, cfg, device=0, wave_members=0):
+        self.cfg = cfg
+        self._h = C.c_void_p()
+        _check(lib().egg_ctx_create(C.byref(cfg), device, wave_members, C.byref(self._h)))
+
+    def close(self):
+        if self._h:
+            lib().egg_ctx_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def sync(self):
+        _check(lib().egg_sync(self._h))
+
+    def upload_model(self, model):
+        model = np.ascontiguousarray(model, np.int8)
+        _check(lib().egg_upload_model(self._h, _ptr(model), model.nbytes))
+
+    def download_model(self):
+        out = np.zeros(model_bytes(self.cfg), np.int8)
+        _check(lib().egg_download_model(self._h, _ptr(out), out.nbytes))
+        return out
+
+    def upload_opt_state(self, state):
+        state = np.ascontiguousarray(state, np.uint8)
+        _check(lib().egg_upload_opt_state(self._h, _ptr(state), state.nbytes))
+
+    def download_opt_state(self):
+        out = np.zeros(opt_state_bytes(self.cfg), np.uint8)
+        _check(lib().egg_download_opt_state(self._h, _ptr(out), out.nbytes))
+        return out
+
+    def set_dataset(self, tokens):
+        tokens = np.ascontiguousarray(tokens, np.uint8)
+        _check(lib().egg_set_dataset(self._h, _ptr(tokens), tokens.nbytes))
+
+    def eval_chunk(self, step_seed, start_idx, pop_offset, count):
+        _check(lib().egg_eval_chunk(self._h, step_seed & 0xFFFFFFFF, start_idx, pop_offset, count))
+
+    def read_losses(self, offset, count):
+        out = np.zeros(count, np.int32)
+        _check(lib().egg_read_losses(self._h, _ptr(out), offset, count))
+        return out
+
+    def compute_fitness_pairs(self, pair_offset, pair_count):
+        _check(lib().egg_compute_fitness_pairs(self._h, pair_offset, pair_count))
+
+    def write_fitness(self, fit, pair_offset=0):
+        fit = np.ascontiguousarray(fit, np.int32)
+        _check(lib().egg_write_fitness(self._h, _ptr(fit), pair_offset, len(fit)))
+
+    def read_fitness(self, pair_offset, pair_count):
+        out = np.zeros(pair_count, np.int32)
+        _check(lib().egg_read_fitness(self._h, _ptr(out), pair_offset, pair_count))
+        return out
+
+    def comm_init(self, id128, rank, world):
+        buf = (C.c_char * 128).from_buffer_copy(bytes(id128))
+        _check(lib().egg_comm_init(self._h, buf, rank, world))
+
+    def allgather_fitness(self):
+        _check(lib().egg_allgather_fitness(self._h))
+
+    def apply_update(self, step_seed, lr):
+        n = C.c_uint64(0)
+        _check(lib().egg_apply_update(self._h, step_seed & 0xFFFFFFFF, C.c_float(lr), C.byref(n)))
+        return n.value
+
+    def generation_host(self, tokens, step, step_seed, lr, losses_out=None):
+        """tokens: pinned/pageable host uint8 array or None to keep the resident dataset."""
+        n = C.c_uint64(0)
+        tp, tl = (None, 0) if tokens is None else (_ptr(tokens), tokens.nbytes)
+        _check(lib().egg_generation_host(self._h, tp, tl, step, step_seed & 0xFFFFFFFF, C.c_float(lr), _ptr(losses_out), C.byref(n)))
+        return n.value
+
+    def perturbed_projection(self, x, w_packed, y, rows, k_dim, n_dim, rows_per_member, seed, off_a, off_b,
+                             rank1_shift, out_shift, on_device=False):
+        _check(lib().egg_perturbed_projection(self._h, _ptr(x), _ptr(w_packed), _ptr(y), rows, k_dim, n_dim, rows_per_member,
+                                              seed & 0xFFFFFFFF, off_a, off_b, rank1_shift, out_shift, 1 if on_device else 0))
+
+    def update_reconstruct(self, fitness, pairs, rows_k, cols_n, off_a, off_b, seed_base, step_seed, vote_out, on_device=False):
+        _check(lib().egg_update_reconstruct(self._h, _ptr(fitness), pairs, rows_k, cols_n, off_a, off_b, seed_base,
+                                            step_seed & 0xFFFFFFFF, _ptr(vote_out), 1 if on_device else 0))
+
+
+def nccl_unique_id():
+    buf = (C.c_char * 128)()
+    _check(lib().egg_nccl_unique_id(buf))
+    return bytes(buf)

@@ -1,0 +1,850 @@
+// C ABI of the library (include/egg_b200.h): context, uploads, the layer-major
+// evaluation pipeline, fitness, NCCL exchange, update reconstruction + optimiser.
+// "mgpu.cu" = full_cuda_train_transformer_adam_mgpu.cu of the reference.
+#include "egg_kernels.cuh"
+
+#include <dlfcn.h>
+#include <math.h>
+#include <stdarg.h>
+#include <string.h>
+
+#include <vector>
+
+#include <nccl.h>
+
+namespace egg {
+
+static thread_local char g_err[512] = "";
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+// ---- NCCL, resolved at run time so that single-GPU users need no NCCL at all ----
+struct NcclApi {
+    void *h = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    const char *(*GetErrorString)(ncclResult_t) = nullptr;
+};
+static NcclApi g_nccl;
+static int nccl_load() {
+    if (g_nccl.h) return EGG_OK;
+    const char *names[] = {getenv("EGG_NCCL_LIB"), "libnccl.so.2", "libnccl.so"};
+    for (const char *n : names) {
+        if (!n) continue;
+        g_nccl.h = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (g_nccl.h) break;
+    }
+    if (!g_nccl.h) { set_error("cannot load NCCL (set EGG_NCCL_LIB): %s", dlerror()); return EGG_E_NCCL; }
+    *(void **)&g_nccl.GetUniqueId = dlsym(g_nccl.h, "ncclGetUniqueId");
+    *(void **)&g_nccl.CommInitRank = dlsym(g_nccl.h, "ncclCommInitRank");
+    *(void **)&g_nccl.AllGather = dlsym(g_nccl.h, "ncclAllGather");
+    *(void **)&g_nccl.CommDestroy = dlsym(g_nccl.h, "ncclCommDestroy");
+    *(void **)&g_nccl.GetErrorString = dlsym(g_nccl.h, "ncclGetErrorString");
+    if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllGather || !g_nccl.CommDestroy) {
+        set_error("NCCL library lacks required symbols");
+        return EGG_E_NCCL;
+    }
+    return EGG_OK;
+}
+
+}  // namespace egg
+
+using namespace egg;
+
+struct ShadowOff { int64_t init_up, init_dn, emb, layer0, layer_stride, qkv, o, up, dn; };
+
+struct egg_ctx {
+    egg_config cfg;
+    int device = 0, num_sms = 0;
+    cudaStream_t stream = nullptr;
+    ModelLayout L;
+    int64_t model_bytes = 0, opt_bytes = 0;
+    int8_t *d_model = nullptr;
+    uint8_t *d_opt = nullptr;
+    int8_t *d_shadow = nullptr;
+    ShadowOff so;
+    std::vector<ParamDesc> params;
+    bool have_model = false;
+    // tables
+    int32_t *d_exp_lut = nullptr, *d_rope_lut = nullptr;
+    int8_t *d_act_lut = nullptr;
+    // dataset
+    uint8_t *d_data = nullptr;
+    int64_t data_len = 0, data_cap = 0;
+    // population buffers
+    int32_t *d_loss = nullptr, *d_fit = nullptr;
+    // wave scratch
+    int wave_members = 0;
+    int64_t R = 0;
+    int8_t *d_x = nullptr, *d_h = nullptr, *d_u = nullptr, *d_q = nullptr, *d_k = nullptr, *d_v = nullptr, *d_ao = nullptr;
+    int32_t *d_pre = nullptr, *d_xb = nullptr, *d_xb2 = nullptr, *d_rowmax = nullptr, *d_rowmax3 = nullptr, *d_xbo = nullptr,
+            *d_wave_loss = nullptr;
+    // noise
+    NoiseMap nmap;
+    NoiseSeg *d_segs = nullptr;
+    int nsegs = 0;
+    int8_t *d_nt = nullptr;
+    // update scratch
+    int8_t *d_na = nullptr, *d_nb = nullptr;
+    int kp = 0;
+    MuonWs muon = {nullptr, nullptr, nullptr, nullptr};
+    unsigned long long *d_updates = nullptr;
+    int *d_err = nullptr;
+    // multi-GPU
+    ncclComm_t comm = nullptr;
+    int rank = 0, world = 1;
+};
+
+// ---------------------------------------------------------------- config
+
+extern "C" void egg_config_defaults(egg_config *c) {
+    memset(c, 0, sizeof(*c));
+    c->hidden_dim = 256; c->head_dim = 64; c->n_layers = 4; c->seq_len = 32; c->vocab_size = 256;
+    c->population_size = 8192 * 2 * 4;
+    c->fixed_point = 4; c->sigma_shift = 3; c->sigma_shift_vector = 4;
+    c->shift_attn = 8; c->shift_out = 9; c->shift_logit = 8; c->shift_mlp_up = 8; c->shift_mlp_down = 10;
+    c->softmax_scale_bit = 18; c->rope_scale_bit = 20;
+    c->device_mask = 15; c->device_gaussian = 0; c->host_mask = 15;
+    c->use_same_data = 0; c->use_muon = 0; c->chunk_relative_loss = 0;
+    c->softmax_exp_scale = 6.0;
+    c->adam_beta1 = 0.9f; c->adam_beta2 = 0.95f; c->adam_eps = 1e-8f; c->adam_weight_decay = 0.01f;
+    c->muon_momentum = 0.85f; c->muon_lr_scale = 1.0f;
+}
+
+extern "C" int egg_config_validate(const egg_config *c, const char **why) {
+    const char *w = nullptr;
+    if (c->hidden_dim < 128 || c->hidden_dim > 1024 || c->hidden_dim % 128) w = "hidden_dim must be a multiple of 128 in [128,1024]";
+    else if (c->head_dim != 64) w = "head_dim must be 64";
+    else if (c->n_layers < 1 || c->n_layers > 64) w = "n_layers out of range";
+    else if (c->seq_len < 16 || c->seq_len % 16 || c->seq_len > 4096) w = "seq_len must be a multiple of 16 in [16,4096]";
+    else if (c->vocab_size != 256) w = "vocab_size must be 256 (byte tokens)";
+    else if (c->population_size < 2 || c->population_size % 2) w = "population_size must be even";
+    else if (c->device_mask < 0 || c->device_mask > 15) w = "device_mask must be in [0,15]";
+    else if (c->softmax_scale_bit < 1 || c->softmax_scale_bit > 20) w = "softmax_scale_bit must be in [1,20] (three 7-bit weight limbs)";
+    else if (c->rope_scale_bit < 1 || c->rope_scale_bit > 30) w = "rope_scale_bit out of range";
+    else if (c->fixed_point < 0 || c->fixed_point > 7) w = "fixed_point out of range";
+    else if (c->sigma_shift_vector < 0 || c->sigma_shift_vector > 16 || c->sigma_shift < 0 || c->sigma_shift > 16) w = "sigma shifts out of range";
+    if (why) *why = w ? w : "";
+    if (w) { set_error("invalid configuration: %s", w); return EGG_E_INVALID; }
+    return EGG_OK;
+}
+
+extern "C" int64_t egg_model_bytes(const egg_config *c) { return model_layout(*c).total; }
+
+static void build_params(const egg_config &c, const ModelLayout &L, const ShadowOff &so, std::vector<ParamDesc> &out, int64_t *opt_total) {
+    // optimiser-state offsets follow the field order of AdamModel (mgpu.cu:337-370)
+    const int64_t H = c.hidden_dim, V = c.vocab_size, NL = c.n_layers;
+    struct F { int64_t off, n; int hidden; };
+    F fields[] = {{L.embedding, V * H, 0}, {L.emb_bias, H, 0}, {L.ln_init, H, 0}, {L.ln_init_bias, H, 0},
+                  {L.w_emb_mlp_up, 4 * H * H, 1}, {L.mlp_emb_bias_up, 4 * H, 0}, {L.w_emb_mlp_down, 4 * H * H, 1},
+                  {L.mlp_emb_bias_down, H, 0}, {L.ln_1, NL * H, 0}, {L.ln_1_bias, NL * H, 0}, {L.w_q, NL * H * H, 1},
+                  {L.w_k, NL * H * H, 1}, {L.w_v, NL * H * H, 1}, {L.w_o, NL * H * H, 1}, {L.ln_2, NL * H, 0},
+                  {L.ln_2_bias, NL * H, 0}, {L.w_up, NL * 4 * H * H, 1}, {L.mlp_bias_up, NL * 4 * H, 0},
+                  {L.w_down, NL * 4 * H * H, 1}, {L.mlp_bias_down, NL * H, 0}, {L.ln_f, H, 0}, {L.ln_f_bias, H, 0}};
+    const int nf = sizeof(fields) / sizeof(fields[0]);
+    std::vector<int64_t> fopt(nf);
+    int64_t bytes = 0;
+    for (int i = 0; i < nf; i++) { fopt[i] = bytes; bytes += fields[i].n * ((fields[i].hidden && c.use_muon) ? 8 : 12); }
+    if (opt_total) *opt_total = bytes;
+    auto opt_of = [&](int64_t model_off, int *esz) {
+        for (int i = nf - 1; i >= 0; i--)
+            if (fields[i].off <= model_off) {
+                int e = (fields[i].hidden && c.use_muon) ? 8 : 12;
+                if (esz) *esz = e;
+                return fopt[i] + (model_off - fields[i].off) * e;
+            }
+        return (int64_t)-1;
+    };
+    auto mat = [&](int64_t off, int rows, int cols, int a, int b, int base, int hidden, int64_t shadow) {
+        ParamDesc d; d.model_off = off; d.opt_off = opt_of(off, nullptr); d.rows_k = rows; d.cols_n = cols; d.off_a = a; d.off_b = b;
+        d.seed_base = base; d.lr_scale = 1.0f; d.muon = hidden && c.use_muon; d.shadow_off = shadow; out.push_back(d);
+    };
+    auto vec = [&](int64_t off, int len, int a, int b, int base, float sc) {
+        ParamDesc d; d.model_off = off; d.opt_off = opt_of(off, nullptr); d.rows_k = 0; d.cols_n = len; d.off_a = a; d.off_b = b;
+        d.seed_base = base; d.lr_scale = sc; d.muon = 0; d.shadow_off = -1; out.push_back(d);
+    };
+    const int h = (int)H;
+    for (int l = 0; l < c.n_layers; l++) {     // mgpu.cu:1603-1621
+        int sb = l * 1000;
+        int64_t hh = H * H, sl = so.layer0 + l * so.layer_stride;
+        mat(L.w_q + l * hh, h, h, 200, 201, sb, 1, sl + so.qkv);
+        mat(L.w_k + l * hh, h, h, 202, 203, sb, 1, sl + so.qkv + hh);
+        mat(L.w_v + l * hh, h, h, 204, 205, sb, 1, sl + so.qkv + 2 * hh);
+        mat(L.w_o + l * hh, h, h, 206, 207, sb, 1, sl + so.o);
+        mat(L.w_up + l * 4 * hh, h, 4 * h, 400, 401, sb, 1, sl + so.up);
+        mat(L.w_down + l * 4 * hh, 4 * h, h, 402, 403, sb, 1, sl + so.dn);
+        vec(L.ln_1 + l * H, h, 100, 101, sb, 1.0f);
+        vec(L.ln_1_bias + l * H, h, 110, 111, sb, 1.0f);
+        vec(L.ln_2 + l * H, h, 300, 301, sb, 1.0f);
+        vec(L.ln_2_bias + l * H, h, 310, 311, sb, 1.0f);
+        vec(L.mlp_bias_up + l * 4 * H, 4 * h, 410, 411, sb, 1.0f);
+        vec(L.mlp_bias_down + l * H, h, 412, 413, sb, 1.0f);
+    }
+    vec(L.ln_f, h, 900, 901, 0, 1.0f);             // mgpu.cu:1623-1643
+    vec(L.ln_f_bias, h, 910, 911, 0, 1.0f);
+    vec(L.ln_init, h, 500, 501, 0, 1.0f);
+    vec(L.ln_init_bias, h, 502, 503, 0, 1.0f);
+    mat(L.w_emb_mlp_up, h, 4 * h, 510, 511, 0, 1, so.init_up);
+    vec(L.mlp_emb_bias_up, 4 * h, 514, 515, 0, 1.0f);
+    mat(L.w_emb_mlp_down, 4 * h, h, 512, 513, 0, 1, so.init_dn);
+    vec(L.mlp_emb_bias_down, h, 516, 517, 0, 1.0f);
+    vec(L.emb_bias, h, 50, 51, 0, 0.1f);
+    mat(L.embedding, h, (int)V, 0, 0 + h, 0, 0, so.emb);
+}
+
+static ShadowOff shadow_offsets(const egg_config &c, int64_t *total) {
+    const int64_t H = c.hidden_dim, V = c.vocab_size;
+    ShadowOff s; int64_t o = 0;
+    s.init_up = o; o += 4 * H * H;
+    s.init_dn = o; o += 4 * H * H;
+    s.emb = o; o += V * H;
+    s.layer0 = o;
+    s.qkv = 0; s.o = 3 * H * H; s.up = 4 * H * H; s.dn = 8 * H * H; s.layer_stride = 12 * H * H;
+    o += c.n_layers * s.layer_stride;
+    if (total) *total = o;
+    return s;
+}
+
+extern "C" int64_t egg_opt_state_bytes(const egg_config *c) {
+    ModelLayout L = model_layout(*c);
+    ShadowOff so = shadow_offsets(*c, nullptr);
+    std::vector<ParamDesc> p; int64_t total = 0;
+    build_params(*c, L, so, p, &total);
+    return total;
+}
+
+extern "C" const char *egg_last_error(void) { return g_err; }
+
+// ---------------------------------------------------------------- tables (init_tables, mgpu.cu:394-426)
+static void host_tables(const egg_config &c, std::vector<int32_t> &exp_lut, std::vector<int8_t> &act_lut, std::vector<int32_t> &rope) {
+    exp_lut.resize(256); act_lut.resize(256); rope.resize((size_t)c.seq_len * c.head_dim);
+    const double softmax_scale = (double)(1 << c.softmax_scale_bit);
+    for (int i = 0; i < 256; i++) {
+        double val = exp(-(double)i / c.softmax_exp_scale) * softmax_scale;
+        exp_lut[i] = (val >= 1.0) ? (int32_t)round(val) : 0;
+    }
+    for (int i = 0; i < 256; i++) {
+        int8_t input = (int8_t)i;
+        double x = (double)input / (1 << c.fixed_point);
+        double y = 0.5 * x * (1.0 + erf(x / 1.41421356));
+        int val = (int)round(y * (1 << c.fixed_point));
+        act_lut[i] = (int8_t)((val > 127) ? 127 : ((val < -127) ? -127 : val));
+    }
+    const double rope_scale = (double)(1 << c.rope_scale_bit);
+    for (int t = 0; t < c.seq_len; t++)
+        for (int i = 0; i < c.head_dim / 2; i++) {
+            double theta = pow(10000.0, -2.0 * i / c.head_dim);
+            double alpha = t * theta;
+            rope[(size_t)t * c.head_dim + 2 * i] = (int32_t)round(cos(alpha) * rope_scale);
+            rope[(size_t)t * c.head_dim + 2 * i + 1] = (int32_t)round(sin(alpha) * rope_scale);
+        }
+}
+
+// ---------------------------------------------------------------- context
+
+template <typename T>
+static int dev_alloc(T **p, int64_t count) {
+    cudaError_t e = cudaMalloc((void **)p, (size_t)(count > 0 ? count : 1) * sizeof(T));
+    if (e != cudaSuccess) { set_error("cudaMalloc of %lld bytes failed: %s", (long long)(count * (int64_t)sizeof(T)), cudaGetErrorString(e)); *p = nullptr; return EGG_E_NOMEM; }
+    return EGG_OK;
+}
+
+extern "C" void egg_ctx_destroy(egg_ctx *c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
+    void *ptrs[] = {c->d_model, c->d_opt, c->d_shadow, c->d_exp_lut, c->d_rope_lut, c->d_act_lut, c->d_data, c->d_loss, c->d_fit,
+                    c->d_x, c->d_h, c->d_u, c->d_q, c->d_k, c->d_v, c->d_ao, c->d_pre, c->d_xb, c->d_xb2, c->d_rowmax,
+                    c->d_rowmax3, c->d_xbo, c->d_wave_loss, c->d_segs, c->d_nt, c->d_na, c->d_nb, c->muon.x, c->muon.g,
+                    c->muon.y, c->muon.norm2, c->d_updates, c->d_err};
+    for (void *p : ptrs) if (p) cudaFree(p);
+    if (c->stream) cudaStreamDestroy(c->stream);
+    delete c;
+}
+
+extern "C" int egg_ctx_create(const egg_config *cfg, int device, int wave_members, egg_ctx **out) {
+    if (!cfg || !out) { set_error("null argument"); return EGG_E_INVALID; }
+    *out = nullptr;
+    int rc = egg_config_validate(cfg, nullptr);
+    if (rc) return rc;
+    int ndev = 0;
+    EGG_CUDA(cudaGetDeviceCount(&ndev));
+    if (device < 0 || device >= ndev) { set_error("device %d not present (%d devices)", device, ndev); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    EGG_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) { set_error("this library is built for sm_100a only (device is sm_%d%d)", prop.major, prop.minor); return EGG_E_INVALID; }
+    if ((rc = gemm_init())) return rc;
+
+    egg_ctx *c = new egg_ctx();
+    c->cfg = *cfg; c->device = device; c->num_sms = prop.multiProcessorCount;
+    c->L = model_layout(*cfg);
+    c->model_bytes = c->L.total;
+    int64_t shadow_total = 0;
+    c->so = shadow_offsets(*cfg, &shadow_total);
+    build_params(*cfg, c->L, c->so, c->params, &c->opt_bytes);
+#define TRY(x) do { rc = (x); if (rc) { egg_ctx_destroy(c); return rc; } } while (0)
+#define TRYC(x) do { cudaError_t e_ = (x); if (e_ != cudaSuccess) { set_error("%s: %s", #x, cudaGetErrorString(e_)); egg_ctx_destroy(c); return EGG_E_CUDA; } } while (0)
+    TRYC(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    const int64_t H = cfg->hidden_dim, S = cfg->seq_len, POP = cfg->population_size;
+    TRY(dev_alloc(&c->d_model, c->model_bytes));
+    TRY(dev_alloc(&c->d_opt, c->opt_bytes));
+    TRY(dev_alloc(&c->d_shadow, shadow_total));
+    TRYC(cudaMemset(c->d_opt, 0, (size_t)c->opt_bytes));
+    TRY(dev_alloc(&c->d_exp_lut, 256)); TRY(dev_alloc(&c->d_act_lut, 256)); TRY(dev_alloc(&c->d_rope_lut, S * cfg->head_dim));
+    {
+        std::vector<int32_t> e, r; std::vector<int8_t> a;
+        host_tables(*cfg, e, a, r);
+        TRYC(cudaMemcpy(c->d_exp_lut, e.data(), 256 * 4, cudaMemcpyHostToDevice));
+        TRYC(cudaMemcpy(c->d_act_lut, a.data(), 256, cudaMemcpyHostToDevice));
+        TRYC(cudaMemcpy(c->d_rope_lut, r.data(), r.size() * 4, cudaMemcpyHostToDevice));
+    }
+    TRY(dev_alloc(&c->d_loss, POP)); TRY(dev_alloc(&c->d_fit, POP / 2));
+    TRYC(cudaMemset(c->d_loss, 0, (size_t)POP * 4)); TRYC(cudaMemset(c->d_fit, 0, (size_t)(POP / 2) * 4));
+    TRY(dev_alloc(&c->d_updates, 1)); TRY(dev_alloc(&c->d_err, 2));
+    TRYC(cudaMemset(c->d_err, 0, 8));
+
+    // noise map
+    std::vector<NoiseSeg> segs(32 + 32 * cfg->n_layers);
+    build_noise_map(*cfg, &c->nmap, segs.data(), &c->nsegs, (int)segs.size());
+    TRY(dev_alloc(&c->d_segs, c->nsegs));
+    TRYC(cudaMemcpy(c->d_segs, segs.data(), c->nsegs * sizeof(NoiseSeg), cudaMemcpyHostToDevice));
+
+    // wave scratch: 23 H bytes + 36 bytes per row, noise table per pair
+    const int64_t per_member = S * (23 * H + 40) + c->nmap.stride / 2 + 8;
+    if (wave_members <= 0) {
+        size_t free_b = 0, total_b = 0;
+        TRYC(cudaMemGetInfo(&free_b, &total_b));
+        int64_t budget = (int64_t)(free_b / 3);
+        if (budget > (24ll << 30)) budget = 24ll << 30;
+        int64_t wm = budget / per_member;
+        wave_members = (int)(wm > 4096 ? 4096 : wm);
+    }
+    if (wave_members > POP) wave_members = (int)POP;
+    wave_members &= ~1;
+    // keep rows a multiple of the GEMM tile where possible
+    while (wave_members > 2 && (wave_members * S) % 128) wave_members -= 2;
+    if (wave_members < 2) wave_members = 2;
+    c->wave_members = wave_members;
+    const int64_t R = (int64_t)wave_members * S;
+    c->R = R;
+    TRY(dev_alloc(&c->d_x, R * H)); TRY(dev_alloc(&c->d_h, R * H)); TRY(dev_alloc(&c->d_u, R * 4 * H));
+    TRY(dev_alloc(&c->d_q, R * H)); TRY(dev_alloc(&c->d_k, R * H)); TRY(dev_alloc(&c->d_v, R * H)); TRY(dev_alloc(&c->d_ao, R * H));
+    TRY(dev_alloc(&c->d_pre, R * 3 * H));
+    TRY(dev_alloc(&c->d_xb, R * 3)); TRY(dev_alloc(&c->d_xb2, R)); TRY(dev_alloc(&c->d_rowmax, R)); TRY(dev_alloc(&c->d_rowmax3, R * 3));
+    TRY(dev_alloc(&c->d_xbo, R)); TRY(dev_alloc(&c->d_wave_loss, wave_members));
+    TRY(dev_alloc(&c->d_nt, (int64_t)(wave_members / 2) * c->nmap.stride));
+
+    // update scratch
+    c->kp = (int)(((POP / 2) + 127) / 128 * 128);
+    TRY(dev_alloc(&c->d_na, 4 * H * (int64_t)c->kp)); TRY(dev_alloc(&c->d_nb, 4 * H * (int64_t)c->kp));
+    if (cfg->use_muon) {
+        TRY(dev_alloc(&c->muon.x, 4 * H * H)); TRY(dev_alloc(&c->muon.y, 4 * H * H)); TRY(dev_alloc(&c->muon.g, H * H));
+        TRY(dev_alloc(&c->muon.norm2, 1));
+    }
+#undef TRY
+#undef TRYC
+    *out = c;
+    return EGG_OK;
+}
+
+static int check_dev_err(egg_ctx *c) {
+    int h[2] = {0, 0};
+    EGG_CUDA(cudaMemcpy(h, c->d_err, 8, cudaMemcpyDeviceToHost));
+    if (h[0]) {
+        set_error("a device-side wait timed out (code %d)", h[0]);
+        cudaMemset(c->d_err, 0, 8);
+        return EGG_E_TIMEOUT;
+    }
+    return EGG_OK;
+}
+
+extern "C" int egg_sync(egg_ctx *c) {
+    if (!c) { set_error("null context"); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    EGG_CUDA(cudaStreamSynchronize(c->stream));
+    return check_dev_err(c);
+}
+
+// ---------------------------------------------------------------- uploads
+
+static int refresh_shadows(egg_ctx *c) {
+    for (const ParamDesc &d : c->params) {
+        if (d.rows_k == 0) continue;
+        int rc = launch_unpack_transpose(c->stream, c->d_model + d.model_off, c->d_shadow + d.shadow_off, d.rows_k, d.cols_n);
+        if (rc) return rc;
+    }
+    return EGG_OK;
+}
+
+extern "C" int egg_upload_model(egg_ctx *c, const void *host_model, int64_t nbytes) {
+    if (!c || !host_model) { set_error("null argument"); return EGG_E_INVALID; }
+    if (nbytes != c->model_bytes) { set_error("model is %lld bytes, this configuration needs %lld", (long long)nbytes, (long long)c->model_bytes); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    EGG_CUDA(cudaMemcpyAsync(c->d_model, host_model, (size_t)nbytes, cudaMemcpyHostToDevice, c->stream));
+    int rc = refresh_shadows(c);
+    if (rc) return rc;
+    EGG_CUDA(cudaStreamSynchronize(c->stream));
+    c->have_model = true;
+    return EGG_OK;
+}
+
+extern "C" int egg_download_model(egg_ctx *c, void *host_model, int64_t nbytes) {
+    if (!c || !host_model) { set_error("null argument"); return EGG_E_INVALID; }
+    if (nbytes != c->model_bytes) { set_error("model is %lld bytes", (long long)c->model_bytes); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    EGG_CUDA(cudaMemcpyAsync(host_model, c->d_model, (size_t)nbytes, cudaMemcpyDeviceToHost, c->stream));
+    EGG_CUDA(cudaStreamSynchronize(c->stream));
+    return EGG_OK;
+}
+
+extern "C" int egg_upload_opt_state(egg_ctx *c, const void *host_state, int64_t nbytes) {
+    if (!c || !host_state) { set_error("null argument"); return EGG_E_INVALID; }
+    if (nbytes != c->opt_bytes) { set_error("optimiser state is %lld bytes, expected %lld", (long long)nbytes, (long long)c->opt_bytes); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    EGG_CUDA(cudaMemcpyAsync(c->d_opt, host_state, (size_t)nbytes, cudaMemcpyHostToDevice, c->stream));
+    EGG_CUDA(cudaStreamSynchronize(c->stream));
+    return EGG_OK;
+}
+
+extern "C" int egg_download_opt_state(egg_ctx *c, void *host_state, int64_t nbytes) {
+    if (!c || !host_state) { set_error("null argument"); return EGG_E_INVALID; }
+    if (nbytes != c->opt_bytes) { set_error("optimiser state is %lld bytes", (long long)c->opt_bytes); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    EGG_CUDA(cudaMemcpyAsync(host_state, c->d_opt, (size_t)nbytes, cudaMemcpyDeviceToHost, c->stream));
+    EGG_CUDA(cudaStreamSynchronize(c->stream));
+    return EGG_OK;
+}
+
+static int set_dataset_async(egg_ctx *c, const uint8_t *host_tokens, int64_t n) {
+    if (n <= c->cfg.seq_len + 1) { set_error("dataset must be longer than seq_len+1"); return EGG_E_INVALID; }
+    if (n > c->data_cap) {
+        if (c->d_data) { EGG_CUDA(cudaStreamSynchronize(c->stream)); cudaFree(c->d_data); c->d_data = nullptr; }
+        int rc = dev_alloc(&c->d_data, n);
+        if (rc) return rc;
+        c->data_cap = n;
+    }
+    EGG_CUDA(cudaMemcpyAsync(c->d_data, host_tokens, (size_t)n, cudaMemcpyHostToDevice, c->stream));
+    c->data_len = n;
+    return EGG_OK;
+}
+
+extern "C" int egg_set_dataset(egg_ctx *c, const uint8_t *host_tokens, int64_t n_tokens) {
+    if (!c || !host_tokens) { set_error("null argument"); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    int rc = set_dataset_async(c, host_tokens, n_tokens);
+    if (rc) return rc;
+    EGG_CUDA(cudaStreamSynchronize(c->stream));
+    return EGG_OK;
+}
+
+// ---------------------------------------------------------------- evaluation
+
+static GemmParams base_gemm(egg_ctx *c, int M, int N, int K) {
+    GemmParams g;
+    memset(&g, 0, sizeof(g));
+    g.M = M; g.N = N; g.K = K;
+    g.seq_len = c->cfg.seq_len;
+    g.nt = c->d_nt; g.nt_stride = c->nmap.stride;
+    g.nt_c_off = -1;
+    g.rank1_shift = c->cfg.fixed_point + c->cfg.sigma_shift;
+    g.act_lut = c->d_act_lut; g.exp_lut = c->d_exp_lut; g.rope_lut = c->d_rope_lut;
+    g.head_dim = c->cfg.head_dim; g.rope_bit = c->cfg.rope_scale_bit;
+    g.err = c->d_err;
+    return g;
+}
+
+// norm + up + down of one MLP block (compute_mlp, mgpu.cu:708-759); X, Hn, xb[.,0] are ready on entry
+static int run_mlp(egg_ctx *c, int M, const MlpOff &mo, int nt_base, const int8_t *up_t, const int8_t *up_bias, const int8_t *dn_t,
+                   const int8_t *dn_bias) {
+    const int H = c->cfg.hidden_dim;
+    GemmParams g = base_gemm(c, M, 4 * H, H);
+    g.nt_a_off = nt_base + mo.up_a; g.nt_c_off = nt_base + mo.bup_d; g.nt_d_off = nt_base + mo.dn_b;
+    g.xb = c->d_xb; g.xb_stride = 3; g.out_shift = c->cfg.shift_mlp_up; g.bias = up_bias; g.out8 = c->d_u; g.rowstat = c->d_xb2;
+    int rc = launch_gemm(c->stream, EPI_GELU, c->d_h, up_t, g, c->num_sms);
+    if (rc) return rc;
+    GemmParams d = base_gemm(c, M, H, 4 * H);
+    d.nt_a_off = nt_base + mo.dn_a; d.nt_c_off = nt_base + mo.bdn_d;
+    d.xb = c->d_xb2; d.xb_stride = 1; d.out_shift = c->cfg.shift_mlp_down; d.bias = dn_bias; d.resid = c->d_x; d.out32 = c->d_pre;
+    d.rowstat = c->d_rowmax;
+    return launch_gemm(c->stream, EPI_PRE32, c->d_u, dn_t, d, c->num_sms);
+}
+
+static RowParams base_row(egg_ctx *c, int M) {
+    RowParams r;
+    memset(&r, 0, sizeof(r));
+    r.M = M; r.H = c->cfg.hidden_dim; r.seq_len = c->cfg.seq_len;
+    r.nt = c->d_nt; r.nt_stride = c->nmap.stride;
+    r.pre32 = c->d_pre; r.rowmax = c->d_rowmax;
+    r.x_out = c->d_x; r.h_out = c->d_h;
+    r.xb_out = c->d_xb; r.xb_stride = 3;
+    r.zero1 = c->d_xb2; r.zero2 = c->d_xbo; r.zero3 = c->d_rowmax3;
+    return r;
+}
+
+static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_base, int members, int32_t *loss_dst) {
+    const egg_config &cf = c->cfg;
+    const int H = cf.hidden_dim, S = cf.seq_len, V = cf.vocab_size;
+    const int M = members * S;
+    const ModelLayout &L = c->L;
+    const NoiseMap &nm = c->nmap;
+    const int8_t *mdl = c->d_model, *sh = c->d_shadow;
+    cudaStream_t st = c->stream;
+    int rc;
+    if ((rc = launch_noise_fill(st, c->d_nt, nm.stride, c->d_segs, c->nsegs, members / 2, step_seed, pop_base / 2, cf.device_mask, cf.device_gaussian))) return rc;
+    EGG_CUDA(cudaMemsetAsync(c->d_wave_loss, 0, (size_t)members * 4, st));
+    EGG_CUDA(cudaMemsetAsync(c->d_rowmax, 0, (size_t)M * 4, st));
+    const int64_t data_stride = c->data_len / (cf.population_size / 2);
+
+    // embedding + initial norm (mgpu.cu:902-934)
+    RowParams r0 = base_row(c, M);
+    r0.dataset = c->d_data; r0.data_len = c->data_len; r0.start_idx = start_idx; r0.data_stride = data_stride;
+    r0.pop_base = pop_base; r0.use_same_data = cf.use_same_data;
+    r0.emb_packed = mdl + L.embedding; r0.emb_bias = mdl + L.emb_bias; r0.vocab = V;
+    r0.nt_emb_a = nm.emb_a; r0.nt_emb_b = nm.emb_b; r0.nt_emb_bias_d = nm.emb_bias_d; r0.emb_shift = cf.fixed_point + cf.sigma_shift;
+    r0.ln_w = mdl + L.ln_init; r0.ln_b = mdl + L.ln_init_bias; r0.nt_w_d = nm.ln_init.w_d; r0.nt_b_d = nm.ln_init.b_d;
+    r0.ndots = 1; r0.nt_dot[0] = nm.mlp_init.up_b;
+    if ((rc = launch_rowwise(st, r0, 0))) return rc;
+    if ((rc = run_mlp(c, M, nm.mlp_init, 0, sh + c->so.init_up, mdl + L.mlp_emb_bias_up, sh + c->so.init_dn, mdl + L.mlp_emb_bias_down))) return rc;
+
+    for (int l = 0; l < cf.n_layers; l++) {
+        const int nb = nm.layer0 + l * nm.layer_stride;
+        const LayerOff &lo = nm.layer_rel;
+        const int8_t *shl = sh + c->so.layer0 + (int64_t)l * c->so.layer_stride;
+        // ALN of the previous block -> x ; LN1 -> h ; Σ h·b for q,k,v (mgpu.cu:770-776)
+        RowParams ra = base_row(c, M);
+        ra.ln_w = mdl + L.ln_1 + (int64_t)l * H; ra.ln_b = mdl + L.ln_1_bias + (int64_t)l * H;
+        ra.nt_w_d = nb + lo.ln1.w_d; ra.nt_b_d = nb + lo.ln1.b_d;
+        ra.ndots = 3; ra.nt_dot[0] = nb + lo.qkv_b; ra.nt_dot[1] = nb + lo.qkv_b + H; ra.nt_dot[2] = nb + lo.qkv_b + 2 * H;
+        if ((rc = launch_rowwise(st, ra, 1))) return rc;
+        // fused Q|K|V projection + RoPE (mgpu.cu:779-784)
+        GemmParams gq = base_gemm(c, M, 3 * H, H);
+        gq.nt_a_off = nb + lo.qkv_a; gq.xb = c->d_xb; gq.xb_stride = 3; gq.out32 = c->d_pre; gq.rowstat = c->d_rowmax3; gq.third = H;
+        if ((rc = launch_gemm(st, EPI_QKV, c->d_h, shl + c->so.qkv, gq, c->num_sms))) return rc;
+        AqnParams aq; aq.M = M; aq.H = H; aq.pre3 = c->d_pre; aq.rowmax3 = c->d_rowmax3; aq.q = c->d_q; aq.k = c->d_k; aq.v = c->d_v;
+        if ((rc = launch_aqn(st, aq))) return rc;
+        AttnParams ap; ap.members = members; ap.H = H; ap.head_dim = cf.head_dim; ap.seq_len = S; ap.shift_attn = cf.shift_attn;
+        ap.q = c->d_q; ap.k = c->d_k; ap.v = c->d_v; ap.ao = c->d_ao; ap.exp_lut = c->d_exp_lut; ap.nt = c->d_nt;
+        ap.nt_stride = nm.stride; ap.nt_o_b = nb + lo.o_b; ap.xbo = c->d_xbo;
+        if ((rc = launch_attention(st, ap))) return rc;
+        // output projection + residual (mgpu.cu:828-830)
+        GemmParams go = base_gemm(c, M, H, H);
+        go.nt_a_off = nb + lo.o_a; go.xb = c->d_xbo; go.xb_stride = 1; go.out_shift = cf.shift_out; go.resid = c->d_x;
+        go.out32 = c->d_pre; go.rowstat = c->d_rowmax;
+        if ((rc = launch_gemm(st, EPI_PRE32, c->d_ao, shl + c->so.o, go, c->num_sms))) return rc;
+        // ALN -> x ; LN2 -> h ; Σ h·b_up
+        RowParams rb = base_row(c, M);
+        rb.ln_w = mdl + L.ln_2 + (int64_t)l * H; rb.ln_b = mdl + L.ln_2_bias + (int64_t)l * H;
+        rb.nt_w_d = nb + lo.ln2.w_d; rb.nt_b_d = nb + lo.ln2.b_d;
+        rb.ndots = 1; rb.nt_dot[0] = nb + lo.mlp.up_b;
+        if ((rc = launch_rowwise(st, rb, 1))) return rc;
+        if ((rc = run_mlp(c, M, lo.mlp, nb, shl + c->so.up, mdl + L.mlp_bias_up + (int64_t)l * 4 * H, shl + c->so.dn,
+                          mdl + L.mlp_bias_down + (int64_t)l * H))) return rc;
+    }
+    // final norm + tied-embedding head + cross-entropy (mgpu.cu:954-1024)
+    RowParams rf = base_row(c, M);
+    rf.ln_w = mdl + L.ln_f; rf.ln_b = mdl + L.ln_f_bias; rf.nt_w_d = nm.ln_f.w_d; rf.nt_b_d = nm.ln_f.b_d;
+    rf.ndots = 1; rf.nt_dot[0] = nm.emb_b;
+    if ((rc = launch_rowwise(st, rf, 1))) return rc;
+    GemmParams gh = base_gemm(c, M, V, H);
+    gh.nt_a_off = nm.emb_a; gh.xb = c->d_xb; gh.xb_stride = 3; gh.out_shift = cf.shift_logit;
+    gh.dataset = c->d_data; gh.data_len = c->data_len; gh.start_idx = start_idx; gh.data_stride = data_stride; gh.pop_base = pop_base;
+    gh.use_same_data = cf.use_same_data; gh.softmax_scale_bit = cf.softmax_scale_bit; gh.loss = c->d_wave_loss;
+    if ((rc = launch_gemm(st, EPI_HEAD, c->d_h, sh + c->so.emb, gh, c->num_sms))) return rc;
+    EGG_CUDA(cudaMemcpyAsync(loss_dst, c->d_wave_loss, (size_t)members * 4, cudaMemcpyDeviceToDevice, st));
+    return EGG_OK;
+}
+
+extern "C" int egg_eval_chunk(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_offset, int count) {
+    if (!c) { set_error("null context"); return EGG_E_INVALID; }
+    if (!c->have_model || !c->d_data) { set_error("upload a model and a dataset first"); return EGG_E_STATE; }
+    if (pop_offset < 0 || count <= 0 || (pop_offset & 1) || (count & 1) || pop_offset + count > c->cfg.population_size) {
+        set_error("population range [%d,%d) must be pair-aligned and inside the population", pop_offset, pop_offset + count);
+        return EGG_E_INVALID;
+    }
+    EGG_CUDA(cudaSetDevice(c->device));
+    for (int off = 0; off < count; off += c->wave_members) {
+        int members = count - off < c->wave_members ? count - off : c->wave_members;
+        int32_t *dst = c->d_loss + (c->cfg.chunk_relative_loss ? off : pop_offset + off);
+        int rc = eval_wave(c, step_seed, start_idx, pop_offset + off, members, dst);
+        if (rc) return rc;
+    }
+    return EGG_OK;
+}
+
+extern "C" int egg_read_losses(egg_ctx *c, int32_t *host_losses, int offset, int count) {
+    if (!c || !host_losses || offset < 0 || count < 0 || offset + count > c->cfg.population_size) { set_error("bad loss range"); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    EGG_CUDA(cudaMemcpyAsync(host_losses, c->d_loss + offset, (size_t)count * 4, cudaMemcpyDeviceToHost, c->stream));
+    EGG_CUDA(cudaStreamSynchronize(c->stream));
+    return check_dev_err(c);
+}
+
+extern "C" int egg_compute_fitness_pairs(egg_ctx *c, int pair_offset, int pair_count) {
+    if (!c || pair_offset < 0 || pair_count <= 0 || pair_offset + pair_count > c->cfg.population_size / 2) { set_error("bad pair range"); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    return launch_fitness(c->stream, c->d_loss + 2 * (int64_t)pair_offset, c->d_fit + pair_offset, pair_count);
+}
+
+extern "C" int egg_write_fitness(egg_ctx *c, const int32_t *host_fitness, int pair_offset, int pair_count) {
+    if (!c || !host_fitness || pair_offset < 0 || pair_count < 0 || pair_offset + pair_count > c->cfg.population_size / 2) { set_error("bad pair range"); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    EGG_CUDA(cudaMemcpyAsync(c->d_fit + pair_offset, host_fitness, (size_t)pair_count * 4, cudaMemcpyHostToDevice, c->stream));
+    EGG_CUDA(cudaStreamSynchronize(c->stream));
+    return EGG_OK;
+}
+
+extern "C" int egg_read_fitness(egg_ctx *c, int32_t *host_fitness, int pair_offset, int pair_count) {
+    if (!c || !host_fitness || pair_offset < 0 || pair_count < 0 || pair_offset + pair_count > c->cfg.population_size / 2) { set_error("bad pair range"); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    EGG_CUDA(cudaMemcpyAsync(host_fitness, c->d_fit + pair_offset, (size_t)pair_count * 4, cudaMemcpyDeviceToHost, c->stream));
+    EGG_CUDA(cudaStreamSynchronize(c->stream));
+    return EGG_OK;
+}
+
+// ---------------------------------------------------------------- multi-GPU
+
+extern "C" int egg_nccl_unique_id(void *id128) {
+    int rc = nccl_load();
+    if (rc) return rc;
+    ncclUniqueId id;
+    ncclResult_t r = g_nccl.GetUniqueId(&id);
+    if (r != ncclSuccess) { set_error("ncclGetUniqueId failed (%d)", (int)r); return EGG_E_NCCL; }
+    memcpy(id128, &id, sizeof(id));
+    return EGG_OK;
+}
+
+extern "C" int egg_comm_init(egg_ctx *c, const void *id128, int rank, int world) {
+    if (!c || !id128 || world < 1 || rank < 0 || rank >= world) { set_error("bad communicator arguments"); return EGG_E_INVALID; }
+    if ((c->cfg.population_size / 2) % world) { set_error("POP/2 = %d pairs do not divide over %d ranks", c->cfg.population_size / 2, world); return EGG_E_INVALID; }
+    int rc = nccl_load();
+    if (rc) return rc;
+    EGG_CUDA(cudaSetDevice(c->device));
+    ncclUniqueId id;
+    memcpy(&id, id128, sizeof(id));
+    ncclResult_t r = g_nccl.CommInitRank(&c->comm, world, id, rank);
+    if (r != ncclSuccess) { set_error("ncclCommInitRank failed (%d)", (int)r); return EGG_E_NCCL; }
+    c->rank = rank; c->world = world;
+    return EGG_OK;
+}
+
+extern "C" int egg_allgather_fitness(egg_ctx *c) {
+    if (!c) { set_error("null context"); return EGG_E_INVALID; }
+    if (c->world == 1) return EGG_OK;
+    if (!c->comm) { set_error("no communicator attached"); return EGG_E_STATE; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    const size_t per = (size_t)(c->cfg.population_size / 2 / c->world);
+    // in place: rank r's slice already sits at d_fit + r*per
+    ncclResult_t r = g_nccl.AllGather(c->d_fit + (size_t)c->rank * per, c->d_fit, per, ncclInt32, c->comm, c->stream);
+    if (r != ncclSuccess) { set_error("ncclAllGather failed (%d)", (int)r); return EGG_E_NCCL; }
+    return EGG_OK;
+}
+
+// ---------------------------------------------------------------- update
+
+static int update_matrix(egg_ctx *c, const ParamDesc &d, uint32_t step_seed, float lr) {
+    const egg_config &cf = c->cfg;
+    const int pairs = cf.population_size / 2;
+    int rc = launch_update_operands(c->stream, c->d_na, c->d_nb, c->d_fit, pairs, c->kp, d.rows_k, d.cols_n, d.off_a, d.off_b,
+                                    d.seed_base, step_seed, cf.device_mask, cf.device_gaussian, 0);
+    if (rc) return rc;
+    GemmParams g;
+    memset(&g, 0, sizeof(g));
+    g.M = d.cols_n; g.N = d.rows_k; g.K = c->kp; g.seq_len = 1 << 20;
+    g.w_packed = c->d_model + d.model_off;
+    g.opt = reinterpret_cast<float *>(c->d_opt + d.opt_off);
+    g.lr = lr * d.lr_scale; g.beta1 = cf.adam_beta1; g.beta2 = cf.adam_beta2; g.eps = cf.adam_eps; g.wd = cf.adam_weight_decay;
+    g.mu = cf.muon_momentum; g.total_updates = c->d_updates; g.err = c->d_err;
+    if (!d.muon) return launch_gemm(c->stream, EPI_ADAM, c->d_na, c->d_nb, g, c->num_sms);
+    g.m_rowmajor = c->muon.x;
+    if ((rc = launch_gemm(c->stream, EPI_MUON_M, c->d_na, c->d_nb, g, c->num_sms))) return rc;
+    if ((rc = launch_newton_schulz(c->stream, c->muon, d.rows_k, d.cols_n))) return rc;
+    return launch_muon_apply(c->stream, c->d_model + d.model_off, reinterpret_cast<float *>(c->d_opt + d.opt_off), c->muon.x,
+                             d.rows_k, d.cols_n, lr * cf.muon_lr_scale, cf.adam_weight_decay, c->d_updates);
+}
+
+static int apply_update_async(egg_ctx *c, uint32_t step_seed, float lr) {
+    const egg_config &cf = c->cfg;
+    EGG_CUDA(cudaMemsetAsync(c->d_updates, 0, sizeof(unsigned long long), c->stream));
+    for (const ParamDesc &d : c->params) {
+        int rc;
+        if (d.rows_k) {
+            rc = update_matrix(c, d, step_seed, lr);
+        } else {
+            VecUpdParams v;
+            v.v = c->d_model + d.model_off; v.opt = reinterpret_cast<float *>(c->d_opt + d.opt_off); v.len = d.cols_n;
+            v.off_a = d.off_a; v.off_b = d.off_b; v.seed_base = d.seed_base; v.fit = c->d_fit; v.pairs = cf.population_size / 2;
+            v.step_seed = step_seed; v.lr = lr * d.lr_scale; v.beta1 = cf.adam_beta1; v.beta2 = cf.adam_beta2; v.eps = cf.adam_eps;
+            v.wd = cf.adam_weight_decay; v.mask = cf.device_mask; v.gaussian = cf.device_gaussian; v.total_updates = c->d_updates;
+            rc = launch_update_vector(c->stream, v);
+        }
+        if (rc) return rc;
+    }
+    return refresh_shadows(c);
+}
+
+extern "C" int egg_apply_update(egg_ctx *c, uint32_t step_seed, float learning_rate, uint64_t *total_updates) {
+    if (!c) { set_error("null context"); return EGG_E_INVALID; }
+    if (!c->have_model) { set_error("upload a model first"); return EGG_E_STATE; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    int rc = apply_update_async(c, step_seed, learning_rate);
+    if (rc) return rc;
+    unsigned long long u = 0;
+    EGG_CUDA(cudaMemcpyAsync(&u, c->d_updates, sizeof(u), cudaMemcpyDeviceToHost, c->stream));
+    EGG_CUDA(cudaStreamSynchronize(c->stream));
+    if (total_updates) *total_updates = u;
+    return check_dev_err(c);
+}
+
+extern "C" int egg_generation_host(egg_ctx *c, const uint8_t *host_tokens, int64_t n_tokens, int64_t step, uint32_t step_seed,
+                                   float learning_rate, int32_t *host_losses, uint64_t *total_updates) {
+    if (!c) { set_error("null context"); return EGG_E_INVALID; }
+    if (!c->have_model) { set_error("upload a model first"); return EGG_E_STATE; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    int rc;
+    if (host_tokens && (rc = set_dataset_async(c, host_tokens, n_tokens))) return rc;
+    if (!c->d_data) { set_error("no dataset"); return EGG_E_STATE; }
+    const int POP = c->cfg.population_size;
+    const int per = POP / c->world, off = c->rank * per;
+    if (per & 1) { set_error("population slice per rank must be even"); return EGG_E_INVALID; }
+    const int saved = c->cfg.chunk_relative_loss;
+    c->cfg.chunk_relative_loss = 0;                       // the fitness vector is indexed globally
+    rc = egg_eval_chunk(c, step_seed, step * c->cfg.seq_len, off, per);   // start_idx = step*SEQ_LEN, mgpu.cu:1532
+    c->cfg.chunk_relative_loss = saved;
+    if (rc) return rc;
+    if ((rc = launch_fitness(c->stream, c->d_loss + off, c->d_fit + off / 2, per / 2))) return rc;
+    if ((rc = egg_allgather_fitness(c))) return rc;
+    if ((rc = apply_update_async(c, step_seed, learning_rate))) return rc;
+    unsigned long long u = 0;
+    if (host_losses) EGG_CUDA(cudaMemcpyAsync(host_losses, c->d_loss + off, (size_t)per * 4, cudaMemcpyDeviceToHost, c->stream));
+    EGG_CUDA(cudaMemcpyAsync(&u, c->d_updates, sizeof(u), cudaMemcpyDeviceToHost, c->stream));
+    EGG_CUDA(cudaStreamSynchronize(c->stream));
+    if (total_updates) *total_updates = u;
+    return check_dev_err(c);
+}
+
+// ---------------------------------------------------------------- isolated primitives
+
+__global__ void rowdot_kernel(const int8_t *x, const int8_t *nt, int64_t nt_stride, int nt_b_off, int rows_per_member, int64_t rows,
+                              int K, int32_t *xb) {
+    const int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (r >= rows) return;
+    const int8_t *b = nt + ((r / rows_per_member) >> 1) * nt_stride + nt_b_off;
+    int s = 0;
+    for (int k = lane * 4; k < K; k += 128) {
+        int32_t xv = *reinterpret_cast<const int32_t *>(x + r * K + k);
+        int32_t bv = *reinterpret_cast<const int32_t *>(b + k);
+        s = __dp4a(xv, bv, s);
+    }
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
+    if (lane == 0) xb[r] = s;
+}
+
+extern "C" int egg_perturbed_projection(egg_ctx *c, const int8_t *x, const int8_t *w_packed, int8_t *y, int64_t rows, int K, int N,
+                                        int rows_per_member, uint32_t seed, int off_a, int off_b, int rank1_shift, int out_shift,
+                                        int on_device) {
+    if (!c || !x || !w_packed || !y) { set_error("null argument"); return EGG_E_INVALID; }
+    if (rows <= 0 || rows > 0x7FFFFF00ll || K % 128 || N % 128 || K <= 0 || N <= 0 || rows_per_member < 8 || rows % (2 * (int64_t)rows_per_member)) {
+        set_error("projection shape unsupported (rows %lld, K %d, N %d, rows/member %d)", (long long)rows, K, N, rows_per_member);
+        return EGG_E_INVALID;
+    }
+    EGG_CUDA(cudaSetDevice(c->device));
+    cudaStream_t st = c->stream;
+    const int64_t pairs = rows / rows_per_member / 2;
+    const int64_t stride = (int64_t)N + K;
+    int8_t *d_x = nullptr, *d_w = nullptr, *d_y = nullptr, *d_wt = nullptr, *d_nt = nullptr;
+    int32_t *d_xb = nullptr;
+    NoiseSeg *d_segs = nullptr;
+    int rc = EGG_OK;
+    auto cleanup = [&]() {
+        cudaStreamSynchronize(st);
+        if (!on_device) { if (d_x) cudaFree(d_x); if (d_w) cudaFree(d_w); if (d_y) cudaFree(d_y); }
+        if (d_wt) cudaFree(d_wt); if (d_nt) cudaFree(d_nt); if (d_xb) cudaFree(d_xb); if (d_segs) cudaFree(d_segs);
+    };
+#define PTRY(e) do { rc = (e); if (rc) { cleanup(); return rc; } } while (0)
+#define PTRYC(e) do { cudaError_t e_ = (e); if (e_ != cudaSuccess) { set_error("%s: %s", #e, cudaGetErrorString(e_)); cleanup(); return EGG_E_CUDA; } } while (0)
+    if (on_device) { d_x = const_cast<int8_t *>(x); d_w = const_cast<int8_t *>(w_packed); d_y = y; }
+    else {
+        PTRY(dev_alloc(&d_x, rows * K)); PTRY(dev_alloc(&d_w, (int64_t)K * N)); PTRY(dev_alloc(&d_y, rows * N));
+        PTRYC(cudaMemcpyAsync(d_x, x, (size_t)(rows * K), cudaMemcpyHostToDevice, st));
+        PTRYC(cudaMemcpyAsync(d_w, w_packed, (size_t)K * N, cudaMemcpyHostToDevice, st));
+    }
+    PTRY(dev_alloc(&d_wt, (int64_t)K * N)); PTRY(dev_alloc(&d_nt, pairs * stride)); PTRY(dev_alloc(&d_xb, rows)); PTRY(dev_alloc(&d_segs, 2));
+    NoiseSeg segs[2] = {{0, N, 0, off_a, 0, 0}, {N, K, 0, off_b, 0, 0}};
+    PTRYC(cudaMemcpyAsync(d_segs, segs, sizeof(segs), cudaMemcpyHostToDevice, st));
+    PTRY(launch_unpack_transpose(st, d_w, d_wt, K, N));
+    PTRY(launch_noise_fill(st, d_nt, stride, d_segs, 2, (int)pairs, seed, 0, c->cfg.device_mask, c->cfg.device_gaussian));
+    rowdot_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(d_x, d_nt, stride, N, rows_per_member, rows, K, d_xb);
+    PTRYC(cudaGetLastError());
+    GemmParams g;
+    memset(&g, 0, sizeof(g));
+    g.M = (int)rows; g.N = N; g.K = K; g.seq_len = rows_per_member; g.nt = d_nt; g.nt_stride = stride; g.nt_a_off = 0; g.nt_c_off = -1;
+    g.xb = d_xb; g.xb_stride = 1; g.rank1_shift = rank1_shift; g.out_shift = out_shift; g.out8 = d_y; g.err = c->d_err;
+    PTRY(launch_gemm(st, EPI_CLIP8, d_x, d_wt, g, c->num_sms));
+    if (!on_device) PTRYC(cudaMemcpyAsync(y, d_y, (size_t)(rows * N), cudaMemcpyDeviceToHost, st));
+    PTRYC(cudaStreamSynchronize(st));
+    cleanup();
+#undef PTRY
+#undef PTRYC
+    return check_dev_err(c);
+}
+
+extern "C" int egg_update_reconstruct(egg_ctx *c, const int32_t *fitness, int pairs, int rows_k, int cols_n, int off_a, int off_b,
+                                      int seed_base, uint32_t step_seed, int32_t *vote_out, int on_device) {
+    if (!c || !fitness || !vote_out) { set_error("null argument"); return EGG_E_INVALID; }
+    if (pairs <= 0 || rows_k % 128 || cols_n % 128 || rows_k <= 0 || cols_n <= 0) { set_error("reconstruct shape unsupported"); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    cudaStream_t st = c->stream;
+    const int kp = (pairs + 127) / 128 * 128;
+    int32_t *d_fit = nullptr, *d_vote = nullptr;
+    int8_t *d_na = nullptr, *d_nb = nullptr;
+    int rc = EGG_OK;
+    auto cleanup = [&]() {
+        cudaStreamSynchronize(st);
+        if (!on_device) { if (d_fit) cudaFree(d_fit); if (d_vote) cudaFree(d_vote); }
+        if (d_na) cudaFree(d_na); if (d_nb) cudaFree(d_nb);
+    };
+#define PTRY(e) do { rc = (e); if (rc) { cleanup(); return rc; } } while (0)
+#define PTRYC(e) do { cudaError_t e_ = (e); if (e_ != cudaSuccess) { set_error("%s: %s", #e, cudaGetErrorString(e_)); cleanup(); return EGG_E_CUDA; } } while (0)
+    // fitness range decides whether f*a fits int8 directly or needs the base-16 split
+    int fmax = 0;
+    if (on_device) {
+        d_fit = const_cast<int32_t *>(fitness); d_vote = vote_out;
+        std::vector<int32_t> hf((size_t)pairs);
+        PTRYC(cudaMemcpyAsync(hf.data(), fitness, (size_t)pairs * 4, cudaMemcpyDeviceToHost, st));
+        PTRYC(cudaStreamSynchronize(st));
+        for (int i = 0; i < pairs; i++) { int a = hf[i] < 0 ? -hf[i] : hf[i]; if (a > fmax) fmax = a; }
+    } else {
+        for (int i = 0; i < pairs; i++) { int a = fitness[i] < 0 ? -fitness[i] : fitness[i]; if (a > fmax) fmax = a; }
+        PTRY(dev_alloc(&d_fit, pairs)); PTRY(dev_alloc(&d_vote, (int64_t)rows_k * cols_n));
+        PTRYC(cudaMemcpyAsync(d_fit, fitness, (size_t)pairs * 4, cudaMemcpyHostToDevice, st));
+    }
+    const int amax = c->cfg.device_gaussian ? 3 * c->cfg.device_mask : c->cfg.device_mask;
+    if (fmax > 127) { set_error("fitness magnitude %d exceeds 127", fmax); cleanup(); return EGG_E_INVALID; }
+    int split = fmax * amax > 127;
+    if (split && (15 * amax > 127 || 16 * amax > 127)) {
+        set_error("int8 fitness with noise magnitude %d does not fit the two-digit operand split", amax); cleanup(); return EGG_E_INVALID;
+    }
+    const int ktot = split ? 2 * kp : kp;
+    PTRY(dev_alloc(&d_na, (int64_t)cols_n * ktot)); PTRY(dev_alloc(&d_nb, (int64_t)rows_k * ktot));
+    PTRY(launch_update_operands(st, d_na, d_nb, d_fit, pairs, kp, rows_k, cols_n, off_a, off_b, seed_base, step_seed,
+                                c->cfg.device_mask, c->cfg.device_gaussian, split));
+    GemmParams g;
+    memset(&g, 0, sizeof(g));
+    g.M = cols_n; g.N = rows_k; g.K = ktot; g.seq_len = 1 << 20; g.vote_out = d_vote; g.err = c->d_err;
+    PTRY(launch_gemm(st, EPI_VOTE, d_na, d_nb, g, c->num_sms));
+    if (!on_device) PTRYC(cudaMemcpyAsync(vote_out, d_vote, (size_t)rows_k * cols_n * 4, cudaMemcpyDeviceToHost, st));
+    PTRYC(cudaStreamSynchronize(st));
+    cleanup();
+#undef PTRY
+#undef PTRYC
+    return check_dev_err(c);
+}

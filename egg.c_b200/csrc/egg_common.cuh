@@ -1,0 +1,102 @@
+// Shared device/host definitions of the B200 EGGROLL library.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/egg_b200.h"
+
+namespace egg {
+
+// ---------------------------------------------------------------- RNG
+// Counter hash of the reference (full_cuda_train_transformer_adam_mgpu.cu:525-538;
+// d-eggs/include/utils/egg_math.h:17-34).
+__host__ __device__ __forceinline__ uint32_t hash_rng(uint32_t s, uint32_t idx) {
+    uint32_t x = s + idx * 0x9e3779b9u;
+    x ^= x >> 16; x *= 0x85ebca6bu;
+    x ^= x >> 13; x *= 0xc2b2ae35u;
+    x ^= x >> 16;
+    return x;
+}
+
+__host__ __device__ __forceinline__ int noise_field(uint32_t r, int sign_bit, int shift, int mask) {
+    int mag = (int)((r >> shift) & (uint32_t)mask);
+    return (r & (1u << sign_bit)) ? mag : -mag;
+}
+
+// gaussian: sum of three fields (DEVICE_GAUSSIAN), else one field.
+__host__ __device__ __forceinline__ int noise_from_hash(uint32_t s, uint32_t idx, int mask, int gaussian) {
+    uint32_t r = hash_rng(s, idx);
+    if (gaussian)
+        return (int)(int8_t)(noise_field(r, 0, 1, mask) + noise_field(r, 5, 6, mask) + noise_field(r, 10, 11, mask));
+    return noise_field(r, 0, 1, mask);
+}
+
+__host__ __device__ __forceinline__ int clip8(int a) { return a > 127 ? 127 : (a < -127 ? -127 : a); }
+
+// ---------------------------------------------------------------- model layout
+// Field order of TransformerModel (mgpu.cu:284-318); element offsets.
+struct ModelLayout {
+    int64_t embedding, emb_bias, ln_init, ln_init_bias, w_emb_mlp_up, mlp_emb_bias_up, w_emb_mlp_down,
+        mlp_emb_bias_down, ln_1, ln_1_bias, w_q, w_k, w_v, w_o, ln_2, ln_2_bias, w_up, mlp_bias_up, w_down,
+        mlp_bias_down, ln_f, ln_f_bias, total;
+};
+
+inline ModelLayout model_layout(const egg_config &c) {
+    ModelLayout L;
+    int64_t H = c.hidden_dim, V = c.vocab_size, NL = c.n_layers, o = 0;
+    L.embedding = o;         o += V * H;
+    L.emb_bias = o;          o += H;
+    L.ln_init = o;           o += H;
+    L.ln_init_bias = o;      o += H;
+    L.w_emb_mlp_up = o;      o += H * 4 * H;
+    L.mlp_emb_bias_up = o;   o += 4 * H;
+    L.w_emb_mlp_down = o;    o += 4 * H * H;
+    L.mlp_emb_bias_down = o; o += H;
+    L.ln_1 = o;              o += NL * H;
+    L.ln_1_bias = o;         o += NL * H;
+    L.w_q = o;               o += NL * H * H;
+    L.w_k = o;               o += NL * H * H;
+    L.w_v = o;               o += NL * H * H;
+    L.w_o = o;               o += NL * H * H;
+    L.ln_2 = o;              o += NL * H;
+    L.ln_2_bias = o;         o += NL * H;
+    L.w_up = o;              o += NL * H * 4 * H;
+    L.mlp_bias_up = o;       o += NL * 4 * H;
+    L.w_down = o;            o += NL * 4 * H * H;
+    L.mlp_bias_down = o;     o += NL * H;
+    L.ln_f = o;              o += H;
+    L.ln_f_bias = o;         o += H;
+    L.total = o;
+    return L;
+}
+
+// One trainable parameter of the update sequence (mgpu.cu:1603-1643).
+struct ParamDesc {
+    int64_t model_off;   // element offset in TransformerModel
+    int64_t opt_off;     // byte offset in AdamModel
+    int rows_k;          // input dim (0 for vectors)
+    int cols_n;          // output dim (length for vectors)
+    int off_a, off_b, seed_base;
+    float lr_scale;
+    int muon;            // state is MuonParam{m,acc} and the step is Muon
+    int64_t shadow_off;  // element offset of the K-major shadow copy (-1: none)
+};
+
+// ---------------------------------------------------------------- errors
+void set_error(const char *fmt, ...);
+
+#define EGG_CUDA(call)                                                                        \
+    do {                                                                                      \
+        cudaError_t e_ = (call);                                                              \
+        if (e_ != cudaSuccess) {                                                              \
+            egg::set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
+            return EGG_E_CUDA;                                                                \
+        }                                                                                     \
+    } while (0)
+
+// device-side error record: flag[0] = code (0 ok), flag[1] = where
+enum DevErr { DEV_OK = 0, DEV_TIMEOUT_FULL = 1, DEV_TIMEOUT_EMPTY = 2, DEV_TIMEOUT_TMEM_FULL = 3, DEV_TIMEOUT_TMEM_EMPTY = 4 };
+
+}  // namespace egg

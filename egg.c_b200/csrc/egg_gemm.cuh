@@ -1,0 +1,493 @@
+// Persistent, warp-specialised int8 GEMM for sm_100a:
+//   D[M,N] (int32, TMEM) = A[M,K] (int8, K-major) x B[N,K]^T (int8, K-major)
+// TMA (128-byte swizzle) -> 4-stage shared-memory ring -> tcgen05.mma kind::i8 ->
+// two TMEM accumulator stages -> 8 epilogue warps.  The epilogue is where the
+// EGGROLL arithmetic lives: the per-member rank-1 term
+//   acc += ((x·b_p) * a_p[n] * sign) >> (FIXED_POINT + SIGMA_SHIFT)
+// (compute_linear_projection, mgpu.cu:553-572) and the call-site specific
+// requantisation (mgpu.cu:729-756, 779-784, 829-830, 975-1023) or, for the
+// update GEMM, the ES-AdamW / Muon-momentum step (mgpu.cu:1040-1111,
+// muon_internal.cuh:15-50).
+#pragma once
+
+#include "egg_common.cuh"
+#include "egg_ptx.cuh"
+
+namespace egg {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 128;            // bytes (= int8 elements) per k-block: one swizzle row
+constexpr int GEMM_STAGES = 4;
+constexpr int GEMM_THREADS = 320;       // warp0 TMA, warp1 MMA, warps 2..9 epilogue
+constexpr int GEMM_EPI_THREADS = 256;
+constexpr int GEMM_MAX_SLOTS = 9;       // distinct population pairs a 128-row tile can touch (seq_len >= 8)
+
+enum GemmEpi {
+    EPI_CLIP8 = 0,   // y = clip((acc + r1) >> out_shift)                       -> int8
+    EPI_GELU = 1,    // u = GELU[(u8)clip(((acc+r1)>>s) + b + vn)]              -> int8, Σ u·noise -> xb2
+    EPI_PRE32 = 2,   // pre = resid + ((acc+r1)>>s) + b + vn                    -> int32 + row abs-max
+    EPI_QKV = 3,     // rope(acc + r1) for q,k ; acc + r1 for v                 -> int32 + row abs-max per q/k/v
+    EPI_HEAD = 4,    // logits = (acc+r1)>>s ; integer cross-entropy            -> loss[member] +=
+    EPI_ADAM = 5,    // vote tile -> ES-AdamW step on packed weights
+    EPI_MUON_M = 6,  // vote tile -> m = mu*m + vote ; row-major copy of m
+    EPI_VOTE = 7,    // vote tile -> int32 votes in packed index order
+};
+
+struct GemmParams {
+    int M, N, K;
+    // ---- row -> member mapping (evaluation epilogues) ----
+    int seq_len;                 // rows per member
+    const int8_t *nt;            // per-pair noise table of this wave
+    int64_t nt_stride;           // bytes per pair
+    int nt_a_off;                // A-noise vector (length N) of this projection
+    int nt_c_off;                // bias-noise deltas [2][N] (-1: none)
+    int nt_d_off;                // B-noise vector of the NEXT projection (EPI_GELU), length N
+    const int32_t *xb;           // Σ_k x_k b_k per row: xb[r*xb_stride + xb_col(+n0/third)]
+    int xb_stride;
+    int rank1_shift;
+    int out_shift;
+    const int8_t *bias;          // [N] or null
+    // outputs
+    int8_t *out8;                // [M,N]
+    int32_t *out32;              // [M,N]
+    int32_t *rowstat;            // EPI_GELU: xb2[M] (+=); EPI_PRE32: rowmax[M]; EPI_QKV: rowmax[M][3]
+    const int8_t *resid;         // [M,N] int8 (EPI_PRE32)
+    const int8_t *act_lut;       // 256
+    const int32_t *exp_lut;      // 256
+    const int32_t *rope_lut;     // [seq_len][head_dim]
+    int third;                   // EPI_QKV: N/3 (= hidden)
+    int head_dim;
+    int rope_bit;                // ROPE_SCALE_BIT
+    // EPI_HEAD
+    const uint8_t *dataset;
+    int64_t data_len, start_idx, data_stride;   // data_stride = data_len / (POP/2)
+    int pop_base;                // global index of member 0 of this wave
+    int use_same_data;
+    int softmax_scale_bit;
+    int32_t *loss;               // [wave members] +=
+    // ---- update epilogues: GEMM M = cols_n (output dim), GEMM N = rows_k (input dim) ----
+    int8_t *w_packed;            // [rows_k/4][cols_n][4]
+    float *opt;                  // AdamParam{m,v,acc} or MuonParam{m,acc} per packed index
+    float *m_rowmajor;           // EPI_MUON_M: [rows_k][cols_n]
+    float lr, beta1, beta2, eps, wd, mu;
+    unsigned long long *total_updates;
+    int32_t *vote_out;
+    // ---- device error record ----
+    int *err;
+};
+
+template <int BN>
+struct GemmSmem {
+    alignas(1024) uint8_t a[GEMM_STAGES][GEMM_BM * GEMM_BK];
+    alignas(1024) uint8_t b[GEMM_STAGES][BN * GEMM_BK];
+    alignas(16) int8_t a_tab[GEMM_MAX_SLOTS][BN];
+    alignas(16) int8_t c_tab[GEMM_MAX_SLOTS][2][BN];
+    alignas(16) int8_t d_tab[GEMM_MAX_SLOTS][BN];
+    alignas(16) int8_t bias[BN];
+    alignas(16) int8_t act_lut[256];
+    alignas(16) int32_t exp_lut[256];
+    alignas(8) uint64_t full[GEMM_STAGES];
+    uint64_t empty[GEMM_STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    volatile int abort_flag;
+    volatile int epi_ok;
+};
+
+__device__ __forceinline__ void gemm_fail(const GemmParams &p, volatile int *abort_flag, int code) {
+    *abort_flag = 1;
+    if (p.err) { atomicCAS(p.err, 0, code); }
+}
+
+// AdamW element step; expressions and their order are those of apply_adam_update
+// (mgpu.cu:1040-1064) so that the compiler contracts them the same way.
+__device__ __forceinline__ int adam_apply(float &m, float &v, float &acc, int &w, float g, float lr, float b1, float b2,
+                                          float eps, float wd) {
+    m = b1 * m + (1.0f - b1) * g;
+    v = b2 * v + (1.0f - b2) * (g * g);
+    float step = -lr * (m / (sqrtf(v) + eps) + wd * (float)w);
+    acc += step;
+    int change = 0;
+    if (acc >= 1.0f) {
+        if (w < 127) { w++; change = 1; acc -= 1.0f; }
+        else acc = 1.0f;
+    } else if (acc <= -1.0f) {
+        if (w > -127) { w--; change = 1; acc += 1.0f; }
+        else acc = -1.0f;
+    }
+    return change;
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    GemmSmem<BN> &sm = *reinterpret_cast<GemmSmem<BN> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_n = p.N / BN;
+    const int tiles_m = (p.M + GEMM_BM - 1) / GEMM_BM;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
+    constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+    constexpr uint32_t STAGE_BYTES = GEMM_BM * GEMM_BK + BN * GEMM_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < GEMM_STAGES; s++) { ptx::mbar_init(&sm.full[s], 1); ptx::mbar_init(&sm.empty[s], 1); }
+        for (int a = 0; a < 2; a++) { ptx::mbar_init(&sm.tmem_full[a], 1); ptx::mbar_init(&sm.tmem_empty[a], 8); }
+        sm.abort_flag = 0;
+        sm.epi_ok = 1;
+        ptx::fence_barrier_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(&sm.tmem_base, TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    if (warp >= 2) {
+        int e = threadIdx.x - 64;
+        if (EPI == EPI_GELU && p.act_lut) sm.act_lut[e] = p.act_lut[e];
+        if (EPI == EPI_HEAD && p.exp_lut) sm.exp_lut[e] = p.exp_lut[e];
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = sm.tmem_base;
+
+    if (warp == 0) {
+        // ===================== TMA producer =====================
+        if (ptx::elect_one()) {
+            ptx::prefetch_tmap(&tmap_a);
+            ptx::prefetch_tmap(&tmap_b);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int m0 = (tile / tiles_n) * GEMM_BM, n0 = (tile % tiles_n) * BN;
+                for (int kb = 0; kb < num_kb; kb++, it++) {
+                    int s = it % GEMM_STAGES;
+                    uint32_t ph = (it / GEMM_STAGES) & 1;
+                    if (!ptx::mbar_wait(&sm.empty[s], ph ^ 1) || sm.abort_flag) { gemm_fail(p, &sm.abort_flag, DEV_TIMEOUT_EMPTY); ok = false; break; }
+                    ptx::mbar_arrive_expect_tx(&sm.full[s], STAGE_BYTES);
+                    ptx::tma_load_2d(sm.a[s], &tmap_a, &sm.full[s], kb * GEMM_BK, m0);
+                    ptx::tma_load_2d(sm.b[s], &tmap_b, &sm.full[s], kb * GEMM_BK, n0);
+                }
+            }
+            if (!ok) {   // let copies already in flight land before the CTA tears down
+                uint64_t t0 = ptx::globaltimer();
+                while (ptx::globaltimer() - t0 < 200000ull) { __nanosleep(1000); }
+            }
+        }
+    } else if (warp == 1) {
+        // ===================== MMA issuer =====================
+        if (ptx::elect_one()) {
+            constexpr uint32_t idesc = ptx::make_idesc_i8(GEMM_BM, BN);
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tcount++) {
+                int as = tcount & 1;
+                uint32_t aph = (tcount >> 1) & 1;
+                if (!ptx::mbar_wait(&sm.tmem_empty[as], aph ^ 1) || sm.abort_flag) { gemm_fail(p, &sm.abort_flag, DEV_TIMEOUT_TMEM_EMPTY); ok = false; break; }
+                ptx::tc_fence_after();
+                uint32_t d_tmem = tmem_base + (uint32_t)(as * BN);
+                for (int kb = 0; kb < num_kb; kb++, it++) {
+                    int s = it % GEMM_STAGES;
+                    uint32_t ph = (it / GEMM_STAGES) & 1;
+                    if (!ptx::mbar_wait(&sm.full[s], ph) || sm.abort_flag) { gemm_fail(p, &sm.abort_flag, DEV_TIMEOUT_FULL); ok = false; break; }
+                    ptx::tc_fence_after();
+                    uint64_t da = ptx::make_smem_desc_sw128(ptx::smem_u32(sm.a[s]));
+                    uint64_t db = ptx::make_smem_desc_sw128(ptx::smem_u32(sm.b[s]));
+#pragma unroll
+                    for (int k = 0; k < GEMM_BK / 32; k++) {
+                        // +32 bytes along K inside the swizzle row = +2 in the 16-byte address field
+                        ptx::mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    ptx::mma_commit(&sm.empty[s]);
+                }
+                if (ok) ptx::mma_commit(&sm.tmem_full[as]);
+            }
+        }
+    } else {
+        // ===================== epilogue (8 warps) =====================
+        const int e = threadIdx.x - 64;            // 0..255
+        const int ew = warp - 2;                   // 0..7
+        const int quarter = warp & 3;              // TMEM lane quarter this warp may read
+        constexpr int NHALF = (EPI == EPI_HEAD) ? 1 : 2;   // the head needs whole rows in one thread
+        constexpr int COLS_PER = BN / NHALF;
+        const int half = (NHALF == 2) ? (ew >> 2) : 0;     // which half of the tile's columns
+        const bool active = (NHALF == 2) || ew < 4;
+        const int row_in_tile = quarter * 32 + lane;
+        uint32_t tcount = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tcount++) {
+            const int as = tcount & 1;
+            const uint32_t aph = (tcount >> 1) & 1;
+            const int m0 = (tile / tiles_n) * GEMM_BM, n0 = (tile % tiles_n) * BN;
+            const int r = m0 + row_in_tile;
+            const bool row_ok = r < p.M;
+
+            // ---- per-tile tables (evaluation epilogues) ----
+            int first_pl = 0, slot = 0, sgn = 0;
+            if (EPI <= EPI_HEAD) {
+                int last_row = min(m0 + GEMM_BM, p.M) - 1;
+                first_pl = (m0 / p.seq_len) >> 1;
+                int nslots = ((last_row / p.seq_len) >> 1) - first_pl + 1;
+                int mem = (row_ok ? r : last_row) / p.seq_len;
+                slot = (mem >> 1) - first_pl;
+                sgn = mem & 1;
+                for (int i = e; i < nslots * (BN / 4); i += GEMM_EPI_THREADS) {
+                    int sl = i / (BN / 4), j = (i % (BN / 4)) * 4;
+                    const int8_t *base = p.nt + (int64_t)(first_pl + sl) * p.nt_stride;
+                    *reinterpret_cast<int32_t *>(&sm.a_tab[sl][j]) = *reinterpret_cast<const int32_t *>(base + p.nt_a_off + n0 + j);
+                    if ((EPI == EPI_GELU || EPI == EPI_PRE32) && p.nt_c_off >= 0) {
+                        *reinterpret_cast<int32_t *>(&sm.c_tab[sl][0][j]) = *reinterpret_cast<const int32_t *>(base + p.nt_c_off + n0 + j);
+                        *reinterpret_cast<int32_t *>(&sm.c_tab[sl][1][j]) = *reinterpret_cast<const int32_t *>(base + p.nt_c_off + p.N + n0 + j);
+                    }
+                    if (EPI == EPI_GELU)
+                        *reinterpret_cast<int32_t *>(&sm.d_tab[sl][j]) = *reinterpret_cast<const int32_t *>(base + p.nt_d_off + n0 + j);
+                }
+                if ((EPI == EPI_GELU || EPI == EPI_PRE32) && e < BN) sm.bias[e] = p.bias ? p.bias[n0 + e] : (int8_t)0;
+            }
+            // one thread waits for the accumulator, everybody learns the outcome at the barrier
+            if (e == 0) {
+                bool ok = ptx::mbar_wait(&sm.tmem_full[as], aph) && !sm.abort_flag;
+                if (!ok) { gemm_fail(p, &sm.abort_flag, DEV_TIMEOUT_TMEM_FULL); sm.epi_ok = 0; }
+            }
+            ptx::named_bar_sync(1, GEMM_EPI_THREADS);
+            if (!sm.epi_ok) break;
+            ptx::tc_fence_after();
+
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * BN + half * COLS_PER);
+            const int cbase = half * COLS_PER;       // column offset inside the tile
+
+            if (!active) {
+                // nothing to compute; still takes part in the barrier protocol below
+            } else if (EPI <= EPI_HEAD) {
+                // ---------------- evaluation epilogues ----------------
+                int xbs = 0;
+                if (row_ok) {
+                    int xcol = (EPI == EPI_QKV) ? (n0 / p.third) : 0;
+                    int xbv = p.xb[(int64_t)r * p.xb_stride + xcol];
+                    xbs = sgn ? -xbv : xbv;
+                }
+                const int8_t *atab = sm.a_tab[slot];
+                if (EPI == EPI_HEAD) {
+                    // pass 1: row max of the logits; pass 2: Σ exp-LUT and the target logit (mgpu.cu:969-1023)
+                    int mx = INT_MIN;
+                    for (int c = 0; c < BN; c += 32) {
+                        uint32_t v[32];
+                        ptx::tmem_ld32(taddr + c, v);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            int lg = ((int)v[j] + ((xbs * (int)atab[c + j]) >> p.rank1_shift)) >> p.out_shift;
+                            mx = max(mx, lg);
+                        }
+                    }
+                    int target = 0;
+                    if (row_ok) {
+                        int mem = r / p.seq_len, t = r % p.seq_len;
+                        int64_t pair = (p.pop_base + mem) >> 1;
+                        int64_t pos = p.use_same_data ? (p.start_idx % (p.data_len - p.seq_len))
+                                                      : ((p.start_idx + pair * p.data_stride) % (p.data_len - p.seq_len));
+                        target = p.dataset[pos + t + 1];
+                    }
+                    long long sum_ex = 0;
+                    int tgt_logit = 0;
+                    for (int c = 0; c < BN; c += 32) {
+                        uint32_t v[32];
+                        ptx::tmem_ld32(taddr + c, v);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            int lg = ((int)v[j] + ((xbs * (int)atab[c + j]) >> p.rank1_shift)) >> p.out_shift;
+                            int idx = mx - lg;
+                            idx = idx > 255 ? 255 : idx;
+                            sum_ex += sm.exp_lut[idx];
+                            if (c + j == target) tgt_logit = lg;
+                        }
+                    }
+                    if (row_ok) {
+                        int log_sum = 0;
+                        if (sum_ex > 0) {
+                            int pos = 63 - __clzll(sum_ex);              // floor(log2), as the shift ladder of mgpu.cu:1015-1019
+                            log_sum = (pos << 4) - (p.softmax_scale_bit << 4);
+                        }
+                        int l = (log_sum >> 1) + mx - tgt_logit;
+                        atomicAdd(&p.loss[r / p.seq_len], l);
+                    }
+                } else {
+                    int run_max = 0, run_max2 = 0;    // abs-max (PRE32 / QKV)
+                    int dot = 0;                      // Σ u·noise (GELU)
+                    for (int c = 0; c < COLS_PER; c += 32) {
+                        uint32_t v[32];
+                        ptx::tmem_ld32(taddr + c, v);
+                        ptx::tmem_ld_wait();
+                        const int cc = cbase + c;     // column inside the tile
+                        if (EPI == EPI_CLIP8) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                int y = clip8(((int)v[j] + ((xbs * (int)atab[cc + j]) >> p.rank1_shift)) >> p.out_shift);
+                                if ((j & 3) == 0) w[j >> 2] = 0;
+                                w[j >> 2] |= (uint32_t)(y & 0xFF) << ((j & 3) * 8);
+                            }
+                            if (row_ok) {
+                                int4 *dst = reinterpret_cast<int4 *>(p.out8 + (int64_t)r * p.N + n0 + cc);
+                                dst[0] = make_int4(w[0], w[1], w[2], w[3]);
+                                dst[1] = make_int4(w[4], w[5], w[6], w[7]);
+                            }
+                        } else if (EPI == EPI_GELU) {
+                            uint32_t w[8];
+                            const int8_t *ctab = sm.c_tab[slot][sgn];
+                            const int8_t *dtab = sm.d_tab[slot];
+                            const bool has_c = p.nt_c_off >= 0;
+#pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                int a = (int)v[j] + ((xbs * (int)atab[cc + j]) >> p.rank1_shift);
+                                int z = (a >> p.out_shift) + (int)sm.bias[cc + j] + (has_c ? (int)ctab[cc + j] : 0);
+                                int u = sm.act_lut[(uint8_t)(int8_t)clip8(z)];
+                                dot += u * (int)dtab[cc + j];
+                                if ((j & 3) == 0) w[j >> 2] = 0;
+                                w[j >> 2] |= (uint32_t)(u & 0xFF) << ((j & 3) * 8);
+                            }
+                            if (row_ok) {
+                                int4 *dst = reinterpret_cast<int4 *>(p.out8 + (int64_t)r * p.N + n0 + cc);
+                                dst[0] = make_int4(w[0], w[1], w[2], w[3]);
+                                dst[1] = make_int4(w[4], w[5], w[6], w[7]);
+                            }
+                        } else if (EPI == EPI_PRE32) {
+                            const int8_t *ctab = sm.c_tab[slot][sgn];
+                            const bool has_c = p.nt_c_off >= 0;
+                            int4 rs[2] = {make_int4(0, 0, 0, 0), make_int4(0, 0, 0, 0)};
+                            if (row_ok) {
+                                const int4 *src = reinterpret_cast<const int4 *>(p.resid + (int64_t)r * p.N + n0 + cc);
+                                rs[0] = src[0]; rs[1] = src[1];
+                            }
+                            const int8_t *rb = reinterpret_cast<const int8_t *>(rs);
+#pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                int a = (int)v[j] + ((xbs * (int)atab[cc + j]) >> p.rank1_shift);
+                                int pre = (int)rb[j] + (a >> p.out_shift) + (int)sm.bias[cc + j] + (has_c ? (int)ctab[cc + j] : 0);
+                                v[j] = (uint32_t)pre;
+                                run_max = max(run_max, abs(pre));
+                            }
+                            if (row_ok) {
+                                int4 *dst = reinterpret_cast<int4 *>(p.out32 + (int64_t)r * p.N + n0 + cc);
+#pragma unroll
+                                for (int q = 0; q < 8; q++) dst[q] = make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                            }
+                        } else if (EPI == EPI_QKV) {
+                            const int which = n0 / p.third;           // 0 q, 1 k, 2 v (tile never straddles)
+                            if (which < 2) {
+                                // integer RoPE on adjacent (even, odd) columns (apply_rope_integer, mgpu.cu:624-644)
+                                const int t = (row_ok ? r : 0) % p.seq_len;
+                                const int hd0 = (n0 + cc) % p.head_dim;
+                                const int4 *lut = reinterpret_cast<const int4 *>(p.rope_lut + (int64_t)t * p.head_dim + hd0);
+                                const long long half_ulp = 1ll << (p.rope_bit - 1);
+#pragma unroll
+                                for (int q = 0; q < 8; q++) {
+                                    int4 cs = __ldg(&lut[q]);     // c0 s0 c1 s1
+                                    long long e0 = (int)v[4 * q] + ((xbs * (int)atab[cc + 4 * q]) >> p.rank1_shift);
+                                    long long o0 = (int)v[4 * q + 1] + ((xbs * (int)atab[cc + 4 * q + 1]) >> p.rank1_shift);
+                                    long long e1 = (int)v[4 * q + 2] + ((xbs * (int)atab[cc + 4 * q + 2]) >> p.rank1_shift);
+                                    long long o1 = (int)v[4 * q + 3] + ((xbs * (int)atab[cc + 4 * q + 3]) >> p.rank1_shift);
+                                    v[4 * q] = (uint32_t)(int)((e0 * cs.x - o0 * cs.y + half_ulp) >> p.rope_bit);
+                                    v[4 * q + 1] = (uint32_t)(int)((e0 * cs.y + o0 * cs.x + half_ulp) >> p.rope_bit);
+                                    v[4 * q + 2] = (uint32_t)(int)((e1 * cs.z - o1 * cs.w + half_ulp) >> p.rope_bit);
+                                    v[4 * q + 3] = (uint32_t)(int)((e1 * cs.w + o1 * cs.z + half_ulp) >> p.rope_bit);
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; j++) v[j] = (uint32_t)((int)v[j] + ((xbs * (int)atab[cc + j]) >> p.rank1_shift));
+                            }
+#pragma unroll
+                            for (int j = 0; j < 32; j++) run_max = max(run_max, abs((int)v[j]));
+                            if (row_ok) {
+                                int4 *dst = reinterpret_cast<int4 *>(p.out32 + (int64_t)r * p.N + n0 + cc);
+#pragma unroll
+                                for (int q = 0; q < 8; q++) dst[q] = make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                            }
+                        }
+                    }
+                    (void)run_max2;
+                    if (row_ok) {
+                        if (EPI == EPI_GELU) atomicAdd(&p.rowstat[r], dot);
+                        if (EPI == EPI_PRE32) atomicMax(&p.rowstat[r], run_max);
+                        if (EPI == EPI_QKV) atomicMax(&p.rowstat[(int64_t)r * 3 + n0 / p.third], run_max);
+                    }
+                }
+            } else {
+                // ---------------- update epilogues: row r = output column n, tile columns = input index k ----------------
+                const int n = r;
+                const int cols_n = p.M;
+                int changes = 0;
+                for (int c = 0; c < COLS_PER; c += 32) {
+                    uint32_t v[32];
+                    ptx::tmem_ld32(taddr + c, v);
+                    ptx::tmem_ld_wait();
+                    if (!row_ok) continue;
+                    const int k0 = n0 + cbase + c;           // multiple of 32
+#pragma unroll
+                    for (int q = 0; q < 8; q++) {
+                        const int64_t word = (int64_t)((k0 >> 2) + q) * cols_n + n;
+                        const int64_t idx = word * 4;
+                        if (EPI == EPI_VOTE) {
+                            *reinterpret_cast<int4 *>(p.vote_out + idx) = make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                        } else if (EPI == EPI_ADAM) {
+                            uint32_t wword = *reinterpret_cast<const uint32_t *>(p.w_packed + idx);
+                            float4 *st = reinterpret_cast<float4 *>(p.opt + idx * 3);
+                            float4 s0 = st[0], s1 = st[1], s2 = st[2];
+                            float f[12] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w, s2.x, s2.y, s2.z, s2.w};
+                            uint32_t neww = 0;
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                int w = (int)(int8_t)(wword >> (8 * j));
+                                float g = -(float)(int)v[4 * q + j];
+                                changes += adam_apply(f[3 * j], f[3 * j + 1], f[3 * j + 2], w, g, p.lr, p.beta1, p.beta2, p.eps, p.wd);
+                                neww |= (uint32_t)(w & 0xFF) << (8 * j);
+                            }
+                            *reinterpret_cast<uint32_t *>(p.w_packed + idx) = neww;
+                            st[0] = make_float4(f[0], f[1], f[2], f[3]);
+                            st[1] = make_float4(f[4], f[5], f[6], f[7]);
+                            st[2] = make_float4(f[8], f[9], f[10], f[11]);
+                        } else if (EPI == EPI_MUON_M) {
+                            float4 *st = reinterpret_cast<float4 *>(p.opt + idx * 2);
+                            float4 s0 = st[0], s1 = st[1];     // m0 acc0 m1 acc1 | m2 acc2 m3 acc3
+                            s0.x = p.mu * s0.x + (float)(int)v[4 * q];          // muon_internal.cuh:45-47
+                            s0.z = p.mu * s0.z + (float)(int)v[4 * q + 1];
+                            s1.x = p.mu * s1.x + (float)(int)v[4 * q + 2];
+                            s1.z = p.mu * s1.z + (float)(int)v[4 * q + 3];
+                            st[0] = s0; st[1] = s1;
+                            const int k = k0 + 4 * q;
+                            p.m_rowmajor[(int64_t)k * cols_n + n] = s0.x;        // gather, muon_internal.cuh:53-74
+                            p.m_rowmajor[(int64_t)(k + 1) * cols_n + n] = s0.z;
+                            p.m_rowmajor[(int64_t)(k + 2) * cols_n + n] = s1.x;
+                            p.m_rowmajor[(int64_t)(k + 3) * cols_n + n] = s1.z;
+                        }
+                    }
+                }
+                if (EPI == EPI_ADAM) {
+                    for (int off = 16; off > 0; off >>= 1) changes += __shfl_down_sync(0xFFFFFFFFu, changes, off);
+                    if (lane == 0 && changes > 0) atomicAdd(p.total_updates, (unsigned long long)changes);
+                }
+            }
+            // release the accumulator stage
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&sm.tmem_empty[as]);
+            // tables are rewritten at the top of the next tile: everybody must be done reading them
+            ptx::named_bar_sync(1, GEMM_EPI_THREADS);
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int BN>
+constexpr size_t gemm_smem_bytes() { return sizeof(GemmSmem<BN>) + 1024; }
+
+}  // namespace egg

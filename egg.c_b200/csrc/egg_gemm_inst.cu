@@ -1,0 +1,104 @@
+// Instantiations and host launcher of the tcgen05 int8 GEMM.
+#include "egg_kernels.cuh"
+
+#include <cudaTypedefs.h>
+
+namespace egg {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+template <int BN, int EPI>
+static int set_attr() {
+    EGG_CUDA(cudaFuncSetAttribute(gemm_i8_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes<BN>()));
+    return EGG_OK;
+}
+
+template <int EPI>
+static int set_attr_both() {
+    int rc = set_attr<128, EPI>();
+    if (rc) return rc;
+    return set_attr<256, EPI>();
+}
+
+int gemm_init() {
+    if (!g_encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        EGG_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return EGG_E_CUDA; }
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    int rc;
+    if ((rc = set_attr_both<EPI_CLIP8>())) return rc;
+    if ((rc = set_attr_both<EPI_GELU>())) return rc;
+    if ((rc = set_attr_both<EPI_PRE32>())) return rc;
+    if ((rc = set_attr_both<EPI_QKV>())) return rc;
+    if ((rc = set_attr<256, EPI_HEAD>())) return rc;
+    if ((rc = set_attr_both<EPI_ADAM>())) return rc;
+    if ((rc = set_attr_both<EPI_MUON_M>())) return rc;
+    if ((rc = set_attr_both<EPI_VOTE>())) return rc;
+    return EGG_OK;
+}
+
+// [rows][k] int8 row-major; box = 128 (k) x box_rows, 128-byte swizzle, out-of-range reads give zeros.
+static int make_tmap(CUtensorMap *m, const void *ptr, uint64_t rows, uint64_t k, uint32_t box_rows) {
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (k & 15)) { set_error("GEMM operand is not 16-byte aligned (ptr %p, k %llu)", ptr, (unsigned long long)k); return EGG_E_INVALID; }
+    cuuint64_t gdim[2] = {k, rows};
+    cuuint64_t gstride[1] = {k};
+    cuuint32_t box[2] = {(cuuint32_t)GEMM_BK, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), gdim, gstride, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%d) rows=%llu k=%llu box_rows=%u", (int)r, (unsigned long long)rows, (unsigned long long)k, box_rows); return EGG_E_CUDA; }
+    return EGG_OK;
+}
+
+template <int BN, int EPI>
+static int launch_one(cudaStream_t st, const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int num_sms) {
+    int tiles = ((p.M + GEMM_BM - 1) / GEMM_BM) * (p.N / BN);
+    int grid = tiles < num_sms ? tiles : num_sms;
+    gemm_i8_kernel<BN, EPI><<<grid, GEMM_THREADS, gemm_smem_bytes<BN>(), st>>>(ta, tb, p);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
+
+template <int EPI>
+static int launch_bn(cudaStream_t st, int bn, const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int num_sms) {
+    if (bn == 256) return launch_one<256, EPI>(st, ta, tb, p, num_sms);
+    return launch_one<128, EPI>(st, ta, tb, p, num_sms);
+}
+
+int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, const GemmParams &p, int num_sms) {
+    if (!g_encode) { set_error("gemm_init() was not called"); return EGG_E_STATE; }
+    if (p.M <= 0 || p.N % 128 || p.K % 16) { set_error("unsupported GEMM shape M=%d N=%d K=%d", p.M, p.N, p.K); return EGG_E_INVALID; }
+    int bn = (p.N % 256 == 0) ? 256 : 128;
+    if (epi == EPI_QKV && (p.third % bn)) bn = 128;
+    if (epi == EPI_QKV && (p.third % 128)) { set_error("hidden_dim must be a multiple of 128"); return EGG_E_INVALID; }
+    if (epi == EPI_HEAD && p.N != 256) { set_error("head GEMM needs vocab_size == 256"); return EGG_E_INVALID; }
+    if (epi <= EPI_HEAD) {
+        int max_slots = ((GEMM_BM - 1) / p.seq_len) / 2 + 2;
+        if (max_slots > GEMM_MAX_SLOTS) { set_error("seq_len %d too small for the epilogue tables", p.seq_len); return EGG_E_INVALID; }
+    }
+    CUtensorMap ta, tb;
+    int rc;
+    if ((rc = make_tmap(&ta, A, (uint64_t)p.M, (uint64_t)p.K, GEMM_BM))) return rc;
+    if ((rc = make_tmap(&tb, B, (uint64_t)p.N, (uint64_t)p.K, (uint32_t)bn))) return rc;
+    switch (epi) {
+        case EPI_CLIP8: return launch_bn<EPI_CLIP8>(st, bn, ta, tb, p, num_sms);
+        case EPI_GELU: return launch_bn<EPI_GELU>(st, bn, ta, tb, p, num_sms);
+        case EPI_PRE32: return launch_bn<EPI_PRE32>(st, bn, ta, tb, p, num_sms);
+        case EPI_QKV: return launch_bn<EPI_QKV>(st, bn, ta, tb, p, num_sms);
+        case EPI_HEAD: return launch_one<256, EPI_HEAD>(st, ta, tb, p, num_sms);
+        case EPI_ADAM: return launch_bn<EPI_ADAM>(st, bn, ta, tb, p, num_sms);
+        case EPI_MUON_M: return launch_bn<EPI_MUON_M>(st, bn, ta, tb, p, num_sms);
+        case EPI_VOTE: return launch_bn<EPI_VOTE>(st, bn, ta, tb, p, num_sms);
+    }
+    set_error("unknown epilogue %d", epi);
+    return EGG_E_INVALID;
+}
+
+}  // namespace egg

@@ -1,0 +1,670 @@
+// Non-GEMM kernels of the evaluation and update paths: per-pair noise tables,
+// row-wise embedding / adaptive-normalise / mean-abs-norm, Q/K/V requantisation,
+// causal integer-softmax attention, fitness, update operand generation, vector
+// AdamW, Muon Newton–Schulz.  "mgpu.cu" = full_cuda_train_transformer_adam_mgpu.cu.
+#include "egg_kernels.cuh"
+
+#include <limits.h>
+
+namespace egg {
+
+// =========================================================================
+// noise table
+// =========================================================================
+
+void build_noise_map(const egg_config &c, NoiseMap *map, NoiseSeg *segs, int *nsegs, int max_segs) {
+    const int H = c.hidden_dim, V = c.vocab_size;
+    const int ssv = c.sigma_shift_vector;
+    int n = 0, off = 0;
+    auto plain = [&](int len, int seed) { int o = off; if (n < max_segs) segs[n] = NoiseSeg{off, len, 0, seed, 0, 0}; n++; off += len; return o; };
+    auto delta = [&](int len, int sa, int sb) { int o = off; if (n < max_segs) segs[n] = NoiseSeg{off, len, 1, sa, sb, ssv}; n++; off += 2 * len; return o; };
+    auto norm = [&](int base, int wa, int wb, int ba, int bb) { NormOff r; r.w_d = delta(H, base + wa, base + wb); r.b_d = delta(H, base + ba, base + bb); return r; };
+    auto mlp = [&](int base, int up_a, int up_b, int bu_a, int bu_b, int dn_a, int dn_b, int bd_a, int bd_b) {
+        MlpOff r;
+        r.up_b = plain(H, base + up_b);
+        r.up_a = plain(4 * H, base + up_a);
+        r.bup_d = delta(4 * H, base + bu_a, base + bu_b);
+        r.dn_b = plain(4 * H, base + dn_b);
+        r.dn_a = plain(H, base + dn_a);
+        r.bdn_d = delta(H, base + bd_a, base + bd_b);
+        return r;
+    };
+    // seed offsets: mgpu.cu:114-165
+    map->emb_a = plain(V, 0);
+    map->emb_b = plain(H, 0 + H);
+    map->emb_bias_d = delta(H, 50, 51);
+    map->ln_init = norm(0, 500, 501, 502, 503);
+    map->ln_f = norm(0, 900, 901, 910, 911);
+    map->mlp_init = mlp(0, 510, 511, 514, 515, 512, 513, 516, 517);
+    map->layer0 = off;
+    for (int l = 0; l < c.n_layers; l++) {
+        int base = l * 1000, start = off;
+        LayerOff lo;
+        lo.ln1 = norm(base, 100, 101, 110, 111);
+        lo.qkv_b = plain(H, base + 201); plain(H, base + 203); plain(H, base + 205);
+        lo.qkv_a = plain(H, base + 200); plain(H, base + 202); plain(H, base + 204);
+        lo.o_b = plain(H, base + 207);
+        lo.o_a = plain(H, base + 206);
+        lo.ln2 = norm(base, 300, 301, 310, 311);
+        lo.mlp = mlp(base, 400, 401, 410, 411, 402, 403, 412, 413);
+        if (l == 0) {
+            map->layer_stride = off - start;
+            LayerOff rel = lo;
+            int *pi = reinterpret_cast<int *>(&rel);
+            for (size_t i = 0; i < sizeof(LayerOff) / sizeof(int); i++) pi[i] -= start;
+            map->layer_rel = rel;
+        }
+    }
+    map->stride = (off + 15) & ~15;
+    *nsegs = n;
+}
+
+__global__ void noise_fill_kernel(int8_t *nt, int64_t stride, const NoiseSeg *segs, int nsegs, uint32_t step_seed,
+                                  int pair_base, int mask, int gaussian) {
+    extern __shared__ NoiseSeg s_segs[];
+    for (int i = threadIdx.x; i < nsegs; i += blockDim.x) s_segs[i] = segs[i];
+    __syncthreads();
+    const int pair = blockIdx.y;
+    const uint32_t S0 = step_seed + (uint32_t)(pair_base + pair);
+    int8_t *dst = nt + (int64_t)pair * stride;
+    for (int o = blockIdx.x * blockDim.x + threadIdx.x; o < (int)stride; o += gridDim.x * blockDim.x) {
+        int lo = 0, hi = nsegs - 1;
+        while (lo < hi) { int mid = (lo + hi + 1) >> 1; if (s_segs[mid].off <= o) lo = mid; else hi = mid - 1; }
+        const NoiseSeg sg = s_segs[lo];
+        int rel = o - sg.off, val = 0;
+        if (sg.kind == 0) {
+            if (rel < sg.len) val = noise_from_hash(S0 + (uint32_t)sg.seed_a, (uint32_t)rel, mask, gaussian);
+        } else if (rel < 2 * sg.len) {
+            int neg = rel >= sg.len, i = neg ? rel - sg.len : rel;
+            int prod = noise_from_hash(S0 + (uint32_t)sg.seed_a, (uint32_t)i, mask, gaussian) *
+                       noise_from_hash(S0 + (uint32_t)sg.seed_b, (uint32_t)i, mask, gaussian);
+            val = (neg ? -prod : prod) >> sg.shift;
+        }
+        dst[o] = (int8_t)val;
+    }
+}
+
+int launch_noise_fill(cudaStream_t st, int8_t *nt, int64_t stride, const NoiseSeg *d_segs, int nsegs, int n_pairs,
+                      uint32_t step_seed, int pair_base, int mask, int gaussian) {
+    int gx = (int)((stride + 255) / 256); if (gx > 64) gx = 64;
+    dim3 grid((unsigned)gx, (unsigned)n_pairs);
+    noise_fill_kernel<<<grid, 256, nsegs * sizeof(NoiseSeg), st>>>(nt, stride, d_segs, nsegs, step_seed, pair_base, mask, gaussian);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
+
+// =========================================================================
+// row-wise: embedding | adaptive layer normalise -> x ; mean-abs norm -> h ; noise dots
+// =========================================================================
+
+__device__ __forceinline__ int warp_sum(int v) {
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+    return v;
+}
+
+__device__ __forceinline__ int8_t byte_of(int32_t w, int i) { return (int8_t)(w >> (8 * i)); }
+
+// adaptive_layer_normalize / adaptive_qkv_normalize (egg_adaptive_normalize.h:10-103): same float expressions.
+__device__ __forceinline__ int aln_quant(int val, float scale) {
+    float scaled_f = (float)val * scale;
+    int scaled = (int)roundf(scaled_f);
+    if (scaled > 127) scaled = 127;
+    if (scaled < -127) scaled = -127;
+    return scaled;
+}
+__device__ __forceinline__ float aln_scale(int layer_max) { return 127.0f / (float)(layer_max + 1e-9f); }
+
+template <int MODE>
+__global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
+    const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (r >= p.M) return;
+    const int H = p.H, nj = H >> 7;
+    const int mem = r / p.seq_len, t = r % p.seq_len;
+    const int sgn = mem & 1, ns = sgn ? -1 : 1;
+    const int8_t *ntp = p.nt + (int64_t)(mem >> 1) * p.nt_stride;
+    int x[8][4];
+
+    if (MODE == 0) {
+        // embedding (mgpu.cu:902-931)
+        int64_t pair = (p.pop_base + mem) >> 1;
+        int64_t pos = p.use_same_data ? (p.start_idx % (p.data_len - p.seq_len))
+                                      : ((p.start_idx + pair * p.data_stride) % (p.data_len - p.seq_len));
+        const int tok = p.dataset[pos + t];
+        const int a_tok = ntp[p.nt_emb_a + tok];
+        const int32_t *emb32 = reinterpret_cast<const int32_t *>(p.emb_packed);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            if (j >= nj) break;
+            const int d = (j << 7) + (lane << 2);
+            int32_t e4 = emb32[(int64_t)(d >> 2) * p.vocab + tok];
+            int32_t b4 = *reinterpret_cast<const int32_t *>(p.emb_bias + d);
+            int32_t dl4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_emb_bias_d + sgn * H + d);
+            int32_t nb4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_emb_b + d);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                int perturb = (a_tok * (int)byte_of(nb4, i) * ns) >> p.emb_shift;
+                x[j][i] = clip8((int)byte_of(e4, i) + (int)byte_of(b4, i) + (int)byte_of(dl4, i) + perturb);
+            }
+        }
+    } else {
+        const float scale = aln_scale(p.rowmax[r]);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            if (j >= nj) break;
+            const int d = (j << 7) + (lane << 2);
+            int4 v = *reinterpret_cast<const int4 *>(p.pre32 + (int64_t)r * H + d);
+            x[j][0] = aln_quant(v.x, scale); x[j][1] = aln_quant(v.y, scale);
+            x[j][2] = aln_quant(v.z, scale); x[j][3] = aln_quant(v.w, scale);
+        }
+    }
+    int tot = 0;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        if (j >= nj) break;
+        const int d = (j << 7) + (lane << 2);
+        uint32_t w = (uint32_t)(x[j][0] & 0xFF) | ((uint32_t)(x[j][1] & 0xFF) << 8) | ((uint32_t)(x[j][2] & 0xFF) << 16) |
+                     ((uint32_t)(x[j][3] & 0xFF) << 24);
+        *reinterpret_cast<uint32_t *>(p.x_out + (int64_t)r * H + d) = w;
+        tot += abs(x[j][0]) + abs(x[j][1]) + abs(x[j][2]) + abs(x[j][3]);
+    }
+    // mean-abs norm with perturbed gain / bias (mgpu.cu:646-678)
+    tot = warp_sum(tot);
+    int mn = tot / H;
+    if (!mn) mn = 1;
+    int dot0 = 0, dot1 = 0, dot2 = 0;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        if (j >= nj) break;
+        const int d = (j << 7) + (lane << 2);
+        int32_t w4 = *reinterpret_cast<const int32_t *>(p.ln_w + d);
+        int32_t b4 = *reinterpret_cast<const int32_t *>(p.ln_b + d);
+        int32_t wd4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_w_d + sgn * H + d);
+        int32_t bd4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_b_d + sgn * H + d);
+        int y[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            int w_mod = (int)byte_of(w4, i) + (int)byte_of(wd4, i);
+            int b_mod = (int)byte_of(b4, i) + (int)byte_of(bd4, i);
+            y[i] = clip8((x[j][i] * w_mod) / mn + b_mod);
+        }
+        uint32_t w = (uint32_t)(y[0] & 0xFF) | ((uint32_t)(y[1] & 0xFF) << 8) | ((uint32_t)(y[2] & 0xFF) << 16) |
+                     ((uint32_t)(y[3] & 0xFF) << 24);
+        *reinterpret_cast<uint32_t *>(p.h_out + (int64_t)r * H + d) = w;
+        if (p.ndots > 0) {
+            int32_t n4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[0] + d);
+#pragma unroll
+            for (int i = 0; i < 4; i++) dot0 += y[i] * (int)byte_of(n4, i);
+        }
+        if (p.ndots > 1) {
+            int32_t n4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[1] + d);
+#pragma unroll
+            for (int i = 0; i < 4; i++) dot1 += y[i] * (int)byte_of(n4, i);
+        }
+        if (p.ndots > 2) {
+            int32_t n4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[2] + d);
+#pragma unroll
+            for (int i = 0; i < 4; i++) dot2 += y[i] * (int)byte_of(n4, i);
+        }
+    }
+    if (p.ndots > 0) { int s = warp_sum(dot0); if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride] = s; }
+    if (p.ndots > 1) { int s = warp_sum(dot1); if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride + 1] = s; }
+    if (p.ndots > 2) { int s = warp_sum(dot2); if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride + 2] = s; }
+    if (lane == 0) {
+        if (MODE == 1) p.rowmax[r] = 0;
+        if (p.zero1) p.zero1[r] = 0;
+        if (p.zero2) p.zero2[r] = 0;
+        if (p.zero3) { p.zero3[(int64_t)r * 3] = 0; p.zero3[(int64_t)r * 3 + 1] = 0; p.zero3[(int64_t)r * 3 + 2] = 0; }
+    }
+}
+
+int launch_rowwise(cudaStream_t st, const RowParams &p, int mode) {
+    int blocks = (p.M + 7) / 8;
+    if (mode == 0) rowwise_kernel<0><<<blocks, 256, 0, st>>>(p);
+    else rowwise_kernel<1><<<blocks, 256, 0, st>>>(p);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
+
+// Q/K/V requantisation (adaptive_qkv_normalize, mgpu.cu:782-784)
+__global__ void __launch_bounds__(256) aqn_kernel(const AqnParams p) {
+    const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (r >= p.M) return;
+    const int H = p.H, nj = H >> 7;
+    for (int which = 0; which < 3; which++) {
+        const float scale = aln_scale(p.rowmax3[(int64_t)r * 3 + which]);
+        int8_t *out = which == 0 ? p.q : (which == 1 ? p.k : p.v);
+        for (int j = 0; j < nj; j++) {
+            const int d = (j << 7) + (lane << 2);
+            int4 v = *reinterpret_cast<const int4 *>(p.pre3 + ((int64_t)r * 3 + which) * H + d);
+            uint32_t w = (uint32_t)(aln_quant(v.x, scale) & 0xFF) | ((uint32_t)(aln_quant(v.y, scale) & 0xFF) << 8) |
+                         ((uint32_t)(aln_quant(v.z, scale) & 0xFF) << 16) | ((uint32_t)(aln_quant(v.w, scale) & 0xFF) << 24);
+            *reinterpret_cast<uint32_t *>(out + (int64_t)r * H + d) = w;
+        }
+    }
+}
+
+int launch_aqn(cudaStream_t st, const AqnParams &p) {
+    aqn_kernel<<<(p.M + 7) / 8, 256, 0, st>>>(p);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
+
+// =========================================================================
+// causal integer-softmax attention (mgpu.cu:787-825), one block per (member, head)
+// =========================================================================
+// Scores and weighted sums run on the int8 tensor-core path (mma.sync m16n8k32):
+// exact, because every partial sum is proven to fit int32 — scores <= 64*127^2,
+// and the 19-bit softmax weights are split into three 7-bit limbs so that each
+// limb's Σ w·v <= 127*127*seq_len; the limbs are recombined in int64 before the
+// reference's truncating division.
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int ATT_KP = 80;   // K row pitch in shared memory (bytes): conflict-free fragment loads
+
+__global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) uint8_t att_smem[];
+    const int S = p.seq_len, SP = (S + 31) & ~31, VP = SP + 16, H = p.H;
+    int8_t *Ks = reinterpret_cast<int8_t *>(att_smem);          // [SP][80]
+    int8_t *Vt = Ks + SP * ATT_KP;                               // [64][VP]
+    int32_t *lut = reinterpret_cast<int32_t *>(Vt + 64 * VP);    // [256]
+    const int n_heads = H / 64;
+    const int mem = blockIdx.x / n_heads, hd = blockIdx.x % n_heads;
+    const int64_t base = (int64_t)mem * S;
+    const int col0 = hd * 64;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    for (int i = tid; i < SP * 4; i += 128) {
+        int row = i >> 2, ch = i & 3;
+        int4 v = make_int4(0, 0, 0, 0);
+        if (row < S) v = *reinterpret_cast<const int4 *>(p.k + (base + row) * H + col0 + ch * 16);
+        *reinterpret_cast<int4 *>(Ks + row * ATT_KP + ch * 16) = v;
+    }
+    for (int i = tid; i < SP * 4; i += 128) {
+        int row = i >> 2, ch = i & 3;
+        int4 v = make_int4(0, 0, 0, 0);
+        if (row < S) v = *reinterpret_cast<const int4 *>(p.v + (base + row) * H + col0 + ch * 16);
+        const int8_t *b = reinterpret_cast<const int8_t *>(&v);
+#pragma unroll
+        for (int j = 0; j < 16; j++) Vt[(ch * 16 + j) * VP + row] = b[j];
+    }
+    for (int i = tid; i < 256; i += 128) lut[i] = p.exp_lut[i];
+    __syncthreads();
+
+    const int g = lane >> 2, q = lane & 3;
+    const int8_t *nbo = p.nt + (int64_t)(mem >> 1) * p.nt_stride + p.nt_o_b + col0;
+    const int sh = p.shift_attn;
+
+    for (int qb = warp; qb < S / 16; qb += 4) {
+        const int q0 = qb * 16;
+        const int row0 = q0 + g, row1 = q0 + g + 8;
+        uint32_t qa[2][4];
+#pragma unroll
+        for (int ks = 0; ks < 2; ks++) {
+            const int8_t *qp0 = p.q + (base + row0) * H + col0 + 32 * ks + 4 * q;
+            const int8_t *qp1 = p.q + (base + row1) * H + col0 + 32 * ks + 4 * q;
+            qa[ks][0] = *reinterpret_cast<const uint32_t *>(qp0);
+            qa[ks][1] = *reinterpret_cast<const uint32_t *>(qp1);
+            qa[ks][2] = *reinterpret_cast<const uint32_t *>(qp0 + 16);
+            qa[ks][3] = *reinterpret_cast<const uint32_t *>(qp1 + 16);
+        }
+        const int nkb = (q0 + 15) / 32 + 1;
+
+        // ---- pass 1: row maxima over ctx <= t (mgpu.cu:795-802) ----
+        int mx0 = INT_MIN, mx1 = INT_MIN;
+        for (int kb = 0; kb < nkb; kb++) {
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+                int c[4] = {0, 0, 0, 0};
+                const int8_t *kp = Ks + (kb * 32 + nt * 8 + g) * ATT_KP + 4 * q;
+#pragma unroll
+                for (int ks = 0; ks < 2; ks++)
+                    mma_s8(c, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], *reinterpret_cast<const uint32_t *>(kp + 32 * ks),
+                           *reinterpret_cast<const uint32_t *>(kp + 32 * ks + 16));
+                const int key = kb * 32 + nt * 8 + 2 * q;
+                if (key <= row0) mx0 = max(mx0, c[0]);
+                if (key + 1 <= row0) mx0 = max(mx0, c[1]);
+                if (key <= row1) mx1 = max(mx1, c[2]);
+                if (key + 1 <= row1) mx1 = max(mx1, c[3]);
+            }
+        }
+        mx0 = max(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 1)); mx0 = max(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 2));
+        mx1 = max(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 1)); mx1 = max(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 2));
+        const int mxs0 = mx0 >> sh, mxs1 = mx1 >> sh;
+
+        // ---- pass 2: weights, Σ w·v in three 7-bit limbs (mgpu.cu:810-824) ----
+        int acc[8][3][4];
+#pragma unroll
+        for (int a = 0; a < 8; a++)
+#pragma unroll
+            for (int l = 0; l < 3; l++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) acc[a][l][i] = 0;
+        uint32_t tot0 = 0, tot1 = 0;
+        for (int kb = 0; kb < nkb; kb++) {
+            int w[4][4];
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+                int c[4] = {0, 0, 0, 0};
+                const int8_t *kp = Ks + (kb * 32 + nt * 8 + g) * ATT_KP + 4 * q;
+#pragma unroll
+                for (int ks = 0; ks < 2; ks++)
+                    mma_s8(c, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], *reinterpret_cast<const uint32_t *>(kp + 32 * ks),
+                           *reinterpret_cast<const uint32_t *>(kp + 32 * ks + 16));
+                const int key = kb * 32 + nt * 8 + 2 * q;
+                w[nt][0] = (key <= row0) ? lut[min(255, mxs0 - (c[0] >> sh))] : 0;
+                w[nt][1] = (key + 1 <= row0) ? lut[min(255, mxs0 - (c[1] >> sh))] : 0;
+                w[nt][2] = (key <= row1) ? lut[min(255, mxs1 - (c[2] >> sh))] : 0;
+                w[nt][3] = (key + 1 <= row1) ? lut[min(255, mxs1 - (c[3] >> sh))] : 0;
+                tot0 += (uint32_t)(w[nt][0] + w[nt][1]);
+                tot1 += (uint32_t)(w[nt][2] + w[nt][3]);
+            }
+            // A fragments of the three limbs; k-slot 4q+{0,1,2,3} <-> keys {2q, 2q+1, 8+2q, 9+2q} (+16 for a2/a3)
+            uint32_t al[3][4];
+#pragma unroll
+            for (int l = 0; l < 3; l++) {
+                const int s = 7 * l;
+#define LIMB(x) ((uint32_t)(((x) >> s) & 127))
+                al[l][0] = LIMB(w[0][0]) | (LIMB(w[0][1]) << 8) | (LIMB(w[1][0]) << 16) | (LIMB(w[1][1]) << 24);
+                al[l][1] = LIMB(w[0][2]) | (LIMB(w[0][3]) << 8) | (LIMB(w[1][2]) << 16) | (LIMB(w[1][3]) << 24);
+                al[l][2] = LIMB(w[2][0]) | (LIMB(w[2][1]) << 8) | (LIMB(w[3][0]) << 16) | (LIMB(w[3][1]) << 24);
+                al[l][3] = LIMB(w[2][2]) | (LIMB(w[2][3]) << 8) | (LIMB(w[3][2]) << 16) | (LIMB(w[3][3]) << 24);
+#undef LIMB
+            }
+#pragma unroll
+            for (int dn = 0; dn < 8; dn++) {
+                const int8_t *vp = Vt + (dn * 8 + g) * VP + kb * 32 + 2 * q;
+                uint32_t b0 = (uint32_t)*reinterpret_cast<const uint16_t *>(vp) | ((uint32_t)*reinterpret_cast<const uint16_t *>(vp + 8) << 16);
+                uint32_t b1 = (uint32_t)*reinterpret_cast<const uint16_t *>(vp + 16) | ((uint32_t)*reinterpret_cast<const uint16_t *>(vp + 24) << 16);
+#pragma unroll
+                for (int l = 0; l < 3; l++) mma_s8(acc[dn][l], al[l][0], al[l][1], al[l][2], al[l][3], b0, b1);
+            }
+        }
+        tot0 += __shfl_xor_sync(0xFFFFFFFFu, tot0, 1); tot0 += __shfl_xor_sync(0xFFFFFFFFu, tot0, 2);
+        tot1 += __shfl_xor_sync(0xFFFFFFFFu, tot1, 1); tot1 += __shfl_xor_sync(0xFFFFFFFFu, tot1, 2);
+        const long long den0 = tot0 ? (long long)tot0 : 1, den1 = tot1 ? (long long)tot1 : 1;
+        int dot0 = 0, dot1 = 0;
+#pragma unroll
+        for (int dn = 0; dn < 8; dn++) {
+            int o[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                long long num = (long long)acc[dn][0][i] + ((long long)acc[dn][1][i] << 7) + ((long long)acc[dn][2][i] << 14);
+                o[i] = clip8((int)(num / (i < 2 ? den0 : den1)));
+            }
+            const int dim = dn * 8 + 2 * q;
+            *reinterpret_cast<uint16_t *>(p.ao + (base + row0) * H + col0 + dim) = (uint16_t)((o[0] & 0xFF) | ((o[1] & 0xFF) << 8));
+            *reinterpret_cast<uint16_t *>(p.ao + (base + row1) * H + col0 + dim) = (uint16_t)((o[2] & 0xFF) | ((o[3] & 0xFF) << 8));
+            const int nb0 = nbo[dim], nb1 = nbo[dim + 1];
+            dot0 += o[0] * nb0 + o[1] * nb1;
+            dot1 += o[2] * nb0 + o[3] * nb1;
+        }
+        dot0 += __shfl_xor_sync(0xFFFFFFFFu, dot0, 1); dot0 += __shfl_xor_sync(0xFFFFFFFFu, dot0, 2);
+        dot1 += __shfl_xor_sync(0xFFFFFFFFu, dot1, 1); dot1 += __shfl_xor_sync(0xFFFFFFFFu, dot1, 2);
+        if (q == 0) {
+            atomicAdd(&p.xbo[base + row0], dot0);
+            atomicAdd(&p.xbo[base + row1], dot1);
+        }
+    }
+}
+
+static size_t attention_smem_bytes(int S) {
+    int SP = (S + 31) & ~31;
+    return (size_t)SP * ATT_KP + 64 * (size_t)(SP + 16) + 256 * 4;
+}
+
+int launch_attention(cudaStream_t st, const AttnParams &p) {
+    size_t smem = attention_smem_bytes(p.seq_len);
+    static size_t configured = 0;
+    if (smem > configured) {
+        EGG_CUDA(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    int blocks = p.members * (p.H / 64);
+    attention_kernel<<<blocks, 128, smem, st>>>(p);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
+
+// =========================================================================
+// weights: packed [K/4][N][4] -> K-major shadow [N][K]
+// =========================================================================
+__global__ void unpack_transpose_kernel(const int32_t *packed, int8_t *shadow, int rows_k, int cols_n) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t words = (int64_t)(rows_k >> 2) * cols_n;
+    if (i >= words) return;
+    // consecutive threads take consecutive k4 of one output column: 128-byte coalesced writes
+    int k4 = (int)(i % (rows_k >> 2));
+    int n = (int)(i / (rows_k >> 2));
+    int32_t w = packed[(int64_t)k4 * cols_n + n];
+    *reinterpret_cast<int32_t *>(shadow + (int64_t)n * rows_k + 4 * k4) = w;
+}
+
+int launch_unpack_transpose(cudaStream_t st, const int8_t *packed, int8_t *shadow, int rows_k, int cols_n) {
+    int64_t words = (int64_t)(rows_k >> 2) * cols_n;
+    unpack_transpose_kernel<<<(unsigned)((words + 255) / 256), 256, 0, st>>>(reinterpret_cast<const int32_t *>(packed), shadow, rows_k, cols_n);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
+
+// =========================================================================
+// fitness (mgpu.cu:1031-1036)
+// =========================================================================
+__global__ void fitness_kernel(const int32_t *loss, int32_t *fit, int pairs) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= pairs) return;
+    int32_t pz = loss[2 * i], n = loss[2 * i + 1];
+    fit[i] = (pz < n) ? 1 : ((n < pz) ? -1 : 0);
+}
+int launch_fitness(cudaStream_t st, const int32_t *loss, int32_t *fit, int pairs) {
+    fitness_kernel<<<(pairs + 255) / 256, 256, 0, st>>>(loss, fit, pairs);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
+
+// =========================================================================
+// update operands: the two noise matrices of vote = Σ_p f_p a_p b_p^T, pair index contiguous
+// =========================================================================
+__global__ void update_operands_kernel(int8_t *na, int8_t *nb, const int32_t *fit, int pairs, int kp, int rows_k, int cols_n,
+                                       int off_a, int off_b, int seed_base, uint32_t step_seed, int mask, int gaussian, int split) {
+    const int row = blockIdx.y;                 // 0..cols_n-1 -> NA, cols_n.. -> NB
+    const int ktot = split ? 2 * kp : kp;
+    for (int pp = blockIdx.x * blockDim.x + threadIdx.x; pp < ktot; pp += gridDim.x * blockDim.x) {
+        const int hi = pp >= kp;
+        const int pidx = hi ? pp - kp : pp;
+        int val = 0;
+        if (pidx < pairs) {
+            const uint32_t s = step_seed + (uint32_t)pidx + (uint32_t)seed_base;    // mgpu.cu:1095
+            if (row < cols_n) {
+                int f = fit[pidx];
+                if (split) { int f1 = f >> 4, f0 = f - (f1 << 4); f = hi ? f1 : f0; }
+                val = f * noise_from_hash(s + (uint32_t)off_a, (uint32_t)row, mask, gaussian);
+            } else {
+                val = noise_from_hash(s + (uint32_t)off_b, (uint32_t)(row - cols_n), mask, gaussian);
+                if (hi) val *= 16;
+            }
+        }
+        if (row < cols_n) na[(int64_t)row * ktot + pp] = (int8_t)val;
+        else nb[(int64_t)(row - cols_n) * ktot + pp] = (int8_t)val;
+    }
+}
+
+int launch_update_operands(cudaStream_t st, int8_t *na, int8_t *nb, const int32_t *fit, int pairs, int kp, int rows_k,
+                           int cols_n, int off_a, int off_b, int seed_base, uint32_t step_seed, int mask, int gaussian,
+                           int split) {
+    int ktot = split ? 2 * kp : kp;
+    int gx = (ktot + 255) / 256; if (gx > 32) gx = 32;
+    dim3 grid((unsigned)gx, (unsigned)(rows_k + cols_n));
+    update_operands_kernel<<<grid, 256, 0, st>>>(na, nb, fit, pairs, kp, rows_k, cols_n, off_a, off_b, seed_base, step_seed, mask, gaussian, split);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
+
+// =========================================================================
+// vector parameters (update_vector_adam_kernel, mgpu.cu:1114-1152): one block per element
+// =========================================================================
+__global__ void __launch_bounds__(256) update_vector_kernel(const VecUpdParams p) {
+    const int idx = blockIdx.x;
+    int vote = 0;
+    for (int pr = threadIdx.x; pr < p.pairs; pr += blockDim.x) {
+        int f = p.fit[pr];
+        if (f == 0) continue;
+        uint32_t s = p.step_seed + (uint32_t)pr + (uint32_t)p.seed_base;
+        vote += f * noise_from_hash(s + (uint32_t)p.off_a, (uint32_t)idx, p.mask, p.gaussian) *
+                noise_from_hash(s + (uint32_t)p.off_b, (uint32_t)idx, p.mask, p.gaussian);
+    }
+    __shared__ int s_part[8];
+    vote = warp_sum(vote);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = vote;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int total = 0;
+        for (int i = 0; i < 8; i++) total += s_part[i];
+        float m = p.opt[idx * 3], v = p.opt[idx * 3 + 1], acc = p.opt[idx * 3 + 2];
+        int w = p.v[idx];
+        int ch = adam_apply(m, v, acc, w, -(float)total, p.lr, p.beta1, p.beta2, p.eps, p.wd);
+        p.opt[idx * 3] = m; p.opt[idx * 3 + 1] = v; p.opt[idx * 3 + 2] = acc;
+        p.v[idx] = (int8_t)w;
+        if (ch) atomicAdd(p.total_updates, 1ull);
+    }
+}
+int launch_update_vector(cudaStream_t st, const VecUpdParams &p) {
+    update_vector_kernel<<<p.len, 256, 0, st>>>(p);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
+
+// =========================================================================
+// Muon: Frobenius normalise + 5 cubic Newton–Schulz steps in fp32 (muon_internal.cuh:182-342)
+// =========================================================================
+__global__ void sumsq_kernel(const float *x, int64_t n, double *out) {
+    // double accumulation: the result feeds one fp32 division per element
+    double s = 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) s += (double)x[i] * x[i];
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
+    __shared__ double part[8];
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0;
+        for (int i = 0; i < (int)(blockDim.x >> 5); i++) t += part[i];
+        atomicAdd(out, t);
+    }
+}
+__global__ void scale_by_norm_kernel(float *x, int64_t n, const double *sumsq) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float norm = (float)sqrt(*sumsq);
+    if (norm > 1e-6f) x[i] /= norm;          // muon_scale_by_norm_kernel, muon_internal.cuh:77-85
+}
+
+// C[i][j] = alpha * Σ_t A(i,t) B(t,j), strided operands, optional "3I - C" epilogue.
+// 64x64 tile, 16-deep steps, 256 threads x (4x4) outputs, plain FFMA.
+__global__ void __launch_bounds__(256) sgemm_strided_kernel(const float *A, int64_t as0, int64_t as1, const float *B, int64_t bs0,
+                                                            int64_t bs1, float *C, int Mm, int Nn, int Kk, float alpha, int three_i_minus) {
+    __shared__ float sa[16][64 + 4], sb[16][64 + 4];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int i0 = blockIdx.y * 64, j0 = blockIdx.x * 64;
+    float acc[4][4] = {};
+    for (int t0 = 0; t0 < Kk; t0 += 16) {
+        for (int e = threadIdx.x; e < 64 * 16; e += 256) {
+            int a_i, a_t, b_t, b_j;
+            if (as1 == 1) { a_t = e & 15; a_i = e >> 4; } else { a_i = e & 63; a_t = e >> 6; }
+            if (bs1 == 1) { b_j = e & 63; b_t = e >> 6; } else { b_t = e & 15; b_j = e >> 4; }
+            int gi = i0 + a_i, gt = t0 + a_t;
+            sa[a_t][a_i] = (gi < Mm && gt < Kk) ? A[gi * as0 + gt * as1] : 0.0f;
+            int gj = j0 + b_j, gt2 = t0 + b_t;
+            sb[b_t][b_j] = (gj < Nn && gt2 < Kk) ? B[gt2 * bs0 + gj * bs1] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int t = 0; t < 16; t++) {
+            float a[4], b[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) { a[u] = sa[t][ty * 4 + u]; b[u] = sb[t][tx * 4 + u]; }
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int w = 0; w < 4; w++) acc[u][w] = fmaf(a[u], b[w], acc[u][w]);
+        }
+        __syncthreads();
+    }
+    for (int u = 0; u < 4; u++)
+        for (int w = 0; w < 4; w++) {
+            int i = i0 + ty * 4 + u, j = j0 + tx * 4 + w;
+            if (i < Mm && j < Nn) {
+                float val = alpha * acc[u][w];
+                if (three_i_minus) val = (i == j) ? 3.0f - val : -val;     // muon_newton_schulz_term_kernel, :91-109
+                C[(int64_t)i * Nn + j] = val;
+            }
+        }
+}
+
+int launch_newton_schulz(cudaStream_t st, const MuonWs &ws, int rows, int cols) {
+    const int64_t n = (int64_t)rows * cols;
+    const bool use_rows = rows < cols;
+    const int K = use_rows ? rows : cols;
+    EGG_CUDA(cudaMemsetAsync(ws.norm2, 0, sizeof(double), st));
+    sumsq_kernel<<<256, 256, 0, st>>>(ws.x, n, ws.norm2);
+    scale_by_norm_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ws.x, n, ws.norm2);
+    float *x = ws.x, *y = ws.y;
+    for (int it = 0; it < 5; it++) {
+        dim3 gg((K + 63) / 64, (K + 63) / 64);
+        if (use_rows)   // G = X X^T : A(i,t)=X[i][t], B(t,j)=X[j][t]
+            sgemm_strided_kernel<<<gg, 256, 0, st>>>(x, cols, 1, x, 1, cols, ws.g, K, K, cols, 1.0f, 1);
+        else            // G = X^T X : A(i,t)=X[t][i], B(t,j)=X[t][j]
+            sgemm_strided_kernel<<<gg, 256, 0, st>>>(x, 1, cols, x, cols, 1, ws.g, K, K, rows, 1.0f, 1);
+        dim3 gy((cols + 63) / 64, (rows + 63) / 64);
+        if (use_rows)   // Y = 0.5 * B X
+            sgemm_strided_kernel<<<gy, 256, 0, st>>>(ws.g, K, 1, x, cols, 1, y, rows, cols, K, 0.5f, 0);
+        else            // Y = 0.5 * X B
+            sgemm_strided_kernel<<<gy, 256, 0, st>>>(x, cols, 1, ws.g, K, 1, y, rows, cols, K, 0.5f, 0);
+        float *tmp = x; x = y; y = tmp;
+    }
+    // five swaps: the result lives in ws.y; copy back so callers always read ws.x
+    EGG_CUDA(cudaMemcpyAsync(ws.x, x, n * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
+
+// muon_apply_update_kernel (muon_internal.cuh:112-166)
+__global__ void muon_apply_kernel(int8_t *w_packed, float *opt, const float *upd, int rows_k, int cols_n, float lr, float wd,
+                                  unsigned long long *total_updates) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int change = 0;
+    if (idx < (int64_t)rows_k * cols_n) {
+        int byte_off = (int)(idx & 3);
+        int64_t word = idx >> 2;
+        int n = (int)(word % cols_n), k = (int)(word / cols_n) * 4 + byte_off;
+        int8_t w = w_packed[idx];
+        float acc = opt[idx * 2 + 1];
+        float u = upd[(int64_t)k * cols_n + n];
+        float step = -lr * (u + wd * (float)w);
+        acc += step;
+        if (acc >= 1.0f) {
+            if (w < 127) { w++; change = 1; acc -= 1.0f; } else acc = 1.0f;
+        } else if (acc <= -1.0f) {
+            if (w > -127) { w--; change = 1; acc += 1.0f; } else acc = -1.0f;
+        }
+        w_packed[idx] = w;
+        opt[idx * 2 + 1] = acc;
+    }
+    unsigned ballot = __ballot_sync(0xFFFFFFFFu, change);
+    if ((threadIdx.x & 31) == 0 && ballot) atomicAdd(total_updates, (unsigned long long)__popc(ballot));
+}
+int launch_muon_apply(cudaStream_t st, int8_t *w_packed, float *opt, const float *upd_rowmajor, int rows_k, int cols_n,
+                      float lr, float wd, unsigned long long *total_updates) {
+    int64_t n = (int64_t)rows_k * cols_n;
+    muon_apply_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(w_packed, opt, upd_rowmajor, rows_k, cols_n, lr, wd, total_updates);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
+
+}  // namespace egg

@@ -1,0 +1,111 @@
+// Declarations shared between the kernel translation units and the C-ABI layer.
+#pragma once
+
+#include <cuda.h>
+#include "egg_common.cuh"
+#include "egg_gemm.cuh"
+
+namespace egg {
+
+// ---- per-pair noise table -------------------------------------------------
+// Every noise vector a wave needs is generated once per (pair, generation) by
+// the counter hash and kept in HBM/L2; the 2*seq_len rows of a pair share it.
+struct NoiseSeg {
+    int off;        // byte offset inside the pair's table
+    int len;        // elements (a delta segment occupies 2*len bytes: [+sign][len], [-sign][len])
+    int kind;       // 0: noise(S0+seed_a, i)   1: ((n(S0+seed_a,i)*n(S0+seed_b,i)*sign) >> shift) per sign
+    int seed_a, seed_b;
+    int shift;
+};
+
+struct NormOff { int w_d, b_d; };                       // delta [2][H] each
+struct MlpOff { int up_b, up_a, bup_d, dn_b, dn_a, bdn_d; };
+struct LayerOff { NormOff ln1; int qkv_b; int qkv_a; int o_b, o_a; NormOff ln2; MlpOff mlp; };
+
+struct NoiseMap {
+    int64_t stride;          // bytes per pair (multiple of 16)
+    int emb_a, emb_b, emb_bias_d;
+    NormOff ln_init, ln_f;
+    MlpOff mlp_init;
+    int layer0, layer_stride;   // byte offset of layer 0 block, bytes per layer block
+    LayerOff layer_rel;         // offsets relative to the layer block
+};
+
+// Builds the map and the segment list for a configuration (host).
+void build_noise_map(const egg_config &c, NoiseMap *map, NoiseSeg *segs, int *nsegs, int max_segs);
+
+int launch_noise_fill(cudaStream_t st, int8_t *nt, int64_t stride, const NoiseSeg *d_segs, int nsegs, int n_pairs,
+                      uint32_t step_seed, int pair_base, int mask, int gaussian);
+
+// ---- row-wise kernels -------------------------------------------------------
+struct RowParams {
+    int M, H, seq_len;
+    const int8_t *nt; int64_t nt_stride;
+    // source: embedding (mode 0) or adaptive layer normalise of pre32 (mode 1)
+    const uint8_t *dataset; int64_t data_len, start_idx, data_stride; int pop_base, use_same_data;
+    const int8_t *emb_packed; const int8_t *emb_bias; int vocab;
+    int nt_emb_a, nt_emb_b, nt_emb_bias_d, emb_shift;
+    const int32_t *pre32; int32_t *rowmax;
+    // residual stream out
+    int8_t *x_out;
+    // mean-abs norm (apply_standard_norm, mgpu.cu:646-678)
+    const int8_t *ln_w, *ln_b; int nt_w_d, nt_b_d;
+    int8_t *h_out;
+    // Σ_d h_d * noise_B[d] for up to three following projections
+    int ndots; int nt_dot[3]; int32_t *xb_out; int xb_stride;
+    // accumulators to clear for the kernels that follow
+    int32_t *zero1;      // [M]
+    int32_t *zero2;      // [M]
+    int32_t *zero3;      // [M][3]
+};
+int launch_rowwise(cudaStream_t st, const RowParams &p, int mode);
+
+struct AqnParams {
+    int M, H;
+    const int32_t *pre3;      // [M][3H]
+    const int32_t *rowmax3;   // [M][3]
+    int8_t *q, *k, *v;        // [M][H] each
+};
+int launch_aqn(cudaStream_t st, const AqnParams &p);
+
+struct AttnParams {
+    int members, H, head_dim, seq_len, shift_attn;
+    const int8_t *q, *k, *v;  // [members*seq_len][H]
+    int8_t *ao;               // [members*seq_len][H]
+    const int32_t *exp_lut;
+    const int8_t *nt; int64_t nt_stride; int nt_o_b;
+    int32_t *xbo;             // [members*seq_len] += Σ_d ao_d * noise_B_o[d]
+};
+int launch_attention(cudaStream_t st, const AttnParams &p);
+
+// ---- weights ----------------------------------------------------------------
+// packed [K/4][N][4] -> K-major shadow [N][K]
+int launch_unpack_transpose(cudaStream_t st, const int8_t *packed, int8_t *shadow, int rows_k, int cols_n);
+
+// ---- GEMM -------------------------------------------------------------------
+// A: [M][K] int8 row-major, B: [N][K] int8 row-major (both device pointers).
+int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, const GemmParams &p, int num_sms);
+int gemm_init();   // resolves the driver entry point for tensor-map encoding, sets smem attributes
+
+// ---- fitness / update -------------------------------------------------------
+int launch_fitness(cudaStream_t st, const int32_t *loss, int32_t *fit, int pairs);
+
+// operand generation for the update GEMM: NA[n][Kp] = f_p * noise(s_p+off_a, n), NB[k][Kp] = noise(s_p+off_b, k)
+// split = 1 doubles the contraction: [f0*a | f1*a] x [b ; 16 b] with f = 16 f1 + f0.
+int launch_update_operands(cudaStream_t st, int8_t *na, int8_t *nb, const int32_t *fit, int pairs, int kp, int rows_k,
+                           int cols_n, int off_a, int off_b, int seed_base, uint32_t step_seed, int mask, int gaussian,
+                           int split);
+
+struct VecUpdParams {
+    int8_t *v; float *opt; int len; int off_a, off_b, seed_base; const int32_t *fit; int pairs;
+    uint32_t step_seed; float lr, beta1, beta2, eps, wd; int mask, gaussian; unsigned long long *total_updates;
+};
+int launch_update_vector(cudaStream_t st, const VecUpdParams &p);
+
+// Muon (muon_internal.cuh:77-342): Frobenius normalise, 5 Newton–Schulz steps, quantised apply.
+struct MuonWs { float *x, *g, *y; double *norm2; };   // x: rows*cols, g: K*K, y: rows*cols, norm2: 1
+int launch_newton_schulz(cudaStream_t st, const MuonWs &ws, int rows, int cols);
+int launch_muon_apply(cudaStream_t st, int8_t *w_packed, float *opt, const float *upd_rowmajor, int rows_k, int cols_n,
+                      float lr, float wd, unsigned long long *total_updates);
+
+}  // namespace egg

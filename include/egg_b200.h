@@ -1,0 +1,195 @@
+/*
+ * egg_b200.h — C ABI of the B200-native EGGROLL population-evaluation path.
+ *
+ * The reference project (d0rc/egg.c) has no library interface: its hot path is
+ * a handful of kernel launches inside main() of
+ * full_cuda_train_transformer_adam_mgpu.cu and d-eggs/src/worker.cu.  Every
+ * entry point below stands where one of those launches (or the host code
+ * between them) stands, takes plain pointers and sizes, and returns 0 or a
+ * negative EGG_E_* code.  No exceptions cross the boundary, nothing here
+ * falls back to the CPU: if the CUDA side is unavailable the call fails.
+ *
+ * Threading: one host thread per egg_ctx; all work is enqueued on the
+ * context's stream; egg_sync() and the *_host / read_* calls block.
+ */
+#ifndef EGG_B200_H
+#define EGG_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- error codes ------------------------------------------------------- */
+#define EGG_OK            0
+#define EGG_E_INVALID    -1   /* bad argument / unsupported configuration      */
+#define EGG_E_CUDA       -2   /* a CUDA runtime / driver call failed            */
+#define EGG_E_NOMEM      -3   /* device or host allocation failed               */
+#define EGG_E_TIMEOUT    -4   /* a bounded device-side wait gave up             */
+#define EGG_E_NCCL       -5   /* an NCCL call failed                            */
+#define EGG_E_STATE      -6   /* call made in the wrong state (no model, ...)   */
+
+/*
+ * Run-time mirror of the reference's compile-time configuration macros
+ * (full_cuda_train_transformer_adam_mgpu.cu:35-270, d-eggs/include/config.h:5-242).
+ * Field names are the lower-cased macro names.  egg_config_defaults() fills in
+ * the reference's own defaults.
+ */
+typedef struct egg_config {
+    int32_t hidden_dim;          /* HIDDEN_DIM  (multiple of 64, <= 1024)          */
+    int32_t head_dim;            /* HEAD_DIM    (64)                                */
+    int32_t n_layers;            /* N_LAYERS                                        */
+    int32_t seq_len;             /* SEQ_LEN     (>= 8)                              */
+    int32_t vocab_size;          /* VOCAB_SIZE  (256: byte tokens)                  */
+    int32_t population_size;     /* POPULATION_SIZE (even)                          */
+    int32_t fixed_point;         /* FIXED_POINT                                     */
+    int32_t sigma_shift;         /* SIGMA_SHIFT                                     */
+    int32_t sigma_shift_vector;  /* SIGMA_SHIFT_VECTOR                              */
+    int32_t shift_attn;          /* SHIFT_ATTN                                      */
+    int32_t shift_out;           /* SHIFT_OUT                                       */
+    int32_t shift_logit;         /* SHIFT_LOGIT                                     */
+    int32_t shift_mlp_up;        /* SHIFT_MLP_UP                                    */
+    int32_t shift_mlp_down;      /* SHIFT_MLP_DOWN                                  */
+    int32_t softmax_scale_bit;   /* SOFTMAX_SCALE_BIT                               */
+    int32_t rope_scale_bit;      /* ROPE_SCALE_BIT                                  */
+    int32_t device_mask;         /* DEVICE_MASK                                     */
+    int32_t device_gaussian;     /* DEVICE_GAUSSIAN (0/1)                           */
+    int32_t host_mask;           /* HOST_MASK (weight initialisation only)          */
+    int32_t use_same_data;       /* USE_SAME_DATA                                   */
+    int32_t use_muon;            /* USE_MUON: hidden matrices use Muon, rest AdamW  */
+    int32_t chunk_relative_loss; /* 0: accum_loss[global member] (mgpu :1028);
+                                    1: accum_loss[member - pop_offset] (d-eggs
+                                       kernels.cu:297)                              */
+    double  softmax_exp_scale;   /* SOFTMAX_EXP_SCALE                               */
+    float   adam_beta1;          /* ADAM_BETA1                                      */
+    float   adam_beta2;          /* ADAM_BETA2                                      */
+    float   adam_eps;            /* ADAM_EPS                                        */
+    float   adam_weight_decay;   /* ADAM_WEIGHT_DECAY                               */
+    float   muon_momentum;       /* MUON_MOMENTUM                                   */
+    float   muon_lr_scale;       /* MUON_LR_SCALE                                   */
+} egg_config;
+
+/* Defaults of full_cuda_train_transformer_adam_mgpu.cu:35-270. */
+void egg_config_defaults(egg_config *cfg);
+
+/* Returns EGG_OK or EGG_E_INVALID; *why (optional) gets a static message. */
+int egg_config_validate(const egg_config *cfg, const char **why);
+
+/* sizeof(TransformerModel) / sizeof(AdamModel) for this configuration
+ * (mgpu.cu:284-370, d-eggs/include/model/definitions.h:21-89). */
+int64_t egg_model_bytes(const egg_config *cfg);
+int64_t egg_opt_state_bytes(const egg_config *cfg);
+
+/* ---- context ----------------------------------------------------------- */
+typedef struct egg_ctx egg_ctx;
+
+/*
+ * One context per process per GPU (≙ struct GPUContext, mgpu.cu:1287-1302).
+ * wave_members: how many population members are evaluated per internal wave
+ * (activation scratch scales with it; 0 picks a default from free memory).
+ */
+int  egg_ctx_create(const egg_config *cfg, int device, int wave_members, egg_ctx **out);
+void egg_ctx_destroy(egg_ctx *ctx);
+/* Message of the last failing call made on this thread ("" if none). */
+const char *egg_last_error(void);
+/* cudaStreamSynchronize of the context stream; also surfaces device-side
+ * timeout flags as EGG_E_TIMEOUT. */
+int  egg_sync(egg_ctx *ctx);
+
+/* ---- model / optimiser bytes (reference layout, host pointers) ---------- */
+/* ≙ cudaMemcpy(d_model, h_model, sizeof(TransformerModel)) (mgpu.cu:1461).
+ * Matrices are in the reference's packed [K/4][N][4] layout (repack_matrix,
+ * mgpu.cu:443-459); the library derives its own K-major shadow copies. */
+int egg_upload_model(egg_ctx *ctx, const void *host_model, int64_t nbytes);
+int egg_download_model(egg_ctx *ctx, void *host_model, int64_t nbytes);
+/* ≙ cudaMemcpy of AdamModel (mgpu.cu:1464). */
+int egg_upload_opt_state(egg_ctx *ctx, const void *host_state, int64_t nbytes);
+int egg_download_opt_state(egg_ctx *ctx, void *host_state, int64_t nbytes);
+
+/* ≙ cudaMemcpy(d_dataset, ds.data, ds.length) (mgpu.cu:1466-1467). Byte tokens. */
+int egg_set_dataset(egg_ctx *ctx, const uint8_t *host_tokens, int64_t n_tokens);
+
+/* ---- evaluation -------------------------------------------------------- */
+/*
+ * ≙ train_sequence_kernel<<<count, ...>>>(dataset, len, start_idx, model, kv,
+ *     accum_loss, step_seed, pop_offset, step)  (mgpu.cu:847-1029, launch :1531;
+ *     d-eggs/src/kernels.cu:90-298, launch worker.cu:626).
+ * Evaluates members [pop_offset, pop_offset+count) (both even) and leaves
+ * int32 losses in the context's device loss buffer.
+ */
+int egg_eval_chunk(egg_ctx *ctx, uint32_t step_seed, int64_t start_idx,
+                   int pop_offset, int count);
+/* ≙ cudaMemcpyAsync(h_loss+off, d_loss+off, n*4, D2H) + sync (mgpu.cu:1537-1552). */
+int egg_read_losses(egg_ctx *ctx, int32_t *host_losses, int offset, int count);
+
+/* ≙ compute_fitness_kernel / compute_fitness_host (mgpu.cu:1031-1036, 1305-1311):
+ * fitness[p] = sign(loss[2p+1] - loss[2p]) for pairs [pair_offset, +pair_count). */
+int egg_compute_fitness_pairs(egg_ctx *ctx, int pair_offset, int pair_count);
+/* ≙ cudaMemcpyAsync(d_fit, h_fit, POP/2*4, H2D) (mgpu.cu:1571). */
+int egg_write_fitness(egg_ctx *ctx, const int32_t *host_fitness, int pair_offset, int pair_count);
+int egg_read_fitness(egg_ctx *ctx, int32_t *host_fitness, int pair_offset, int pair_count);
+
+/* ---- multi-GPU --------------------------------------------------------- */
+/* NCCL communicator over the ranks that share one population.  The caller
+ * obtains the 128-byte unique id on rank 0 and distributes it out of band. */
+int egg_nccl_unique_id(void *id128);
+int egg_comm_init(egg_ctx *ctx, const void *id128, int rank, int world);
+/*
+ * Replaces the reference's host bounce (D2H losses → compute_fitness_host →
+ * H2D to every GPU, mgpu.cu:1537-1571): each rank contributes the fitness of
+ * its contiguous slice of POP/2/world pairs; one ncclAllGather fills the whole
+ * device fitness vector on every rank.
+ */
+int egg_allgather_fitness(egg_ctx *ctx);
+
+/* ---- update ------------------------------------------------------------ */
+/*
+ * ≙ the LAUNCH_ADAM_MATRIX / LAUNCH_ADAM_VECTOR sequence (mgpu.cu:1573-1668):
+ * rebuilds vote = Σ_p fit_p·a_p·b_pᵀ for every parameter from the device
+ * fitness vector and applies ES-AdamW (or Muon for hidden matrices when
+ * use_muon), emb_bias at 0.1·lr.  *total_updates ≙ d_total_updates.
+ */
+int egg_apply_update(egg_ctx *ctx, uint32_t step_seed, float learning_rate,
+                     uint64_t *total_updates);
+
+/*
+ * One whole generation through host buffers (≙ one iteration of the training
+ * loop, mgpu.cu:1506-1688): uploads the dataset bytes if host_tokens != NULL,
+ * evaluates this rank's slice of the population, computes fitness, exchanges
+ * it when a communicator is attached, applies the update, copies this rank's
+ * losses back.  host_losses may be NULL.
+ */
+int egg_generation_host(egg_ctx *ctx, const uint8_t *host_tokens, int64_t n_tokens,
+                        int64_t step, uint32_t step_seed, float learning_rate,
+                        int32_t *host_losses, uint64_t *total_updates);
+
+/* ---- isolated primitives ---------------------------------------------- */
+/*
+ * Perturbed int8 projection, host or device buffers chosen by `on_device`
+ * (≙ compute_linear_projection + ">>8 and clip", mgpu.cu:553-572 and
+ * full_cuda_train_egg_transformer.cu:249):
+ *   y[r][n] = clip((Σ_k x[r][k]·W[k][n] + ((xb_r·a_j[n]·ns_r) >> rank1_shift)) >> out_shift)
+ * with member = r / rows_per_member, j = member/2, ns = +1/-1 for even/odd
+ * member, a_j[n] = noise(seed + j + off_a, n), b_j[k] = noise(seed + j + off_b, k),
+ * xb_r = Σ_k x[r][k]·b_j[k].  W is in the packed [K/4][N][4] layout.
+ */
+int egg_perturbed_projection(egg_ctx *ctx, const int8_t *x, const int8_t *w_packed,
+                             int8_t *y, int64_t rows, int k_dim, int n_dim,
+                             int rows_per_member, uint32_t seed, int off_a, int off_b,
+                             int rank1_shift, int out_shift, int on_device);
+
+/*
+ * Update reconstruction for one matrix (≙ the vote loop of
+ * update_matrix_adam_kernel, mgpu.cu:1092-1098), accepting any int fitness in
+ * [-127,127]: vote[idx] (packed index order) = Σ_p f_p·noise(s_p+off_a, n)·
+ * noise(s_p+off_b, k), s_p = step_seed + p + seed_base.
+ */
+int egg_update_reconstruct(egg_ctx *ctx, const int32_t *fitness, int pairs,
+                           int rows_k, int cols_n, int off_a, int off_b, int seed_base,
+                           uint32_t step_seed, int32_t *vote_out, int on_device);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EGG_B200_H */

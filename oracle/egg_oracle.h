@@ -1,0 +1,98 @@
+/*
+ * egg_oracle.h — CPU restatement of the reference's EGGROLL hot path.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This is the checker the CUDA library is compared
+ * against; the product never links, imports or calls it.  Every function
+ * cites the reference lines it restates ("mgpu.cu" =
+ * full_cuda_train_transformer_adam_mgpu.cu).
+ *
+ * Parity pinning: the reference holds no golden vectors for this path (its
+ * only test is d-eggs/test_ternary.cpp).  The oracle is pinned by (1) the
+ * hash/noise known answers produced by compiling the reference's own
+ * d-eggs/include/utils/egg_math.h with g++ (tests/golden/rng_kat.json),
+ * (2) the ternary codec cases of d-eggs/test_ternary.cpp, and (3) losses /
+ * fitness / post-update weights produced by the reference's own kernels
+ * (built from the reference sources by oracle/Makefile into oracle/_ref/ and
+ * run on a B200), committed under tests/golden/.
+ */
+#ifndef EGG_ORACLE_H
+#define EGG_ORACLE_H
+
+#include <stdint.h>
+#include "../include/egg_b200.h"   /* egg_config only */
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* --- RNG (mgpu.cu:525-538; d-eggs/include/utils/egg_math.h:17-34) --- */
+uint32_t oracle_hash_rng(uint32_t s, uint32_t idx);
+int      oracle_noise(const egg_config *cfg, uint32_t s, uint32_t idx);
+/* host xorshift stream used by init_model (mgpu.cu:428-441) */
+int      oracle_gen_noise_host(const egg_config *cfg, uint32_t *state);
+
+/* --- sizes / layout --- */
+int64_t oracle_model_bytes(const egg_config *cfg);
+int64_t oracle_opt_bytes(const egg_config *cfg);
+int64_t oracle_scales_bytes(const egg_config *cfg);
+
+/* --- tables (mgpu.cu:394-426) --- */
+void oracle_init_tables(const egg_config *cfg, int32_t *exp_lut256, int8_t *act_lut256,
+                        int32_t *rope_lut /* seq_len*head_dim */);
+
+/* --- model initialisation (mgpu.cu:443-519) --- */
+void oracle_repack_matrix(int8_t *dst, const int8_t *src, int rows, int cols);
+void oracle_init_model(const egg_config *cfg, int8_t *model, uint32_t seed);
+
+/* --- evaluation (mgpu.cu:847-1029; d-eggs/src/kernels.cu:90-298) ---
+ * losses_out[i] is the loss of member pop_offset+i (always chunk-relative).
+ * scales: AdaptiveScales bytes (d-eggs/include/model/definitions.h:92-142) or NULL. */
+void oracle_eval(const egg_config *cfg, const int8_t *model, const int8_t *scales,
+                 const uint8_t *dataset, int64_t data_len, int64_t start_idx,
+                 uint32_t step_seed, int pop_offset, int count, int32_t *losses_out);
+
+/* per-token trace of one member for debugging/cross-checks: fills
+ * x_after_layers[(n_layers+1)][seq_len][H] (index 0 = after the initial MLP),
+ * logits[seq_len][V] (int32, after >>shift_logit).  Either may be NULL. */
+void oracle_eval_trace(const egg_config *cfg, const int8_t *model, const int8_t *scales,
+                       const uint8_t *dataset, int64_t data_len, int64_t start_idx,
+                       uint32_t step_seed, int member, int8_t *x_after_layers,
+                       int32_t *logits, int32_t *loss_out);
+
+/* --- fitness (mgpu.cu:1031-1036, 1305-1311) --- */
+void oracle_fitness(const int32_t *losses, int32_t *fitness, int pairs);
+
+/* --- update (mgpu.cu:1040-1152, 1573-1668; muon_internal.cuh) ---
+ * fma_mode: 0 = every float op rounded separately; 1 = the contraction
+ * pattern nvcc's default -fmad=true produces for the reference source. */
+uint64_t oracle_update(const egg_config *cfg, int8_t *model, void *opt_state,
+                       const int32_t *fitness, uint32_t step_seed, float lr, int fma_mode);
+
+/* vote of one matrix in packed index order (mgpu.cu:1085-1098) */
+void oracle_vote_matrix(const egg_config *cfg, const int32_t *fitness, int pairs,
+                        int rows_k, int cols_n, int off_a, int off_b, int seed_base,
+                        uint32_t step_seed, int32_t *vote);
+
+/* one AdamW element step (mgpu.cu:1040-1064); returns 1 if w changed */
+int oracle_adam_step(const egg_config *cfg, float *m, float *v, float *acc, int8_t *w,
+                     float g, float lr, int fma_mode);
+
+/* Newton–Schulz orthogonalisation of a row-major rows×cols fp32 matrix
+ * (muon_internal.cuh:182-342), double accumulation, fp32 storage. */
+void oracle_newton_schulz(float *x, int rows, int cols);
+
+/* --- isolated perturbed projection (mgpu.cu:553-572 + ">>8, clip" of
+ * full_cuda_train_egg_transformer.cu:249) --- */
+void oracle_projection(const egg_config *cfg, const int8_t *x, const int8_t *w_packed,
+                       int8_t *y, int64_t rows, int k_dim, int n_dim, int rows_per_member,
+                       uint32_t seed, int off_a, int off_b, int rank1_shift, int out_shift);
+
+/* --- ternary codec (d-eggs/include/utils/ternary_pack.h:12-87) --- */
+int64_t oracle_ternary_packed_size(int64_t count);
+void oracle_ternary_pack(const int32_t *values, int64_t count, uint8_t *out);
+void oracle_ternary_unpack(const uint8_t *in, int64_t count, int32_t *values);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,199 @@
+"""ctypes binding of the CPU oracle (liboracle.so).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by __graft_entry__.smoke() and by
+bench.py's cpu_baseline / reference legs, never by the library itself.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+class EggConfig(C.Structure):
+    """Mirror of struct egg_config (include/egg_b200.h); defaults are the
+    reference's (full_cuda_train_transformer_adam_mgpu.cu:35-270)."""
+    _fields_ = [(n, C.c_int32) for n in (
+        "hidden_dim", "head_dim", "n_layers", "seq_len", "vocab_size", "population_size",
+        "fixed_point", "sigma_shift", "sigma_shift_vector", "shift_attn", "shift_out",
+        "shift_logit", "shift_mlp_up", "shift_mlp_down", "softmax_scale_bit", "rope_scale_bit",
+        "device_mask", "device_gaussian", "host_mask", "use_same_data", "use_muon",
+        "chunk_relative_loss")] + [
+        ("softmax_exp_scale", C.c_double), ("adam_beta1", C.c_float), ("adam_beta2", C.c_float),
+        ("adam_eps", C.c_float), ("adam_weight_decay", C.c_float), ("muon_momentum", C.c_float),
+        ("muon_lr_scale", C.c_float)]
+
+
+def make_config(**kw):
+    d = dict(hidden_dim=256, head_dim=64, n_layers=4, seq_len=32, vocab_size=256,
+             population_size=8192 * 2 * 4, fixed_point=4, sigma_shift=3, sigma_shift_vector=4,
+             shift_attn=8, shift_out=9, shift_logit=8, shift_mlp_up=8, shift_mlp_down=10,
+             softmax_scale_bit=18, rope_scale_bit=20, device_mask=15, device_gaussian=0,
+             host_mask=15, use_same_data=0, use_muon=0, chunk_relative_loss=0,
+             softmax_exp_scale=6.0, adam_beta1=0.9, adam_beta2=0.95, adam_eps=1e-8,
+             adam_weight_decay=0.01, muon_momentum=0.85, muon_lr_scale=1.0)
+    for k in kw:
+        if k not in d:
+            raise KeyError(k)
+    d.update(kw)
+    return EggConfig(**d)
+
+
+def build(force=False):
+    so = os.path.join(_HERE, "liboracle.so")
+    if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(os.path.join(_HERE, "egg_oracle.c")):
+        subprocess.run(["make", "-C", _HERE, "liboracle.so"], check=True, capture_output=True)
+    return so
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        L = C.CDLL(build())
+        P = C.POINTER
+        cfgp = P(EggConfig)
+        L.oracle_hash_rng.restype = C.c_uint32
+        L.oracle_hash_rng.argtypes = [C.c_uint32, C.c_uint32]
+        L.oracle_noise.restype = C.c_int
+        L.oracle_noise.argtypes = [cfgp, C.c_uint32, C.c_uint32]
+        L.oracle_gen_noise_host.restype = C.c_int
+        L.oracle_gen_noise_host.argtypes = [cfgp, P(C.c_uint32)]
+        for f in (L.oracle_model_bytes, L.oracle_opt_bytes, L.oracle_scales_bytes):
+            f.restype = C.c_int64
+            f.argtypes = [cfgp]
+        L.oracle_init_tables.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.oracle_init_model.argtypes = [cfgp, C.c_void_p, C.c_uint32]
+        L.oracle_repack_matrix.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int]
+        L.oracle_eval.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                  C.c_uint32, C.c_int, C.c_int, C.c_void_p]
+        L.oracle_eval_trace.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                        C.c_uint32, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.oracle_fitness.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+        L.oracle_update.restype = C.c_uint64
+        L.oracle_update.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_float, C.c_int]
+        L.oracle_vote_matrix.argtypes = [cfgp, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                         C.c_int, C.c_uint32, C.c_void_p]
+        L.oracle_newton_schulz.argtypes = [C.c_void_p, C.c_int, C.c_int]
+        L.oracle_projection.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int,
+                                        C.c_int, C.c_uint32, C.c_int, C.c_int, C.c_int, C.c_int]
+        L.oracle_ternary_packed_size.restype = C.c_int64
+        L.oracle_ternary_packed_size.argtypes = [C.c_int64]
+        L.oracle_ternary_pack.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
+        L.oracle_ternary_unpack.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
+        _lib = L
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def hash_rng(s, idx):
+    return lib().oracle_hash_rng(s & 0xFFFFFFFF, idx & 0xFFFFFFFF)
+
+
+def noise(cfg, s, idx):
+    return lib().oracle_noise(C.byref(cfg), s & 0xFFFFFFFF, idx & 0xFFFFFFFF)
+
+
+def model_bytes(cfg):
+    return lib().oracle_model_bytes(C.byref(cfg))
+
+
+def opt_bytes(cfg):
+    return lib().oracle_opt_bytes(C.byref(cfg))
+
+
+def scales_bytes(cfg):
+    return lib().oracle_scales_bytes(C.byref(cfg))
+
+
+def init_tables(cfg):
+    exp = np.zeros(256, np.int32)
+    act = np.zeros(256, np.int8)
+    rope = np.zeros(cfg.seq_len * cfg.head_dim, np.int32)
+    lib().oracle_init_tables(C.byref(cfg), _p(exp), _p(act), _p(rope))
+    return exp, act, rope
+
+
+def init_model(cfg, seed=42):
+    m = np.zeros(model_bytes(cfg), np.int8)
+    lib().oracle_init_model(C.byref(cfg), _p(m), seed)
+    return m
+
+
+def eval_losses(cfg, model, dataset, start_idx, step_seed, pop_offset, count, scales=None):
+    out = np.zeros(count, np.int32)
+    lib().oracle_eval(C.byref(cfg), _p(model), _p(scales), _p(dataset), len(dataset), start_idx,
+                      step_seed & 0xFFFFFFFF, pop_offset, count, _p(out))
+    return out
+
+
+def eval_trace(cfg, model, dataset, start_idx, step_seed, member, scales=None):
+    x = np.zeros((cfg.n_layers + 1, cfg.seq_len, cfg.hidden_dim), np.int8)
+    lg = np.zeros((cfg.seq_len, cfg.vocab_size), np.int32)
+    loss = np.zeros(1, np.int32)
+    lib().oracle_eval_trace(C.byref(cfg), _p(model), _p(scales), _p(dataset), len(dataset), start_idx,
+                            step_seed & 0xFFFFFFFF, member, _p(x), _p(lg), _p(loss))
+    return x, lg, int(loss[0])
+
+
+def fitness(losses):
+    f = np.zeros(len(losses) // 2, np.int32)
+    lib().oracle_fitness(_p(np.ascontiguousarray(losses, np.int32)), _p(f), len(f))
+    return f
+
+
+def update(cfg, model, opt_state, fit, step_seed, lr, fma_mode=1):
+    """In-place on model (int8) and opt_state (uint8 bytes); returns update count."""
+    fit = np.ascontiguousarray(fit, np.int32)
+    return int(lib().oracle_update(C.byref(cfg), _p(model), _p(opt_state), _p(fit), step_seed & 0xFFFFFFFF,
+                                   C.c_float(lr), fma_mode))
+
+
+def vote_matrix(cfg, fit, rows_k, cols_n, off_a, off_b, seed_base, step_seed):
+    fit = np.ascontiguousarray(fit, np.int32)
+    v = np.zeros(rows_k * cols_n, np.int32)
+    lib().oracle_vote_matrix(C.byref(cfg), _p(fit), len(fit), rows_k, cols_n, off_a, off_b, seed_base,
+                             step_seed & 0xFFFFFFFF, _p(v))
+    return v
+
+
+def newton_schulz(x):
+    x = np.ascontiguousarray(x, np.float32).copy()
+    lib().oracle_newton_schulz(_p(x), x.shape[0], x.shape[1])
+    return x
+
+
+def projection(cfg, x, w_packed, k_dim, n_dim, rows_per_member, seed, off_a, off_b, rank1_shift, out_shift):
+    rows = x.size // k_dim
+    y = np.zeros((rows, n_dim), np.int8)
+    lib().oracle_projection(C.byref(cfg), _p(x), _p(w_packed), _p(y), rows, k_dim, n_dim, rows_per_member,
+                            seed & 0xFFFFFFFF, off_a, off_b, rank1_shift, out_shift)
+    return y
+
+
+def repack(src_k_by_n):
+    """[K][N] row-major int8 -> the reference's packed [K/4][N][4] bytes."""
+    K, N = src_k_by_n.shape
+    dst = np.zeros(K * N, np.int8)
+    lib().oracle_repack_matrix(_p(dst), _p(np.ascontiguousarray(src_k_by_n, np.int8)), K, N)
+    return dst
+
+
+def ternary_pack(values):
+    values = np.ascontiguousarray(values, np.int32)
+    out = np.zeros(lib().oracle_ternary_packed_size(len(values)), np.uint8)
+    lib().oracle_ternary_pack(_p(values), len(values), _p(out))
+    return out
+
+
+def ternary_unpack(packed, count):
+    out = np.zeros(count, np.int32)
+    lib().oracle_ternary_unpack(_p(np.ascontiguousarray(packed, np.uint8)), count, _p(out))
+    return out

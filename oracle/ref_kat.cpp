@@ -1,0 +1,50 @@
+// Known-answer generator: compiles the REFERENCE's own host-callable headers
+// (d-eggs/include/utils/egg_math.h, ternary_pack.h) and prints their outputs as
+// JSON.  Built into oracle/_ref/ref_kat by oracle/Makefile; its output is
+// committed as tests/golden/rng_kat.json (see tests/golden/make_golden.py).
+// Usage: ref_kat            (DEVICE_MASK / HOST_MASK come from -D, default 15)
+#include <cstdio>
+#include <cstdint>
+#include <vector>
+#include "utils/egg_math.h"
+#include "utils/ternary_pack.h"
+
+int main() {
+    printf("{\n \"device_mask\": %d, \"host_mask\": %d,\n", DEVICE_MASK, HOST_MASK);
+    const uint32_t seeds[] = {0u, 1u, 42u, 0xFFFFFFFFu, 12648430u, 0x00C0FFEEu, 2u};
+    const uint32_t idxs[] = {0u, 1u, 511u, 0xFFFFFFFFu, 4095u};
+    printf(" \"hash_rng\": [");
+    bool first = true;
+    for (uint32_t s : seeds) for (uint32_t i : idxs) {
+        printf("%s[%u, %u, %u]", first ? "" : ", ", s, i, hash_rng(s, i)); first = false;
+    }
+    printf("],\n \"noise\": [");
+    first = true;
+    for (uint32_t s : seeds) {
+        printf("%s{\"seed\": %u, \"values\": [", first ? "" : ", ", s); first = false;
+        for (uint32_t i = 0; i < 64; i++) printf("%s%d", i ? ", " : "", (int)noise_from_hash(s, i));
+        printf("]}");
+    }
+    printf("],\n \"gen_noise_host\": {\"state\": 42, \"values\": [");
+    uint32_t st = 42;
+    for (int i = 0; i < 64; i++) printf("%s%d", i ? ", " : "", (int)gen_noise_host(&st));
+    printf("]},\n \"ternary\": [");
+    // the two round-trip cases of d-eggs/test_ternary.cpp plus an LCG stream
+    std::vector<std::vector<int32_t>> cases = {
+        {-1, 0, 1, -1, 0, 1, 1, 0, -1, 0}, {-1, 0, 1, -1, 0, 1, 1}, {}, {1}, {-1, -1, -1, -1, -1}};
+    std::vector<int32_t> lcg; uint32_t x = 12345;
+    for (int i = 0; i < 103; i++) { x = x * 1664525u + 1013904223u; lcg.push_back((int)((x >> 16) % 3) - 1); }
+    cases.push_back(lcg);
+    first = true;
+    for (auto &c : cases) {
+        std::vector<uint8_t> packed(ternary_pack_estimate_size(c.size()) + 1, 0);
+        ternary_pack(c.data(), c.size(), packed.data());
+        printf("%s{\"values\": [", first ? "" : ", "); first = false;
+        for (size_t i = 0; i < c.size(); i++) printf("%s%d", i ? ", " : "", c[i]);
+        printf("], \"packed\": [");
+        for (size_t i = 0; i < ternary_pack_estimate_size(c.size()); i++) printf("%s%u", i ? ", " : "", packed[i]);
+        printf("]}");
+    }
+    printf("]\n}\n");
+    return 0;
+}

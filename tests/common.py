@@ -1,0 +1,98 @@
+"""Shared helpers of the test-suite: package loader, oracle import, reference
+harness runner, seeded cases."""
+import importlib.util
+import json
+import os
+import struct
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def load_pkg():
+    """The package directory is named egg.c_b200 (not an identifier): import it as egg_c_b200."""
+    if "egg_c_b200" in sys.modules:
+        return sys.modules["egg_c_b200"]
+    d = os.path.join(ROOT, "egg.c_b200")
+    spec = importlib.util.spec_from_file_location("egg_c_b200", os.path.join(d, "__init__.py"), submodule_search_locations=[d])
+    m = importlib.util.module_from_spec(spec)
+    sys.modules["egg_c_b200"] = m
+    spec.loader.exec_module(m)
+    return m
+
+
+def load_oracle():
+    if "egg_oracle" in sys.modules:
+        return sys.modules["egg_oracle"]
+    spec = importlib.util.spec_from_file_location("egg_oracle", os.path.join(ROOT, "oracle", "oracle.py"))
+    m = importlib.util.module_from_spec(spec)
+    sys.modules["egg_oracle"] = m
+    spec.loader.exec_module(m)
+    return m
+
+
+# configurations the reference harness binaries in oracle/_ref were compiled for (oracle/Makefile)
+REF_CONFIGS = {
+    "tiny": dict(hidden_dim=128, n_layers=1, seq_len=16, population_size=32, device_mask=15),
+    "small": dict(hidden_dim=256, n_layers=2, seq_len=32, population_size=64, device_mask=3),
+    "med": dict(hidden_dim=512, n_layers=4, seq_len=256, population_size=256, device_mask=3),
+    "muon_tiny": dict(hidden_dim=128, n_layers=1, seq_len=16, population_size=32, device_mask=15, use_muon=1),
+    "muon_small": dict(hidden_dim=256, n_layers=2, seq_len=32, population_size=64, device_mask=3, use_muon=1),
+}
+
+
+def cfg_pair(**kw):
+    """(library config, oracle config) with identical fields."""
+    pkg, orc = load_pkg(), load_oracle()
+    return pkg.default_config(**kw), orc.make_config(**kw)
+
+
+def ref_binary(tag):
+    p = os.path.join(ROOT, "oracle", "_ref", "ref_mgpu_" + tag)
+    return p if os.path.exists(p) else None
+
+
+def run_ref_mgpu(tag, model, dataset, step_seed, start_idx, pop_offset, count, lr=0.0, do_update=False, opt_state=None):
+    """Runs the reference's own kernels (oracle/_ref/ref_mgpu_<tag>) on the visible GPU."""
+    exe = ref_binary(tag)
+    assert exe, "reference harness %s not built" % tag
+    sizes = json.loads(subprocess.run([exe, "--sizes"], check=True, capture_output=True, text=True).stdout)
+    with tempfile.TemporaryDirectory() as td:
+        fin, fout = os.path.join(td, "in.bin"), os.path.join(td, "out.bin")
+        with open(fin, "wb") as f:
+            f.write(struct.pack("<IIqqiifiii", 0x46524745, step_seed & 0xFFFFFFFF, start_idx, len(dataset), pop_offset, count,
+                                lr, 1 if do_update else 0, 1 if opt_state is not None else 0, 0))
+            f.write(np.ascontiguousarray(model, np.int8).tobytes())
+            if opt_state is not None:
+                f.write(np.ascontiguousarray(opt_state, np.uint8).tobytes())
+            f.write(np.ascontiguousarray(dataset, np.uint8).tobytes())
+        r = subprocess.run([exe, fin, fout], capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout + r.stderr
+        info = json.loads(r.stdout.strip().splitlines()[-1])
+        raw = open(fout, "rb").read()
+    out = {"info": info, "losses": np.frombuffer(raw, np.int32, count).copy()}
+    if do_update:
+        o = 4 * count
+        pairs = sizes["population_size"] // 2
+        out["fitness"] = np.frombuffer(raw, np.int32, pairs, o).copy(); o += 4 * pairs
+        out["updates"] = struct.unpack_from("<Q", raw, o)[0]; o += 8
+        out["model"] = np.frombuffer(raw, np.int8, sizes["model_bytes"], o).copy(); o += sizes["model_bytes"]
+        out["opt"] = np.frombuffer(raw, np.uint8, sizes["opt_bytes"], o).copy()
+    return out
+
+
+def make_case(kw, data_len=200000, data_seed=1, model_seed=0, model_kind="init"):
+    """Config pair, model bytes and a Zipf byte stream for a small case."""
+    pkg, orc = load_pkg(), load_oracle()
+    cfg, ocfg = cfg_pair(**kw)
+    from egg_c_b200 import synth
+    if model_kind == "init":
+        model = orc.init_model(ocfg, 42)            # the reference's own initialisation
+    else:
+        model = synth.random_model(cfg, model_seed, "uniform", gains_random=(model_kind == "random_all"))
+    data = synth.zipf_bytes(data_seed, data_len)
+    return cfg, ocfg, model, data

@@ -1,0 +1,151 @@
+"""CPU tests: the oracle against the reference's known answers, host logic, ABI surface."""
+import ctypes as C
+import json
+import os
+import re
+
+import numpy as np
+import pytest
+
+from common import ROOT, load_oracle, load_pkg, cfg_pair
+
+GOLD = os.path.join(ROOT, "tests", "golden")
+
+
+def _kat(mask):
+    return json.load(open(os.path.join(GOLD, "rng_kat_mask%d.json" % mask)))
+
+
+@pytest.mark.parametrize("mask", [15, 3])
+def test_hash_and_noise_match_reference_known_answers(mask):
+    O = load_oracle()
+    k = _kat(mask)
+    cfg = O.make_config(device_mask=mask)
+    for s, i, h in k["hash_rng"]:
+        assert O.hash_rng(s, i) == h
+    for ent in k["noise"]:
+        got = [O.noise(cfg, ent["seed"], i) for i in range(len(ent["values"]))]
+        assert got == ent["values"]
+    st = C.c_uint32(k["gen_noise_host"]["state"])
+    got = [O.lib().oracle_gen_noise_host(C.byref(cfg), C.byref(st)) for _ in k["gen_noise_host"]["values"]]
+    assert got == k["gen_noise_host"]["values"]
+
+
+def test_ternary_codec_matches_reference_cases():
+    O = load_oracle()
+    for case in _kat(15)["ternary"]:
+        vals = np.array(case["values"], np.int32)
+        packed = O.ternary_pack(vals)
+        assert packed.tolist() == case["packed"]
+        assert O.ternary_unpack(packed, len(vals)).tolist() == case["values"]
+    # size law of ternary_pack_estimate_size: 5 trits per byte
+    assert [O.lib().oracle_ternary_packed_size(n) for n in (0, 1, 5, 6, 10, 11)] == [0, 1, 1, 2, 2, 3]
+
+
+def test_struct_sizes_match_reference_sizeof():
+    # sizeof(TransformerModel) / sizeof(AdamModel) printed by the reference TUs at the benchmark configurations
+    O = load_oracle()
+    c2 = O.make_config(hidden_dim=512, n_layers=4, seq_len=256, population_size=40960)
+    assert (O.model_bytes(c2), O.opt_bytes(c2)) == (14834688, 178016256)
+    c5 = O.make_config(hidden_dim=1024, n_layers=12, seq_len=512, population_size=262144)
+    assert (O.model_bytes(c5), O.opt_bytes(c5), O.scales_bytes(c5)) == (159766528, 1917198336, 353536)
+
+
+def test_library_sizes_agree_with_oracle():
+    pkg, O = load_pkg(), load_oracle()
+    for kw in (dict(hidden_dim=128, n_layers=1), dict(hidden_dim=512, n_layers=4), dict(hidden_dim=1024, n_layers=12),
+               dict(hidden_dim=256, n_layers=2, use_muon=1)):
+        cfg, ocfg = cfg_pair(**kw)
+        assert pkg.model_bytes(cfg) == O.model_bytes(ocfg)
+        assert pkg.opt_state_bytes(cfg) == O.opt_bytes(ocfg)
+
+
+def test_library_exports_every_declared_symbol():
+    pkg = load_pkg()
+    hdr = open(os.path.join(ROOT, "include", "egg_b200.h")).read()
+    declared = set(re.findall(r"\b(egg_[a-z0-9_]+)\s*\(", hdr))
+    declared -= {"egg_config", "egg_ctx"}
+    L = pkg.lib()
+    for name in sorted(declared):
+        assert hasattr(L, name), name
+    assert declared == set(pkg.EXPORTS)
+
+
+def test_config_validation_messages():
+    pkg = load_pkg()
+    L = pkg.lib()
+    for kw in (dict(hidden_dim=100), dict(seq_len=8), dict(vocab_size=8192), dict(population_size=7), dict(head_dim=32)):
+        cfg = pkg.default_config(**kw)
+        why = C.c_char_p()
+        assert L.egg_config_validate(C.byref(cfg), C.byref(why)) == pkg.EGG_E_INVALID
+        assert why.value
+    cfg = pkg.default_config()
+    assert L.egg_config_validate(C.byref(cfg), None) == 0
+
+
+def test_no_gpu_fails_loudly():
+    """Without a device the context must refuse; nothing computes on the CPU."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    pkg = load_pkg()
+    with pytest.raises(pkg.EggError):
+        pkg.Context(pkg.default_config())
+
+
+def test_tables_shape_and_known_values():
+    O = load_oracle()
+    exp, act, rope = O.init_tables(O.make_config(seq_len=16))
+    assert exp[0] == 1 << 18 and exp[75] == 0 and exp[74] > 0      # exp(-i/6)*2^18 drops below 1 at i=75
+    assert act[0] == 0 and act[127] == 127 and act[(-128) & 0xFF] == 0
+    assert rope[0] == 1 << 20 and rope[1] == 0                      # t=0: cos=1, sin=0
+
+
+def test_eval_is_deterministic_and_antithetic_pairs_share_data():
+    O = load_oracle()
+    cfg = O.make_config(hidden_dim=128, n_layers=1, seq_len=16, population_size=8)
+    model = O.init_model(cfg, 42)
+    rng = np.random.default_rng(5)
+    data = rng.integers(0, 256, 5000).astype(np.uint8)
+    a = O.eval_losses(cfg, model, data, 0, 1234, 0, 8)
+    b = O.eval_losses(cfg, model, data, 0, 1234, 0, 8)
+    assert (a == b).all()
+    # chunked evaluation equals whole evaluation
+    c = np.concatenate([O.eval_losses(cfg, model, data, 0, 1234, off, 2) for off in range(0, 8, 2)])
+    assert (a == c).all()
+    # with no noise magnitude both members of a pair see the same model: equal losses, zero fitness
+    cfg0 = O.make_config(hidden_dim=128, n_layers=1, seq_len=16, population_size=8, device_mask=0)
+    l0 = O.eval_losses(cfg0, model, data, 0, 1234, 0, 8)
+    assert (l0[0::2] == l0[1::2]).all() and (O.fitness(l0) == 0).all()
+
+
+def test_vote_matrix_linearity_and_update_count():
+    O = load_oracle()
+    cfg = O.make_config(hidden_dim=128, n_layers=1, seq_len=16, population_size=64)
+    rng = np.random.default_rng(0)
+    f1 = rng.integers(-1, 2, 32).astype(np.int32)
+    f2 = rng.integers(-1, 2, 32).astype(np.int32)
+    v1 = O.vote_matrix(cfg, f1, 128, 128, 200, 201, 0, 77)
+    v2 = O.vote_matrix(cfg, f2, 128, 128, 200, 201, 0, 77)
+    v12 = O.vote_matrix(cfg, f1 + f2, 128, 128, 200, 201, 0, 77)
+    assert (v1 + v2 == v12).all()
+    model = O.init_model(cfg, 42)
+    before = model.copy()
+    opt = np.zeros(O.opt_bytes(cfg), np.uint8)
+    # one AdamW step from zero state moves acc by ~0.45*lr: weights flip only after a few steps
+    assert O.update(cfg, model, opt, f1, 77, 0.5) == 0 and (model == before).all()
+    n = sum(O.update(cfg, model, opt, f1, 77, 0.5) for _ in range(5))
+    assert n > 0 and n >= int((model != before).sum())
+    assert np.abs(model.astype(int) - before.astype(int)).max() <= 5
+
+
+def test_newton_schulz_orthogonalises():
+    O = load_oracle()
+    rng = np.random.default_rng(1)
+    for shape in ((64, 64), (32, 128), (128, 32)):
+        x = rng.standard_normal(shape).astype(np.float32)
+        y = O.newton_schulz(x).astype(np.float64)
+        g = y @ y.T if shape[0] <= shape[1] else y.T @ y
+        # 5 cubic iterations from Frobenius normalisation move singular values toward 1 (not all the way)
+        s = np.linalg.svd(y, compute_uv=False)
+        assert s.max() < 1.3 and np.isfinite(g).all()
