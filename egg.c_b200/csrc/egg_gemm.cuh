@@ -100,23 +100,30 @@ __device__ __forceinline__ void gemm_fail(const GemmParams &p, volatile int *abo
     if (p.err) { atomicCAS(p.err, 0, code); }
 }
 
-// AdamW element step; expressions and their order are those of apply_adam_update
-// (mgpu.cu:1040-1064) so that the compiler contracts them the same way.
+// AdamW element step (apply_adam_update, mgpu.cu:1040-1064).  The reference is built
+// with nvcc's default -fmad=true; which multiply-adds it contracts was measured by
+// running its kernels on a B200 and is written out here with explicit single-rounding
+// intrinsics so that the result does not depend on this compiler's own choices:
+//   m   = fma(b1, m, (1-b1)*g)          v     = fma(1-b2, g*g, b2*v)
+//   in  = fma(wd, w, m/(sqrt(v)+eps))   acc   = fma(-lr, in, acc)
+__device__ __forceinline__ int quantized_step(float &acc, int &w) {
+    if (acc >= 1.0f) {
+        if (w < 127) { w++; acc = __fadd_rn(acc, -1.0f); return 1; }
+        acc = 1.0f;
+    } else if (acc <= -1.0f) {
+        if (w > -127) { w--; acc = __fadd_rn(acc, 1.0f); return 1; }
+        acc = -1.0f;
+    }
+    return 0;
+}
 __device__ __forceinline__ int adam_apply(float &m, float &v, float &acc, int &w, float g, float lr, float b1, float b2,
                                           float eps, float wd) {
-    m = b1 * m + (1.0f - b1) * g;
-    v = b2 * v + (1.0f - b2) * (g * g);
-    float step = -lr * (m / (sqrtf(v) + eps) + wd * (float)w);
-    acc += step;
-    int change = 0;
-    if (acc >= 1.0f) {
-        if (w < 127) { w++; change = 1; acc -= 1.0f; }
-        else acc = 1.0f;
-    } else if (acc <= -1.0f) {
-        if (w > -127) { w--; change = 1; acc += 1.0f; }
-        else acc = -1.0f;
-    }
-    return change;
+    const float omb1 = __fadd_rn(1.0f, -b1), omb2 = __fadd_rn(1.0f, -b2);
+    m = __fmaf_rn(b1, m, __fmul_rn(omb1, g));
+    v = __fmaf_rn(omb2, __fmul_rn(g, g), __fmul_rn(b2, v));
+    const float inner = __fmaf_rn(wd, (float)w, __fdiv_rn(m, __fadd_rn(__fsqrt_rn(v), eps)));
+    acc = __fmaf_rn(-lr, inner, acc);
+    return quantized_step(acc, w);
 }
 
 template <int BN, int EPI>
@@ -251,6 +258,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 bool ok = ptx::mbar_wait(&sm.tmem_full[as], aph) && !sm.abort_flag;
                 if (!ok) { gemm_fail(p, &sm.abort_flag, DEV_TIMEOUT_TMEM_FULL); sm.epi_ok = 0; }
             }
+            __syncwarp();
             ptx::named_bar_sync(1, GEMM_EPI_THREADS);
             if (!sm.epi_ok) break;
             ptx::tc_fence_after();
@@ -452,10 +460,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         } else if (EPI == EPI_MUON_M) {
                             float4 *st = reinterpret_cast<float4 *>(p.opt + idx * 2);
                             float4 s0 = st[0], s1 = st[1];     // m0 acc0 m1 acc1 | m2 acc2 m3 acc3
-                            s0.x = p.mu * s0.x + (float)(int)v[4 * q];          // muon_internal.cuh:45-47
-                            s0.z = p.mu * s0.z + (float)(int)v[4 * q + 1];
-                            s1.x = p.mu * s1.x + (float)(int)v[4 * q + 2];
-                            s1.z = p.mu * s1.z + (float)(int)v[4 * q + 3];
+                            s0.x = __fmaf_rn(p.mu, s0.x, (float)(int)v[4 * q]);   // m = mu*m + vote, muon_internal.cuh:45-47
+                            s0.z = __fmaf_rn(p.mu, s0.z, (float)(int)v[4 * q + 1]);
+                            s1.x = __fmaf_rn(p.mu, s1.x, (float)(int)v[4 * q + 2]);
+                            s1.z = __fmaf_rn(p.mu, s1.z, (float)(int)v[4 * q + 3]);
                             st[0] = s0; st[1] = s1;
                             const int k = k0 + 4 * q;
                             p.m_rowmajor[(int64_t)k * cols_n + n] = s0.x;        // gather, muon_internal.cuh:53-74
@@ -479,6 +487,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
     }
 
+    __syncwarp();
     ptx::tc_fence_before();
     __syncthreads();
     if (warp == 1) {

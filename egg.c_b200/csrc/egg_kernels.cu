@@ -646,13 +646,10 @@ __global__ void muon_apply_kernel(int8_t *w_packed, float *opt, const float *upd
         int8_t w = w_packed[idx];
         float acc = opt[idx * 2 + 1];
         float u = upd[(int64_t)k * cols_n + n];
-        float step = -lr * (u + wd * (float)w);
-        acc += step;
-        if (acc >= 1.0f) {
-            if (w < 127) { w++; change = 1; acc -= 1.0f; } else acc = 1.0f;
-        } else if (acc <= -1.0f) {
-            if (w > -127) { w--; change = 1; acc += 1.0f; } else acc = -1.0f;
-        }
+        int wi = w;
+        acc = __fmaf_rn(-lr, __fmaf_rn(wd, (float)wi, u), acc);     // acc += -lr*(u + wd*w), contracted as nvcc does
+        change = quantized_step(acc, wi);
+        w = (int8_t)wi;
         w_packed[idx] = w;
         opt[idx * 2 + 1] = acc;
     }

@@ -495,17 +495,23 @@ static int32_t eval_member(const eval_env *E, const uint8_t *dataset, int64_t da
             int32_t perturb = (prod * ns) >> (c->fixed_point + c->sigma_shift);
             x[d] = (int8_t)clip8(emb + ebias + chk + perturb);
         }
+        const int nst = 3 + 2 * NL;
+#define STAGE(i, buf) do { if (trace_x) memcpy(trace_x + ((int64_t)t * nst + (i)) * H, (buf), (size_t)H); } while (0)
+        STAGE(0, x);
         mlp_block(E, -1, x, S0, ns);
-        if (trace_x) memcpy(trace_x + ((int64_t)0 * S + t) * H, x, (size_t)H);
+        STAGE(1, x);
         for (int l = 0; l < NL; l++) {
             uint32_t seed_base = S0 + (uint32_t)(l * 1000);
             int8_t *kc = kv + (int64_t)l * 2 * S * H, *vc = kc + (int64_t)S * H;
             attention_block(E, l, t, x, kc, vc, seed_base, ns);
+            STAGE(2 + 2 * l, x);
             mlp_block(E, l, x, seed_base, ns);
-            if (trace_x) memcpy(trace_x + ((int64_t)(l + 1) * S + t) * H, x, (size_t)H);
+            STAGE(3 + 2 * l, x);
         }
         /* head + loss, mgpu.cu:954-1024 */
         standard_norm(E, x, nf, M + L->ln_f, M + L->ln_f_bias, S0, 900, 901, 910, 911, ns, SC->ln_f, SC->ln_f_bias);
+        STAGE(2 + 2 * NL, nf);
+#undef STAGE
         int32_t sbh = noise_dot(E, nf, H, S0 + (uint32_t)H, SC->embedding_col);
         int32_t mx = INT_MIN;
         for (int v = 0; v < V; v++) {
@@ -622,26 +628,31 @@ static int quantized_update(int8_t *w, float *acc) {
     return 0;
 }
 
-/* mgpu.cu:1040-1064 */
+/* mgpu.cu:1040-1064.  fma_mode selects which multiply-adds are contracted into a
+ * single-rounding fma, as nvcc's default -fmad=true may do on the reference source:
+ *   mode = m_sel + 3*v_sel + 9*inner_sel + 18*acc_sel
+ *   m_sel:     0 separate | 1 fma(b1, m, (1-b1)*g)        | 2 fma(1-b1, g, b1*m)
+ *   v_sel:     0 separate | 1 fma(b2, v, (1-b2)*(g*g))    | 2 fma(1-b2, g*g, b2*v)
+ *   inner_sel: 0 separate | 1 fma(wd, w, m/(sqrt(v)+eps))
+ *   acc_sel:   0 separate | 1 fma(-lr, inner, acc)
+ * ORACLE_FMA_NVCC is the pattern calibrated against the reference kernels on a B200. */
+static inline float mul_rn(float a, float b) { volatile float r = a * b; return r; }
+static inline float add_rn(float a, float b) { volatile float r = a + b; return r; }
 int oracle_adam_step(const egg_config *c, float *m, float *v, float *acc, int8_t *w, float g, float lr, int fma_mode) {
-    float b1 = c->adam_beta1, b2 = c->adam_beta2;
-    float omb1 = 1.0f - b1, omb2 = 1.0f - b2;
-    if (fma_mode) {
-        /* nvcc -fmad=true: the first product of a*b + c*d fuses with the add;
-         * "acc += -lr * inner" fuses into one fma. */
-        *m = fmaf(b1, *m, omb1 * g);
-        *v = fmaf(b2, *v, omb2 * (g * g));
-        float inner = fmaf(c->adam_weight_decay, (float)*w, *m / (sqrtf(*v) + c->adam_eps));
-        *acc = fmaf(-lr, inner, *acc);
-    } else {
-        volatile float t1 = b1 * *m, t2 = omb1 * g;
-        *m = t1 + t2;
-        volatile float gg = g * g; volatile float t3 = b2 * *v, t4 = omb2 * gg;
-        *v = t3 + t4;
-        volatile float dv = *m / (sqrtf(*v) + c->adam_eps); volatile float wdw = c->adam_weight_decay * (float)*w;
-        volatile float inner = dv + wdw; volatile float step = -lr * inner;
-        *acc = *acc + step;
-    }
+    const float b1 = c->adam_beta1, b2 = c->adam_beta2;
+    const float omb1 = 1.0f - b1, omb2 = 1.0f - b2;
+    const int m_sel = fma_mode % 3, v_sel = (fma_mode / 3) % 3, inner_sel = (fma_mode / 9) % 2, acc_sel = (fma_mode / 18) % 2;
+    if (m_sel == 1) *m = fmaf(b1, *m, mul_rn(omb1, g));
+    else if (m_sel == 2) *m = fmaf(omb1, g, mul_rn(b1, *m));
+    else *m = add_rn(mul_rn(b1, *m), mul_rn(omb1, g));
+    const float gg = mul_rn(g, g);
+    if (v_sel == 1) *v = fmaf(b2, *v, mul_rn(omb2, gg));
+    else if (v_sel == 2) *v = fmaf(omb2, gg, mul_rn(b2, *v));
+    else *v = add_rn(mul_rn(b2, *v), mul_rn(omb2, gg));
+    volatile float den = sqrtf(*v) + c->adam_eps;
+    volatile float dv = *m / den;
+    const float inner = inner_sel ? fmaf(c->adam_weight_decay, (float)*w, dv) : add_rn(dv, mul_rn(c->adam_weight_decay, (float)*w));
+    *acc = acc_sel ? fmaf(-lr, inner, *acc) : add_rn(*acc, mul_rn(-lr, inner));
     return quantized_update(w, acc);
 }
 

@@ -52,8 +52,10 @@ void oracle_eval(const egg_config *cfg, const int8_t *model, const int8_t *scale
                  uint32_t step_seed, int pop_offset, int count, int32_t *losses_out);
 
 /* per-token trace of one member for debugging/cross-checks: fills
- * x_after_layers[(n_layers+1)][seq_len][H] (index 0 = after the initial MLP),
- * logits[seq_len][V] (int32, after >>shift_logit).  Either may be NULL. */
+ * stages[seq_len][3 + 2*n_layers][H] with the residual stream after the
+ * embedding, after the initial MLP, after each layer's attention and MLP block,
+ * and the final normalised vector; logits[seq_len][V] (int32, after
+ * >>shift_logit).  Either may be NULL. */
 void oracle_eval_trace(const egg_config *cfg, const int8_t *model, const int8_t *scales,
                        const uint8_t *dataset, int64_t data_len, int64_t start_idx,
                        uint32_t step_seed, int member, int8_t *x_after_layers,
@@ -63,8 +65,9 @@ void oracle_eval_trace(const egg_config *cfg, const int8_t *model, const int8_t 
 void oracle_fitness(const int32_t *losses, int32_t *fitness, int pairs);
 
 /* --- update (mgpu.cu:1040-1152, 1573-1668; muon_internal.cuh) ---
- * fma_mode: 0 = every float op rounded separately; 1 = the contraction
- * pattern nvcc's default -fmad=true produces for the reference source. */
+ * fma_mode: 0 = every float op rounded separately; 34 = the contraction
+ * pattern nvcc's default -fmad=true produces for the reference source
+ * (calibrated on a B200; encoding in oracle_adam_step). */
 uint64_t oracle_update(const egg_config *cfg, int8_t *model, void *opt_state,
                        const int32_t *fitness, uint32_t step_seed, float lr, int fma_mode);
 

@@ -135,7 +135,7 @@ def eval_losses(cfg, model, dataset, start_idx, step_seed, pop_offset, count, sc
 
 
 def eval_trace(cfg, model, dataset, start_idx, step_seed, member, scales=None):
-    x = np.zeros((cfg.n_layers + 1, cfg.seq_len, cfg.hidden_dim), np.int8)
+    x = np.zeros((cfg.seq_len, 3 + 2 * cfg.n_layers, cfg.hidden_dim), np.int8)
     lg = np.zeros((cfg.seq_len, cfg.vocab_size), np.int32)
     loss = np.zeros(1, np.int32)
     lib().oracle_eval_trace(C.byref(cfg), _p(model), _p(scales), _p(dataset), len(dataset), start_idx,
@@ -149,7 +149,10 @@ def fitness(losses):
     return f
 
 
-def update(cfg, model, opt_state, fit, step_seed, lr, fma_mode=1):
+FMA_NVCC = 34   # contraction pattern of the reference kernels under nvcc -fmad=true (see oracle_adam_step)
+
+
+def update(cfg, model, opt_state, fit, step_seed, lr, fma_mode=FMA_NVCC):
     """In-place on model (int8) and opt_state (uint8 bytes); returns update count."""
     fit = np.ascontiguousarray(fit, np.int32)
     return int(lib().oracle_update(C.byref(cfg), _p(model), _p(opt_state), _p(fit), step_seed & 0xFFFFFFFF,

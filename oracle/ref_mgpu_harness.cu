@@ -27,6 +27,7 @@ struct ref_case_header {
     int32_t do_update;     // needs pop_offset == 0 && count == POPULATION_SIZE
     int32_t has_opt;
     int32_t reserved;
+    int32_t cfg_check[6];  // hidden_dim, n_layers, seq_len, population_size, device_mask, use_muon
 };
 
 static void die(const char *m) { fprintf(stderr, "ref harness: %s\n", m); exit(2); }
@@ -44,6 +45,11 @@ int main(int argc, char **argv) {
     if (!f) die("cannot open input");
     ref_case_header h;
     if (fread(&h, sizeof(h), 1, f) != 1 || h.magic != 0x46524745u) die("bad header");
+    {
+        const int want[6] = {HIDDEN_DIM, N_LAYERS, SEQ_LEN, POPULATION_SIZE, DEVICE_MASK, USE_MUON};
+        for (int i = 0; i < 6; i++)
+            if (h.cfg_check[i] != want[i]) { fprintf(stderr, "ref harness: case was made for another configuration (field %d: %d vs compiled %d)\n", i, h.cfg_check[i], want[i]); return 3; }
+    }
     TransformerModel *h_model = (TransformerModel *)calloc(1, sizeof(TransformerModel));
     AdamModel *h_opt = (AdamModel *)calloc(1, sizeof(AdamModel));
     if (fread(h_model, sizeof(TransformerModel), 1, f) != 1) die("short model");

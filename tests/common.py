@@ -66,6 +66,9 @@ def run_ref_mgpu(tag, model, dataset, step_seed, start_idx, pop_offset, count, l
         with open(fin, "wb") as f:
             f.write(struct.pack("<IIqqiifiii", 0x46524745, step_seed & 0xFFFFFFFF, start_idx, len(dataset), pop_offset, count,
                                 lr, 1 if do_update else 0, 1 if opt_state is not None else 0, 0))
+            kw = REF_CONFIGS[tag]
+            f.write(struct.pack("<6i", kw["hidden_dim"], kw["n_layers"], kw["seq_len"], kw["population_size"], kw["device_mask"],
+                                kw.get("use_muon", 0)))
             f.write(np.ascontiguousarray(model, np.int8).tobytes())
             if opt_state is not None:
                 f.write(np.ascontiguousarray(opt_state, np.uint8).tobytes())

@@ -29,20 +29,34 @@ def kat():
         print("wrote rng_kat_mask%d.json" % mask)
 
 
+GOLD_STEPS = 4
+GOLD_SEED = 0x00C0FFEE
+GOLD_LR = 0.5
+
+
 def mgpu(outdir):
+    """Four chained generations (eval -> host fitness -> update) of the reference's own kernels per
+    configuration; weights only start to flip after a few AdamW steps."""
+    import zlib
     from common import REF_CONFIGS, make_case, run_ref_mgpu
     os.makedirs(outdir, exist_ok=True)
     for tag in ("tiny", "small", "muon_tiny"):
         kw = REF_CONFIGS[tag]
-        cfg, ocfg, model, data = make_case(kw, data_len=50000)
-        pop = kw["population_size"]
-        r = run_ref_mgpu(tag, model, data, 0x00C0FFEE, 0, 0, pop, lr=0.5, do_update=True)
-        changed = np.nonzero(r["model"] != model)[0]
-        np.savez_compressed(os.path.join(outdir, "ref_mgpu_%s.npz" % tag), losses=r["losses"], fitness=r["fitness"],
-                            updates=np.uint64(r["updates"]), changed_idx=changed.astype(np.int64),
-                            changed_val=r["model"][changed], opt_crc=np.uint32(0),
-                            opt_sample=r["opt"].view(np.float32)[:: max(1, len(r["opt"]) // 4 // 4096)][:4096])
-        print("wrote", tag, r["info"])
+        cfg, ocfg, model0, data = make_case(kw, data_len=50000)
+        pop, S = kw["population_size"], kw["seq_len"]
+        model, opt = model0.copy(), None
+        losses, fits, ups = [], [], []
+        for step in range(GOLD_STEPS):
+            r = run_ref_mgpu(tag, model, data, GOLD_SEED + step, step * S, 0, pop, lr=GOLD_LR, do_update=True, opt_state=opt)
+            losses.append(r["losses"]); fits.append(r["fitness"]); ups.append(r["updates"])
+            model, opt = r["model"], r["opt"]
+        changed = np.nonzero(model != model0)[0]
+        np.savez_compressed(os.path.join(outdir, "ref_mgpu_%s.npz" % tag), losses=np.array(losses), fitness=np.array(fits),
+                            updates=np.array(ups, np.uint64), changed_count=np.int64(len(changed)),
+                            changed_idx=changed[:2048].astype(np.int64), changed_val=model[changed[:2048]],
+                            model_crc=np.uint32(zlib.crc32(model.tobytes())), opt_crc=np.uint32(zlib.crc32(opt.tobytes())),
+                            opt_head=opt.view(np.float32)[:768].copy())
+        print("wrote", tag, "updates", ups, "changed", len(changed))
 
 
 if __name__ == "__main__":
