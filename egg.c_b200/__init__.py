@@ -21,7 +21,10 @@ EXPORTS = [
     "egg_download_opt_state", "egg_set_dataset", "egg_eval_chunk", "egg_read_losses", "egg_compute_fitness_pairs",
     "egg_write_fitness", "egg_read_fitness", "egg_nccl_unique_id", "egg_comm_init", "egg_allgather_fitness",
     "egg_apply_update", "egg_generation_host", "egg_perturbed_projection", "egg_update_reconstruct",
+    "egg_timer_start", "egg_timer_stop", "egg_profile_enable", "egg_profile_read", "egg_profile_name", "egg_launch_count",
+    "egg_wave_members",
 ]
+EGG_PROF_N = 14
 
 
 class EggConfig(C.Structure):
@@ -91,6 +94,15 @@ def lib():
         L.egg_perturbed_projection.argtypes = [vp, vp, vp, vp, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_int,
                                                C.c_int, C.c_int, C.c_int, C.c_int]
         L.egg_update_reconstruct.argtypes = [vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint32, vp, C.c_int]
+        L.egg_timer_start.argtypes = [vp]
+        L.egg_timer_stop.argtypes = [vp, P(C.c_float)]
+        L.egg_profile_enable.argtypes = [vp, C.c_int]
+        L.egg_profile_read.argtypes = [vp, P(C.c_float), P(C.c_int64)]
+        L.egg_profile_name.argtypes = [C.c_int]
+        L.egg_profile_name.restype = C.c_char_p
+        L.egg_launch_count.argtypes = [vp]
+        L.egg_launch_count.restype = C.c_int64
+        L.egg_wave_members.argtypes = [vp]
         _lib = L
     return _lib
 
@@ -217,6 +229,31 @@ class Context:
     def update_reconstruct(self, fitness, pairs, rows_k, cols_n, off_a, off_b, seed_base, step_seed, vote_out, on_device=False):
         _check(lib().egg_update_reconstruct(self._h, _ptr(fitness), pairs, rows_k, cols_n, off_a, off_b, seed_base,
                                             step_seed & 0xFFFFFFFF, _ptr(vote_out), 1 if on_device else 0))
+
+
+    def timer_start(self):
+        _check(lib().egg_timer_start(self._h))
+
+    def timer_stop(self):
+        ms = C.c_float(0)
+        _check(lib().egg_timer_stop(self._h, C.byref(ms)))
+        return ms.value
+
+    def profile_enable(self, on=True):
+        _check(lib().egg_profile_enable(self._h, 1 if on else 0))
+
+    def profile_read(self):
+        """{class name: (milliseconds, launches)} since the last read."""
+        ms = (C.c_float * EGG_PROF_N)()
+        n = (C.c_int64 * EGG_PROF_N)()
+        _check(lib().egg_profile_read(self._h, ms, n))
+        return {lib().egg_profile_name(i).decode(): (ms[i], n[i]) for i in range(EGG_PROF_N)}
+
+    def launch_count(self):
+        return lib().egg_launch_count(self._h)
+
+    def wave_members(self):
+        return lib().egg_wave_members(self._h)
 
 
 def nccl_unique_id():

@@ -96,10 +96,41 @@ struct egg_ctx {
     MuonWs muon = {nullptr, nullptr, nullptr, nullptr};
     unsigned long long *d_updates = nullptr;
     int *d_err = nullptr;
+    // measurement
+    cudaEvent_t t0 = nullptr, t1 = nullptr;
+    bool prof_on = false;
+    std::vector<cudaEvent_t> prof_ev;      // pairs
+    std::vector<int> prof_cls;             // class of pair i
+    size_t prof_used = 0;
+    int64_t launches = 0;
+    int64_t prof_launches[EGG_PROF_N] = {};
     // multi-GPU
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1;
 };
+
+// Brackets one launch (or launch group) with events when profiling is on.
+struct ProfScope {
+    egg_ctx *c; int idx;
+    ProfScope(egg_ctx *ctx, int cls, int nlaunch = 1) : c(ctx), idx(-1) {
+        c->launches += nlaunch;
+        if (!c->prof_on) return;
+        c->prof_launches[cls] += nlaunch;
+        if (c->prof_used + 2 > c->prof_ev.size()) {
+            size_t old = c->prof_ev.size();
+            c->prof_ev.resize(old + 512);
+            for (size_t i = old; i < c->prof_ev.size(); i++) cudaEventCreate(&c->prof_ev[i]);
+        }
+        idx = (int)c->prof_used;
+        c->prof_used += 2;
+        c->prof_cls.resize(c->prof_used / 2);
+        c->prof_cls[idx / 2] = cls;
+        cudaEventRecord(c->prof_ev[idx], c->stream);
+    }
+    ~ProfScope() { if (idx >= 0) cudaEventRecord(c->prof_ev[idx + 1], c->stream); }
+};
+#define PROF(cls, call) [&]() { ProfScope ps_(c, cls); return (call); }()
+#define PROFN(cls, n, call) [&]() { ProfScope ps_(c, cls, n); return (call); }()
 
 // ---------------------------------------------------------------- config
 
@@ -265,6 +296,9 @@ extern "C" void egg_ctx_destroy(egg_ctx *c) {
                     c->d_rowmax3, c->d_xbo, c->d_wave_loss, c->d_segs, c->d_nt, c->d_na, c->d_nb, c->muon.x, c->muon.g,
                     c->muon.y, c->muon.norm2, c->d_updates, c->d_err};
     for (void *p : ptrs) if (p) cudaFree(p);
+    for (cudaEvent_t e : c->prof_ev) cudaEventDestroy(e);
+    if (c->t0) cudaEventDestroy(c->t0);
+    if (c->t1) cudaEventDestroy(c->t1);
     if (c->stream) cudaStreamDestroy(c->stream);
     delete c;
 }
@@ -293,6 +327,7 @@ extern "C" int egg_ctx_create(const egg_config *cfg, int device, int wave_member
 #define TRY(x) do { rc = (x); if (rc) { egg_ctx_destroy(c); return rc; } } while (0)
 #define TRYC(x) do { cudaError_t e_ = (x); if (e_ != cudaSuccess) { set_error("%s: %s", #x, cudaGetErrorString(e_)); egg_ctx_destroy(c); return EGG_E_CUDA; } } while (0)
     TRYC(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    TRYC(cudaEventCreate(&c->t0)); TRYC(cudaEventCreate(&c->t1));
     const int64_t H = cfg->hidden_dim, S = cfg->seq_len, POP = cfg->population_size;
     TRY(dev_alloc(&c->d_model, c->model_bytes));
     TRY(dev_alloc(&c->d_opt, c->opt_bytes));
@@ -378,7 +413,7 @@ extern "C" int egg_sync(egg_ctx *c) {
 static int refresh_shadows(egg_ctx *c) {
     for (const ParamDesc &d : c->params) {
         if (d.rows_k == 0) continue;
-        int rc = launch_unpack_transpose(c->stream, c->d_model + d.model_off, c->d_shadow + d.shadow_off, d.rows_k, d.cols_n);
+        int rc = PROF(EGG_PROF_TRANSPOSE, launch_unpack_transpose(c->stream, c->d_model + d.model_off, c->d_shadow + d.shadow_off, d.rows_k, d.cols_n));
         if (rc) return rc;
     }
     return EGG_OK;
@@ -468,13 +503,13 @@ static int run_mlp(egg_ctx *c, int M, const MlpOff &mo, int nt_base, const int8_
     GemmParams g = base_gemm(c, M, 4 * H, H);
     g.nt_a_off = nt_base + mo.up_a; g.nt_c_off = nt_base + mo.bup_d; g.nt_d_off = nt_base + mo.dn_b;
     g.xb = c->d_xb; g.xb_stride = 3; g.out_shift = c->cfg.shift_mlp_up; g.bias = up_bias; g.out8 = c->d_u; g.rowstat = c->d_xb2;
-    int rc = launch_gemm(c->stream, EPI_GELU, c->d_h, up_t, g, c->num_sms);
+    int rc = PROF(EGG_PROF_GEMM_GELU, launch_gemm(c->stream, EPI_GELU, c->d_h, up_t, g, c->num_sms));
     if (rc) return rc;
     GemmParams d = base_gemm(c, M, H, 4 * H);
     d.nt_a_off = nt_base + mo.dn_a; d.nt_c_off = nt_base + mo.bdn_d;
     d.xb = c->d_xb2; d.xb_stride = 1; d.out_shift = c->cfg.shift_mlp_down; d.bias = dn_bias; d.resid = c->d_x; d.out32 = c->d_pre;
     d.rowstat = c->d_rowmax;
-    return launch_gemm(c->stream, EPI_PRE32, c->d_u, dn_t, d, c->num_sms);
+    return PROF(EGG_PROF_GEMM_PRE32, launch_gemm(c->stream, EPI_PRE32, c->d_u, dn_t, d, c->num_sms));
 }
 
 static RowParams base_row(egg_ctx *c, int M) {
@@ -498,7 +533,7 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
     const int8_t *mdl = c->d_model, *sh = c->d_shadow;
     cudaStream_t st = c->stream;
     int rc;
-    if ((rc = launch_noise_fill(st, c->d_nt, nm.stride, c->d_segs, c->nsegs, members / 2, step_seed, pop_base / 2, cf.device_mask, cf.device_gaussian))) return rc;
+    if ((rc = PROF(EGG_PROF_NOISE, launch_noise_fill(st, c->d_nt, nm.stride, c->d_segs, c->nsegs, members / 2, step_seed, pop_base / 2, cf.device_mask, cf.device_gaussian)))) return rc;
     EGG_CUDA(cudaMemsetAsync(c->d_wave_loss, 0, (size_t)members * 4, st));
     EGG_CUDA(cudaMemsetAsync(c->d_rowmax, 0, (size_t)M * 4, st));
     const int64_t data_stride = c->data_len / (cf.population_size / 2);
@@ -511,7 +546,7 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
     r0.nt_emb_a = nm.emb_a; r0.nt_emb_b = nm.emb_b; r0.nt_emb_bias_d = nm.emb_bias_d; r0.emb_shift = cf.fixed_point + cf.sigma_shift;
     r0.ln_w = mdl + L.ln_init; r0.ln_b = mdl + L.ln_init_bias; r0.nt_w_d = nm.ln_init.w_d; r0.nt_b_d = nm.ln_init.b_d;
     r0.ndots = 1; r0.nt_dot[0] = nm.mlp_init.up_b;
-    if ((rc = launch_rowwise(st, r0, 0))) return rc;
+    if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, r0, 0)))) return rc;
     if ((rc = run_mlp(c, M, nm.mlp_init, 0, sh + c->so.init_up, mdl + L.mlp_emb_bias_up, sh + c->so.init_dn, mdl + L.mlp_emb_bias_down))) return rc;
 
     for (int l = 0; l < cf.n_layers; l++) {
@@ -523,28 +558,28 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
         ra.ln_w = mdl + L.ln_1 + (int64_t)l * H; ra.ln_b = mdl + L.ln_1_bias + (int64_t)l * H;
         ra.nt_w_d = nb + lo.ln1.w_d; ra.nt_b_d = nb + lo.ln1.b_d;
         ra.ndots = 3; ra.nt_dot[0] = nb + lo.qkv_b; ra.nt_dot[1] = nb + lo.qkv_b + H; ra.nt_dot[2] = nb + lo.qkv_b + 2 * H;
-        if ((rc = launch_rowwise(st, ra, 1))) return rc;
+        if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, ra, 1)))) return rc;
         // fused Q|K|V projection + RoPE (mgpu.cu:779-784)
         GemmParams gq = base_gemm(c, M, 3 * H, H);
         gq.nt_a_off = nb + lo.qkv_a; gq.xb = c->d_xb; gq.xb_stride = 3; gq.out32 = c->d_pre; gq.rowstat = c->d_rowmax3; gq.third = H;
-        if ((rc = launch_gemm(st, EPI_QKV, c->d_h, shl + c->so.qkv, gq, c->num_sms))) return rc;
+        if ((rc = PROF(EGG_PROF_GEMM_QKV, launch_gemm(st, EPI_QKV, c->d_h, shl + c->so.qkv, gq, c->num_sms)))) return rc;
         AqnParams aq; aq.M = M; aq.H = H; aq.pre3 = c->d_pre; aq.rowmax3 = c->d_rowmax3; aq.q = c->d_q; aq.k = c->d_k; aq.v = c->d_v;
-        if ((rc = launch_aqn(st, aq))) return rc;
+        if ((rc = PROF(EGG_PROF_AQN, launch_aqn(st, aq)))) return rc;
         AttnParams ap; ap.members = members; ap.H = H; ap.head_dim = cf.head_dim; ap.seq_len = S; ap.shift_attn = cf.shift_attn;
         ap.q = c->d_q; ap.k = c->d_k; ap.v = c->d_v; ap.ao = c->d_ao; ap.exp_lut = c->d_exp_lut; ap.nt = c->d_nt;
         ap.nt_stride = nm.stride; ap.nt_o_b = nb + lo.o_b; ap.xbo = c->d_xbo;
-        if ((rc = launch_attention(st, ap))) return rc;
+        if ((rc = PROF(EGG_PROF_ATTENTION, launch_attention(st, ap)))) return rc;
         // output projection + residual (mgpu.cu:828-830)
         GemmParams go = base_gemm(c, M, H, H);
         go.nt_a_off = nb + lo.o_a; go.xb = c->d_xbo; go.xb_stride = 1; go.out_shift = cf.shift_out; go.resid = c->d_x;
         go.out32 = c->d_pre; go.rowstat = c->d_rowmax;
-        if ((rc = launch_gemm(st, EPI_PRE32, c->d_ao, shl + c->so.o, go, c->num_sms))) return rc;
+        if ((rc = PROF(EGG_PROF_GEMM_PRE32, launch_gemm(st, EPI_PRE32, c->d_ao, shl + c->so.o, go, c->num_sms)))) return rc;
         // ALN -> x ; LN2 -> h ; Σ h·b_up
         RowParams rb = base_row(c, M);
         rb.ln_w = mdl + L.ln_2 + (int64_t)l * H; rb.ln_b = mdl + L.ln_2_bias + (int64_t)l * H;
         rb.nt_w_d = nb + lo.ln2.w_d; rb.nt_b_d = nb + lo.ln2.b_d;
         rb.ndots = 1; rb.nt_dot[0] = nb + lo.mlp.up_b;
-        if ((rc = launch_rowwise(st, rb, 1))) return rc;
+        if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, rb, 1)))) return rc;
         if ((rc = run_mlp(c, M, lo.mlp, nb, shl + c->so.up, mdl + L.mlp_bias_up + (int64_t)l * 4 * H, shl + c->so.dn,
                           mdl + L.mlp_bias_down + (int64_t)l * H))) return rc;
     }
@@ -552,12 +587,12 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
     RowParams rf = base_row(c, M);
     rf.ln_w = mdl + L.ln_f; rf.ln_b = mdl + L.ln_f_bias; rf.nt_w_d = nm.ln_f.w_d; rf.nt_b_d = nm.ln_f.b_d;
     rf.ndots = 1; rf.nt_dot[0] = nm.emb_b;
-    if ((rc = launch_rowwise(st, rf, 1))) return rc;
+    if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, rf, 1)))) return rc;
     GemmParams gh = base_gemm(c, M, V, H);
     gh.nt_a_off = nm.emb_a; gh.xb = c->d_xb; gh.xb_stride = 3; gh.out_shift = cf.shift_logit;
     gh.dataset = c->d_data; gh.data_len = c->data_len; gh.start_idx = start_idx; gh.data_stride = data_stride; gh.pop_base = pop_base;
     gh.use_same_data = cf.use_same_data; gh.softmax_scale_bit = cf.softmax_scale_bit; gh.loss = c->d_wave_loss;
-    if ((rc = launch_gemm(st, EPI_HEAD, c->d_h, sh + c->so.emb, gh, c->num_sms))) return rc;
+    if ((rc = PROF(EGG_PROF_GEMM_HEAD, launch_gemm(st, EPI_HEAD, c->d_h, sh + c->so.emb, gh, c->num_sms)))) return rc;
     EGG_CUDA(cudaMemcpyAsync(loss_dst, c->d_wave_loss, (size_t)members * 4, cudaMemcpyDeviceToDevice, st));
     return EGG_OK;
 }
@@ -590,7 +625,7 @@ extern "C" int egg_read_losses(egg_ctx *c, int32_t *host_losses, int offset, int
 extern "C" int egg_compute_fitness_pairs(egg_ctx *c, int pair_offset, int pair_count) {
     if (!c || pair_offset < 0 || pair_count <= 0 || pair_offset + pair_count > c->cfg.population_size / 2) { set_error("bad pair range"); return EGG_E_INVALID; }
     EGG_CUDA(cudaSetDevice(c->device));
-    return launch_fitness(c->stream, c->d_loss + 2 * (int64_t)pair_offset, c->d_fit + pair_offset, pair_count);
+    return PROF(EGG_PROF_FITNESS, launch_fitness(c->stream, c->d_loss + 2 * (int64_t)pair_offset, c->d_fit + pair_offset, pair_count));
 }
 
 extern "C" int egg_write_fitness(egg_ctx *c, const int32_t *host_fitness, int pair_offset, int pair_count) {
@@ -652,8 +687,8 @@ extern "C" int egg_allgather_fitness(egg_ctx *c) {
 static int update_matrix(egg_ctx *c, const ParamDesc &d, uint32_t step_seed, float lr) {
     const egg_config &cf = c->cfg;
     const int pairs = cf.population_size / 2;
-    int rc = launch_update_operands(c->stream, c->d_na, c->d_nb, c->d_fit, pairs, c->kp, d.rows_k, d.cols_n, d.off_a, d.off_b,
-                                    d.seed_base, step_seed, cf.device_mask, cf.device_gaussian, 0);
+    int rc = PROF(EGG_PROF_UPD_OPERANDS, launch_update_operands(c->stream, c->d_na, c->d_nb, c->d_fit, pairs, c->kp, d.rows_k, d.cols_n, d.off_a, d.off_b,
+                                    d.seed_base, step_seed, cf.device_mask, cf.device_gaussian, 0));
     if (rc) return rc;
     GemmParams g;
     memset(&g, 0, sizeof(g));
@@ -662,10 +697,11 @@ static int update_matrix(egg_ctx *c, const ParamDesc &d, uint32_t step_seed, flo
     g.opt = reinterpret_cast<float *>(c->d_opt + d.opt_off);
     g.lr = lr * d.lr_scale; g.beta1 = cf.adam_beta1; g.beta2 = cf.adam_beta2; g.eps = cf.adam_eps; g.wd = cf.adam_weight_decay;
     g.mu = cf.muon_momentum; g.total_updates = c->d_updates; g.err = c->d_err;
-    if (!d.muon) return launch_gemm(c->stream, EPI_ADAM, c->d_na, c->d_nb, g, c->num_sms);
+    if (!d.muon) return PROF(EGG_PROF_UPD_GEMM, launch_gemm(c->stream, EPI_ADAM, c->d_na, c->d_nb, g, c->num_sms));
     g.m_rowmajor = c->muon.x;
-    if ((rc = launch_gemm(c->stream, EPI_MUON_M, c->d_na, c->d_nb, g, c->num_sms))) return rc;
-    if ((rc = launch_newton_schulz(c->stream, c->muon, d.rows_k, d.cols_n))) return rc;
+    if ((rc = PROF(EGG_PROF_UPD_GEMM, launch_gemm(c->stream, EPI_MUON_M, c->d_na, c->d_nb, g, c->num_sms)))) return rc;
+    if ((rc = PROFN(EGG_PROF_MUON, 12, launch_newton_schulz(c->stream, c->muon, d.rows_k, d.cols_n)))) return rc;
+    ProfScope ps_apply(c, EGG_PROF_MUON);
     return launch_muon_apply(c->stream, c->d_model + d.model_off, reinterpret_cast<float *>(c->d_opt + d.opt_off), c->muon.x,
                              d.rows_k, d.cols_n, lr * cf.muon_lr_scale, cf.adam_weight_decay, c->d_updates);
 }
@@ -683,7 +719,7 @@ static int apply_update_async(egg_ctx *c, uint32_t step_seed, float lr) {
             v.off_a = d.off_a; v.off_b = d.off_b; v.seed_base = d.seed_base; v.fit = c->d_fit; v.pairs = cf.population_size / 2;
             v.step_seed = step_seed; v.lr = lr * d.lr_scale; v.beta1 = cf.adam_beta1; v.beta2 = cf.adam_beta2; v.eps = cf.adam_eps;
             v.wd = cf.adam_weight_decay; v.mask = cf.device_mask; v.gaussian = cf.device_gaussian; v.total_updates = c->d_updates;
-            rc = launch_update_vector(c->stream, v);
+            rc = PROF(EGG_PROF_UPD_VECTOR, launch_update_vector(c->stream, v));
         }
         if (rc) return rc;
     }
@@ -719,7 +755,7 @@ extern "C" int egg_generation_host(egg_ctx *c, const uint8_t *host_tokens, int64
     rc = egg_eval_chunk(c, step_seed, step * c->cfg.seq_len, off, per);   // start_idx = step*SEQ_LEN, mgpu.cu:1532
     c->cfg.chunk_relative_loss = saved;
     if (rc) return rc;
-    if ((rc = launch_fitness(c->stream, c->d_loss + off, c->d_fit + off / 2, per / 2))) return rc;
+    if ((rc = PROF(EGG_PROF_FITNESS, launch_fitness(c->stream, c->d_loss + off, c->d_fit + off / 2, per / 2)))) return rc;
     if ((rc = egg_allgather_fitness(c))) return rc;
     if ((rc = apply_update_async(c, step_seed, learning_rate))) return rc;
     unsigned long long u = 0;
@@ -848,3 +884,51 @@ extern "C" int egg_update_reconstruct(egg_ctx *c, const int32_t *fitness, int pa
 #undef PTRYC
     return check_dev_err(c);
 }
+
+// ---------------------------------------------------------------- measurement
+
+extern "C" int egg_timer_start(egg_ctx *c) {
+    if (!c) { set_error("null context"); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    EGG_CUDA(cudaEventRecord(c->t0, c->stream));
+    return EGG_OK;
+}
+
+extern "C" int egg_timer_stop(egg_ctx *c, float *ms) {
+    if (!c || !ms) { set_error("null argument"); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    EGG_CUDA(cudaEventRecord(c->t1, c->stream));
+    EGG_CUDA(cudaEventSynchronize(c->t1));
+    EGG_CUDA(cudaEventElapsedTime(ms, c->t0, c->t1));
+    return check_dev_err(c);
+}
+
+extern "C" int egg_profile_enable(egg_ctx *c, int enable) {
+    if (!c) { set_error("null context"); return EGG_E_INVALID; }
+    c->prof_on = enable != 0;
+    return EGG_OK;
+}
+
+extern "C" int egg_profile_read(egg_ctx *c, float *ms, int64_t *launches) {
+    if (!c || !ms || !launches) { set_error("null argument"); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    EGG_CUDA(cudaStreamSynchronize(c->stream));
+    for (int i = 0; i < EGG_PROF_N; i++) { ms[i] = 0.0f; launches[i] = c->prof_launches[i]; c->prof_launches[i] = 0; }
+    for (size_t i = 0; i + 1 < c->prof_used; i += 2) {
+        float t = 0.0f;
+        EGG_CUDA(cudaEventElapsedTime(&t, c->prof_ev[i], c->prof_ev[i + 1]));
+        ms[c->prof_cls[i / 2]] += t;
+    }
+    c->prof_used = 0;
+    return EGG_OK;
+}
+
+extern "C" const char *egg_profile_name(int cls) {
+    static const char *names[EGG_PROF_N] = {"noise_fill", "rowwise", "gemm_gelu", "gemm_pre32", "gemm_qkv", "gemm_head", "aqn",
+                                            "attention", "fitness", "update_operands", "update_gemm", "update_vector", "muon",
+                                            "transpose"};
+    return (cls >= 0 && cls < EGG_PROF_N) ? names[cls] : "";
+}
+
+extern "C" int64_t egg_launch_count(egg_ctx *c) { return c ? c->launches : 0; }
+extern "C" int egg_wave_members(egg_ctx *c) { return c ? c->wave_members : 0; }

@@ -37,10 +37,10 @@ extern "C" {
  * the reference's own defaults.
  */
 typedef struct egg_config {
-    int32_t hidden_dim;          /* HIDDEN_DIM  (multiple of 64, <= 1024)          */
+    int32_t hidden_dim;          /* HIDDEN_DIM  (multiple of 128, <= 1024)         */
     int32_t head_dim;            /* HEAD_DIM    (64)                                */
     int32_t n_layers;            /* N_LAYERS                                        */
-    int32_t seq_len;             /* SEQ_LEN     (>= 8)                              */
+    int32_t seq_len;             /* SEQ_LEN     (multiple of 16)                    */
     int32_t vocab_size;          /* VOCAB_SIZE  (256: byte tokens)                  */
     int32_t population_size;     /* POPULATION_SIZE (even)                          */
     int32_t fixed_point;         /* FIXED_POINT                                     */
@@ -188,6 +188,45 @@ int egg_perturbed_projection(egg_ctx *ctx, const int8_t *x, const int8_t *w_pack
 int egg_update_reconstruct(egg_ctx *ctx, const int32_t *fitness, int pairs,
                            int rows_k, int cols_n, int off_a, int off_b, int seed_base,
                            uint32_t step_seed, int32_t *vote_out, int on_device);
+
+/* ---- measurement ------------------------------------------------------ */
+/*
+ * The reference times a generation with clock_gettime around its launches
+ * (mgpu.cu:1510, 1680) and has no per-kernel timing.  These helpers time on the
+ * device instead: CUDA events recorded on the context's own stream.
+ */
+int egg_timer_start(egg_ctx *ctx);
+/* Records the stop event, synchronises the stream, returns elapsed milliseconds. */
+int egg_timer_stop(egg_ctx *ctx, float *ms);
+
+/* Kernel classes of the per-class profile. */
+enum {
+    EGG_PROF_NOISE = 0,     /* per-pair noise tables                                  */
+    EGG_PROF_ROWWISE,       /* embedding / adaptive-normalise / mean-abs norm rows    */
+    EGG_PROF_GEMM_GELU,     /* MLP up projection  (tcgen05 int8)                      */
+    EGG_PROF_GEMM_PRE32,    /* O and MLP down projections                             */
+    EGG_PROF_GEMM_QKV,      /* fused Q|K|V projection + RoPE                          */
+    EGG_PROF_GEMM_HEAD,     /* tied-embedding head + cross-entropy                    */
+    EGG_PROF_AQN,           /* Q/K/V requantisation                                   */
+    EGG_PROF_ATTENTION,     /* causal integer-softmax attention                       */
+    EGG_PROF_FITNESS,
+    EGG_PROF_UPD_OPERANDS,  /* noise operands of the update GEMM                      */
+    EGG_PROF_UPD_GEMM,      /* update reconstruction GEMM + AdamW / Muon momentum     */
+    EGG_PROF_UPD_VECTOR,    /* vector parameters                                      */
+    EGG_PROF_MUON,          /* Newton–Schulz + apply                                  */
+    EGG_PROF_TRANSPOSE,     /* packed -> K-major weight shadows                       */
+    EGG_PROF_N
+};
+/* enable != 0: every launch is bracketed by events (a few microseconds each). */
+int egg_profile_enable(egg_ctx *ctx, int enable);
+/* Synchronises, then adds up what was recorded since the last read:
+ * ms[EGG_PROF_N] device time and launches[EGG_PROF_N] launch counts per class. */
+int egg_profile_read(egg_ctx *ctx, float *ms, int64_t *launches);
+const char *egg_profile_name(int cls);
+/* Kernels launched by this context since it was created. */
+int64_t egg_launch_count(egg_ctx *ctx);
+/* Members evaluated per internal wave (chosen at creation). */
+int egg_wave_members(egg_ctx *ctx);
 
 #ifdef __cplusplus
 }

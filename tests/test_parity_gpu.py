@@ -164,3 +164,32 @@ def test_update_reconstruct_matches_oracle(ternary):
     ctx.update_reconstruct(fit, 300, 256, 128, 402, 403, 1000, 2, vote)
     assert (vote == want).all()
     ctx.close()
+
+
+def test_benchmark_config_sample_matches_reference_kernels():
+    """Full benchmark configuration (H=512, L=4, S=256, POP=40960): two 64-member slices of the
+    population against the reference's own kernels, and the whole-population loss checksum is stable
+    across wave sizes."""
+    if not ref_binary("c2"):
+        pytest.skip("oracle/_ref/ref_mgpu_c2 not built")
+    pkg = load_pkg()
+    from egg_c_b200 import synth
+    kw = REF_CONFIGS["c2"]
+    cfg, ocfg = cfg_pair(**kw)
+    model = synth.random_model(cfg, 0, "uniform")
+    data = synth.zipf_bytes(1, 8 << 20)
+    ctx = _ctx(cfg, wave=64)
+    ctx.upload_model(model)
+    ctx.set_dataset(data)
+    for off in (0, 40960 - 64):
+        ctx.eval_chunk(SEED, 256, off, 64)
+        got = ctx.read_losses(off, 64)
+        ref = run_ref_mgpu("c2", model, data, SEED, 256, off, 64)
+        assert (got == ref["losses"]).all(), (off, got[:6], ref["losses"][:6])
+    ctx.close()
+    ctx2 = _ctx(cfg, wave=48)      # a wave size that leaves a ragged last wave
+    ctx2.upload_model(model)
+    ctx2.set_dataset(data)
+    ctx2.eval_chunk(SEED, 256, 40960 - 64, 64)
+    assert (ctx2.read_losses(40960 - 64, 64) == got).all()
+    ctx2.close()
