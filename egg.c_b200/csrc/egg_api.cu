@@ -533,7 +533,7 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
     const int8_t *mdl = c->d_model, *sh = c->d_shadow;
     cudaStream_t st = c->stream;
     int rc;
-    if ((rc = PROF(EGG_PROF_NOISE, launch_noise_fill(st, c->d_nt, nm.stride, c->d_segs, c->nsegs, members / 2, step_seed, pop_base / 2, cf.device_mask, cf.device_gaussian)))) return rc;
+    if ((rc = PROF(EGG_PROF_NOISE, launch_noise_fill(st, c->d_nt, nm.stride, c->d_segs, c->nsegs, members / 2, step_seed, pop_base / 2, cf.device_mask, cf.device_gaussian, mdl)))) return rc;
     EGG_CUDA(cudaMemsetAsync(c->d_wave_loss, 0, (size_t)members * 4, st));
     EGG_CUDA(cudaMemsetAsync(c->d_rowmax, 0, (size_t)M * 4, st));
     const int64_t data_stride = c->data_len / (cf.population_size / 2);
@@ -544,7 +544,7 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
     r0.pop_base = pop_base; r0.use_same_data = cf.use_same_data;
     r0.emb_packed = mdl + L.embedding; r0.emb_bias = mdl + L.emb_bias; r0.vocab = V;
     r0.nt_emb_a = nm.emb_a; r0.nt_emb_b = nm.emb_b; r0.nt_emb_bias_d = nm.emb_bias_d; r0.emb_shift = cf.fixed_point + cf.sigma_shift;
-    r0.ln_w = mdl + L.ln_init; r0.ln_b = mdl + L.ln_init_bias; r0.nt_w_d = nm.ln_init.w_d; r0.nt_b_d = nm.ln_init.b_d;
+    r0.nt_w_m = nm.ln_init.w_m; r0.nt_b_m = nm.ln_init.b_m;
     r0.ndots = 1; r0.nt_dot[0] = nm.mlp_init.up_b;
     if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, r0, 0)))) return rc;
     if ((rc = run_mlp(c, M, nm.mlp_init, 0, sh + c->so.init_up, mdl + L.mlp_emb_bias_up, sh + c->so.init_dn, mdl + L.mlp_emb_bias_down))) return rc;
@@ -555,8 +555,7 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
         const int8_t *shl = sh + c->so.layer0 + (int64_t)l * c->so.layer_stride;
         // ALN of the previous block -> x ; LN1 -> h ; Σ h·b for q,k,v (mgpu.cu:770-776)
         RowParams ra = base_row(c, M);
-        ra.ln_w = mdl + L.ln_1 + (int64_t)l * H; ra.ln_b = mdl + L.ln_1_bias + (int64_t)l * H;
-        ra.nt_w_d = nb + lo.ln1.w_d; ra.nt_b_d = nb + lo.ln1.b_d;
+        ra.nt_w_m = nb + lo.ln1.w_m; ra.nt_b_m = nb + lo.ln1.b_m;
         ra.ndots = 3; ra.nt_dot[0] = nb + lo.qkv_b; ra.nt_dot[1] = nb + lo.qkv_b + H; ra.nt_dot[2] = nb + lo.qkv_b + 2 * H;
         if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, ra, 1)))) return rc;
         // fused Q|K|V projection + RoPE (mgpu.cu:779-784)
@@ -576,8 +575,7 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
         if ((rc = PROF(EGG_PROF_GEMM_PRE32, launch_gemm(st, EPI_PRE32, c->d_ao, shl + c->so.o, go, c->num_sms)))) return rc;
         // ALN -> x ; LN2 -> h ; Σ h·b_up
         RowParams rb = base_row(c, M);
-        rb.ln_w = mdl + L.ln_2 + (int64_t)l * H; rb.ln_b = mdl + L.ln_2_bias + (int64_t)l * H;
-        rb.nt_w_d = nb + lo.ln2.w_d; rb.nt_b_d = nb + lo.ln2.b_d;
+        rb.nt_w_m = nb + lo.ln2.w_m; rb.nt_b_m = nb + lo.ln2.b_m;
         rb.ndots = 1; rb.nt_dot[0] = nb + lo.mlp.up_b;
         if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, rb, 1)))) return rc;
         if ((rc = run_mlp(c, M, lo.mlp, nb, shl + c->so.up, mdl + L.mlp_bias_up + (int64_t)l * 4 * H, shl + c->so.dn,
@@ -585,7 +583,7 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
     }
     // final norm + tied-embedding head + cross-entropy (mgpu.cu:954-1024)
     RowParams rf = base_row(c, M);
-    rf.ln_w = mdl + L.ln_f; rf.ln_b = mdl + L.ln_f_bias; rf.nt_w_d = nm.ln_f.w_d; rf.nt_b_d = nm.ln_f.b_d;
+    rf.nt_w_m = nm.ln_f.w_m; rf.nt_b_m = nm.ln_f.b_m;
     rf.ndots = 1; rf.nt_dot[0] = nm.emb_b;
     if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, rf, 1)))) return rc;
     GemmParams gh = base_gemm(c, M, V, H);
@@ -814,10 +812,10 @@ extern "C" int egg_perturbed_projection(egg_ctx *c, const int8_t *x, const int8_
         PTRYC(cudaMemcpyAsync(d_w, w_packed, (size_t)K * N, cudaMemcpyHostToDevice, st));
     }
     PTRY(dev_alloc(&d_wt, (int64_t)K * N)); PTRY(dev_alloc(&d_nt, pairs * stride)); PTRY(dev_alloc(&d_xb, rows)); PTRY(dev_alloc(&d_segs, 2));
-    NoiseSeg segs[2] = {{0, N, 0, off_a, 0, 0}, {N, K, 0, off_b, 0, 0}};
+    NoiseSeg segs[2] = {{0, N, 0, off_a, 0, 0, -1}, {N, K, 0, off_b, 0, 0, -1}};
     PTRYC(cudaMemcpyAsync(d_segs, segs, sizeof(segs), cudaMemcpyHostToDevice, st));
     PTRY(launch_unpack_transpose(st, d_w, d_wt, K, N));
-    PTRY(launch_noise_fill(st, d_nt, stride, d_segs, 2, (int)pairs, seed, 0, c->cfg.device_mask, c->cfg.device_gaussian));
+    PTRY(launch_noise_fill(st, d_nt, stride, d_segs, 2, (int)pairs, seed, 0, c->cfg.device_mask, c->cfg.device_gaussian, nullptr));
     rowdot_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(d_x, d_nt, stride, N, rows_per_member, rows, K, d_xb);
     PTRYC(cudaGetLastError());
     GemmParams g;

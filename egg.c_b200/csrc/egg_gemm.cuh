@@ -17,7 +17,7 @@ namespace egg {
 
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 128;            // bytes (= int8 elements) per k-block: one swizzle row
-constexpr int GEMM_STAGES = 4;
+constexpr int GEMM_STAGES = 3;
 constexpr int GEMM_THREADS = 320;       // warp0 TMA, warp1 MMA, warps 2..9 epilogue
 constexpr int GEMM_EPI_THREADS = 256;
 constexpr int GEMM_MAX_SLOTS = 9;       // distinct population pairs a 128-row tile can touch (seq_len >= 8)
@@ -80,10 +80,10 @@ template <int BN>
 struct GemmSmem {
     alignas(1024) uint8_t a[GEMM_STAGES][GEMM_BM * GEMM_BK];
     alignas(1024) uint8_t b[GEMM_STAGES][BN * GEMM_BK];
-    alignas(16) int8_t a_tab[GEMM_MAX_SLOTS][BN];
-    alignas(16) int8_t c_tab[GEMM_MAX_SLOTS][2][BN];
-    alignas(16) int8_t d_tab[GEMM_MAX_SLOTS][BN];
-    alignas(16) int8_t bias[BN];
+    alignas(16) int32_t stage[8][32][36];               // per epilogue warp: 32 rows x 32 columns (+4 pad) transpose buffer
+    alignas(16) int8_t a_tab[GEMM_MAX_SLOTS][BN];       // A-noise of this projection per pair slot
+    alignas(16) int16_t bc_tab[GEMM_MAX_SLOTS][2][BN];  // bias + bias-noise delta per pair slot and sign
+    alignas(16) int8_t d_tab[GEMM_MAX_SLOTS][BN];       // B-noise of the next projection (EPI_GELU)
     alignas(16) int8_t act_lut[256];
     alignas(16) int32_t exp_lut[256];
     alignas(8) uint64_t full[GEMM_STAGES];
@@ -244,14 +244,23 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     int sl = i / (BN / 4), j = (i % (BN / 4)) * 4;
                     const int8_t *base = p.nt + (int64_t)(first_pl + sl) * p.nt_stride;
                     *reinterpret_cast<int32_t *>(&sm.a_tab[sl][j]) = *reinterpret_cast<const int32_t *>(base + p.nt_a_off + n0 + j);
-                    if ((EPI == EPI_GELU || EPI == EPI_PRE32) && p.nt_c_off >= 0) {
-                        *reinterpret_cast<int32_t *>(&sm.c_tab[sl][0][j]) = *reinterpret_cast<const int32_t *>(base + p.nt_c_off + n0 + j);
-                        *reinterpret_cast<int32_t *>(&sm.c_tab[sl][1][j]) = *reinterpret_cast<const int32_t *>(base + p.nt_c_off + p.N + n0 + j);
+                    if (EPI == EPI_GELU || EPI == EPI_PRE32) {
+                        int32_t b4 = p.bias ? *reinterpret_cast<const int32_t *>(p.bias + n0 + j) : 0;
+                        int32_t cp = 0, cn = 0;
+                        if (p.nt_c_off >= 0) {
+                            cp = *reinterpret_cast<const int32_t *>(base + p.nt_c_off + n0 + j);
+                            cn = *reinterpret_cast<const int32_t *>(base + p.nt_c_off + p.N + n0 + j);
+                        }
+#pragma unroll
+                        for (int b = 0; b < 4; b++) {
+                            int bb = (int)(int8_t)(b4 >> (8 * b));
+                            sm.bc_tab[sl][0][j + b] = (int16_t)(bb + (int)(int8_t)(cp >> (8 * b)));
+                            sm.bc_tab[sl][1][j + b] = (int16_t)(bb + (int)(int8_t)(cn >> (8 * b)));
+                        }
                     }
                     if (EPI == EPI_GELU)
                         *reinterpret_cast<int32_t *>(&sm.d_tab[sl][j]) = *reinterpret_cast<const int32_t *>(base + p.nt_d_off + n0 + j);
                 }
-                if ((EPI == EPI_GELU || EPI == EPI_PRE32) && e < BN) sm.bias[e] = p.bias ? p.bias[n0 + e] : (int8_t)0;
             }
             // one thread waits for the accumulator, everybody learns the outcome at the barrier
             if (e == 0) {
@@ -270,157 +279,153 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 // nothing to compute; still takes part in the barrier protocol below
             } else if (EPI <= EPI_HEAD) {
                 // ---------------- evaluation epilogues ----------------
-                int xbs = 0;
-                if (row_ok) {
-                    int xcol = (EPI == EPI_QKV) ? (n0 / p.third) : 0;
-                    int xbv = p.xb[(int64_t)r * p.xb_stride + xcol];
-                    xbs = sgn ? -xbv : xbv;
+                // Accumulators leave TMEM one row per lane; they are transposed through shared memory so
+                // that 8 consecutive lanes own 32 consecutive columns of one row: every global access below
+                // is then a run of full 32-byte sectors, and the per-column tables are read as words.
+                int32_t(*st)[36] = sm.stage[ew];
+                const int lrow = lane >> 3, pc = lane & 7;          // row group / 4-column piece of this lane
+                int rrow[8], xbs[8], slot_sgn[8], aux[8];           // per-row state of the 8 rows this lane touches
+                bool rok[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int rr = m0 + quarter * 32 + i * 4 + lrow;
+                    rok[i] = rr < p.M;
+                    const int rc = rok[i] ? rr : (p.M - 1);
+                    rrow[i] = rc;
+                    const int mem = rc / p.seq_len;
+                    const int sg = mem & 1;
+                    slot_sgn[i] = (((mem >> 1) - first_pl) << 1) | sg;
+                    const int xcol = (EPI == EPI_QKV) ? (n0 / p.third) : 0;
+                    const int xbv = p.xb[(int64_t)rc * p.xb_stride + xcol];
+                    xbs[i] = sg ? -xbv : xbv;
+                    aux[i] = 0;
+                    if (EPI == EPI_QKV) aux[i] = rc - mem * p.seq_len;                 // token position t
+                    if (EPI == EPI_HEAD) {                                             // target byte of this row
+                        const int t = rc - mem * p.seq_len;
+                        const int64_t pair = (p.pop_base + mem) >> 1;
+                        const int64_t pos = p.use_same_data ? (p.start_idx % (p.data_len - p.seq_len))
+                                                            : ((p.start_idx + pair * p.data_stride) % (p.data_len - p.seq_len));
+                        aux[i] = p.dataset[pos + t + 1];
+                    }
                 }
-                const int8_t *atab = sm.a_tab[slot];
-                if (EPI == EPI_HEAD) {
-                    // pass 1: row max of the logits; pass 2: Σ exp-LUT and the target logit (mgpu.cu:969-1023)
-                    int mx = INT_MIN;
-                    for (int c = 0; c < BN; c += 32) {
-                        uint32_t v[32];
-                        ptx::tmem_ld32(taddr + c, v);
-                        ptx::tmem_ld_wait();
+                int racc[8];                                        // running abs-max / dot / row max per row
 #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            int lg = ((int)v[j] + ((xbs * (int)atab[c + j]) >> p.rank1_shift)) >> p.out_shift;
-                            mx = max(mx, lg);
-                        }
-                    }
-                    int target = 0;
-                    if (row_ok) {
-                        int mem = r / p.seq_len, t = r % p.seq_len;
-                        int64_t pair = (p.pop_base + mem) >> 1;
-                        int64_t pos = p.use_same_data ? (p.start_idx % (p.data_len - p.seq_len))
-                                                      : ((p.start_idx + pair * p.data_stride) % (p.data_len - p.seq_len));
-                        target = p.dataset[pos + t + 1];
-                    }
-                    long long sum_ex = 0;
-                    int tgt_logit = 0;
-                    for (int c = 0; c < BN; c += 32) {
-                        uint32_t v[32];
-                        ptx::tmem_ld32(taddr + c, v);
-                        ptx::tmem_ld_wait();
+                for (int i = 0; i < 8; i++) racc[i] = (EPI == EPI_HEAD) ? INT_MIN : 0;
+                int rsum[8], rtgt[8];
 #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            int lg = ((int)v[j] + ((xbs * (int)atab[c + j]) >> p.rank1_shift)) >> p.out_shift;
-                            int idx = mx - lg;
-                            idx = idx > 255 ? 255 : idx;
-                            sum_ex += sm.exp_lut[idx];
-                            if (c + j == target) tgt_logit = lg;
+                for (int i = 0; i < 8; i++) { rsum[i] = 0; rtgt[i] = 0; }
+
+                constexpr int NPASS = (EPI == EPI_HEAD) ? 2 : 1;
+#pragma unroll 1
+                for (int pass = 0; pass < NPASS; pass++) {
+                    if (EPI == EPI_HEAD && pass == 1) {
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {               // finish the row maxima of pass 0
+                            int m = racc[i];
+                            m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+                            m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
+                            m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 4));
+                            racc[i] = m;
                         }
                     }
-                    if (row_ok) {
-                        int log_sum = 0;
-                        if (sum_ex > 0) {
-                            int pos = 63 - __clzll(sum_ex);              // floor(log2), as the shift ladder of mgpu.cu:1015-1019
-                            log_sum = (pos << 4) - (p.softmax_scale_bit << 4);
-                        }
-                        int l = (log_sum >> 1) + mx - tgt_logit;
-                        atomicAdd(&p.loss[r / p.seq_len], l);
-                    }
-                } else {
-                    int run_max = 0, run_max2 = 0;    // abs-max (PRE32 / QKV)
-                    int dot = 0;                      // Σ u·noise (GELU)
+#pragma unroll 1
                     for (int c = 0; c < COLS_PER; c += 32) {
-                        uint32_t v[32];
-                        ptx::tmem_ld32(taddr + c, v);
-                        ptx::tmem_ld_wait();
-                        const int cc = cbase + c;     // column inside the tile
-                        if (EPI == EPI_CLIP8) {
-                            uint32_t w[8];
+                        {
+                            uint32_t v[32];
+                            ptx::tmem_ld32(taddr + c, v);
+                            ptx::tmem_ld_wait();
 #pragma unroll
-                            for (int j = 0; j < 32; j++) {
-                                int y = clip8(((int)v[j] + ((xbs * (int)atab[cc + j]) >> p.rank1_shift)) >> p.out_shift);
-                                if ((j & 3) == 0) w[j >> 2] = 0;
-                                w[j >> 2] |= (uint32_t)(y & 0xFF) << ((j & 3) * 8);
-                            }
-                            if (row_ok) {
-                                int4 *dst = reinterpret_cast<int4 *>(p.out8 + (int64_t)r * p.N + n0 + cc);
-                                dst[0] = make_int4(w[0], w[1], w[2], w[3]);
-                                dst[1] = make_int4(w[4], w[5], w[6], w[7]);
-                            }
-                        } else if (EPI == EPI_GELU) {
-                            uint32_t w[8];
-                            const int8_t *ctab = sm.c_tab[slot][sgn];
-                            const int8_t *dtab = sm.d_tab[slot];
-                            const bool has_c = p.nt_c_off >= 0;
+                            for (int qd = 0; qd < 8; qd++)
+                                *reinterpret_cast<int4 *>(&st[lane][4 * qd]) = make_int4(v[4 * qd], v[4 * qd + 1], v[4 * qd + 2], v[4 * qd + 3]);
+                        }
+                        __syncwarp();
+                        const int col = cbase + c + 4 * pc;          // column inside the tile of this lane's 4 values
 #pragma unroll
-                            for (int j = 0; j < 32; j++) {
-                                int a = (int)v[j] + ((xbs * (int)atab[cc + j]) >> p.rank1_shift);
-                                int z = (a >> p.out_shift) + (int)sm.bias[cc + j] + (has_c ? (int)ctab[cc + j] : 0);
-                                int u = sm.act_lut[(uint8_t)(int8_t)clip8(z)];
-                                dot += u * (int)dtab[cc + j];
-                                if ((j & 3) == 0) w[j >> 2] = 0;
-                                w[j >> 2] |= (uint32_t)(u & 0xFF) << ((j & 3) * 8);
-                            }
-                            if (row_ok) {
-                                int4 *dst = reinterpret_cast<int4 *>(p.out8 + (int64_t)r * p.N + n0 + cc);
-                                dst[0] = make_int4(w[0], w[1], w[2], w[3]);
-                                dst[1] = make_int4(w[4], w[5], w[6], w[7]);
-                            }
-                        } else if (EPI == EPI_PRE32) {
-                            const int8_t *ctab = sm.c_tab[slot][sgn];
-                            const bool has_c = p.nt_c_off >= 0;
-                            int4 rs[2] = {make_int4(0, 0, 0, 0), make_int4(0, 0, 0, 0)};
-                            if (row_ok) {
-                                const int4 *src = reinterpret_cast<const int4 *>(p.resid + (int64_t)r * p.N + n0 + cc);
-                                rs[0] = src[0]; rs[1] = src[1];
-                            }
-                            const int8_t *rb = reinterpret_cast<const int8_t *>(rs);
-#pragma unroll
-                            for (int j = 0; j < 32; j++) {
-                                int a = (int)v[j] + ((xbs * (int)atab[cc + j]) >> p.rank1_shift);
-                                int pre = (int)rb[j] + (a >> p.out_shift) + (int)sm.bias[cc + j] + (has_c ? (int)ctab[cc + j] : 0);
-                                v[j] = (uint32_t)pre;
-                                run_max = max(run_max, abs(pre));
-                            }
-                            if (row_ok) {
-                                int4 *dst = reinterpret_cast<int4 *>(p.out32 + (int64_t)r * p.N + n0 + cc);
-#pragma unroll
-                                for (int q = 0; q < 8; q++) dst[q] = make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                            }
-                        } else if (EPI == EPI_QKV) {
-                            const int which = n0 / p.third;           // 0 q, 1 k, 2 v (tile never straddles)
-                            if (which < 2) {
-                                // integer RoPE on adjacent (even, odd) columns (apply_rope_integer, mgpu.cu:624-644)
-                                const int t = (row_ok ? r : 0) % p.seq_len;
-                                const int hd0 = (n0 + cc) % p.head_dim;
-                                const int4 *lut = reinterpret_cast<const int4 *>(p.rope_lut + (int64_t)t * p.head_dim + hd0);
-                                const long long half_ulp = 1ll << (p.rope_bit - 1);
-#pragma unroll
-                                for (int q = 0; q < 8; q++) {
-                                    int4 cs = __ldg(&lut[q]);     // c0 s0 c1 s1
-                                    long long e0 = (int)v[4 * q] + ((xbs * (int)atab[cc + 4 * q]) >> p.rank1_shift);
-                                    long long o0 = (int)v[4 * q + 1] + ((xbs * (int)atab[cc + 4 * q + 1]) >> p.rank1_shift);
-                                    long long e1 = (int)v[4 * q + 2] + ((xbs * (int)atab[cc + 4 * q + 2]) >> p.rank1_shift);
-                                    long long o1 = (int)v[4 * q + 3] + ((xbs * (int)atab[cc + 4 * q + 3]) >> p.rank1_shift);
-                                    v[4 * q] = (uint32_t)(int)((e0 * cs.x - o0 * cs.y + half_ulp) >> p.rope_bit);
-                                    v[4 * q + 1] = (uint32_t)(int)((e0 * cs.y + o0 * cs.x + half_ulp) >> p.rope_bit);
-                                    v[4 * q + 2] = (uint32_t)(int)((e1 * cs.z - o1 * cs.w + half_ulp) >> p.rope_bit);
-                                    v[4 * q + 3] = (uint32_t)(int)((e1 * cs.w + o1 * cs.z + half_ulp) >> p.rope_bit);
+                        for (int i = 0; i < 8; i++) {
+                            const int4 a4 = *reinterpret_cast<const int4 *>(&st[i * 4 + lrow][4 * pc]);
+                            const int sl = slot_sgn[i] >> 1, sg = slot_sgn[i] & 1;
+                            const int32_t aw = *reinterpret_cast<const int32_t *>(&sm.a_tab[sl][col]);
+                            int v0 = a4.x + ((xbs[i] * (int)(int8_t)(aw)) >> p.rank1_shift);
+                            int v1 = a4.y + ((xbs[i] * (int)(int8_t)(aw >> 8)) >> p.rank1_shift);
+                            int v2 = a4.z + ((xbs[i] * (int)(int8_t)(aw >> 16)) >> p.rank1_shift);
+                            int v3 = a4.w + ((xbs[i] * (int)(aw >> 24)) >> p.rank1_shift);
+                            const int64_t gofs = (int64_t)rrow[i] * p.N + n0 + col;
+                            if (EPI == EPI_CLIP8) {
+                                uint32_t w = (uint32_t)(clip8(v0 >> p.out_shift) & 0xFF) | ((uint32_t)(clip8(v1 >> p.out_shift) & 0xFF) << 8) |
+                                             ((uint32_t)(clip8(v2 >> p.out_shift) & 0xFF) << 16) | ((uint32_t)(clip8(v3 >> p.out_shift) & 0xFF) << 24);
+                                if (rok[i]) *reinterpret_cast<uint32_t *>(p.out8 + gofs) = w;
+                            } else if (EPI == EPI_GELU) {
+                                const int2 bc = *reinterpret_cast<const int2 *>(&sm.bc_tab[sl][sg][col]);
+                                const int u0 = sm.act_lut[(uint8_t)(int8_t)clip8((v0 >> p.out_shift) + (int)(int16_t)(bc.x & 0xFFFF))];
+                                const int u1 = sm.act_lut[(uint8_t)(int8_t)clip8((v1 >> p.out_shift) + (bc.x >> 16))];
+                                const int u2 = sm.act_lut[(uint8_t)(int8_t)clip8((v2 >> p.out_shift) + (int)(int16_t)(bc.y & 0xFFFF))];
+                                const int u3 = sm.act_lut[(uint8_t)(int8_t)clip8((v3 >> p.out_shift) + (bc.y >> 16))];
+                                const uint32_t w = (uint32_t)(u0 & 0xFF) | ((uint32_t)(u1 & 0xFF) << 8) | ((uint32_t)(u2 & 0xFF) << 16) | ((uint32_t)(u3 & 0xFF) << 24);
+                                racc[i] = __dp4a((int)w, *reinterpret_cast<const int32_t *>(&sm.d_tab[sl][col]), racc[i]);
+                                if (rok[i]) *reinterpret_cast<uint32_t *>(p.out8 + gofs) = w;
+                            } else if (EPI == EPI_PRE32) {
+                                const int2 bc = *reinterpret_cast<const int2 *>(&sm.bc_tab[sl][sg][col]);
+                                const int32_t rs = *reinterpret_cast<const int32_t *>(p.resid + gofs);
+                                v0 = (int)(int8_t)(rs) + (v0 >> p.out_shift) + (int)(int16_t)(bc.x & 0xFFFF);
+                                v1 = (int)(int8_t)(rs >> 8) + (v1 >> p.out_shift) + (bc.x >> 16);
+                                v2 = (int)(int8_t)(rs >> 16) + (v2 >> p.out_shift) + (int)(int16_t)(bc.y & 0xFFFF);
+                                v3 = (int)(rs >> 24) + (v3 >> p.out_shift) + (bc.y >> 16);
+                                racc[i] = max(racc[i], max(max(abs(v0), abs(v1)), max(abs(v2), abs(v3))));
+                                if (rok[i]) *reinterpret_cast<int4 *>(p.out32 + gofs) = make_int4(v0, v1, v2, v3);
+                            } else if (EPI == EPI_QKV) {
+                                if (n0 < 2 * p.third) {
+                                    // integer RoPE on adjacent (even, odd) columns (apply_rope_integer, mgpu.cu:624-644)
+                                    const int hd0 = (n0 + col) % p.head_dim;
+                                    const int4 cs = __ldg(reinterpret_cast<const int4 *>(p.rope_lut + (int64_t)aux[i] * p.head_dim + hd0));
+                                    const long long half_ulp = 1ll << (p.rope_bit - 1);
+                                    const long long e0 = v0, o0 = v1, e1 = v2, o1 = v3;
+                                    v0 = (int)((e0 * cs.x - o0 * cs.y + half_ulp) >> p.rope_bit);
+                                    v1 = (int)((e0 * cs.y + o0 * cs.x + half_ulp) >> p.rope_bit);
+                                    v2 = (int)((e1 * cs.z - o1 * cs.w + half_ulp) >> p.rope_bit);
+                                    v3 = (int)((e1 * cs.w + o1 * cs.z + half_ulp) >> p.rope_bit);
                                 }
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 32; j++) v[j] = (uint32_t)((int)v[j] + ((xbs * (int)atab[cc + j]) >> p.rank1_shift));
-                            }
-#pragma unroll
-                            for (int j = 0; j < 32; j++) run_max = max(run_max, abs((int)v[j]));
-                            if (row_ok) {
-                                int4 *dst = reinterpret_cast<int4 *>(p.out32 + (int64_t)r * p.N + n0 + cc);
-#pragma unroll
-                                for (int q = 0; q < 8; q++) dst[q] = make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                                racc[i] = max(racc[i], max(max(abs(v0), abs(v1)), max(abs(v2), abs(v3))));
+                                if (rok[i]) *reinterpret_cast<int4 *>(p.out32 + gofs) = make_int4(v0, v1, v2, v3);
+                            } else if (EPI == EPI_HEAD) {
+                                // pass 0: row max of the logits; pass 1: Σ exp-LUT and the target logit (mgpu.cu:969-1023)
+                                const int l0 = v0 >> p.out_shift, l1 = v1 >> p.out_shift, l2 = v2 >> p.out_shift, l3 = v3 >> p.out_shift;
+                                if (pass == 0) {
+                                    racc[i] = max(racc[i], max(max(l0, l1), max(l2, l3)));
+                                } else {
+                                    const int mx = racc[i];
+                                    rsum[i] += sm.exp_lut[min(255, mx - l0)] + sm.exp_lut[min(255, mx - l1)] +
+                                               sm.exp_lut[min(255, mx - l2)] + sm.exp_lut[min(255, mx - l3)];
+                                    const int tc = aux[i] - (n0 + col);
+                                    if (tc == 0) rtgt[i] = l0; else if (tc == 1) rtgt[i] = l1; else if (tc == 2) rtgt[i] = l2; else if (tc == 3) rtgt[i] = l3;
+                                }
                             }
                         }
+                        __syncwarp();
                     }
-                    (void)run_max2;
-                    if (row_ok) {
-                        if (EPI == EPI_GELU) atomicAdd(&p.rowstat[r], dot);
-                        if (EPI == EPI_PRE32) atomicMax(&p.rowstat[r], run_max);
-                        if (EPI == EPI_QKV) atomicMax(&p.rowstat[(int64_t)r * 3 + n0 / p.third], run_max);
+                }
+                // ---- per-row results: combine the 8 lanes that share a row ----
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    if (EPI == EPI_GELU) {
+                        int d = racc[i];
+                        d += __shfl_xor_sync(0xFFFFFFFFu, d, 1); d += __shfl_xor_sync(0xFFFFFFFFu, d, 2); d += __shfl_xor_sync(0xFFFFFFFFu, d, 4);
+                        if (pc == 0 && rok[i]) atomicAdd(&p.rowstat[rrow[i]], d);
+                    } else if (EPI == EPI_PRE32 || EPI == EPI_QKV) {
+                        int m = racc[i];
+                        m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1)); m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2)); m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 4));
+                        if (pc == 0 && rok[i]) {
+                            if (EPI == EPI_PRE32) atomicMax(&p.rowstat[rrow[i]], m);
+                            else atomicMax(&p.rowstat[(int64_t)rrow[i] * 3 + n0 / p.third], m);
+                        }
+                    } else if (EPI == EPI_HEAD) {
+                        int sm_ = rsum[i], tg = rtgt[i];          // the target column lives in exactly one lane: others hold 0
+                        sm_ += __shfl_xor_sync(0xFFFFFFFFu, sm_, 1); sm_ += __shfl_xor_sync(0xFFFFFFFFu, sm_, 2); sm_ += __shfl_xor_sync(0xFFFFFFFFu, sm_, 4);
+                        tg += __shfl_xor_sync(0xFFFFFFFFu, tg, 1); tg += __shfl_xor_sync(0xFFFFFFFFu, tg, 2); tg += __shfl_xor_sync(0xFFFFFFFFu, tg, 4);
+                        if (pc == 0 && rok[i]) {
+                            int log_sum = 0;
+                            if (sm_ > 0) log_sum = ((31 - __clz(sm_)) << 4) - (p.softmax_scale_bit << 4);   // floor(log2), shift ladder of mgpu.cu:1015-1019
+                            atomicAdd(&p.loss[rrow[i] / p.seq_len], (log_sum >> 1) + racc[i] - tg);
+                        }
                     }
                 }
             } else {

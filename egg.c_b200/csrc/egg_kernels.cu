@@ -16,9 +16,11 @@ void build_noise_map(const egg_config &c, NoiseMap *map, NoiseSeg *segs, int *ns
     const int H = c.hidden_dim, V = c.vocab_size;
     const int ssv = c.sigma_shift_vector;
     int n = 0, off = 0;
-    auto plain = [&](int len, int seed) { int o = off; if (n < max_segs) segs[n] = NoiseSeg{off, len, 0, seed, 0, 0}; n++; off += len; return o; };
-    auto delta = [&](int len, int sa, int sb) { int o = off; if (n < max_segs) segs[n] = NoiseSeg{off, len, 1, sa, sb, ssv}; n++; off += 2 * len; return o; };
-    auto norm = [&](int base, int wa, int wb, int ba, int bb) { NormOff r; r.w_d = delta(H, base + wa, base + wb); r.b_d = delta(H, base + ba, base + bb); return r; };
+    auto plain = [&](int len, int seed) { int o = off; if (n < max_segs) { segs[n] = NoiseSeg{off, len, 0, seed, 0, 0}; segs[n].model_off = -1; } n++; off += len; return o; };
+    auto delta = [&](int len, int sa, int sb) { int o = off; if (n < max_segs) { segs[n] = NoiseSeg{off, len, 1, sa, sb, ssv}; segs[n].model_off = -1; } n++; off += 2 * len; return o; };
+    // kind 2: model byte + delta, both signs, as int16 [2][len] (4*len bytes); mw/mb = element offsets in TransformerModel
+    auto comb = [&](int len, int sa, int sb, int64_t moff) { int o = off; if (n < max_segs) { segs[n] = NoiseSeg{off, len, 2, sa, sb, ssv}; segs[n].model_off = moff; } n++; off += 4 * len; return o; };
+    auto norm = [&](int base, int wa, int wb, int ba, int bb, int64_t mw, int64_t mb) { NormOff r; r.w_m = comb(H, base + wa, base + wb, mw); r.b_m = comb(H, base + ba, base + bb, mb); return r; };
     auto mlp = [&](int base, int up_a, int up_b, int bu_a, int bu_b, int dn_a, int dn_b, int bd_a, int bd_b) {
         MlpOff r;
         r.up_b = plain(H, base + up_b);
@@ -33,19 +35,20 @@ void build_noise_map(const egg_config &c, NoiseMap *map, NoiseSeg *segs, int *ns
     map->emb_a = plain(V, 0);
     map->emb_b = plain(H, 0 + H);
     map->emb_bias_d = delta(H, 50, 51);
-    map->ln_init = norm(0, 500, 501, 502, 503);
-    map->ln_f = norm(0, 900, 901, 910, 911);
+    const ModelLayout ML = model_layout(c);
+    map->ln_init = norm(0, 500, 501, 502, 503, ML.ln_init, ML.ln_init_bias);
+    map->ln_f = norm(0, 900, 901, 910, 911, ML.ln_f, ML.ln_f_bias);
     map->mlp_init = mlp(0, 510, 511, 514, 515, 512, 513, 516, 517);
     map->layer0 = off;
     for (int l = 0; l < c.n_layers; l++) {
         int base = l * 1000, start = off;
         LayerOff lo;
-        lo.ln1 = norm(base, 100, 101, 110, 111);
+        lo.ln1 = norm(base, 100, 101, 110, 111, ML.ln_1 + (int64_t)l * H, ML.ln_1_bias + (int64_t)l * H);
         lo.qkv_b = plain(H, base + 201); plain(H, base + 203); plain(H, base + 205);
         lo.qkv_a = plain(H, base + 200); plain(H, base + 202); plain(H, base + 204);
         lo.o_b = plain(H, base + 207);
         lo.o_a = plain(H, base + 206);
-        lo.ln2 = norm(base, 300, 301, 310, 311);
+        lo.ln2 = norm(base, 300, 301, 310, 311, ML.ln_2 + (int64_t)l * H, ML.ln_2_bias + (int64_t)l * H);
         lo.mlp = mlp(base, 400, 401, 410, 411, 402, 403, 412, 413);
         if (l == 0) {
             map->layer_stride = off - start;
@@ -60,13 +63,14 @@ void build_noise_map(const egg_config &c, NoiseMap *map, NoiseSeg *segs, int *ns
 }
 
 __global__ void noise_fill_kernel(int8_t *nt, int64_t stride, const NoiseSeg *segs, int nsegs, uint32_t step_seed,
-                                  int pair_base, int mask, int gaussian) {
+                                  int pair_base, int mask, int gaussian, const int8_t *model) {
     extern __shared__ NoiseSeg s_segs[];
     for (int i = threadIdx.x; i < nsegs; i += blockDim.x) s_segs[i] = segs[i];
     __syncthreads();
     const int pair = blockIdx.y;
     const uint32_t S0 = step_seed + (uint32_t)(pair_base + pair);
     int8_t *dst = nt + (int64_t)pair * stride;
+    // one thread per table element (kind 2 elements are two bytes wide: o counts int8 slots, stepping over them in pairs)
     for (int o = blockIdx.x * blockDim.x + threadIdx.x; o < (int)stride; o += gridDim.x * blockDim.x) {
         int lo = 0, hi = nsegs - 1;
         while (lo < hi) { int mid = (lo + hi + 1) >> 1; if (s_segs[mid].off <= o) lo = mid; else hi = mid - 1; }
@@ -74,21 +78,36 @@ __global__ void noise_fill_kernel(int8_t *nt, int64_t stride, const NoiseSeg *se
         int rel = o - sg.off, val = 0;
         if (sg.kind == 0) {
             if (rel < sg.len) val = noise_from_hash(S0 + (uint32_t)sg.seed_a, (uint32_t)rel, mask, gaussian);
-        } else if (rel < 2 * sg.len) {
-            int neg = rel >= sg.len, i = neg ? rel - sg.len : rel;
-            int prod = noise_from_hash(S0 + (uint32_t)sg.seed_a, (uint32_t)i, mask, gaussian) *
-                       noise_from_hash(S0 + (uint32_t)sg.seed_b, (uint32_t)i, mask, gaussian);
-            val = (neg ? -prod : prod) >> sg.shift;
+            dst[o] = (int8_t)val;
+        } else if (sg.kind == 1) {
+            if (rel < 2 * sg.len) {
+                int neg = rel >= sg.len, i = neg ? rel - sg.len : rel;
+                int prod = noise_from_hash(S0 + (uint32_t)sg.seed_a, (uint32_t)i, mask, gaussian) *
+                           noise_from_hash(S0 + (uint32_t)sg.seed_b, (uint32_t)i, mask, gaussian);
+                val = (neg ? -prod : prod) >> sg.shift;
+            }
+            dst[o] = (int8_t)val;
+        } else {
+            if (rel & 1) continue;                      // the even slot writes the whole int16
+            int e = rel >> 1;                           // 0 .. 2*len-1
+            if (e < 2 * sg.len) {
+                int neg = e >= sg.len, i = neg ? e - sg.len : e;
+                int prod = noise_from_hash(S0 + (uint32_t)sg.seed_a, (uint32_t)i, mask, gaussian) *
+                           noise_from_hash(S0 + (uint32_t)sg.seed_b, (uint32_t)i, mask, gaussian);
+                val = (int)model[sg.model_off + i] + ((neg ? -prod : prod) >> sg.shift);
+                *reinterpret_cast<int16_t *>(dst + o) = (int16_t)val;
+            } else {
+                dst[o] = 0; dst[o + 1] = 0;
+            }
         }
-        dst[o] = (int8_t)val;
     }
 }
 
 int launch_noise_fill(cudaStream_t st, int8_t *nt, int64_t stride, const NoiseSeg *d_segs, int nsegs, int n_pairs,
-                      uint32_t step_seed, int pair_base, int mask, int gaussian) {
+                      uint32_t step_seed, int pair_base, int mask, int gaussian, const int8_t *model) {
     int gx = (int)((stride + 255) / 256); if (gx > 64) gx = 64;
     dim3 grid((unsigned)gx, (unsigned)n_pairs);
-    noise_fill_kernel<<<grid, 256, nsegs * sizeof(NoiseSeg), st>>>(nt, stride, d_segs, nsegs, step_seed, pair_base, mask, gaussian);
+    noise_fill_kernel<<<grid, 256, nsegs * sizeof(NoiseSeg), st>>>(nt, stride, d_segs, nsegs, step_seed, pair_base, mask, gaussian, model);
     EGG_CUDA(cudaGetLastError());
     return EGG_OK;
 }
@@ -103,16 +122,49 @@ __device__ __forceinline__ int warp_sum(int v) {
 }
 
 __device__ __forceinline__ int8_t byte_of(int32_t w, int i) { return (int8_t)(w >> (8 * i)); }
-
-// adaptive_layer_normalize / adaptive_qkv_normalize (egg_adaptive_normalize.h:10-103): same float expressions.
-__device__ __forceinline__ int aln_quant(int val, float scale) {
-    float scaled_f = (float)val * scale;
-    int scaled = (int)roundf(scaled_f);
-    if (scaled > 127) scaled = 127;
-    if (scaled < -127) scaled = -127;
-    return scaled;
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+    return (uint32_t)(a & 0xFF) | ((uint32_t)(b & 0xFF) << 8) | ((uint32_t)(c & 0xFF) << 16) | ((uint32_t)(d & 0xFF) << 24);
 }
+
+// ---- exact float arithmetic without the conversion unit ----
+// The reference's requantisation is float math ((float)v * scale, roundf, int division);
+// the same values are produced here with adds against 1.5*2^23 on the ALU/FMA pipes,
+// because int<->float conversion instructions run at a small fraction of their rate.
+constexpr float kMagic = 12582912.0f;          // 1.5 * 2^23
+constexpr int kMagicBits = 0x4B400000;
+// (float)v for |v| < 2^22, exact
+__device__ __forceinline__ float i2f_small(int v) { return __int_as_float(kMagicBits + v) - kMagic; }
+// roundf(x) (half away from zero) as a float, for |x| < 2^22: round-to-nearest-even by the
+// magic add, then the two tie cases that differ are corrected (x - rint(x) is exact).
+__device__ __forceinline__ float roundf_small(float x) {
+    float rf = (x + kMagic) - kMagic;
+    float d = x - rf;
+    if (d == 0.5f && x > 0.0f) rf += 1.0f;
+    if (d == -0.5f && x < 0.0f) rf -= 1.0f;
+    return rf;
+}
+// integer value of a float that holds an integer, |f| < 2^22
+__device__ __forceinline__ int f2i_exact(float f) { return __float_as_int(f + kMagic) - kMagicBits; }
+
+// adaptive_layer_normalize / adaptive_qkv_normalize (egg_adaptive_normalize.h:10-103):
+//   scale = 127.0f / (float)(max + 1e-9f);  out = clamp((int)roundf((float)v * scale), -127, 127)
 __device__ __forceinline__ float aln_scale(int layer_max) { return 127.0f / (float)(layer_max + 1e-9f); }
+template <bool SMALL>
+__device__ __forceinline__ int aln_quant(int val, float scale) {
+    float vf = SMALL ? i2f_small(val) : (float)val;
+    float r = roundf_small(vf * scale);              // |vf*scale| <= 127*(1+eps)
+    r = fminf(fmaxf(r, -127.0f), 127.0f);
+    return f2i_exact(r);
+}
+
+// trunc(a / mn) as C integer division does, for |a| < 2^15 and 1 <= mn <= 127:
+// a*(1/mn) is off by < 0.003, exact quotients are pushed off the integer by a bias of
+// 0.004 (the nearest non-integer quotient is 1/127 away), then truncated by rounding y -/+ 0.5.
+__device__ __forceinline__ int div_small(int a, float rinv) {
+    float af = i2f_small(a);
+    float y = fmaf(af, rinv, copysignf(0.004f, af));
+    return f2i_exact((y - copysignf(0.5f, y) + kMagic) - kMagic);
+}
 
 template <int MODE>
 __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
@@ -148,14 +200,26 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
             }
         }
     } else {
-        const float scale = aln_scale(p.rowmax[r]);
+        const int mx = p.rowmax[r];
+        const float scale = aln_scale(mx);
+        if (mx < (1 << 22)) {
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            if (j >= nj) break;
-            const int d = (j << 7) + (lane << 2);
-            int4 v = *reinterpret_cast<const int4 *>(p.pre32 + (int64_t)r * H + d);
-            x[j][0] = aln_quant(v.x, scale); x[j][1] = aln_quant(v.y, scale);
-            x[j][2] = aln_quant(v.z, scale); x[j][3] = aln_quant(v.w, scale);
+            for (int j = 0; j < 8; j++) {
+                if (j >= nj) break;
+                const int d = (j << 7) + (lane << 2);
+                int4 v = *reinterpret_cast<const int4 *>(p.pre32 + (int64_t)r * H + d);
+                x[j][0] = aln_quant<true>(v.x, scale); x[j][1] = aln_quant<true>(v.y, scale);
+                x[j][2] = aln_quant<true>(v.z, scale); x[j][3] = aln_quant<true>(v.w, scale);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                if (j >= nj) break;
+                const int d = (j << 7) + (lane << 2);
+                int4 v = *reinterpret_cast<const int4 *>(p.pre32 + (int64_t)r * H + d);
+                x[j][0] = aln_quant<false>(v.x, scale); x[j][1] = aln_quant<false>(v.y, scale);
+                x[j][2] = aln_quant<false>(v.z, scale); x[j][3] = aln_quant<false>(v.w, scale);
+            }
         }
     }
     int tot = 0;
@@ -163,49 +227,34 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
     for (int j = 0; j < 8; j++) {
         if (j >= nj) break;
         const int d = (j << 7) + (lane << 2);
-        uint32_t w = (uint32_t)(x[j][0] & 0xFF) | ((uint32_t)(x[j][1] & 0xFF) << 8) | ((uint32_t)(x[j][2] & 0xFF) << 16) |
-                     ((uint32_t)(x[j][3] & 0xFF) << 24);
+        uint32_t w = pack4(x[j][0], x[j][1], x[j][2], x[j][3]);
         *reinterpret_cast<uint32_t *>(p.x_out + (int64_t)r * H + d) = w;
-        tot += abs(x[j][0]) + abs(x[j][1]) + abs(x[j][2]) + abs(x[j][3]);
+        tot = __dp4a((int)__vabsss4(w), 0x01010101, tot);    // sum of |x|, four at a time
     }
-    // mean-abs norm with perturbed gain / bias (mgpu.cu:646-678)
+    // mean-abs norm with perturbed gain / bias (mgpu.cu:646-678): y = clip((x*w')/mn + b')
     tot = warp_sum(tot);
     int mn = tot / H;
     if (!mn) mn = 1;
+    const float rinv = 1.0f / (float)mn;
+    const int16_t *wm = reinterpret_cast<const int16_t *>(ntp + p.nt_w_m) + sgn * H;   // w + ((n1*n2*sign)>>SSV)
+    const int16_t *bm = reinterpret_cast<const int16_t *>(ntp + p.nt_b_m) + sgn * H;
     int dot0 = 0, dot1 = 0, dot2 = 0;
 #pragma unroll
     for (int j = 0; j < 8; j++) {
         if (j >= nj) break;
         const int d = (j << 7) + (lane << 2);
-        int32_t w4 = *reinterpret_cast<const int32_t *>(p.ln_w + d);
-        int32_t b4 = *reinterpret_cast<const int32_t *>(p.ln_b + d);
-        int32_t wd4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_w_d + sgn * H + d);
-        int32_t bd4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_b_d + sgn * H + d);
+        const int2 w4 = *reinterpret_cast<const int2 *>(wm + d);
+        const int2 b4 = *reinterpret_cast<const int2 *>(bm + d);
+        const int wv[4] = {(int)(int16_t)(w4.x & 0xFFFF), w4.x >> 16, (int)(int16_t)(w4.y & 0xFFFF), w4.y >> 16};
+        const int bv[4] = {(int)(int16_t)(b4.x & 0xFFFF), b4.x >> 16, (int)(int16_t)(b4.y & 0xFFFF), b4.y >> 16};
         int y[4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            int w_mod = (int)byte_of(w4, i) + (int)byte_of(wd4, i);
-            int b_mod = (int)byte_of(b4, i) + (int)byte_of(bd4, i);
-            y[i] = clip8((x[j][i] * w_mod) / mn + b_mod);
-        }
-        uint32_t w = (uint32_t)(y[0] & 0xFF) | ((uint32_t)(y[1] & 0xFF) << 8) | ((uint32_t)(y[2] & 0xFF) << 16) |
-                     ((uint32_t)(y[3] & 0xFF) << 24);
-        *reinterpret_cast<uint32_t *>(p.h_out + (int64_t)r * H + d) = w;
-        if (p.ndots > 0) {
-            int32_t n4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[0] + d);
-#pragma unroll
-            for (int i = 0; i < 4; i++) dot0 += y[i] * (int)byte_of(n4, i);
-        }
-        if (p.ndots > 1) {
-            int32_t n4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[1] + d);
-#pragma unroll
-            for (int i = 0; i < 4; i++) dot1 += y[i] * (int)byte_of(n4, i);
-        }
-        if (p.ndots > 2) {
-            int32_t n4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[2] + d);
-#pragma unroll
-            for (int i = 0; i < 4; i++) dot2 += y[i] * (int)byte_of(n4, i);
-        }
+        for (int i = 0; i < 4; i++) y[i] = clip8(div_small(x[j][i] * wv[i], rinv) + bv[i]);
+        const uint32_t yw = pack4(y[0], y[1], y[2], y[3]);
+        *reinterpret_cast<uint32_t *>(p.h_out + (int64_t)r * H + d) = yw;
+        if (p.ndots > 0) dot0 = __dp4a((int)yw, *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[0] + d), dot0);
+        if (p.ndots > 1) dot1 = __dp4a((int)yw, *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[1] + d), dot1);
+        if (p.ndots > 2) dot2 = __dp4a((int)yw, *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[2] + d), dot2);
     }
     if (p.ndots > 0) { int s = warp_sum(dot0); if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride] = s; }
     if (p.ndots > 1) { int s = warp_sum(dot1); if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride + 1] = s; }
@@ -233,14 +282,24 @@ __global__ void __launch_bounds__(256) aqn_kernel(const AqnParams p) {
     if (r >= p.M) return;
     const int H = p.H, nj = H >> 7;
     for (int which = 0; which < 3; which++) {
-        const float scale = aln_scale(p.rowmax3[(int64_t)r * 3 + which]);
+        const int mx = p.rowmax3[(int64_t)r * 3 + which];
+        const float scale = aln_scale(mx);
         int8_t *out = which == 0 ? p.q : (which == 1 ? p.k : p.v);
-        for (int j = 0; j < nj; j++) {
-            const int d = (j << 7) + (lane << 2);
-            int4 v = *reinterpret_cast<const int4 *>(p.pre3 + ((int64_t)r * 3 + which) * H + d);
-            uint32_t w = (uint32_t)(aln_quant(v.x, scale) & 0xFF) | ((uint32_t)(aln_quant(v.y, scale) & 0xFF) << 8) |
-                         ((uint32_t)(aln_quant(v.z, scale) & 0xFF) << 16) | ((uint32_t)(aln_quant(v.w, scale) & 0xFF) << 24);
-            *reinterpret_cast<uint32_t *>(out + (int64_t)r * H + d) = w;
+        const int32_t *src = p.pre3 + ((int64_t)r * 3 + which) * H;
+        if (mx < (1 << 22)) {
+            for (int j = 0; j < nj; j++) {
+                const int d = (j << 7) + (lane << 2);
+                int4 v = *reinterpret_cast<const int4 *>(src + d);
+                *reinterpret_cast<uint32_t *>(out + (int64_t)r * H + d) =
+                    pack4(aln_quant<true>(v.x, scale), aln_quant<true>(v.y, scale), aln_quant<true>(v.z, scale), aln_quant<true>(v.w, scale));
+            }
+        } else {
+            for (int j = 0; j < nj; j++) {
+                const int d = (j << 7) + (lane << 2);
+                int4 v = *reinterpret_cast<const int4 *>(src + d);
+                *reinterpret_cast<uint32_t *>(out + (int64_t)r * H + d) =
+                    pack4(aln_quant<false>(v.x, scale), aln_quant<false>(v.y, scale), aln_quant<false>(v.z, scale), aln_quant<false>(v.w, scale));
+            }
         }
     }
 }
@@ -269,12 +328,42 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
 
 constexpr int ATT_KP = 80;   // K row pitch in shared memory (bytes): conflict-free fragment loads
 
+// scores of one 16-query x 32-key block: c[nt][0..3] for the four 8-key n-tiles
+__device__ __forceinline__ void att_scores(int (&c)[4][4], const uint32_t (&qa)[2][4], const int8_t *Ks, int kb, int g, int q) {
+#pragma unroll
+    for (int nt = 0; nt < 4; nt++) {
+        c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0;
+        const int8_t *kp = Ks + (kb * 32 + nt * 8 + g) * ATT_KP + 4 * q;
+#pragma unroll
+        for (int ks = 0; ks < 2; ks++)
+            mma_s8(c[nt], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], *reinterpret_cast<const uint32_t *>(kp + 32 * ks),
+                   *reinterpret_cast<const uint32_t *>(kp + 32 * ks + 16));
+    }
+}
+
+// exact float of an int with |v| < 2^23 (no conversion instruction)
+__device__ __forceinline__ float i2f_23(int v) {
+    float f = __int_as_float(0x4B000000 | abs(v)) - 8388608.0f;
+    return v < 0 ? -f : f;
+}
+
+// trunc(num / den) as C does, for |num/den| <= 127: the quotient is estimated in float from the three
+// limb sums and fixed up with one exact int64 remainder test.
+__device__ __forceinline__ int att_div(int p0, int p1, int p2, long long den, float rden, bool small) {
+    const long long num = (long long)p0 + ((long long)p1 << 7) + ((long long)p2 << 14);
+    float fn = small ? fmaf(i2f_23(p2), 16384.0f, fmaf(i2f_23(p1), 128.0f, i2f_23(p0))) : (float)num;
+    int k = f2i_exact(fn * rden);                     // nearest integer to the real quotient (|error| < 1e-3)
+    long long r = num - (long long)k * den;
+    if (num >= 0) { if (r < 0) k--; } else { if (r > 0) k++; }
+    return k;
+}
+
 __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
     extern __shared__ __align__(16) uint8_t att_smem[];
     const int S = p.seq_len, SP = (S + 31) & ~31, VP = SP + 16, H = p.H;
     int8_t *Ks = reinterpret_cast<int8_t *>(att_smem);          // [SP][80]
-    int8_t *Vt = Ks + SP * ATT_KP;                               // [64][VP]
-    int32_t *lut = reinterpret_cast<int32_t *>(Vt + 64 * VP);    // [256]
+    int8_t *Vt = Ks + SP * ATT_KP;                               // [64][VP]  (V transposed: dim-major)
+    uint32_t *lut3 = reinterpret_cast<uint32_t *>(Vt + 64 * VP); // [256] softmax weight as three 7-bit limbs, one per byte
     const int n_heads = H / 64;
     const int mem = blockIdx.x / n_heads, hd = blockIdx.x % n_heads;
     const int64_t base = (int64_t)mem * S;
@@ -287,20 +376,40 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
         if (row < S) v = *reinterpret_cast<const int4 *>(p.k + (base + row) * H + col0 + ch * 16);
         *reinterpret_cast<int4 *>(Ks + row * ATT_KP + ch * 16) = v;
     }
-    for (int i = tid; i < SP * 4; i += 128) {
-        int row = i >> 2, ch = i & 3;
-        int4 v = make_int4(0, 0, 0, 0);
-        if (row < S) v = *reinterpret_cast<const int4 *>(p.v + (base + row) * H + col0 + ch * 16);
-        const int8_t *b = reinterpret_cast<const int8_t *>(&v);
+    // V: each item = 4 consecutive keys x 16 dims, transposed in registers (4x4 byte blocks) and written as
+    // 32-bit words Vt[dim][key..key+3]; consecutive lanes take consecutive key groups -> conflict-free stores.
+    for (int i = tid; i < (SP / 4) * 4; i += 128) {
+        const int kg = i % (SP / 4), ch = i / (SP / 4);
+        int4 r[4];
 #pragma unroll
-        for (int j = 0; j < 16; j++) Vt[(ch * 16 + j) * VP + row] = b[j];
+        for (int kk = 0; kk < 4; kk++) {
+            const int row = kg * 4 + kk;
+            r[kk] = make_int4(0, 0, 0, 0);
+            if (row < S) r[kk] = *reinterpret_cast<const int4 *>(p.v + (base + row) * H + col0 + ch * 16);
+        }
+        const uint32_t *w0 = reinterpret_cast<const uint32_t *>(&r[0]), *w1 = reinterpret_cast<const uint32_t *>(&r[1]);
+        const uint32_t *w2 = reinterpret_cast<const uint32_t *>(&r[2]), *w3 = reinterpret_cast<const uint32_t *>(&r[3]);
+#pragma unroll
+        for (int dq = 0; dq < 4; dq++) {       // dims 4dq..4dq+3 of this chunk
+            uint32_t t0 = __byte_perm(w0[dq], w1[dq], 0x5140), t1 = __byte_perm(w2[dq], w3[dq], 0x5140);   // [a0 b0 a1 b1]
+            uint32_t t2 = __byte_perm(w0[dq], w1[dq], 0x7362), t3 = __byte_perm(w2[dq], w3[dq], 0x7362);   // [a2 b2 a3 b3]
+            const int dim = ch * 16 + dq * 4;
+            *reinterpret_cast<uint32_t *>(Vt + (dim + 0) * VP + kg * 4) = __byte_perm(t0, t1, 0x5410);
+            *reinterpret_cast<uint32_t *>(Vt + (dim + 1) * VP + kg * 4) = __byte_perm(t0, t1, 0x7632);
+            *reinterpret_cast<uint32_t *>(Vt + (dim + 2) * VP + kg * 4) = __byte_perm(t2, t3, 0x5410);
+            *reinterpret_cast<uint32_t *>(Vt + (dim + 3) * VP + kg * 4) = __byte_perm(t2, t3, 0x7632);
+        }
     }
-    for (int i = tid; i < 256; i += 128) lut[i] = p.exp_lut[i];
+    for (int i = tid; i < 256; i += 128) {
+        uint32_t w = (uint32_t)p.exp_lut[i];
+        lut3[i] = (w & 127u) | (((w >> 7) & 127u) << 8) | ((w >> 14) << 16);
+    }
     __syncthreads();
 
     const int g = lane >> 2, q = lane & 3;
     const int8_t *nbo = p.nt + (int64_t)(mem >> 1) * p.nt_stride + p.nt_o_b + col0;
     const int sh = p.shift_attn;
+    const bool small_limbs = S <= 512;     // every limb sum < 127*127*512 < 2^23
 
     for (int qb = warp; qb < S / 16; qb += 4) {
         const int q0 = qb * 16;
@@ -315,25 +424,24 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
             qa[ks][2] = *reinterpret_cast<const uint32_t *>(qp0 + 16);
             qa[ks][3] = *reinterpret_cast<const uint32_t *>(qp1 + 16);
         }
-        const int nkb = (q0 + 15) / 32 + 1;
+        const int last = (q0 + 15) / 32;          // the only key block that needs the causal mask
 
         // ---- pass 1: row maxima over ctx <= t (mgpu.cu:795-802) ----
         int mx0 = INT_MIN, mx1 = INT_MIN;
-        for (int kb = 0; kb < nkb; kb++) {
+        int c[4][4];
+        for (int kb = 0; kb < last; kb++) {
+            att_scores(c, qa, Ks, kb, g, q);
 #pragma unroll
-            for (int nt = 0; nt < 4; nt++) {
-                int c[4] = {0, 0, 0, 0};
-                const int8_t *kp = Ks + (kb * 32 + nt * 8 + g) * ATT_KP + 4 * q;
+            for (int nt = 0; nt < 4; nt++) { mx0 = max(mx0, max(c[nt][0], c[nt][1])); mx1 = max(mx1, max(c[nt][2], c[nt][3])); }
+        }
+        att_scores(c, qa, Ks, last, g, q);
 #pragma unroll
-                for (int ks = 0; ks < 2; ks++)
-                    mma_s8(c, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], *reinterpret_cast<const uint32_t *>(kp + 32 * ks),
-                           *reinterpret_cast<const uint32_t *>(kp + 32 * ks + 16));
-                const int key = kb * 32 + nt * 8 + 2 * q;
-                if (key <= row0) mx0 = max(mx0, c[0]);
-                if (key + 1 <= row0) mx0 = max(mx0, c[1]);
-                if (key <= row1) mx1 = max(mx1, c[2]);
-                if (key + 1 <= row1) mx1 = max(mx1, c[3]);
-            }
+        for (int nt = 0; nt < 4; nt++) {
+            const int key = last * 32 + nt * 8 + 2 * q;
+            if (key <= row0) mx0 = max(mx0, c[nt][0]);
+            if (key + 1 <= row0) mx0 = max(mx0, c[nt][1]);
+            if (key <= row1) mx1 = max(mx1, c[nt][2]);
+            if (key + 1 <= row1) mx1 = max(mx1, c[nt][3]);
         }
         mx0 = max(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 1)); mx0 = max(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 2));
         mx1 = max(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 1)); mx1 = max(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 2));
@@ -347,36 +455,39 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
             for (int l = 0; l < 3; l++)
 #pragma unroll
                 for (int i = 0; i < 4; i++) acc[a][l][i] = 0;
-        uint32_t tot0 = 0, tot1 = 0;
-        for (int kb = 0; kb < nkb; kb++) {
-            int w[4][4];
+        int tl0[3] = {0, 0, 0}, tl1[3] = {0, 0, 0};      // per-limb Σ w for rows g and g+8
+        for (int kb = 0; kb <= last; kb++) {
+            att_scores(c, qa, Ks, kb, g, q);
+            uint32_t w[4][4];                             // limb-packed weights
+            if (kb < last) {
 #pragma unroll
-            for (int nt = 0; nt < 4; nt++) {
-                int c[4] = {0, 0, 0, 0};
-                const int8_t *kp = Ks + (kb * 32 + nt * 8 + g) * ATT_KP + 4 * q;
+                for (int nt = 0; nt < 4; nt++) {
+                    w[nt][0] = lut3[min(255, mxs0 - (c[nt][0] >> sh))];
+                    w[nt][1] = lut3[min(255, mxs0 - (c[nt][1] >> sh))];
+                    w[nt][2] = lut3[min(255, mxs1 - (c[nt][2] >> sh))];
+                    w[nt][3] = lut3[min(255, mxs1 - (c[nt][3] >> sh))];
+                }
+            } else {
 #pragma unroll
-                for (int ks = 0; ks < 2; ks++)
-                    mma_s8(c, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], *reinterpret_cast<const uint32_t *>(kp + 32 * ks),
-                           *reinterpret_cast<const uint32_t *>(kp + 32 * ks + 16));
-                const int key = kb * 32 + nt * 8 + 2 * q;
-                w[nt][0] = (key <= row0) ? lut[min(255, mxs0 - (c[0] >> sh))] : 0;
-                w[nt][1] = (key + 1 <= row0) ? lut[min(255, mxs0 - (c[1] >> sh))] : 0;
-                w[nt][2] = (key <= row1) ? lut[min(255, mxs1 - (c[2] >> sh))] : 0;
-                w[nt][3] = (key + 1 <= row1) ? lut[min(255, mxs1 - (c[3] >> sh))] : 0;
-                tot0 += (uint32_t)(w[nt][0] + w[nt][1]);
-                tot1 += (uint32_t)(w[nt][2] + w[nt][3]);
+                for (int nt = 0; nt < 4; nt++) {
+                    const int key = kb * 32 + nt * 8 + 2 * q;
+                    w[nt][0] = (key <= row0) ? lut3[min(255, mxs0 - (c[nt][0] >> sh))] : 0u;
+                    w[nt][1] = (key + 1 <= row0) ? lut3[min(255, mxs0 - (c[nt][1] >> sh))] : 0u;
+                    w[nt][2] = (key <= row1) ? lut3[min(255, mxs1 - (c[nt][2] >> sh))] : 0u;
+                    w[nt][3] = (key + 1 <= row1) ? lut3[min(255, mxs1 - (c[nt][3] >> sh))] : 0u;
+                }
             }
             // A fragments of the three limbs; k-slot 4q+{0,1,2,3} <-> keys {2q, 2q+1, 8+2q, 9+2q} (+16 for a2/a3)
             uint32_t al[3][4];
 #pragma unroll
             for (int l = 0; l < 3; l++) {
-                const int s = 7 * l;
-#define LIMB(x) ((uint32_t)(((x) >> s) & 127))
-                al[l][0] = LIMB(w[0][0]) | (LIMB(w[0][1]) << 8) | (LIMB(w[1][0]) << 16) | (LIMB(w[1][1]) << 24);
-                al[l][1] = LIMB(w[0][2]) | (LIMB(w[0][3]) << 8) | (LIMB(w[1][2]) << 16) | (LIMB(w[1][3]) << 24);
-                al[l][2] = LIMB(w[2][0]) | (LIMB(w[2][1]) << 8) | (LIMB(w[3][0]) << 16) | (LIMB(w[3][1]) << 24);
-                al[l][3] = LIMB(w[2][2]) | (LIMB(w[2][3]) << 8) | (LIMB(w[3][2]) << 16) | (LIMB(w[3][3]) << 24);
-#undef LIMB
+                const uint32_t sel = (uint32_t)l | ((uint32_t)(4 + l) << 4);       // byte l of x, byte l of y
+                al[l][0] = __byte_perm(__byte_perm(w[0][0], w[0][1], sel), __byte_perm(w[1][0], w[1][1], sel), 0x5410);
+                al[l][1] = __byte_perm(__byte_perm(w[0][2], w[0][3], sel), __byte_perm(w[1][2], w[1][3], sel), 0x5410);
+                al[l][2] = __byte_perm(__byte_perm(w[2][0], w[2][1], sel), __byte_perm(w[3][0], w[3][1], sel), 0x5410);
+                al[l][3] = __byte_perm(__byte_perm(w[2][2], w[2][3], sel), __byte_perm(w[3][2], w[3][3], sel), 0x5410);
+                tl0[l] = __dp4a((int)al[l][0], 0x01010101, __dp4a((int)al[l][2], 0x01010101, tl0[l]));
+                tl1[l] = __dp4a((int)al[l][1], 0x01010101, __dp4a((int)al[l][3], 0x01010101, tl1[l]));
             }
 #pragma unroll
             for (int dn = 0; dn < 8; dn++) {
@@ -387,18 +498,19 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
                 for (int l = 0; l < 3; l++) mma_s8(acc[dn][l], al[l][0], al[l][1], al[l][2], al[l][3], b0, b1);
             }
         }
+        uint32_t tot0 = (uint32_t)tl0[0] + ((uint32_t)tl0[1] << 7) + ((uint32_t)tl0[2] << 14);
+        uint32_t tot1 = (uint32_t)tl1[0] + ((uint32_t)tl1[1] << 7) + ((uint32_t)tl1[2] << 14);
         tot0 += __shfl_xor_sync(0xFFFFFFFFu, tot0, 1); tot0 += __shfl_xor_sync(0xFFFFFFFFu, tot0, 2);
         tot1 += __shfl_xor_sync(0xFFFFFFFFu, tot1, 1); tot1 += __shfl_xor_sync(0xFFFFFFFFu, tot1, 2);
         const long long den0 = tot0 ? (long long)tot0 : 1, den1 = tot1 ? (long long)tot1 : 1;
+        const float rden0 = 1.0f / (float)den0, rden1 = 1.0f / (float)den1;
         int dot0 = 0, dot1 = 0;
 #pragma unroll
         for (int dn = 0; dn < 8; dn++) {
             int o[4];
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                long long num = (long long)acc[dn][0][i] + ((long long)acc[dn][1][i] << 7) + ((long long)acc[dn][2][i] << 14);
-                o[i] = clip8((int)(num / (i < 2 ? den0 : den1)));
-            }
+            for (int i = 0; i < 4; i++)
+                o[i] = clip8(att_div(acc[dn][0][i], acc[dn][1][i], acc[dn][2][i], i < 2 ? den0 : den1, i < 2 ? rden0 : rden1, small_limbs));
             const int dim = dn * 8 + 2 * q;
             *reinterpret_cast<uint16_t *>(p.ao + (base + row0) * H + col0 + dim) = (uint16_t)((o[0] & 0xFF) | ((o[1] & 0xFF) << 8));
             *reinterpret_cast<uint16_t *>(p.ao + (base + row1) * H + col0 + dim) = (uint16_t)((o[2] & 0xFF) | ((o[3] & 0xFF) << 8));

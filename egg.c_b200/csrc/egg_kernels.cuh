@@ -13,12 +13,14 @@ namespace egg {
 struct NoiseSeg {
     int off;        // byte offset inside the pair's table
     int len;        // elements (a delta segment occupies 2*len bytes: [+sign][len], [-sign][len])
-    int kind;       // 0: noise(S0+seed_a, i)   1: ((n(S0+seed_a,i)*n(S0+seed_b,i)*sign) >> shift) per sign
+    int kind;       // 0: noise(S0+seed_a, i)   1: ((n(S0+seed_a,i)*n(S0+seed_b,i)*sign) >> shift) per sign, int8 [2][len]
+                    // 2: model[model_off+i] + that delta, int16 [2][len] (occupies 4*len bytes)
     int seed_a, seed_b;
     int shift;
+    int64_t model_off;
 };
 
-struct NormOff { int w_d, b_d; };                       // delta [2][H] each
+struct NormOff { int w_m, b_m; };                       // perturbed gain / bias, int16 [2][H] each
 struct MlpOff { int up_b, up_a, bup_d, dn_b, dn_a, bdn_d; };
 struct LayerOff { NormOff ln1; int qkv_b; int qkv_a; int o_b, o_a; NormOff ln2; MlpOff mlp; };
 
@@ -35,7 +37,7 @@ struct NoiseMap {
 void build_noise_map(const egg_config &c, NoiseMap *map, NoiseSeg *segs, int *nsegs, int max_segs);
 
 int launch_noise_fill(cudaStream_t st, int8_t *nt, int64_t stride, const NoiseSeg *d_segs, int nsegs, int n_pairs,
-                      uint32_t step_seed, int pair_base, int mask, int gaussian);
+                      uint32_t step_seed, int pair_base, int mask, int gaussian, const int8_t *model);
 
 // ---- row-wise kernels -------------------------------------------------------
 struct RowParams {
@@ -49,7 +51,7 @@ struct RowParams {
     // residual stream out
     int8_t *x_out;
     // mean-abs norm (apply_standard_norm, mgpu.cu:646-678)
-    const int8_t *ln_w, *ln_b; int nt_w_d, nt_b_d;
+    int nt_w_m, nt_b_m;          // perturbed gain / bias tables (int16 [2][H])
     int8_t *h_out;
     // Σ_d h_d * noise_B[d] for up to three following projections
     int ndots; int nt_dot[3]; int32_t *xb_out; int xb_stride;
