@@ -319,7 +319,7 @@ def main():
             "clocks": clocks,
             "cpu_baseline": cpu,
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     ctx.close()
     if dist:
         dist.destroy_process_group()

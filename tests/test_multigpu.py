@@ -1,0 +1,64 @@
+"""2-GPU run through the C ABI: pair-aligned population slices, one NCCL all-gather of fitness per
+generation, replicated update.  Every rank must hold byte-identical weights and optimiser state, equal
+to the single-GPU generation.  Skipped where fewer than two GPUs are visible."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from common import ROOT, load_pkg, make_case
+
+pytestmark = pytest.mark.gpu
+KW = dict(hidden_dim=256, n_layers=2, seq_len=32, population_size=64, device_mask=3)
+SEED, LR, STEPS = 4242, 0.5, 3
+
+
+def _rank_main(rank, world, ident, q):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    pkg = load_pkg()
+    cfg, ocfg, model, data = make_case(KW, data_len=40000)
+    ctx = pkg.Context(cfg, rank, 0)
+    ctx.upload_model(model)
+    ctx.set_dataset(data)
+    ctx.comm_init(ident, rank, world)
+    per = KW["population_size"] // world
+    losses = np.zeros(per, np.int32)
+    ups = []
+    for step in range(STEPS):
+        ups.append(ctx.generation_host(None, step, SEED + step, LR, losses))
+    q.put((rank, ctx.download_model().tobytes(), ctx.download_opt_state().tobytes(), losses.tobytes(), ups))
+    ctx.close()
+
+
+def test_two_gpu_generation_matches_single_gpu():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    pkg = load_pkg()
+    cfg, ocfg, model, data = make_case(KW, data_len=40000)
+    ctx = pkg.Context(cfg, 0, 0)
+    ctx.upload_model(model)
+    ctx.set_dataset(data)
+    pop = KW["population_size"]
+    losses = np.zeros(pop, np.int32)
+    ups = [ctx.generation_host(None, step, SEED + step, LR, losses) for step in range(STEPS)]
+    want_m, want_o = ctx.download_model().tobytes(), ctx.download_opt_state().tobytes()
+    ctx.close()
+    ident = pkg.nccl_unique_id()
+    mpc = mp.get_context("spawn")
+    q = mpc.Queue()
+    procs = [mpc.Process(target=_rank_main, args=(r, 2, ident, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, mb, ob, lb, u in got:
+        assert mb == want_m and ob == want_o, "rank %d diverged from the single-GPU generation" % rank
+        assert u == ups
+        per = pop // 2
+        assert lb == losses[rank * per:(rank + 1) * per].tobytes()

@@ -1,0 +1,79 @@
+"""world_size-2 run of the sharded generation on CPU ranks (gloo): each rank evaluates its pair-aligned
+slice with the oracle, all-gathers fitness, applies the replicated update; every rank must end with the
+same bytes as the single-process generation."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from common import ROOT, load_oracle, load_pkg, make_case
+
+KW = dict(hidden_dim=128, n_layers=1, seq_len=16, population_size=16, device_mask=15)
+SEED, LR = 77, 0.5
+
+
+def _rank_main(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    O = load_oracle()
+    load_pkg()
+    from egg_c_b200 import sharding
+    cfg, ocfg, model, data = make_case(KW, data_len=20000)
+    opt = np.zeros(O.opt_bytes(ocfg), np.uint8)
+    pop = KW["population_size"]
+    for step in range(3):
+        off, per = sharding.member_slice(rank, world, pop)
+        losses = O.eval_losses(ocfg, model, data, step * KW["seq_len"], SEED + step, off, per)
+        mine = torch.from_numpy(O.fitness(losses))
+        parts = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        fit = torch.cat(parts).numpy()
+        O.update(ocfg, model, opt, fit, SEED + step, LR)
+    q.put((rank, model.tobytes(), opt.tobytes()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_generation_equals_single_process():
+    O = load_oracle()
+    cfg, ocfg, model, data = make_case(KW, data_len=20000)
+    opt = np.zeros(O.opt_bytes(ocfg), np.uint8)
+    pop = KW["population_size"]
+    for step in range(3):
+        losses = O.eval_losses(ocfg, model, data, step * KW["seq_len"], SEED + step, 0, pop)
+        O.update(ocfg, model, opt, O.fitness(losses), SEED + step, LR)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, mb, ob in got:
+        assert mb == model.tobytes(), "rank %d model differs" % rank
+        assert ob == opt.tobytes(), "rank %d optimiser state differs" % rank
+
+
+def test_slices_are_pair_aligned_and_cover_population():
+    load_pkg()
+    from egg_c_b200 import sharding
+    for world in (1, 2, 4, 8):
+        pop = 40960 * world
+        seen = []
+        for r in range(world):
+            off, per = sharding.member_slice(r, world, pop)
+            assert off % 2 == 0 and per % 2 == 0
+            assert sharding.pair_slice(r, world, pop) == (off // 2, per // 2)
+            seen.append((off, per))
+        assert seen[0][0] == 0 and sum(p for _, p in seen) == pop
+        assert all(seen[i][0] + seen[i][1] == seen[i + 1][0] for i in range(world - 1))
+    with pytest.raises(ValueError):
+        sharding.member_slice(0, 4, 36)
