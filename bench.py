@@ -165,6 +165,10 @@ def main():
     if args.small:
         args.pop, args.no_cpu_baseline = 1024, True
 
+    # libraries (NCCL's version banner, for one) may write to stdout: keep fd 1 for the single JSON line
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
     import torch   # device discovery and the process group only; the hot path is the C ABI
     pkg = load_pkg()
     from egg_c_b200 import synth
@@ -319,7 +323,8 @@ def main():
             "clocks": clocks,
             "cpu_baseline": cpu,
         }
-        print(json.dumps(line), flush=True)
+        real_stdout.write(json.dumps(line) + "\n")
+        real_stdout.flush()
     ctx.close()
     if dist:
         dist.destroy_process_group()
