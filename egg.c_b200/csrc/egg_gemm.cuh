@@ -18,8 +18,9 @@ namespace egg {
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 128;            // bytes (= int8 elements) per k-block: one swizzle row
 constexpr int GEMM_STAGES = 3;
-constexpr int GEMM_THREADS = 320;       // warp0 TMA, warp1 MMA, warps 2..9 epilogue
-constexpr int GEMM_EPI_THREADS = 256;
+constexpr int GEMM_THREADS = 576;       // warp0 TMA, warp1 MMA, warps 2..17 epilogue
+constexpr int GEMM_EPI_THREADS = 512;
+constexpr int GEMM_EPI_WARPS = 16;
 constexpr int GEMM_MAX_SLOTS = 9;       // distinct population pairs a 128-row tile can touch (seq_len >= 8)
 
 enum GemmEpi {
@@ -80,7 +81,7 @@ template <int BN>
 struct GemmSmem {
     alignas(1024) uint8_t a[GEMM_STAGES][GEMM_BM * GEMM_BK];
     alignas(1024) uint8_t b[GEMM_STAGES][BN * GEMM_BK];
-    alignas(16) int32_t stage[8][32][36];               // per epilogue warp: 32 rows x 32 columns (+4 pad) transpose buffer
+    alignas(16) int32_t stage[GEMM_EPI_WARPS][32][20];  // per epilogue warp: 32 rows x 16 columns (+4 pad) transpose buffer
     alignas(16) int8_t a_tab[GEMM_MAX_SLOTS][BN];       // A-noise of this projection per pair slot
     alignas(16) int16_t bc_tab[GEMM_MAX_SLOTS][2][BN];  // bias + bias-noise delta per pair slot and sign
     alignas(16) int8_t d_tab[GEMM_MAX_SLOTS][BN];       // B-noise of the next projection (EPI_GELU)
@@ -142,7 +143,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < GEMM_STAGES; s++) { ptx::mbar_init(&sm.full[s], 1); ptx::mbar_init(&sm.empty[s], 1); }
-        for (int a = 0; a < 2; a++) { ptx::mbar_init(&sm.tmem_full[a], 1); ptx::mbar_init(&sm.tmem_empty[a], 8); }
+        for (int a = 0; a < 2; a++) { ptx::mbar_init(&sm.tmem_full[a], 1); ptx::mbar_init(&sm.tmem_empty[a], GEMM_EPI_WARPS); }
         sm.abort_flag = 0;
         sm.epi_ok = 1;
         ptx::fence_barrier_init();
@@ -153,8 +154,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     if (warp >= 2) {
         int e = threadIdx.x - 64;
-        if (EPI == EPI_GELU && p.act_lut) sm.act_lut[e] = p.act_lut[e];
-        if (EPI == EPI_HEAD && p.exp_lut) sm.exp_lut[e] = p.exp_lut[e];
+        if (EPI == EPI_GELU && p.act_lut && e < 256) sm.act_lut[e] = p.act_lut[e];
+        if (EPI == EPI_HEAD && p.exp_lut && e < 256) sm.exp_lut[e] = p.exp_lut[e];
     }
     ptx::tc_fence_before();
     __syncthreads();
@@ -214,14 +215,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
         }
     } else {
-        // ===================== epilogue (8 warps) =====================
-        const int e = threadIdx.x - 64;            // 0..255
-        const int ew = warp - 2;                   // 0..7
+        // ===================== epilogue (16 warps) =====================
+        const int e = threadIdx.x - 64;            // 0..511
+        const int ew = warp - 2;                   // 0..15
         const int quarter = warp & 3;              // TMEM lane quarter this warp may read
-        constexpr int NHALF = (EPI == EPI_HEAD) ? 1 : 2;   // the head needs whole rows in one thread
+        constexpr int NHALF = (EPI == EPI_HEAD) ? 1 : 4;   // column parts per lane quarter; the head keeps whole rows in one warp
         constexpr int COLS_PER = BN / NHALF;
-        const int half = (NHALF == 2) ? (ew >> 2) : 0;     // which half of the tile's columns
-        const bool active = (NHALF == 2) || ew < 4;
+        const int half = (NHALF == 4) ? (ew >> 2) : 0;     // which part of the tile's columns
+        const bool active = (NHALF == 4) || ew < 4;
         const int row_in_tile = quarter * 32 + lane;
         uint32_t tcount = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tcount++) {
@@ -280,15 +281,15 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             } else if (EPI <= EPI_HEAD) {
                 // ---------------- evaluation epilogues ----------------
                 // Accumulators leave TMEM one row per lane; they are transposed through shared memory so
-                // that 8 consecutive lanes own 32 consecutive columns of one row: every global access below
+                // that 4 consecutive lanes own 16 consecutive columns of one row: every global access below
                 // is then a run of full 32-byte sectors, and the per-column tables are read as words.
-                int32_t(*st)[36] = sm.stage[ew];
-                const int lrow = lane >> 3, pc = lane & 7;          // row group / 4-column piece of this lane
-                int rrow[8], xbs[8], slot_sgn[8], aux[8];           // per-row state of the 8 rows this lane touches
-                bool rok[8];
+                int32_t(*st)[20] = sm.stage[ew];
+                const int lrow = lane >> 2, pc = lane & 3;          // row group / 4-column piece of this lane
+                int rrow[4], xbs[4], slot_sgn[4], aux[4];           // per-row state of the 4 rows this lane touches
+                bool rok[4];
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const int rr = m0 + quarter * 32 + i * 4 + lrow;
+                for (int i = 0; i < 4; i++) {
+                    const int rr = m0 + quarter * 32 + i * 8 + lrow;
                     rok[i] = rr < p.M;
                     const int rc = rok[i] ? rr : (p.M - 1);
                     rrow[i] = rc;
@@ -308,41 +309,40 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         aux[i] = p.dataset[pos + t + 1];
                     }
                 }
-                int racc[8];                                        // running abs-max / dot / row max per row
+                int racc[4];                                        // running abs-max / dot / row max per row
 #pragma unroll
-                for (int i = 0; i < 8; i++) racc[i] = (EPI == EPI_HEAD) ? INT_MIN : 0;
-                int rsum[8], rtgt[8];
+                for (int i = 0; i < 4; i++) racc[i] = (EPI == EPI_HEAD) ? INT_MIN : 0;
+                int rsum[4], rtgt[4];
 #pragma unroll
-                for (int i = 0; i < 8; i++) { rsum[i] = 0; rtgt[i] = 0; }
+                for (int i = 0; i < 4; i++) { rsum[i] = 0; rtgt[i] = 0; }
 
                 constexpr int NPASS = (EPI == EPI_HEAD) ? 2 : 1;
 #pragma unroll 1
                 for (int pass = 0; pass < NPASS; pass++) {
                     if (EPI == EPI_HEAD && pass == 1) {
 #pragma unroll
-                        for (int i = 0; i < 8; i++) {               // finish the row maxima of pass 0
+                        for (int i = 0; i < 4; i++) {               // finish the row maxima of pass 0
                             int m = racc[i];
                             m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
                             m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
-                            m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 4));
                             racc[i] = m;
                         }
                     }
 #pragma unroll 1
-                    for (int c = 0; c < COLS_PER; c += 32) {
+                    for (int c = 0; c < COLS_PER; c += 16) {
                         {
-                            uint32_t v[32];
-                            ptx::tmem_ld32(taddr + c, v);
+                            uint32_t v[16];
+                            ptx::tmem_ld16(taddr + c, v);
                             ptx::tmem_ld_wait();
 #pragma unroll
-                            for (int qd = 0; qd < 8; qd++)
+                            for (int qd = 0; qd < 4; qd++)
                                 *reinterpret_cast<int4 *>(&st[lane][4 * qd]) = make_int4(v[4 * qd], v[4 * qd + 1], v[4 * qd + 2], v[4 * qd + 3]);
                         }
                         __syncwarp();
                         const int col = cbase + c + 4 * pc;          // column inside the tile of this lane's 4 values
 #pragma unroll
-                        for (int i = 0; i < 8; i++) {
-                            const int4 a4 = *reinterpret_cast<const int4 *>(&st[i * 4 + lrow][4 * pc]);
+                        for (int i = 0; i < 4; i++) {
+                            const int4 a4 = *reinterpret_cast<const int4 *>(&st[i * 8 + lrow][4 * pc]);
                             const int sl = slot_sgn[i] >> 1, sg = slot_sgn[i] & 1;
                             const int32_t aw = *reinterpret_cast<const int32_t *>(&sm.a_tab[sl][col]);
                             int v0 = a4.x + ((xbs[i] * (int)(int8_t)(aw)) >> p.rank1_shift);
@@ -405,22 +405,22 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
                 // ---- per-row results: combine the 8 lanes that share a row ----
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
+                for (int i = 0; i < 4; i++) {
                     if (EPI == EPI_GELU) {
                         int d = racc[i];
-                        d += __shfl_xor_sync(0xFFFFFFFFu, d, 1); d += __shfl_xor_sync(0xFFFFFFFFu, d, 2); d += __shfl_xor_sync(0xFFFFFFFFu, d, 4);
+                        d += __shfl_xor_sync(0xFFFFFFFFu, d, 1); d += __shfl_xor_sync(0xFFFFFFFFu, d, 2);
                         if (pc == 0 && rok[i]) atomicAdd(&p.rowstat[rrow[i]], d);
                     } else if (EPI == EPI_PRE32 || EPI == EPI_QKV) {
                         int m = racc[i];
-                        m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1)); m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2)); m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 4));
+                        m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1)); m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
                         if (pc == 0 && rok[i]) {
                             if (EPI == EPI_PRE32) atomicMax(&p.rowstat[rrow[i]], m);
                             else atomicMax(&p.rowstat[(int64_t)rrow[i] * 3 + n0 / p.third], m);
                         }
                     } else if (EPI == EPI_HEAD) {
                         int sm_ = rsum[i], tg = rtgt[i];          // the target column lives in exactly one lane: others hold 0
-                        sm_ += __shfl_xor_sync(0xFFFFFFFFu, sm_, 1); sm_ += __shfl_xor_sync(0xFFFFFFFFu, sm_, 2); sm_ += __shfl_xor_sync(0xFFFFFFFFu, sm_, 4);
-                        tg += __shfl_xor_sync(0xFFFFFFFFu, tg, 1); tg += __shfl_xor_sync(0xFFFFFFFFu, tg, 2); tg += __shfl_xor_sync(0xFFFFFFFFu, tg, 4);
+                        sm_ += __shfl_xor_sync(0xFFFFFFFFu, sm_, 1); sm_ += __shfl_xor_sync(0xFFFFFFFFu, sm_, 2);
+                        tg += __shfl_xor_sync(0xFFFFFFFFu, tg, 1); tg += __shfl_xor_sync(0xFFFFFFFFu, tg, 2);
                         if (pc == 0 && rok[i]) {
                             int log_sum = 0;
                             if (sm_ > 0) log_sum = ((31 - __clz(sm_)) << 4) - (p.softmax_scale_bit << 4);   // floor(log2), shift ladder of mgpu.cu:1015-1019
