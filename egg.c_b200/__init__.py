@@ -22,7 +22,8 @@ EXPORTS = [
     "egg_write_fitness", "egg_read_fitness", "egg_nccl_unique_id", "egg_comm_init", "egg_allgather_fitness",
     "egg_apply_update", "egg_generation_host", "egg_perturbed_projection", "egg_update_reconstruct",
     "egg_timer_start", "egg_timer_stop", "egg_profile_enable", "egg_profile_read", "egg_profile_name", "egg_launch_count",
-    "egg_wave_members",
+    "egg_wave_members", "egg_wire_fixed_bytes", "egg_wire_encode", "egg_wire_decode_header", "egg_wire_decode_body",
+    "egg_ternary_packed_size", "egg_ternary_pack", "egg_ternary_unpack", "egg_deggs_chunk_fitness", "egg_next_seed",
 ]
 EGG_PROF_N = 14
 
@@ -38,6 +39,12 @@ class EggConfig(C.Structure):
         ("softmax_exp_scale", C.c_double), ("adam_beta1", C.c_float), ("adam_beta2", C.c_float),
         ("adam_eps", C.c_float), ("adam_weight_decay", C.c_float), ("muon_momentum", C.c_float),
         ("muon_lr_scale", C.c_float)]
+
+
+class WireMsg(C.Structure):
+    """struct egg_wire_msg."""
+    _fields_ = [("opcode", C.c_int32), ("payload_size", C.c_uint32), ("seed", C.c_uint64), ("last_step", C.c_uint64),
+                ("data_position", C.c_uint64), ("updates_count", C.c_uint64), ("sum_loss", C.c_int64)]
 
 
 class EggError(RuntimeError):
@@ -103,6 +110,19 @@ def lib():
         L.egg_launch_count.argtypes = [vp]
         L.egg_launch_count.restype = C.c_int64
         L.egg_wave_members.argtypes = [vp]
+        L.egg_wire_fixed_bytes.argtypes = [C.c_int]
+        L.egg_wire_encode.argtypes = [P(WireMsg), vp, C.c_int]
+        L.egg_wire_decode_header.argtypes = [vp, P(C.c_int), P(C.c_uint32)]
+        L.egg_wire_decode_body.argtypes = [C.c_int, vp, C.c_int, P(WireMsg)]
+        L.egg_ternary_packed_size.argtypes = [C.c_int64]
+        L.egg_ternary_packed_size.restype = C.c_int64
+        L.egg_ternary_pack.argtypes = [vp, C.c_int64, vp]
+        L.egg_ternary_pack.restype = None
+        L.egg_ternary_unpack.argtypes = [vp, C.c_int64, vp]
+        L.egg_ternary_unpack.restype = None
+        L.egg_deggs_chunk_fitness.argtypes = [vp, C.c_int, C.c_int, C.c_double, C.c_int, C.c_double, vp, P(C.c_int64)]
+        L.egg_next_seed.argtypes = [C.c_uint32, C.c_uint64]
+        L.egg_next_seed.restype = C.c_uint32
         _lib = L
     return _lib
 
@@ -260,3 +280,53 @@ def nccl_unique_id():
     buf = (C.c_char * 128)()
     _check(lib().egg_nccl_unique_id(buf))
     return bytes(buf)
+
+
+# ---- d-eggs worker boundary (host side) ----
+def wire_encode(msg):
+    buf = (C.c_uint8 * 64)()
+    n = lib().egg_wire_encode(C.byref(msg), buf, 64)
+    if n < 0:
+        raise EggError(n, "cannot encode wire message")
+    return bytes(buf[:n])
+
+
+def wire_decode(data):
+    """(WireMsg, total_len) of an encoded header + fixed body."""
+    raw = (C.c_uint8 * len(data)).from_buffer_copy(data)
+    op, total = C.c_int(0), C.c_uint32(0)
+    rc = lib().egg_wire_decode_header(raw, C.byref(op), C.byref(total))
+    if rc:
+        raise EggError(rc, "bad wire header")
+    msg = WireMsg()
+    body = (C.c_uint8 * (len(data) - 10)).from_buffer_copy(data[10:])
+    rc = lib().egg_wire_decode_body(op.value, body, len(data) - 10, C.byref(msg))
+    if rc:
+        raise EggError(rc, "bad wire body")
+    return msg, total.value
+
+
+def ternary_pack(values):
+    values = np.ascontiguousarray(values, np.int32)
+    out = np.zeros(lib().egg_ternary_packed_size(len(values)), np.uint8)
+    lib().egg_ternary_pack(_ptr(values), len(values), _ptr(out))
+    return out
+
+
+def ternary_unpack(packed, count):
+    packed = np.ascontiguousarray(packed, np.uint8)
+    out = np.zeros(count, np.int32)
+    lib().egg_ternary_unpack(_ptr(packed), count, _ptr(out))
+    return out
+
+
+def deggs_chunk_fitness(losses, mean_filter=1, exponent=1.2, adaptive=1, alpha=0.1):
+    losses = np.ascontiguousarray(losses, np.int32)
+    fit = np.zeros(len(losses) // 2, np.int32)
+    sl = C.c_int64(0)
+    _check(lib().egg_deggs_chunk_fitness(_ptr(losses), len(losses), mean_filter, exponent, adaptive, alpha, _ptr(fit), C.byref(sl)))
+    return fit, sl.value
+
+
+def next_seed(seed, step):
+    return lib().egg_next_seed(seed & 0xFFFFFFFF, step)

@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libegg_b200.so")
-SOURCES = ["egg_api.cu", "egg_kernels.cu", "egg_gemm_inst.cu"]
+SOURCES = ["egg_api.cu", "egg_kernels.cu", "egg_gemm_inst.cu", "egg_wire.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 
@@ -46,7 +46,7 @@ def build(force=False, verbose=False):
     inc = _nccl_include()
 
     def compile_one(src):
-        obj = os.path.join(objdir, src.replace(".cu", ".o"))
+        obj = os.path.join(objdir, os.path.splitext(src)[0] + ".o")
         cmd = ["nvcc"] + NVCC_FLAGS + inc + (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:

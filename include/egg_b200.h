@@ -189,6 +189,41 @@ int egg_update_reconstruct(egg_ctx *ctx, const int32_t *fitness, int pairs,
                            int rows_k, int cols_n, int off_a, int off_b, int seed_base,
                            uint32_t step_seed, int32_t *vote_out, int on_device);
 
+/* ---- d-eggs worker boundary (host side, no GPU involved) ------------------ */
+/* Opcodes and the 10-byte "JOBS" header of d-eggs/include/protocol.h:8-56. */
+#define EGG_OP_JOB_REQUEST  0
+#define EGG_OP_RESULT       1
+#define EGG_OP_JOB_RESPONSE 2
+#define EGG_OP_LOG_MESSAGE  3
+#define EGG_WIRE_HEADER_BYTES 10
+/* Union of the fields of EggJobRequest / EggJobResponseHeader / EggResultHeader
+ * (protocol.h:61-160); payload_size is model_size resp. result_size. */
+typedef struct egg_wire_msg {
+    int32_t  opcode;
+    uint32_t payload_size;
+    uint64_t seed, last_step, data_position;   /* data_position == (uint64_t)-1: "wait" (coordinator.cpp:277-286) */
+    uint64_t updates_count;
+    int64_t  sum_loss;
+} egg_wire_msg;
+int egg_wire_fixed_bytes(int opcode);
+/* ≙ egg_write_header + egg_serialize_* ; returns bytes written (header + fixed body). */
+int egg_wire_encode(const egg_wire_msg *msg, uint8_t *out, int cap);
+/* ≙ egg_parse_header: 0, or -1 bad magic, -2 bad version. total_len = fixed body + payload. */
+int egg_wire_decode_header(const uint8_t *buf10, int *opcode, uint32_t *total_len);
+/* ≙ egg_deserialize_* */
+int egg_wire_decode_body(int opcode, const uint8_t *body, int len, egg_wire_msg *msg);
+/* ≙ ternary_pack_estimate_size / ternary_pack / ternary_unpack (d-eggs/include/utils/ternary_pack.h:12-87). */
+int64_t egg_ternary_packed_size(int64_t count);
+void egg_ternary_pack(const int32_t *values, int64_t count, uint8_t *out);
+void egg_ternary_unpack(const uint8_t *in, int64_t count, int32_t *values);
+/* ≙ the worker's per-chunk host fitness (worker.cu:635-687): CHUNK_MEAN_FILTER with
+ * CHUNK_MEAN_EXPONENT, USE_ADAPTIVE_THRESHOLD with ADAPTIVE_THRESHOLD_ALPHA.
+ * losses[count] chunk-relative; fitness[count/2] in {-1,0,1}; *sum_loss = Σ losses. */
+int egg_deggs_chunk_fitness(const int32_t *losses, int count, int mean_filter, double exponent,
+                            int adaptive_threshold, double alpha, int32_t *fitness, int64_t *sum_loss);
+/* ≙ seed = hash_rng(seed, step) after every update (worker.cu:542, coordinator.cpp:406). */
+uint32_t egg_next_seed(uint32_t seed, uint64_t step);
+
 /* ---- measurement ------------------------------------------------------ */
 /*
  * The reference times a generation with clock_gettime around its launches

@@ -805,6 +805,40 @@ void oracle_projection(const egg_config *cfg, const int8_t *x, const int8_t *w_p
     }
 }
 
+/* ------------------------------------------------- d-eggs per-chunk fitness */
+
+/* d-eggs/src/worker.cu:635-687 with CHUNK_MEAN_FILTER and USE_ADAPTIVE_THRESHOLD as flags */
+void oracle_deggs_chunk_fitness(const int32_t *losses, int count, int mean_filter, double exponent, int adaptive,
+                                double alpha, int32_t *fit, int64_t *sum_loss) {
+    int num = count / 2;
+    int32_t *diffs = (int32_t *)malloc(sizeof(int32_t) * (size_t)num);
+    int64_t sl = 0; double sum_diff_val = 0.0;
+    for (int i = 0; i < num; i++) {
+        int32_t p = losses[2 * i], n = losses[2 * i + 1];
+        sl += p + n;
+        diffs[i] = n - p;
+        sum_diff_val += diffs[i];
+    }
+    if (mean_filter) {
+        double mean_diff = sum_diff_val / num;
+        if (mean_diff != 0.0) {
+            double sign = (mean_diff > 0) ? 1.0 : -1.0;
+            mean_diff = sign * pow(fabs(mean_diff), exponent);
+        }
+        for (int i = 0; i < num; i++) diffs[i] += (int32_t)mean_diff;
+    }
+    if (adaptive) {
+        double sum_abs_diff = 0.0;
+        for (int i = 0; i < num; i++) sum_abs_diff += fabs((double)diffs[i]);
+        double threshold = (sum_abs_diff / num) * alpha;
+        for (int i = 0; i < num; i++) fit[i] = (fabs((double)diffs[i]) < threshold) ? 0 : ((diffs[i] > 0) ? 1 : -1);
+    } else {
+        for (int i = 0; i < num; i++) fit[i] = (diffs[i] > 0) ? 1 : ((diffs[i] < 0) ? -1 : 0);
+    }
+    if (sum_loss) *sum_loss = sl;
+    free(diffs);
+}
+
 /* --------------------------------------------------------- ternary codec */
 
 /* d-eggs/include/utils/ternary_pack.h:12-14 */

@@ -90,6 +90,11 @@ void oracle_projection(const egg_config *cfg, const int8_t *x, const int8_t *w_p
                        int8_t *y, int64_t rows, int k_dim, int n_dim, int rows_per_member,
                        uint32_t seed, int off_a, int off_b, int rank1_shift, int out_shift);
 
+/* --- d-eggs worker host fitness (d-eggs/src/worker.cu:635-687). Parity unpinned: the reference
+ * has this code inline in main(), it cannot be called; restated by reading. --- */
+void oracle_deggs_chunk_fitness(const int32_t *losses, int count, int mean_filter, double exponent, int adaptive,
+                                double alpha, int32_t *fit, int64_t *sum_loss);
+
 /* --- ternary codec (d-eggs/include/utils/ternary_pack.h:12-87) --- */
 int64_t oracle_ternary_packed_size(int64_t count);
 void oracle_ternary_pack(const int32_t *values, int64_t count, uint8_t *out);

@@ -81,6 +81,7 @@ def lib():
         L.oracle_newton_schulz.argtypes = [C.c_void_p, C.c_int, C.c_int]
         L.oracle_projection.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int,
                                         C.c_int, C.c_uint32, C.c_int, C.c_int, C.c_int, C.c_int]
+        L.oracle_deggs_chunk_fitness.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_double, C.c_int, C.c_double, C.c_void_p, C.c_void_p]
         L.oracle_ternary_packed_size.restype = C.c_int64
         L.oracle_ternary_packed_size.argtypes = [C.c_int64]
         L.oracle_ternary_pack.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
@@ -200,3 +201,11 @@ def ternary_unpack(packed, count):
     out = np.zeros(count, np.int32)
     lib().oracle_ternary_unpack(_p(np.ascontiguousarray(packed, np.uint8)), count, _p(out))
     return out
+
+
+def deggs_chunk_fitness(losses, mean_filter=1, exponent=1.2, adaptive=1, alpha=0.1):
+    losses = np.ascontiguousarray(losses, np.int32)
+    fit = np.zeros(len(losses) // 2, np.int32)
+    sl = np.zeros(1, np.int64)
+    lib().oracle_deggs_chunk_fitness(_p(losses), len(losses), mean_filter, exponent, adaptive, alpha, _p(fit), _p(sl))
+    return fit, int(sl[0])

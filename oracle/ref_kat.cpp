@@ -8,6 +8,7 @@
 #include <vector>
 #include "utils/egg_math.h"
 #include "utils/ternary_pack.h"
+#include "protocol.h"
 
 int main() {
     printf("{\n \"device_mask\": %d, \"host_mask\": %d,\n", DEVICE_MASK, HOST_MASK);
@@ -44,6 +45,25 @@ int main() {
         printf("], \"packed\": [");
         for (size_t i = 0; i < ternary_pack_estimate_size(c.size()); i++) printf("%s%u", i ? ", " : "", packed[i]);
         printf("]}");
+    }
+    printf("],\n \"wire\": [");
+    // the three message kinds of d-eggs/include/protocol.h, serialised by the reference's own helpers
+    auto hex = [](const uint8_t *b, int n) { for (int i = 0; i < n; i++) printf("%02x", b[i]); };
+    {
+        uint8_t buf[64];
+        EggJobRequest rq = {0x1122334455667788ull, 930, 0xFFFFFFFFFFFFFFFFull};
+        egg_write_header(buf, OP_JOB_REQUEST, 24); egg_serialize_job_request(buf + 10, &rq);
+        printf("{\"opcode\": 0, \"seed\": %llu, \"last_step\": %llu, \"data_position\": %llu, \"payload_size\": 0, \"updates_count\": 0, \"sum_loss\": 0, \"hex\": \"",
+               (unsigned long long)rq.seed, (unsigned long long)rq.last_step, (unsigned long long)rq.data_position);
+        hex(buf, 34); printf("\"}, ");
+        EggJobResponseHeader rs = {42, 7, 123456789012ull, 26215};
+        egg_write_header(buf, OP_JOB_RESPONSE, 28 + rs.model_size); egg_serialize_job_response_header(buf + 10, &rs);
+        printf("{\"opcode\": 2, \"seed\": 42, \"last_step\": 7, \"data_position\": 123456789012, \"payload_size\": 26215, \"updates_count\": 0, \"sum_loss\": 0, \"hex\": \"");
+        hex(buf, 38); printf("\"}, ");
+        EggResultHeader rr = {0xC0FFEE, 15470, 4096, 591871, (uint64_t)(int64_t)-123456789, 3277};
+        egg_write_header(buf, OP_RESULT, 44 + rr.result_size); egg_serialize_result_header(buf + 10, &rr);
+        printf("{\"opcode\": 1, \"seed\": %u, \"last_step\": 15470, \"data_position\": 4096, \"payload_size\": 3277, \"updates_count\": 591871, \"sum_loss\": -123456789, \"hex\": \"", 0xC0FFEE);
+        hex(buf, 54); printf("\"}");
     }
     printf("]\n}\n");
     return 0;
