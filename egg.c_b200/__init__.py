@@ -21,6 +21,7 @@ EXPORTS = [
     "egg_download_opt_state", "egg_set_dataset", "egg_eval_chunk", "egg_read_losses", "egg_compute_fitness_pairs",
     "egg_write_fitness", "egg_read_fitness", "egg_nccl_unique_id", "egg_comm_init", "egg_allgather_fitness",
     "egg_apply_update", "egg_generation_host", "egg_perturbed_projection", "egg_update_reconstruct",
+    "egg_update_reconstruct_noalloc",
     "egg_timer_start", "egg_timer_stop", "egg_profile_enable", "egg_profile_read", "egg_profile_name", "egg_launch_count",
     "egg_wave_members", "egg_wire_fixed_bytes", "egg_wire_encode", "egg_wire_decode_header", "egg_wire_decode_body",
     "egg_ternary_packed_size", "egg_ternary_pack", "egg_ternary_unpack", "egg_deggs_chunk_fitness", "egg_next_seed",
@@ -101,6 +102,7 @@ def lib():
         L.egg_perturbed_projection.argtypes = [vp, vp, vp, vp, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_int,
                                                C.c_int, C.c_int, C.c_int, C.c_int]
         L.egg_update_reconstruct.argtypes = [vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint32, vp, C.c_int]
+        L.egg_update_reconstruct_noalloc.argtypes = [vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_int, vp]
         L.egg_timer_start.argtypes = [vp]
         L.egg_timer_stop.argtypes = [vp, P(C.c_float)]
         L.egg_profile_enable.argtypes = [vp, C.c_int]
@@ -250,6 +252,11 @@ class Context:
         _check(lib().egg_update_reconstruct(self._h, _ptr(fitness), pairs, rows_k, cols_n, off_a, off_b, seed_base,
                                             step_seed & 0xFFFFFFFF, _ptr(vote_out), 1 if on_device else 0))
 
+
+    def update_reconstruct_noalloc(self, d_fitness, pairs, rows_k, cols_n, off_a, off_b, seed_base, step_seed, split, d_vote_out):
+        """Device pointers in and out; uses the library's built-in operand buffer, allocates nothing."""
+        _check(lib().egg_update_reconstruct_noalloc(self._h, _ptr(d_fitness), pairs, rows_k, cols_n, off_a, off_b, seed_base,
+                                                    step_seed & 0xFFFFFFFF, 1 if split else 0, _ptr(d_vote_out)))
 
     def timer_start(self):
         _check(lib().egg_timer_start(self._h))

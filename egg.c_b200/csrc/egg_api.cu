@@ -883,6 +883,48 @@ extern "C" int egg_update_reconstruct(egg_ctx *c, const int32_t *fitness, int pa
     return check_dev_err(c);
 }
 
+// ---------------------------------------------------------------- allocation-free reconstruct
+
+// Operand scratch of egg_update_reconstruct_noalloc: part of the library image, one copy per GPU.
+// In host code this name is only a handle for cudaGetSymbolAddress, never a pointer to hand to a kernel.
+static __device__ __align__(256) int8_t g_noalloc_scratch[EGG_NOALLOC_SCRATCH_BYTES];
+static int8_t *g_noalloc_ptr[64] = {};     // device address of the array, per device ordinal
+
+extern "C" int egg_update_reconstruct_noalloc(egg_ctx *c, const int32_t *d_fitness, int pairs, int rows_k, int cols_n, int off_a,
+                                              int off_b, int seed_base, uint32_t step_seed, int split, int32_t *d_vote_out) {
+    if (!c || !d_fitness || !d_vote_out) { set_error("null argument"); return EGG_E_INVALID; }
+    if (pairs <= 0 || rows_k % 128 || cols_n % 128 || rows_k <= 0 || cols_n <= 0) { set_error("reconstruct shape unsupported"); return EGG_E_INVALID; }
+    const int kp = (pairs + 127) / 128 * 128;
+    const int64_t ktot = split ? 2 * (int64_t)kp : kp;
+    const int64_t need = ((int64_t)rows_k + cols_n) * ktot;
+    if (need > (int64_t)EGG_NOALLOC_SCRATCH_BYTES) {
+        set_error("needs %lld bytes of operand scratch, the built-in buffer holds %u: use egg_update_reconstruct", (long long)need,
+                  EGG_NOALLOC_SCRATCH_BYTES);
+        return EGG_E_INVALID;
+    }
+    const int amax = c->cfg.device_gaussian ? 3 * c->cfg.device_mask : c->cfg.device_mask;
+    if (split && 16 * amax > 127) { set_error("noise magnitude %d does not fit the two-digit operand split", amax); return EGG_E_INVALID; }
+    if (c->device < 0 || c->device >= 64) { set_error("device ordinal out of range"); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    if (!g_noalloc_ptr[c->device]) {       // set-up, once per device, with that device current
+        void *ptr = nullptr;
+        EGG_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        g_noalloc_ptr[c->device] = static_cast<int8_t *>(ptr);
+    }
+    int8_t *na = g_noalloc_ptr[c->device];
+    int8_t *nb = na + (int64_t)cols_n * ktot;           // cols_n*ktot is a multiple of 128*128: stays 256-byte aligned
+    int rc = launch_update_operands(c->stream, na, nb, d_fitness, pairs, kp, rows_k, cols_n, off_a, off_b, seed_base, step_seed,
+                                    c->cfg.device_mask, c->cfg.device_gaussian, split ? 1 : 0);
+    if (rc) return rc;
+    c->launches += 2;
+    GemmParams g;
+    memset(&g, 0, sizeof(g));
+    g.M = cols_n; g.N = rows_k; g.K = (int)ktot; g.seq_len = 1 << 20; g.vote_out = d_vote_out; g.err = c->d_err;
+    if ((rc = launch_gemm(c->stream, EPI_VOTE, na, nb, g, c->num_sms))) return rc;
+    EGG_CUDA(cudaStreamSynchronize(c->stream));
+    return check_dev_err(c);
+}
+
 // ---------------------------------------------------------------- measurement
 
 extern "C" int egg_timer_start(egg_ctx *c) {

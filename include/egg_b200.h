@@ -189,6 +189,36 @@ int egg_update_reconstruct(egg_ctx *ctx, const int32_t *fitness, int pairs,
                            int rows_k, int cols_n, int off_a, int off_b, int seed_base,
                            uint32_t step_seed, int32_t *vote_out, int on_device);
 
+/*
+ * Allocation-free variant of egg_update_reconstruct.  It has no counterpart in the
+ * reference.  It exists for callers that must not allocate device memory while they
+ * run: a d-eggs style worker that was handed a fixed memory budget at start-up, code
+ * running inside a memory pool that forbids cudaMalloc, or a loop where the implicit
+ * device synchronisation of cudaMalloc/cudaFree would stall other streams.
+ *
+ * The two noise operand matrices that the vote GEMM needs are kept in one fixed
+ * 8 MiB buffer that lives inside the library image on every GPU that loads it
+ * (EGG_NOALLOC_SCRATCH_BYTES, held until the process exits).  The call is refused
+ * with EGG_E_INVALID when (rows_k + cols_n) * K exceeds it, where K is `pairs`
+ * rounded up to 128, doubled when `split` is set.
+ *
+ * fitness and vote_out are DEVICE pointers owned by the caller.  split = 0 promises
+ * |fitness| * (largest noise magnitude) <= 127 (ternary fitness always qualifies);
+ * split = 1 selects the two-digit operand form for int8 fitness (needs
+ * 16 * noise magnitude <= 127).  Nothing is read back to check the promise.
+ *
+ * The first call on a device looks up the buffer's device address; make that first
+ * call outside any stream capture.  All calls share the buffer and it keeps the last
+ * call's operands; every call rewrites the whole region it uses (zero padding
+ * included), so nothing has to be cleared, but two calls that overlap on the GPU
+ * (different contexts or streams on one device) race on it.
+ * Calls no cudaMalloc / cudaFree; blocks until the votes are written.
+ */
+#define EGG_NOALLOC_SCRATCH_BYTES (8u << 20)
+int egg_update_reconstruct_noalloc(egg_ctx *ctx, const int32_t *d_fitness, int pairs,
+                                   int rows_k, int cols_n, int off_a, int off_b, int seed_base,
+                                   uint32_t step_seed, int split, int32_t *d_vote_out);
+
 /* ---- d-eggs worker boundary (host side, no GPU involved) ------------------ */
 /* Opcodes and the 10-byte "JOBS" header of d-eggs/include/protocol.h:8-56. */
 #define EGG_OP_JOB_REQUEST  0
