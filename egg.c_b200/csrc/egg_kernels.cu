@@ -166,17 +166,34 @@ __device__ __forceinline__ int div_small(int a, float rinv) {
     return f2i_exact((y - copysignf(0.5f, y) + kMagic) - kMagic);
 }
 
-template <int MODE>
+// One warp per row; NJ = H/128 chunks of 4 elements per lane.  Every global load of the row (the int32
+// pre-activations or the embedding bytes, the perturbed gain/bias tables, the noise vectors of the
+// following projections) is issued before any arithmetic, so that one memory latency is exposed per row
+// instead of three.
+template <int MODE, int NJ>
 __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
     const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (r >= p.M) return;
-    const int H = p.H, nj = H >> 7;
+    const int H = NJ * 128;
     const int mem = r / p.seq_len, t = r % p.seq_len;
     const int sgn = mem & 1, ns = sgn ? -1 : 1;
     const int8_t *ntp = p.nt + (int64_t)(mem >> 1) * p.nt_stride;
-    int x[8][4];
+    const int16_t *wm = reinterpret_cast<const int16_t *>(ntp + p.nt_w_m) + sgn * H;   // w + ((n1*n2*sign)>>SSV)
+    const int16_t *bm = reinterpret_cast<const int16_t *>(ntp + p.nt_b_m) + sgn * H;
+    int x[NJ][4];
 
+    // ---- loads ----
+    int2 w4[NJ], b4[NJ];
+    int32_t n4[3][NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; j++) {
+        const int d = (j << 7) + (lane << 2);
+        w4[j] = *reinterpret_cast<const int2 *>(wm + d);
+        b4[j] = *reinterpret_cast<const int2 *>(bm + d);
+#pragma unroll
+        for (int q = 0; q < 3; q++) n4[q][j] = (q < p.ndots) ? *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[q] + d) : 0;
+    }
     if (MODE == 0) {
         // embedding (mgpu.cu:902-931)
         int64_t pair = (p.pop_base + mem) >> 1;
@@ -186,46 +203,41 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
         const int a_tok = ntp[p.nt_emb_a + tok];
         const int32_t *emb32 = reinterpret_cast<const int32_t *>(p.emb_packed);
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            if (j >= nj) break;
+        for (int j = 0; j < NJ; j++) {
             const int d = (j << 7) + (lane << 2);
             int32_t e4 = emb32[(int64_t)(d >> 2) * p.vocab + tok];
-            int32_t b4 = *reinterpret_cast<const int32_t *>(p.emb_bias + d);
+            int32_t eb4 = *reinterpret_cast<const int32_t *>(p.emb_bias + d);
             int32_t dl4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_emb_bias_d + sgn * H + d);
             int32_t nb4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_emb_b + d);
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 int perturb = (a_tok * (int)byte_of(nb4, i) * ns) >> p.emb_shift;
-                x[j][i] = clip8((int)byte_of(e4, i) + (int)byte_of(b4, i) + (int)byte_of(dl4, i) + perturb);
+                x[j][i] = clip8((int)byte_of(e4, i) + (int)byte_of(eb4, i) + (int)byte_of(dl4, i) + perturb);
             }
         }
     } else {
+        int4 v[NJ];
+#pragma unroll
+        for (int j = 0; j < NJ; j++) v[j] = *reinterpret_cast<const int4 *>(p.pre32 + (int64_t)r * H + (j << 7) + (lane << 2));
         const int mx = p.rowmax[r];
         const float scale = aln_scale(mx);
         if (mx < (1 << 22)) {
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                if (j >= nj) break;
-                const int d = (j << 7) + (lane << 2);
-                int4 v = *reinterpret_cast<const int4 *>(p.pre32 + (int64_t)r * H + d);
-                x[j][0] = aln_quant<true>(v.x, scale); x[j][1] = aln_quant<true>(v.y, scale);
-                x[j][2] = aln_quant<true>(v.z, scale); x[j][3] = aln_quant<true>(v.w, scale);
+            for (int j = 0; j < NJ; j++) {
+                x[j][0] = aln_quant<true>(v[j].x, scale); x[j][1] = aln_quant<true>(v[j].y, scale);
+                x[j][2] = aln_quant<true>(v[j].z, scale); x[j][3] = aln_quant<true>(v[j].w, scale);
             }
         } else {
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                if (j >= nj) break;
-                const int d = (j << 7) + (lane << 2);
-                int4 v = *reinterpret_cast<const int4 *>(p.pre32 + (int64_t)r * H + d);
-                x[j][0] = aln_quant<false>(v.x, scale); x[j][1] = aln_quant<false>(v.y, scale);
-                x[j][2] = aln_quant<false>(v.z, scale); x[j][3] = aln_quant<false>(v.w, scale);
+            for (int j = 0; j < NJ; j++) {
+                x[j][0] = aln_quant<false>(v[j].x, scale); x[j][1] = aln_quant<false>(v[j].y, scale);
+                x[j][2] = aln_quant<false>(v[j].z, scale); x[j][3] = aln_quant<false>(v[j].w, scale);
             }
         }
     }
     int tot = 0;
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
-        if (j >= nj) break;
+    for (int j = 0; j < NJ; j++) {
         const int d = (j << 7) + (lane << 2);
         uint32_t w = pack4(x[j][0], x[j][1], x[j][2], x[j][3]);
         *reinterpret_cast<uint32_t *>(p.x_out + (int64_t)r * H + d) = w;
@@ -236,25 +248,20 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
     int mn = tot / H;
     if (!mn) mn = 1;
     const float rinv = 1.0f / (float)mn;
-    const int16_t *wm = reinterpret_cast<const int16_t *>(ntp + p.nt_w_m) + sgn * H;   // w + ((n1*n2*sign)>>SSV)
-    const int16_t *bm = reinterpret_cast<const int16_t *>(ntp + p.nt_b_m) + sgn * H;
     int dot0 = 0, dot1 = 0, dot2 = 0;
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
-        if (j >= nj) break;
+    for (int j = 0; j < NJ; j++) {
         const int d = (j << 7) + (lane << 2);
-        const int2 w4 = *reinterpret_cast<const int2 *>(wm + d);
-        const int2 b4 = *reinterpret_cast<const int2 *>(bm + d);
-        const int wv[4] = {(int)(int16_t)(w4.x & 0xFFFF), w4.x >> 16, (int)(int16_t)(w4.y & 0xFFFF), w4.y >> 16};
-        const int bv[4] = {(int)(int16_t)(b4.x & 0xFFFF), b4.x >> 16, (int)(int16_t)(b4.y & 0xFFFF), b4.y >> 16};
+        const int wv[4] = {(int)(int16_t)(w4[j].x & 0xFFFF), w4[j].x >> 16, (int)(int16_t)(w4[j].y & 0xFFFF), w4[j].y >> 16};
+        const int bv[4] = {(int)(int16_t)(b4[j].x & 0xFFFF), b4[j].x >> 16, (int)(int16_t)(b4[j].y & 0xFFFF), b4[j].y >> 16};
         int y[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) y[i] = clip8(div_small(x[j][i] * wv[i], rinv) + bv[i]);
         const uint32_t yw = pack4(y[0], y[1], y[2], y[3]);
         *reinterpret_cast<uint32_t *>(p.h_out + (int64_t)r * H + d) = yw;
-        if (p.ndots > 0) dot0 = __dp4a((int)yw, *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[0] + d), dot0);
-        if (p.ndots > 1) dot1 = __dp4a((int)yw, *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[1] + d), dot1);
-        if (p.ndots > 2) dot2 = __dp4a((int)yw, *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[2] + d), dot2);
+        dot0 = __dp4a((int)yw, n4[0][j], dot0);
+        dot1 = __dp4a((int)yw, n4[1][j], dot1);
+        dot2 = __dp4a((int)yw, n4[2][j], dot2);
     }
     if (p.ndots > 0) { int s = warp_sum(dot0); if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride] = s; }
     if (p.ndots > 1) { int s = warp_sum(dot1); if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride + 1] = s; }
@@ -267,12 +274,26 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
     }
 }
 
-int launch_rowwise(cudaStream_t st, const RowParams &p, int mode) {
-    int blocks = (p.M + 7) / 8;
-    if (mode == 0) rowwise_kernel<0><<<blocks, 256, 0, st>>>(p);
-    else rowwise_kernel<1><<<blocks, 256, 0, st>>>(p);
+template <int MODE>
+static int launch_rowwise_nj(cudaStream_t st, const RowParams &p) {
+    const int blocks = (p.M + 7) / 8;
+    switch (p.H >> 7) {
+        case 1: rowwise_kernel<MODE, 1><<<blocks, 256, 0, st>>>(p); break;
+        case 2: rowwise_kernel<MODE, 2><<<blocks, 256, 0, st>>>(p); break;
+        case 3: rowwise_kernel<MODE, 3><<<blocks, 256, 0, st>>>(p); break;
+        case 4: rowwise_kernel<MODE, 4><<<blocks, 256, 0, st>>>(p); break;
+        case 5: rowwise_kernel<MODE, 5><<<blocks, 256, 0, st>>>(p); break;
+        case 6: rowwise_kernel<MODE, 6><<<blocks, 256, 0, st>>>(p); break;
+        case 7: rowwise_kernel<MODE, 7><<<blocks, 256, 0, st>>>(p); break;
+        case 8: rowwise_kernel<MODE, 8><<<blocks, 256, 0, st>>>(p); break;
+        default: set_error("hidden_dim %d unsupported by the row-wise kernel", p.H); return EGG_E_INVALID;
+    }
     EGG_CUDA(cudaGetLastError());
     return EGG_OK;
+}
+
+int launch_rowwise(cudaStream_t st, const RowParams &p, int mode) {
+    return mode == 0 ? launch_rowwise_nj<0>(st, p) : launch_rowwise_nj<1>(st, p);
 }
 
 // Q/K/V requantisation (adaptive_qkv_normalize, mgpu.cu:782-784)
