@@ -263,6 +263,44 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         *reinterpret_cast<int32_t *>(&sm.d_tab[sl][j]) = *reinterpret_cast<const int32_t *>(base + p.nt_d_off + n0 + j);
                 }
             }
+            // ---- per-row state of the 4 rows this lane owns after the transpose, and the loads that do not
+            // depend on the accumulator: all issued before waiting for the MMAs of this tile ----
+            const int cbase = half * COLS_PER;       // column offset inside the tile
+            int32_t(*st)[20] = sm.stage[ew];
+            const int lrow = lane >> 2, pc = lane & 3;          // row group / 4-column piece of this lane
+            int rrow[4], xbs[4], slot_sgn[4], aux[4];           // per-row state of the 4 rows this lane touches
+            bool rok[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                if (EPI > EPI_HEAD) { rrow[i] = 0; xbs[i] = 0; slot_sgn[i] = 0; aux[i] = 0; rok[i] = false; continue; }
+                const int rr = m0 + quarter * 32 + i * 8 + lrow;
+                rok[i] = rr < p.M;
+                const int rc = rok[i] ? rr : (p.M - 1);
+                rrow[i] = rc;
+                const int mem = rc / p.seq_len;
+                const int sg = mem & 1;
+                slot_sgn[i] = (((mem >> 1) - first_pl) << 1) | sg;
+                const int xcol = (EPI == EPI_QKV) ? (n0 / p.third) : 0;
+                const int xbv = p.xb[(int64_t)rc * p.xb_stride + xcol];
+                xbs[i] = sg ? -xbv : xbv;
+                aux[i] = 0;
+                if (EPI == EPI_QKV) aux[i] = rc - mem * p.seq_len;                 // token position t
+                if (EPI == EPI_HEAD) {                                             // target byte of this row
+                    const int t = rc - mem * p.seq_len;
+                    const int64_t pair = (p.pop_base + mem) >> 1;
+                    const int64_t pos = p.use_same_data ? (p.start_idx % (p.data_len - p.seq_len))
+                                                        : ((p.start_idx + pair * p.data_stride) % (p.data_len - p.seq_len));
+                    aux[i] = p.dataset[pos + t + 1];
+                }
+            }
+            int32_t rs_pre[COLS_PER / 16][4];        // residual bytes of every chunk (EPI_PRE32)
+            if (EPI == EPI_PRE32 && active) {
+#pragma unroll
+                for (int cc = 0; cc < COLS_PER / 16; cc++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        rs_pre[cc][i] = *reinterpret_cast<const int32_t *>(p.resid + (int64_t)rrow[i] * p.N + n0 + cbase + cc * 16 + 4 * pc);
+            }
             // one thread waits for the accumulator, everybody learns the outcome at the barrier
             if (e == 0) {
                 bool ok = ptx::mbar_wait(&sm.tmem_full[as], aph) && !sm.abort_flag;
@@ -274,7 +312,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             ptx::tc_fence_after();
 
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * BN + half * COLS_PER);
-            const int cbase = half * COLS_PER;       // column offset inside the tile
 
             if (!active) {
                 // nothing to compute; still takes part in the barrier protocol below
@@ -283,32 +320,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 // Accumulators leave TMEM one row per lane; they are transposed through shared memory so
                 // that 4 consecutive lanes own 16 consecutive columns of one row: every global access below
                 // is then a run of full 32-byte sectors, and the per-column tables are read as words.
-                int32_t(*st)[20] = sm.stage[ew];
-                const int lrow = lane >> 2, pc = lane & 3;          // row group / 4-column piece of this lane
-                int rrow[4], xbs[4], slot_sgn[4], aux[4];           // per-row state of the 4 rows this lane touches
-                bool rok[4];
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int rr = m0 + quarter * 32 + i * 8 + lrow;
-                    rok[i] = rr < p.M;
-                    const int rc = rok[i] ? rr : (p.M - 1);
-                    rrow[i] = rc;
-                    const int mem = rc / p.seq_len;
-                    const int sg = mem & 1;
-                    slot_sgn[i] = (((mem >> 1) - first_pl) << 1) | sg;
-                    const int xcol = (EPI == EPI_QKV) ? (n0 / p.third) : 0;
-                    const int xbv = p.xb[(int64_t)rc * p.xb_stride + xcol];
-                    xbs[i] = sg ? -xbv : xbv;
-                    aux[i] = 0;
-                    if (EPI == EPI_QKV) aux[i] = rc - mem * p.seq_len;                 // token position t
-                    if (EPI == EPI_HEAD) {                                             // target byte of this row
-                        const int t = rc - mem * p.seq_len;
-                        const int64_t pair = (p.pop_base + mem) >> 1;
-                        const int64_t pos = p.use_same_data ? (p.start_idx % (p.data_len - p.seq_len))
-                                                            : ((p.start_idx + pair * p.data_stride) % (p.data_len - p.seq_len));
-                        aux[i] = p.dataset[pos + t + 1];
-                    }
-                }
                 int racc[4];                                        // running abs-max / dot / row max per row
 #pragma unroll
                 for (int i = 0; i < 4; i++) racc[i] = (EPI == EPI_HEAD) ? INT_MIN : 0;
@@ -328,7 +339,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                             racc[i] = m;
                         }
                     }
-#pragma unroll 1
+                    constexpr int CHUNK_UNROLL = (EPI == EPI_HEAD) ? 1 : COLS_PER / 16;
+#pragma unroll CHUNK_UNROLL
                     for (int c = 0; c < COLS_PER; c += 16) {
                         {
                             uint32_t v[16];
@@ -365,7 +377,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                 if (rok[i]) *reinterpret_cast<uint32_t *>(p.out8 + gofs) = w;
                             } else if (EPI == EPI_PRE32) {
                                 const int2 bc = *reinterpret_cast<const int2 *>(&sm.bc_tab[sl][sg][col]);
-                                const int32_t rs = *reinterpret_cast<const int32_t *>(p.resid + gofs);
+                                const int32_t rs = rs_pre[c / 16][i];
                                 v0 = (int)(int8_t)(rs) + (v0 >> p.out_shift) + (int)(int16_t)(bc.x & 0xFFFF);
                                 v1 = (int)(int8_t)(rs >> 8) + (v1 >> p.out_shift) + (bc.x >> 16);
                                 v2 = (int)(int8_t)(rs >> 16) + (v2 >> p.out_shift) + (int)(int16_t)(bc.y & 0xFFFF);
