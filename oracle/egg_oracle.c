@@ -690,40 +690,59 @@ void oracle_newton_schulz(float *x, int rows, int cols) {
     free(G); free(Y);
 }
 
-typedef struct { int64_t off; int rows, cols, off_a, off_b, seed_base; float lr_scale; int hidden; } param_desc;
+typedef struct { int64_t off; int rows, cols, off_a, off_b, seed_base; float lr_scale; int hidden; int64_t ov_in, ov_out; } param_desc;
 
 /* the launch sequence of mgpu.cu:1603-1643 as a table (matrices: rows=K in, cols=N out; vectors: rows=0) */
-static int build_params(const egg_config *c, const model_layout *L, param_desc *P) {
+/* ov_in / ov_out: AdaptiveScales offsets of the overlay over the input index k ("*_row") and the output index n
+ * ("*_col"), as worker.cu:465-517 passes them; for the embedding these are embedding_col / embedding_row. */
+static int build_params(const egg_config *c, const model_layout *L, const scales_layout *S, param_desc *P) {
     int H = c->hidden_dim, V = c->vocab_size, n = 0;
-#define MAT(o, r, cl, a, b, base, hid) P[n++] = (param_desc){(o), (r), (cl), (a), (b), (base), 1.0f, (hid)}
-#define VEC(o, len, a, b, base, sc) P[n++] = (param_desc){(o), 0, (len), (a), (b), (base), (sc), 0}
+#define MAT(o, r, cl, a, b, base, hid, oi, oo) P[n++] = (param_desc){(o), (r), (cl), (a), (b), (base), 1.0f, (hid), (oi), (oo)}
+#define VEC(o, len, a, b, base, sc, oi) P[n++] = (param_desc){(o), 0, (len), (a), (b), (base), (sc), 0, (oi), -1}
     for (int l = 0; l < c->n_layers; l++) {
-        int sb = l * 1000; int64_t hh = (int64_t)H * H;
-        MAT(L->w_q + l * hh, H, H, 200, 201, sb, 1);  MAT(L->w_k + l * hh, H, H, 202, 203, sb, 1);
-        MAT(L->w_v + l * hh, H, H, 204, 205, sb, 1);  MAT(L->w_o + l * hh, H, H, 206, 207, sb, 1);
-        MAT(L->w_up + l * 4 * hh, H, 4 * H, 400, 401, sb, 1);
-        MAT(L->w_down + l * 4 * hh, 4 * H, H, 402, 403, sb, 1);
-        VEC(L->ln_1 + (int64_t)l * H, H, 100, 101, sb, 1.0f);   VEC(L->ln_1_bias + (int64_t)l * H, H, 110, 111, sb, 1.0f);
-        VEC(L->ln_2 + (int64_t)l * H, H, 300, 301, sb, 1.0f);   VEC(L->ln_2_bias + (int64_t)l * H, H, 310, 311, sb, 1.0f);
-        VEC(L->mlp_bias_up + (int64_t)l * 4 * H, 4 * H, 410, 411, sb, 1.0f);
-        VEC(L->mlp_bias_down + (int64_t)l * H, H, 412, 413, sb, 1.0f);
+        int sb = l * 1000; int64_t hh = (int64_t)H * H, lH = (int64_t)l * H;
+        MAT(L->w_q + l * hh, H, H, 200, 201, sb, 1, S->w_q_row + lH, S->w_q_col + lH);  MAT(L->w_k + l * hh, H, H, 202, 203, sb, 1, S->w_k_row + lH, S->w_k_col + lH);
+        MAT(L->w_v + l * hh, H, H, 204, 205, sb, 1, S->w_v_row + lH, S->w_v_col + lH);  MAT(L->w_o + l * hh, H, H, 206, 207, sb, 1, S->w_o_row + lH, S->w_o_col + lH);
+        MAT(L->w_up + l * 4 * hh, H, 4 * H, 400, 401, sb, 1, S->w_up_row + lH, S->w_up_col + 4 * lH);
+        MAT(L->w_down + l * 4 * hh, 4 * H, H, 402, 403, sb, 1, S->w_down_row + 4 * lH, S->w_down_col + lH);
+        VEC(L->ln_1 + (int64_t)l * H, H, 100, 101, sb, 1.0f, S->ln_1 + lH);   VEC(L->ln_1_bias + (int64_t)l * H, H, 110, 111, sb, 1.0f, S->ln_1_bias + lH);
+        VEC(L->ln_2 + (int64_t)l * H, H, 300, 301, sb, 1.0f, S->ln_2 + lH);   VEC(L->ln_2_bias + (int64_t)l * H, H, 310, 311, sb, 1.0f, S->ln_2_bias + lH);
+        VEC(L->mlp_bias_up + (int64_t)l * 4 * H, 4 * H, 410, 411, sb, 1.0f, S->mlp_bias_up + 4 * lH);
+        VEC(L->mlp_bias_down + (int64_t)l * H, H, 412, 413, sb, 1.0f, S->mlp_bias_down + lH);
     }
-    VEC(L->ln_f, H, 900, 901, 0, 1.0f);        VEC(L->ln_f_bias, H, 910, 911, 0, 1.0f);
-    VEC(L->ln_init, H, 500, 501, 0, 1.0f);     VEC(L->ln_init_bias, H, 502, 503, 0, 1.0f);
-    MAT(L->w_emb_mlp_up, H, 4 * H, 510, 511, 0, 1);    VEC(L->mlp_emb_bias_up, 4 * H, 514, 515, 0, 1.0f);
-    MAT(L->w_emb_mlp_down, 4 * H, H, 512, 513, 0, 1);  VEC(L->mlp_emb_bias_down, H, 516, 517, 0, 1.0f);
-    VEC(L->emb_bias, H, 50, 51, 0, 0.1f);
-    MAT(L->embedding, H, V, 0, 0 + H, 0, 0);    /* always AdamW, mgpu.cu:1636-1643 */
+    VEC(L->ln_f, H, 900, 901, 0, 1.0f, S->ln_f);        VEC(L->ln_f_bias, H, 910, 911, 0, 1.0f, S->ln_f_bias);
+    VEC(L->ln_init, H, 500, 501, 0, 1.0f, S->ln_init);     VEC(L->ln_init_bias, H, 502, 503, 0, 1.0f, S->ln_init_bias);
+    MAT(L->w_emb_mlp_up, H, 4 * H, 510, 511, 0, 1, S->w_emb_mlp_up_row, S->w_emb_mlp_up_col);    VEC(L->mlp_emb_bias_up, 4 * H, 514, 515, 0, 1.0f, S->mlp_emb_bias_up);
+    MAT(L->w_emb_mlp_down, 4 * H, H, 512, 513, 0, 1, S->w_emb_mlp_down_row, S->w_emb_mlp_down_col);  VEC(L->mlp_emb_bias_down, H, 516, 517, 0, 1.0f, S->mlp_emb_bias_down);
+    VEC(L->emb_bias, H, 50, 51, 0, 0.1f, S->emb_bias);
+    MAT(L->embedding, H, V, 0, 0 + H, 0, 0, S->embedding_col, S->embedding_row);    /* always AdamW, mgpu.cu:1636-1643 */
 #undef MAT
 #undef VEC
     return n;
 }
 
+/* update_overlay_kernel (d-eggs/src/kernels.cu:61-77): +5 where something changed, -1 elsewhere, clamped */
+static void overlay_step(int8_t *ov, const uint8_t *changed, int n) {
+    for (int i = 0; i < n; i++) {
+        int v = ov[i];
+        if (changed[i]) { v += 5; if (v > 127) v = 127; } else { v -= 1; if (v < -127) v = -127; }
+        ov[i] = (int8_t)v;
+    }
+}
+
 uint64_t oracle_update(const egg_config *c, int8_t *model, void *opt_state, const int32_t *fitness,
                        uint32_t step_seed, float lr, int fma_mode) {
+    return oracle_update_scaled(c, model, opt_state, fitness, step_seed, lr, fma_mode, NULL);
+}
+
+uint64_t oracle_update_scaled(const egg_config *c, int8_t *model, void *opt_state, const int32_t *fitness,
+                              uint32_t step_seed, float lr, int fma_mode, int8_t *scales) {
     model_layout L; layout_of(c, &L);
+    scales_layout SL; scales_layout_of(c, &SL);
     param_desc *P = (param_desc *)malloc(sizeof(param_desc) * (size_t)(c->n_layers * 12 + 16));
-    int np = build_params(c, &L, P);
+    int np = build_params(c, &L, &SL, P);
+    int maxdim = 4 * c->hidden_dim > c->vocab_size ? 4 * c->hidden_dim : c->vocab_size;
+    uint8_t *ch_in = (uint8_t *)malloc((size_t)maxdim), *ch_out = (uint8_t *)malloc((size_t)maxdim);
     int pairs = c->population_size / 2;
     uint64_t total_updates = 0;
     for (int i = 0; i < np; i++) {
@@ -751,9 +770,19 @@ uint64_t oracle_update(const egg_config *c, int8_t *model, void *opt_state, cons
         else vote_vector(c, fitness, pairs, d->cols, d->off_a, d->off_b, d->seed_base, step_seed, vote);
         int8_t *w = model + d->off;
         if (!muon) {
+            memset(ch_in, 0, (size_t)maxdim); memset(ch_out, 0, (size_t)maxdim);
             for (int64_t j = 0; j < count; j++) {
                 float *s = (float *)(st + j * 12);
-                total_updates += (uint64_t)oracle_adam_step(c, &s[0], &s[1], &s[2], &w[j], -(float)vote[j], plr, fma_mode);
+                int ch = oracle_adam_step(c, &s[0], &s[1], &s[2], &w[j], -(float)vote[j], plr, fma_mode);
+                total_updates += (uint64_t)ch;
+                if (ch) {
+                    if (d->rows) { ch_out[(j >> 2) % d->cols] = 1; ch_in[((j >> 2) / d->cols) * 4 + (j & 3)] = 1; }
+                    else ch_in[j] = 1;
+                }
+            }
+            if (scales) {   /* worker.cu:445-463: overlay of the input index, then of the output index */
+                overlay_step(scales + d->ov_in, ch_in, d->rows ? d->rows : d->cols);
+                if (d->rows) overlay_step(scales + d->ov_out, ch_out, d->cols);
             }
         } else {
             /* muon_internal.cuh:15-50 momentum, :53-74 gather, NS, :112-166 apply */
@@ -779,7 +808,7 @@ uint64_t oracle_update(const egg_config *c, int8_t *model, void *opt_state, cons
         }
         free(vote);
     }
-    free(P);
+    free(P); free(ch_in); free(ch_out);
     return total_updates;
 }
 

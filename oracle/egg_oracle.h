@@ -71,6 +71,11 @@ void oracle_fitness(const int32_t *losses, int32_t *fitness, int pairs);
 uint64_t oracle_update(const egg_config *cfg, int8_t *model, void *opt_state,
                        const int32_t *fitness, uint32_t step_seed, float lr, int fma_mode);
 
+/* d-eggs variant: after each parameter's AdamW step the adaptive-noise overlays of the rows / columns that
+ * changed go up by 5, the others down by 1 (worker.cu:445-517, kernels.cu:61-77). scales may be NULL. */
+uint64_t oracle_update_scaled(const egg_config *cfg, int8_t *model, void *opt_state,
+                              const int32_t *fitness, uint32_t step_seed, float lr, int fma_mode, int8_t *scales);
+
 /* vote of one matrix in packed index order (mgpu.cu:1085-1098) */
 void oracle_vote_matrix(const egg_config *cfg, const int32_t *fitness, int pairs,
                         int rows_k, int cols_n, int off_a, int off_b, int seed_base,

@@ -76,6 +76,8 @@ def lib():
         L.oracle_fitness.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         L.oracle_update.restype = C.c_uint64
         L.oracle_update.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_float, C.c_int]
+        L.oracle_update_scaled.restype = C.c_uint64
+        L.oracle_update_scaled.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_float, C.c_int, C.c_void_p]
         L.oracle_vote_matrix.argtypes = [cfgp, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                          C.c_int, C.c_uint32, C.c_void_p]
         L.oracle_newton_schulz.argtypes = [C.c_void_p, C.c_int, C.c_int]
@@ -158,6 +160,13 @@ def update(cfg, model, opt_state, fit, step_seed, lr, fma_mode=FMA_NVCC):
     fit = np.ascontiguousarray(fit, np.int32)
     return int(lib().oracle_update(C.byref(cfg), _p(model), _p(opt_state), _p(fit), step_seed & 0xFFFFFFFF,
                                    C.c_float(lr), fma_mode))
+
+
+def update_scaled(cfg, model, opt_state, fit, step_seed, lr, scales, fma_mode=FMA_NVCC):
+    """d-eggs update: also steps the adaptive-noise overlays in `scales` (int8 array, in place)."""
+    fit = np.ascontiguousarray(fit, np.int32)
+    return int(lib().oracle_update_scaled(C.byref(cfg), _p(model), _p(opt_state), _p(fit), step_seed & 0xFFFFFFFF,
+                                          C.c_float(lr), fma_mode, _p(scales)))
 
 
 def vote_matrix(cfg, fit, rows_k, cols_n, off_a, off_b, seed_base, step_seed):

@@ -41,6 +41,7 @@ REF_CONFIGS = {
     "small": dict(hidden_dim=256, n_layers=2, seq_len=32, population_size=64, device_mask=3),
     "med": dict(hidden_dim=512, n_layers=4, seq_len=256, population_size=256, device_mask=3),
     "c2": dict(hidden_dim=512, n_layers=4, seq_len=256, population_size=40960, device_mask=3),
+    "c5": dict(hidden_dim=1024, n_layers=12, seq_len=512, population_size=262144, device_mask=15),
     "muon_tiny": dict(hidden_dim=128, n_layers=1, seq_len=16, population_size=32, device_mask=15, use_muon=1),
     "muon_small": dict(hidden_dim=256, n_layers=2, seq_len=32, population_size=64, device_mask=3, use_muon=1),
 }

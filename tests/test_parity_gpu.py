@@ -193,3 +193,25 @@ def test_benchmark_config_sample_matches_reference_kernels():
     ctx2.eval_chunk(SEED, 256, 40960 - 64, 64)
     assert (ctx2.read_losses(40960 - 64, 64) == got).all()
     ctx2.close()
+
+
+def test_deggs_scale_config_sample_matches_reference_kernels():
+    """d-eggs-scale shapes (H=1024, 16 heads, L=12, S=512, POP=262144, ternary weight values in the
+    reference int8 layout): a 16-member slice against the reference's own kernels."""
+    if not ref_binary("c5"):
+        pytest.skip("oracle/_ref/ref_mgpu_c5 not built")
+    pkg = load_pkg()
+    from egg_c_b200 import synth
+    kw = REF_CONFIGS["c5"]
+    cfg, ocfg = cfg_pair(**kw)
+    model = synth.random_model(cfg, 0, "ternary")
+    data = synth.zipf_bytes(1, 8 << 20)
+    ctx = _ctx(cfg, wave=16)
+    ctx.upload_model(model)
+    ctx.set_dataset(data)
+    off = 262144 - 16
+    ctx.eval_chunk(SEED, 512, off, 16)
+    got = ctx.read_losses(off, 16)
+    ref = run_ref_mgpu("c5", model, data, SEED, 512, off, 16)
+    assert (got == ref["losses"]).all(), (got[:6], ref["losses"][:6])
+    ctx.close()
