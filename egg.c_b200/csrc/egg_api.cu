@@ -786,7 +786,7 @@ extern "C" int egg_perturbed_projection(egg_ctx *c, const int8_t *x, const int8_
                                         int rows_per_member, uint32_t seed, int off_a, int off_b, int rank1_shift, int out_shift,
                                         int on_device) {
     if (!c || !x || !w_packed || !y) { set_error("null argument"); return EGG_E_INVALID; }
-    if (rows <= 0 || rows > 0x7FFFFF00ll || K % 128 || N % 128 || K <= 0 || N <= 0 || rows_per_member < 8 || rows % (2 * (int64_t)rows_per_member)) {
+    if (rows <= 0 || rows > 0x7FFFFF00ll || K % 128 || N % 128 || K <= 0 || N <= 0 || rows_per_member < 16 || rows % (2 * (int64_t)rows_per_member)) {
         set_error("projection shape unsupported (rows %lld, K %d, N %d, rows/member %d)", (long long)rows, K, N, rows_per_member);
         return EGG_E_INVALID;
     }

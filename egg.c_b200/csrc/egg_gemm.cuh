@@ -21,7 +21,7 @@ constexpr int GEMM_STAGES = 3;
 constexpr int GEMM_THREADS = 576;       // warp0 TMA, warp1 MMA, warps 2..17 epilogue
 constexpr int GEMM_EPI_THREADS = 512;
 constexpr int GEMM_EPI_WARPS = 16;
-constexpr int GEMM_MAX_SLOTS = 9;       // distinct population pairs a 128-row tile can touch (seq_len >= 8)
+constexpr int GEMM_MAX_SLOTS = 5;       // distinct population pairs a 128-row tile can touch (seq_len >= 16)
 
 enum GemmEpi {
     EPI_CLIP8 = 0,   // y = clip((acc + r1) >> out_shift)                       -> int8
@@ -154,7 +154,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     if (warp >= 2) {
         int e = threadIdx.x - 64;
-        if (EPI == EPI_GELU && p.act_lut && e < 256) sm.act_lut[e] = p.act_lut[e];
+        if (EPI == EPI_GELU && p.act_lut && e < 256) sm.act_lut[e] = p.act_lut[e == 0x80 ? 0x81 : e];   // saturating pack yields -128 where the reference clips to -127
         if (EPI == EPI_HEAD && p.exp_lut && e < 256) sm.exp_lut[e] = p.exp_lut[e];
     }
     ptx::tc_fence_before();
@@ -357,31 +357,35 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                             const int4 a4 = *reinterpret_cast<const int4 *>(&st[i * 8 + lrow][4 * pc]);
                             const int sl = slot_sgn[i] >> 1, sg = slot_sgn[i] & 1;
                             const int32_t aw = *reinterpret_cast<const int32_t *>(&sm.a_tab[sl][col]);
-                            int v0 = a4.x + ((xbs[i] * (int)(int8_t)(aw)) >> p.rank1_shift);
-                            int v1 = a4.y + ((xbs[i] * (int)(int8_t)(aw >> 8)) >> p.rank1_shift);
-                            int v2 = a4.z + ((xbs[i] * (int)(int8_t)(aw >> 16)) >> p.rank1_shift);
-                            int v3 = a4.w + ((xbs[i] * (int)(aw >> 24)) >> p.rank1_shift);
+                            const int4 an = make_int4((int)(int8_t)aw, (int)(int8_t)(aw >> 8), (int)(int8_t)(aw >> 16), aw >> 24);
+                            int v0 = a4.x + ((xbs[i] * an.x) >> p.rank1_shift);
+                            int v1 = a4.y + ((xbs[i] * an.y) >> p.rank1_shift);
+                            int v2 = a4.z + ((xbs[i] * an.z) >> p.rank1_shift);
+                            int v3 = a4.w + ((xbs[i] * an.w) >> p.rank1_shift);
                             const int64_t gofs = (int64_t)rrow[i] * p.N + n0 + col;
                             if (EPI == EPI_CLIP8) {
-                                uint32_t w = (uint32_t)(clip8(v0 >> p.out_shift) & 0xFF) | ((uint32_t)(clip8(v1 >> p.out_shift) & 0xFF) << 8) |
-                                             ((uint32_t)(clip8(v2 >> p.out_shift) & 0xFF) << 16) | ((uint32_t)(clip8(v3 >> p.out_shift) & 0xFF) << 24);
+                                // saturate to int8 and pack (two instructions), then lift -128 to the reference's -127
+                                uint32_t w = ptx::pack_sat_s8(v0 >> p.out_shift, v1 >> p.out_shift, v2 >> p.out_shift, v3 >> p.out_shift);
+                                w = __vmaxs4(w, 0x81818181u);
                                 if (rok[i]) *reinterpret_cast<uint32_t *>(p.out8 + gofs) = w;
                             } else if (EPI == EPI_GELU) {
-                                const int2 bc = *reinterpret_cast<const int2 *>(&sm.bc_tab[sl][sg][col]);
-                                const int u0 = sm.act_lut[(uint8_t)(int8_t)clip8((v0 >> p.out_shift) + (int)(int16_t)(bc.x & 0xFFFF))];
-                                const int u1 = sm.act_lut[(uint8_t)(int8_t)clip8((v1 >> p.out_shift) + (bc.x >> 16))];
-                                const int u2 = sm.act_lut[(uint8_t)(int8_t)clip8((v2 >> p.out_shift) + (int)(int16_t)(bc.y & 0xFFFF))];
-                                const int u3 = sm.act_lut[(uint8_t)(int8_t)clip8((v3 >> p.out_shift) + (bc.y >> 16))];
-                                const uint32_t w = (uint32_t)(u0 & 0xFF) | ((uint32_t)(u1 & 0xFF) << 8) | ((uint32_t)(u2 & 0xFF) << 16) | ((uint32_t)(u3 & 0xFF) << 24);
+                                const int2 bcw = *reinterpret_cast<const int2 *>(&sm.bc_tab[sl][sg][col]);
+                                const int4 bc = make_int4((int)(int16_t)(bcw.x & 0xFFFF), bcw.x >> 16, (int)(int16_t)(bcw.y & 0xFFFF), bcw.y >> 16);
+                                const uint32_t z = ptx::pack_sat_s8((v0 >> p.out_shift) + bc.x, (v1 >> p.out_shift) + bc.y,
+                                                                    (v2 >> p.out_shift) + bc.z, (v3 >> p.out_shift) + bc.w);
+                                const uint32_t u0 = (uint8_t)sm.act_lut[z & 0xFF], u1 = (uint8_t)sm.act_lut[(z >> 8) & 0xFF];
+                                const uint32_t u2 = (uint8_t)sm.act_lut[(z >> 16) & 0xFF], u3 = (uint8_t)sm.act_lut[z >> 24];
+                                const uint32_t w = __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
                                 racc[i] = __dp4a((int)w, *reinterpret_cast<const int32_t *>(&sm.d_tab[sl][col]), racc[i]);
                                 if (rok[i]) *reinterpret_cast<uint32_t *>(p.out8 + gofs) = w;
                             } else if (EPI == EPI_PRE32) {
-                                const int2 bc = *reinterpret_cast<const int2 *>(&sm.bc_tab[sl][sg][col]);
+                                const int2 bcw = *reinterpret_cast<const int2 *>(&sm.bc_tab[sl][sg][col]);
+                                const int4 bc = make_int4((int)(int16_t)(bcw.x & 0xFFFF), bcw.x >> 16, (int)(int16_t)(bcw.y & 0xFFFF), bcw.y >> 16);
                                 const int32_t rs = rs_pre[c / 16][i];
-                                v0 = (int)(int8_t)(rs) + (v0 >> p.out_shift) + (int)(int16_t)(bc.x & 0xFFFF);
-                                v1 = (int)(int8_t)(rs >> 8) + (v1 >> p.out_shift) + (bc.x >> 16);
-                                v2 = (int)(int8_t)(rs >> 16) + (v2 >> p.out_shift) + (int)(int16_t)(bc.y & 0xFFFF);
-                                v3 = (int)(rs >> 24) + (v3 >> p.out_shift) + (bc.y >> 16);
+                                v0 = (int)(int8_t)(rs) + (v0 >> p.out_shift) + bc.x;
+                                v1 = (int)(int8_t)(rs >> 8) + (v1 >> p.out_shift) + bc.y;
+                                v2 = (int)(int8_t)(rs >> 16) + (v2 >> p.out_shift) + bc.z;
+                                v3 = (int)(rs >> 24) + (v3 >> p.out_shift) + bc.w;
                                 racc[i] = max(racc[i], max(max(abs(v0), abs(v1)), max(abs(v2), abs(v3))));
                                 if (rok[i]) *reinterpret_cast<int4 *>(p.out32 + gofs) = make_int4(v0, v1, v2, v3);
                             } else if (EPI == EPI_QKV) {
