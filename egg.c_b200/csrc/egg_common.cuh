@@ -72,6 +72,63 @@ inline ModelLayout model_layout(const egg_config &c) {
     return L;
 }
 
+// AdaptiveScales (d-eggs/include/model/definitions.h:92-142): one int8 overlay per input index ("_row")
+// and per output index ("_col") of every matrix and per element of every vector; byte offsets.
+struct ScalesLayout {
+    int64_t embedding_row, embedding_col, emb_bias, ln_init, ln_init_bias, w_emb_mlp_up_row, w_emb_mlp_up_col,
+        mlp_emb_bias_up, w_emb_mlp_down_row, w_emb_mlp_down_col, mlp_emb_bias_down, ln_1, ln_1_bias, w_q_row, w_q_col,
+        w_k_row, w_k_col, w_v_row, w_v_col, w_o_row, w_o_col, ln_2, ln_2_bias, w_up_row, w_up_col, mlp_bias_up,
+        w_down_row, w_down_col, mlp_bias_down, ln_f, ln_f_bias, total;
+};
+
+inline ScalesLayout scales_layout(const egg_config &c) {
+    ScalesLayout S;
+    int64_t H = c.hidden_dim, V = c.vocab_size, NL = c.n_layers, o = 0;
+    S.embedding_row = o;      o += V;
+    S.embedding_col = o;      o += H;
+    S.emb_bias = o;           o += H;
+    S.ln_init = o;            o += H;
+    S.ln_init_bias = o;       o += H;
+    S.w_emb_mlp_up_row = o;   o += H;
+    S.w_emb_mlp_up_col = o;   o += 4 * H;
+    S.mlp_emb_bias_up = o;    o += 4 * H;
+    S.w_emb_mlp_down_row = o; o += 4 * H;
+    S.w_emb_mlp_down_col = o; o += H;
+    S.mlp_emb_bias_down = o;  o += H;
+    S.ln_1 = o;               o += NL * H;
+    S.ln_1_bias = o;          o += NL * H;
+    S.w_q_row = o;            o += NL * H;
+    S.w_q_col = o;            o += NL * H;
+    S.w_k_row = o;            o += NL * H;
+    S.w_k_col = o;            o += NL * H;
+    S.w_v_row = o;            o += NL * H;
+    S.w_v_col = o;            o += NL * H;
+    S.w_o_row = o;            o += NL * H;
+    S.w_o_col = o;            o += NL * H;
+    S.ln_2 = o;               o += NL * H;
+    S.ln_2_bias = o;          o += NL * H;
+    S.w_up_row = o;           o += NL * H;
+    S.w_up_col = o;           o += NL * 4 * H;
+    S.mlp_bias_up = o;        o += NL * 4 * H;
+    S.w_down_row = o;         o += NL * 4 * H;
+    S.w_down_col = o;         o += NL * H;
+    S.mlp_bias_down = o;      o += NL * H;
+    S.ln_f = o;               o += H;
+    S.ln_f_bias = o;          o += H;
+    S.total = o;
+    return S;
+}
+
+// get_adaptive_factor, ADAPTIVE_NOISE_MODE 1 (d-eggs/include/model/layers.cuh:12-19), as the numerator of
+// a fraction over 64: negative overlays switch the noise off, 0..63 scale it by ov/64, larger ones leave it.
+__host__ __device__ __forceinline__ int overlay_num(int ov) { return ov < 0 ? 0 : (ov < 64 ? ov : 64); }
+// (int)(v * (num / 64.0f)) for an integer v with |v * num| < 2^24: the float product is exact, the
+// conversion truncates toward zero.
+__host__ __device__ __forceinline__ int scale_trunc(int v, int num) {
+    const int q = v * num;
+    return (q + ((q >> 31) & 63)) >> 6;
+}
+
 // One trainable parameter of the update sequence (mgpu.cu:1603-1643).
 struct ParamDesc {
     int64_t model_off;   // element offset in TransformerModel
@@ -82,6 +139,7 @@ struct ParamDesc {
     float lr_scale;
     int muon;            // state is MuonParam{m,acc} and the step is Muon
     int64_t shadow_off;  // element offset of the K-major shadow copy (-1: none)
+    int64_t ov_in, ov_out;   // AdaptiveScales offsets of the overlays over the input index (or the vector) and the output index
 };
 
 // ---------------------------------------------------------------- errors

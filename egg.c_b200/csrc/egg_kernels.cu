@@ -15,41 +15,56 @@ namespace egg {
 void build_noise_map(const egg_config &c, NoiseMap *map, NoiseSeg *segs, int *nsegs, int max_segs) {
     const int H = c.hidden_dim, V = c.vocab_size;
     const int ssv = c.sigma_shift_vector;
+    const ScalesLayout SL = scales_layout(c);
     int n = 0, off = 0;
-    auto plain = [&](int len, int seed) { int o = off; if (n < max_segs) { segs[n] = NoiseSeg{off, len, 0, seed, 0, 0}; segs[n].model_off = -1; } n++; off += len; return o; };
-    auto delta = [&](int len, int sa, int sb) { int o = off; if (n < max_segs) { segs[n] = NoiseSeg{off, len, 1, sa, sb, ssv}; segs[n].model_off = -1; } n++; off += 2 * len; return o; };
-    // kind 2: model byte + delta, both signs, as int16 [2][len] (4*len bytes); mw/mb = element offsets in TransformerModel
-    auto comb = [&](int len, int sa, int sb, int64_t moff) { int o = off; if (n < max_segs) { segs[n] = NoiseSeg{off, len, 2, sa, sb, ssv}; segs[n].model_off = moff; } n++; off += 4 * len; return o; };
-    auto norm = [&](int base, int wa, int wb, int ba, int bb, int64_t mw, int64_t mb) { NormOff r; r.w_m = comb(H, base + wa, base + wb, mw); r.b_m = comb(H, base + ba, base + bb, mb); return r; };
-    auto mlp = [&](int base, int up_a, int up_b, int bu_a, int bu_b, int dn_a, int dn_b, int bd_a, int bd_b) {
+    // sc = AdaptiveScales offset of the overlay that scales the segment (-1: the segment holds raw noise)
+    auto put = [&](int kind, int len, int sa, int sb, int shift, int64_t moff, int64_t sc, int bytes) {
+        int o = off;
+        if (n < max_segs) { segs[n] = NoiseSeg{off, len, kind, sa, sb, shift, moff, sc}; }
+        n++; off += bytes; return o;
+    };
+    auto plain = [&](int len, int seed, int64_t sc) { return put(0, len, seed, 0, 0, -1, sc, len); };
+    auto delta = [&](int len, int sa, int sb, int64_t sc) { return put(1, len, sa, sb, ssv, -1, sc, 2 * len); };
+    // kind 2: model byte + delta, both signs, as int16 [2][len] (4*len bytes); moff = element offset in TransformerModel
+    auto comb = [&](int len, int sa, int sb, int64_t moff, int64_t sc) { return put(2, len, sa, sb, ssv, moff, sc, 4 * len); };
+    auto norm = [&](int base, int wa, int wb, int ba, int bb, int64_t mw, int64_t mb, int64_t sw, int64_t sbias) {
+        NormOff r; r.w_m = comb(H, base + wa, base + wb, mw, sw); r.b_m = comb(H, base + ba, base + bb, mb, sbias); return r;
+    };
+    auto mlp = [&](int base, int up_a, int up_b, int bu_a, int bu_b, int dn_a, int dn_b, int bd_a, int bd_b, int64_t s_up_col,
+                   int64_t s_bup, int64_t s_dn_col, int64_t s_bdn) {
         MlpOff r;
-        r.up_b = plain(H, base + up_b);
-        r.up_a = plain(4 * H, base + up_a);
-        r.bup_d = delta(4 * H, base + bu_a, base + bu_b);
-        r.dn_b = plain(4 * H, base + dn_b);
-        r.dn_a = plain(H, base + dn_a);
-        r.bdn_d = delta(H, base + bd_a, base + bd_b);
+        r.up_b = plain(H, base + up_b, -1);
+        r.up_a = plain(4 * H, base + up_a, s_up_col);
+        r.bup_d = delta(4 * H, base + bu_a, base + bu_b, s_bup);
+        r.dn_b = plain(4 * H, base + dn_b, -1);
+        r.dn_a = plain(H, base + dn_a, s_dn_col);
+        r.bdn_d = delta(H, base + bd_a, base + bd_b, s_bdn);
         return r;
     };
-    // seed offsets: mgpu.cu:114-165
-    map->emb_a = plain(V, 0);
-    map->emb_b = plain(H, 0 + H);
-    map->emb_bias_d = delta(H, 50, 51);
+    // seed offsets: mgpu.cu:114-165.  Vectors that feed a row dot (the "B" side) stay raw: their overlay is
+    // applied per term of the dot.  emb_a is read raw by the embedding and scaled (head_a) by the head.
+    map->emb_a = plain(V, 0, -1);
+    map->head_a = plain(V, 0, SL.embedding_row);
+    map->emb_b = plain(H, 0 + H, -1);
+    map->emb_bias_d = delta(H, 50, 51, SL.emb_bias);
     const ModelLayout ML = model_layout(c);
-    map->ln_init = norm(0, 500, 501, 502, 503, ML.ln_init, ML.ln_init_bias);
-    map->ln_f = norm(0, 900, 901, 910, 911, ML.ln_f, ML.ln_f_bias);
-    map->mlp_init = mlp(0, 510, 511, 514, 515, 512, 513, 516, 517);
+    map->ln_init = norm(0, 500, 501, 502, 503, ML.ln_init, ML.ln_init_bias, SL.ln_init, SL.ln_init_bias);
+    map->ln_f = norm(0, 900, 901, 910, 911, ML.ln_f, ML.ln_f_bias, SL.ln_f, SL.ln_f_bias);
+    map->mlp_init = mlp(0, 510, 511, 514, 515, 512, 513, 516, 517, SL.w_emb_mlp_up_col, SL.mlp_emb_bias_up, SL.w_emb_mlp_down_col,
+                        SL.mlp_emb_bias_down);
     map->layer0 = off;
     for (int l = 0; l < c.n_layers; l++) {
         int base = l * 1000, start = off;
+        const int64_t lH = (int64_t)l * H;
         LayerOff lo;
-        lo.ln1 = norm(base, 100, 101, 110, 111, ML.ln_1 + (int64_t)l * H, ML.ln_1_bias + (int64_t)l * H);
-        lo.qkv_b = plain(H, base + 201); plain(H, base + 203); plain(H, base + 205);
-        lo.qkv_a = plain(H, base + 200); plain(H, base + 202); plain(H, base + 204);
-        lo.o_b = plain(H, base + 207);
-        lo.o_a = plain(H, base + 206);
-        lo.ln2 = norm(base, 300, 301, 310, 311, ML.ln_2 + (int64_t)l * H, ML.ln_2_bias + (int64_t)l * H);
-        lo.mlp = mlp(base, 400, 401, 410, 411, 402, 403, 412, 413);
+        lo.ln1 = norm(base, 100, 101, 110, 111, ML.ln_1 + lH, ML.ln_1_bias + lH, SL.ln_1 + lH, SL.ln_1_bias + lH);
+        lo.qkv_b = plain(H, base + 201, -1); plain(H, base + 203, -1); plain(H, base + 205, -1);
+        lo.qkv_a = plain(H, base + 200, SL.w_q_col + lH); plain(H, base + 202, SL.w_k_col + lH); plain(H, base + 204, SL.w_v_col + lH);
+        lo.o_b = plain(H, base + 207, -1);
+        lo.o_a = plain(H, base + 206, SL.w_o_col + lH);
+        lo.ln2 = norm(base, 300, 301, 310, 311, ML.ln_2 + lH, ML.ln_2_bias + lH, SL.ln_2 + lH, SL.ln_2_bias + lH);
+        lo.mlp = mlp(base, 400, 401, 410, 411, 402, 403, 412, 413, SL.w_up_col + 4 * lH, SL.mlp_bias_up + 4 * lH, SL.w_down_col + lH,
+                     SL.mlp_bias_down + lH);
         if (l == 0) {
             map->layer_stride = off - start;
             LayerOff rel = lo;
@@ -62,8 +77,11 @@ void build_noise_map(const egg_config &c, NoiseMap *map, NoiseSeg *segs, int *ns
     *nsegs = n;
 }
 
+// scales: AdaptiveScales bytes or null.  With scales, every segment that has an overlay holds
+// (int)(noise * factor) (A vectors, layers.cuh:90) or the delta built from (int)(n1 * n2 * factor)
+// (vectors, layers.cuh:176-180), so that the consumers of the table need not know about overlays.
 __global__ void noise_fill_kernel(int8_t *nt, int64_t stride, const NoiseSeg *segs, int nsegs, uint32_t step_seed,
-                                  int pair_base, int mask, int gaussian, const int8_t *model) {
+                                  int pair_base, int mask, int gaussian, const int8_t *model, const int8_t *scales) {
     extern __shared__ NoiseSeg s_segs[];
     for (int i = threadIdx.x; i < nsegs; i += blockDim.x) s_segs[i] = segs[i];
     __syncthreads();
@@ -75,15 +93,20 @@ __global__ void noise_fill_kernel(int8_t *nt, int64_t stride, const NoiseSeg *se
         int lo = 0, hi = nsegs - 1;
         while (lo < hi) { int mid = (lo + hi + 1) >> 1; if (s_segs[mid].off <= o) lo = mid; else hi = mid - 1; }
         const NoiseSeg sg = s_segs[lo];
+        const bool scaled = scales != nullptr && sg.scale_off >= 0;
         int rel = o - sg.off, val = 0;
         if (sg.kind == 0) {
-            if (rel < sg.len) val = noise_from_hash(S0 + (uint32_t)sg.seed_a, (uint32_t)rel, mask, gaussian);
+            if (rel < sg.len) {
+                val = noise_from_hash(S0 + (uint32_t)sg.seed_a, (uint32_t)rel, mask, gaussian);
+                if (scaled) val = scale_trunc(val, overlay_num(scales[sg.scale_off + rel]));
+            }
             dst[o] = (int8_t)val;
         } else if (sg.kind == 1) {
             if (rel < 2 * sg.len) {
                 int neg = rel >= sg.len, i = neg ? rel - sg.len : rel;
                 int prod = noise_from_hash(S0 + (uint32_t)sg.seed_a, (uint32_t)i, mask, gaussian) *
                            noise_from_hash(S0 + (uint32_t)sg.seed_b, (uint32_t)i, mask, gaussian);
+                if (scaled) prod = scale_trunc(prod, overlay_num(scales[sg.scale_off + i]));
                 val = (neg ? -prod : prod) >> sg.shift;
             }
             dst[o] = (int8_t)val;
@@ -94,6 +117,7 @@ __global__ void noise_fill_kernel(int8_t *nt, int64_t stride, const NoiseSeg *se
                 int neg = e >= sg.len, i = neg ? e - sg.len : e;
                 int prod = noise_from_hash(S0 + (uint32_t)sg.seed_a, (uint32_t)i, mask, gaussian) *
                            noise_from_hash(S0 + (uint32_t)sg.seed_b, (uint32_t)i, mask, gaussian);
+                if (scaled) prod = scale_trunc(prod, overlay_num(scales[sg.scale_off + i]));
                 val = (int)model[sg.model_off + i] + ((neg ? -prod : prod) >> sg.shift);
                 *reinterpret_cast<int16_t *>(dst + o) = (int16_t)val;
             } else {
@@ -104,10 +128,10 @@ __global__ void noise_fill_kernel(int8_t *nt, int64_t stride, const NoiseSeg *se
 }
 
 int launch_noise_fill(cudaStream_t st, int8_t *nt, int64_t stride, const NoiseSeg *d_segs, int nsegs, int n_pairs,
-                      uint32_t step_seed, int pair_base, int mask, int gaussian, const int8_t *model) {
+                      uint32_t step_seed, int pair_base, int mask, int gaussian, const int8_t *model, const int8_t *scales) {
     int gx = (int)((stride + 255) / 256); if (gx > 64) gx = 64;
     dim3 grid((unsigned)gx, (unsigned)n_pairs);
-    noise_fill_kernel<<<grid, 256, nsegs * sizeof(NoiseSeg), st>>>(nt, stride, d_segs, nsegs, step_seed, pair_base, mask, gaussian, model);
+    noise_fill_kernel<<<grid, 256, nsegs * sizeof(NoiseSeg), st>>>(nt, stride, d_segs, nsegs, step_seed, pair_base, mask, gaussian, model, scales);
     EGG_CUDA(cudaGetLastError());
     return EGG_OK;
 }

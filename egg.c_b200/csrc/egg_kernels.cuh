@@ -18,6 +18,7 @@ struct NoiseSeg {
     int seed_a, seed_b;
     int shift;
     int64_t model_off;
+    int64_t scale_off;   // AdaptiveScales offset of the overlay scaling this segment (-1: raw noise)
 };
 
 struct NormOff { int w_m, b_m; };                       // perturbed gain / bias, int16 [2][H] each
@@ -27,6 +28,7 @@ struct LayerOff { NormOff ln1; int qkv_b; int qkv_a; int o_b, o_a; NormOff ln2; 
 struct NoiseMap {
     int64_t stride;          // bytes per pair (multiple of 16)
     int emb_a, emb_b, emb_bias_d;
+    int head_a;              // emb_a scaled by the embedding_row overlay (equal to emb_a without overlays)
     NormOff ln_init, ln_f;
     MlpOff mlp_init;
     int layer0, layer_stride;   // byte offset of layer 0 block, bytes per layer block
@@ -37,7 +39,7 @@ struct NoiseMap {
 void build_noise_map(const egg_config &c, NoiseMap *map, NoiseSeg *segs, int *nsegs, int max_segs);
 
 int launch_noise_fill(cudaStream_t st, int8_t *nt, int64_t stride, const NoiseSeg *d_segs, int nsegs, int n_pairs,
-                      uint32_t step_seed, int pair_base, int mask, int gaussian, const int8_t *model);
+                      uint32_t step_seed, int pair_base, int mask, int gaussian, const int8_t *model, const int8_t *scales);
 
 // ---- row-wise kernels -------------------------------------------------------
 struct RowParams {

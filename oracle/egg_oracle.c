@@ -295,6 +295,24 @@ static int32_t noise_dot(const eval_env *E, const int8_t *in, int K, uint32_t se
     return s;
 }
 
+/* The down projection's dot (layers.cuh:272-280): thread tid adds its four terms tid, tid+H, tid+2H, tid+3H
+ * into an int32 with `pb += int * int8 * float`, i.e. pb = (int32)((float)pb + product) after every term, so
+ * the truncation applies to the running sum of the thread, not to the term; the threads' sums are then added. */
+static int32_t noise_dot_down(const eval_env *E, const int8_t *in, int H, uint32_t seed, int64_t sc_off) {
+    if (!E->scales || sc_off < 0) return noise_dot(E, in, 4 * H, seed, sc_off);
+    int32_t s = 0;
+    for (int tid = 0; tid < H; tid++) {
+        int32_t pb = 0;
+        for (int sub = 0; sub < 4; sub++) {
+            int k = tid + sub * H;
+            int32_t prod = (int32_t)in[k] * oracle_noise(E->c, seed, (uint32_t)k);
+            pb = (int32_t)((float)pb + (float)prod * adaptive_factor(E, sc_off, k));
+        }
+        s += pb;
+    }
+    return s;
+}
+
 /* vector ("universal rank-1") noise: ((n1*n2*f)*ns) >> SSV  (mgpu.cu:668-674) */
 static inline int32_t vec_noise(const eval_env *E, uint32_t seed_base, int off_a, int off_b, int idx,
                                 int ns, int64_t sc_off) {
@@ -392,7 +410,7 @@ static void mlp_block(const eval_env *E, int l, int8_t *x, uint32_t seed_base, i
         int32_t nv = vec_noise(E, seed_base, cfg->off_bias_up_a, cfg->off_bias_up_b, o, ns, sc_up_b);
         u[o] = E->act_lut[(uint8_t)(int8_t)clip8((a >> c->shift_mlp_up) + up_b[o] + nv)];
     }
-    int32_t sb2 = noise_dot(E, u, 4 * H, seed_base + (uint32_t)cfg->off_dn_b, sc_dn_row);
+    int32_t sb2 = noise_dot_down(E, u, H, seed_base + (uint32_t)cfg->off_dn_b, sc_dn_row);
     for (int d = 0; d < H; d++) {
         int32_t a = linear_projection(E, u, dn_w, 4 * H, H, d, sb2, seed_base + (uint32_t)cfg->off_dn_a, ns,
                                       adaptive_factor(E, sc_dn_col, d));

@@ -47,6 +47,14 @@ REF_CONFIGS = {
 }
 
 
+# configurations of the d-eggs harness binaries (oracle/_ref/ref_deggs_<tag>); population = 8 * POPULATION_BATCH_SIZE
+DEGGS_CONFIGS = {
+    "tiny": dict(hidden_dim=128, n_layers=1, seq_len=16, population_size=128, device_mask=15, chunk_relative_loss=1),
+    "small": dict(hidden_dim=256, n_layers=2, seq_len=32, population_size=256, device_mask=3, chunk_relative_loss=1),
+}
+DEGGS_CHUNK = {"tiny": 32, "small": 64}
+
+
 def cfg_pair(**kw):
     """(library config, oracle config) with identical fields."""
     pkg, orc = load_pkg(), load_oracle()
@@ -88,6 +96,48 @@ def run_ref_mgpu(tag, model, dataset, step_seed, start_idx, pop_offset, count, l
         out["model"] = np.frombuffer(raw, np.int8, sizes["model_bytes"], o).copy(); o += sizes["model_bytes"]
         out["opt"] = np.frombuffer(raw, np.uint8, sizes["opt_bytes"], o).copy()
     return out
+
+
+def deggs_binary(tag):
+    p = os.path.join(ROOT, "oracle", "_ref", "ref_deggs_" + tag)
+    return p if os.path.exists(p) else None
+
+
+def run_ref_deggs(tag, model, opt_state, scales, dataset, seed, step, generations, lr):
+    """Runs the d-eggs worker's own kernels (oracle/_ref/ref_deggs_<tag>) for some generations on the visible GPU."""
+    exe = deggs_binary(tag)
+    assert exe, "d-eggs harness %s not built" % tag
+    sizes = json.loads(subprocess.run([exe, "--sizes"], check=True, capture_output=True, text=True).stdout)
+    kw = DEGGS_CONFIGS[tag]
+    with tempfile.TemporaryDirectory() as td:
+        fin, fout = os.path.join(td, "in.bin"), os.path.join(td, "out.bin")
+        with open(fin, "wb") as f:
+            f.write(struct.pack("<IIqqif", 0x53474745, seed & 0xFFFFFFFF, step, len(dataset), generations, lr))
+            f.write(struct.pack("<6i", kw["hidden_dim"], kw["n_layers"], kw["seq_len"], kw["population_size"], kw["device_mask"],
+                                DEGGS_CHUNK[tag]))
+            f.write(np.ascontiguousarray(model, np.int8).tobytes())
+            f.write(np.ascontiguousarray(opt_state, np.uint8).tobytes())
+            f.write(np.ascontiguousarray(scales, np.int8).tobytes())
+            f.write(np.ascontiguousarray(dataset, np.uint8).tobytes())
+        r = subprocess.run([exe, fin, fout], capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout + r.stderr
+        raw = open(fout, "rb").read()
+    pop, sb = sizes["population_size"], sizes["scales_bytes"]
+    out = {"sizes": sizes, "losses": [], "updates": [], "scales": []}
+    o = 0
+    for _ in range(generations):
+        out["losses"].append(np.frombuffer(raw, np.int32, pop, o).copy()); o += 4 * pop
+        out["updates"].append(struct.unpack_from("<Q", raw, o)[0]); o += 8
+        out["scales"].append(np.frombuffer(raw, np.int8, sb, o).copy()); o += sb
+    out["model"] = np.frombuffer(raw, np.int8, sizes["model_bytes"], o).copy(); o += sizes["model_bytes"]
+    out["opt"] = np.frombuffer(raw, np.uint8, sizes["opt_bytes"], o).copy()
+    return out
+
+
+def deggs_initial_scales(n, seed=7):
+    """Overlay bytes covering every branch of the factor: negative (0), 0..63 (ov/64) and >= 64 (1)."""
+    rng = np.random.RandomState(seed)
+    return rng.randint(-12, 100, size=n).astype(np.int8)
 
 
 def make_case(kw, data_len=200000, data_seed=1, model_seed=0, model_kind="init"):

@@ -4,6 +4,8 @@
                                                reference's egg_math.h / ternary_pack.h)
   python tests/golden/make_golden.py mgpu     (on a B200: runs oracle/_ref/ref_mgpu_*, the
                                                reference's own kernels, on seeded cases)
+  python tests/golden/make_golden.py deggs    (on a B200: runs oracle/_ref/ref_deggs_*, the d-eggs
+                                               worker's kernels with adaptive-noise overlays)
 """
 import json
 import os
@@ -59,8 +61,40 @@ def mgpu(outdir):
         print("wrote", tag, "updates", ups, "changed", len(changed))
 
 
+DEGGS_GENS = 6
+DEGGS_SEED = 42
+DEGGS_LR = 0.5
+
+
+def deggs(outdir):
+    """Six generations of the d-eggs worker's kernels per configuration, starting from seeded overlays;
+    the seed follows the worker's chain seed = hash_rng(seed, step + 1)."""
+    import zlib
+    from common import DEGGS_CONFIGS, deggs_initial_scales, load_oracle, make_case, run_ref_deggs
+    O = load_oracle()
+    os.makedirs(outdir, exist_ok=True)
+    for tag in ("tiny", "small"):
+        kw = DEGGS_CONFIGS[tag]
+        cfg, ocfg, model0, data = make_case(kw, data_len=50000)
+        opt0 = np.zeros(O.opt_bytes(ocfg), np.uint8)
+        scales0 = deggs_initial_scales(O.scales_bytes(ocfg))
+        r = run_ref_deggs(tag, model0, opt0, scales0, data, DEGGS_SEED, 0, DEGGS_GENS, DEGGS_LR)
+        assert r["sizes"]["model_bytes"] == len(model0) and r["sizes"]["scales_bytes"] == len(scales0)
+        model, opt = r["model"], r["opt"]
+        changed = np.nonzero(model != model0)[0]
+        np.savez_compressed(os.path.join(outdir, "ref_deggs_%s.npz" % tag), losses=np.array(r["losses"]),
+                            updates=np.array(r["updates"], np.uint64), scales_final=r["scales"][-1],
+                            scales_crc=np.array([zlib.crc32(x.tobytes()) for x in r["scales"]], np.uint32),
+                            changed_count=np.int64(len(changed)), changed_idx=changed[:2048].astype(np.int64),
+                            changed_val=model[changed[:2048]], model_crc=np.uint32(zlib.crc32(model.tobytes())),
+                            opt_crc=np.uint32(zlib.crc32(opt.tobytes())), sizes=json.dumps(r["sizes"]))
+        print("wrote", tag, "updates", r["updates"], "changed", len(changed))
+
+
 if __name__ == "__main__":
     if sys.argv[1] == "kat":
         kat()
+    elif sys.argv[1] == "deggs":
+        deggs(sys.argv[2] if len(sys.argv) > 2 else os.path.join(ROOT, "gpurun_out", "golden"))
     else:
         mgpu(sys.argv[2] if len(sys.argv) > 2 else os.path.join(ROOT, "gpurun_out", "golden"))
