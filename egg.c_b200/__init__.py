@@ -21,12 +21,12 @@ EXPORTS = [
     "egg_download_opt_state", "egg_set_dataset", "egg_eval_chunk", "egg_read_losses", "egg_compute_fitness_pairs",
     "egg_write_fitness", "egg_read_fitness", "egg_nccl_unique_id", "egg_comm_init", "egg_allgather_fitness",
     "egg_apply_update", "egg_generation_host", "egg_perturbed_projection", "egg_update_reconstruct",
-    "egg_update_reconstruct_noalloc",
+    "egg_update_reconstruct_noalloc", "egg_scales_bytes", "egg_upload_scales", "egg_download_scales", "egg_set_overlay_steps",
     "egg_timer_start", "egg_timer_stop", "egg_profile_enable", "egg_profile_read", "egg_profile_name", "egg_launch_count",
     "egg_wave_members", "egg_wire_fixed_bytes", "egg_wire_encode", "egg_wire_decode_header", "egg_wire_decode_body",
     "egg_ternary_packed_size", "egg_ternary_pack", "egg_ternary_unpack", "egg_deggs_chunk_fitness", "egg_next_seed",
 ]
-EGG_PROF_N = 14
+EGG_PROF_N = 15
 
 
 class EggConfig(C.Structure):
@@ -82,12 +82,16 @@ def lib():
         L.egg_model_bytes.restype = C.c_int64
         L.egg_opt_state_bytes.argtypes = [cfgp]
         L.egg_opt_state_bytes.restype = C.c_int64
+        L.egg_scales_bytes.argtypes = [cfgp]
+        L.egg_scales_bytes.restype = C.c_int64
+        L.egg_set_overlay_steps.argtypes = [C.c_void_p, C.c_int, C.c_int]
         L.egg_ctx_create.argtypes = [cfgp, C.c_int, C.c_int, P(vp)]
         L.egg_ctx_destroy.argtypes = [vp]
         L.egg_ctx_destroy.restype = None
         L.egg_last_error.restype = C.c_char_p
         L.egg_sync.argtypes = [vp]
-        for f in (L.egg_upload_model, L.egg_download_model, L.egg_upload_opt_state, L.egg_download_opt_state, L.egg_set_dataset):
+        for f in (L.egg_upload_model, L.egg_download_model, L.egg_upload_opt_state, L.egg_download_opt_state, L.egg_set_dataset,
+                  L.egg_upload_scales, L.egg_download_scales):
             f.argtypes = [vp, vp, C.c_int64]
         L.egg_eval_chunk.argtypes = [vp, C.c_uint32, C.c_int64, C.c_int, C.c_int]
         L.egg_read_losses.argtypes = [vp, vp, C.c_int, C.c_int]
@@ -152,6 +156,10 @@ def opt_state_bytes(cfg):
     return lib().egg_opt_state_bytes(C.byref(cfg))
 
 
+def scales_bytes(cfg):
+    return lib().egg_scales_bytes(C.byref(cfg))
+
+
 def _ptr(a):
     if a is None:
         return None
@@ -199,6 +207,22 @@ class Context:
         out = np.zeros(opt_state_bytes(self.cfg), np.uint8)
         _check(lib().egg_download_opt_state(self._h, _ptr(out), out.nbytes))
         return out
+
+    def upload_scales(self, scales):
+        """AdaptiveScales bytes (d-eggs adaptive-noise overlays); None switches back to unscaled noise."""
+        if scales is None:
+            _check(lib().egg_upload_scales(self._h, None, 0))
+            return
+        scales = np.ascontiguousarray(scales, np.int8)
+        _check(lib().egg_upload_scales(self._h, _ptr(scales), scales.nbytes))
+
+    def download_scales(self):
+        out = np.zeros(scales_bytes(self.cfg), np.int8)
+        _check(lib().egg_download_scales(self._h, _ptr(out), out.nbytes))
+        return out
+
+    def set_overlay_steps(self, inc, dec):
+        _check(lib().egg_set_overlay_steps(self._h, inc, dec))
 
     def set_dataset(self, tokens):
         tokens = np.ascontiguousarray(tokens, np.uint8)

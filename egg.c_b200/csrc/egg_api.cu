@@ -71,6 +71,12 @@ struct egg_ctx {
     ShadowOff so;
     std::vector<ParamDesc> params;
     bool have_model = false;
+    // adaptive-noise overlays (d-eggs): null until uploaded
+    ScalesLayout SL;
+    int8_t *d_scales = nullptr;
+    bool scales_on = false;
+    uint8_t *d_ch_in = nullptr, *d_ch_out = nullptr;
+    int ov_inc = 5, ov_dec = 1;
     // tables
     int32_t *d_exp_lut = nullptr, *d_rope_lut = nullptr;
     int8_t *d_act_lut = nullptr;
@@ -192,41 +198,45 @@ static void build_params(const egg_config &c, const ModelLayout &L, const Shadow
             }
         return (int64_t)-1;
     };
-    auto mat = [&](int64_t off, int rows, int cols, int a, int b, int base, int hidden, int64_t shadow) {
+    const ScalesLayout S = scales_layout(c);
+    // ov_in / ov_out: overlays over the input index k ("_row") and the output index n ("_col") as the worker passes
+    // them (worker.cu:465-517); for the embedding these are embedding_col / embedding_row (worker.cu:499-519)
+    auto mat = [&](int64_t off, int rows, int cols, int a, int b, int base, int hidden, int64_t shadow, int64_t ov_in, int64_t ov_out) {
         ParamDesc d; d.model_off = off; d.opt_off = opt_of(off, nullptr); d.rows_k = rows; d.cols_n = cols; d.off_a = a; d.off_b = b;
-        d.seed_base = base; d.lr_scale = 1.0f; d.muon = hidden && c.use_muon; d.shadow_off = shadow; out.push_back(d);
+        d.seed_base = base; d.lr_scale = 1.0f; d.muon = hidden && c.use_muon; d.shadow_off = shadow; d.ov_in = ov_in; d.ov_out = ov_out;
+        out.push_back(d);
     };
-    auto vec = [&](int64_t off, int len, int a, int b, int base, float sc) {
+    auto vec = [&](int64_t off, int len, int a, int b, int base, float sc, int64_t ov) {
         ParamDesc d; d.model_off = off; d.opt_off = opt_of(off, nullptr); d.rows_k = 0; d.cols_n = len; d.off_a = a; d.off_b = b;
-        d.seed_base = base; d.lr_scale = sc; d.muon = 0; d.shadow_off = -1; out.push_back(d);
+        d.seed_base = base; d.lr_scale = sc; d.muon = 0; d.shadow_off = -1; d.ov_in = ov; d.ov_out = -1; out.push_back(d);
     };
     const int h = (int)H;
     for (int l = 0; l < c.n_layers; l++) {     // mgpu.cu:1603-1621
         int sb = l * 1000;
-        int64_t hh = H * H, sl = so.layer0 + l * so.layer_stride;
-        mat(L.w_q + l * hh, h, h, 200, 201, sb, 1, sl + so.qkv);
-        mat(L.w_k + l * hh, h, h, 202, 203, sb, 1, sl + so.qkv + hh);
-        mat(L.w_v + l * hh, h, h, 204, 205, sb, 1, sl + so.qkv + 2 * hh);
-        mat(L.w_o + l * hh, h, h, 206, 207, sb, 1, sl + so.o);
-        mat(L.w_up + l * 4 * hh, h, 4 * h, 400, 401, sb, 1, sl + so.up);
-        mat(L.w_down + l * 4 * hh, 4 * h, h, 402, 403, sb, 1, sl + so.dn);
-        vec(L.ln_1 + l * H, h, 100, 101, sb, 1.0f);
-        vec(L.ln_1_bias + l * H, h, 110, 111, sb, 1.0f);
-        vec(L.ln_2 + l * H, h, 300, 301, sb, 1.0f);
-        vec(L.ln_2_bias + l * H, h, 310, 311, sb, 1.0f);
-        vec(L.mlp_bias_up + l * 4 * H, 4 * h, 410, 411, sb, 1.0f);
-        vec(L.mlp_bias_down + l * H, h, 412, 413, sb, 1.0f);
+        int64_t hh = H * H, sl = so.layer0 + l * so.layer_stride, lH = l * H;
+        mat(L.w_q + l * hh, h, h, 200, 201, sb, 1, sl + so.qkv, S.w_q_row + lH, S.w_q_col + lH);
+        mat(L.w_k + l * hh, h, h, 202, 203, sb, 1, sl + so.qkv + hh, S.w_k_row + lH, S.w_k_col + lH);
+        mat(L.w_v + l * hh, h, h, 204, 205, sb, 1, sl + so.qkv + 2 * hh, S.w_v_row + lH, S.w_v_col + lH);
+        mat(L.w_o + l * hh, h, h, 206, 207, sb, 1, sl + so.o, S.w_o_row + lH, S.w_o_col + lH);
+        mat(L.w_up + l * 4 * hh, h, 4 * h, 400, 401, sb, 1, sl + so.up, S.w_up_row + lH, S.w_up_col + 4 * lH);
+        mat(L.w_down + l * 4 * hh, 4 * h, h, 402, 403, sb, 1, sl + so.dn, S.w_down_row + 4 * lH, S.w_down_col + lH);
+        vec(L.ln_1 + l * H, h, 100, 101, sb, 1.0f, S.ln_1 + lH);
+        vec(L.ln_1_bias + l * H, h, 110, 111, sb, 1.0f, S.ln_1_bias + lH);
+        vec(L.ln_2 + l * H, h, 300, 301, sb, 1.0f, S.ln_2 + lH);
+        vec(L.ln_2_bias + l * H, h, 310, 311, sb, 1.0f, S.ln_2_bias + lH);
+        vec(L.mlp_bias_up + l * 4 * H, 4 * h, 410, 411, sb, 1.0f, S.mlp_bias_up + 4 * lH);
+        vec(L.mlp_bias_down + l * H, h, 412, 413, sb, 1.0f, S.mlp_bias_down + lH);
     }
-    vec(L.ln_f, h, 900, 901, 0, 1.0f);             // mgpu.cu:1623-1643
-    vec(L.ln_f_bias, h, 910, 911, 0, 1.0f);
-    vec(L.ln_init, h, 500, 501, 0, 1.0f);
-    vec(L.ln_init_bias, h, 502, 503, 0, 1.0f);
-    mat(L.w_emb_mlp_up, h, 4 * h, 510, 511, 0, 1, so.init_up);
-    vec(L.mlp_emb_bias_up, 4 * h, 514, 515, 0, 1.0f);
-    mat(L.w_emb_mlp_down, 4 * h, h, 512, 513, 0, 1, so.init_dn);
-    vec(L.mlp_emb_bias_down, h, 516, 517, 0, 1.0f);
-    vec(L.emb_bias, h, 50, 51, 0, 0.1f);
-    mat(L.embedding, h, (int)V, 0, 0 + h, 0, 0, so.emb);
+    vec(L.ln_f, h, 900, 901, 0, 1.0f, S.ln_f);             // mgpu.cu:1623-1643
+    vec(L.ln_f_bias, h, 910, 911, 0, 1.0f, S.ln_f_bias);
+    vec(L.ln_init, h, 500, 501, 0, 1.0f, S.ln_init);
+    vec(L.ln_init_bias, h, 502, 503, 0, 1.0f, S.ln_init_bias);
+    mat(L.w_emb_mlp_up, h, 4 * h, 510, 511, 0, 1, so.init_up, S.w_emb_mlp_up_row, S.w_emb_mlp_up_col);
+    vec(L.mlp_emb_bias_up, 4 * h, 514, 515, 0, 1.0f, S.mlp_emb_bias_up);
+    mat(L.w_emb_mlp_down, 4 * h, h, 512, 513, 0, 1, so.init_dn, S.w_emb_mlp_down_row, S.w_emb_mlp_down_col);
+    vec(L.mlp_emb_bias_down, h, 516, 517, 0, 1.0f, S.mlp_emb_bias_down);
+    vec(L.emb_bias, h, 50, 51, 0, 0.1f, S.emb_bias);
+    mat(L.embedding, h, (int)V, 0, 0 + h, 0, 0, so.emb, S.embedding_col, S.embedding_row);
 }
 
 static ShadowOff shadow_offsets(const egg_config &c, int64_t *total) {
@@ -294,7 +304,7 @@ extern "C" void egg_ctx_destroy(egg_ctx *c) {
     void *ptrs[] = {c->d_model, c->d_opt, c->d_shadow, c->d_exp_lut, c->d_rope_lut, c->d_act_lut, c->d_data, c->d_loss, c->d_fit,
                     c->d_x, c->d_h, c->d_u, c->d_q, c->d_k, c->d_v, c->d_ao, c->d_pre, c->d_xb, c->d_xb2, c->d_rowmax,
                     c->d_rowmax3, c->d_xbo, c->d_wave_loss, c->d_segs, c->d_nt, c->d_na, c->d_nb, c->muon.x, c->muon.g,
-                    c->muon.y, c->muon.norm2, c->d_updates, c->d_err};
+                    c->muon.y, c->muon.norm2, c->d_updates, c->d_err, c->d_scales, c->d_ch_in, c->d_ch_out};
     for (void *p : ptrs) if (p) cudaFree(p);
     for (cudaEvent_t e : c->prof_ev) cudaEventDestroy(e);
     if (c->t0) cudaEventDestroy(c->t0);
@@ -345,6 +355,15 @@ extern "C" int egg_ctx_create(const egg_config *cfg, int device, int wave_member
     TRYC(cudaMemset(c->d_loss, 0, (size_t)POP * 4)); TRYC(cudaMemset(c->d_fit, 0, (size_t)(POP / 2) * 4));
     TRY(dev_alloc(&c->d_updates, 1)); TRY(dev_alloc(&c->d_err, 2));
     TRYC(cudaMemset(c->d_err, 0, 8));
+
+    // adaptive-noise overlays and the per-index change flags of one parameter update
+    c->SL = scales_layout(*cfg);
+    TRY(dev_alloc(&c->d_scales, c->SL.total));
+    {
+        const int64_t nflag = 4 * H > cfg->vocab_size ? 4 * H : cfg->vocab_size;
+        TRY(dev_alloc(&c->d_ch_in, nflag)); TRY(dev_alloc(&c->d_ch_out, nflag));
+        TRYC(cudaMemset(c->d_ch_in, 0, (size_t)nflag)); TRYC(cudaMemset(c->d_ch_out, 0, (size_t)nflag));
+    }
 
     // noise map
     std::vector<NoiseSeg> segs(32 + 32 * cfg->n_layers);
@@ -458,6 +477,35 @@ extern "C" int egg_download_opt_state(egg_ctx *c, void *host_state, int64_t nbyt
     return EGG_OK;
 }
 
+extern "C" int64_t egg_scales_bytes(const egg_config *c) { return c ? scales_layout(*c).total : 0; }
+
+extern "C" int egg_upload_scales(egg_ctx *c, const void *host_scales, int64_t nbytes) {
+    if (!c) { set_error("null context"); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    if (!host_scales) { EGG_CUDA(cudaStreamSynchronize(c->stream)); c->scales_on = false; return EGG_OK; }
+    if (nbytes != c->SL.total) { set_error("overlays are %lld bytes, this configuration needs %lld", (long long)nbytes, (long long)c->SL.total); return EGG_E_INVALID; }
+    EGG_CUDA(cudaMemcpyAsync(c->d_scales, host_scales, (size_t)nbytes, cudaMemcpyHostToDevice, c->stream));
+    EGG_CUDA(cudaStreamSynchronize(c->stream));
+    c->scales_on = true;
+    return EGG_OK;
+}
+
+extern "C" int egg_download_scales(egg_ctx *c, void *host_scales, int64_t nbytes) {
+    if (!c || !host_scales) { set_error("null argument"); return EGG_E_INVALID; }
+    if (!c->scales_on) { set_error("no overlays uploaded"); return EGG_E_STATE; }
+    if (nbytes != c->SL.total) { set_error("overlays are %lld bytes, buffer is %lld", (long long)c->SL.total, (long long)nbytes); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    EGG_CUDA(cudaMemcpyAsync(host_scales, c->d_scales, (size_t)nbytes, cudaMemcpyDeviceToHost, c->stream));
+    EGG_CUDA(cudaStreamSynchronize(c->stream));
+    return EGG_OK;
+}
+
+extern "C" int egg_set_overlay_steps(egg_ctx *c, int inc, int dec) {
+    if (!c || inc < 0 || dec < 0 || inc > 127 || dec > 127) { set_error("overlay steps must be in [0, 127]"); return EGG_E_INVALID; }
+    c->ov_inc = inc; c->ov_dec = dec;
+    return EGG_OK;
+}
+
 static int set_dataset_async(egg_ctx *c, const uint8_t *host_tokens, int64_t n) {
     if (n <= c->cfg.seq_len + 1) { set_error("dataset must be longer than seq_len+1"); return EGG_E_INVALID; }
     if (n > c->data_cap) {
@@ -497,14 +545,30 @@ static GemmParams base_gemm(egg_ctx *c, int M, int N, int K) {
 }
 
 // norm + up + down of one MLP block (compute_mlp, mgpu.cu:708-759); X, Hn, xb[.,0] are ready on entry
+// Row dots under adaptive-noise overlays: overwrite what the unscaled producers left in `out`.
+static int scaled_dots(egg_ctx *c, int M, const int8_t *x, int terms, int ndots, const int *nt_dot, const int64_t *ov_off,
+                       int32_t *out, int out_stride) {
+    ScaledDotParams sp;
+    memset(&sp, 0, sizeof(sp));
+    sp.M = M; sp.H = c->cfg.hidden_dim; sp.seq_len = c->cfg.seq_len; sp.terms = terms; sp.x = x;
+    sp.nt = c->d_nt; sp.nt_stride = c->nmap.stride; sp.ndots = ndots;
+    for (int q = 0; q < ndots; q++) { sp.nt_dot[q] = nt_dot[q]; sp.ov[q] = c->d_scales + ov_off[q]; }
+    sp.out = out; sp.out_stride = out_stride;
+    return PROF(EGG_PROF_OVERLAY, launch_scaled_dot(c->stream, sp));
+}
+static int scaled_dot1(egg_ctx *c, int M, const int8_t *x, int terms, int nt_dot, int64_t ov_off, int32_t *out, int out_stride) {
+    return scaled_dots(c, M, x, terms, 1, &nt_dot, &ov_off, out, out_stride);
+}
+
 static int run_mlp(egg_ctx *c, int M, const MlpOff &mo, int nt_base, const int8_t *up_t, const int8_t *up_bias, const int8_t *dn_t,
-                   const int8_t *dn_bias) {
+                   const int8_t *dn_bias, int64_t ov_dn_row) {
     const int H = c->cfg.hidden_dim;
     GemmParams g = base_gemm(c, M, 4 * H, H);
     g.nt_a_off = nt_base + mo.up_a; g.nt_c_off = nt_base + mo.bup_d; g.nt_d_off = nt_base + mo.dn_b;
     g.xb = c->d_xb; g.xb_stride = 3; g.out_shift = c->cfg.shift_mlp_up; g.bias = up_bias; g.out8 = c->d_u; g.rowstat = c->d_xb2;
     int rc = PROF(EGG_PROF_GEMM_GELU, launch_gemm(c->stream, EPI_GELU, c->d_h, up_t, g, c->num_sms));
     if (rc) return rc;
+    if (c->scales_on && (rc = scaled_dot1(c, M, c->d_u, 4, nt_base + mo.dn_b, ov_dn_row, c->d_xb2, 1))) return rc;
     GemmParams d = base_gemm(c, M, H, 4 * H);
     d.nt_a_off = nt_base + mo.dn_a; d.nt_c_off = nt_base + mo.bdn_d;
     d.xb = c->d_xb2; d.xb_stride = 1; d.out_shift = c->cfg.shift_mlp_down; d.bias = dn_bias; d.resid = c->d_x; d.out32 = c->d_pre;
@@ -532,8 +596,10 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
     const NoiseMap &nm = c->nmap;
     const int8_t *mdl = c->d_model, *sh = c->d_shadow;
     cudaStream_t st = c->stream;
+    const ScalesLayout &SL = c->SL;
+    const bool sc = c->scales_on;
     int rc;
-    if ((rc = PROF(EGG_PROF_NOISE, launch_noise_fill(st, c->d_nt, nm.stride, c->d_segs, c->nsegs, members / 2, step_seed, pop_base / 2, cf.device_mask, cf.device_gaussian, mdl)))) return rc;
+    if ((rc = PROF(EGG_PROF_NOISE, launch_noise_fill(st, c->d_nt, nm.stride, c->d_segs, c->nsegs, members / 2, step_seed, pop_base / 2, cf.device_mask, cf.device_gaussian, mdl, c->scales_on ? c->d_scales : nullptr)))) return rc;
     EGG_CUDA(cudaMemsetAsync(c->d_wave_loss, 0, (size_t)members * 4, st));
     EGG_CUDA(cudaMemsetAsync(c->d_rowmax, 0, (size_t)M * 4, st));
     const int64_t data_stride = c->data_len / (cf.population_size / 2);
@@ -546,8 +612,11 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
     r0.nt_emb_a = nm.emb_a; r0.nt_emb_b = nm.emb_b; r0.nt_emb_bias_d = nm.emb_bias_d; r0.emb_shift = cf.fixed_point + cf.sigma_shift;
     r0.nt_w_m = nm.ln_init.w_m; r0.nt_b_m = nm.ln_init.b_m;
     r0.ndots = 1; r0.nt_dot[0] = nm.mlp_init.up_b;
+    if (sc) { r0.ov_emb_row = c->d_scales + SL.embedding_row; r0.ov_emb_col = c->d_scales + SL.embedding_col; }
     if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, r0, 0)))) return rc;
-    if ((rc = run_mlp(c, M, nm.mlp_init, 0, sh + c->so.init_up, mdl + L.mlp_emb_bias_up, sh + c->so.init_dn, mdl + L.mlp_emb_bias_down))) return rc;
+    if (sc && (rc = scaled_dot1(c, M, c->d_h, 1, nm.mlp_init.up_b, SL.w_emb_mlp_up_row, c->d_xb, 3))) return rc;
+    if ((rc = run_mlp(c, M, nm.mlp_init, 0, sh + c->so.init_up, mdl + L.mlp_emb_bias_up, sh + c->so.init_dn, mdl + L.mlp_emb_bias_down,
+                      SL.w_emb_mlp_down_row))) return rc;
 
     for (int l = 0; l < cf.n_layers; l++) {
         const int nb = nm.layer0 + l * nm.layer_stride;
@@ -558,6 +627,11 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
         ra.nt_w_m = nb + lo.ln1.w_m; ra.nt_b_m = nb + lo.ln1.b_m;
         ra.ndots = 3; ra.nt_dot[0] = nb + lo.qkv_b; ra.nt_dot[1] = nb + lo.qkv_b + H; ra.nt_dot[2] = nb + lo.qkv_b + 2 * H;
         if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, ra, 1)))) return rc;
+        const int64_t lH = (int64_t)l * H;
+        if (sc) {
+            const int64_t ovq[3] = {SL.w_q_row + lH, SL.w_k_row + lH, SL.w_v_row + lH};
+            if ((rc = scaled_dots(c, M, c->d_h, 1, 3, ra.nt_dot, ovq, c->d_xb, 3))) return rc;
+        }
         // fused Q|K|V projection + RoPE (mgpu.cu:779-784)
         GemmParams gq = base_gemm(c, M, 3 * H, H);
         gq.nt_a_off = nb + lo.qkv_a; gq.xb = c->d_xb; gq.xb_stride = 3; gq.out32 = c->d_pre; gq.rowstat = c->d_rowmax3; gq.third = H;
@@ -568,6 +642,7 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
         ap.q = c->d_q; ap.k = c->d_k; ap.v = c->d_v; ap.ao = c->d_ao; ap.exp_lut = c->d_exp_lut; ap.nt = c->d_nt;
         ap.nt_stride = nm.stride; ap.nt_o_b = nb + lo.o_b; ap.xbo = c->d_xbo;
         if ((rc = PROF(EGG_PROF_ATTENTION, launch_attention(st, ap)))) return rc;
+        if (sc && (rc = scaled_dot1(c, M, c->d_ao, 1, nb + lo.o_b, SL.w_o_row + lH, c->d_xbo, 1))) return rc;
         // output projection + residual (mgpu.cu:828-830)
         GemmParams go = base_gemm(c, M, H, H);
         go.nt_a_off = nb + lo.o_a; go.xb = c->d_xbo; go.xb_stride = 1; go.out_shift = cf.shift_out; go.resid = c->d_x;
@@ -578,16 +653,18 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
         rb.nt_w_m = nb + lo.ln2.w_m; rb.nt_b_m = nb + lo.ln2.b_m;
         rb.ndots = 1; rb.nt_dot[0] = nb + lo.mlp.up_b;
         if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, rb, 1)))) return rc;
+        if (sc && (rc = scaled_dot1(c, M, c->d_h, 1, nb + lo.mlp.up_b, SL.w_up_row + lH, c->d_xb, 3))) return rc;
         if ((rc = run_mlp(c, M, lo.mlp, nb, shl + c->so.up, mdl + L.mlp_bias_up + (int64_t)l * 4 * H, shl + c->so.dn,
-                          mdl + L.mlp_bias_down + (int64_t)l * H))) return rc;
+                          mdl + L.mlp_bias_down + (int64_t)l * H, SL.w_down_row + 4 * lH))) return rc;
     }
     // final norm + tied-embedding head + cross-entropy (mgpu.cu:954-1024)
     RowParams rf = base_row(c, M);
     rf.nt_w_m = nm.ln_f.w_m; rf.nt_b_m = nm.ln_f.b_m;
     rf.ndots = 1; rf.nt_dot[0] = nm.emb_b;
     if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, rf, 1)))) return rc;
+    if (sc && (rc = scaled_dot1(c, M, c->d_h, 1, nm.emb_b, SL.embedding_col, c->d_xb, 3))) return rc;
     GemmParams gh = base_gemm(c, M, V, H);
-    gh.nt_a_off = nm.emb_a; gh.xb = c->d_xb; gh.xb_stride = 3; gh.out_shift = cf.shift_logit;
+    gh.nt_a_off = nm.head_a; gh.xb = c->d_xb; gh.xb_stride = 3; gh.out_shift = cf.shift_logit;
     gh.dataset = c->d_data; gh.data_len = c->data_len; gh.start_idx = start_idx; gh.data_stride = data_stride; gh.pop_base = pop_base;
     gh.use_same_data = cf.use_same_data; gh.softmax_scale_bit = cf.softmax_scale_bit; gh.loss = c->d_wave_loss;
     if ((rc = PROF(EGG_PROF_GEMM_HEAD, launch_gemm(st, EPI_HEAD, c->d_h, sh + c->so.emb, gh, c->num_sms)))) return rc;
@@ -695,7 +772,14 @@ static int update_matrix(egg_ctx *c, const ParamDesc &d, uint32_t step_seed, flo
     g.opt = reinterpret_cast<float *>(c->d_opt + d.opt_off);
     g.lr = lr * d.lr_scale; g.beta1 = cf.adam_beta1; g.beta2 = cf.adam_beta2; g.eps = cf.adam_eps; g.wd = cf.adam_weight_decay;
     g.mu = cf.muon_momentum; g.total_updates = c->d_updates; g.err = c->d_err;
-    if (!d.muon) return PROF(EGG_PROF_UPD_GEMM, launch_gemm(c->stream, EPI_ADAM, c->d_na, c->d_nb, g, c->num_sms));
+    if (!d.muon) {
+        if (c->scales_on) { g.ch_in = c->d_ch_in; g.ch_out = c->d_ch_out; }
+        if ((rc = PROF(EGG_PROF_UPD_GEMM, launch_gemm(c->stream, EPI_ADAM, c->d_na, c->d_nb, g, c->num_sms)))) return rc;
+        if (!c->scales_on) return EGG_OK;
+        // UPDATE_OVERLAY of the input-index and the output-index overlay (worker.cu:445-455)
+        if ((rc = PROF(EGG_PROF_OVERLAY, launch_overlay_step(c->stream, c->d_scales + d.ov_in, c->d_ch_in, d.rows_k, c->ov_inc, c->ov_dec)))) return rc;
+        return PROF(EGG_PROF_OVERLAY, launch_overlay_step(c->stream, c->d_scales + d.ov_out, c->d_ch_out, d.cols_n, c->ov_inc, c->ov_dec));
+    }
     g.m_rowmajor = c->muon.x;
     if ((rc = PROF(EGG_PROF_UPD_GEMM, launch_gemm(c->stream, EPI_MUON_M, c->d_na, c->d_nb, g, c->num_sms)))) return rc;
     if ((rc = PROFN(EGG_PROF_MUON, 12, launch_newton_schulz(c->stream, c->muon, d.rows_k, d.cols_n)))) return rc;
@@ -717,7 +801,10 @@ static int apply_update_async(egg_ctx *c, uint32_t step_seed, float lr) {
             v.off_a = d.off_a; v.off_b = d.off_b; v.seed_base = d.seed_base; v.fit = c->d_fit; v.pairs = cf.population_size / 2;
             v.step_seed = step_seed; v.lr = lr * d.lr_scale; v.beta1 = cf.adam_beta1; v.beta2 = cf.adam_beta2; v.eps = cf.adam_eps;
             v.wd = cf.adam_weight_decay; v.mask = cf.device_mask; v.gaussian = cf.device_gaussian; v.total_updates = c->d_updates;
+            v.changed = c->scales_on ? c->d_ch_in : nullptr;
             rc = PROF(EGG_PROF_UPD_VECTOR, launch_update_vector(c->stream, v));
+            if (!rc && c->scales_on)
+                rc = PROF(EGG_PROF_OVERLAY, launch_overlay_step(c->stream, c->d_scales + d.ov_in, c->d_ch_in, d.cols_n, c->ov_inc, c->ov_dec));
         }
         if (rc) return rc;
     }
@@ -812,10 +899,10 @@ extern "C" int egg_perturbed_projection(egg_ctx *c, const int8_t *x, const int8_
         PTRYC(cudaMemcpyAsync(d_w, w_packed, (size_t)K * N, cudaMemcpyHostToDevice, st));
     }
     PTRY(dev_alloc(&d_wt, (int64_t)K * N)); PTRY(dev_alloc(&d_nt, pairs * stride)); PTRY(dev_alloc(&d_xb, rows)); PTRY(dev_alloc(&d_segs, 2));
-    NoiseSeg segs[2] = {{0, N, 0, off_a, 0, 0, -1}, {N, K, 0, off_b, 0, 0, -1}};
+    NoiseSeg segs[2] = {{0, N, 0, off_a, 0, 0, -1, -1}, {N, K, 0, off_b, 0, 0, -1, -1}};
     PTRYC(cudaMemcpyAsync(d_segs, segs, sizeof(segs), cudaMemcpyHostToDevice, st));
     PTRY(launch_unpack_transpose(st, d_w, d_wt, K, N));
-    PTRY(launch_noise_fill(st, d_nt, stride, d_segs, 2, (int)pairs, seed, 0, c->cfg.device_mask, c->cfg.device_gaussian, nullptr));
+    PTRY(launch_noise_fill(st, d_nt, stride, d_segs, 2, (int)pairs, seed, 0, c->cfg.device_mask, c->cfg.device_gaussian, nullptr, nullptr));
     rowdot_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(d_x, d_nt, stride, N, rows_per_member, rows, K, d_xb);
     PTRYC(cudaGetLastError());
     GemmParams g;
@@ -966,7 +1053,7 @@ extern "C" int egg_profile_read(egg_ctx *c, float *ms, int64_t *launches) {
 extern "C" const char *egg_profile_name(int cls) {
     static const char *names[EGG_PROF_N] = {"noise_fill", "rowwise", "gemm_gelu", "gemm_pre32", "gemm_qkv", "gemm_head", "aqn",
                                             "attention", "fitness", "update_operands", "update_gemm", "update_vector", "muon",
-                                            "transpose"};
+                                            "transpose", "overlay"};
     return (cls >= 0 && cls < EGG_PROF_N) ? names[cls] : "";
 }
 

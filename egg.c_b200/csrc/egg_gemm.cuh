@@ -72,6 +72,7 @@ struct GemmParams {
     float *m_rowmajor;           // EPI_MUON_M: [rows_k][cols_n]
     float lr, beta1, beta2, eps, wd, mu;
     unsigned long long *total_updates;
+    uint8_t *ch_in, *ch_out;     // EPI_ADAM: set to 1 for every input index k / output index n with a changed weight (or null)
     int32_t *vote_out;
     // ---- device error record ----
     int *err;
@@ -471,7 +472,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                             for (int j = 0; j < 4; j++) {
                                 int w = (int)(int8_t)(wword >> (8 * j));
                                 float g = -(float)(int)v[4 * q + j];
-                                changes += adam_apply(f[3 * j], f[3 * j + 1], f[3 * j + 2], w, g, p.lr, p.beta1, p.beta2, p.eps, p.wd);
+                                const int ch = adam_apply(f[3 * j], f[3 * j + 1], f[3 * j + 2], w, g, p.lr, p.beta1, p.beta2, p.eps, p.wd);
+                                changes += ch;
+                                if (ch && p.ch_in) { p.ch_in[k0 + 4 * q + j] = 1; p.ch_out[n] = 1; }   // adam.cuh:77-83
                                 neww |= (uint32_t)(w & 0xFF) << (8 * j);
                             }
                             *reinterpret_cast<uint32_t *>(p.w_packed + idx) = neww;

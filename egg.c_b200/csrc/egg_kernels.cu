@@ -225,6 +225,7 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
                                       : ((p.start_idx + pair * p.data_stride) % (p.data_len - p.seq_len));
         const int tok = p.dataset[pos + t];
         const int a_tok = ntp[p.nt_emb_a + tok];
+        const float f_row = p.ov_emb_row ? __fdiv_rn((float)overlay_num(p.ov_emb_row[tok]), 64.0f) : 1.0f;
         const int32_t *emb32 = reinterpret_cast<const int32_t *>(p.emb_packed);
 #pragma unroll
         for (int j = 0; j < NJ; j++) {
@@ -233,9 +234,18 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
             int32_t eb4 = *reinterpret_cast<const int32_t *>(p.emb_bias + d);
             int32_t dl4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_emb_bias_d + sgn * H + d);
             int32_t nb4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_emb_b + d);
+            int32_t oc4 = 0;
+            if (p.ov_emb_col) oc4 = *reinterpret_cast<const int32_t *>(p.ov_emb_col + d);
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                int perturb = (a_tok * (int)byte_of(nb4, i) * ns) >> p.emb_shift;
+                int prod = a_tok * (int)byte_of(nb4, i);
+                if (p.ov_emb_col) {
+                    // (AccumType)(a_tok * b_dim * s_emb_row * s_emb_col), d-eggs kernels.cu:150-158: two float
+                    // multiplications, each rounded, then the truncating conversion
+                    const float fc = __fdiv_rn((float)overlay_num(byte_of(oc4, i)), 64.0f);
+                    prod = __float2int_rz(__fmul_rn(__fmul_rn((float)prod, f_row), fc));
+                }
+                int perturb = (prod * ns) >> p.emb_shift;
                 x[j][i] = clip8((int)byte_of(e4, i) + (int)byte_of(eb4, i) + (int)byte_of(dl4, i) + perturb);
             }
         }
@@ -318,6 +328,67 @@ static int launch_rowwise_nj(cudaStream_t st, const RowParams &p) {
 
 int launch_rowwise(cudaStream_t st, const RowParams &p, int mode) {
     return mode == 0 ? launch_rowwise_nj<0>(st, p) : launch_rowwise_nj<1>(st, p);
+}
+
+// Row dots under adaptive-noise overlays (d-eggs/include/model/layers.cuh:250, 272-280, 339-341, 396):
+//   out[r][q] = Σ_tid pb(tid),  pb = 0;  for sub < terms:  pb = (int)((float)pb + x[k] * noise_q[k] * factor_q[k]),
+//   k = tid + sub*H
+// — with one term per thread this truncates every product, with four (the down projection) it truncates
+// the thread's running sum.  All values are multiples of 1/64 below 2^17, so the float arithmetic of the
+// reference is exact and is done here in integers: pb = trunc((64*pb + x*n*num) / 64).
+__global__ void __launch_bounds__(256) scaled_dot_kernel(const ScaledDotParams p) {
+    const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (r >= p.M) return;
+    const int H = p.H, K = H * p.terms;
+    const int mem = r / p.seq_len;
+    const int8_t *ntp = p.nt + (int64_t)(mem >> 1) * p.nt_stride;
+    const int8_t *xr = p.x + (int64_t)r * K;
+    for (int q = 0; q < p.ndots; q++) {
+        const int8_t *nz = ntp + p.nt_dot[q];
+        const int8_t *ov = p.ov[q];
+        int acc = 0;
+        for (int d = lane << 2; d < H; d += 128) {
+            int pb[4] = {0, 0, 0, 0};
+            for (int sub = 0; sub < p.terms; sub++) {
+                const int k = d + sub * H;
+                const int32_t x4 = *reinterpret_cast<const int32_t *>(xr + k);
+                const int32_t n4 = *reinterpret_cast<const int32_t *>(nz + k);
+                const int32_t o4 = *reinterpret_cast<const int32_t *>(ov + k);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int t = (pb[i] << 6) + (int)byte_of(x4, i) * (int)byte_of(n4, i) * overlay_num(byte_of(o4, i));
+                    pb[i] = (t + ((t >> 31) & 63)) >> 6;
+                }
+            }
+            acc += pb[0] + pb[1] + pb[2] + pb[3];
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) p.out[(int64_t)r * p.out_stride + q] = acc;
+    }
+}
+
+int launch_scaled_dot(cudaStream_t st, const ScaledDotParams &p) {
+    scaled_dot_kernel<<<(p.M + 7) / 8, 256, 0, st>>>(p);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
+
+// update_overlay_kernel (d-eggs/src/kernels.cu:61-77): +inc where a weight of the row / column / element
+// changed in this update, -dec elsewhere, clamped to [-127, 127]; the change flags are cleared for the next use.
+__global__ void overlay_step_kernel(int8_t *ov, uint8_t *changed, int n, int inc, int dec) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int v = ov[i];
+    if (changed[i]) { v += inc; if (v > 127) v = 127; } else { v -= dec; if (v < -127) v = -127; }
+    ov[i] = (int8_t)v;
+    changed[i] = 0;
+}
+
+int launch_overlay_step(cudaStream_t st, int8_t *ov, uint8_t *changed, int n, int inc, int dec) {
+    overlay_step_kernel<<<(n + 255) / 256, 256, 0, st>>>(ov, changed, n, inc, dec);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
 }
 
 // Q/K/V requantisation (adaptive_qkv_normalize, mgpu.cu:782-784)
@@ -689,7 +760,7 @@ __global__ void __launch_bounds__(256) update_vector_kernel(const VecUpdParams p
         int ch = adam_apply(m, v, acc, w, -(float)total, p.lr, p.beta1, p.beta2, p.eps, p.wd);
         p.opt[idx * 3] = m; p.opt[idx * 3 + 1] = v; p.opt[idx * 3 + 2] = acc;
         p.v[idx] = (int8_t)w;
-        if (ch) atomicAdd(p.total_updates, 1ull);
+        if (ch) { atomicAdd(p.total_updates, 1ull); if (p.changed) p.changed[idx] = 1; }
     }
 }
 int launch_update_vector(cudaStream_t st, const VecUpdParams &p) {

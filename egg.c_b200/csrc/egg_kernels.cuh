@@ -49,6 +49,7 @@ struct RowParams {
     const uint8_t *dataset; int64_t data_len, start_idx, data_stride; int pop_base, use_same_data;
     const int8_t *emb_packed; const int8_t *emb_bias; int vocab;
     int nt_emb_a, nt_emb_b, nt_emb_bias_d, emb_shift;
+    const int8_t *ov_emb_row, *ov_emb_col;   // adaptive-noise overlays of the embedding ([vocab], [H]) or null
     const int32_t *pre32; int32_t *rowmax;
     // residual stream out
     int8_t *x_out;
@@ -63,6 +64,19 @@ struct RowParams {
     int32_t *zero3;      // [M][3]
 };
 int launch_rowwise(cudaStream_t st, const RowParams &p, int mode);
+
+// Σ x·noise·factor per row under adaptive-noise overlays; overwrites out[r*out_stride + q].
+struct ScaledDotParams {
+    int M, H, seq_len;
+    int terms;                   // 1: x is [M][H];  4: x is [M][4H], four terms per thread summed with a running truncation
+    const int8_t *x;
+    const int8_t *nt; int64_t nt_stride;
+    int ndots; int nt_dot[3];    // offsets of the raw noise vectors (length H*terms) in the pair table
+    const int8_t *ov[3];         // overlays over the input index (length H*terms)
+    int32_t *out; int out_stride;
+};
+int launch_scaled_dot(cudaStream_t st, const ScaledDotParams &p);
+int launch_overlay_step(cudaStream_t st, int8_t *ov, uint8_t *changed, int n, int inc, int dec);
 
 struct AqnParams {
     int M, H;
@@ -103,6 +117,7 @@ int launch_update_operands(cudaStream_t st, int8_t *na, int8_t *nb, const int32_
 struct VecUpdParams {
     int8_t *v; float *opt; int len; int off_a, off_b, seed_base; const int32_t *fit; int pairs;
     uint32_t step_seed; float lr, beta1, beta2, eps, wd; int mask, gaussian; unsigned long long *total_updates;
+    uint8_t *changed;    // [len] set to 1 where the element changed (adaptive-noise overlays) or null
 };
 int launch_update_vector(cudaStream_t st, const VecUpdParams &p);
 

@@ -107,6 +107,23 @@ int egg_download_model(egg_ctx *ctx, void *host_model, int64_t nbytes);
 int egg_upload_opt_state(egg_ctx *ctx, const void *host_state, int64_t nbytes);
 int egg_download_opt_state(egg_ctx *ctx, void *host_state, int64_t nbytes);
 
+/* ---- adaptive-noise overlays (d-eggs only) ------------------------------ */
+/* sizeof(AdaptiveScales) (d-eggs/include/model/definitions.h:92-142). */
+int64_t egg_scales_bytes(const egg_config *cfg);
+/*
+ * ≙ the worker's d_scales (worker.cu: cudaMallocManaged + init to ADAPTIVE_NOISE_INIT) and the
+ * `scales` argument of train_sequence_kernel (d-eggs/src/kernels.cu:96).  Uploading the bytes
+ * switches the context to ADAPTIVE_NOISE_MODE 1: every noise term of the evaluation is multiplied by
+ * get_adaptive_factor(overlay) (layers.cuh:12-19) and every egg_apply_update is followed by
+ * update_overlay_kernel (kernels.cu:61-77) per parameter.  host_scales == NULL switches back to
+ * unscaled noise (ADAPTIVE_NOISE_MODE 0, the mgpu program).  Mode 2 (stochastic gate) is not provided.
+ * Muon-optimised matrices keep their overlays unchanged (the worker never combines the two).
+ */
+int egg_upload_scales(egg_ctx *ctx, const void *host_scales, int64_t nbytes);
+int egg_download_scales(egg_ctx *ctx, void *host_scales, int64_t nbytes);
+/* ADAPTIVE_NOISE_INC / ADAPTIVE_NOISE_DEC (d-eggs/include/config.h:231-236); defaults 5 and 1. */
+int egg_set_overlay_steps(egg_ctx *ctx, int inc, int dec);
+
 /* ≙ cudaMemcpy(d_dataset, ds.data, ds.length) (mgpu.cu:1466-1467). Byte tokens. */
 int egg_set_dataset(egg_ctx *ctx, const uint8_t *host_tokens, int64_t n_tokens);
 
@@ -280,6 +297,7 @@ enum {
     EGG_PROF_UPD_VECTOR,    /* vector parameters                                      */
     EGG_PROF_MUON,          /* Newton–Schulz + apply                                  */
     EGG_PROF_TRANSPOSE,     /* packed -> K-major weight shadows                       */
+    EGG_PROF_OVERLAY,       /* adaptive-noise: scaled row dots, overlay steps          */
     EGG_PROF_N
 };
 /* enable != 0: every launch is bracketed by events (a few microseconds each). */
