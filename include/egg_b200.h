@@ -236,6 +236,53 @@ int egg_update_reconstruct_noalloc(egg_ctx *ctx, const int32_t *d_fitness, int p
                                    int rows_k, int cols_n, int off_a, int off_b, int seed_base,
                                    uint32_t step_seed, int split, int32_t *d_vote_out);
 
+/* ---- the recurrent (GRU + MLP) model of full_trained_egg.c ------------------ */
+/*
+ * The reference's CPU trainer is a different model from the transformer above: a 4-layer
+ * minGRU-style recurrent network with one persistent RecurrentState per population member and
+ * noise drawn from a sequential xorshift32 stream (full_trained_egg.c:70-105), updated by a plain
+ * vote threshold instead of AdamW.  Its compile-time #defines (full_trained_egg.c:10-21) become
+ * this struct; bytes of EggModel (:42-50) and RecurrentState (:37-39) are the reference's.
+ */
+typedef struct egg_gru_config {
+    int32_t hidden_dim;        /* HIDDEN_DIM, multiple of 128, <= 1024            */
+    int32_t n_layers;          /* N_LAYERS                                        */
+    int32_t vocab_size;        /* VOCAB_SIZE, must be 256                         */
+    int32_t seq_len;           /* SEQ_LEN: tokens per generation and the modulus of the stream position (:546) */
+    int32_t population_size;   /* POPULATION_SIZE (even, multiple of 32, <= 1024) */
+    int32_t fixed_point;       /* FIXED_POINT                                     */
+    int32_t sigma_shift;       /* SIGMA_SHIFT                                     */
+    int32_t update_threshold;  /* UPDATE_THRESHOLD                                */
+} egg_gru_config;
+/* Defaults of full_trained_egg.c:10-21 (H 512, 4 layers, seq 4096, population 128, threshold 160). */
+void egg_gru_config_defaults(egg_gru_config *cfg);
+/* sizeof(EggModel) and sizeof(RecurrentState) * POPULATION_SIZE. */
+int64_t egg_gru_model_bytes(const egg_gru_config *cfg);
+int64_t egg_gru_state_bytes(const egg_gru_config *cfg);
+
+typedef struct egg_gru_ctx egg_gru_ctx;
+int  egg_gru_create(const egg_gru_config *cfg, int device, egg_gru_ctx **out);
+void egg_gru_destroy(egg_gru_ctx *ctx);
+/* EggModel bytes: matrices are row-major [out][in] as matmul_perturbed reads them (:108-177). */
+int egg_gru_upload_model(egg_gru_ctx *ctx, const void *host_model, int64_t nbytes);
+int egg_gru_download_model(egg_gru_ctx *ctx, void *host_model, int64_t nbytes);
+/* pop_states (:515-517): RecurrentState[POPULATION_SIZE], zero after create. */
+int egg_gru_upload_states(egg_gru_ctx *ctx, const void *host_states, int64_t nbytes);
+int egg_gru_download_states(egg_gru_ctx *ctx, void *host_states, int64_t nbytes);
+int egg_gru_set_dataset(egg_gru_ctx *ctx, const uint8_t *host_tokens, int64_t n_tokens);
+/*
+ * ≙ one iteration of the training loop (full_trained_egg.c:529-575): every pair p runs
+ * forward_pass twice (noise sign +1 / -1, seed step_seed + p) over `tokens` tokens (<= seq_len; the
+ * reference always runs seq_len) starting at (start_idx + p * (len / pairs)) % (len - seq_len),
+ * carrying its RecurrentState; fitness = sign of the loss difference; if do_update, every matrix goes
+ * through update_matrix (:332-409, :564-574).  host_losses[POPULATION_SIZE] and
+ * host_fitness[POPULATION_SIZE/2] may be NULL.
+ */
+int egg_gru_generation(egg_gru_ctx *ctx, uint32_t step_seed, int64_t start_idx, int tokens, int do_update,
+                       int32_t *host_losses, int32_t *host_fitness);
+/* Kernel launches issued by this context so far. */
+int64_t egg_gru_launch_count(egg_gru_ctx *ctx);
+
 /* ---- d-eggs worker boundary (host side, no GPU involved) ------------------ */
 /* Opcodes and the 10-byte "JOBS" header of d-eggs/include/protocol.h:8-56. */
 #define EGG_OP_JOB_REQUEST  0

@@ -105,6 +105,15 @@ int64_t oracle_ternary_packed_size(int64_t count);
 void oracle_ternary_pack(const int32_t *values, int64_t count, uint8_t *out);
 void oracle_ternary_unpack(const uint8_t *in, int64_t count, int32_t *values);
 
+/* --- the recurrent model of full_trained_egg.c (egg_gru_oracle.c) --- */
+int64_t oracle_gru_model_bytes(const egg_gru_config *cfg);
+void oracle_gru_init_model(const egg_gru_config *cfg, int8_t *model, uint32_t seed);          /* main(), :491-515 */
+void oracle_gru_exp2_table(const egg_gru_config *cfg, int32_t *table256);                      /* init_tables, :58-61 */
+/* one iteration of the training loop (:529-575); states [population][n_layers][H] are carried */
+void oracle_gru_generation(const egg_gru_config *cfg, int8_t *model, int8_t *states, const uint8_t *data,
+                           int64_t data_len, uint32_t step_seed, int64_t start_idx, int tokens, int do_update,
+                           int32_t *losses, int32_t *fitness);
+
 #ifdef __cplusplus
 }
 #endif

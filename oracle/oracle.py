@@ -26,6 +26,22 @@ class EggConfig(C.Structure):
         ("muon_lr_scale", C.c_float)]
 
 
+class GruConfig(C.Structure):
+    """Mirror of struct egg_gru_config; defaults are full_trained_egg.c:10-21."""
+    _fields_ = [(n, C.c_int32) for n in ("hidden_dim", "n_layers", "vocab_size", "seq_len", "population_size",
+                                          "fixed_point", "sigma_shift", "update_threshold")]
+
+
+def make_gru_config(**kw):
+    d = dict(hidden_dim=512, n_layers=4, vocab_size=256, seq_len=4096, population_size=128, fixed_point=4, sigma_shift=4,
+             update_threshold=160)
+    for k in kw:
+        if k not in d:
+            raise KeyError(k)
+    d.update(kw)
+    return GruConfig(**d)
+
+
 def make_config(**kw):
     d = dict(hidden_dim=256, head_dim=64, n_layers=4, seq_len=32, vocab_size=256,
              population_size=8192 * 2 * 4, fixed_point=4, sigma_shift=3, sigma_shift_vector=4,
@@ -88,6 +104,12 @@ def lib():
         L.oracle_ternary_packed_size.argtypes = [C.c_int64]
         L.oracle_ternary_pack.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
         L.oracle_ternary_unpack.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
+        gcp = P(GruConfig)
+        L.oracle_gru_model_bytes.restype = C.c_int64
+        L.oracle_gru_model_bytes.argtypes = [gcp]
+        L.oracle_gru_init_model.argtypes = [gcp, C.c_void_p, C.c_uint32]
+        L.oracle_gru_generation.argtypes = [gcp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_uint32, C.c_int64,
+                                            C.c_int, C.c_int, C.c_void_p, C.c_void_p]
         _lib = L
     return _lib
 
@@ -218,3 +240,27 @@ def deggs_chunk_fitness(losses, mean_filter=1, exponent=1.2, adaptive=1, alpha=0
     sl = np.zeros(1, np.int64)
     lib().oracle_deggs_chunk_fitness(_p(losses), len(losses), mean_filter, exponent, adaptive, alpha, _p(fit), _p(sl))
     return fit, int(sl[0])
+
+
+# ---- the recurrent model of full_trained_egg.c
+def gru_model_bytes(gcfg):
+    return lib().oracle_gru_model_bytes(C.byref(gcfg))
+
+
+def gru_state_bytes(gcfg):
+    return gcfg.population_size * gcfg.n_layers * gcfg.hidden_dim
+
+
+def gru_init_model(gcfg, seed=42):
+    m = np.zeros(gru_model_bytes(gcfg), np.int8)
+    lib().oracle_gru_init_model(C.byref(gcfg), _p(m), seed)
+    return m
+
+
+def gru_generation(gcfg, model, states, data, step_seed, start_idx, tokens, do_update=True):
+    """In place on model and states; returns (losses[pop], fitness[pop/2])."""
+    losses = np.zeros(gcfg.population_size, np.int32)
+    fit = np.zeros(gcfg.population_size // 2, np.int32)
+    lib().oracle_gru_generation(C.byref(gcfg), _p(model), _p(states), _p(data), len(data), step_seed & 0xFFFFFFFF, start_idx,
+                                tokens, 1 if do_update else 0, _p(losses), _p(fit))
+    return losses, fit

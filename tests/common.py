@@ -151,3 +151,34 @@ def make_case(kw, data_len=200000, data_seed=1, model_seed=0, model_kind="init")
         model = synth.random_model(cfg, model_seed, "uniform", gains_random=(model_kind == "random_all"))
     data = synth.zipf_bytes(data_seed, data_len)
     return cfg, ocfg, model, data
+
+
+def ref_gru_binary():
+    p = os.path.join(ROOT, "oracle", "_ref", "ref_cpu_gru")
+    return p if os.path.exists(p) else None
+
+
+def run_ref_gru(model, data, step_seed, tokens, steps=1, pairs=None):
+    """Runs the reference's CPU trainer functions (oracle/_ref/ref_cpu_gru: full_trained_egg.c lines 1-476,
+    unmodified) for `steps` generations of `tokens` tokens; CPU only."""
+    exe = ref_gru_binary()
+    assert exe, "oracle/_ref/ref_cpu_gru not built"
+    sizes = json.loads(subprocess.run([exe, "--sizes"], check=True, capture_output=True, text=True).stdout)
+    pop = sizes["population_size"]
+    pairs = pairs or pop // 2
+    with tempfile.TemporaryDirectory() as td:
+        fin, fout = os.path.join(td, "in.bin"), os.path.join(td, "out.bin")
+        with open(fin, "wb") as f:
+            f.write(np.uint32(step_seed & 0xFFFFFFFF).tobytes()); f.write(np.int64(len(data)).tobytes())
+            f.write(np.ascontiguousarray(model, np.int8).tobytes()); f.write(np.ascontiguousarray(data, np.uint8).tobytes())
+        r = subprocess.run([exe, fin, fout, str(pairs), str(tokens), str(steps)], capture_output=True, text=True, timeout=1800)
+        assert r.returncode == 0, r.stdout + r.stderr
+        raw = open(fout, "rb").read()
+    out = {"sizes": sizes, "losses": [], "fitness": [], "info": json.loads(r.stdout.strip().splitlines()[-1])}
+    o = 0
+    for _ in range(steps):
+        out["losses"].append(np.frombuffer(raw, np.int32, 2 * pairs, o).copy()); o += 8 * pairs
+        out["fitness"].append(np.frombuffer(raw, np.int32, pairs, o).copy()); o += 4 * pairs
+    out["model"] = np.frombuffer(raw, np.int8, sizes["model_bytes"], o).copy(); o += sizes["model_bytes"]
+    out["states"] = np.frombuffer(raw, np.int8, pop * sizes["n_layers"] * sizes["hidden_dim"], o).copy()
+    return out
