@@ -25,6 +25,9 @@ EXPORTS = [
     "egg_timer_start", "egg_timer_stop", "egg_profile_enable", "egg_profile_read", "egg_profile_name", "egg_launch_count",
     "egg_wave_members", "egg_wire_fixed_bytes", "egg_wire_encode", "egg_wire_decode_header", "egg_wire_decode_body",
     "egg_ternary_packed_size", "egg_ternary_pack", "egg_ternary_unpack", "egg_deggs_chunk_fitness", "egg_next_seed",
+    "egg_gru_config_defaults", "egg_gru_model_bytes", "egg_gru_state_bytes", "egg_gru_create", "egg_gru_destroy",
+    "egg_gru_upload_model", "egg_gru_download_model", "egg_gru_upload_states", "egg_gru_download_states", "egg_gru_set_dataset",
+    "egg_gru_generation", "egg_gru_launch_count",
 ]
 EGG_PROF_N = 15
 
@@ -40,6 +43,12 @@ class EggConfig(C.Structure):
         ("softmax_exp_scale", C.c_double), ("adam_beta1", C.c_float), ("adam_beta2", C.c_float),
         ("adam_eps", C.c_float), ("adam_weight_decay", C.c_float), ("muon_momentum", C.c_float),
         ("muon_lr_scale", C.c_float)]
+
+
+class GruConfig(C.Structure):
+    """struct egg_gru_config: the #defines of full_trained_egg.c:10-21."""
+    _fields_ = [(n, C.c_int32) for n in ("hidden_dim", "n_layers", "vocab_size", "seq_len", "population_size",
+                                          "fixed_point", "sigma_shift", "update_threshold")]
 
 
 class WireMsg(C.Structure):
@@ -82,6 +91,21 @@ def lib():
         L.egg_model_bytes.restype = C.c_int64
         L.egg_opt_state_bytes.argtypes = [cfgp]
         L.egg_opt_state_bytes.restype = C.c_int64
+        gcp = P(GruConfig)
+        L.egg_gru_config_defaults.argtypes = [gcp]
+        L.egg_gru_config_defaults.restype = None
+        for f in (L.egg_gru_model_bytes, L.egg_gru_state_bytes):
+            f.argtypes = [gcp]
+            f.restype = C.c_int64
+        L.egg_gru_create.argtypes = [gcp, C.c_int, P(vp)]
+        L.egg_gru_destroy.argtypes = [vp]
+        L.egg_gru_destroy.restype = None
+        for f in (L.egg_gru_upload_model, L.egg_gru_download_model, L.egg_gru_upload_states, L.egg_gru_download_states,
+                  L.egg_gru_set_dataset):
+            f.argtypes = [vp, vp, C.c_int64]
+        L.egg_gru_generation.argtypes = [vp, C.c_uint32, C.c_int64, C.c_int, C.c_int, vp, vp]
+        L.egg_gru_launch_count.argtypes = [vp]
+        L.egg_gru_launch_count.restype = C.c_int64
         L.egg_scales_bytes.argtypes = [cfgp]
         L.egg_scales_bytes.restype = C.c_int64
         L.egg_set_overlay_steps.argtypes = [C.c_void_p, C.c_int, C.c_int]
@@ -150,6 +174,24 @@ def default_config(**kw):
 
 def model_bytes(cfg):
     return lib().egg_model_bytes(C.byref(cfg))
+
+
+def default_gru_config(**kw):
+    cfg = GruConfig()
+    lib().egg_gru_config_defaults(C.byref(cfg))
+    for k, v in kw.items():
+        if not hasattr(cfg, k):
+            raise KeyError(k)
+        setattr(cfg, k, v)
+    return cfg
+
+
+def gru_model_bytes(gcfg):
+    return lib().egg_gru_model_bytes(C.byref(gcfg))
+
+
+def gru_state_bytes(gcfg):
+    return lib().egg_gru_state_bytes(C.byref(gcfg))
 
 
 def opt_state_bytes(cfg):
@@ -361,3 +403,56 @@ def deggs_chunk_fitness(losses, mean_filter=1, exponent=1.2, adaptive=1, alpha=0
 
 def next_seed(seed, step):
     return lib().egg_next_seed(seed & 0xFFFFFFFF, step)
+
+
+class GruContext:
+    """egg_gru_ctx: the recurrent model of full_trained_egg.c on one GPU (no CPU fallback)."""
+
+    def __init__(self, gcfg, device=0):
+        self.cfg = gcfg
+        self._h = C.c_void_p()
+        _check(lib().egg_gru_create(C.byref(gcfg), device, C.byref(self._h)))
+
+    def close(self):
+        if self._h:
+            lib().egg_gru_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def upload_model(self, model):
+        model = np.ascontiguousarray(model, np.int8)
+        _check(lib().egg_gru_upload_model(self._h, _ptr(model), model.nbytes))
+
+    def download_model(self):
+        out = np.zeros(gru_model_bytes(self.cfg), np.int8)
+        _check(lib().egg_gru_download_model(self._h, _ptr(out), out.nbytes))
+        return out
+
+    def upload_states(self, states):
+        states = np.ascontiguousarray(states, np.int8)
+        _check(lib().egg_gru_upload_states(self._h, _ptr(states), states.nbytes))
+
+    def download_states(self):
+        out = np.zeros(gru_state_bytes(self.cfg), np.int8)
+        _check(lib().egg_gru_download_states(self._h, _ptr(out), out.nbytes))
+        return out
+
+    def set_dataset(self, tokens):
+        tokens = np.ascontiguousarray(tokens, np.uint8)
+        _check(lib().egg_gru_set_dataset(self._h, _ptr(tokens), tokens.nbytes))
+
+    def generation(self, step_seed, start_idx, tokens, do_update=True):
+        """Returns (losses[population], fitness[population/2])."""
+        losses = np.zeros(self.cfg.population_size, np.int32)
+        fit = np.zeros(self.cfg.population_size // 2, np.int32)
+        _check(lib().egg_gru_generation(self._h, step_seed & 0xFFFFFFFF, start_idx, tokens, 1 if do_update else 0,
+                                        _ptr(losses), _ptr(fit)))
+        return losses, fit
+
+    def launch_count(self):
+        return lib().egg_gru_launch_count(self._h)
