@@ -145,6 +145,28 @@ def run_reference_arm(args, rank):
     print(json.dumps(line))
 
 
+def gru_model_run(pkg, synth, device, tokens=512, reps=2):
+    """The model the CPU baseline runs (full_trained_egg.c: GRU + MLP, H 512, 4 layers, population 128) through this
+    library's GPU path, so that the two numbers of the JSON line that share a unit also share a model.  Wall clock
+    around the blocking C-ABI call (noise generation, token steps, fitness, update, losses D2H)."""
+    import time
+    gcfg = pkg.default_gru_config()
+    ctx = pkg.GruContext(gcfg, device)
+    ctx.upload_model(synth.uniform_int8(0, pkg.gru_model_bytes(gcfg)))
+    ctx.set_dataset(synth.zipf_bytes(1, 1 << 20))
+    ctx.generation(0x00C0FFEE, 0, 32, True)                    # warm-up: graph capture
+    n0 = ctx.launch_count()
+    t0 = time.perf_counter()
+    for r in range(reps):
+        ctx.generation(0x00C0FFEE + 1 + r, (r + 1) * gcfg.seq_len, tokens, True)
+    dt = (time.perf_counter() - t0) / reps
+    launches = (ctx.launch_count() - n0) // reps
+    ctx.close()
+    return {"value": gcfg.population_size * tokens / dt, "unit": UNIT, "ms_per_generation_sample": dt * 1e3,
+            "sample": "%d members x %d tokens per generation (the reference runs 4096 tokens), update included" % (gcfg.population_size, tokens),
+            "gpu_launches": int(launches), "timing": "wall clock around the blocking call"}
+
+
 # ----------------------------------------------------------------------------- our arm
 def main():
     ap = argparse.ArgumentParser()
@@ -305,6 +327,13 @@ def main():
         except Exception as e:   # the baseline is reported, never allowed to break the bench line
             cpu = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference", "sample": "failed: %s" % e}
 
+    gru = None
+    if rank == 0 and world == 1 and not args.small:
+        try:
+            gru = gru_model_run(pkg, synth, local_rank)
+        except Exception as e:
+            gru = {"value": None, "unit": UNIT, "sample": "failed: %s" % e}
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": n_warm,
@@ -322,6 +351,7 @@ def main():
             "kernels": kernel_share,
             "clocks": clocks,
             "cpu_baseline": cpu,
+            "gru_model_gpu": gru,
         }
         real_stdout.write(json.dumps(line) + "\n")
         real_stdout.flush()

@@ -76,6 +76,7 @@ struct GemmParams {
     int32_t *vote_out;
     // ---- device error record ----
     int *err;
+    int rpl;                     // -1 forces the transposed evaluation epilogue (tests); otherwise chosen from seq_len
 };
 
 template <int BN>
@@ -83,6 +84,10 @@ struct GemmSmem {
     alignas(1024) uint8_t a[GEMM_STAGES][GEMM_BM * GEMM_BK];
     alignas(1024) uint8_t b[GEMM_STAGES][BN * GEMM_BK];
     alignas(16) int32_t stage[GEMM_EPI_WARPS][32][20];  // per epilogue warp: 32 rows x 16 columns (+4 pad) transpose buffer
+    struct {                                            // row-per-lane epilogues: tables widened to int32, read as uniform LDS.128
+        alignas(16) int32_t a32[GEMM_MAX_SLOTS][BN];        // A-noise of this projection per pair slot
+        alignas(16) int32_t bcs32[GEMM_MAX_SLOTS][2][BN];   // (bias + bias-noise delta) << out_shift per pair slot and sign
+    } rpl;
     alignas(16) int8_t a_tab[GEMM_MAX_SLOTS][BN];       // A-noise of this projection per pair slot
     alignas(16) int16_t bc_tab[GEMM_MAX_SLOTS][2][BN];  // bias + bias-noise delta per pair slot and sign
     alignas(16) int8_t d_tab[GEMM_MAX_SLOTS][BN];       // B-noise of the next projection (EPI_GELU)
@@ -128,7 +133,108 @@ __device__ __forceinline__ int adam_apply(float &m, float &v, float &acc, int &w
     return quantized_step(acc, w);
 }
 
+// ---- row-per-lane evaluation epilogues ----
+// Used when every warp's 32 accumulator rows belong to one population member (seq_len % 32 == 0): the rank-1 factor,
+// pair slot and sign are then per-lane scalars and the per-column tables are read at warp-uniform addresses, so the
+// accumulators are consumed straight from the TMEM layout (lane = row, registers = columns) with no transpose, no
+// shuffles and about half the instructions of the transposed form.  TMEM loads are double-buffered.
 template <int BN, int EPI>
+__device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &sm, uint32_t taddr, int r, bool row_ok, int n0,
+                                             int cbase, int slot, int sgn, int32_t (*st)[20], int lane, int m0q) {
+    constexpr int NCH = BN / 4 / 16;                       // 16-column chunks of this warp's quarter of the tile
+    const int rc = row_ok ? r : (p.M - 1);
+    const int mem = rc / p.seq_len;
+    const int part = (EPI == EPI_QKV) ? (n0 / p.third) : 0;
+    const int xbv = p.xb[(int64_t)rc * p.xb_stride + part];
+    const int xbs = sgn ? -xbv : xbv;
+    const int32_t *a32 = sm.rpl.a32[slot] + cbase;
+    const int32_t *bcs = sm.rpl.bcs32[slot][sgn] + cbase;
+    const int8_t *dt = sm.d_tab[slot] + cbase;
+    const int64_t gofs = (int64_t)rc * p.N + n0 + cbase;
+    int4 rs_pre[NCH];                                      // residual bytes of every chunk (EPI_PRE32)
+    if (EPI == EPI_PRE32) {
+#pragma unroll
+        for (int c = 0; c < NCH; c++) rs_pre[c] = *reinterpret_cast<const int4 *>(p.resid + gofs + 16 * c);
+    }
+    const int32_t *rope = p.rope_lut + (int64_t)(rc - mem * p.seq_len) * p.head_dim;     // row of this token position
+    const bool do_rope = (EPI == EPI_QKV) && part < 2;
+    const long long half_ulp = 1ll << (p.rope_bit - 1);
+    int racc = 0;
+    uint32_t v[2][16];
+    ptx::tmem_ld16(taddr, v[0]);
+#pragma unroll
+    for (int c = 0; c < NCH; c++) {
+        int4 cs[4];
+        if (EPI == EPI_QKV && do_rope) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) cs[q4] = __ldg(reinterpret_cast<const int4 *>(rope + (n0 + cbase + 16 * c) % p.head_dim + 4 * q4));
+        }
+        uint32_t *vc = v[c & 1];
+        ptx::tmem_ld_wait16(vc);
+        if (c + 1 < NCH) ptx::tmem_ld16(taddr + 16 * (c + 1), v[(c + 1) & 1]);
+        uint32_t outw[4];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; q4++) {
+            const int col = 16 * c + 4 * q4;
+            const int4 an = *reinterpret_cast<const int4 *>(a32 + col);
+            int x0 = (int)vc[4 * q4] + ((xbs * an.x) >> p.rank1_shift);
+            int x1 = (int)vc[4 * q4 + 1] + ((xbs * an.y) >> p.rank1_shift);
+            int x2 = (int)vc[4 * q4 + 2] + ((xbs * an.z) >> p.rank1_shift);
+            int x3 = (int)vc[4 * q4 + 3] + ((xbs * an.w) >> p.rank1_shift);
+            if (EPI == EPI_GELU) {
+                // ((acc + r1) >> s) + b  ==  (acc + r1 + (b << s)) >> s
+                const int4 b4 = *reinterpret_cast<const int4 *>(bcs + col);
+                const int z0 = min(max((x0 + b4.x) >> p.out_shift, -127), 127), z1 = min(max((x1 + b4.y) >> p.out_shift, -127), 127);
+                const int z2 = min(max((x2 + b4.z) >> p.out_shift, -127), 127), z3 = min(max((x3 + b4.w) >> p.out_shift, -127), 127);
+                const uint32_t u0 = (uint8_t)sm.act_lut[z0 & 0xFF], u1 = (uint8_t)sm.act_lut[z1 & 0xFF];
+                const uint32_t u2 = (uint8_t)sm.act_lut[z2 & 0xFF], u3 = (uint8_t)sm.act_lut[z3 & 0xFF];
+                outw[q4] = __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
+                racc = __dp4a((int)outw[q4], *reinterpret_cast<const int32_t *>(dt + col), racc);
+            } else if (EPI == EPI_PRE32) {
+                const int4 b4 = *reinterpret_cast<const int4 *>(bcs + col);
+                const int32_t rs = q4 == 0 ? rs_pre[c].x : (q4 == 1 ? rs_pre[c].y : (q4 == 2 ? rs_pre[c].z : rs_pre[c].w));
+                x0 = (int)(int8_t)(rs) + ((x0 + b4.x) >> p.out_shift);
+                x1 = (int)(int8_t)(rs >> 8) + ((x1 + b4.y) >> p.out_shift);
+                x2 = (int)(int8_t)(rs >> 16) + ((x2 + b4.z) >> p.out_shift);
+                x3 = (int)(rs >> 24) + ((x3 + b4.w) >> p.out_shift);
+                racc = max(racc, max(max(abs(x0), abs(x1)), max(abs(x2), abs(x3))));
+                *reinterpret_cast<int4 *>(&st[lane][4 * q4]) = make_int4(x0, x1, x2, x3);
+            } else if (EPI == EPI_QKV) {
+                if (do_rope) {
+                    // integer RoPE on adjacent (even, odd) columns (apply_rope_integer, mgpu.cu:624-644)
+                    const long long e0 = x0, o0 = x1, e1 = x2, o1 = x3;
+                    x0 = (int)((e0 * cs[q4].x - o0 * cs[q4].y + half_ulp) >> p.rope_bit);
+                    x1 = (int)((e0 * cs[q4].y + o0 * cs[q4].x + half_ulp) >> p.rope_bit);
+                    x2 = (int)((e1 * cs[q4].z - o1 * cs[q4].w + half_ulp) >> p.rope_bit);
+                    x3 = (int)((e1 * cs[q4].w + o1 * cs[q4].z + half_ulp) >> p.rope_bit);
+                }
+                racc = max(racc, max(max(abs(x0), abs(x1)), max(abs(x2), abs(x3))));
+                *reinterpret_cast<int4 *>(&st[lane][4 * q4]) = make_int4(x0, x1, x2, x3);
+            }
+        }
+        if (EPI == EPI_PRE32 || EPI == EPI_QKV) {
+            // int32 results leave through a 32 x 16 shared-memory transpose: a lane writing its own row would
+            // spread every store instruction over 32 cache lines; this way one covers 8 rows x 64 contiguous bytes
+            __syncwarp();
+            const int lrow = lane >> 2, pc = lane & 3;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int rr = m0q + i * 8 + lrow;
+                const int4 o = *reinterpret_cast<const int4 *>(&st[i * 8 + lrow][4 * pc]);
+                if (rr < p.M) *reinterpret_cast<int4 *>(p.out32 + (int64_t)rr * p.N + n0 + cbase + 16 * c + 4 * pc) = o;
+            }
+            __syncwarp();
+        }
+        if (EPI == EPI_GELU && row_ok) *reinterpret_cast<int4 *>(p.out8 + gofs + 16 * c) = make_int4(outw[0], outw[1], outw[2], outw[3]);
+    }
+    if (row_ok) {
+        if (EPI == EPI_GELU) atomicAdd(&p.rowstat[rc], racc);
+        else if (EPI == EPI_PRE32) atomicMax(&p.rowstat[rc], racc);
+        else if (EPI == EPI_QKV) atomicMax(&p.rowstat[(int64_t)rc * 3 + part], racc);
+    }
+}
+
+template <int BN, int EPI, int RPL>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -245,7 +351,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 for (int i = e; i < nslots * (BN / 4); i += GEMM_EPI_THREADS) {
                     int sl = i / (BN / 4), j = (i % (BN / 4)) * 4;
                     const int8_t *base = p.nt + (int64_t)(first_pl + sl) * p.nt_stride;
-                    *reinterpret_cast<int32_t *>(&sm.a_tab[sl][j]) = *reinterpret_cast<const int32_t *>(base + p.nt_a_off + n0 + j);
+                    const int32_t a4w = *reinterpret_cast<const int32_t *>(base + p.nt_a_off + n0 + j);
+                    if (RPL) *reinterpret_cast<int4 *>(&sm.rpl.a32[sl][j]) = make_int4((int)(int8_t)a4w, (int)(int8_t)(a4w >> 8), (int)(int8_t)(a4w >> 16), a4w >> 24);
+                    else *reinterpret_cast<int32_t *>(&sm.a_tab[sl][j]) = a4w;
                     if (EPI == EPI_GELU || EPI == EPI_PRE32) {
                         int32_t b4 = p.bias ? *reinterpret_cast<const int32_t *>(p.bias + n0 + j) : 0;
                         int32_t cp = 0, cn = 0;
@@ -256,8 +364,13 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                         for (int b = 0; b < 4; b++) {
                             int bb = (int)(int8_t)(b4 >> (8 * b));
-                            sm.bc_tab[sl][0][j + b] = (int16_t)(bb + (int)(int8_t)(cp >> (8 * b)));
-                            sm.bc_tab[sl][1][j + b] = (int16_t)(bb + (int)(int8_t)(cn >> (8 * b)));
+                            if (RPL) {
+                                sm.rpl.bcs32[sl][0][j + b] = (bb + (int)(int8_t)(cp >> (8 * b))) << p.out_shift;
+                                sm.rpl.bcs32[sl][1][j + b] = (bb + (int)(int8_t)(cn >> (8 * b))) << p.out_shift;
+                            } else {
+                                sm.bc_tab[sl][0][j + b] = (int16_t)(bb + (int)(int8_t)(cp >> (8 * b)));
+                                sm.bc_tab[sl][1][j + b] = (int16_t)(bb + (int)(int8_t)(cn >> (8 * b)));
+                            }
                         }
                     }
                     if (EPI == EPI_GELU)
@@ -273,7 +386,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             bool rok[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                if (EPI > EPI_HEAD) { rrow[i] = 0; xbs[i] = 0; slot_sgn[i] = 0; aux[i] = 0; rok[i] = false; continue; }
+                if (EPI > EPI_HEAD || RPL) { rrow[i] = 0; xbs[i] = 0; slot_sgn[i] = 0; aux[i] = 0; rok[i] = false; continue; }
                 const int rr = m0 + quarter * 32 + i * 8 + lrow;
                 rok[i] = rr < p.M;
                 const int rc = rok[i] ? rr : (p.M - 1);
@@ -295,7 +408,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
             }
             int32_t rs_pre[COLS_PER / 16][4];        // residual bytes of every chunk (EPI_PRE32)
-            if (EPI == EPI_PRE32 && active) {
+            if (EPI == EPI_PRE32 && active && !RPL) {
 #pragma unroll
                 for (int cc = 0; cc < COLS_PER / 16; cc++)
 #pragma unroll
@@ -316,6 +429,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
             if (!active) {
                 // nothing to compute; still takes part in the barrier protocol below
+            } else if (RPL) {
+                epilogue_rpl<BN, EPI>(p, sm, taddr, r, row_ok, n0, cbase, slot, sgn, sm.stage[ew], lane, m0 + quarter * 32);
             } else if (EPI <= EPI_HEAD) {
                 // ---------------- evaluation epilogues ----------------
                 // Accumulators leave TMEM one row per lane; they are transposed through shared memory so

@@ -10,17 +10,17 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 static EncodeTiledFn g_encode = nullptr;
 
-template <int BN, int EPI>
+template <int BN, int EPI, int RPL = 0>
 static int set_attr() {
-    EGG_CUDA(cudaFuncSetAttribute(gemm_i8_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes<BN>()));
+    EGG_CUDA(cudaFuncSetAttribute(gemm_i8_kernel<BN, EPI, RPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes<BN>()));
     return EGG_OK;
 }
 
-template <int EPI>
+template <int EPI, int RPL = 0>
 static int set_attr_both() {
-    int rc = set_attr<128, EPI>();
+    int rc = set_attr<128, EPI, RPL>();
     if (rc) return rc;
-    return set_attr<256, EPI>();
+    return set_attr<256, EPI, RPL>();
 }
 
 int gemm_init() {
@@ -36,6 +36,9 @@ int gemm_init() {
     if ((rc = set_attr_both<EPI_GELU>())) return rc;
     if ((rc = set_attr_both<EPI_PRE32>())) return rc;
     if ((rc = set_attr_both<EPI_QKV>())) return rc;
+    if ((rc = set_attr_both<EPI_GELU, 1>())) return rc;
+    if ((rc = set_attr_both<EPI_PRE32, 1>())) return rc;
+    if ((rc = set_attr_both<EPI_QKV, 1>())) return rc;
     if ((rc = set_attr<256, EPI_HEAD>())) return rc;
     if ((rc = set_attr_both<EPI_ADAM>())) return rc;
     if ((rc = set_attr_both<EPI_MUON_M>())) return rc;
@@ -57,19 +60,26 @@ static int make_tmap(CUtensorMap *m, const void *ptr, uint64_t rows, uint64_t k,
     return EGG_OK;
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, int RPL = 0>
 static int launch_one(cudaStream_t st, const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int num_sms) {
     int tiles = ((p.M + GEMM_BM - 1) / GEMM_BM) * (p.N / BN);
     int grid = tiles < num_sms ? tiles : num_sms;
-    gemm_i8_kernel<BN, EPI><<<grid, GEMM_THREADS, gemm_smem_bytes<BN>(), st>>>(ta, tb, p);
+    gemm_i8_kernel<BN, EPI, RPL><<<grid, GEMM_THREADS, gemm_smem_bytes<BN>(), st>>>(ta, tb, p);
     EGG_CUDA(cudaGetLastError());
     return EGG_OK;
 }
 
-template <int EPI>
+template <int EPI, int RPL = 0>
 static int launch_bn(cudaStream_t st, int bn, const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int num_sms) {
-    if (bn == 256) return launch_one<256, EPI>(st, ta, tb, p, num_sms);
-    return launch_one<128, EPI>(st, ta, tb, p, num_sms);
+    if (bn == 256) return launch_one<256, EPI, RPL>(st, ta, tb, p, num_sms);
+    return launch_one<128, EPI, RPL>(st, ta, tb, p, num_sms);
+}
+
+// evaluation epilogues whose rows come in whole 32-row groups per member take the row-per-lane form
+template <int EPI>
+static int launch_eval(cudaStream_t st, int bn, const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int num_sms) {
+    if (p.seq_len % 32 == 0 && p.rpl >= 0) return launch_bn<EPI, 1>(st, bn, ta, tb, p, num_sms);
+    return launch_bn<EPI, 0>(st, bn, ta, tb, p, num_sms);
 }
 
 int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, const GemmParams &p, int num_sms) {
@@ -89,9 +99,9 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
     if ((rc = make_tmap(&tb, B, (uint64_t)p.N, (uint64_t)p.K, (uint32_t)bn))) return rc;
     switch (epi) {
         case EPI_CLIP8: return launch_bn<EPI_CLIP8>(st, bn, ta, tb, p, num_sms);
-        case EPI_GELU: return launch_bn<EPI_GELU>(st, bn, ta, tb, p, num_sms);
-        case EPI_PRE32: return launch_bn<EPI_PRE32>(st, bn, ta, tb, p, num_sms);
-        case EPI_QKV: return launch_bn<EPI_QKV>(st, bn, ta, tb, p, num_sms);
+        case EPI_GELU: return launch_eval<EPI_GELU>(st, bn, ta, tb, p, num_sms);
+        case EPI_PRE32: return launch_eval<EPI_PRE32>(st, bn, ta, tb, p, num_sms);
+        case EPI_QKV: return launch_eval<EPI_QKV>(st, bn, ta, tb, p, num_sms);
         case EPI_HEAD: return launch_one<256, EPI_HEAD>(st, ta, tb, p, num_sms);
         case EPI_ADAM: return launch_bn<EPI_ADAM>(st, bn, ta, tb, p, num_sms);
         case EPI_MUON_M: return launch_bn<EPI_MUON_M>(st, bn, ta, tb, p, num_sms);

@@ -137,31 +137,25 @@ constexpr int GRU_BN = 32;      // outputs per block
 // Block = 4 warps x 32 members, all of them on the same 32 outputs.  Returns in r[mt][nt][e] the int8-range results
 //   clip((x·w[n] + ((xB * A[n] * sign) >> rank1_shift)) >> shift)
 // for the thread's fragment elements: member = m0 + 16*mt + g + 8*(e>>1), output = n0 + 8*nt + 2*q + (e&1).
-__device__ __forceinline__ void gru_product(const GruMmParams &p, const GruOperand &op, int m0, int n0, int lane, int *s_xb, int (&r)[2][4][4]) {
+// xB = x·B_pair rides on the same tensor-core loop: the B vectors of the warp's 16 pairs are two more 8-column
+// operand tiles, and member row r needs only column r/2 of them, which lies in tile mt for both 16-row tiles —
+// one extra MMA per 16 rows and k-step, no reduction loop.
+__device__ __forceinline__ void gru_product(const GruMmParams &p, const GruOperand &op, int m0, int n0, int lane, int (&r)[2][4][4]) {
     const int g = lane >> 2, q = lane & 3;
     const int K = p.K;
-    // xB of this warp's 32 members: lanes split K
-    for (int i = 0; i < 32; i++) {
-        const int m = m0 + i;
-        const int8_t *xr = op.x + (int64_t)m * op.x_stride;
-        const int8_t *br = op.nb + (int64_t)(m >> 1) * K;
-        int d = 0;
-        for (int k = lane * 4; k < K; k += 128)
-            d = __dp4a(*reinterpret_cast<const int32_t *>(xr + k), *reinterpret_cast<const int32_t *>(br + k), d);
-        for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, off);
-        if (lane == 0) s_xb[i] = d;
-    }
-    __syncwarp();
-    int acc[2][4][4];
+    int acc[2][4][4], xacc[2][4];
 #pragma unroll
-    for (int mt = 0; mt < 2; mt++)
+    for (int mt = 0; mt < 2; mt++) {
+        xacc[mt][0] = xacc[mt][1] = xacc[mt][2] = xacc[mt][3] = 0;
 #pragma unroll
         for (int nt = 0; nt < 4; nt++) acc[mt][nt][0] = acc[mt][nt][1] = acc[mt][nt][2] = acc[mt][nt][3] = 0;
+    }
     const int8_t *xa = op.x + (int64_t)(m0 + g) * op.x_stride + 4 * q;
     const int8_t *wb = op.w + (int64_t)(n0 + g) * K + 4 * q;
+    const int8_t *nbp = op.nb + (int64_t)((m0 >> 1) + g) * K + 4 * q;     // B of pair (m0/2 + 8*mt + g)
 #pragma unroll 4
     for (int k0 = 0; k0 < K; k0 += 32) {
-        uint32_t a[2][4], b[4][2];
+        uint32_t a[2][4], b[4][2], bn[2][2];
 #pragma unroll
         for (int mt = 0; mt < 2; mt++) {
             const int8_t *xp = xa + (int64_t)(16 * mt) * op.x_stride + k0;
@@ -169,6 +163,9 @@ __device__ __forceinline__ void gru_product(const GruMmParams &p, const GruOpera
             a[mt][1] = *reinterpret_cast<const uint32_t *>(xp + 8 * op.x_stride);
             a[mt][2] = *reinterpret_cast<const uint32_t *>(xp + 16);
             a[mt][3] = *reinterpret_cast<const uint32_t *>(xp + 8 * op.x_stride + 16);
+            const int8_t *np = nbp + (int64_t)(8 * mt) * K + k0;
+            bn[mt][0] = __ldg(reinterpret_cast<const uint32_t *>(np));
+            bn[mt][1] = __ldg(reinterpret_cast<const uint32_t *>(np + 16));
         }
 #pragma unroll
         for (int nt = 0; nt < 4; nt++) {
@@ -177,16 +174,21 @@ __device__ __forceinline__ void gru_product(const GruMmParams &p, const GruOpera
             b[nt][1] = __ldg(reinterpret_cast<const uint32_t *>(wp + 16));
         }
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++)
+        for (int mt = 0; mt < 2; mt++) {
 #pragma unroll
             for (int nt = 0; nt < 4; nt++) gru_mma(acc[mt][nt], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b[nt][0], b[nt][1]);
+            gru_mma(xacc[mt], a[mt][0], a[mt][1], a[mt][2], a[mt][3], bn[mt][0], bn[mt][1]);
+        }
     }
 #pragma unroll
     for (int mt = 0; mt < 2; mt++)
 #pragma unroll
         for (int e2 = 0; e2 < 2; e2++) {
             const int ml = 16 * mt + g + 8 * e2, m = m0 + ml;
-            const int xb = s_xb[ml];
+            // column (ml/2 - 8*mt) of the xB tile: held by lane 4*g + (col >> 1), element 2*e2 + (col & 1)
+            const int col = (g + 8 * e2) >> 1;
+            const int mine = (col & 1) ? xacc[mt][2 * e2 + 1] : xacc[mt][2 * e2];
+            const int xb = __shfl_sync(0xFFFFFFFFu, mine, 4 * g + (col >> 1));
             const int sign = (m & 1) ? -1 : 1;
             const int8_t *ar = op.na + (int64_t)(m >> 1) * p.N + n0 + 2 * q;
 #pragma unroll
@@ -200,20 +202,18 @@ __device__ __forceinline__ void gru_product(const GruMmParams &p, const GruOpera
                 }
             }
         }
-    __syncwarp();
 }
 
 template <int MODE>
 __global__ void __launch_bounds__(128) gru_mm_kernel(const GruMmParams p) {
-    __shared__ int s_xb[4][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * GRU_BN;
     const int m0 = blockIdx.y * 128 + warp * 32;
     if (m0 >= p.pop) return;                       // population is a multiple of 32: whole warps drop out
     const int g = lane >> 2, q = lane & 3;
     int r1[2][4][4], r2[2][4][4];
-    gru_product(p, p.op[0], m0, n0, lane, s_xb[warp], r1);
-    if (MODE == GRU_FT || MODE == GRU_HT) gru_product(p, p.op[1], m0, n0, lane, s_xb[warp], r2);
+    gru_product(p, p.op[0], m0, n0, lane, r1);
+    if (MODE == GRU_FT || MODE == GRU_HT) gru_product(p, p.op[1], m0, n0, lane, r2);
 #pragma unroll
     for (int mt = 0; mt < 2; mt++)
 #pragma unroll

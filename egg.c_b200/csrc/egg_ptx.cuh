@@ -125,6 +125,15 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t *r) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The same wait, naming the 16 destination registers of an earlier tmem_ld16 as read-write operands: arithmetic on
+// them cannot be scheduled above the wait even while a second load into other registers is still in flight.
+__device__ __forceinline__ void tmem_ld_wait16(uint32_t *r) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                   "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :
+                 : "memory");
+}
 
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of
 // 128 bytes, 8-row groups 1024 bytes apart (tile base 1024-byte aligned).
