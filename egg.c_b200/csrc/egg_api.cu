@@ -79,6 +79,7 @@ struct egg_ctx {
     int ov_inc = 5, ov_dec = 1;
     // tables
     int32_t *d_exp_lut = nullptr, *d_rope_lut = nullptr;
+    int2 *d_rope_t = nullptr;           // the same (cos, sin) pairs, [head_dim/2][seq_len]: consecutive tokens are consecutive in memory
     int8_t *d_act_lut = nullptr;
     // dataset
     uint8_t *d_data = nullptr;
@@ -301,7 +302,7 @@ extern "C" void egg_ctx_destroy(egg_ctx *c) {
     cudaSetDevice(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
-    void *ptrs[] = {c->d_model, c->d_opt, c->d_shadow, c->d_exp_lut, c->d_rope_lut, c->d_act_lut, c->d_data, c->d_loss, c->d_fit,
+    void *ptrs[] = {c->d_model, c->d_opt, c->d_shadow, c->d_exp_lut, c->d_rope_lut, c->d_rope_t, c->d_act_lut, c->d_data, c->d_loss, c->d_fit,
                     c->d_x, c->d_h, c->d_u, c->d_q, c->d_k, c->d_v, c->d_ao, c->d_pre, c->d_xb, c->d_xb2, c->d_rowmax,
                     c->d_rowmax3, c->d_xbo, c->d_wave_loss, c->d_segs, c->d_nt, c->d_na, c->d_nb, c->muon.x, c->muon.g,
                     c->muon.y, c->muon.norm2, c->d_updates, c->d_err, c->d_scales, c->d_ch_in, c->d_ch_out};
@@ -350,6 +351,12 @@ extern "C" int egg_ctx_create(const egg_config *cfg, int device, int wave_member
         TRYC(cudaMemcpy(c->d_exp_lut, e.data(), 256 * 4, cudaMemcpyHostToDevice));
         TRYC(cudaMemcpy(c->d_act_lut, a.data(), 256, cudaMemcpyHostToDevice));
         TRYC(cudaMemcpy(c->d_rope_lut, r.data(), r.size() * 4, cudaMemcpyHostToDevice));
+        const int hp = cfg->head_dim / 2;
+        std::vector<int2> rt((size_t)hp * S);
+        for (int t = 0; t < S; t++)
+            for (int i = 0; i < hp; i++) rt[(size_t)i * S + t] = make_int2(r[(size_t)t * cfg->head_dim + 2 * i], r[(size_t)t * cfg->head_dim + 2 * i + 1]);
+        TRY(dev_alloc(&c->d_rope_t, (int64_t)hp * S));
+        TRYC(cudaMemcpy(c->d_rope_t, rt.data(), rt.size() * sizeof(int2), cudaMemcpyHostToDevice));
     }
     TRY(dev_alloc(&c->d_loss, POP)); TRY(dev_alloc(&c->d_fit, POP / 2));
     TRYC(cudaMemset(c->d_loss, 0, (size_t)POP * 4)); TRYC(cudaMemset(c->d_fit, 0, (size_t)(POP / 2) * 4));
@@ -538,7 +545,7 @@ static GemmParams base_gemm(egg_ctx *c, int M, int N, int K) {
     g.nt = c->d_nt; g.nt_stride = c->nmap.stride;
     g.nt_c_off = -1;
     g.rank1_shift = c->cfg.fixed_point + c->cfg.sigma_shift;
-    g.act_lut = c->d_act_lut; g.exp_lut = c->d_exp_lut; g.rope_lut = c->d_rope_lut;
+    g.act_lut = c->d_act_lut; g.exp_lut = c->d_exp_lut; g.rope_lut = c->d_rope_lut; g.rope_t = c->d_rope_t;
     g.head_dim = c->cfg.head_dim; g.rope_bit = c->cfg.rope_scale_bit;
     g.err = c->d_err;
     return g;

@@ -56,6 +56,7 @@ struct GemmParams {
     const int8_t *act_lut;       // 256
     const int32_t *exp_lut;      // 256
     const int32_t *rope_lut;     // [seq_len][head_dim]
+    const int2 *rope_t;          // [head_dim/2][seq_len] (cos, sin): the same values, token index fastest
     int third;                   // EPI_QKV: N/3 (= hidden)
     int head_dim;
     int rope_bit;                // ROPE_SCALE_BIT
@@ -156,7 +157,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
 #pragma unroll
         for (int c = 0; c < NCH; c++) rs_pre[c] = *reinterpret_cast<const int4 *>(p.resid + gofs + 16 * c);
     }
-    const int32_t *rope = p.rope_lut + (int64_t)(rc - mem * p.seq_len) * p.head_dim;     // row of this token position
+    const int2 *rope = p.rope_t + (rc - mem * p.seq_len);                                // column of this token position
     const bool do_rope = (EPI == EPI_QKV) && part < 2;
     const long long half_ulp = 1ll << (p.rope_bit - 1);
     int racc = 0;
@@ -166,8 +167,13 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
     for (int c = 0; c < NCH; c++) {
         int4 cs[4];
         if (EPI == EPI_QKV && do_rope) {
+            // the lanes of a warp are consecutive tokens of one member: every load below is one contiguous run
+            const int pair0 = ((n0 + cbase + 16 * c) % p.head_dim) >> 1;
 #pragma unroll
-            for (int q4 = 0; q4 < 4; q4++) cs[q4] = __ldg(reinterpret_cast<const int4 *>(rope + (n0 + cbase + 16 * c) % p.head_dim + 4 * q4));
+            for (int q4 = 0; q4 < 4; q4++) {
+                const int2 c0 = __ldg(rope + (int64_t)(pair0 + 2 * q4) * p.seq_len), c1 = __ldg(rope + (int64_t)(pair0 + 2 * q4 + 1) * p.seq_len);
+                cs[q4] = make_int4(c0.x, c0.y, c1.x, c1.y);
+            }
         }
         uint32_t *vc = v[c & 1];
         ptx::tmem_ld_wait16(vc);
