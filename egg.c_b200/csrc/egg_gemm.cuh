@@ -92,6 +92,7 @@ struct GemmSmem {
     alignas(16) int8_t a_tab[GEMM_MAX_SLOTS][BN];       // A-noise of this projection per pair slot
     alignas(16) int16_t bc_tab[GEMM_MAX_SLOTS][2][BN];  // bias + bias-noise delta per pair slot and sign
     alignas(16) int8_t d_tab[GEMM_MAX_SLOTS][BN];       // B-noise of the next projection (EPI_GELU)
+    alignas(16) int32_t rowpart[4][GEMM_BM];            // row-per-lane epilogues: per-row partial of each column quarter
     alignas(16) int8_t act_lut[256];
     alignas(16) int32_t exp_lut[256];
     alignas(8) uint64_t full[GEMM_STAGES];
@@ -141,22 +142,16 @@ __device__ __forceinline__ int adam_apply(float &m, float &v, float &acc, int &w
 // shuffles and about half the instructions of the transposed form.  TMEM loads are double-buffered.
 template <int BN, int EPI>
 __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &sm, uint32_t taddr, int r, bool row_ok, int n0,
-                                             int cbase, int slot, int sgn, int32_t (*st)[20], int lane, int m0q) {
+                                             int cbase, int slot, int sgn, int32_t (*st)[20], int lane, int m0q, int xbs,
+                                             const int4 (&rs_pre)[BN / 4 / 16]) {
     constexpr int NCH = BN / 4 / 16;                       // 16-column chunks of this warp's quarter of the tile
     const int rc = row_ok ? r : (p.M - 1);
     const int mem = rc / p.seq_len;
     const int part = (EPI == EPI_QKV) ? (n0 / p.third) : 0;
-    const int xbv = p.xb[(int64_t)rc * p.xb_stride + part];
-    const int xbs = sgn ? -xbv : xbv;
     const int32_t *a32 = sm.rpl.a32[slot] + cbase;
     const int32_t *bcs = sm.rpl.bcs32[slot][sgn] + cbase;
     const int8_t *dt = sm.d_tab[slot] + cbase;
     const int64_t gofs = (int64_t)rc * p.N + n0 + cbase;
-    int4 rs_pre[NCH];                                      // residual bytes of every chunk (EPI_PRE32)
-    if (EPI == EPI_PRE32) {
-#pragma unroll
-        for (int c = 0; c < NCH; c++) rs_pre[c] = *reinterpret_cast<const int4 *>(p.resid + gofs + 16 * c);
-    }
     const int2 *rope = p.rope_t + (rc - mem * p.seq_len);                                // column of this token position
     const bool do_rope = (EPI == EPI_QKV) && part < 2;
     const long long half_ulp = 1ll << (p.rope_bit - 1);
@@ -178,7 +173,6 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
         uint32_t *vc = v[c & 1];
         ptx::tmem_ld_wait16(vc);
         if (c + 1 < NCH) ptx::tmem_ld16(taddr + 16 * (c + 1), v[(c + 1) & 1]);
-        uint32_t outw[4];
 #pragma unroll
         for (int q4 = 0; q4 < 4; q4++) {
             const int col = 16 * c + 4 * q4;
@@ -190,12 +184,14 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
             if (EPI == EPI_GELU) {
                 // ((acc + r1) >> s) + b  ==  (acc + r1 + (b << s)) >> s
                 const int4 b4 = *reinterpret_cast<const int4 *>(bcs + col);
-                const int z0 = min(max((x0 + b4.x) >> p.out_shift, -127), 127), z1 = min(max((x1 + b4.y) >> p.out_shift, -127), 127);
-                const int z2 = min(max((x2 + b4.z) >> p.out_shift, -127), 127), z3 = min(max((x3 + b4.w) >> p.out_shift, -127), 127);
-                const uint32_t u0 = (uint8_t)sm.act_lut[z0 & 0xFF], u1 = (uint8_t)sm.act_lut[z1 & 0xFF];
-                const uint32_t u2 = (uint8_t)sm.act_lut[z2 & 0xFF], u3 = (uint8_t)sm.act_lut[z3 & 0xFF];
-                outw[q4] = __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
-                racc = __dp4a((int)outw[q4], *reinterpret_cast<const int32_t *>(dt + col), racc);
+                // saturate to [-128, 127] while packing; the table entry of -128 holds the value of -127 (the reference's clip)
+                const uint32_t z = ptx::pack_sat_s8((x0 + b4.x) >> p.out_shift, (x1 + b4.y) >> p.out_shift, (x2 + b4.z) >> p.out_shift,
+                                                    (x3 + b4.w) >> p.out_shift);
+                const uint32_t u0 = (uint8_t)sm.act_lut[z & 0xFF], u1 = (uint8_t)sm.act_lut[(z >> 8) & 0xFF];
+                const uint32_t u2 = (uint8_t)sm.act_lut[(z >> 16) & 0xFF], u3 = (uint8_t)sm.act_lut[z >> 24];
+                const uint32_t w = __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
+                racc = __dp4a((int)w, *reinterpret_cast<const int32_t *>(dt + col), racc);
+                st[lane][4 * c + q4] = (int32_t)w;
             } else if (EPI == EPI_PRE32) {
                 const int4 b4 = *reinterpret_cast<const int4 *>(bcs + col);
                 const int32_t rs = q4 == 0 ? rs_pre[c].x : (q4 == 1 ? rs_pre[c].y : (q4 == 2 ? rs_pre[c].z : rs_pre[c].w));
@@ -231,13 +227,28 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
             }
             __syncwarp();
         }
-        if (EPI == EPI_GELU && row_ok) *reinterpret_cast<int4 *>(p.out8 + gofs + 16 * c) = make_int4(outw[0], outw[1], outw[2], outw[3]);
     }
-    if (row_ok) {
-        if (EPI == EPI_GELU) atomicAdd(&p.rowstat[rc], racc);
-        else if (EPI == EPI_PRE32) atomicMax(&p.rowstat[rc], racc);
-        else if (EPI == EPI_QKV) atomicMax(&p.rowstat[(int64_t)rc * 3 + part], racc);
+    if (EPI == EPI_GELU) {
+        // the lane's 4*NCH packed words (its row's quarter of the tile) leave through the same transpose: one store
+        // instruction then covers 8 rows x (BN/4) contiguous bytes
+        __syncwarp();
+        const int lrow = lane >> 2, pc = lane & 3;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int rr = m0q + i * 8 + lrow;
+            int8_t *dst = p.out8 + (int64_t)rr * p.N + n0 + cbase + NCH * 4 * pc;
+            if (NCH == 4) {
+                const int4 o = *reinterpret_cast<const int4 *>(&st[i * 8 + lrow][4 * pc]);
+                if (rr < p.M) *reinterpret_cast<int4 *>(dst) = o;
+            } else {
+                const int2 o = *reinterpret_cast<const int2 *>(&st[i * 8 + lrow][2 * pc]);
+                if (rr < p.M) *reinterpret_cast<int2 *>(dst) = o;
+            }
+        }
+        __syncwarp();
     }
+    // per-row partial of this column quarter; the quarters are combined after the end-of-tile barrier
+    sm.rowpart[cbase / (BN / 4)][m0q + lane - (m0q & ~(GEMM_BM - 1))] = racc;
 }
 
 template <int BN, int EPI, int RPL>
@@ -413,6 +424,19 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     aux[i] = p.dataset[pos + t + 1];
                 }
             }
+            // row-per-lane form: the lane's rank-1 factor and residual bytes, loaded before the accumulator wait
+            int xbs_l = 0;
+            int4 rs_l[BN / 4 / 16];
+            if (RPL && active) {
+                const int rc = row_ok ? r : (p.M - 1);
+                const int xbv = p.xb[(int64_t)rc * p.xb_stride + ((EPI == EPI_QKV) ? (n0 / p.third) : 0)];
+                xbs_l = sgn ? -xbv : xbv;
+                if (EPI == EPI_PRE32) {
+#pragma unroll
+                    for (int cc = 0; cc < BN / 4 / 16; cc++)
+                        rs_l[cc] = *reinterpret_cast<const int4 *>(p.resid + (int64_t)rc * p.N + n0 + cbase + 16 * cc);
+                }
+            }
             int32_t rs_pre[COLS_PER / 16][4];        // residual bytes of every chunk (EPI_PRE32)
             if (EPI == EPI_PRE32 && active && !RPL) {
 #pragma unroll
@@ -436,7 +460,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (!active) {
                 // nothing to compute; still takes part in the barrier protocol below
             } else if (RPL) {
-                epilogue_rpl<BN, EPI>(p, sm, taddr, r, row_ok, n0, cbase, slot, sgn, sm.stage[ew], lane, m0 + quarter * 32);
+                epilogue_rpl<BN, EPI>(p, sm, taddr, r, row_ok, n0, cbase, slot, sgn, sm.stage[ew], lane, m0 + quarter * 32, xbs_l, rs_l);
             } else if (EPI <= EPI_HEAD) {
                 // ---------------- evaluation epilogues ----------------
                 // Accumulators leave TMEM one row per lane; they are transposed through shared memory so
@@ -629,6 +653,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (lane == 0) ptx::mbar_arrive(&sm.tmem_empty[as]);
             // tables are rewritten at the top of the next tile: everybody must be done reading them
             ptx::named_bar_sync(1, GEMM_EPI_THREADS);
+            if (RPL && half == 0 && row_ok) {
+                // one atomic per row and tile instead of one per column quarter
+                const int a0 = sm.rowpart[0][row_in_tile], a1 = sm.rowpart[1][row_in_tile], a2 = sm.rowpart[2][row_in_tile],
+                          a3 = sm.rowpart[3][row_in_tile];
+                if (EPI == EPI_GELU) atomicAdd(&p.rowstat[r], a0 + a1 + a2 + a3);
+                else if (EPI == EPI_PRE32) atomicMax(&p.rowstat[r], max(max(a0, a1), max(a2, a3)));
+                else if (EPI == EPI_QKV) atomicMax(&p.rowstat[(int64_t)r * 3 + n0 / p.third], max(max(a0, a1), max(a2, a3)));
+            }
         }
     }
 
