@@ -135,6 +135,54 @@ __device__ __forceinline__ int adam_apply(float &m, float &v, float &acc, int &w
     return quantized_step(acc, w);
 }
 
+// ---- per-tile epilogue tables ----
+// One work item = 4 consecutive columns of one pair slot; GEMM_MAX_SLOTS * BN / 4 <= GEMM_EPI_THREADS, so a thread has at
+// most one.  Split into the global loads and the shared-memory stores so that the loads of the NEXT tile can be in
+// flight while the current one is computed.
+struct TabWords { int32_t a, b, cp, cn, d; };
+
+template <int BN, int EPI>
+__device__ __forceinline__ bool tab_load(const GemmParams &p, int e, int m0, int n0, TabWords &w) {
+    const int last_row = min(m0 + GEMM_BM, p.M) - 1;
+    const int first_pl = (m0 / p.seq_len) >> 1;
+    const int nslots = ((last_row / p.seq_len) >> 1) - first_pl + 1;
+    if (e >= nslots * (BN / 4)) return false;
+    const int sl = e / (BN / 4), j = (e % (BN / 4)) * 4;
+    const int8_t *base = p.nt + (int64_t)(first_pl + sl) * p.nt_stride;
+    w.a = *reinterpret_cast<const int32_t *>(base + p.nt_a_off + n0 + j);
+    w.b = 0; w.cp = 0; w.cn = 0; w.d = 0;
+    if (EPI == EPI_GELU || EPI == EPI_PRE32) {
+        if (p.bias) w.b = *reinterpret_cast<const int32_t *>(p.bias + n0 + j);
+        if (p.nt_c_off >= 0) {
+            w.cp = *reinterpret_cast<const int32_t *>(base + p.nt_c_off + n0 + j);
+            w.cn = *reinterpret_cast<const int32_t *>(base + p.nt_c_off + p.N + n0 + j);
+        }
+    }
+    if (EPI == EPI_GELU) w.d = *reinterpret_cast<const int32_t *>(base + p.nt_d_off + n0 + j);
+    return true;
+}
+
+template <int BN, int EPI, int RPL>
+__device__ __forceinline__ void tab_store(const GemmParams &p, GemmSmem<BN> &sm, int e, const TabWords &w) {
+    const int sl = e / (BN / 4), j = (e % (BN / 4)) * 4;
+    if (RPL) *reinterpret_cast<int4 *>(&sm.rpl.a32[sl][j]) = make_int4((int)(int8_t)w.a, (int)(int8_t)(w.a >> 8), (int)(int8_t)(w.a >> 16), w.a >> 24);
+    else *reinterpret_cast<int32_t *>(&sm.a_tab[sl][j]) = w.a;
+    if (EPI == EPI_GELU || EPI == EPI_PRE32) {
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            const int bb = (int)(int8_t)(w.b >> (8 * b));
+            if (RPL) {
+                sm.rpl.bcs32[sl][0][j + b] = (bb + (int)(int8_t)(w.cp >> (8 * b))) << p.out_shift;
+                sm.rpl.bcs32[sl][1][j + b] = (bb + (int)(int8_t)(w.cn >> (8 * b))) << p.out_shift;
+            } else {
+                sm.bc_tab[sl][0][j + b] = (int16_t)(bb + (int)(int8_t)(w.cp >> (8 * b)));
+                sm.bc_tab[sl][1][j + b] = (int16_t)(bb + (int)(int8_t)(w.cn >> (8 * b)));
+            }
+        }
+    }
+    if (EPI == EPI_GELU) *reinterpret_cast<int32_t *>(&sm.d_tab[sl][j]) = w.d;
+}
+
 // ---- row-per-lane evaluation epilogues ----
 // Used when every warp's 32 accumulator rows belong to one population member (seq_len % 32 == 0): the rank-1 factor,
 // pair slot and sign are then per-lane scalars and the per-column tables are read at warp-uniform addresses, so the
@@ -356,42 +404,18 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const int r = m0 + row_in_tile;
             const bool row_ok = r < p.M;
 
-            // ---- per-tile tables (evaluation epilogues) ----
+            // ---- per-tile tables (evaluation epilogues): built here for a block's first tile, otherwise already
+            // written at the end of the previous tile from words prefetched during its epilogue ----
             int first_pl = 0, slot = 0, sgn = 0;
             if (EPI <= EPI_HEAD) {
                 int last_row = min(m0 + GEMM_BM, p.M) - 1;
                 first_pl = (m0 / p.seq_len) >> 1;
-                int nslots = ((last_row / p.seq_len) >> 1) - first_pl + 1;
                 int mem = (row_ok ? r : last_row) / p.seq_len;
                 slot = (mem >> 1) - first_pl;
                 sgn = mem & 1;
-                for (int i = e; i < nslots * (BN / 4); i += GEMM_EPI_THREADS) {
-                    int sl = i / (BN / 4), j = (i % (BN / 4)) * 4;
-                    const int8_t *base = p.nt + (int64_t)(first_pl + sl) * p.nt_stride;
-                    const int32_t a4w = *reinterpret_cast<const int32_t *>(base + p.nt_a_off + n0 + j);
-                    if (RPL) *reinterpret_cast<int4 *>(&sm.rpl.a32[sl][j]) = make_int4((int)(int8_t)a4w, (int)(int8_t)(a4w >> 8), (int)(int8_t)(a4w >> 16), a4w >> 24);
-                    else *reinterpret_cast<int32_t *>(&sm.a_tab[sl][j]) = a4w;
-                    if (EPI == EPI_GELU || EPI == EPI_PRE32) {
-                        int32_t b4 = p.bias ? *reinterpret_cast<const int32_t *>(p.bias + n0 + j) : 0;
-                        int32_t cp = 0, cn = 0;
-                        if (p.nt_c_off >= 0) {
-                            cp = *reinterpret_cast<const int32_t *>(base + p.nt_c_off + n0 + j);
-                            cn = *reinterpret_cast<const int32_t *>(base + p.nt_c_off + p.N + n0 + j);
-                        }
-#pragma unroll
-                        for (int b = 0; b < 4; b++) {
-                            int bb = (int)(int8_t)(b4 >> (8 * b));
-                            if (RPL) {
-                                sm.rpl.bcs32[sl][0][j + b] = (bb + (int)(int8_t)(cp >> (8 * b))) << p.out_shift;
-                                sm.rpl.bcs32[sl][1][j + b] = (bb + (int)(int8_t)(cn >> (8 * b))) << p.out_shift;
-                            } else {
-                                sm.bc_tab[sl][0][j + b] = (int16_t)(bb + (int)(int8_t)(cp >> (8 * b)));
-                                sm.bc_tab[sl][1][j + b] = (int16_t)(bb + (int)(int8_t)(cn >> (8 * b)));
-                            }
-                        }
-                    }
-                    if (EPI == EPI_GELU)
-                        *reinterpret_cast<int32_t *>(&sm.d_tab[sl][j]) = *reinterpret_cast<const int32_t *>(base + p.nt_d_off + n0 + j);
+                if (tcount == 0) {
+                    TabWords w;
+                    if (tab_load<BN, EPI>(p, e, m0, n0, w)) tab_store<BN, EPI, RPL>(p, sm, e, w);
                 }
             }
             // ---- per-row state of the 4 rows this lane owns after the transpose, and the loads that do not
@@ -454,6 +478,13 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             ptx::named_bar_sync(1, GEMM_EPI_THREADS);
             if (!sm.epi_ok) break;
             ptx::tc_fence_after();
+            // words of the next tile's tables: in flight while this tile is computed
+            TabWords nxt;
+            bool have_nxt = false;
+            if (EPI <= EPI_HEAD) {
+                const int ntile = tile + gridDim.x;
+                if (ntile < num_tiles) have_nxt = tab_load<BN, EPI>(p, e, (ntile / tiles_n) * GEMM_BM, (ntile % tiles_n) * BN, nxt);
+            }
 
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * BN + half * COLS_PER);
 
@@ -661,6 +692,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 else if (EPI == EPI_PRE32) atomicMax(&p.rowstat[r], max(max(a0, a1), max(a2, a3)));
                 else if (EPI == EPI_QKV) atomicMax(&p.rowstat[(int64_t)r * 3 + n0 / p.third], max(max(a0, a1), max(a2, a3)));
             }
+            if (EPI <= EPI_HEAD && have_nxt) tab_store<BN, EPI, RPL>(p, sm, e, nxt);   // published by the next tile's barrier
         }
     }
 
