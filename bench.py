@@ -176,6 +176,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--pop", type=int, default=POP_PER_GPU, help="members per GPU (benchmark value: 40960)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--wave", type=int, default=0, help="members per internal wave (0: the library's default)")
     ap.add_argument("--small", action="store_true", help="profiling-sized run: 1024 members, one warm-up step, no end-to-end / CPU legs")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -205,7 +206,7 @@ def main():
 
     pop = args.pop * world                       # weak scaling: fixed members per GPU
     cfg = pkg.default_config(population_size=pop, **C2)
-    ctx = pkg.Context(cfg, local_rank, 0)
+    ctx = pkg.Context(cfg, local_rank, args.wave)
     model = synth.random_model(cfg, 0, "uniform")
     ctx.upload_model(model)
     data_np = synth.zipf_bytes(1, DATA_LEN)

@@ -85,13 +85,20 @@ struct GemmSmem {
     alignas(1024) uint8_t a[GEMM_STAGES][GEMM_BM * GEMM_BK];
     alignas(1024) uint8_t b[GEMM_STAGES][BN * GEMM_BK];
     alignas(16) int32_t stage[GEMM_EPI_WARPS][32][20];  // per epilogue warp: 32 rows x 16 columns (+4 pad) transpose buffer
-    struct {                                            // row-per-lane epilogues: tables widened to int32, read as uniform LDS.128
-        alignas(16) int32_t a32[GEMM_MAX_SLOTS][BN];        // A-noise of this projection per pair slot
-        alignas(16) int32_t bcs32[GEMM_MAX_SLOTS][2][BN];   // (bias + bias-noise delta) << out_shift per pair slot and sign
-    } rpl;
-    alignas(16) int8_t a_tab[GEMM_MAX_SLOTS][BN];       // A-noise of this projection per pair slot
-    alignas(16) int16_t bc_tab[GEMM_MAX_SLOTS][2][BN];  // bias + bias-noise delta per pair slot and sign
+    union {
+        struct {                                            // transposed epilogues: compact tables
+            alignas(16) int8_t a_tab[GEMM_MAX_SLOTS][BN];       // A-noise of this projection per pair slot
+            alignas(16) int16_t bc_tab[GEMM_MAX_SLOTS][2][BN];  // bias + bias-noise delta per pair slot and sign
+        };
+        struct {                                            // row-per-lane epilogues: tables widened to int32, read as uniform LDS.128
+            alignas(16) int32_t a32[GEMM_MAX_SLOTS][BN];        // A-noise of this projection per pair slot
+            alignas(16) int32_t bcs32[GEMM_MAX_SLOTS][2][BN];   // (bias + bias-noise delta) << out_shift per pair slot and sign
+        } rpl;
+    };
     alignas(16) int8_t d_tab[GEMM_MAX_SLOTS][BN];       // B-noise of the next projection (EPI_GELU)
+    // GELU table for the row-per-lane epilogue: every lane looks up its own row's value, so a single 256-byte
+    // table would serialise on bank conflicts; 16 word-wide copies put lane l's entry in bank l % 16 (+16 * (i & 1))
+    alignas(16) uint32_t lut16[256][16];
     alignas(16) int32_t rowpart[4][GEMM_BM];            // row-per-lane epilogues: per-row partial of each column quarter
     alignas(16) int8_t act_lut[256];
     alignas(16) int32_t exp_lut[256];
@@ -221,6 +228,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
         uint32_t *vc = v[c & 1];
         ptx::tmem_ld_wait16(vc);
         if (c + 1 < NCH) ptx::tmem_ld16(taddr + 16 * (c + 1), v[(c + 1) & 1]);
+        uint32_t outw[4];
 #pragma unroll
         for (int q4 = 0; q4 < 4; q4++) {
             const int col = 16 * c + 4 * q4;
@@ -235,11 +243,12 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                 // saturate to [-128, 127] while packing; the table entry of -128 holds the value of -127 (the reference's clip)
                 const uint32_t z = ptx::pack_sat_s8((x0 + b4.x) >> p.out_shift, (x1 + b4.y) >> p.out_shift, (x2 + b4.z) >> p.out_shift,
                                                     (x3 + b4.w) >> p.out_shift);
-                const uint32_t u0 = (uint8_t)sm.act_lut[z & 0xFF], u1 = (uint8_t)sm.act_lut[(z >> 8) & 0xFF];
-                const uint32_t u2 = (uint8_t)sm.act_lut[(z >> 16) & 0xFF], u3 = (uint8_t)sm.act_lut[z >> 24];
+                const uint32_t *lut = &sm.lut16[0][lane & 15];
+                const uint32_t u0 = lut[(z & 0xFF) * 16], u1 = lut[((z >> 8) & 0xFF) * 16];
+                const uint32_t u2 = lut[((z >> 16) & 0xFF) * 16], u3 = lut[(z >> 24) * 16];
                 const uint32_t w = __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
                 racc = __dp4a((int)w, *reinterpret_cast<const int32_t *>(dt + col), racc);
-                st[lane][4 * c + q4] = (int32_t)w;
+                outw[q4] = w;
             } else if (EPI == EPI_PRE32) {
                 const int4 b4 = *reinterpret_cast<const int4 *>(bcs + col);
                 const int32_t rs = q4 == 0 ? rs_pre[c].x : (q4 == 1 ? rs_pre[c].y : (q4 == 2 ? rs_pre[c].z : rs_pre[c].w));
@@ -262,6 +271,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                 *reinterpret_cast<int4 *>(&st[lane][4 * q4]) = make_int4(x0, x1, x2, x3);
             }
         }
+        if (EPI == EPI_GELU) *reinterpret_cast<int4 *>(&st[lane][4 * c]) = make_int4(outw[0], outw[1], outw[2], outw[3]);
         if (EPI == EPI_PRE32 || EPI == EPI_QKV) {
             // int32 results leave through a 32 x 16 shared-memory transpose: a lane writing its own row would
             // spread every store instruction over 32 cache lines; this way one covers 8 rows x 64 contiguous bytes
@@ -328,6 +338,12 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         int e = threadIdx.x - 64;
         if (EPI == EPI_GELU && p.act_lut && e < 256) sm.act_lut[e] = p.act_lut[e == 0x80 ? 0x81 : e];   // saturating pack yields -128 where the reference clips to -127
         if (EPI == EPI_HEAD && p.exp_lut && e < 256) sm.exp_lut[e] = p.exp_lut[e];
+        if (EPI == EPI_GELU && RPL && p.act_lut) {
+            for (int i = e; i < 256 * 16; i += GEMM_EPI_THREADS) {
+                const int idx = i >> 4;
+                sm.lut16[idx][i & 15] = (uint32_t)(uint8_t)p.act_lut[idx == 0x80 ? 0x81 : idx];
+            }
+        }
     }
     ptx::tc_fence_before();
     __syncthreads();
@@ -397,6 +413,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const bool active = (NHALF == 4) || ew < 4;
         const int row_in_tile = quarter * 32 + lane;
         uint32_t tcount = 0;
+        int pf_xb = 0;                              // row-per-lane form: values of the next tile, loaded a tile ahead
+        int4 pf_rs0 = make_int4(0, 0, 0, 0);
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tcount++) {
             const int as = tcount & 1;
             const uint32_t aph = (tcount >> 1) & 1;
@@ -448,16 +466,21 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     aux[i] = p.dataset[pos + t + 1];
                 }
             }
-            // row-per-lane form: the lane's rank-1 factor and residual bytes, loaded before the accumulator wait
+            // row-per-lane form: the lane's rank-1 factor (raw Σ x·b of its row) and the first chunk of residual bytes
+            // were loaded during the previous tile (pf_*); only a block's first tile loads them here
             int xbs_l = 0;
             int4 rs_l[BN / 4 / 16];
             if (RPL && active) {
                 const int rc = row_ok ? r : (p.M - 1);
-                const int xbv = p.xb[(int64_t)rc * p.xb_stride + ((EPI == EPI_QKV) ? (n0 / p.third) : 0)];
-                xbs_l = sgn ? -xbv : xbv;
+                if (tcount == 0) {
+                    pf_xb = p.xb[(int64_t)rc * p.xb_stride + ((EPI == EPI_QKV) ? (n0 / p.third) : 0)];
+                    if (EPI == EPI_PRE32) pf_rs0 = *reinterpret_cast<const int4 *>(p.resid + (int64_t)rc * p.N + n0 + cbase);
+                }
+                xbs_l = sgn ? -pf_xb : pf_xb;
                 if (EPI == EPI_PRE32) {
+                    rs_l[0] = pf_rs0;
 #pragma unroll
-                    for (int cc = 0; cc < BN / 4 / 16; cc++)
+                    for (int cc = 1; cc < BN / 4 / 16; cc++)      // used one chunk of arithmetic later each
                         rs_l[cc] = *reinterpret_cast<const int4 *>(p.resid + (int64_t)rc * p.N + n0 + cbase + 16 * cc);
                 }
             }
@@ -483,7 +506,15 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             bool have_nxt = false;
             if (EPI <= EPI_HEAD) {
                 const int ntile = tile + gridDim.x;
-                if (ntile < num_tiles) have_nxt = tab_load<BN, EPI>(p, e, (ntile / tiles_n) * GEMM_BM, (ntile % tiles_n) * BN, nxt);
+                if (ntile < num_tiles) {
+                    const int nm0 = (ntile / tiles_n) * GEMM_BM, nn0 = (ntile % tiles_n) * BN;
+                    have_nxt = tab_load<BN, EPI>(p, e, nm0, nn0, nxt);
+                    if (RPL && active) {
+                        const int nr = nm0 + row_in_tile, nrc = nr < p.M ? nr : (p.M - 1);
+                        pf_xb = p.xb[(int64_t)nrc * p.xb_stride + ((EPI == EPI_QKV) ? (nn0 / p.third) : 0)];
+                        if (EPI == EPI_PRE32) pf_rs0 = *reinterpret_cast<const int4 *>(p.resid + (int64_t)nrc * p.N + nn0 + half * COLS_PER);
+                    }
+                }
             }
 
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * BN + half * COLS_PER);
