@@ -328,6 +328,14 @@ def main():
         except Exception as e:   # the baseline is reported, never allowed to break the bench line
             cpu = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference", "sample": "failed: %s" % e}
 
+    # what the GEMM's own TMA + tcgen05 loop sustains on this GPU with the accumulators dropped (operands in L2)
+    mma_loop_tops = None
+    if rank == 0 and not args.small:
+        try:
+            mma_loop_tops = ctx.measure_int8_peak(16384, 2048, 2048, 20)
+        except Exception:
+            mma_loop_tops = None
+
     gru = None
     if rank == 0 and world == 1 and not args.small:
         try:
@@ -348,7 +356,9 @@ def main():
                     "d2h_bytes_per_step": int(per * 4 + 8)},
             "gpu_launches": int(launches),
             "roofline": roof,
-            "projection_gemms": {"tops": gemm_tops, "frac_of_peak": (gemm_tops / tensor_peak) if gemm_tops else None, "peak": tensor_peak},
+            "projection_gemms": {"tops": gemm_tops, "frac_of_peak": (gemm_tops / tensor_peak) if gemm_tops else None, "peak": tensor_peak,
+                                 "mma_loop_tops_measured": mma_loop_tops,
+                                 "frac_of_mma_loop": (gemm_tops / mma_loop_tops) if (gemm_tops and mma_loop_tops) else None},
             "kernels": kernel_share,
             "clocks": clocks,
             "cpu_baseline": cpu,

@@ -1064,5 +1064,35 @@ extern "C" const char *egg_profile_name(int cls) {
     return (cls >= 0 && cls < EGG_PROF_N) ? names[cls] : "";
 }
 
+extern "C" int egg_measure_int8_peak(egg_ctx *c, int m, int n, int k, int iters, double *tops) {
+    if (!c || !tops || m <= 0 || n <= 0 || k <= 0 || iters <= 0 || m % 256 || n % 256 || k % 128) { set_error("m, n must be multiples of 256, k of 128, iters positive"); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    int8_t *a = nullptr, *b = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    int rc = EGG_OK;
+    auto cleanup = [&]() { cudaStreamSynchronize(c->stream); if (a) cudaFree(a); if (b) cudaFree(b); if (e0) cudaEventDestroy(e0); if (e1) cudaEventDestroy(e1); };
+#define MTRY(x) do { cudaError_t e_ = (x); if (e_ != cudaSuccess) { set_error("%s: %s", #x, cudaGetErrorString(e_)); cleanup(); return EGG_E_CUDA; } } while (0)
+    MTRY(cudaMalloc(&a, (size_t)m * k)); MTRY(cudaMalloc(&b, (size_t)n * k));
+    MTRY(cudaMemsetAsync(a, 0, (size_t)m * k, c->stream)); MTRY(cudaMemsetAsync(b, 0, (size_t)n * k, c->stream));
+    MTRY(cudaEventCreate(&e0)); MTRY(cudaEventCreate(&e1));
+    GemmParams g;
+    memset(&g, 0, sizeof(g));
+    g.M = m; g.N = n; g.K = k; g.seq_len = 1 << 20; g.err = c->d_err;
+    for (int i = 0; i < 3 && !rc; i++) rc = launch_gemm(c->stream, EPI_NULL, a, b, g, c->num_sms);
+    if (rc) { cleanup(); return rc; }
+    MTRY(cudaEventRecord(e0, c->stream));
+    for (int i = 0; i < iters && !rc; i++) rc = launch_gemm(c->stream, EPI_NULL, a, b, g, c->num_sms);
+    if (rc) { cleanup(); return rc; }
+    MTRY(cudaEventRecord(e1, c->stream));
+    MTRY(cudaEventSynchronize(e1));
+    float ms = 0;
+    MTRY(cudaEventElapsedTime(&ms, e0, e1));
+#undef MTRY
+    c->launches += iters + 3;
+    *tops = 2.0 * m * n * (double)k * iters / (ms * 1e-3) / 1e12;
+    cleanup();
+    return check_dev_err(c);
+}
+
 extern "C" int64_t egg_launch_count(egg_ctx *c) { return c ? c->launches : 0; }
 extern "C" int egg_wave_members(egg_ctx *c) { return c ? c->wave_members : 0; }

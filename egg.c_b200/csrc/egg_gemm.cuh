@@ -32,6 +32,7 @@ enum GemmEpi {
     EPI_ADAM = 5,    // vote tile -> ES-AdamW step on packed weights
     EPI_MUON_M = 6,  // vote tile -> m = mu*m + vote ; row-major copy of m
     EPI_VOTE = 7,    // vote tile -> int32 votes in packed index order
+    EPI_NULL = 8,    // accumulators are dropped: the loop of TMA loads and tcgen05 MMAs alone (peak measurement)
 };
 
 struct GemmParams {
@@ -652,6 +653,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         }
                     }
                 }
+            } else if (EPI == EPI_NULL) {
+                // nothing: the accumulator stage is released right away
             } else {
                 // ---------------- update epilogues: row r = output column n, tile columns = input index k ----------------
                 const int n = r;

@@ -43,6 +43,7 @@ int gemm_init() {
     if ((rc = set_attr_both<EPI_ADAM>())) return rc;
     if ((rc = set_attr_both<EPI_MUON_M>())) return rc;
     if ((rc = set_attr_both<EPI_VOTE>())) return rc;
+    if ((rc = set_attr<256, EPI_NULL>())) return rc;
     return EGG_OK;
 }
 
@@ -106,6 +107,7 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
         case EPI_ADAM: return launch_bn<EPI_ADAM>(st, bn, ta, tb, p, num_sms);
         case EPI_MUON_M: return launch_bn<EPI_MUON_M>(st, bn, ta, tb, p, num_sms);
         case EPI_VOTE: return launch_bn<EPI_VOTE>(st, bn, ta, tb, p, num_sms);
+        case EPI_NULL: return launch_one<256, EPI_NULL>(st, ta, tb, p, num_sms);
     }
     set_error("unknown epilogue %d", epi);
     return EGG_E_INVALID;

@@ -357,6 +357,14 @@ const char *egg_profile_name(int cls);
 int64_t egg_launch_count(egg_ctx *ctx);
 /* Members evaluated per internal wave (chosen at creation). */
 int egg_wave_members(egg_ctx *ctx);
+/*
+ * Measures what the tensor-core loop of the projection GEMM sustains by itself on this GPU: the same
+ * kernel (TMA loads, tcgen05.mma kind::i8, two TMEM accumulator stages) with an epilogue that drops the
+ * accumulators, on zero-filled operands A[m][k], B[n][k] small enough to stay in L2 (m, n multiples of
+ * 256, k a multiple of 128).  *tops = 2*m*n*k*iters / device time, in 1e12 int8 ops per second.  No
+ * counterpart in the reference; it is the denominator the projection GEMMs are reported against.
+ */
+int egg_measure_int8_peak(egg_ctx *ctx, int m, int n, int k, int iters, double *tops);
 
 #ifdef __cplusplus
 }
