@@ -23,7 +23,7 @@ EXPORTS = [
     "egg_apply_update", "egg_generation_host", "egg_perturbed_projection", "egg_update_reconstruct",
     "egg_update_reconstruct_noalloc", "egg_scales_bytes", "egg_upload_scales", "egg_download_scales", "egg_set_overlay_steps",
     "egg_timer_start", "egg_timer_stop", "egg_profile_enable", "egg_profile_read", "egg_profile_name", "egg_launch_count",
-    "egg_wave_members", "egg_measure_int8_peak", "egg_wire_fixed_bytes", "egg_wire_encode", "egg_wire_decode_header", "egg_wire_decode_body",
+    "egg_wave_members", "egg_measure_int8_peak", "egg_generate", "egg_wire_fixed_bytes", "egg_wire_encode", "egg_wire_decode_header", "egg_wire_decode_body",
     "egg_ternary_packed_size", "egg_ternary_pack", "egg_ternary_unpack", "egg_deggs_chunk_fitness", "egg_next_seed",
     "egg_gru_config_defaults", "egg_gru_model_bytes", "egg_gru_state_bytes", "egg_gru_create", "egg_gru_destroy",
     "egg_gru_upload_model", "egg_gru_download_model", "egg_gru_upload_states", "egg_gru_download_states", "egg_gru_set_dataset",
@@ -107,6 +107,7 @@ def lib():
         L.egg_gru_launch_count.argtypes = [vp]
         L.egg_gru_launch_count.restype = C.c_int64
         L.egg_measure_int8_peak.argtypes = [vp, C.c_int, C.c_int, C.c_int, C.c_int, P(C.c_double)]
+        L.egg_generate.argtypes = [vp, vp, C.c_int, C.c_int, C.c_uint32, C.c_float, C.c_float, C.c_float]
         L.egg_scales_bytes.argtypes = [cfgp]
         L.egg_scales_bytes.restype = C.c_int64
         L.egg_set_overlay_steps.argtypes = [C.c_void_p, C.c_int, C.c_int]
@@ -266,6 +267,13 @@ class Context:
 
     def set_overlay_steps(self, inc, dec):
         _check(lib().egg_set_overlay_steps(self._h, inc, dec))
+
+    def generate(self, seed_tokens, gen_len, seed, temp=1.0, min_p=0.0, penalty=0.0):
+        """Returns the seed tokens followed by gen_len sampled ones (uint8)."""
+        buf = np.zeros(len(seed_tokens) + gen_len, np.uint8)
+        buf[:len(seed_tokens)] = seed_tokens
+        _check(lib().egg_generate(self._h, _ptr(buf), len(seed_tokens), gen_len, seed & 0xFFFFFFFF, temp, min_p, penalty))
+        return buf
 
     def measure_int8_peak(self, m=16384, n=2048, k=2048, iters=20):
         """1e12 int8 ops/s of the GEMM's TMA + tcgen05 loop alone (accumulators dropped, operands in L2)."""

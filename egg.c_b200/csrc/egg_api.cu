@@ -726,6 +726,46 @@ extern "C" int egg_read_fitness(egg_ctx *c, int32_t *host_fitness, int pair_offs
     return EGG_OK;
 }
 
+// ---------------------------------------------------------------- sampling
+
+extern "C" int egg_generate(egg_ctx *c, uint8_t *host_tokens, int seed_len, int gen_len, uint32_t seed, float temp, float min_p,
+                            float penalty) {
+    if (!c || !host_tokens) { set_error("null argument"); return EGG_E_INVALID; }
+    if (!c->have_model) { set_error("upload a model first"); return EGG_E_STATE; }
+    const egg_config &cf = c->cfg;
+    const int total = seed_len + gen_len;
+    if (seed_len < 1 || gen_len < 0 || total > cf.seq_len || total > 256) { set_error("need 1 <= seed_len and seed_len + gen_len <= min(seq_len, 256)"); return EGG_E_INVALID; }
+    if (!(temp > 0.0f)) { set_error("temperature must be positive"); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    int8_t *kv = nullptr; uint8_t *tok = nullptr;
+    auto cleanup = [&]() { cudaStreamSynchronize(c->stream); if (kv) cudaFree(kv); if (tok) cudaFree(tok); };
+#define GTRYC(x) do { cudaError_t e_ = (x); if (e_ != cudaSuccess) { set_error("%s: %s", #x, cudaGetErrorString(e_)); cleanup(); return EGG_E_CUDA; } } while (0)
+    const size_t kvb = (size_t)cf.n_layers * 2 * total * cf.hidden_dim;
+    GTRYC(cudaMalloc(&kv, kvb)); GTRYC(cudaMalloc(&tok, 256));
+    GTRYC(cudaMemsetAsync(kv, 0, kvb, c->stream));
+    GTRYC(cudaMemsetAsync(tok, 0, 256, c->stream));
+    GTRYC(cudaMemcpyAsync(tok, host_tokens, (size_t)seed_len, cudaMemcpyHostToDevice, c->stream));
+    GenParams g;
+    memset(&g, 0, sizeof(g));
+    g.H = cf.hidden_dim; g.V = cf.vocab_size; g.head_dim = cf.head_dim; g.n_layers = cf.n_layers;
+    g.shift_attn = cf.shift_attn; g.shift_out = cf.shift_out; g.shift_logit = cf.shift_logit; g.shift_mlp_up = cf.shift_mlp_up;
+    g.shift_mlp_down = cf.shift_mlp_down; g.rope_bit = cf.rope_scale_bit;
+    g.model = c->d_model; g.L = c->L; g.act_lut = c->d_act_lut; g.exp_lut = c->d_exp_lut; g.rope_lut = c->d_rope_lut;
+    g.kv = kv; g.tokens = tok; g.seed_len = seed_len; g.gen_len = gen_len; g.seed = seed; g.temp = temp;
+    g.filter = min_p > 0.0f;
+    g.min_p_limit = g.filter ? (int32_t)(logf(min_p) * cf.softmax_exp_scale) : 0;     // kernels.cu:375
+    g.penalty_int = (int32_t)(penalty * (float)(1 << cf.shift_logit));                // kernels.cu:374
+    g.scan_block = ((cf.hidden_dim + 31) & ~31) > 1024 ? 1024 : ((cf.hidden_dim + 31) & ~31);   // EGG_BLOCK_THREADS, config.h:36-37
+    int rc = launch_generate(c->stream, g);
+    if (rc) { cleanup(); return rc; }
+    c->launches++;
+    GTRYC(cudaMemcpyAsync(host_tokens, tok, (size_t)total, cudaMemcpyDeviceToHost, c->stream));
+    GTRYC(cudaStreamSynchronize(c->stream));
+#undef GTRYC
+    cleanup();
+    return check_dev_err(c);
+}
+
 // ---------------------------------------------------------------- multi-GPU
 
 extern "C" int egg_nccl_unique_id(void *id128) {

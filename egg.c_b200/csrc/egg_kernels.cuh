@@ -96,6 +96,21 @@ struct AttnParams {
 };
 int launch_attention(cudaStream_t st, const AttnParams &p);
 
+// ---- sampling -----------------------------------------------------------------
+struct GenParams {
+    int H, V, head_dim, n_layers;
+    int shift_attn, shift_out, shift_logit, shift_mlp_up, shift_mlp_down, rope_bit;
+    const int8_t *model; ModelLayout L;
+    const int8_t *act_lut; const int32_t *exp_lut; const int32_t *rope_lut;
+    int8_t *kv;                  // [n_layers][2][seed_len + gen_len][H]
+    uint8_t *tokens;             // [seed_len + gen_len]: first seed_len given, rest written
+    int seed_len, gen_len;
+    uint32_t seed;
+    float temp; int filter, min_p_limit, penalty_int;
+    int scan_block;              // block size of the reference kernel: fixes the order of its weighted draw
+};
+int launch_generate(cudaStream_t st, const GenParams &p);
+
 // ---- weights ----------------------------------------------------------------
 // packed [K/4][N][4] -> K-major shadow [N][K]
 int launch_unpack_transpose(cudaStream_t st, const int8_t *packed, int8_t *shadow, int rows_k, int cols_n);

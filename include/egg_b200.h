@@ -147,6 +147,18 @@ int egg_compute_fitness_pairs(egg_ctx *ctx, int pair_offset, int pair_count);
 int egg_write_fitness(egg_ctx *ctx, const int32_t *host_fitness, int pair_offset, int pair_count);
 int egg_read_fitness(egg_ctx *ctx, int32_t *host_fitness, int pair_offset, int pair_count);
 
+/* ---- sampling ---------------------------------------------------------- */
+/*
+ * ≙ generate_sequence_kernel<<<1, ...>>>(buffer, seed_len, gen_len, model, kv, seed, temp, min_p, penalty)
+ * (d-eggs/src/kernels.cu:307-490, launch worker.cu:568; mgpu.cu:1154-1285, launch :1703 is the case
+ * temp = 1, min_p = 0, penalty = 0): decodes one un-perturbed stream with a KV cache.  host_tokens holds
+ * seed_len given bytes followed by room for gen_len sampled ones; seed_len >= 1 and
+ * seed_len + gen_len <= min(seq_len, 256) (the reference's RoPE table and token window).  The draw at
+ * position t uses hash_rng(seed + 555 t, 0); min_p <= 0 switches the min-p filter off.
+ */
+int egg_generate(egg_ctx *ctx, uint8_t *host_tokens, int seed_len, int gen_len, uint32_t seed,
+                 float temp, float min_p, float penalty);
+
 /* ---- multi-GPU --------------------------------------------------------- */
 /* NCCL communicator over the ranks that share one population.  The caller
  * obtains the 128-byte unique id on rank 0 and distributes it out of band. */

@@ -583,6 +583,63 @@ void oracle_eval_trace(const egg_config *cfg, const int8_t *model, const int8_t 
     free(E.rope_lut);
 }
 
+/* generate_sequence_kernel (d-eggs/src/kernels.cu:307-490; mgpu.cu:1154-1285 is the same with temp 1, no min-p
+ * filter and no penalty): one un-perturbed stream decoded token by token with a KV cache; the first seed_len
+ * tokens of `tokens` are given, the following gen_len are written.  The weighted draw walks the vocabulary in
+ * the order the kernel's block scan sees it: thread-major, thread tid owning v = tid, tid + B, ... with
+ * B = EGG_BLOCK_THREADS = min(hidden_dim rounded up to 32, 1024) (config.h:36-37). */
+void oracle_generate(const egg_config *cfg, const int8_t *model, uint8_t *tokens, int seed_len, int gen_len,
+                     uint32_t seed, float temp, float min_p, float penalty) {
+    eval_env E; env_init(&E, cfg, model, NULL);
+    const egg_config *c = cfg; const int H = c->hidden_dim, V = c->vocab_size, NL = c->n_layers;
+    const model_layout *L = &E.L; const int8_t *M = model;
+    const int total = seed_len + gen_len;
+    int8_t *x = malloc((size_t)H), *nf = malloc((size_t)H);
+    int8_t *kv = calloc((size_t)NL * 2 * total * H, 1);
+    int32_t *lg = malloc(sizeof(int32_t) * (size_t)V), *ex = malloc(sizeof(int32_t) * (size_t)V);
+    const int32_t penalty_int = (int32_t)(penalty * (float)(1 << c->shift_logit));
+    const int filter = min_p > 0.0f;
+    const int32_t min_p_limit = filter ? (int32_t)(logf(min_p) * c->softmax_exp_scale) : 0;
+    int B = (H + 31) & ~31; if (B > 1024) B = 1024;
+    for (int t = 0; t < total - 1; t++) {
+        const int tok = tokens[t];
+        for (int d = 0; d < H; d++)
+            x[d] = (int8_t)clip8((int32_t)M[L->embedding + ((int64_t)(d >> 2) * V + tok) * 4 + (d & 3)] + M[L->emb_bias + d]);
+        mlp_block(&E, -1, x, 0, 0);
+        for (int l = 0; l < NL; l++) {
+            /* the kernel's cache is [layer][k|v][total][H]; attention_block only needs one k and one v plane per layer */
+            int8_t *kc = kv + (int64_t)l * 2 * total * H, *vc = kc + (int64_t)total * H;
+            attention_block(&E, l, t, x, kc, vc, 0, 0);
+            mlp_block(&E, l, x, 0, 0);
+        }
+        standard_norm(&E, x, nf, M + L->ln_f, M + L->ln_f_bias, 0, 0, 0, 0, 0, 0, -1, -1);
+        int32_t mx = INT_MIN;
+        for (int v = 0; v < V; v++) {
+            int32_t ah = linear_projection(&E, nf, M + L->embedding, H, V, v, 0, 0, 0, 1.0f);
+            int32_t l = ah >> c->shift_logit;
+            for (int i = 0; i <= t && i < 256; i++) if (tokens[i] == (uint8_t)v) l -= penalty_int;   /* presence penalty, per occurrence */
+            lg[v] = l;
+            if (l > mx) mx = l;
+        }
+        int64_t sum = 0;
+        for (int v = 0; v < V; v++) {
+            int32_t scaled = (int32_t)((float)(lg[v] - mx) / temp);
+            ex[v] = (!filter || scaled >= min_p_limit) ? softmax_exp_lookup(&E, scaled) : 0;
+            sum += ex[v];
+        }
+        uint32_t r = oracle_hash_rng(seed + (uint32_t)t * 555u, 0);
+        int64_t thresh = sum > 0 ? (int64_t)(r % (uint64_t)sum) : 0;
+        int selected = 0; int64_t running = 0; int done = 0;
+        for (int tid = 0; tid < B && !done; tid++)
+            for (int v = tid; v < V; v += B) {
+                running += ex[v];
+                if (running > thresh) { selected = v; done = 1; break; }
+            }
+        if (t >= seed_len - 1) tokens[t + 1] = (uint8_t)selected;
+    }
+    free(x); free(nf); free(kv); free(lg); free(ex); free(E.rope_lut);
+}
+
 /* mgpu.cu:1031-1036 / 1305-1311 */
 void oracle_fitness(const int32_t *losses, int32_t *fitness, int pairs) {
     for (int i = 0; i < pairs; i++) {

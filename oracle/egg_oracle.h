@@ -61,6 +61,11 @@ void oracle_eval_trace(const egg_config *cfg, const int8_t *model, const int8_t 
                        uint32_t step_seed, int member, int8_t *x_after_layers,
                        int32_t *logits, int32_t *loss_out);
 
+/* --- sampling (generate_sequence_kernel, d-eggs/src/kernels.cu:307-490; mgpu.cu:1154-1285) ---
+ * tokens[0..seed_len) given, tokens[seed_len..seed_len+gen_len) written; min_p <= 0 disables the filter. */
+void oracle_generate(const egg_config *cfg, const int8_t *model, uint8_t *tokens, int seed_len, int gen_len,
+                     uint32_t seed, float temp, float min_p, float penalty);
+
 /* --- fitness (mgpu.cu:1031-1036, 1305-1311) --- */
 void oracle_fitness(const int32_t *losses, int32_t *fitness, int pairs);
 

@@ -90,6 +90,7 @@ def lib():
         L.oracle_eval_trace.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                                         C.c_uint32, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         L.oracle_fitness.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+        L.oracle_generate.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_uint32, C.c_float, C.c_float, C.c_float]
         L.oracle_update.restype = C.c_uint64
         L.oracle_update.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_float, C.c_int]
         L.oracle_update_scaled.restype = C.c_uint64
@@ -264,3 +265,11 @@ def gru_generation(gcfg, model, states, data, step_seed, start_idx, tokens, do_u
     lib().oracle_gru_generation(C.byref(gcfg), _p(model), _p(states), _p(data), len(data), step_seed & 0xFFFFFFFF, start_idx,
                                 tokens, 1 if do_update else 0, _p(losses), _p(fit))
     return losses, fit
+
+
+def generate(cfg, model, seed_tokens, gen_len, seed, temp=1.0, min_p=0.0, penalty=0.0):
+    """Returns the seed tokens followed by gen_len sampled ones (uint8)."""
+    buf = np.zeros(len(seed_tokens) + gen_len, np.uint8)
+    buf[:len(seed_tokens)] = seed_tokens
+    lib().oracle_generate(C.byref(cfg), _p(model), _p(buf), len(seed_tokens), gen_len, seed & 0xFFFFFFFF, temp, min_p, penalty)
+    return buf

@@ -6,6 +6,7 @@
 // compile-time configuration, built by oracle/Makefile into oracle/_ref/.
 //
 //   ref_deggs_<tag> <in.bin> <out.bin>
+//   ref_deggs_<tag> --generate <in.bin> <out.bin>      (generate_sequence_kernel, see below)
 //
 // in.bin : struct deggs_case_header, TransformerModel, AdamModel, AdaptiveScales, dataset bytes
 // out.bin: per generation: int32 losses[POPULATION_SIZE], uint64 updates, AdaptiveScales;
@@ -57,7 +58,46 @@ int main(int argc, char **argv) {
                ADAPTIVE_NOISE_INIT);
         return 0;
     }
-    if (argc < 3) die("usage: ref_deggs_<tag> in.bin out.bin | --sizes");
+    if (argc == 4 && std::string(argv[1]) == "--generate") {
+        // in : struct {u32 magic "EGGG", u32 seed, i32 seed_len, i32 gen_len, f32 temp, f32 min_p, f32 penalty, i32 cfg_check[3]},
+        //      TransformerModel, seed_len token bytes;   out: seed_len + gen_len token bytes
+        // ≙ worker.cu:563-573: generate_sequence_kernel<<<1, EGG_BLOCK_THREADS, sm_size>>>(buf, seed_len, gen_len, model, kv, seed, temp, min_p, penalty)
+        struct { uint32_t magic, seed; int32_t seed_len, gen_len; float temp, min_p, penalty; int32_t cfg_check[3]; } g;
+        FILE *f = fopen(argv[2], "rb");
+        if (!f || fread(&g, sizeof(g), 1, f) != 1 || g.magic != 0x47474745u) die("bad generate header");
+        const int want[3] = {HIDDEN_DIM, N_LAYERS, SEQ_LEN};
+        for (int i = 0; i < 3; i++) if (g.cfg_check[i] != want[i]) { fprintf(stderr, "d-eggs harness: case was made for another configuration\n"); return 3; }
+        const int total = g.seed_len + g.gen_len;
+        if (g.seed_len < 1 || g.gen_len < 0 || total > SEQ_LEN || total > 256) die("bad lengths");
+        TransformerModel *h_model = (TransformerModel *)calloc(1, sizeof(TransformerModel));
+        if (fread(h_model, sizeof(TransformerModel), 1, f) != 1) die("short model");
+        uint8_t raw[256] = {0};
+        if (fread(raw, 1, g.seed_len, f) != (size_t)g.seed_len) die("short tokens");
+        fclose(f);
+        TokenType h_buf[256] = {0};
+        for (int i = 0; i < g.seed_len; i++) h_buf[i] = raw[i];
+        CK(cudaSetDevice(0));
+        init_tables();
+        copy_tables_to_device();
+        TransformerModel *d_model; TokenType *d_buf; ActType *d_kv;
+        CK(cudaMalloc(&d_model, sizeof(TransformerModel)));
+        CK(cudaMalloc(&d_buf, 256 * sizeof(TokenType)));
+        CK(cudaMalloc(&d_kv, (size_t)N_LAYERS * 2 * total * HIDDEN_DIM));
+        CK(cudaMemset(d_kv, 0, (size_t)N_LAYERS * 2 * total * HIDDEN_DIM));
+        CK(cudaMemcpy(d_model, h_model, sizeof(TransformerModel), cudaMemcpyHostToDevice));
+        CK(cudaMemcpy(d_buf, h_buf, sizeof(h_buf), cudaMemcpyHostToDevice));
+        const size_t sm = 2 * HIDDEN_DIM + 512 + (4 * HIDDEN_DIM);
+        generate_sequence_kernel<<<1, EGG_BLOCK_THREADS, sm>>>(d_buf, g.seed_len, g.gen_len, d_model, d_kv, g.seed, g.temp, g.min_p, g.penalty);
+        CK(cudaDeviceSynchronize());
+        CK(cudaMemcpy(h_buf, d_buf, sizeof(h_buf), cudaMemcpyDeviceToHost));
+        FILE *o = fopen(argv[3], "wb");
+        if (!o) die("cannot open output");
+        for (int i = 0; i < total; i++) { uint8_t b = (uint8_t)h_buf[i]; fwrite(&b, 1, 1, o); }
+        fclose(o);
+        printf("{\"ref\": \"d-eggs generate\", \"total\": %d}\n", total);
+        return 0;
+    }
+    if (argc < 3) die("usage: ref_deggs_<tag> in.bin out.bin | --generate in.bin out.bin | --sizes");
     FILE *f = fopen(argv[1], "rb");
     if (!f) die("cannot open input");
     deggs_case_header h;

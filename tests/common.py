@@ -182,3 +182,20 @@ def run_ref_gru(model, data, step_seed, tokens, steps=1, pairs=None):
     out["model"] = np.frombuffer(raw, np.int8, sizes["model_bytes"], o).copy(); o += sizes["model_bytes"]
     out["states"] = np.frombuffer(raw, np.int8, pop * sizes["n_layers"] * sizes["hidden_dim"], o).copy()
     return out
+
+
+def run_ref_generate(tag, model, seed_tokens, gen_len, seed, temp, min_p, penalty):
+    """Runs the d-eggs generate_sequence_kernel (oracle/_ref/ref_deggs_<tag> --generate) on the visible GPU."""
+    exe = deggs_binary(tag)
+    assert exe, "d-eggs harness %s not built" % tag
+    kw = DEGGS_CONFIGS[tag]
+    with tempfile.TemporaryDirectory() as td:
+        fin, fout = os.path.join(td, "in.bin"), os.path.join(td, "out.bin")
+        with open(fin, "wb") as f:
+            f.write(struct.pack("<IIiifff3i", 0x47474745, seed & 0xFFFFFFFF, len(seed_tokens), gen_len, temp, min_p, penalty,
+                                kw["hidden_dim"], kw["n_layers"], kw["seq_len"]))
+            f.write(np.ascontiguousarray(model, np.int8).tobytes())
+            f.write(np.ascontiguousarray(seed_tokens, np.uint8).tobytes())
+        r = subprocess.run([exe, "--generate", fin, fout], capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout + r.stderr
+        return np.frombuffer(open(fout, "rb").read(), np.uint8).copy()

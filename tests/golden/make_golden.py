@@ -6,6 +6,8 @@
                                                reference's own kernels, on seeded cases)
   python tests/golden/make_golden.py deggs    (on a B200: runs oracle/_ref/ref_deggs_*, the d-eggs
                                                worker's kernels with adaptive-noise overlays)
+  python tests/golden/make_golden.py generate (on a B200: the d-eggs generate_sequence_kernel through
+                                               the same harness binaries)
 """
 import json
 import os
@@ -91,8 +93,31 @@ def deggs(outdir):
         print("wrote", tag, "updates", r["updates"], "changed", len(changed))
 
 
+GEN_CASES = [  # (tag, seed_len, gen_len, model kind, rng seed, temperature, min_p, presence penalty)
+    ("tiny", 6, 10, "init", 1041, 0.6, 0.08, 0.2), ("tiny", 6, 10, "random_all", 7, 1.0, 0.0, 0.0),
+    ("tiny", 4, 12, "random_all", 99, 0.9, 0.3, 1.5), ("small", 12, 20, "init", 1041, 0.6, 0.08, 0.2),
+    ("small", 12, 20, "random_all", 7, 1.0, 0.0, 0.0), ("small", 1, 31, "random_all", 99, 0.9, 0.3, 1.5),
+]
+
+
+def generate(outdir):
+    """Sampled continuations of the d-eggs generate_sequence_kernel for seeded models and byte streams."""
+    from common import DEGGS_CONFIGS, make_case, run_ref_generate
+    os.makedirs(outdir, exist_ok=True)
+    out = []
+    for tag, sl, gl, kind, seed, temp, mp, pen in GEN_CASES:
+        cfg, ocfg, model, data = make_case(DEGGS_CONFIGS[tag], data_len=50000, model_kind=kind, model_seed=5)
+        toks = run_ref_generate(tag, model, data[100:100 + sl], gl, seed, temp, mp, pen)
+        out.append(dict(tag=tag, seed_len=sl, gen_len=gl, model_kind=kind, seed=seed, temp=temp, min_p=mp, penalty=pen,
+                        tokens=[int(x) for x in toks]))
+        print(tag, kind, seed, toks[sl:sl + 10])
+    json.dump(out, open(os.path.join(outdir, "ref_generate.json"), "w"), indent=0)
+
+
 if __name__ == "__main__":
-    if sys.argv[1] == "kat":
+    if sys.argv[1] == "generate":
+        generate(sys.argv[2] if len(sys.argv) > 2 else os.path.join(ROOT, "gpurun_out", "golden"))
+    elif sys.argv[1] == "kat":
         kat()
     elif sys.argv[1] == "deggs":
         deggs(sys.argv[2] if len(sys.argv) > 2 else os.path.join(ROOT, "gpurun_out", "golden"))
