@@ -23,7 +23,7 @@ EXPORTS = [
     "egg_apply_update", "egg_generation_host", "egg_perturbed_projection", "egg_update_reconstruct",
     "egg_update_reconstruct_noalloc", "egg_scales_bytes", "egg_upload_scales", "egg_download_scales", "egg_set_overlay_steps",
     "egg_timer_start", "egg_timer_stop", "egg_profile_enable", "egg_profile_read", "egg_profile_name", "egg_launch_count",
-    "egg_wave_members", "egg_measure_int8_peak", "egg_generate", "egg_wire_fixed_bytes", "egg_wire_encode", "egg_wire_decode_header", "egg_wire_decode_body",
+    "egg_wave_members", "egg_measure_int8_peak", "egg_generate", "egg_save_checkpoint", "egg_load_checkpoint", "egg_wire_fixed_bytes", "egg_wire_encode", "egg_wire_decode_header", "egg_wire_decode_body",
     "egg_ternary_packed_size", "egg_ternary_pack", "egg_ternary_unpack", "egg_deggs_chunk_fitness", "egg_next_seed",
     "egg_gru_config_defaults", "egg_gru_model_bytes", "egg_gru_state_bytes", "egg_gru_create", "egg_gru_destroy",
     "egg_gru_upload_model", "egg_gru_download_model", "egg_gru_upload_states", "egg_gru_download_states", "egg_gru_set_dataset",
@@ -108,6 +108,8 @@ def lib():
         L.egg_gru_launch_count.restype = C.c_int64
         L.egg_measure_int8_peak.argtypes = [vp, C.c_int, C.c_int, C.c_int, C.c_int, P(C.c_double)]
         L.egg_generate.argtypes = [vp, vp, C.c_int, C.c_int, C.c_uint32, C.c_float, C.c_float, C.c_float]
+        L.egg_save_checkpoint.argtypes = [vp, C.c_char_p, C.c_int64]
+        L.egg_load_checkpoint.argtypes = [vp, C.c_char_p, C.c_char_p]
         L.egg_scales_bytes.argtypes = [cfgp]
         L.egg_scales_bytes.restype = C.c_int64
         L.egg_set_overlay_steps.argtypes = [C.c_void_p, C.c_int, C.c_int]
@@ -274,6 +276,12 @@ class Context:
         buf[:len(seed_tokens)] = seed_tokens
         _check(lib().egg_generate(self._h, _ptr(buf), len(seed_tokens), gen_len, seed & 0xFFFFFFFF, temp, min_p, penalty))
         return buf
+
+    def save_checkpoint(self, directory, step):
+        _check(lib().egg_save_checkpoint(self._h, os.fsencode(directory), step))
+
+    def load_checkpoint(self, model_path, adam_path=None):
+        _check(lib().egg_load_checkpoint(self._h, os.fsencode(model_path), os.fsencode(adam_path) if adam_path else None))
 
     def measure_int8_peak(self, m=16384, n=2048, k=2048, iters=20):
         """1e12 int8 ops/s of the GEMM's TMA + tcgen05 loop alone (accumulators dropped, operands in L2)."""

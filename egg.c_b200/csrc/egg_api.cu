@@ -3,6 +3,10 @@
 // "mgpu.cu" = full_cuda_train_transformer_adam_mgpu.cu of the reference.
 #include "egg_kernels.cuh"
 
+#include <string>
+#include <sys/stat.h>
+#include <unistd.h>
+
 #include <dlfcn.h>
 #include <math.h>
 #include <stdarg.h>
@@ -481,6 +485,68 @@ extern "C" int egg_download_opt_state(egg_ctx *c, void *host_state, int64_t nbyt
     EGG_CUDA(cudaSetDevice(c->device));
     EGG_CUDA(cudaMemcpyAsync(host_state, c->d_opt, (size_t)nbytes, cudaMemcpyDeviceToHost, c->stream));
     EGG_CUDA(cudaStreamSynchronize(c->stream));
+    return EGG_OK;
+}
+
+// ---------------------------------------------------------------- checkpoint files (egg_disk_utils.h:1-81)
+
+static int write_file(const std::string &path, const void *data, size_t n) {
+    FILE *f = fopen(path.c_str(), "wb");
+    if (!f) { set_error("cannot open %s for writing", path.c_str()); return EGG_E_INVALID; }
+    size_t w = fwrite(data, 1, n, f);
+    if (fclose(f) != 0 || w != n) { set_error("short write to %s", path.c_str()); return EGG_E_INVALID; }
+    return EGG_OK;
+}
+
+static int read_file(const char *path, std::vector<uint8_t> &out, int64_t want) {
+    FILE *f = fopen(path, "rb");
+    if (!f) { set_error("cannot open %s", path); return EGG_E_INVALID; }
+    fseek(f, 0, SEEK_END);
+    long n = ftell(f);
+    fseek(f, 0, SEEK_SET);
+    if (n != want) { fclose(f); set_error("%s is %ld bytes, this configuration needs %lld", path, n, (long long)want); return EGG_E_INVALID; }
+    out.resize((size_t)n);
+    size_t r = fread(out.data(), 1, (size_t)n, f);
+    fclose(f);
+    if (r != (size_t)n) { set_error("short read from %s", path); return EGG_E_INVALID; }
+    return EGG_OK;
+}
+
+extern "C" int egg_save_checkpoint(egg_ctx *c, const char *dir, int64_t step) {
+    if (!c || !dir || step < 0) { set_error("bad checkpoint arguments"); return EGG_E_INVALID; }
+    if (!c->have_model) { set_error("upload a model first"); return EGG_E_STATE; }
+    struct stat sb;
+    if (stat(dir, &sb) == -1 && mkdir(dir, 0700) != 0) { set_error("cannot create directory %s", dir); return EGG_E_INVALID; }
+    std::vector<uint8_t> model((size_t)c->model_bytes), opt((size_t)c->opt_bytes);
+    int rc;
+    if ((rc = egg_download_model(c, model.data(), c->model_bytes))) return rc;
+    if ((rc = egg_download_opt_state(c, opt.data(), c->opt_bytes))) return rc;
+    char name_model[128], name_adam[128];
+    snprintf(name_model, sizeof(name_model), "egg_step-%08ld.model.bin", (long)step);
+    snprintf(name_adam, sizeof(name_adam), "egg_step-%08ld.adam.bin", (long)step);
+    const std::string d(dir);
+    auto relink = [&](const char *target, const char *link) {
+        const std::string lp = d + "/" + link;
+        unlink(lp.c_str());
+        (void)!symlink(target, lp.c_str());
+    };
+    if ((rc = write_file(d + "/" + name_model, model.data(), model.size()))) return rc;
+    relink(name_model, "egg_transformer_last.model.bin");
+    if ((rc = write_file(d + "/" + name_adam, opt.data(), opt.size()))) return rc;
+    relink(name_adam, "egg_transformer_last.adam.bin");
+    return EGG_OK;
+}
+
+extern "C" int egg_load_checkpoint(egg_ctx *c, const char *model_path, const char *adam_path) {
+    if (!c || !model_path) { set_error("bad checkpoint arguments"); return EGG_E_INVALID; }
+    std::vector<uint8_t> buf;
+    int rc;
+    if ((rc = read_file(model_path, buf, c->model_bytes))) return rc;
+    if ((rc = egg_upload_model(c, buf.data(), c->model_bytes))) return rc;
+    if (adam_path) {
+        if ((rc = read_file(adam_path, buf, c->opt_bytes))) return rc;
+        if ((rc = egg_upload_opt_state(c, buf.data(), c->opt_bytes))) return rc;
+    }
     return EGG_OK;
 }
 

@@ -107,6 +107,19 @@ int egg_download_model(egg_ctx *ctx, void *host_model, int64_t nbytes);
 int egg_upload_opt_state(egg_ctx *ctx, const void *host_state, int64_t nbytes);
 int egg_download_opt_state(egg_ctx *ctx, void *host_state, int64_t nbytes);
 
+/* ---- checkpoint files ---------------------------------------------------- */
+/*
+ * ≙ save_checkpoint (egg_disk_utils.h:46-68; d-eggs/include/utils/io.h:55-79): writes the raw
+ * TransformerModel bytes to <dir>/egg_step-%08ld.model.bin and the raw AdamModel bytes to
+ * <dir>/egg_step-%08ld.adam.bin (the reference hard-codes dir = "models" and creates it), then points the
+ * symlinks <dir>/egg_transformer_last.{model,adam}.bin at them.  Files written by either code base load
+ * into the other.
+ */
+int egg_save_checkpoint(egg_ctx *ctx, const char *dir, int64_t step);
+/* ≙ load_model (egg_disk_utils.h:70-81) and the matching read of the optimiser state (mgpu.cu:1431-1441);
+ * adam_path may be NULL (state stays as it is).  A file whose size differs from the struct is rejected. */
+int egg_load_checkpoint(egg_ctx *ctx, const char *model_path, const char *adam_path);
+
 /* ---- adaptive-noise overlays (d-eggs only) ------------------------------ */
 /* sizeof(AdaptiveScales) (d-eggs/include/model/definitions.h:92-142). */
 int64_t egg_scales_bytes(const egg_config *cfg);
