@@ -2,7 +2,8 @@
 // vote-threshold update) on the GPU.  The reference runs one population member at a time through the
 // whole sequence on one CPU core; here every token step is batched over the population: the six
 // perturbed matrix products of a layer become [population x K] x [K x N] int8 contractions on the
-// tensor cores (mma.sync m16n8k32, exact int32 accumulation), with the member's rank-1 term, the
+// tensor cores (mma.sync m16n8k32, exact int32 accumulation; the contraction split over the warps of a block
+// because the population is only a few hundred rows), with the member's rank-1 term, the
 // shift/clip and the GRU gate arithmetic fused behind them.  The recurrence over tokens is inherently
 // serial: a generation is seq_len dependent steps of 6*layers+3 small kernels, replayed from a CUDA graph.
 #include <math.h>
@@ -134,15 +135,20 @@ __device__ __forceinline__ void gru_mma(int (&c)[4], uint32_t a0, uint32_t a1, u
 }
 
 constexpr int GRU_BN = 32;      // outputs per block
-// Block = 4 warps x 32 members, all of them on the same 32 outputs.  Returns in r[mt][nt][e] the int8-range results
-//   clip((x·w[n] + ((xB * A[n] * sign) >> rank1_shift)) >> shift)
-// for the thread's fragment elements: member = m0 + 16*mt + g + 8*(e>>1), output = n0 + 8*nt + 2*q + (e&1).
-// xB = x·B_pair rides on the same tensor-core loop: the B vectors of the warp's 16 pairs are two more 8-column
-// operand tiles, and member row r needs only column r/2 of them, which lies in tile mt for both 16-row tiles —
-// one extra MMA per 16 rows and k-step, no reduction loop.
-__device__ __forceinline__ void gru_product(const GruMmParams &p, const GruOperand &op, int m0, int n0, int lane, int (&r)[2][4][4]) {
+constexpr int GRU_BM = 32;      // members per block
+// Block = KS warps, all on the same 32 members x 32 outputs, each over its own K / KS slice of the contraction
+// (the population is small, so parallelism has to come from the contraction: 4 warps for K = H, 8 for K = 4H).
+// A warp's fragment loop also carries xB = x·B_pair: the B vectors of the block's 16 pairs are two more
+// 8-column operand tiles, and member row r needs only column r/2 of them, which lies in tile mt for both
+// 16-row tiles — one extra MMA per 16 rows and k-step, no reduction loop.
+// The partial accumulators meet in shared memory; warp w < 4 then owns the 8-output tile nt = w and returns
+//   r[mt][e] = clip((x·w[n] + ((xB * A[n] * sign) >> rank1_shift)) >> shift)
+// for member = m0 + 16*mt + g + 8*(e>>1), output = n0 + 8*w + 2*q + (e&1).
+template <int KS>
+__device__ __forceinline__ void gru_product(const GruMmParams &p, const GruOperand &op, int m0, int n0, int warp, int lane,
+                                            int (*red)[40][32], int (&r)[2][4]) {
     const int g = lane >> 2, q = lane & 3;
-    const int K = p.K;
+    const int K = p.K, ksl = K / KS, kb = warp * ksl;
     int acc[2][4][4], xacc[2][4];
 #pragma unroll
     for (int mt = 0; mt < 2; mt++) {
@@ -150,11 +156,11 @@ __device__ __forceinline__ void gru_product(const GruMmParams &p, const GruOpera
 #pragma unroll
         for (int nt = 0; nt < 4; nt++) acc[mt][nt][0] = acc[mt][nt][1] = acc[mt][nt][2] = acc[mt][nt][3] = 0;
     }
-    const int8_t *xa = op.x + (int64_t)(m0 + g) * op.x_stride + 4 * q;
-    const int8_t *wb = op.w + (int64_t)(n0 + g) * K + 4 * q;
-    const int8_t *nbp = op.nb + (int64_t)((m0 >> 1) + g) * K + 4 * q;     // B of pair (m0/2 + 8*mt + g)
+    const int8_t *xa = op.x + (int64_t)(m0 + g) * op.x_stride + 4 * q + kb;
+    const int8_t *wb = op.w + (int64_t)(n0 + g) * K + 4 * q + kb;
+    const int8_t *nbp = op.nb + (int64_t)((m0 >> 1) + g) * K + 4 * q + kb;     // B of pair (m0/2 + 8*mt + g)
 #pragma unroll 4
-    for (int k0 = 0; k0 < K; k0 += 32) {
+    for (int k0 = 0; k0 < ksl; k0 += 32) {
         uint32_t a[2][4], b[4][2], bn[2][2];
 #pragma unroll
         for (int mt = 0; mt < 2; mt++) {
@@ -180,83 +186,101 @@ __device__ __forceinline__ void gru_product(const GruMmParams &p, const GruOpera
             gru_mma(xacc[mt], a[mt][0], a[mt][1], a[mt][2], a[mt][3], bn[mt][0], bn[mt][1]);
         }
     }
+    // partial sums -> shared memory, value index major / lane minor (conflict-free)
 #pragma unroll
-    for (int mt = 0; mt < 2; mt++)
+    for (int mt = 0; mt < 2; mt++) {
 #pragma unroll
-        for (int e2 = 0; e2 < 2; e2++) {
-            const int ml = 16 * mt + g + 8 * e2, m = m0 + ml;
-            // column (ml/2 - 8*mt) of the xB tile: held by lane 4*g + (col >> 1), element 2*e2 + (col & 1)
-            const int col = (g + 8 * e2) >> 1;
-            const int mine = (col & 1) ? xacc[mt][2 * e2 + 1] : xacc[mt][2 * e2];
-            const int xb = __shfl_sync(0xFFFFFFFFu, mine, 4 * g + (col >> 1));
-            const int sign = (m & 1) ? -1 : 1;
-            const int8_t *ar = op.na + (int64_t)(m >> 1) * p.N + n0 + 2 * q;
+        for (int nt = 0; nt < 4; nt++)
 #pragma unroll
-            for (int nt = 0; nt < 4; nt++) {
-                const int16_t a2 = *reinterpret_cast<const int16_t *>(ar + 8 * nt);
+            for (int e = 0; e < 4; e++) red[warp][(mt * 4 + nt) * 4 + e][lane] = acc[mt][nt][e];
+#pragma unroll
+        for (int e = 0; e < 4; e++) red[warp][32 + mt * 4 + e][lane] = xacc[mt][e];
+    }
+    __syncthreads();
+    if (warp < 4) {
+        int a8[2][4], x8[2][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                int sa = 0, sx = 0;
+#pragma unroll
+                for (int w = 0; w < KS; w++) { sa += red[w][(mt * 4 + warp) * 4 + e][lane]; sx += red[w][32 + mt * 4 + e][lane]; }
+                a8[mt][e] = sa; x8[mt][e] = sx;
+            }
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int e2 = 0; e2 < 2; e2++) {
+                const int ml = 16 * mt + g + 8 * e2, m = m0 + ml;
+                // column (ml/2 - 8*mt) of the xB tile: held by lane 4*g + (col >> 1), element 2*e2 + (col & 1)
+                const int col = (g + 8 * e2) >> 1;
+                const int mine = (col & 1) ? x8[mt][2 * e2 + 1] : x8[mt][2 * e2];
+                const int xb = __shfl_sync(0xFFFFFFFFu, mine, 4 * g + (col >> 1));
+                const int sign = (m & 1) ? -1 : 1;
+                const int16_t a2 = *reinterpret_cast<const int16_t *>(op.na + (int64_t)(m >> 1) * p.N + n0 + 8 * warp + 2 * q);
 #pragma unroll
                 for (int e1 = 0; e1 < 2; e1++) {
                     const int an = (int)(int8_t)(a2 >> (8 * e1));
-                    const int v = acc[mt][nt][2 * e2 + e1] + (((xb * an) * sign) >> p.rank1_shift);
-                    r[mt][nt][2 * e2 + e1] = gru_clip(v >> p.shift);
+                    const int v = a8[mt][2 * e2 + e1] + (((xb * an) * sign) >> p.rank1_shift);
+                    r[mt][2 * e2 + e1] = gru_clip(v >> p.shift);
                 }
             }
-        }
+    }
+    __syncthreads();          // the partial-sum buffer is reused by the next product
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(128) gru_mm_kernel(const GruMmParams p) {
+template <int MODE, int KS>
+__global__ void __launch_bounds__(KS * 32) gru_mm_kernel(const GruMmParams p) {
+    __shared__ int red[KS][40][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * GRU_BN;
-    const int m0 = blockIdx.y * 128 + warp * 32;
-    if (m0 >= p.pop) return;                       // population is a multiple of 32: whole warps drop out
+    const int n0 = blockIdx.x * GRU_BN, m0 = blockIdx.y * GRU_BM;      // population is a multiple of 32
     const int g = lane >> 2, q = lane & 3;
-    int r1[2][4][4], r2[2][4][4];
-    gru_product(p, p.op[0], m0, n0, lane, r1);
-    if (MODE == GRU_FT || MODE == GRU_HT) gru_product(p, p.op[1], m0, n0, lane, r2);
+    int r1[2][4], r2[2][4];
+    gru_product<KS>(p, p.op[0], m0, n0, warp, lane, red, r1);
+    if (MODE == GRU_FT || MODE == GRU_HT) gru_product<KS>(p, p.op[1], m0, n0, warp, lane, red, r2);
+    if (warp >= 4) return;
 #pragma unroll
     for (int mt = 0; mt < 2; mt++)
 #pragma unroll
         for (int e2 = 0; e2 < 2; e2++) {
             const int m = m0 + 16 * mt + g + 8 * e2;
+            const int n = n0 + 8 * warp + 2 * q;
+            int o0[2], o1[2];
 #pragma unroll
-            for (int nt = 0; nt < 4; nt++) {
-                const int n = n0 + 8 * nt + 2 * q;
-                int o0[2], o1[2];
-#pragma unroll
-                for (int e1 = 0; e1 < 2; e1++) {
-                    const int v1 = r1[mt][nt][2 * e2 + e1];
-                    if (MODE == GRU_FT) {
-                        // ft = clip(clip(b1 + b2) + bf); gated_past = ((ft + 127) * h) >> 8   (:248-252)
-                        const int ft = gru_clip(gru_clip(v1 + r2[mt][nt][2 * e2 + e1]) + (int)p.bias[n + e1]);
-                        const int h = p.state[(int64_t)m * p.state_stride + n + e1];
-                        o0[e1] = ft; o1[e1] = ((ft + 127) * h) >> 8;
-                    } else if (MODE == GRU_HT) {
-                        // ht = clip(clip(b1 + b2) + bh); h += ((ft + 127) * (ht - h)) >> 8; x = clip(h + residual)   (:257-268)
-                        const int ht = gru_clip(gru_clip(v1 + r2[mt][nt][2 * e2 + e1]) + (int)p.bias[n + e1]);
-                        const int h = p.state[(int64_t)m * p.state_stride + n + e1];
-                        const int ft = p.ft[(int64_t)m * p.N + n + e1];
-                        const int hn = gru_clip(h + (((ft + 127) * (ht - h)) >> 8));
-                        o0[e1] = hn; o1[e1] = gru_clip(hn + (int)p.x[(int64_t)m * p.N + n + e1]);
-                    } else if (MODE == GRU_PROJ) {
-                        o0[e1] = gru_clip(v1 + (int)p.x[(int64_t)m * p.N + n + e1]);          // :283-285
-                    } else {
-                        o0[e1] = v1;
-                    }
-                }
-                const uint16_t w0 = (uint16_t)((o0[0] & 0xFF) | ((o0[1] & 0xFF) << 8));
-                const uint16_t w1 = (uint16_t)((o1[0] & 0xFF) | ((o1[1] & 0xFF) << 8));
+            for (int e1 = 0; e1 < 2; e1++) {
+                const int v1 = r1[mt][2 * e2 + e1];
+                o1[e1] = 0;
                 if (MODE == GRU_FT) {
-                    *reinterpret_cast<uint16_t *>(p.ft + (int64_t)m * p.N + n) = w0;
-                    *reinterpret_cast<uint16_t *>(p.gp + (int64_t)m * p.N + n) = w1;
+                    // ft = clip(clip(b1 + b2) + bf); gated_past = ((ft + 127) * h) >> 8   (:248-252)
+                    const int ft = gru_clip(gru_clip(v1 + r2[mt][2 * e2 + e1]) + (int)p.bias[n + e1]);
+                    const int h = p.state[(int64_t)m * p.state_stride + n + e1];
+                    o0[e1] = ft; o1[e1] = ((ft + 127) * h) >> 8;
                 } else if (MODE == GRU_HT) {
-                    *reinterpret_cast<uint16_t *>(p.state + (int64_t)m * p.state_stride + n) = w0;
-                    *reinterpret_cast<uint16_t *>(p.x + (int64_t)m * p.N + n) = w1;
+                    // ht = clip(clip(b1 + b2) + bh); h += ((ft + 127) * (ht - h)) >> 8; x = clip(h + residual)   (:257-268)
+                    const int ht = gru_clip(gru_clip(v1 + r2[mt][2 * e2 + e1]) + (int)p.bias[n + e1]);
+                    const int h = p.state[(int64_t)m * p.state_stride + n + e1];
+                    const int ft = p.ft[(int64_t)m * p.N + n + e1];
+                    const int hn = gru_clip(h + (((ft + 127) * (ht - h)) >> 8));
+                    o0[e1] = hn; o1[e1] = gru_clip(hn + (int)p.x[(int64_t)m * p.N + n + e1]);
                 } else if (MODE == GRU_PROJ) {
-                    *reinterpret_cast<uint16_t *>(p.x + (int64_t)m * p.N + n) = w0;
+                    o0[e1] = gru_clip(v1 + (int)p.x[(int64_t)m * p.N + n + e1]);          // :283-285
                 } else {
-                    *reinterpret_cast<uint16_t *>(p.out + (int64_t)m * p.N + n) = w0;
+                    o0[e1] = v1;
                 }
+            }
+            const uint16_t w0 = (uint16_t)((o0[0] & 0xFF) | ((o0[1] & 0xFF) << 8));
+            const uint16_t w1 = (uint16_t)((o1[0] & 0xFF) | ((o1[1] & 0xFF) << 8));
+            if (MODE == GRU_FT) {
+                *reinterpret_cast<uint16_t *>(p.ft + (int64_t)m * p.N + n) = w0;
+                *reinterpret_cast<uint16_t *>(p.gp + (int64_t)m * p.N + n) = w1;
+            } else if (MODE == GRU_HT) {
+                *reinterpret_cast<uint16_t *>(p.state + (int64_t)m * p.state_stride + n) = w0;
+                *reinterpret_cast<uint16_t *>(p.x + (int64_t)m * p.N + n) = w1;
+            } else if (MODE == GRU_PROJ) {
+                *reinterpret_cast<uint16_t *>(p.x + (int64_t)m * p.N + n) = w0;
+            } else {
+                *reinterpret_cast<uint16_t *>(p.out + (int64_t)m * p.N + n) = w0;
             }
         }
 }
@@ -479,8 +503,7 @@ static int gru_token_step(egg_gru_ctx *c, int *nlaunch) {
     const GruLayout &L = c->L;
     cudaStream_t st = c->stream;
     const int ln_blocks = (POP + 7) / 8;
-    const dim3 mm_block(128);
-    const unsigned mby = (unsigned)((POP + 127) / 128);
+    const unsigned mby = (unsigned)(POP / GRU_BM);
     int n = 0;
     auto operand = [&](const int8_t *x, int64_t xs, const int8_t *w, const GruStream &s) {
         GruOperand o; o.x = x; o.x_stride = xs; o.w = w; o.na = c->d_noise + s.a_off; o.nb = c->d_noise + s.b_off; return o;
@@ -506,27 +529,27 @@ static int gru_token_step(egg_gru_ctx *c, int *nlaunch) {
         GruMmParams ft = base(H, H, 8);
         ft.op[0] = operand(c->d_xn, H, gw, S[0]); ft.op[1] = operand(hl, hs, gw + (int64_t)H * H, S[1]);
         ft.bias = gb; ft.state = hl; ft.state_stride = hs; ft.ft = c->d_ft; ft.gp = c->d_gp;
-        gru_mm_kernel<GRU_FT><<<dim3(H / GRU_BN, mby), mm_block, 0, st>>>(ft); n++;
+        gru_mm_kernel<GRU_FT, 4><<<dim3(H / GRU_BN, mby), 128, 0, st>>>(ft); n++;
         GruMmParams ht = base(H, H, 8);
         ht.op[0] = operand(c->d_xn, H, gw + 2 * (int64_t)H * H, S[2]); ht.op[1] = operand(c->d_gp, H, gw + 3 * (int64_t)H * H, S[3]);
         ht.bias = gb + H; ht.state = hl; ht.state_stride = hs; ht.ft = c->d_ft; ht.x = c->d_x;
-        gru_mm_kernel<GRU_HT><<<dim3(H / GRU_BN, mby), mm_block, 0, st>>>(ht); n++;
+        gru_mm_kernel<GRU_HT, 4><<<dim3(H / GRU_BN, mby), 128, 0, st>>>(ht); n++;
         GruLnParams ln2; memset(&ln2, 0, sizeof(ln2));
         ln2.pop = POP; ln2.H = H; ln2.w = lw + H; ln2.xn = c->d_xn; ln2.x_in = c->d_x;
         gru_ln_kernel<<<ln_blocks, 256, 0, st>>>(ln2); n++;
         GruMmParams ex = base(4 * H, H, 8);
         ex.op[0] = operand(c->d_xn, H, mw, S[4]); ex.out = c->d_buf;
-        gru_mm_kernel<GRU_EXP><<<dim3(4 * H / GRU_BN, mby), mm_block, 0, st>>>(ex); n++;
+        gru_mm_kernel<GRU_EXP, 4><<<dim3(4 * H / GRU_BN, mby), 128, 0, st>>>(ex); n++;
         GruMmParams pr = base(H, 4 * H, 9);
         pr.op[0] = operand(c->d_buf, 4 * H, mw + 4 * (int64_t)H * H, S[5]); pr.x = c->d_x;
-        gru_mm_kernel<GRU_PROJ><<<dim3(H / GRU_BN, mby), mm_block, 0, st>>>(pr); n++;
+        gru_mm_kernel<GRU_PROJ, 8><<<dim3(H / GRU_BN, mby), 256, 0, st>>>(pr); n++;
     }
     GruLnParams lf; memset(&lf, 0, sizeof(lf));
     lf.pop = POP; lf.H = H; lf.w = c->d_model + L.ln_out; lf.xn = c->d_xn; lf.x_in = c->d_x;
     gru_ln_kernel<<<ln_blocks, 256, 0, st>>>(lf); n++;
     GruMmParams hd = base(V, H, 8);
     hd.op[0] = operand(c->d_xn, H, c->d_model + L.head, c->streams[cf.n_layers * 6]); hd.out = c->d_logits;
-    gru_mm_kernel<GRU_HEAD><<<dim3(V / GRU_BN, mby), mm_block, 0, st>>>(hd); n++;
+    gru_mm_kernel<GRU_HEAD, 4><<<dim3(V / GRU_BN, mby), 128, 0, st>>>(hd); n++;
     GruLossParams lp; lp.pop = POP; lp.V = V; lp.logits = c->d_logits; lp.exp2_table = c->d_exp2; lp.data = c->d_data;
     lp.data_len = c->data_len; lp.start_idx = start_idx; lp.seq_len = cf.seq_len; lp.t = c->d_t; lp.loss = c->d_loss;
     gru_loss_kernel<<<ln_blocks, 256, 0, st>>>(lp); n++;
