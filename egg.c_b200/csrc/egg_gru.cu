@@ -76,7 +76,7 @@ struct GruLnParams {
     int8_t *xn;                  // [pop][H]
 };
 
-__global__ void __launch_bounds__(256) gru_ln_kernel(const GruLnParams p) {
+__global__ void __launch_bounds__(128) gru_ln_kernel(const GruLnParams p) {
     const int m = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (m >= p.pop) return;
     const int8_t *src;
@@ -95,13 +95,18 @@ __global__ void __launch_bounds__(256) gru_ln_kernel(const GruLnParams p) {
     if (sum == 0) sum = 1;                               // full_trained_egg.c:199-201
     int mean = sum / p.H;
     if (mean == 0) mean = 1;
+    // (x * w) / mean truncates toward zero; |x * w| < 2^15 and mean <= 127, so |a| / mean == (|a| * M) >> 22 with
+    // M = floor(2^22 / mean) + 1 exactly (the error term |a| * (M * mean - 2^22) stays below 2^22)
+    const int M = (1 << 22) / mean + 1;
     for (int d = lane * 4; d < p.H; d += 128) {
         const int32_t v = *reinterpret_cast<const int32_t *>(src + d);
         const int32_t w = *reinterpret_cast<const int32_t *>(p.w + d);
         uint32_t o = 0;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const int val = ((int)(int8_t)(v >> (8 * i)) * (int)(int8_t)(w >> (8 * i))) / mean;   // C division, truncating
+            const int a = (int)(int8_t)(v >> (8 * i)) * (int)(int8_t)(w >> (8 * i));
+            const int qa = (abs(a) * M) >> 22;
+            const int val = a < 0 ? -qa : qa;
             o |= (uint32_t)(gru_clip(val) & 0xFF) << (8 * i);
         }
         *reinterpret_cast<uint32_t *>(p.xn + (int64_t)m * p.H + d) = o;
@@ -502,7 +507,7 @@ static int gru_token_step(egg_gru_ctx *c, int *nlaunch) {
     const int H = cf.hidden_dim, V = cf.vocab_size, POP = cf.population_size;
     const GruLayout &L = c->L;
     cudaStream_t st = c->stream;
-    const int ln_blocks = (POP + 7) / 8;
+    const int ln_blocks = (POP + 3) / 4;          // one warp per member, 4 per block: the rows spread over more SMs
     const unsigned mby = (unsigned)(POP / GRU_BM);
     int n = 0;
     auto operand = [&](const int8_t *x, int64_t xs, const int8_t *w, const GruStream &s) {
@@ -525,7 +530,7 @@ static int gru_token_step(egg_gru_ctx *c, int *nlaunch) {
             ln.embedding = c->d_model + L.embedding; ln.data = c->d_data; ln.data_len = c->data_len; ln.start_idx = start_idx;
             ln.seq_len = cf.seq_len; ln.t = c->d_t; ln.x_out = c->d_x;
         } else ln.x_in = c->d_x;
-        gru_ln_kernel<<<ln_blocks, 256, 0, st>>>(ln); n++;
+        gru_ln_kernel<<<ln_blocks, 128, 0, st>>>(ln); n++;
         GruMmParams ft = base(H, H, 8);
         ft.op[0] = operand(c->d_xn, H, gw, S[0]); ft.op[1] = operand(hl, hs, gw + (int64_t)H * H, S[1]);
         ft.bias = gb; ft.state = hl; ft.state_stride = hs; ft.ft = c->d_ft; ft.gp = c->d_gp;
@@ -536,7 +541,7 @@ static int gru_token_step(egg_gru_ctx *c, int *nlaunch) {
         gru_mm_kernel<GRU_HT, 4><<<dim3(H / GRU_BN, mby), 128, 0, st>>>(ht); n++;
         GruLnParams ln2; memset(&ln2, 0, sizeof(ln2));
         ln2.pop = POP; ln2.H = H; ln2.w = lw + H; ln2.xn = c->d_xn; ln2.x_in = c->d_x;
-        gru_ln_kernel<<<ln_blocks, 256, 0, st>>>(ln2); n++;
+        gru_ln_kernel<<<ln_blocks, 128, 0, st>>>(ln2); n++;
         GruMmParams ex = base(4 * H, H, 8);
         ex.op[0] = operand(c->d_xn, H, mw, S[4]); ex.out = c->d_buf;
         gru_mm_kernel<GRU_EXP, 4><<<dim3(4 * H / GRU_BN, mby), 128, 0, st>>>(ex); n++;
@@ -546,13 +551,13 @@ static int gru_token_step(egg_gru_ctx *c, int *nlaunch) {
     }
     GruLnParams lf; memset(&lf, 0, sizeof(lf));
     lf.pop = POP; lf.H = H; lf.w = c->d_model + L.ln_out; lf.xn = c->d_xn; lf.x_in = c->d_x;
-    gru_ln_kernel<<<ln_blocks, 256, 0, st>>>(lf); n++;
+    gru_ln_kernel<<<ln_blocks, 128, 0, st>>>(lf); n++;
     GruMmParams hd = base(V, H, 8);
     hd.op[0] = operand(c->d_xn, H, c->d_model + L.head, c->streams[cf.n_layers * 6]); hd.out = c->d_logits;
     gru_mm_kernel<GRU_HEAD, 4><<<dim3(V / GRU_BN, mby), 128, 0, st>>>(hd); n++;
     GruLossParams lp; lp.pop = POP; lp.V = V; lp.logits = c->d_logits; lp.exp2_table = c->d_exp2; lp.data = c->d_data;
     lp.data_len = c->data_len; lp.start_idx = start_idx; lp.seq_len = cf.seq_len; lp.t = c->d_t; lp.loss = c->d_loss;
-    gru_loss_kernel<<<ln_blocks, 256, 0, st>>>(lp); n++;
+    gru_loss_kernel<<<(POP + 7) / 8, 256, 0, st>>>(lp); n++;
     gru_advance_kernel<<<1, 1, 0, st>>>(c->d_t); n++;
     EGG_CUDA(cudaGetLastError());
     *nlaunch = n;
