@@ -85,7 +85,10 @@ template <int BN>
 struct GemmSmem {
     alignas(1024) uint8_t a[GEMM_STAGES][GEMM_BM * GEMM_BK];
     alignas(1024) uint8_t b[GEMM_STAGES][BN * GEMM_BK];
-    alignas(16) int32_t stage[GEMM_EPI_WARPS][32][20];  // per epilogue warp: 32 rows x 16 columns (+4 pad) transpose buffer
+    union {
+        alignas(1024) int32_t stage[GEMM_EPI_WARPS][32][20];   // per epilogue warp: 32 rows x 16 columns (+4 pad) transpose buffer
+        alignas(1024) int32_t ostage[GEMM_EPI_WARPS][32 * 16];  // row-per-lane int32 outputs: dense 32 x 16 box per warp, 64-byte swizzle, source of a TMA store
+    };
     union {
         struct {                                            // transposed epilogues: compact tables
             alignas(16) int8_t a_tab[GEMM_MAX_SLOTS][BN];       // A-noise of this projection per pair slot
@@ -199,7 +202,7 @@ __device__ __forceinline__ void tab_store(const GemmParams &p, GemmSmem<BN> &sm,
 template <int BN, int EPI>
 __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &sm, uint32_t taddr, int r, bool row_ok, int n0,
                                              int cbase, int slot, int sgn, int32_t (*st)[20], int lane, int m0q, int xbs,
-                                             const int4 (&rs_pre)[BN / 4 / 16]) {
+                                             const int4 (&rs_pre)[BN / 4 / 16], const CUtensorMap *tmap_o, int32_t *ost) {
     constexpr int NCH = BN / 4 / 16;                       // 16-column chunks of this warp's quarter of the tile
     const int rc = row_ok ? r : (p.M - 1);
     const int mem = rc / p.seq_len;
@@ -230,6 +233,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
         ptx::tmem_ld_wait16(vc);
         if (c + 1 < NCH) ptx::tmem_ld16(taddr + 16 * (c + 1), v[(c + 1) & 1]);
         uint32_t outw[4];
+        int4 o4[4];
 #pragma unroll
         for (int q4 = 0; q4 < 4; q4++) {
             const int col = 16 * c + 4 * q4;
@@ -258,7 +262,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                 x2 = (int)(int8_t)(rs >> 16) + ((x2 + b4.z) >> p.out_shift);
                 x3 = (int)(rs >> 24) + ((x3 + b4.w) >> p.out_shift);
                 racc = max(racc, max(max(abs(x0), abs(x1)), max(abs(x2), abs(x3))));
-                *reinterpret_cast<int4 *>(&st[lane][4 * q4]) = make_int4(x0, x1, x2, x3);
+                o4[q4] = make_int4(x0, x1, x2, x3);
             } else if (EPI == EPI_QKV) {
                 if (do_rope) {
                     // integer RoPE on adjacent (even, odd) columns (apply_rope_integer, mgpu.cu:624-644)
@@ -269,22 +273,24 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                     x3 = (int)((e1 * cs[q4].w + o1 * cs[q4].z + half_ulp) >> p.rope_bit);
                 }
                 racc = max(racc, max(max(abs(x0), abs(x1)), max(abs(x2), abs(x3))));
-                *reinterpret_cast<int4 *>(&st[lane][4 * q4]) = make_int4(x0, x1, x2, x3);
+                o4[q4] = make_int4(x0, x1, x2, x3);
             }
         }
         if (EPI == EPI_GELU) *reinterpret_cast<int4 *>(&st[lane][4 * c]) = make_int4(outw[0], outw[1], outw[2], outw[3]);
         if (EPI == EPI_PRE32 || EPI == EPI_QKV) {
-            // int32 results leave through a 32 x 16 shared-memory transpose: a lane writing its own row would
-            // spread every store instruction over 32 cache lines; this way one covers 8 rows x 64 contiguous bytes
+            // int32 results leave as one TMA store per warp and chunk: each lane writes its row's 64 bytes into a dense
+            // 32 x 16 box (16-byte pieces XOR-swizzled with the row, the 64-byte pattern the tensor map expects, which
+            // also makes the stores conflict-free); the copy engine does the coalescing and clips rows beyond M
+            if (lane == 0) ptx::tma_store_wait_read<0>();       // the previous chunk's box has been read out
             __syncwarp();
-            const int lrow = lane >> 2, pc = lane & 3;
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int rr = m0q + i * 8 + lrow;
-                const int4 o = *reinterpret_cast<const int4 *>(&st[i * 8 + lrow][4 * pc]);
-                if (rr < p.M) *reinterpret_cast<int4 *>(p.out32 + (int64_t)rr * p.N + n0 + cbase + 16 * c + 4 * pc) = o;
-            }
+            for (int q4 = 0; q4 < 4; q4++) *reinterpret_cast<int4 *>(ost + lane * 16 + ((q4 ^ ((lane >> 1) & 3)) << 2)) = o4[q4];
+            ptx::fence_proxy_async();
             __syncwarp();
+            if (lane == 0) {
+                ptx::tma_store_2d(tmap_o, ost, n0 + cbase + 16 * c, m0q);
+                ptx::tma_store_commit();
+            }
         }
     }
     if (EPI == EPI_GELU) {
@@ -312,7 +318,8 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
 
 template <int BN, int EPI, int RPL>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ CUtensorMap tmap_o, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     GemmSmem<BN> &sm = *reinterpret_cast<GemmSmem<BN> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -523,7 +530,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (!active) {
                 // nothing to compute; still takes part in the barrier protocol below
             } else if (RPL) {
-                epilogue_rpl<BN, EPI>(p, sm, taddr, r, row_ok, n0, cbase, slot, sgn, sm.stage[ew], lane, m0 + quarter * 32, xbs_l, rs_l);
+                epilogue_rpl<BN, EPI>(p, sm, taddr, r, row_ok, n0, cbase, slot, sgn, sm.stage[ew], lane, m0 + quarter * 32, xbs_l, rs_l, &tmap_o,
+                                      sm.ostage[ew]);
             } else if (EPI <= EPI_HEAD) {
                 // ---------------- evaluation epilogues ----------------
                 // Accumulators leave TMEM one row per lane; they are transposed through shared memory so
@@ -730,6 +738,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
     }
 
+    // output boxes still being copied out of shared memory must land before the block retires
+    if (RPL && (EPI == EPI_PRE32 || EPI == EPI_QKV) && warp >= 2 && lane == 0) ptx::tma_store_wait_all<0>();
     __syncwarp();
     ptx::tc_fence_before();
     __syncthreads();

@@ -61,26 +61,40 @@ static int make_tmap(CUtensorMap *m, const void *ptr, uint64_t rows, uint64_t k,
     return EGG_OK;
 }
 
+// [rows][cols] int32 row-major output written by TMA stores of 16-column x 32-row boxes (64-byte swizzle in shared memory)
+static int make_tmap_out(CUtensorMap *m, const void *ptr, uint64_t rows, uint64_t cols) {
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (cols & 3)) { set_error("GEMM output is not 16-byte aligned (ptr %p, cols %llu)", ptr, (unsigned long long)cols); return EGG_E_INVALID; }
+    cuuint64_t gdim[2] = {cols, rows};
+    cuuint64_t gstride[1] = {cols * 4};
+    cuuint32_t box[2] = {16, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<void *>(ptr), gdim, gstride, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (output) failed (%d) rows=%llu cols=%llu", (int)r, (unsigned long long)rows, (unsigned long long)cols); return EGG_E_CUDA; }
+    return EGG_OK;
+}
+
 template <int BN, int EPI, int RPL = 0>
-static int launch_one(cudaStream_t st, const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int num_sms) {
+static int launch_one(cudaStream_t st, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to, const GemmParams &p, int num_sms) {
     int tiles = ((p.M + GEMM_BM - 1) / GEMM_BM) * (p.N / BN);
     int grid = tiles < num_sms ? tiles : num_sms;
-    gemm_i8_kernel<BN, EPI, RPL><<<grid, GEMM_THREADS, gemm_smem_bytes<BN>(), st>>>(ta, tb, p);
+    gemm_i8_kernel<BN, EPI, RPL><<<grid, GEMM_THREADS, gemm_smem_bytes<BN>(), st>>>(ta, tb, to, p);
     EGG_CUDA(cudaGetLastError());
     return EGG_OK;
 }
 
 template <int EPI, int RPL = 0>
-static int launch_bn(cudaStream_t st, int bn, const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int num_sms) {
-    if (bn == 256) return launch_one<256, EPI, RPL>(st, ta, tb, p, num_sms);
-    return launch_one<128, EPI, RPL>(st, ta, tb, p, num_sms);
+static int launch_bn(cudaStream_t st, int bn, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to, const GemmParams &p, int num_sms) {
+    if (bn == 256) return launch_one<256, EPI, RPL>(st, ta, tb, to, p, num_sms);
+    return launch_one<128, EPI, RPL>(st, ta, tb, to, p, num_sms);
 }
 
 // evaluation epilogues whose rows come in whole 32-row groups per member take the row-per-lane form
 template <int EPI>
-static int launch_eval(cudaStream_t st, int bn, const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int num_sms) {
-    if (p.seq_len % 32 == 0 && p.rpl >= 0) return launch_bn<EPI, 1>(st, bn, ta, tb, p, num_sms);
-    return launch_bn<EPI, 0>(st, bn, ta, tb, p, num_sms);
+static int launch_eval(cudaStream_t st, int bn, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to, const GemmParams &p, int num_sms) {
+    if (p.seq_len % 32 == 0 && p.rpl >= 0) return launch_bn<EPI, 1>(st, bn, ta, tb, to, p, num_sms);
+    return launch_bn<EPI, 0>(st, bn, ta, tb, to, p, num_sms);
 }
 
 int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, const GemmParams &p, int num_sms) {
@@ -98,16 +112,20 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
     int rc;
     if ((rc = make_tmap(&ta, A, (uint64_t)p.M, (uint64_t)p.K, GEMM_BM))) return rc;
     if ((rc = make_tmap(&tb, B, (uint64_t)p.N, (uint64_t)p.K, (uint32_t)bn))) return rc;
+    CUtensorMap to = ta;       // only the row-per-lane int32 epilogues store through a tensor map
+    if ((epi == EPI_PRE32 || epi == EPI_QKV) && p.seq_len % 32 == 0 && p.rpl >= 0) {
+        if ((rc = make_tmap_out(&to, p.out32, (uint64_t)p.M, (uint64_t)p.N))) return rc;
+    }
     switch (epi) {
-        case EPI_CLIP8: return launch_bn<EPI_CLIP8>(st, bn, ta, tb, p, num_sms);
-        case EPI_GELU: return launch_eval<EPI_GELU>(st, bn, ta, tb, p, num_sms);
-        case EPI_PRE32: return launch_eval<EPI_PRE32>(st, bn, ta, tb, p, num_sms);
-        case EPI_QKV: return launch_eval<EPI_QKV>(st, bn, ta, tb, p, num_sms);
-        case EPI_HEAD: return launch_one<256, EPI_HEAD>(st, ta, tb, p, num_sms);
-        case EPI_ADAM: return launch_bn<EPI_ADAM>(st, bn, ta, tb, p, num_sms);
-        case EPI_MUON_M: return launch_bn<EPI_MUON_M>(st, bn, ta, tb, p, num_sms);
-        case EPI_VOTE: return launch_bn<EPI_VOTE>(st, bn, ta, tb, p, num_sms);
-        case EPI_NULL: return launch_one<256, EPI_NULL>(st, ta, tb, p, num_sms);
+        case EPI_CLIP8: return launch_bn<EPI_CLIP8>(st, bn, ta, tb, to, p, num_sms);
+        case EPI_GELU: return launch_eval<EPI_GELU>(st, bn, ta, tb, to, p, num_sms);
+        case EPI_PRE32: return launch_eval<EPI_PRE32>(st, bn, ta, tb, to, p, num_sms);
+        case EPI_QKV: return launch_eval<EPI_QKV>(st, bn, ta, tb, to, p, num_sms);
+        case EPI_HEAD: return launch_one<256, EPI_HEAD>(st, ta, tb, to, p, num_sms);
+        case EPI_ADAM: return launch_bn<EPI_ADAM>(st, bn, ta, tb, to, p, num_sms);
+        case EPI_MUON_M: return launch_bn<EPI_MUON_M>(st, bn, ta, tb, to, p, num_sms);
+        case EPI_VOTE: return launch_bn<EPI_VOTE>(st, bn, ta, tb, to, p, num_sms);
+        case EPI_NULL: return launch_one<256, EPI_NULL>(st, ta, tb, to, p, num_sms);
     }
     set_error("unknown epilogue %d", epi);
     return EGG_E_INVALID;
