@@ -276,7 +276,18 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                 o4[q4] = make_int4(x0, x1, x2, x3);
             }
         }
-        if (EPI == EPI_GELU) *reinterpret_cast<int4 *>(&st[lane][4 * c]) = make_int4(outw[0], outw[1], outw[2], outw[3]);
+        if (EPI == EPI_GELU) {
+            if (NCH == 4) {
+                // 64 output bytes per lane and tile: same dense swizzled box as below, one TMA store per warp and tile
+                if (c == 0) {
+                    if (lane == 0) ptx::tma_store_wait_read<0>();
+                    __syncwarp();
+                }
+                *reinterpret_cast<int4 *>(ost + lane * 16 + ((c ^ ((lane >> 1) & 3)) << 2)) = make_int4(outw[0], outw[1], outw[2], outw[3]);
+            } else {
+                *reinterpret_cast<int4 *>(&st[lane][4 * c]) = make_int4(outw[0], outw[1], outw[2], outw[3]);
+            }
+        }
         if (EPI == EPI_PRE32 || EPI == EPI_QKV) {
             // int32 results leave as one TMA store per warp and chunk: each lane writes its row's 64 bytes into a dense
             // 32 x 16 box (16-byte pieces XOR-swizzled with the row, the 64-byte pattern the tensor map expects, which
@@ -293,7 +304,14 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
             }
         }
     }
-    if (EPI == EPI_GELU) {
+    if (EPI == EPI_GELU && NCH == 4) {
+        ptx::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+            ptx::tma_store_2d(tmap_o, ost, n0 + cbase, m0q);
+            ptx::tma_store_commit();
+        }
+    } else if (EPI == EPI_GELU) {
         // the lane's 4*NCH packed words (its row's quarter of the tile) leave through the same transpose: one store
         // instruction then covers 8 rows x (BN/4) contiguous bytes
         __syncwarp();
@@ -739,7 +757,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
 
     // output boxes still being copied out of shared memory must land before the block retires
-    if (RPL && (EPI == EPI_PRE32 || EPI == EPI_QKV) && warp >= 2 && lane == 0) ptx::tma_store_wait_all<0>();
+    if (RPL && (EPI == EPI_PRE32 || EPI == EPI_QKV || EPI == EPI_GELU) && warp >= 2 && lane == 0) ptx::tma_store_wait_all<0>();
     __syncwarp();
     ptx::tc_fence_before();
     __syncthreads();

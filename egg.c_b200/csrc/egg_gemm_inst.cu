@@ -75,6 +75,20 @@ static int make_tmap_out(CUtensorMap *m, const void *ptr, uint64_t rows, uint64_
     return EGG_OK;
 }
 
+// [rows][cols] int8 row-major output written by TMA stores of 64-column x 32-row boxes (64-byte swizzle)
+static int make_tmap_out8(CUtensorMap *m, const void *ptr, uint64_t rows, uint64_t cols) {
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (cols & 15)) { set_error("GEMM output is not 16-byte aligned (ptr %p, cols %llu)", ptr, (unsigned long long)cols); return EGG_E_INVALID; }
+    cuuint64_t gdim[2] = {cols, rows};
+    cuuint64_t gstride[1] = {cols};
+    cuuint32_t box[2] = {64, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), gdim, gstride, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (int8 output) failed (%d) rows=%llu cols=%llu", (int)r, (unsigned long long)rows, (unsigned long long)cols); return EGG_E_CUDA; }
+    return EGG_OK;
+}
+
 template <int BN, int EPI, int RPL = 0>
 static int launch_one(cudaStream_t st, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to, const GemmParams &p, int num_sms) {
     int tiles = ((p.M + GEMM_BM - 1) / GEMM_BM) * (p.N / BN);
@@ -115,6 +129,9 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
     CUtensorMap to = ta;       // only the row-per-lane int32 epilogues store through a tensor map
     if ((epi == EPI_PRE32 || epi == EPI_QKV) && p.seq_len % 32 == 0 && p.rpl >= 0) {
         if ((rc = make_tmap_out(&to, p.out32, (uint64_t)p.M, (uint64_t)p.N))) return rc;
+    }
+    if (epi == EPI_GELU && bn == 256 && p.seq_len % 32 == 0 && p.rpl >= 0) {
+        if ((rc = make_tmap_out8(&to, p.out8, (uint64_t)p.M, (uint64_t)p.N))) return rc;
     }
     switch (epi) {
         case EPI_CLIP8: return launch_bn<EPI_CLIP8>(st, bn, ta, tb, to, p, num_sms);
