@@ -187,7 +187,15 @@ __device__ __forceinline__ int aln_quant(int val, float scale) {
 __device__ __forceinline__ int div_small(int a, float rinv) {
     float af = i2f_small(a);
     float y = fmaf(af, rinv, copysignf(0.004f, af));
-    return f2i_exact((y - copysignf(0.5f, y) + kMagic) - kMagic);
+    return __float_as_int((y - copysignf(0.5f, y)) + kMagic) - kMagicBits;      // the magic add rounds to the integer and exposes it
+}
+
+// [sat8(a), sat8(b), sat8(c), sat8(d)] as bytes 0..3 with the reference's clip to [-127, 127]
+__device__ __forceinline__ uint32_t pack_clip8(int a, int b, int c, int d) {
+    uint32_t hi, r;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(d), "r"(c));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(a), "r"(hi));
+    return __vmaxs4(r, 0x81818181u);
 }
 
 // One warp per row; NJ = H/128 chunks of 4 elements per lane.  Every global load of the row (the int32
@@ -290,8 +298,8 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
         const int bv[4] = {(int)(int16_t)(b4[j].x & 0xFFFF), b4[j].x >> 16, (int)(int16_t)(b4[j].y & 0xFFFF), b4[j].y >> 16};
         int y[4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) y[i] = clip8(div_small(x[j][i] * wv[i], rinv) + bv[i]);
-        const uint32_t yw = pack4(y[0], y[1], y[2], y[3]);
+        for (int i = 0; i < 4; i++) y[i] = div_small(x[j][i] * wv[i], rinv) + bv[i];
+        const uint32_t yw = pack_clip8(y[0], y[1], y[2], y[3]);
         *reinterpret_cast<uint32_t *>(p.h_out + (int64_t)r * H + d) = yw;
         dot0 = __dp4a((int)yw, n4[0][j], dot0);
         dot1 = __dp4a((int)yw, n4[1][j], dot1);
