@@ -80,48 +80,46 @@ void build_noise_map(const egg_config &c, NoiseMap *map, NoiseSeg *segs, int *ns
 // scales: AdaptiveScales bytes or null.  With scales, every segment that has an overlay holds
 // (int)(noise * factor) (A vectors, layers.cuh:90) or the delta built from (int)(n1 * n2 * factor)
 // (vectors, layers.cuh:176-180), so that the consumers of the table need not know about overlays.
-__global__ void noise_fill_kernel(int8_t *nt, int64_t stride, const NoiseSeg *segs, int nsegs, uint32_t step_seed,
-                                  int pair_base, int mask, int gaussian, const int8_t *model, const int8_t *scales) {
+__global__ void __launch_bounds__(256) noise_fill_kernel(int8_t *nt, int64_t stride, const NoiseSeg *segs, int nsegs, uint32_t step_seed,
+                                                         int pair_base, int mask, int gaussian, const int8_t *model, const int8_t *scales) {
     extern __shared__ NoiseSeg s_segs[];
+    int *s_first = reinterpret_cast<int *>(s_segs + nsegs);       // first 256-element slice of every segment, then the total
     for (int i = threadIdx.x; i < nsegs; i += blockDim.x) s_segs[i] = segs[i];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int i = 0; i < nsegs; i++) { s_first[i] = acc; acc += (s_segs[i].len + 255) >> 8; }
+        s_first[nsegs] = acc;
+    }
     __syncthreads();
     const int pair = blockIdx.y;
     const uint32_t S0 = step_seed + (uint32_t)(pair_base + pair);
     int8_t *dst = nt + (int64_t)pair * stride;
-    // one thread per table element (kind 2 elements are two bytes wide: o counts int8 slots, stepping over them in pairs)
-    for (int o = blockIdx.x * blockDim.x + threadIdx.x; o < (int)stride; o += gridDim.x * blockDim.x) {
-        int lo = 0, hi = nsegs - 1;
-        while (lo < hi) { int mid = (lo + hi + 1) >> 1; if (s_segs[mid].off <= o) lo = mid; else hi = mid - 1; }
-        const NoiseSeg sg = s_segs[lo];
+    // one block iteration = 256 consecutive elements of one segment; an element of a delta segment is hashed once
+    // and written for both signs
+    int g = 0;
+    for (int sl = blockIdx.x; sl < s_first[nsegs]; sl += gridDim.x) {
+        while (s_first[g + 1] <= sl) g++;                          // slices are visited in increasing order
+        const NoiseSeg sg = s_segs[g];
+        const int i = ((sl - s_first[g]) << 8) + threadIdx.x;
+        if (i >= sg.len) continue;
         const bool scaled = scales != nullptr && sg.scale_off >= 0;
-        int rel = o - sg.off, val = 0;
+        int val = noise_from_hash(S0 + (uint32_t)sg.seed_a, (uint32_t)i, mask, gaussian);
         if (sg.kind == 0) {
-            if (rel < sg.len) {
-                val = noise_from_hash(S0 + (uint32_t)sg.seed_a, (uint32_t)rel, mask, gaussian);
-                if (scaled) val = scale_trunc(val, overlay_num(scales[sg.scale_off + rel]));
-            }
-            dst[o] = (int8_t)val;
-        } else if (sg.kind == 1) {
-            if (rel < 2 * sg.len) {
-                int neg = rel >= sg.len, i = neg ? rel - sg.len : rel;
-                int prod = noise_from_hash(S0 + (uint32_t)sg.seed_a, (uint32_t)i, mask, gaussian) *
-                           noise_from_hash(S0 + (uint32_t)sg.seed_b, (uint32_t)i, mask, gaussian);
-                if (scaled) prod = scale_trunc(prod, overlay_num(scales[sg.scale_off + i]));
-                val = (neg ? -prod : prod) >> sg.shift;
-            }
-            dst[o] = (int8_t)val;
+            if (scaled) val = scale_trunc(val, overlay_num(scales[sg.scale_off + i]));
+            dst[sg.off + i] = (int8_t)val;
         } else {
-            if (rel & 1) continue;                      // the even slot writes the whole int16
-            int e = rel >> 1;                           // 0 .. 2*len-1
-            if (e < 2 * sg.len) {
-                int neg = e >= sg.len, i = neg ? e - sg.len : e;
-                int prod = noise_from_hash(S0 + (uint32_t)sg.seed_a, (uint32_t)i, mask, gaussian) *
-                           noise_from_hash(S0 + (uint32_t)sg.seed_b, (uint32_t)i, mask, gaussian);
-                if (scaled) prod = scale_trunc(prod, overlay_num(scales[sg.scale_off + i]));
-                val = (int)model[sg.model_off + i] + ((neg ? -prod : prod) >> sg.shift);
-                *reinterpret_cast<int16_t *>(dst + o) = (int16_t)val;
+            int prod = val * noise_from_hash(S0 + (uint32_t)sg.seed_b, (uint32_t)i, mask, gaussian);
+            if (scaled) prod = scale_trunc(prod, overlay_num(scales[sg.scale_off + i]));
+            const int dp = prod >> sg.shift, dn = (-prod) >> sg.shift;
+            if (sg.kind == 1) {
+                dst[sg.off + i] = (int8_t)dp;
+                dst[sg.off + sg.len + i] = (int8_t)dn;
             } else {
-                dst[o] = 0; dst[o + 1] = 0;
+                const int m = model[sg.model_off + i];
+                int16_t *d16 = reinterpret_cast<int16_t *>(dst + sg.off);
+                d16[i] = (int16_t)(m + dp);
+                d16[sg.len + i] = (int16_t)(m + dn);
             }
         }
     }
@@ -131,7 +129,8 @@ int launch_noise_fill(cudaStream_t st, int8_t *nt, int64_t stride, const NoiseSe
                       uint32_t step_seed, int pair_base, int mask, int gaussian, const int8_t *model, const int8_t *scales) {
     int gx = (int)((stride + 255) / 256); if (gx > 64) gx = 64;
     dim3 grid((unsigned)gx, (unsigned)n_pairs);
-    noise_fill_kernel<<<grid, 256, nsegs * sizeof(NoiseSeg), st>>>(nt, stride, d_segs, nsegs, step_seed, pair_base, mask, gaussian, model, scales);
+    const size_t smem = nsegs * sizeof(NoiseSeg) + (nsegs + 1) * sizeof(int);
+    noise_fill_kernel<<<grid, 256, smem, st>>>(nt, stride, d_segs, nsegs, step_seed, pair_base, mask, gaussian, model, scales);
     EGG_CUDA(cudaGetLastError());
     return EGG_OK;
 }
