@@ -77,50 +77,55 @@ void build_noise_map(const egg_config &c, NoiseMap *map, NoiseSeg *segs, int *ns
     *nsegs = n;
 }
 
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d);
+
 // scales: AdaptiveScales bytes or null.  With scales, every segment that has an overlay holds
 // (int)(noise * factor) (A vectors, layers.cuh:90) or the delta built from (int)(n1 * n2 * factor)
 // (vectors, layers.cuh:176-180), so that the consumers of the table need not know about overlays.
 __global__ void __launch_bounds__(256) noise_fill_kernel(int8_t *nt, int64_t stride, const NoiseSeg *segs, int nsegs, uint32_t step_seed,
                                                          int pair_base, int mask, int gaussian, const int8_t *model, const int8_t *scales) {
     extern __shared__ NoiseSeg s_segs[];
-    int *s_first = reinterpret_cast<int *>(s_segs + nsegs);       // first 256-element slice of every segment, then the total
+    int *s_first = reinterpret_cast<int *>(s_segs + nsegs);       // first 1024-element slice of every segment, then the total
     for (int i = threadIdx.x; i < nsegs; i += blockDim.x) s_segs[i] = segs[i];
     __syncthreads();
     if (threadIdx.x == 0) {
         int acc = 0;
-        for (int i = 0; i < nsegs; i++) { s_first[i] = acc; acc += (s_segs[i].len + 255) >> 8; }
+        for (int i = 0; i < nsegs; i++) { s_first[i] = acc; acc += (s_segs[i].len + 1023) >> 10; }
         s_first[nsegs] = acc;
     }
     __syncthreads();
     const int pair = blockIdx.y;
     const uint32_t S0 = step_seed + (uint32_t)(pair_base + pair);
     int8_t *dst = nt + (int64_t)pair * stride;
-    // one block iteration = 256 consecutive elements of one segment; an element of a delta segment is hashed once
-    // and written for both signs
+    // one block iteration = 1024 consecutive elements of one segment, four per thread (segment lengths are multiples
+    // of four); an element of a delta segment is hashed once and written for both signs
     int g = 0;
     for (int sl = blockIdx.x; sl < s_first[nsegs]; sl += gridDim.x) {
         while (s_first[g + 1] <= sl) g++;                          // slices are visited in increasing order
         const NoiseSeg sg = s_segs[g];
-        const int i = ((sl - s_first[g]) << 8) + threadIdx.x;
-        if (i >= sg.len) continue;
+        const int i0 = ((sl - s_first[g]) << 10) + (threadIdx.x << 2);
+        if (i0 >= sg.len) continue;
         const bool scaled = scales != nullptr && sg.scale_off >= 0;
-        int val = noise_from_hash(S0 + (uint32_t)sg.seed_a, (uint32_t)i, mask, gaussian);
-        if (sg.kind == 0) {
+        int vp[4], vn[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int i = i0 + e;
+            int val = noise_from_hash(S0 + (uint32_t)sg.seed_a, (uint32_t)i, mask, gaussian);
+            if (sg.kind != 0) val *= noise_from_hash(S0 + (uint32_t)sg.seed_b, (uint32_t)i, mask, gaussian);
             if (scaled) val = scale_trunc(val, overlay_num(scales[sg.scale_off + i]));
-            dst[sg.off + i] = (int8_t)val;
-        } else {
-            int prod = val * noise_from_hash(S0 + (uint32_t)sg.seed_b, (uint32_t)i, mask, gaussian);
-            if (scaled) prod = scale_trunc(prod, overlay_num(scales[sg.scale_off + i]));
-            const int dp = prod >> sg.shift, dn = (-prod) >> sg.shift;
-            if (sg.kind == 1) {
-                dst[sg.off + i] = (int8_t)dp;
-                dst[sg.off + sg.len + i] = (int8_t)dn;
-            } else {
-                const int m = model[sg.model_off + i];
-                int16_t *d16 = reinterpret_cast<int16_t *>(dst + sg.off);
-                d16[i] = (int16_t)(m + dp);
-                d16[sg.len + i] = (int16_t)(m + dn);
+            if (sg.kind == 0) { vp[e] = val; vn[e] = 0; }
+            else {
+                vp[e] = val >> sg.shift; vn[e] = (-val) >> sg.shift;
+                if (sg.kind == 2) { const int m = model[sg.model_off + i]; vp[e] += m; vn[e] += m; }
             }
+        }
+        if (sg.kind == 2) {
+            int16_t *d16 = reinterpret_cast<int16_t *>(dst + sg.off);
+            *reinterpret_cast<int2 *>(d16 + i0) = make_int2((vp[0] & 0xFFFF) | (vp[1] << 16), (vp[2] & 0xFFFF) | (vp[3] << 16));
+            *reinterpret_cast<int2 *>(d16 + sg.len + i0) = make_int2((vn[0] & 0xFFFF) | (vn[1] << 16), (vn[2] & 0xFFFF) | (vn[3] << 16));
+        } else {
+            *reinterpret_cast<uint32_t *>(dst + sg.off + i0) = pack4(vp[0], vp[1], vp[2], vp[3]);
+            if (sg.kind == 1) *reinterpret_cast<uint32_t *>(dst + sg.off + sg.len + i0) = pack4(vn[0], vn[1], vn[2], vn[3]);
         }
     }
 }
