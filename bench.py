@@ -294,6 +294,11 @@ def main():
         "rowwise": 6.0 * H * rows_per_step * (2 * L + 2),
         "aqn": 15.0 * H * rows_per_step * L,
     }
+    # DRAM bytes (read + write) per row of one launch, from the ncu captures summarised under profiles/ (262 144-row
+    # launches of the same kernels; traffic grows in proportion to the rows of a launch)
+    ncu_traffic_per_row = {"attention": (404.054016e6 + 116.210688e6) / 262144, "rowwise": (543.158528e6 + 250.782208e6) / 262144,
+                           "gemm_gelu": (144.439040e6 + 488.345e6) / 262144, "gemm_qkv": (143.108352e6 + 1562.813e6) / 262144,
+                           "gemm_pre32": (675.208704e6 + 496.057e6) / 262144}
     peaks = {}
     pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(pk):
@@ -315,6 +320,10 @@ def main():
         roof = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                 "traffic": None, "peak_source": "hbm_gbs of %s MEASURED_PEAKS" % peak_src}
     roof["avg_launch_ms"] = t_ms / max(1, n_launch)
+    if top in ncu_traffic_per_row:
+        rows_per_launch = min(ctx.wave_members(), per) * S
+        roof["traffic"] = ncu_traffic_per_row[top] * rows_per_launch
+        roof["traffic_source"] = "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 262144-row launch (profiles/), scaled by rows per launch"
     total_prof = sum(v[0] for v in prof.values()) or 1.0
     kernel_share = {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps, "share": v[0] / total_prof}
                     for k, v in prof.items() if v[1] > 0}
