@@ -486,6 +486,18 @@ __device__ __forceinline__ int att_div(int p0, int p1, int p2, long long den, fl
     return k;
 }
 
+// The same quotient when every limb sum is below 2^23 (seq_len <= 512): the estimate needs two conversions, and the
+// remainder num - k*den is assembled limb by limb in 32-bit arithmetic — it is at most den/2 (+ rounding) < 2^27 in
+// magnitude, so the wrapping partial terms add up to its exact value.  d0..d2 are the limb sums of the denominator.
+__device__ __forceinline__ int att_div_small(int p0, int p1, int p2, int d0, int d1, int d2, float rden) {
+    const float fn = fmaf(__int2float_rn(p2 * 128 + p1), 128.0f, __int2float_rn(p0));
+    int k = __float2int_rn(fn * rden);
+    const int r = (p0 - k * d0) + (p1 - k * d1) * 128 + (p2 - k * d2) * 16384;
+    if (k > 0 && r < 0) k--;
+    else if (k < 0 && r > 0) k++;
+    return k;
+}
+
 __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
     extern __shared__ __align__(16) uint8_t att_smem[];
     const int S = p.seq_len, SP = (S + 31) & ~31, VP = SP + 16, H = p.H;
@@ -626,19 +638,30 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
                 for (int l = 0; l < 3; l++) mma_s8(acc[dn][l], al[l][0], al[l][1], al[l][2], al[l][3], b0, b1);
             }
         }
-        uint32_t tot0 = (uint32_t)tl0[0] + ((uint32_t)tl0[1] << 7) + ((uint32_t)tl0[2] << 14);
-        uint32_t tot1 = (uint32_t)tl1[0] + ((uint32_t)tl1[1] << 7) + ((uint32_t)tl1[2] << 14);
-        tot0 += __shfl_xor_sync(0xFFFFFFFFu, tot0, 1); tot0 += __shfl_xor_sync(0xFFFFFFFFu, tot0, 2);
-        tot1 += __shfl_xor_sync(0xFFFFFFFFu, tot1, 1); tot1 += __shfl_xor_sync(0xFFFFFFFFu, tot1, 2);
+#pragma unroll
+        for (int l = 0; l < 3; l++) {                 // limb sums of Σw over the four lanes that share a row
+            tl0[l] += __shfl_xor_sync(0xFFFFFFFFu, tl0[l], 1); tl0[l] += __shfl_xor_sync(0xFFFFFFFFu, tl0[l], 2);
+            tl1[l] += __shfl_xor_sync(0xFFFFFFFFu, tl1[l], 1); tl1[l] += __shfl_xor_sync(0xFFFFFFFFu, tl1[l], 2);
+        }
+        const uint32_t tot0 = (uint32_t)tl0[0] + ((uint32_t)tl0[1] << 7) + ((uint32_t)tl0[2] << 14);
+        const uint32_t tot1 = (uint32_t)tl1[0] + ((uint32_t)tl1[1] << 7) + ((uint32_t)tl1[2] << 14);
         const long long den0 = tot0 ? (long long)tot0 : 1, den1 = tot1 ? (long long)tot1 : 1;
         const float rden0 = 1.0f / (float)den0, rden1 = 1.0f / (float)den1;
         int dot0 = 0, dot1 = 0;
 #pragma unroll
         for (int dn = 0; dn < 8; dn++) {
             int o[4];
+            if (small_limbs) {
+                // |Σw·v / Σw| <= 127 (a weighted mean of int8 values): the reference's clip cannot trigger
 #pragma unroll
-            for (int i = 0; i < 4; i++)
-                o[i] = clip8(att_div(acc[dn][0][i], acc[dn][1][i], acc[dn][2][i], i < 2 ? den0 : den1, i < 2 ? rden0 : rden1, small_limbs));
+                for (int i = 0; i < 4; i++)
+                    o[i] = i < 2 ? att_div_small(acc[dn][0][i], acc[dn][1][i], acc[dn][2][i], tl0[0], tl0[1], tl0[2], rden0)
+                                 : att_div_small(acc[dn][0][i], acc[dn][1][i], acc[dn][2][i], tl1[0], tl1[1], tl1[2], rden1);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    o[i] = clip8(att_div(acc[dn][0][i], acc[dn][1][i], acc[dn][2][i], i < 2 ? den0 : den1, i < 2 ? rden0 : rden1, false));
+            }
             const int dim = dn * 8 + 2 * q;
             *reinterpret_cast<uint16_t *>(p.ao + (base + row0) * H + col0 + dim) = (uint16_t)((o[0] & 0xFF) | ((o[1] & 0xFF) << 8));
             *reinterpret_cast<uint16_t *>(p.ao + (base + row1) * H + col0 + dim) = (uint16_t)((o[2] & 0xFF) | ((o[3] & 0xFF) << 8));
