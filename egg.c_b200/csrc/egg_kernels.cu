@@ -534,10 +534,16 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
             uint32_t t0 = __byte_perm(w0[dq], w1[dq], 0x5140), t1 = __byte_perm(w2[dq], w3[dq], 0x5140);   // [a0 b0 a1 b1]
             uint32_t t2 = __byte_perm(w0[dq], w1[dq], 0x7362), t3 = __byte_perm(w2[dq], w3[dq], 0x7362);   // [a2 b2 a3 b3]
             const int dim = ch * 16 + dq * 4;
-            *reinterpret_cast<uint32_t *>(Vt + (dim + 0) * VP + kg * 4) = __byte_perm(t0, t1, 0x5410);
-            *reinterpret_cast<uint32_t *>(Vt + (dim + 1) * VP + kg * 4) = __byte_perm(t0, t1, 0x7632);
-            *reinterpret_cast<uint32_t *>(Vt + (dim + 2) * VP + kg * 4) = __byte_perm(t2, t3, 0x5410);
-            *reinterpret_cast<uint32_t *>(Vt + (dim + 3) * VP + kg * 4) = __byte_perm(t2, t3, 0x7632);
+            // keys are stored permuted inside every group of 16 so that the four keys an MMA B-fragment register needs
+            // ({2q, 2q+1, 8+2q, 9+2q}) are one aligned word: keys 4m, 4m+1 go to slot (m&1)*8 + (m>>1)*2, keys 4m+2, 4m+3 four further
+            const int m = kg & 3;
+            const int so = (kg >> 2) * 16 + (m & 1) * 8 + (m >> 1) * 2;
+            const uint32_t w0 = __byte_perm(t0, t1, 0x5410), w1 = __byte_perm(t0, t1, 0x7632);
+            const uint32_t w2 = __byte_perm(t2, t3, 0x5410), w3 = __byte_perm(t2, t3, 0x7632);
+            *reinterpret_cast<uint16_t *>(Vt + (dim + 0) * VP + so) = (uint16_t)w0; *reinterpret_cast<uint16_t *>(Vt + (dim + 0) * VP + so + 4) = (uint16_t)(w0 >> 16);
+            *reinterpret_cast<uint16_t *>(Vt + (dim + 1) * VP + so) = (uint16_t)w1; *reinterpret_cast<uint16_t *>(Vt + (dim + 1) * VP + so + 4) = (uint16_t)(w1 >> 16);
+            *reinterpret_cast<uint16_t *>(Vt + (dim + 2) * VP + so) = (uint16_t)w2; *reinterpret_cast<uint16_t *>(Vt + (dim + 2) * VP + so + 4) = (uint16_t)(w2 >> 16);
+            *reinterpret_cast<uint16_t *>(Vt + (dim + 3) * VP + so) = (uint16_t)w3; *reinterpret_cast<uint16_t *>(Vt + (dim + 3) * VP + so + 4) = (uint16_t)(w3 >> 16);
         }
     }
     for (int i = tid; i < 256; i += 128) {
@@ -631,9 +637,8 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
             }
 #pragma unroll
             for (int dn = 0; dn < 8; dn++) {
-                const int8_t *vp = Vt + (dn * 8 + g) * VP + kb * 32 + 2 * q;
-                uint32_t b0 = (uint32_t)*reinterpret_cast<const uint16_t *>(vp) | ((uint32_t)*reinterpret_cast<const uint16_t *>(vp + 8) << 16);
-                uint32_t b1 = (uint32_t)*reinterpret_cast<const uint16_t *>(vp + 16) | ((uint32_t)*reinterpret_cast<const uint16_t *>(vp + 24) << 16);
+                const int8_t *vp = Vt + (dn * 8 + g) * VP + kb * 32 + 4 * q;
+                const uint32_t b0 = *reinterpret_cast<const uint32_t *>(vp), b1 = *reinterpret_cast<const uint32_t *>(vp + 16);
 #pragma unroll
                 for (int l = 0; l < 3; l++) mma_s8(acc[dn][l], al[l][0], al[l][1], al[l][2], al[l][3], b0, b1);
             }
