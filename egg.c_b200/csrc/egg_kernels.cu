@@ -162,6 +162,9 @@ constexpr float kMagic = 12582912.0f;          // 1.5 * 2^23
 constexpr int kMagicBits = 0x4B400000;
 // (float)v for |v| < 2^22, exact
 __device__ __forceinline__ float i2f_small(int v) { return __int_as_float(kMagicBits + v) - kMagic; }
+// the same value through the conversion unit: used for a share of the conversions so that the otherwise idle unit
+// takes load off the integer/float pipes
+__device__ __forceinline__ float i2f_cvt(int v) { return __int2float_rn(v); }
 // roundf(x) (half away from zero) as a float, for |x| < 2^22: round-to-nearest-even by the
 // magic add, then the two tie cases that differ are corrected (x - rint(x) is exact).
 __device__ __forceinline__ float roundf_small(float x) {
@@ -179,7 +182,7 @@ __device__ __forceinline__ int f2i_exact(float f) { return __float_as_int(f + kM
 __device__ __forceinline__ float aln_scale(int layer_max) { return 127.0f / (float)(layer_max + 1e-9f); }
 template <bool SMALL>
 __device__ __forceinline__ int aln_quant(int val, float scale) {
-    float vf = SMALL ? i2f_small(val) : (float)val;
+    float vf = SMALL ? i2f_cvt(val) : (float)val;
     float r = roundf_small(vf * scale);              // |vf*scale| <= 127*(1+eps)
     r = fminf(fmaxf(r, -127.0f), 127.0f);
     return f2i_exact(r);
