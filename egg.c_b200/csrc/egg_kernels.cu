@@ -180,6 +180,12 @@ __device__ __forceinline__ int f2i_exact(float f) { return __float_as_int(f + kM
 // adaptive_layer_normalize / adaptive_qkv_normalize (egg_adaptive_normalize.h:10-103):
 //   scale = 127.0f / (float)(max + 1e-9f);  out = clamp((int)roundf((float)v * scale), -127, 127)
 __device__ __forceinline__ float aln_scale(int layer_max) { return 127.0f / (float)(layer_max + 1e-9f); }
+// the rounded value without the clamp, for callers that clip while packing
+template <bool SMALL>
+__device__ __forceinline__ int aln_quant_raw(int val, float scale) {
+    float vf = SMALL ? i2f_cvt(val) : (float)val;
+    return f2i_exact(roundf_small(vf * scale));          // |vf*scale| <= 127*(1+eps)
+}
 template <bool SMALL>
 __device__ __forceinline__ int aln_quant(int val, float scale) {
     float vf = SMALL ? i2f_cvt(val) : (float)val;
@@ -406,37 +412,53 @@ int launch_overlay_step(cudaStream_t st, int8_t *ov, uint8_t *changed, int n, in
     return EGG_OK;
 }
 
-// Q/K/V requantisation (adaptive_qkv_normalize, mgpu.cu:782-784)
+// Q/K/V requantisation (adaptive_qkv_normalize, mgpu.cu:782-784).  One warp per row; all of the row's loads
+// (three parts x NJ 16-byte pieces per lane) are issued before any arithmetic.
+template <int NJ>
 __global__ void __launch_bounds__(256) aqn_kernel(const AqnParams p) {
     const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (r >= p.M) return;
-    const int H = p.H, nj = H >> 7;
+    constexpr int H = NJ * 128;
+    const int32_t *src = p.pre3 + (int64_t)r * 3 * H + (lane << 2);
+    int4 v[3][NJ];
+#pragma unroll
+    for (int which = 0; which < 3; which++)
+#pragma unroll
+        for (int j = 0; j < NJ; j++) v[which][j] = *reinterpret_cast<const int4 *>(src + which * H + (j << 7));
+    const int mx0 = p.rowmax3[(int64_t)r * 3], mx1 = p.rowmax3[(int64_t)r * 3 + 1], mx2 = p.rowmax3[(int64_t)r * 3 + 2];
+#pragma unroll
     for (int which = 0; which < 3; which++) {
-        const int mx = p.rowmax3[(int64_t)r * 3 + which];
+        const int mx = which == 0 ? mx0 : (which == 1 ? mx1 : mx2);
         const float scale = aln_scale(mx);
-        int8_t *out = which == 0 ? p.q : (which == 1 ? p.k : p.v);
-        const int32_t *src = p.pre3 + ((int64_t)r * 3 + which) * H;
+        int8_t *out = (which == 0 ? p.q : (which == 1 ? p.k : p.v)) + (int64_t)r * H + (lane << 2);
         if (mx < (1 << 22)) {
-            for (int j = 0; j < nj; j++) {
-                const int d = (j << 7) + (lane << 2);
-                int4 v = *reinterpret_cast<const int4 *>(src + d);
-                *reinterpret_cast<uint32_t *>(out + (int64_t)r * H + d) =
-                    pack4(aln_quant<true>(v.x, scale), aln_quant<true>(v.y, scale), aln_quant<true>(v.z, scale), aln_quant<true>(v.w, scale));
-            }
+#pragma unroll
+            for (int j = 0; j < NJ; j++)
+                *reinterpret_cast<uint32_t *>(out + (j << 7)) = pack_clip8(aln_quant_raw<true>(v[which][j].x, scale), aln_quant_raw<true>(v[which][j].y, scale),
+                                                                           aln_quant_raw<true>(v[which][j].z, scale), aln_quant_raw<true>(v[which][j].w, scale));
         } else {
-            for (int j = 0; j < nj; j++) {
-                const int d = (j << 7) + (lane << 2);
-                int4 v = *reinterpret_cast<const int4 *>(src + d);
-                *reinterpret_cast<uint32_t *>(out + (int64_t)r * H + d) =
-                    pack4(aln_quant<false>(v.x, scale), aln_quant<false>(v.y, scale), aln_quant<false>(v.z, scale), aln_quant<false>(v.w, scale));
-            }
+#pragma unroll
+            for (int j = 0; j < NJ; j++)
+                *reinterpret_cast<uint32_t *>(out + (j << 7)) = pack_clip8(aln_quant_raw<false>(v[which][j].x, scale), aln_quant_raw<false>(v[which][j].y, scale),
+                                                                           aln_quant_raw<false>(v[which][j].z, scale), aln_quant_raw<false>(v[which][j].w, scale));
         }
     }
 }
 
 int launch_aqn(cudaStream_t st, const AqnParams &p) {
-    aqn_kernel<<<(p.M + 7) / 8, 256, 0, st>>>(p);
+    const int blocks = (p.M + 7) / 8;
+    switch (p.H >> 7) {
+        case 1: aqn_kernel<1><<<blocks, 256, 0, st>>>(p); break;
+        case 2: aqn_kernel<2><<<blocks, 256, 0, st>>>(p); break;
+        case 3: aqn_kernel<3><<<blocks, 256, 0, st>>>(p); break;
+        case 4: aqn_kernel<4><<<blocks, 256, 0, st>>>(p); break;
+        case 5: aqn_kernel<5><<<blocks, 256, 0, st>>>(p); break;
+        case 6: aqn_kernel<6><<<blocks, 256, 0, st>>>(p); break;
+        case 7: aqn_kernel<7><<<blocks, 256, 0, st>>>(p); break;
+        case 8: aqn_kernel<8><<<blocks, 256, 0, st>>>(p); break;
+        default: set_error("hidden_dim %d unsupported by the requantisation kernel", p.H); return EGG_E_INVALID;
+    }
     EGG_CUDA(cudaGetLastError());
     return EGG_OK;
 }
