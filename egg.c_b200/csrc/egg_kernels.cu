@@ -180,19 +180,21 @@ __device__ __forceinline__ int f2i_exact(float f) { return __float_as_int(f + kM
 // adaptive_layer_normalize / adaptive_qkv_normalize (egg_adaptive_normalize.h:10-103):
 //   scale = 127.0f / (float)(max + 1e-9f);  out = clamp((int)roundf((float)v * scale), -127, 127)
 __device__ __forceinline__ float aln_scale(int layer_max) { return 127.0f / (float)(layer_max + 1e-9f); }
-// the rounded value without the clamp, for callers that clip while packing
+__device__ __forceinline__ float aln_scale24(int layer_max) { return aln_scale(layer_max) * 16777216.0f; }    // exact: a power of two
+// clamp((int)roundf((float)v * scale), -127, 127) for |v| <= max, in fixed point: |v| * (scale * 2^24) is the same
+// float product scaled by a power of two (|x| <= 127 * (1 + 2^-23), so x * 2^24 < 2^31), its truncation to an integer
+// keeps every bit that decides the rounding (for |x| >= 1 the product has at most 23 fraction bits; below 1 only
+// "is it >= 0.5" matters, which truncation preserves), and round-half-away-from-zero becomes (xi + 2^23) >> 24.
+// The result cannot leave [-127, 127], so the reference's clamp needs no instruction.
 template <bool SMALL>
-__device__ __forceinline__ int aln_quant_raw(int val, float scale) {
-    float vf = SMALL ? i2f_cvt(val) : (float)val;
-    return f2i_exact(roundf_small(vf * scale));          // |vf*scale| <= 127*(1+eps)
+__device__ __forceinline__ int aln_quant(int val, float scale24) {
+    const int av = abs(val);
+    const float vf = SMALL ? i2f_cvt(av) : (float)av;
+    const int t = (__float2int_rz(vf * scale24) + (1 << 23)) >> 24;
+    return val < 0 ? -t : t;
 }
 template <bool SMALL>
-__device__ __forceinline__ int aln_quant(int val, float scale) {
-    float vf = SMALL ? i2f_cvt(val) : (float)val;
-    float r = roundf_small(vf * scale);              // |vf*scale| <= 127*(1+eps)
-    r = fminf(fmaxf(r, -127.0f), 127.0f);
-    return f2i_exact(r);
-}
+__device__ __forceinline__ int aln_quant_raw(int val, float scale24) { return aln_quant<SMALL>(val, scale24); }
 
 // trunc(a / mn) as C integer division does, for |a| < 2^15 and 1 <= mn <= 127:
 // a*(1/mn) is off by < 0.003, exact quotients are pushed off the integer by a bias of
@@ -275,7 +277,7 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
 #pragma unroll
         for (int j = 0; j < NJ; j++) v[j] = *reinterpret_cast<const int4 *>(p.pre32 + (int64_t)r * H + (j << 7) + (lane << 2));
         const int mx = p.rowmax[r];
-        const float scale = aln_scale(mx);
+        const float scale = aln_scale24(mx);
         if (mx < (1 << 22)) {
 #pragma unroll
             for (int j = 0; j < NJ; j++) {
@@ -430,7 +432,7 @@ __global__ void __launch_bounds__(256) aqn_kernel(const AqnParams p) {
 #pragma unroll
     for (int which = 0; which < 3; which++) {
         const int mx = which == 0 ? mx0 : (which == 1 ? mx1 : mx2);
-        const float scale = aln_scale(mx);
+        const float scale = aln_scale24(mx);
         int8_t *out = (which == 0 ? p.q : (which == 1 ? p.k : p.v)) + (int64_t)r * H + (lane << 2);
         if (mx < (1 << 22)) {
 #pragma unroll
