@@ -207,6 +207,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
     const int rc = row_ok ? r : (p.M - 1);
     const int mem = rc / p.seq_len;
     const int part = (EPI == EPI_QKV) ? (n0 / p.third) : 0;
+    const uint32_t lut_base = ptx::smem_u32(&sm.lut16[0][lane & 15]);
     const int32_t *a32 = sm.rpl.a32[slot] + cbase;
     const int32_t *bcs = sm.rpl.bcs32[slot][sgn] + cbase;
     const int8_t *dt = sm.d_tab[slot] + cbase;
@@ -248,9 +249,9 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                 // saturate to [-128, 127] while packing; the table entry of -128 holds the value of -127 (the reference's clip)
                 const uint32_t z = ptx::pack_sat_s8((x0 + b4.x) >> p.out_shift, (x1 + b4.y) >> p.out_shift, (x2 + b4.z) >> p.out_shift,
                                                     (x3 + b4.w) >> p.out_shift);
-                const uint32_t *lut = &sm.lut16[0][lane & 15];
-                const uint32_t u0 = lut[(z & 0xFF) * 16], u1 = lut[((z >> 8) & 0xFF) * 16];
-                const uint32_t u2 = lut[((z >> 16) & 0xFF) * 16], u3 = lut[(z >> 24) * 16];
+                // word (idx, lane & 15) of the replicated table: 32-bit shared address = base + idx * 64
+                const uint32_t u0 = ptx::lds_u32(lut_base + ((z & 0xFFu) << 6)), u1 = ptx::lds_u32(lut_base + ((z >> 2) & 0x3FC0u));
+                const uint32_t u2 = ptx::lds_u32(lut_base + ((z >> 10) & 0x3FC0u)), u3 = ptx::lds_u32(lut_base + ((z >> 18) & 0x3FC0u));
                 const uint32_t w = __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
                 racc = __dp4a((int)w, *reinterpret_cast<const int32_t *>(dt + col), racc);
                 outw[q4] = w;

@@ -173,6 +173,13 @@ __device__ __forceinline__ uint32_t pack_sat_s8(int a, int b, int c, int d) {
     return r;
 }
 
+// 32-bit shared-memory load at a 32-bit shared address (kept in order with the barriers, which are volatile too)
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
