@@ -208,8 +208,9 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
     const int mem = rc / p.seq_len;
     const int part = (EPI == EPI_QKV) ? (n0 / p.third) : 0;
     const uint32_t lut_base = ptx::smem_u32(&sm.lut16[0][lane & 15]);
-    const int32_t *a32 = sm.rpl.a32[slot] + cbase;
-    const int32_t *bcs = sm.rpl.bcs32[slot][sgn] + cbase;
+    const uint32_t a32 = ptx::smem_u32(sm.rpl.a32[slot] + cbase);           // 32-bit shared addresses of this lane's tables
+    const uint32_t bcs = ptx::smem_u32(sm.rpl.bcs32[slot][sgn] + cbase);
+    const uint32_t ost_s = ptx::smem_u32(ost) + lane * 64;
     const int8_t *dt = sm.d_tab[slot] + cbase;
     const int64_t gofs = (int64_t)rc * p.N + n0 + cbase;
     const int2 *rope = p.rope_t + (rc - mem * p.seq_len);                                // column of this token position
@@ -238,14 +239,14 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
 #pragma unroll
         for (int q4 = 0; q4 < 4; q4++) {
             const int col = 16 * c + 4 * q4;
-            const int4 an = *reinterpret_cast<const int4 *>(a32 + col);
+            const int4 an = ptx::lds_v4(a32 + 4 * col);
             int x0 = (int)vc[4 * q4] + ((xbs * an.x) >> p.rank1_shift);
             int x1 = (int)vc[4 * q4 + 1] + ((xbs * an.y) >> p.rank1_shift);
             int x2 = (int)vc[4 * q4 + 2] + ((xbs * an.z) >> p.rank1_shift);
             int x3 = (int)vc[4 * q4 + 3] + ((xbs * an.w) >> p.rank1_shift);
             if (EPI == EPI_GELU) {
                 // ((acc + r1) >> s) + b  ==  (acc + r1 + (b << s)) >> s
-                const int4 b4 = *reinterpret_cast<const int4 *>(bcs + col);
+                const int4 b4 = ptx::lds_v4(bcs + 4 * col);
                 // saturate to [-128, 127] while packing; the table entry of -128 holds the value of -127 (the reference's clip)
                 const uint32_t z = ptx::pack_sat_s8((x0 + b4.x) >> p.out_shift, (x1 + b4.y) >> p.out_shift, (x2 + b4.z) >> p.out_shift,
                                                     (x3 + b4.w) >> p.out_shift);
@@ -256,7 +257,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                 racc = __dp4a((int)w, *reinterpret_cast<const int32_t *>(dt + col), racc);
                 outw[q4] = w;
             } else if (EPI == EPI_PRE32) {
-                const int4 b4 = *reinterpret_cast<const int4 *>(bcs + col);
+                const int4 b4 = ptx::lds_v4(bcs + 4 * col);
                 const int32_t rs = q4 == 0 ? rs_pre[c].x : (q4 == 1 ? rs_pre[c].y : (q4 == 2 ? rs_pre[c].z : rs_pre[c].w));
                 x0 = (int)(int8_t)(rs) + ((x0 + b4.x) >> p.out_shift);
                 x1 = (int)(int8_t)(rs >> 8) + ((x1 + b4.y) >> p.out_shift);
@@ -284,7 +285,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                     if (lane == 0) ptx::tma_store_wait_read<0>();
                     __syncwarp();
                 }
-                *reinterpret_cast<int4 *>(ost + lane * 16 + ((c ^ ((lane >> 1) & 3)) << 2)) = make_int4(outw[0], outw[1], outw[2], outw[3]);
+                ptx::sts_v4(ost_s + ((c ^ ((lane >> 1) & 3)) << 4), make_int4(outw[0], outw[1], outw[2], outw[3]));
             } else {
                 *reinterpret_cast<int4 *>(&st[lane][4 * c]) = make_int4(outw[0], outw[1], outw[2], outw[3]);
             }
@@ -296,7 +297,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
             if (lane == 0) ptx::tma_store_wait_read<0>();       // the previous chunk's box has been read out
             __syncwarp();
 #pragma unroll
-            for (int q4 = 0; q4 < 4; q4++) *reinterpret_cast<int4 *>(ost + lane * 16 + ((q4 ^ ((lane >> 1) & 3)) << 2)) = o4[q4];
+            for (int q4 = 0; q4 < 4; q4++) ptx::sts_v4(ost_s + ((q4 ^ ((lane >> 1) & 3)) << 4), o4[q4]);
             ptx::fence_proxy_async();
             __syncwarp();
             if (lane == 0) {
