@@ -268,11 +268,13 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
             } else if (EPI == EPI_QKV) {
                 if (do_rope) {
                     // integer RoPE on adjacent (even, odd) columns (apply_rope_integer, mgpu.cu:624-644)
-                    const long long e0 = x0, o0 = x1, e1 = x2, o1 = x3;
-                    x0 = (int)((e0 * cs[q4].x - o0 * cs[q4].y + half_ulp) >> p.rope_bit);
-                    x1 = (int)((e0 * cs[q4].y + o0 * cs[q4].x + half_ulp) >> p.rope_bit);
-                    x2 = (int)((e1 * cs[q4].z - o1 * cs[q4].w + half_ulp) >> p.rope_bit);
-                    x3 = (int)((e1 * cs[q4].w + o1 * cs[q4].z + half_ulp) >> p.rope_bit);
+                    // (e*c - o*s + half) >> bit and (e*s + o*c + half) >> bit: two wide multiply-adds and one funnel shift
+                    // each (bits [bit, bit+32) of the 64-bit sum are what the cast of the shifted value keeps)
+                    const int e0 = x0, o0 = x1, e1 = x2, o1 = x3;
+                    x0 = ptx::shr64_lo(ptx::mad_wide(-o0, cs[q4].y, ptx::mad_wide(e0, cs[q4].x, half_ulp)), p.rope_bit);
+                    x1 = ptx::shr64_lo(ptx::mad_wide(o0, cs[q4].x, ptx::mad_wide(e0, cs[q4].y, half_ulp)), p.rope_bit);
+                    x2 = ptx::shr64_lo(ptx::mad_wide(-o1, cs[q4].w, ptx::mad_wide(e1, cs[q4].z, half_ulp)), p.rope_bit);
+                    x3 = ptx::shr64_lo(ptx::mad_wide(o1, cs[q4].z, ptx::mad_wide(e1, cs[q4].w, half_ulp)), p.rope_bit);
                 }
                 racc = max(racc, max(max(abs(x0), abs(x1)), max(abs(x2), abs(x3))));
                 o4[q4] = make_int4(x0, x1, x2, x3);

@@ -173,6 +173,17 @@ __device__ __forceinline__ uint32_t pack_sat_s8(int a, int b, int c, int d) {
     return r;
 }
 
+// a * b + c with a 32 x 32 -> 64-bit product (one instruction)
+__device__ __forceinline__ long long mad_wide(int a, int b, long long c) {
+    long long d;
+    asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(d) : "r"(a), "r"(b), "l"(c));
+    return d;
+}
+// low 32 bits of (v >> sh) for 0 < sh < 32: exact whenever the shifted value fits 32 bits
+__device__ __forceinline__ int shr64_lo(long long v, int sh) {
+    return (int)__funnelshift_r((unsigned)v, (unsigned)(v >> 32), sh);
+}
+
 // 32-bit shared-memory load at a 32-bit shared address (kept in order with the barriers, which are volatile too)
 __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
     uint32_t v;
