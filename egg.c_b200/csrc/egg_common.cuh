@@ -129,6 +129,26 @@ __host__ __device__ __forceinline__ int scale_trunc(int v, int num) {
     return (q + ((q >> 31) & 63)) >> 6;
 }
 
+// Division of 0 <= n < 2^31 by a run-time constant d >= 1 as one wide multiply and a shift:
+// with l = ceil(log2 d) and mul = floor(2^(31+l) / d) + 1,  mul*d - 2^(31+l) lies in [1, d] <= 2^l, which makes
+// floor(n * mul / 2^(31+l)) == floor(n / d) for every n below 2^31.
+struct FastDiv {
+    uint32_t mul, shift;
+    int d;
+};
+inline FastDiv make_fastdiv(int d) {
+    FastDiv f;
+    if (d < 1) d = 1;
+    int l = 0;
+    while ((1ll << l) < d) l++;
+    f.mul = (uint32_t)(((1ull << (31 + l)) / (uint64_t)d) + 1ull);
+    f.shift = (uint32_t)(31 + l);
+    f.d = d;
+    return f;
+}
+__device__ __forceinline__ int fast_div(int n, const FastDiv &f) { return (int)(((uint64_t)(uint32_t)n * f.mul) >> f.shift); }
+__device__ __forceinline__ int fast_mod(int n, const FastDiv &f) { return n - fast_div(n, f) * f.d; }
+
 // One trainable parameter of the update sequence (mgpu.cu:1603-1643).
 struct ParamDesc {
     int64_t model_off;   // element offset in TransformerModel

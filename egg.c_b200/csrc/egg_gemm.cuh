@@ -79,6 +79,8 @@ struct GemmParams {
     // ---- device error record ----
     int *err;
     int rpl;                     // -1 forces the transposed evaluation epilogue (tests); otherwise chosen from seq_len
+    // divisors of the per-tile index arithmetic (filled by launch_gemm)
+    FastDiv fd_seq, fd_tiles_n, fd_third, fd_head;
 };
 
 template <int BN>
@@ -155,8 +157,8 @@ struct TabWords { int32_t a, b, cp, cn, d; };
 template <int BN, int EPI>
 __device__ __forceinline__ bool tab_load(const GemmParams &p, int e, int m0, int n0, TabWords &w) {
     const int last_row = min(m0 + GEMM_BM, p.M) - 1;
-    const int first_pl = (m0 / p.seq_len) >> 1;
-    const int nslots = ((last_row / p.seq_len) >> 1) - first_pl + 1;
+    const int first_pl = fast_div(m0, p.fd_seq) >> 1;
+    const int nslots = (fast_div(last_row, p.fd_seq) >> 1) - first_pl + 1;
     if (e >= nslots * (BN / 4)) return false;
     const int sl = e / (BN / 4), j = (e % (BN / 4)) * 4;
     const int8_t *base = p.nt + (int64_t)(first_pl + sl) * p.nt_stride;
@@ -178,14 +180,21 @@ __device__ __forceinline__ void tab_store(const GemmParams &p, GemmSmem<BN> &sm,
     const int sl = e / (BN / 4), j = (e % (BN / 4)) * 4;
     if (RPL) *reinterpret_cast<int4 *>(&sm.rpl.a32[sl][j]) = make_int4((int)(int8_t)w.a, (int)(int8_t)(w.a >> 8), (int)(int8_t)(w.a >> 16), w.a >> 24);
     else *reinterpret_cast<int32_t *>(&sm.a_tab[sl][j]) = w.a;
-    if (EPI == EPI_GELU || EPI == EPI_PRE32) {
+    if ((EPI == EPI_GELU || EPI == EPI_PRE32) && RPL) {
+        int vp[4], vn[4];
 #pragma unroll
         for (int b = 0; b < 4; b++) {
             const int bb = (int)(int8_t)(w.b >> (8 * b));
-            if (RPL) {
-                sm.rpl.bcs32[sl][0][j + b] = (bb + (int)(int8_t)(w.cp >> (8 * b))) << p.out_shift;
-                sm.rpl.bcs32[sl][1][j + b] = (bb + (int)(int8_t)(w.cn >> (8 * b))) << p.out_shift;
-            } else {
+            vp[b] = (bb + (int)(int8_t)(w.cp >> (8 * b))) << p.out_shift;
+            vn[b] = (bb + (int)(int8_t)(w.cn >> (8 * b))) << p.out_shift;
+        }
+        *reinterpret_cast<int4 *>(&sm.rpl.bcs32[sl][0][j]) = make_int4(vp[0], vp[1], vp[2], vp[3]);
+        *reinterpret_cast<int4 *>(&sm.rpl.bcs32[sl][1][j]) = make_int4(vn[0], vn[1], vn[2], vn[3]);
+    } else if (EPI == EPI_GELU || EPI == EPI_PRE32) {
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            const int bb = (int)(int8_t)(w.b >> (8 * b));
+            {
                 sm.bc_tab[sl][0][j + b] = (int16_t)(bb + (int)(int8_t)(w.cp >> (8 * b)));
                 sm.bc_tab[sl][1][j + b] = (int16_t)(bb + (int)(int8_t)(w.cn >> (8 * b)));
             }
@@ -199,14 +208,13 @@ __device__ __forceinline__ void tab_store(const GemmParams &p, GemmSmem<BN> &sm,
 // pair slot and sign are then per-lane scalars and the per-column tables are read at warp-uniform addresses, so the
 // accumulators are consumed straight from the TMEM layout (lane = row, registers = columns) with no transpose, no
 // shuffles and about half the instructions of the transposed form.  TMEM loads are double-buffered.
-template <int BN, int EPI>
+template <int BN, int EPI, bool ROPE>
 __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &sm, uint32_t taddr, int r, bool row_ok, int n0,
                                              int cbase, int slot, int sgn, int32_t (*st)[20], int lane, int m0q, int xbs,
                                              const int4 (&rs_pre)[BN / 4 / 16], const CUtensorMap *tmap_o, int32_t *ost) {
     constexpr int NCH = BN / 4 / 16;                       // 16-column chunks of this warp's quarter of the tile
     const int rc = row_ok ? r : (p.M - 1);
-    const int mem = rc / p.seq_len;
-    const int part = (EPI == EPI_QKV) ? (n0 / p.third) : 0;
+    const int mem = fast_div(rc, p.fd_seq);
     const uint32_t lut_base = ptx::smem_u32(&sm.lut16[0][lane & 15]);
     const uint32_t a32 = ptx::smem_u32(sm.rpl.a32[slot] + cbase);           // 32-bit shared addresses of this lane's tables
     const uint32_t bcs = ptx::smem_u32(sm.rpl.bcs32[slot][sgn] + cbase);
@@ -214,7 +222,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
     const int8_t *dt = sm.d_tab[slot] + cbase;
     const int64_t gofs = (int64_t)rc * p.N + n0 + cbase;
     const int2 *rope = p.rope_t + (rc - mem * p.seq_len);                                // column of this token position
-    const bool do_rope = (EPI == EPI_QKV) && part < 2;
+    constexpr bool do_rope = (EPI == EPI_QKV) && ROPE;      // Q and K column tiles; V passes through
     const long long half_ulp = 1ll << (p.rope_bit - 1);
     int racc = 0;
     uint32_t v[2][16];
@@ -224,7 +232,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
         int4 cs[4];
         if (EPI == EPI_QKV && do_rope) {
             // the lanes of a warp are consecutive tokens of one member: every load below is one contiguous run
-            const int pair0 = ((n0 + cbase + 16 * c) % p.head_dim) >> 1;
+            const int pair0 = fast_mod(n0 + cbase + 16 * c, p.fd_head) >> 1;
 #pragma unroll
             for (int q4 = 0; q4 < 4; q4++) {
                 const int2 c0 = __ldg(rope + (int64_t)(pair0 + 2 * q4) * p.seq_len), c1 = __ldg(rope + (int64_t)(pair0 + 2 * q4 + 1) * p.seq_len);
@@ -388,7 +396,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                int m0 = (tile / tiles_n) * GEMM_BM, n0 = (tile % tiles_n) * BN;
+                int tm_ = fast_div(tile, p.fd_tiles_n), m0 = tm_ * GEMM_BM, n0 = (tile - tm_ * tiles_n) * BN;
                 for (int kb = 0; kb < num_kb; kb++, it++) {
                     int s = it % GEMM_STAGES;
                     uint32_t ph = (it / GEMM_STAGES) & 1;
@@ -448,7 +456,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tcount++) {
             const int as = tcount & 1;
             const uint32_t aph = (tcount >> 1) & 1;
-            const int m0 = (tile / tiles_n) * GEMM_BM, n0 = (tile % tiles_n) * BN;
+            const int tm_ = fast_div(tile, p.fd_tiles_n), m0 = tm_ * GEMM_BM, n0 = (tile - tm_ * tiles_n) * BN;
             const int r = m0 + row_in_tile;
             const bool row_ok = r < p.M;
 
@@ -457,8 +465,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             int first_pl = 0, slot = 0, sgn = 0;
             if (EPI <= EPI_HEAD) {
                 int last_row = min(m0 + GEMM_BM, p.M) - 1;
-                first_pl = (m0 / p.seq_len) >> 1;
-                int mem = (row_ok ? r : last_row) / p.seq_len;
+                first_pl = fast_div(m0, p.fd_seq) >> 1;
+                int mem = fast_div(row_ok ? r : last_row, p.fd_seq);
                 slot = (mem >> 1) - first_pl;
                 sgn = mem & 1;
                 if (tcount == 0) {
@@ -480,10 +488,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 rok[i] = rr < p.M;
                 const int rc = rok[i] ? rr : (p.M - 1);
                 rrow[i] = rc;
-                const int mem = rc / p.seq_len;
+                const int mem = fast_div(rc, p.fd_seq);
                 const int sg = mem & 1;
                 slot_sgn[i] = (((mem >> 1) - first_pl) << 1) | sg;
-                const int xcol = (EPI == EPI_QKV) ? (n0 / p.third) : 0;
+                const int xcol = (EPI == EPI_QKV) ? fast_div(n0, p.fd_third) : 0;
                 const int xbv = p.xb[(int64_t)rc * p.xb_stride + xcol];
                 xbs[i] = sg ? -xbv : xbv;
                 aux[i] = 0;
@@ -503,7 +511,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (RPL && active) {
                 const int rc = row_ok ? r : (p.M - 1);
                 if (tcount == 0) {
-                    pf_xb = p.xb[(int64_t)rc * p.xb_stride + ((EPI == EPI_QKV) ? (n0 / p.third) : 0)];
+                    pf_xb = p.xb[(int64_t)rc * p.xb_stride + ((EPI == EPI_QKV) ? fast_div(n0, p.fd_third) : 0)];
                     if (EPI == EPI_PRE32) pf_rs0 = *reinterpret_cast<const int4 *>(p.resid + (int64_t)rc * p.N + n0 + cbase);
                 }
                 xbs_l = sgn ? -pf_xb : pf_xb;
@@ -537,11 +545,11 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (EPI <= EPI_HEAD) {
                 const int ntile = tile + gridDim.x;
                 if (ntile < num_tiles) {
-                    const int nm0 = (ntile / tiles_n) * GEMM_BM, nn0 = (ntile % tiles_n) * BN;
+                    const int ntm = fast_div(ntile, p.fd_tiles_n), nm0 = ntm * GEMM_BM, nn0 = (ntile - ntm * tiles_n) * BN;
                     have_nxt = tab_load<BN, EPI>(p, e, nm0, nn0, nxt);
                     if (RPL && active) {
                         const int nr = nm0 + row_in_tile, nrc = nr < p.M ? nr : (p.M - 1);
-                        pf_xb = p.xb[(int64_t)nrc * p.xb_stride + ((EPI == EPI_QKV) ? (nn0 / p.third) : 0)];
+                        pf_xb = p.xb[(int64_t)nrc * p.xb_stride + ((EPI == EPI_QKV) ? fast_div(nn0, p.fd_third) : 0)];
                         if (EPI == EPI_PRE32) pf_rs0 = *reinterpret_cast<const int4 *>(p.resid + (int64_t)nrc * p.N + nn0 + half * COLS_PER);
                     }
                 }
@@ -552,8 +560,12 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (!active) {
                 // nothing to compute; still takes part in the barrier protocol below
             } else if (RPL) {
-                epilogue_rpl<BN, EPI>(p, sm, taddr, r, row_ok, n0, cbase, slot, sgn, sm.stage[ew], lane, m0 + quarter * 32, xbs_l, rs_l, &tmap_o,
-                                      sm.ostage[ew]);
+                if (EPI == EPI_QKV && n0 < 2 * p.third)
+                    epilogue_rpl<BN, EPI, true>(p, sm, taddr, r, row_ok, n0, cbase, slot, sgn, sm.stage[ew], lane, m0 + quarter * 32, xbs_l, rs_l,
+                                                &tmap_o, sm.ostage[ew]);
+                else
+                    epilogue_rpl<BN, EPI, false>(p, sm, taddr, r, row_ok, n0, cbase, slot, sgn, sm.stage[ew], lane, m0 + quarter * 32, xbs_l, rs_l,
+                                                 &tmap_o, sm.ostage[ew]);
             } else if (EPI <= EPI_HEAD) {
                 // ---------------- evaluation epilogues ----------------
                 // Accumulators leave TMEM one row per lane; they are transposed through shared memory so
@@ -630,7 +642,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                             } else if (EPI == EPI_QKV) {
                                 if (n0 < 2 * p.third) {
                                     // integer RoPE on adjacent (even, odd) columns (apply_rope_integer, mgpu.cu:624-644)
-                                    const int hd0 = (n0 + col) % p.head_dim;
+                                    const int hd0 = fast_mod(n0 + col, p.fd_head);
                                     const int4 cs = __ldg(reinterpret_cast<const int4 *>(p.rope_lut + (int64_t)aux[i] * p.head_dim + hd0));
                                     const long long half_ulp = 1ll << (p.rope_bit - 1);
                                     const long long e0 = v0, o0 = v1, e1 = v2, o1 = v3;
@@ -670,7 +682,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1)); m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
                         if (pc == 0 && rok[i]) {
                             if (EPI == EPI_PRE32) atomicMax(&p.rowstat[rrow[i]], m);
-                            else atomicMax(&p.rowstat[(int64_t)rrow[i] * 3 + n0 / p.third], m);
+                            else atomicMax(&p.rowstat[(int64_t)rrow[i] * 3 + fast_div(n0, p.fd_third)], m);
                         }
                     } else if (EPI == EPI_HEAD) {
                         int sm_ = rsum[i], tg = rtgt[i];          // the target column lives in exactly one lane: others hold 0
@@ -679,7 +691,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         if (pc == 0 && rok[i]) {
                             int log_sum = 0;
                             if (sm_ > 0) log_sum = ((31 - __clz(sm_)) << 4) - (p.softmax_scale_bit << 4);   // floor(log2), shift ladder of mgpu.cu:1015-1019
-                            atomicAdd(&p.loss[rrow[i] / p.seq_len], (log_sum >> 1) + racc[i] - tg);
+                            atomicAdd(&p.loss[fast_div(rrow[i], p.fd_seq)], (log_sum >> 1) + racc[i] - tg);
                         }
                     }
                 }
@@ -754,7 +766,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                           a3 = sm.rowpart[3][row_in_tile];
                 if (EPI == EPI_GELU) atomicAdd(&p.rowstat[r], a0 + a1 + a2 + a3);
                 else if (EPI == EPI_PRE32) atomicMax(&p.rowstat[r], max(max(a0, a1), max(a2, a3)));
-                else if (EPI == EPI_QKV) atomicMax(&p.rowstat[(int64_t)r * 3 + n0 / p.third], max(max(a0, a1), max(a2, a3)));
+                else if (EPI == EPI_QKV) atomicMax(&p.rowstat[(int64_t)r * 3 + fast_div(n0, p.fd_third)], max(max(a0, a1), max(a2, a3)));
             }
             if (EPI <= EPI_HEAD && have_nxt) tab_store<BN, EPI, RPL>(p, sm, e, nxt);   // published by the next tile's barrier
         }

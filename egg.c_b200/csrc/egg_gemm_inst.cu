@@ -111,7 +111,8 @@ static int launch_eval(cudaStream_t st, int bn, const CUtensorMap &ta, const CUt
     return launch_bn<EPI, 0>(st, bn, ta, tb, to, p, num_sms);
 }
 
-int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, const GemmParams &p, int num_sms) {
+int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, const GemmParams &p_in, int num_sms) {
+    GemmParams p = p_in;
     if (!g_encode) { set_error("gemm_init() was not called"); return EGG_E_STATE; }
     if (p.M <= 0 || p.N % 128 || p.K % 16) { set_error("unsupported GEMM shape M=%d N=%d K=%d", p.M, p.N, p.K); return EGG_E_INVALID; }
     int bn = (p.N % 256 == 0) ? 256 : 128;
@@ -122,6 +123,10 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
         int max_slots = ((GEMM_BM - 1) / p.seq_len) / 2 + 2;
         if (max_slots > GEMM_MAX_SLOTS) { set_error("seq_len %d too small for the epilogue tables", p.seq_len); return EGG_E_INVALID; }
     }
+    p.fd_seq = make_fastdiv(p.seq_len);
+    p.fd_tiles_n = make_fastdiv(p.N / bn);
+    p.fd_third = make_fastdiv(p.third);
+    p.fd_head = make_fastdiv(p.head_dim);
     CUtensorMap ta, tb;
     int rc;
     if ((rc = make_tmap(&ta, A, (uint64_t)p.M, (uint64_t)p.K, GEMM_BM))) return rc;

@@ -198,11 +198,10 @@ __device__ __forceinline__ int aln_quant_raw(int val, float scale24) { return al
 
 // trunc(a / mn) as C integer division does, for |a| < 2^15 and 1 <= mn <= 127:
 // a*(1/mn) is off by < 0.003, exact quotients are pushed off the integer by a bias of
-// 0.004 (the nearest non-integer quotient is 1/127 away), then truncated by rounding y -/+ 0.5.
+// 0.004 (the nearest non-integer quotient is 1/127 away), then truncated by the conversion.
 __device__ __forceinline__ int div_small(int a, float rinv) {
     float af = i2f_small(a);
-    float y = fmaf(af, rinv, copysignf(0.004f, af));
-    return __float_as_int((y - copysignf(0.5f, y)) + kMagic) - kMagicBits;      // the magic add rounds to the integer and exposes it
+    return __float2int_rz(fmaf(af, rinv, copysignf(0.004f, af)));
 }
 
 // [sat8(a), sat8(b), sat8(c), sat8(d)] as bytes 0..3 with the reference's clip to [-127, 127]
@@ -223,7 +222,7 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
     const int lane = threadIdx.x & 31;
     if (r >= p.M) return;
     const int H = NJ * 128;
-    const int mem = r / p.seq_len, t = r % p.seq_len;
+    const int mem = fast_div(r, p.fd_seq), t = r - mem * p.seq_len;
     const int sgn = mem & 1, ns = sgn ? -1 : 1;
     const int8_t *ntp = p.nt + (int64_t)(mem >> 1) * p.nt_stride;
     const int16_t *wm = reinterpret_cast<const int16_t *>(ntp + p.nt_w_m) + sgn * H;   // w + ((n1*n2*sign)>>SSV)
@@ -349,7 +348,9 @@ static int launch_rowwise_nj(cudaStream_t st, const RowParams &p) {
     return EGG_OK;
 }
 
-int launch_rowwise(cudaStream_t st, const RowParams &p, int mode) {
+int launch_rowwise(cudaStream_t st, const RowParams &p_in, int mode) {
+    RowParams p = p_in;
+    p.fd_seq = make_fastdiv(p.seq_len);
     return mode == 0 ? launch_rowwise_nj<0>(st, p) : launch_rowwise_nj<1>(st, p);
 }
 

@@ -44,6 +44,7 @@ int launch_noise_fill(cudaStream_t st, int8_t *nt, int64_t stride, const NoiseSe
 // ---- row-wise kernels -------------------------------------------------------
 struct RowParams {
     int M, H, seq_len;
+    FastDiv fd_seq;              // seq_len as a multiply-shift divisor (filled by launch_rowwise)
     const int8_t *nt; int64_t nt_stride;
     // source: embedding (mode 0) or adaptive layer normalise of pre32 (mode 1)
     const uint8_t *dataset; int64_t data_len, start_idx, data_stride; int pop_base, use_same_data;

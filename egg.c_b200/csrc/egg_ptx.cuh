@@ -49,13 +49,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same test, letting the hardware keep the thread suspended for up to hint_ns while the phase is incomplete:
+// a waiting thread then issues a handful of instructions per microsecond instead of spinning.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t *bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: true when the phase completed, false after ~limit_ns.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint64_t limit_ns = 2000000000ull) {
     if (mbar_try_wait(bar, parity)) return true;
-    uint64_t t0 = globaltimer();
-    for (uint32_t spin = 1;; spin++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 0x3FF) == 0 && globaltimer() - t0 > limit_ns) return false;
+    const uint64_t t0 = globaltimer();
+    for (;;) {
+        if (mbar_try_wait_suspend(bar, parity, 2000u)) return true;
+        if (globaltimer() - t0 > limit_ns) return false;
     }
 }
 
