@@ -145,8 +145,7 @@ int launch_noise_fill(cudaStream_t st, int8_t *nt, int64_t stride, const NoiseSe
 // =========================================================================
 
 __device__ __forceinline__ int warp_sum(int v) {
-    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
-    return v;
+    return __reduce_add_sync(0xFFFFFFFFu, v);       // one warp-wide integer reduction instruction; every lane gets the sum
 }
 
 __device__ __forceinline__ int8_t byte_of(int32_t w, int i) { return (int8_t)(w >> (8 * i)); }
@@ -186,15 +185,13 @@ __device__ __forceinline__ float aln_scale24(int layer_max) { return aln_scale(l
 // keeps every bit that decides the rounding (for |x| >= 1 the product has at most 23 fraction bits; below 1 only
 // "is it >= 0.5" matters, which truncation preserves), and round-half-away-from-zero becomes (xi + 2^23) >> 24.
 // The result cannot leave [-127, 127], so the reference's clamp needs no instruction.
-template <bool SMALL>
+// The float product and its truncation are symmetric in the sign of v, so the sign is carried through: for a negative
+// truncated product xi = -a, -((a + 2^23) >> 24) == (xi + 2^23 - 1) >> 24 (the arithmetic shift floors), which is the
+// positive formula plus the sign word xi >> 31.
 __device__ __forceinline__ int aln_quant(int val, float scale24) {
-    const int av = abs(val);
-    const float vf = SMALL ? i2f_cvt(av) : (float)av;
-    const int t = (__float2int_rz(vf * scale24) + (1 << 23)) >> 24;
-    return val < 0 ? -t : t;
+    const int xi = __float2int_rz(__int2float_rn(val) * scale24);
+    return (xi + (1 << 23) + (xi >> 31)) >> 24;
 }
-template <bool SMALL>
-__device__ __forceinline__ int aln_quant_raw(int val, float scale24) { return aln_quant<SMALL>(val, scale24); }
 
 // trunc(a / mn) as C integer division does, for |a| < 2^15 and 1 <= mn <= 127:
 // a*(1/mn) is off by < 0.003, exact quotients are pushed off the integer by a bias of
@@ -277,18 +274,10 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
         for (int j = 0; j < NJ; j++) v[j] = *reinterpret_cast<const int4 *>(p.pre32 + (int64_t)r * H + (j << 7) + (lane << 2));
         const int mx = p.rowmax[r];
         const float scale = aln_scale24(mx);
-        if (mx < (1 << 22)) {
 #pragma unroll
-            for (int j = 0; j < NJ; j++) {
-                x[j][0] = aln_quant<true>(v[j].x, scale); x[j][1] = aln_quant<true>(v[j].y, scale);
-                x[j][2] = aln_quant<true>(v[j].z, scale); x[j][3] = aln_quant<true>(v[j].w, scale);
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < NJ; j++) {
-                x[j][0] = aln_quant<false>(v[j].x, scale); x[j][1] = aln_quant<false>(v[j].y, scale);
-                x[j][2] = aln_quant<false>(v[j].z, scale); x[j][3] = aln_quant<false>(v[j].w, scale);
-            }
+        for (int j = 0; j < NJ; j++) {
+            x[j][0] = aln_quant(v[j].x, scale); x[j][1] = aln_quant(v[j].y, scale);
+            x[j][2] = aln_quant(v[j].z, scale); x[j][3] = aln_quant(v[j].w, scale);
         }
     }
     int tot = 0;
@@ -435,17 +424,10 @@ __global__ void __launch_bounds__(256) aqn_kernel(const AqnParams p) {
         const int mx = which == 0 ? mx0 : (which == 1 ? mx1 : mx2);
         const float scale = aln_scale24(mx);
         int8_t *out = (which == 0 ? p.q : (which == 1 ? p.k : p.v)) + (int64_t)r * H + (lane << 2);
-        if (mx < (1 << 22)) {
 #pragma unroll
-            for (int j = 0; j < NJ; j++)
-                *reinterpret_cast<uint32_t *>(out + (j << 7)) = pack_clip8(aln_quant_raw<true>(v[which][j].x, scale), aln_quant_raw<true>(v[which][j].y, scale),
-                                                                           aln_quant_raw<true>(v[which][j].z, scale), aln_quant_raw<true>(v[which][j].w, scale));
-        } else {
-#pragma unroll
-            for (int j = 0; j < NJ; j++)
-                *reinterpret_cast<uint32_t *>(out + (j << 7)) = pack_clip8(aln_quant_raw<false>(v[which][j].x, scale), aln_quant_raw<false>(v[which][j].y, scale),
-                                                                           aln_quant_raw<false>(v[which][j].z, scale), aln_quant_raw<false>(v[which][j].w, scale));
-        }
+        for (int j = 0; j < NJ; j++)
+            *reinterpret_cast<uint32_t *>(out + (j << 7)) = pack_clip8(aln_quant(v[which][j].x, scale), aln_quant(v[which][j].y, scale),
+                                                                       aln_quant(v[which][j].z, scale), aln_quant(v[which][j].w, scale));
     }
 }
 
@@ -654,12 +636,18 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
             // A fragments of the three limbs; k-slot 4q+{0,1,2,3} <-> keys {2q, 2q+1, 8+2q, 9+2q} (+16 for a2/a3)
             uint32_t al[3][4];
 #pragma unroll
+            for (int f = 0; f < 4; f++) {
+                // 4 x 3 byte transpose of the four weights of fragment register f (7 byte permutes)
+                const int n0 = (f >> 1) * 2, i0 = (f & 1) * 2;
+                const uint32_t wa = w[n0][i0], wb = w[n0][i0 + 1], wc = w[n0 + 1][i0], wd = w[n0 + 1][i0 + 1];
+                const uint32_t t0 = __byte_perm(wa, wb, 0x5140), t1 = __byte_perm(wc, wd, 0x5140);     // [a0 b0 a1 b1], [c0 d0 c1 d1]
+                const uint32_t t2 = __byte_perm(wa, wb, 0x7362), t3 = __byte_perm(wc, wd, 0x7362);     // [a2 b2 . .], [c2 d2 . .]
+                al[0][f] = __byte_perm(t0, t1, 0x5410);
+                al[1][f] = __byte_perm(t0, t1, 0x7632);
+                al[2][f] = __byte_perm(t2, t3, 0x5410);
+            }
+#pragma unroll
             for (int l = 0; l < 3; l++) {
-                const uint32_t sel = (uint32_t)l | ((uint32_t)(4 + l) << 4);       // byte l of x, byte l of y
-                al[l][0] = __byte_perm(__byte_perm(w[0][0], w[0][1], sel), __byte_perm(w[1][0], w[1][1], sel), 0x5410);
-                al[l][1] = __byte_perm(__byte_perm(w[0][2], w[0][3], sel), __byte_perm(w[1][2], w[1][3], sel), 0x5410);
-                al[l][2] = __byte_perm(__byte_perm(w[2][0], w[2][1], sel), __byte_perm(w[3][0], w[3][1], sel), 0x5410);
-                al[l][3] = __byte_perm(__byte_perm(w[2][2], w[2][3], sel), __byte_perm(w[3][2], w[3][3], sel), 0x5410);
                 tl0[l] = __dp4a((int)al[l][0], 0x01010101, __dp4a((int)al[l][2], 0x01010101, tl0[l]));
                 tl1[l] = __dp4a((int)al[l][1], 0x01010101, __dp4a((int)al[l][3], 0x01010101, tl1[l]));
             }
