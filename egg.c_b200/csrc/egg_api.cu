@@ -1012,7 +1012,8 @@ extern "C" int egg_perturbed_projection(egg_ctx *c, const int8_t *x, const int8_
         PTRYC(cudaMemcpyAsync(d_w, w_packed, (size_t)K * N, cudaMemcpyHostToDevice, st));
     }
     PTRY(dev_alloc(&d_wt, (int64_t)K * N)); PTRY(dev_alloc(&d_nt, pairs * stride)); PTRY(dev_alloc(&d_xb, rows)); PTRY(dev_alloc(&d_segs, 2));
-    NoiseSeg segs[2] = {{0, N, 0, off_a, 0, 0, -1, -1}, {N, K, 0, off_b, 0, 0, -1, -1}};
+    NoiseSeg segs[2] = {{0, N, 0, off_a, 0, 0, -1, -1, 0}, {N, K, 0, off_b, 0, 0, -1, -1, 0}};
+    noise_index_slices(segs, 2);
     PTRYC(cudaMemcpyAsync(d_segs, segs, sizeof(segs), cudaMemcpyHostToDevice, st));
     PTRY(launch_unpack_transpose(st, d_w, d_wt, K, N));
     PTRY(launch_noise_fill(st, d_nt, stride, d_segs, 2, (int)pairs, seed, 0, c->cfg.device_mask, c->cfg.device_gaussian, nullptr, nullptr));

@@ -75,6 +75,7 @@ void build_noise_map(const egg_config &c, NoiseMap *map, NoiseSeg *segs, int *ns
     }
     map->stride = (off + 15) & ~15;
     *nsegs = n;
+    noise_index_slices(segs, n < max_segs ? n : max_segs);
 }
 
 __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d);
@@ -82,28 +83,28 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d);
 // scales: AdaptiveScales bytes or null.  With scales, every segment that has an overlay holds
 // (int)(noise * factor) (A vectors, layers.cuh:90) or the delta built from (int)(n1 * n2 * factor)
 // (vectors, layers.cuh:176-180), so that the consumers of the table need not know about overlays.
+int noise_index_slices(NoiseSeg *segs, int nsegs) {
+    int acc = 0;
+    for (int i = 0; i < nsegs; i++) { segs[i].first = acc; acc += (segs[i].len + 1023) >> 10; }
+    return acc;
+}
+
 __global__ void __launch_bounds__(256) noise_fill_kernel(int8_t *nt, int64_t stride, const NoiseSeg *segs, int nsegs, uint32_t step_seed,
                                                          int pair_base, int mask, int gaussian, const int8_t *model, const int8_t *scales) {
     extern __shared__ NoiseSeg s_segs[];
-    int *s_first = reinterpret_cast<int *>(s_segs + nsegs);       // first 1024-element slice of every segment, then the total
     for (int i = threadIdx.x; i < nsegs; i += blockDim.x) s_segs[i] = segs[i];
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int acc = 0;
-        for (int i = 0; i < nsegs; i++) { s_first[i] = acc; acc += (s_segs[i].len + 1023) >> 10; }
-        s_first[nsegs] = acc;
-    }
-    __syncthreads();
+    const int total_slices = s_segs[nsegs - 1].first + ((s_segs[nsegs - 1].len + 1023) >> 10);
     const int pair = blockIdx.y;
     const uint32_t S0 = step_seed + (uint32_t)(pair_base + pair);
     int8_t *dst = nt + (int64_t)pair * stride;
     // one block iteration = 1024 consecutive elements of one segment, four per thread (segment lengths are multiples
     // of four); an element of a delta segment is hashed once and written for both signs
     int g = 0;
-    for (int sl = blockIdx.x; sl < s_first[nsegs]; sl += gridDim.x) {
-        while (s_first[g + 1] <= sl) g++;                          // slices are visited in increasing order
+    for (int sl = blockIdx.x; sl < total_slices; sl += gridDim.x) {
+        while (g + 1 < nsegs && s_segs[g + 1].first <= sl) g++;    // slices are visited in increasing order
         const NoiseSeg sg = s_segs[g];
-        const int i0 = ((sl - s_first[g]) << 10) + (threadIdx.x << 2);
+        const int i0 = ((sl - sg.first) << 10) + (threadIdx.x << 2);
         if (i0 >= sg.len) continue;
         const bool scaled = scales != nullptr && sg.scale_off >= 0;
         int vp[4], vn[4];
@@ -132,9 +133,9 @@ __global__ void __launch_bounds__(256) noise_fill_kernel(int8_t *nt, int64_t str
 
 int launch_noise_fill(cudaStream_t st, int8_t *nt, int64_t stride, const NoiseSeg *d_segs, int nsegs, int n_pairs,
                       uint32_t step_seed, int pair_base, int mask, int gaussian, const int8_t *model, const int8_t *scales) {
-    int gx = (int)((stride + 255) / 256); if (gx > 64) gx = 64;
+    int gx = (int)((stride + 255) / 256); if (gx > 16) gx = 16;      // a few slices per block amortise the segment-table load
     dim3 grid((unsigned)gx, (unsigned)n_pairs);
-    const size_t smem = nsegs * sizeof(NoiseSeg) + (nsegs + 1) * sizeof(int);
+    const size_t smem = nsegs * sizeof(NoiseSeg);
     noise_fill_kernel<<<grid, 256, smem, st>>>(nt, stride, d_segs, nsegs, step_seed, pair_base, mask, gaussian, model, scales);
     EGG_CUDA(cudaGetLastError());
     return EGG_OK;

@@ -19,7 +19,11 @@ struct NoiseSeg {
     int shift;
     int64_t model_off;
     int64_t scale_off;   // AdaptiveScales offset of the overlay scaling this segment (-1: raw noise)
+    int first;           // index of the segment's first 1024-element slice in the table-wide slice order (set by noise_index_slices)
 };
+
+// Fills NoiseSeg::first for a finished segment list and returns the total number of slices.
+int noise_index_slices(NoiseSeg *segs, int nsegs);
 
 struct NormOff { int w_m, b_m; };                       // perturbed gain / bias, int16 [2][H] each
 struct MlpOff { int up_b, up_a, bup_d, dn_b, dn_a, bdn_d; };
