@@ -224,7 +224,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
     const int2 *rope = p.rope_t + (rc - mem * p.seq_len);                                // column of this token position
     constexpr bool do_rope = (EPI == EPI_QKV) && ROPE;      // Q and K column tiles; V passes through
     const long long half_ulp = 1ll << (p.rope_bit - 1);
-    int racc = 0;
+    int racc = 0, rmx = 0, rmn = 0;
     uint32_t v[2][16];
     ptx::tmem_ld16(taddr, v[0]);
 #pragma unroll
@@ -267,11 +267,13 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
             } else if (EPI == EPI_PRE32) {
                 const int4 b4 = ptx::lds_v4(bcs + 4 * col);
                 const int32_t rs = q4 == 0 ? rs_pre[c].x : (q4 == 1 ? rs_pre[c].y : (q4 == 2 ? rs_pre[c].z : rs_pre[c].w));
-                x0 = (int)(int8_t)(rs) + ((x0 + b4.x) >> p.out_shift);
-                x1 = (int)(int8_t)(rs >> 8) + ((x1 + b4.y) >> p.out_shift);
-                x2 = (int)(int8_t)(rs >> 16) + ((x2 + b4.z) >> p.out_shift);
-                x3 = (int)(rs >> 24) + ((x3 + b4.w) >> p.out_shift);
-                racc = max(racc, max(max(abs(x0), abs(x1)), max(abs(x2), abs(x3))));
+                // residual bytes sign-extended by one byte permute each (selector msb = replicate the byte's sign)
+                x0 = ptx::sx_byte0(rs) + ((x0 + b4.x) >> p.out_shift);
+                x1 = ptx::sx_byte1(rs) + ((x1 + b4.y) >> p.out_shift);
+                x2 = ptx::sx_byte2(rs) + ((x2 + b4.z) >> p.out_shift);
+                x3 = (rs >> 24) + ((x3 + b4.w) >> p.out_shift);
+                rmx = __vimax3_s32(__vimax3_s32(rmx, x0, x1), x2, x3);      // abs-max as max(max, -min): three-input min/max, no abs
+                rmn = __vimin3_s32(__vimin3_s32(rmn, x0, x1), x2, x3);
                 o4[q4] = make_int4(x0, x1, x2, x3);
             } else if (EPI == EPI_QKV) {
                 if (do_rope) {
@@ -284,7 +286,8 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                     x2 = ptx::shr64_lo(ptx::mad_wide(-o1, cs[q4].w, ptx::mad_wide(e1, cs[q4].z, half_ulp)), p.rope_bit);
                     x3 = ptx::shr64_lo(ptx::mad_wide(o1, cs[q4].z, ptx::mad_wide(e1, cs[q4].w, half_ulp)), p.rope_bit);
                 }
-                racc = max(racc, max(max(abs(x0), abs(x1)), max(abs(x2), abs(x3))));
+                rmx = __vimax3_s32(__vimax3_s32(rmx, x0, x1), x2, x3);
+                rmn = __vimin3_s32(__vimin3_s32(rmn, x0, x1), x2, x3);
                 o4[q4] = make_int4(x0, x1, x2, x3);
             }
         }
@@ -342,8 +345,75 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
         }
         __syncwarp();
     }
+    if (EPI == EPI_PRE32 || EPI == EPI_QKV) racc = max(rmx, -rmn);
     // per-row partial of this column quarter; the quarters are combined after the end-of-tile barrier
     sm.rowpart[cbase / (BN / 4)][m0q + lane - (m0q & ~(GEMM_BM - 1))] = racc;
+}
+
+// Head + integer cross-entropy in the row-per-lane form (mgpu.cu:969-1023).  The four warps that share a TMEM lane
+// quarter each take a quarter of the vocabulary columns of the same 32 rows: pass 0 finds the row maximum (partials
+// exchanged through shared memory under a 128-thread named barrier), pass 1 re-reads the accumulators for
+// Σ exp-LUT and the target logit, and the warp of the first column quarter adds one loss term per row, reduced over
+// the warp (all its rows belong to one member) into a single atomic.
+template <int BN>
+__device__ __forceinline__ void epilogue_head_rpl(const GemmParams &p, GemmSmem<BN> &sm, uint32_t taddr, int r, bool row_ok, int cbase,
+                                                  int slot, int lane, int quarter, int row_in_tile, int xbs) {
+    constexpr int NCH = BN / 4 / 16;
+    int32_t(*hp)[4][GEMM_BM] = reinterpret_cast<int32_t(*)[4][GEMM_BM]>(&sm.stage[0][0][0]);    // [max | sum | target][quarter][row]
+    const int cq = cbase / (BN / 4);
+    const int rc = row_ok ? r : (p.M - 1);
+    const int mem = fast_div(rc, p.fd_seq);
+    const int t = rc - mem * p.seq_len;
+    const int64_t pair = (p.pop_base + mem) >> 1;
+    const int64_t pos = p.use_same_data ? (p.start_idx % (p.data_len - p.seq_len)) : ((p.start_idx + pair * p.data_stride) % (p.data_len - p.seq_len));
+    const int tgt_col = (int)p.dataset[pos + t + 1] - cbase;                    // target column relative to this warp's quarter
+    const uint32_t a32 = ptx::smem_u32(sm.rpl.a32[slot] + cbase);
+    uint32_t v[2][16];
+    int mx = INT_MIN, sum = 0, tg = 0;
+#pragma unroll 1
+    for (int pass = 0; pass < 2; pass++) {
+        ptx::tmem_ld16(taddr, v[0]);
+#pragma unroll
+        for (int c = 0; c < NCH; c++) {
+            uint32_t *vc = v[c & 1];
+            ptx::tmem_ld_wait16(vc);
+            if (c + 1 < NCH) ptx::tmem_ld16(taddr + 16 * (c + 1), v[(c + 1) & 1]);
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) {
+                const int col = 16 * c + 4 * q4;
+                const int4 an = ptx::lds_v4(a32 + 4 * col);
+                const int l0 = ((int)vc[4 * q4] + ((xbs * an.x) >> p.rank1_shift)) >> p.out_shift;
+                const int l1 = ((int)vc[4 * q4 + 1] + ((xbs * an.y) >> p.rank1_shift)) >> p.out_shift;
+                const int l2 = ((int)vc[4 * q4 + 2] + ((xbs * an.z) >> p.rank1_shift)) >> p.out_shift;
+                const int l3 = ((int)vc[4 * q4 + 3] + ((xbs * an.w) >> p.rank1_shift)) >> p.out_shift;
+                if (pass == 0) {
+                    mx = __vimax3_s32(__vimax3_s32(mx, l0, l1), l2, l3);
+                } else {
+                    sum += sm.exp_lut[min(255, mx - l0)] + sm.exp_lut[min(255, mx - l1)] + sm.exp_lut[min(255, mx - l2)] +
+                           sm.exp_lut[min(255, mx - l3)];
+                    const int tc = tgt_col - col;
+                    if (tc == 0) tg = l0; else if (tc == 1) tg = l1; else if (tc == 2) tg = l2; else if (tc == 3) tg = l3;
+                }
+            }
+        }
+        if (pass == 0) {
+            hp[0][cq][row_in_tile] = mx;
+            ptx::named_bar_sync(2 + quarter, 128);
+            mx = max(max(hp[0][0][row_in_tile], hp[0][1][row_in_tile]), max(hp[0][2][row_in_tile], hp[0][3][row_in_tile]));
+        }
+    }
+    hp[1][cq][row_in_tile] = sum;
+    hp[2][cq][row_in_tile] = tg;                    // the target column lives in exactly one quarter: the others hold 0
+    ptx::named_bar_sync(2 + quarter, 128);
+    if (cq == 0) {
+        const int sm_ = hp[1][0][row_in_tile] + hp[1][1][row_in_tile] + hp[1][2][row_in_tile] + hp[1][3][row_in_tile];
+        const int tgl = hp[2][0][row_in_tile] + hp[2][1][row_in_tile] + hp[2][2][row_in_tile] + hp[2][3][row_in_tile];
+        int log_sum = 0;
+        if (sm_ > 0) log_sum = ((31 - __clz(sm_)) << 4) - (p.softmax_scale_bit << 4);   // floor(log2), shift ladder of mgpu.cu:1015-1019
+        int term = row_ok ? ((log_sum >> 1) + mx - tgl) : 0;
+        term = __reduce_add_sync(0xFFFFFFFFu, term);        // the warp's 32 rows are consecutive tokens of one member
+        if (lane == 0) atomicAdd(&p.loss[mem], term);
+    }
 }
 
 template <int BN, int EPI, int RPL>
@@ -445,7 +515,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int e = threadIdx.x - 64;            // 0..511
         const int ew = warp - 2;                   // 0..15
         const int quarter = warp & 3;              // TMEM lane quarter this warp may read
-        constexpr int NHALF = (EPI == EPI_HEAD) ? 1 : 4;   // column parts per lane quarter; the head keeps whole rows in one warp
+        constexpr int NHALF = (EPI == EPI_HEAD && !RPL) ? 1 : 4;   // column parts per lane quarter; the transposed head keeps whole rows in one warp
         constexpr int COLS_PER = BN / NHALF;
         const int half = (NHALF == 4) ? (ew >> 2) : 0;     // which part of the tile's columns
         const bool active = (NHALF == 4) || ew < 4;
@@ -559,6 +629,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
             if (!active) {
                 // nothing to compute; still takes part in the barrier protocol below
+            } else if (RPL && EPI == EPI_HEAD) {
+                epilogue_head_rpl<BN>(p, sm, taddr, r, row_ok, cbase, slot, lane, quarter, row_in_tile, xbs_l);
             } else if (RPL) {
                 if (EPI == EPI_QKV && n0 < 2 * p.third)
                     epilogue_rpl<BN, EPI, true>(p, sm, taddr, r, row_ok, n0, cbase, slot, sgn, sm.stage[ew], lane, m0 + quarter * 32, xbs_l, rs_l,
@@ -760,7 +832,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (lane == 0) ptx::mbar_arrive(&sm.tmem_empty[as]);
             // tables are rewritten at the top of the next tile: everybody must be done reading them
             ptx::named_bar_sync(1, GEMM_EPI_THREADS);
-            if (RPL && half == 0 && row_ok) {
+            if (RPL && EPI != EPI_HEAD && half == 0 && row_ok) {
                 // one atomic per row and tile instead of one per column quarter
                 const int a0 = sm.rowpart[0][row_in_tile], a1 = sm.rowpart[1][row_in_tile], a2 = sm.rowpart[2][row_in_tile],
                           a3 = sm.rowpart[3][row_in_tile];

@@ -40,6 +40,7 @@ int gemm_init() {
     if ((rc = set_attr_both<EPI_PRE32, 1>())) return rc;
     if ((rc = set_attr_both<EPI_QKV, 1>())) return rc;
     if ((rc = set_attr<256, EPI_HEAD>())) return rc;
+    if ((rc = set_attr<256, EPI_HEAD, 1>())) return rc;
     if ((rc = set_attr_both<EPI_ADAM>())) return rc;
     if ((rc = set_attr_both<EPI_MUON_M>())) return rc;
     if ((rc = set_attr_both<EPI_VOTE>())) return rc;
@@ -143,7 +144,9 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
         case EPI_GELU: return launch_eval<EPI_GELU>(st, bn, ta, tb, to, p, num_sms);
         case EPI_PRE32: return launch_eval<EPI_PRE32>(st, bn, ta, tb, to, p, num_sms);
         case EPI_QKV: return launch_eval<EPI_QKV>(st, bn, ta, tb, to, p, num_sms);
-        case EPI_HEAD: return launch_one<256, EPI_HEAD>(st, ta, tb, to, p, num_sms);
+        case EPI_HEAD:
+            if (p.seq_len % 32 == 0 && p.rpl >= 0) return launch_one<256, EPI_HEAD, 1>(st, ta, tb, to, p, num_sms);
+            return launch_one<256, EPI_HEAD>(st, ta, tb, to, p, num_sms);
         case EPI_ADAM: return launch_bn<EPI_ADAM>(st, bn, ta, tb, to, p, num_sms);
         case EPI_MUON_M: return launch_bn<EPI_MUON_M>(st, bn, ta, tb, to, p, num_sms);
         case EPI_VOTE: return launch_bn<EPI_VOTE>(st, bn, ta, tb, to, p, num_sms);

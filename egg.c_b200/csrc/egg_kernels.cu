@@ -298,8 +298,9 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
         const int d = (j << 7) + (lane << 2);
-        const int wv[4] = {(int)(int16_t)(w4[j].x & 0xFFFF), w4[j].x >> 16, (int)(int16_t)(w4[j].y & 0xFFFF), w4[j].y >> 16};
-        const int bv[4] = {(int)(int16_t)(b4[j].x & 0xFFFF), b4[j].x >> 16, (int)(int16_t)(b4[j].y & 0xFFFF), b4[j].y >> 16};
+        // low halves sign-extended by one byte permute (selector msb = replicate the byte's sign), high halves by a shift
+        const int wv[4] = {ptx::sx_half0(w4[j].x), w4[j].x >> 16, ptx::sx_half0(w4[j].y), w4[j].y >> 16};
+        const int bv[4] = {ptx::sx_half0(b4[j].x), b4[j].x >> 16, ptx::sx_half0(b4[j].y), b4[j].y >> 16};
         int y[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) y[i] = div_small(x[j][i] * wv[i], rinv) + bv[i];

@@ -186,6 +186,19 @@ __device__ __forceinline__ uint32_t pack_sat_s8(int a, int b, int c, int d) {
     return r;
 }
 
+// prmt.b32 in its default mode: selector nibble n picks byte (nibble & 7) of {b, a}; with the nibble's top bit set the
+// picked byte's sign bit is replicated over the result byte instead -- which makes a sign extension one instruction
+template <uint32_t SEL>
+__device__ __forceinline__ int prmt_sx(uint32_t a) {
+    int d;
+    asm("prmt.b32 %0, %1, 0, %2;" : "=r"(d) : "r"(a), "n"(SEL));
+    return d;
+}
+__device__ __forceinline__ int sx_byte0(uint32_t a) { return prmt_sx<0x8880>(a); }     // (int)(int8_t)a
+__device__ __forceinline__ int sx_byte1(uint32_t a) { return prmt_sx<0x9991>(a); }     // (int)(int8_t)(a >> 8)
+__device__ __forceinline__ int sx_byte2(uint32_t a) { return prmt_sx<0xAAA2>(a); }     // (int)(int8_t)(a >> 16)
+__device__ __forceinline__ int sx_half0(uint32_t a) { return prmt_sx<0x9910>(a); }     // (int)(int16_t)a
+
 // a * b + c with a 32 x 32 -> 64-bit product (one instruction)
 __device__ __forceinline__ long long mad_wide(int a, int b, long long c) {
     long long d;
