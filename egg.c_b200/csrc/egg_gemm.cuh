@@ -22,6 +22,7 @@ constexpr int GEMM_THREADS = 576;       // warp0 TMA, warp1 MMA, warps 2..17 epi
 constexpr int GEMM_EPI_THREADS = 512;
 constexpr int GEMM_EPI_WARPS = 16;
 constexpr int GEMM_MAX_SLOTS = 5;       // distinct population pairs a 128-row tile can touch (seq_len >= 16)
+constexpr int GEMM_RPL_SLOTS = 3;       // the same bound for the row-per-lane epilogues (seq_len a multiple of 32)
 
 enum GemmEpi {
     EPI_CLIP8 = 0,   // y = clip((acc + r1) >> out_shift)                       -> int8
@@ -88,8 +89,19 @@ struct GemmSmem {
     alignas(1024) uint8_t a[GEMM_STAGES][GEMM_BM * GEMM_BK];
     alignas(1024) uint8_t b[GEMM_STAGES][BN * GEMM_BK];
     union {
-        alignas(1024) int32_t stage[GEMM_EPI_WARPS][32][20];   // per epilogue warp: 32 rows x 16 columns (+4 pad) transpose buffer
-        alignas(1024) int32_t ostage[GEMM_EPI_WARPS][32 * 16];  // row-per-lane int32 outputs: dense 32 x 16 box per warp, 64-byte swizzle, source of a TMA store
+        alignas(1024) int32_t stage[GEMM_EPI_WARPS][32][20];   // transposed epilogues, per warp: 32 rows x 16 columns (+4 pad) transpose buffer
+        struct {
+            // row-per-lane outputs: dense 32 x 16-word box per warp (64-byte swizzle), the source of a TMA store.  The
+            // int32 epilogues alternate between two boxes so that one store can drain while the next chunk is written;
+            // the GELU epilogue needs one box per tile and keeps its lookup table where the second boxes would be.
+            alignas(1024) int32_t ostage0[GEMM_EPI_WARPS][32 * 16];
+            union {
+                alignas(1024) int32_t ostage1[GEMM_EPI_WARPS][32 * 16];
+                // GELU table for the row-per-lane epilogue: every lane looks up its own row's value, so a single 256-byte
+                // table would serialise on bank conflicts; 16 word-wide copies put lane l's entry in bank l % 16 (+16 * (i & 1))
+                alignas(16) uint32_t lut16[256][16];
+            };
+        };
     };
     union {
         struct {                                            // transposed epilogues: compact tables
@@ -97,14 +109,11 @@ struct GemmSmem {
             alignas(16) int16_t bc_tab[GEMM_MAX_SLOTS][2][BN];  // bias + bias-noise delta per pair slot and sign
         };
         struct {                                            // row-per-lane epilogues: tables widened to int32, read as uniform LDS.128
-            alignas(16) int32_t a32[GEMM_MAX_SLOTS][BN];        // A-noise of this projection per pair slot
-            alignas(16) int32_t bcs32[GEMM_MAX_SLOTS][2][BN];   // (bias + bias-noise delta) << out_shift per pair slot and sign
+            alignas(16) int32_t a32[GEMM_RPL_SLOTS][BN];        // A-noise of this projection per pair slot
+            alignas(16) int32_t bcs32[GEMM_RPL_SLOTS][2][BN];   // (bias + bias-noise delta) << out_shift per pair slot and sign
         } rpl;
     };
     alignas(16) int8_t d_tab[GEMM_MAX_SLOTS][BN];       // B-noise of the next projection (EPI_GELU)
-    // GELU table for the row-per-lane epilogue: every lane looks up its own row's value, so a single 256-byte
-    // table would serialise on bank conflicts; 16 word-wide copies put lane l's entry in bank l % 16 (+16 * (i & 1))
-    alignas(16) uint32_t lut16[256][16];
     alignas(16) int32_t rowpart[4][GEMM_BM];            // row-per-lane epilogues: per-row partial of each column quarter
     alignas(16) int8_t act_lut[256];
     alignas(16) int32_t exp_lut[256];
@@ -211,7 +220,7 @@ __device__ __forceinline__ void tab_store(const GemmParams &p, GemmSmem<BN> &sm,
 template <int BN, int EPI, bool ROPE>
 __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &sm, uint32_t taddr, int r, bool row_ok, int n0,
                                              int cbase, int slot, int sgn, int32_t (*st)[20], int lane, int m0q, int xbs,
-                                             const int4 (&rs_pre)[BN / 4 / 16], const CUtensorMap *tmap_o, int32_t *ost) {
+                                             const int4 (&rs_pre)[BN / 4 / 16], const CUtensorMap *tmap_o, int32_t *ost, int32_t *ost1) {
     constexpr int NCH = BN / 4 / 16;                       // 16-column chunks of this warp's quarter of the tile
     const int rc = row_ok ? r : (p.M - 1);
     const int mem = fast_div(rc, p.fd_seq);
@@ -219,6 +228,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
     const uint32_t a32 = ptx::smem_u32(sm.rpl.a32[slot] + cbase);           // 32-bit shared addresses of this lane's tables
     const uint32_t bcs = ptx::smem_u32(sm.rpl.bcs32[slot][sgn] + cbase);
     const uint32_t ost_s = ptx::smem_u32(ost) + lane * 64;
+    const uint32_t ost1_s = ptx::smem_u32(ost1) + lane * 64;
     const int8_t *dt = sm.d_tab[slot] + cbase;
     const int64_t gofs = (int64_t)rc * p.N + n0 + cbase;
     const int2 *rope = p.rope_t + (rc - mem * p.seq_len);                                // column of this token position
@@ -300,21 +310,28 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                 }
                 ptx::sts_v4(ost_s + ((c ^ ((lane >> 1) & 3)) << 4), make_int4(outw[0], outw[1], outw[2], outw[3]));
             } else {
-                *reinterpret_cast<int4 *>(&st[lane][4 * c]) = make_int4(outw[0], outw[1], outw[2], outw[3]);
+                *reinterpret_cast<int4 *>(&ost[lane * 16 + 4 * c]) = make_int4(outw[0], outw[1], outw[2], outw[3]);
             }
         }
         if (EPI == EPI_PRE32 || EPI == EPI_QKV) {
             // int32 results leave as one TMA store per warp and chunk: each lane writes its row's 64 bytes into a dense
             // 32 x 16 box (16-byte pieces XOR-swizzled with the row, the 64-byte pattern the tensor map expects, which
             // also makes the stores conflict-free); the copy engine does the coalescing and clips rows beyond M
-            if (lane == 0) ptx::tma_store_wait_read<0>();       // the previous chunk's box has been read out
+            // QKV: chunks alternate between the warp's two boxes; before box c & 1 is rewritten only the store issued two
+            // chunks ago (the same box) must have been read out, the previous one may still be draining (-3 % on that
+            // projection).  The residual projections keep one box: with K = 2048 the copy engine and the shared-memory
+            // port are the busy units, and a second store in flight made them 2.5 % slower on the same GPU.
+            constexpr bool TWO_BOXES = (EPI == EPI_QKV);
+            if (lane == 0) { if (TWO_BOXES) ptx::tma_store_wait_read<1>(); else ptx::tma_store_wait_read<0>(); }
             __syncwarp();
+            const bool second = TWO_BOXES && (c & 1);
+            const uint32_t ob_s = second ? ost1_s : ost_s;
 #pragma unroll
-            for (int q4 = 0; q4 < 4; q4++) ptx::sts_v4(ost_s + ((q4 ^ ((lane >> 1) & 3)) << 4), o4[q4]);
+            for (int q4 = 0; q4 < 4; q4++) ptx::sts_v4(ob_s + ((q4 ^ ((lane >> 1) & 3)) << 4), o4[q4]);
             ptx::fence_proxy_async();
             __syncwarp();
             if (lane == 0) {
-                ptx::tma_store_2d(tmap_o, ost, n0 + cbase + 16 * c, m0q);
+                ptx::tma_store_2d(tmap_o, second ? ost1 : ost, n0 + cbase + 16 * c, m0q);
                 ptx::tma_store_commit();
             }
         }
@@ -336,10 +353,10 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
             const int rr = m0q + i * 8 + lrow;
             int8_t *dst = p.out8 + (int64_t)rr * p.N + n0 + cbase + NCH * 4 * pc;
             if (NCH == 4) {
-                const int4 o = *reinterpret_cast<const int4 *>(&st[i * 8 + lrow][4 * pc]);
+                const int4 o = *reinterpret_cast<const int4 *>(&ost[(i * 8 + lrow) * 16 + 4 * pc]);
                 if (rr < p.M) *reinterpret_cast<int4 *>(dst) = o;
             } else {
-                const int2 o = *reinterpret_cast<const int2 *>(&st[i * 8 + lrow][2 * pc]);
+                const int2 o = *reinterpret_cast<const int2 *>(&ost[(i * 8 + lrow) * 16 + 2 * pc]);
                 if (rr < p.M) *reinterpret_cast<int2 *>(dst) = o;
             }
         }
@@ -634,10 +651,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             } else if (RPL) {
                 if (EPI == EPI_QKV && n0 < 2 * p.third)
                     epilogue_rpl<BN, EPI, true>(p, sm, taddr, r, row_ok, n0, cbase, slot, sgn, sm.stage[ew], lane, m0 + quarter * 32, xbs_l, rs_l,
-                                                &tmap_o, sm.ostage[ew]);
+                                                &tmap_o, sm.ostage0[ew], sm.ostage1[ew]);
                 else
                     epilogue_rpl<BN, EPI, false>(p, sm, taddr, r, row_ok, n0, cbase, slot, sgn, sm.stage[ew], lane, m0 + quarter * 32, xbs_l, rs_l,
-                                                 &tmap_o, sm.ostage[ew]);
+                                                 &tmap_o, sm.ostage0[ew], sm.ostage1[ew]);
             } else if (EPI <= EPI_HEAD) {
                 // ---------------- evaluation epilogues ----------------
                 // Accumulators leave TMEM one row per lane; they are transposed through shared memory so
@@ -857,5 +874,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
 template <int BN>
 constexpr size_t gemm_smem_bytes() { return sizeof(GemmSmem<BN>) + 1024; }
+static_assert(gemm_smem_bytes<256>() <= 227 * 1024, "GEMM shared memory exceeds the 227 KB a block may use");
 
 }  // namespace egg

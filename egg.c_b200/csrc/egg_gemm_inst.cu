@@ -122,7 +122,8 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
     if (epi == EPI_HEAD && p.N != 256) { set_error("head GEMM needs vocab_size == 256"); return EGG_E_INVALID; }
     if (epi <= EPI_HEAD) {
         int max_slots = ((GEMM_BM - 1) / p.seq_len) / 2 + 2;
-        if (max_slots > GEMM_MAX_SLOTS) { set_error("seq_len %d too small for the epilogue tables", p.seq_len); return EGG_E_INVALID; }
+        const bool rpl = p.seq_len % 32 == 0 && p.rpl >= 0 && epi != EPI_CLIP8;
+        if (max_slots > (rpl ? GEMM_RPL_SLOTS : GEMM_MAX_SLOTS)) { set_error("seq_len %d too small for the epilogue tables", p.seq_len); return EGG_E_INVALID; }
     }
     p.fd_seq = make_fastdiv(p.seq_len);
     p.fd_tiles_n = make_fastdiv(p.N / bn);
