@@ -121,6 +121,7 @@ struct GemmSmem {
     uint64_t empty[GEMM_STAGES];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
+    uint64_t rbar[GEMM_EPI_WARPS];      // per epilogue warp: arrival of its residual box (EPI_PRE32, row-per-lane, BN = 256)
     uint32_t tmem_base;
     volatile int abort_flag;
     volatile int epi_ok;
@@ -217,7 +218,7 @@ __device__ __forceinline__ void tab_store(const GemmParams &p, GemmSmem<BN> &sm,
 // pair slot and sign are then per-lane scalars and the per-column tables are read at warp-uniform addresses, so the
 // accumulators are consumed straight from the TMEM layout (lane = row, registers = columns) with no transpose, no
 // shuffles and about half the instructions of the transposed form.  TMEM loads are double-buffered.
-template <int BN, int EPI, bool ROPE>
+template <int BN, int EPI, bool ROPE, bool RES_TMA>
 __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &sm, uint32_t taddr, int r, bool row_ok, int n0,
                                              int cbase, int slot, int sgn, int32_t (*st)[20], int lane, int m0q, int xbs,
                                              const int4 (&rs_pre)[BN / 4 / 16], const CUtensorMap *tmap_o, int32_t *ost, int32_t *ost1) {
@@ -254,6 +255,10 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
         if (c + 1 < NCH) ptx::tmem_ld16(taddr + 16 * (c + 1), v[(c + 1) & 1]);
         uint32_t outw[4];
         int4 o4[4];
+        // residual bytes of this chunk: from the warp's box that the copy engine filled (same 64-byte swizzle as the
+        // output boxes), or from the registers loaded with plain loads
+        int4 rs4 = make_int4(0, 0, 0, 0);
+        if (EPI == EPI_PRE32) rs4 = RES_TMA ? ptx::lds_v4(ost1_s + ((c ^ ((lane >> 1) & 3)) << 4)) : rs_pre[c];
 #pragma unroll
         for (int q4 = 0; q4 < 4; q4++) {
             const int col = 16 * c + 4 * q4;
@@ -276,7 +281,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                 outw[q4] = w;
             } else if (EPI == EPI_PRE32) {
                 const int4 b4 = ptx::lds_v4(bcs + 4 * col);
-                const int32_t rs = q4 == 0 ? rs_pre[c].x : (q4 == 1 ? rs_pre[c].y : (q4 == 2 ? rs_pre[c].z : rs_pre[c].w));
+                const int32_t rs = q4 == 0 ? rs4.x : (q4 == 1 ? rs4.y : (q4 == 2 ? rs4.z : rs4.w));
                 // residual bytes sign-extended by one byte permute each (selector msb = replicate the byte's sign)
                 x0 = ptx::sx_byte0(rs) + ((x0 + b4.x) >> p.out_shift);
                 x1 = ptx::sx_byte1(rs) + ((x1 + b4.y) >> p.out_shift);
@@ -436,7 +441,7 @@ __device__ __forceinline__ void epilogue_head_rpl(const GemmParams &p, GemmSmem<
 template <int BN, int EPI, int RPL>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const __grid_constant__ CUtensorMap tmap_o, const GemmParams p) {
+               const __grid_constant__ CUtensorMap tmap_o, const __grid_constant__ CUtensorMap tmap_r, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     GemmSmem<BN> &sm = *reinterpret_cast<GemmSmem<BN> *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -451,6 +456,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (threadIdx.x == 0) {
         for (int s = 0; s < GEMM_STAGES; s++) { ptx::mbar_init(&sm.full[s], 1); ptx::mbar_init(&sm.empty[s], 1); }
         for (int a = 0; a < 2; a++) { ptx::mbar_init(&sm.tmem_full[a], 1); ptx::mbar_init(&sm.tmem_empty[a], GEMM_EPI_WARPS); }
+        for (int w = 0; w < GEMM_EPI_WARPS; w++) ptx::mbar_init(&sm.rbar[w], 1);
         sm.abort_flag = 0;
         sm.epi_ok = 1;
         ptx::fence_barrier_init();
@@ -595,14 +601,22 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // were loaded during the previous tile (pf_*); only a block's first tile loads them here
             int xbs_l = 0;
             int4 rs_l[BN / 4 / 16];
+            // The residual bytes of the residual projections: with BN = 256 every warp's 32 rows x 64 columns arrive as one
+            // box through the copy engine (requested a tile ahead, at the end of the previous tile's epilogue) -- a lane
+            // loading its own row 16 bytes at a time costs 32 half-used sectors per instruction (12 ms per generation).
+            constexpr bool RES_TMA = (EPI == EPI_PRE32) && RPL && BN == 256;
+            if (RES_TMA && tcount == 0 && lane == 0) {
+                ptx::mbar_arrive_expect_tx(&sm.rbar[ew], 32 * 64);
+                ptx::tma_load_2d(sm.ostage1[ew], &tmap_r, &sm.rbar[ew], n0 + cbase, m0 + quarter * 32);
+            }
             if (RPL && active) {
                 const int rc = row_ok ? r : (p.M - 1);
                 if (tcount == 0) {
                     pf_xb = p.xb[(int64_t)rc * p.xb_stride + ((EPI == EPI_QKV) ? fast_div(n0, p.fd_third) : 0)];
-                    if (EPI == EPI_PRE32) pf_rs0 = *reinterpret_cast<const int4 *>(p.resid + (int64_t)rc * p.N + n0 + cbase);
+                    if (EPI == EPI_PRE32 && !RES_TMA) pf_rs0 = *reinterpret_cast<const int4 *>(p.resid + (int64_t)rc * p.N + n0 + cbase);
                 }
                 xbs_l = sgn ? -pf_xb : pf_xb;
-                if (EPI == EPI_PRE32) {
+                if (EPI == EPI_PRE32 && !RES_TMA) {
                     rs_l[0] = pf_rs0;
 #pragma unroll
                     for (int cc = 1; cc < BN / 4 / 16; cc++)      // used one chunk of arithmetic later each
@@ -637,7 +651,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     if (RPL && active) {
                         const int nr = nm0 + row_in_tile, nrc = nr < p.M ? nr : (p.M - 1);
                         pf_xb = p.xb[(int64_t)nrc * p.xb_stride + ((EPI == EPI_QKV) ? fast_div(nn0, p.fd_third) : 0)];
-                        if (EPI == EPI_PRE32) pf_rs0 = *reinterpret_cast<const int4 *>(p.resid + (int64_t)nrc * p.N + nn0 + half * COLS_PER);
+                        if (EPI == EPI_PRE32 && !RES_TMA) pf_rs0 = *reinterpret_cast<const int4 *>(p.resid + (int64_t)nrc * p.N + nn0 + half * COLS_PER);
                     }
                 }
             }
@@ -649,12 +663,26 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             } else if (RPL && EPI == EPI_HEAD) {
                 epilogue_head_rpl<BN>(p, sm, taddr, r, row_ok, cbase, slot, lane, quarter, row_in_tile, xbs_l);
             } else if (RPL) {
+                if (RES_TMA) {
+                    if (lane == 0 && !ptx::mbar_wait(&sm.rbar[ew], tcount & 1)) gemm_fail(p, &sm.abort_flag, DEV_TIMEOUT_FULL);
+                    __syncwarp();
+                }
                 if (EPI == EPI_QKV && n0 < 2 * p.third)
-                    epilogue_rpl<BN, EPI, true>(p, sm, taddr, r, row_ok, n0, cbase, slot, sgn, sm.stage[ew], lane, m0 + quarter * 32, xbs_l, rs_l,
-                                                &tmap_o, sm.ostage0[ew], sm.ostage1[ew]);
+                    epilogue_rpl<BN, EPI, true, false>(p, sm, taddr, r, row_ok, n0, cbase, slot, sgn, sm.stage[ew], lane, m0 + quarter * 32, xbs_l, rs_l,
+                                                       &tmap_o, sm.ostage0[ew], sm.ostage1[ew]);
                 else
-                    epilogue_rpl<BN, EPI, false>(p, sm, taddr, r, row_ok, n0, cbase, slot, sgn, sm.stage[ew], lane, m0 + quarter * 32, xbs_l, rs_l,
-                                                 &tmap_o, sm.ostage0[ew], sm.ostage1[ew]);
+                    epilogue_rpl<BN, EPI, false, RES_TMA>(p, sm, taddr, r, row_ok, n0, cbase, slot, sgn, sm.stage[ew], lane, m0 + quarter * 32, xbs_l,
+                                                          rs_l, &tmap_o, sm.ostage0[ew], sm.ostage1[ew]);
+                if (RES_TMA) {
+                    // every lane has read its residual bytes: the box may be refilled for the block's next tile
+                    __syncwarp();
+                    const int ntile = tile + gridDim.x;
+                    if (lane == 0 && ntile < num_tiles) {
+                        const int ntm = fast_div(ntile, p.fd_tiles_n);
+                        ptx::mbar_arrive_expect_tx(&sm.rbar[ew], 32 * 64);
+                        ptx::tma_load_2d(sm.ostage1[ew], &tmap_r, &sm.rbar[ew], (ntile - ntm * tiles_n) * BN + cbase, ntm * GEMM_BM + quarter * 32);
+                    }
+                }
             } else if (EPI <= EPI_HEAD) {
                 // ---------------- evaluation epilogues ----------------
                 // Accumulators leave TMEM one row per lane; they are transposed through shared memory so

@@ -94,7 +94,12 @@ template <int BN, int EPI, int RPL = 0>
 static int launch_one(cudaStream_t st, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to, const GemmParams &p, int num_sms) {
     int tiles = ((p.M + GEMM_BM - 1) / GEMM_BM) * (p.N / BN);
     int grid = tiles < num_sms ? tiles : num_sms;
-    gemm_i8_kernel<BN, EPI, RPL><<<grid, GEMM_THREADS, gemm_smem_bytes<BN>(), st>>>(ta, tb, to, p);
+    CUtensorMap tr = ta;       // residual bytes as 64-column x 32-row boxes (row-per-lane residual projections with BN = 256 only)
+    if (EPI == EPI_PRE32 && RPL && BN == 256) {
+        int rc = make_tmap_out8(&tr, p.resid, (uint64_t)p.M, (uint64_t)p.N);
+        if (rc) return rc;
+    }
+    gemm_i8_kernel<BN, EPI, RPL><<<grid, GEMM_THREADS, gemm_smem_bytes<BN>(), st>>>(ta, tb, to, tr, p);
     EGG_CUDA(cudaGetLastError());
     return EGG_OK;
 }
