@@ -296,9 +296,10 @@ def main():
     }
     # DRAM bytes (read + write) per row of one launch, from the ncu captures summarised under profiles/ (262 144-row
     # launches of the same kernels; traffic grows in proportion to the rows of a launch)
-    ncu_traffic_per_row = {"attention": (404.054016e6 + 116.210688e6) / 262144, "rowwise": (543.158528e6 + 250.782208e6) / 262144,
-                           "gemm_gelu": (144.439040e6 + 488.345e6) / 262144, "gemm_qkv": (143.108352e6 + 1562.813e6) / 262144,
-                           "gemm_pre32": (675.208704e6 + 496.057e6) / 262144}
+    ncu_traffic_per_row = {"attention": (404.110e6 + 116.544e6) / 262144, "rowwise": (543.130e6 + 249.417e6) / 262144,
+                           "aqn": (1613.772e6 + 384.940e6) / 262144,
+                           "gemm_gelu": (143.689e6 + 484.641e6) / 262144, "gemm_qkv": (142.191e6 + 1560.224e6) / 262144,
+                           "gemm_pre32": (675.062e6 + 494.890e6) / 262144}
     peaks = {}
     pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(pk):
