@@ -98,8 +98,9 @@ struct GemmSmem {
             union {
                 alignas(1024) int32_t ostage1[GEMM_EPI_WARPS][32 * 16];
                 // GELU table for the row-per-lane epilogue: every lane looks up its own row's value, so a single 256-byte
-                // table would serialise on bank conflicts; 16 word-wide copies put lane l's entry in bank l % 16 (+16 * (i & 1))
-                alignas(16) uint32_t lut16[256][16];
+                // table would serialise on bank conflicts; 32 word-wide copies (exactly the space of the second boxes) give
+                // lane l its own bank whatever the indices are
+                alignas(16) uint32_t lut32[256][32];
             };
         };
     };
@@ -225,7 +226,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
     constexpr int NCH = BN / 4 / 16;                       // 16-column chunks of this warp's quarter of the tile
     const int rc = row_ok ? r : (p.M - 1);
     const int mem = fast_div(rc, p.fd_seq);
-    const uint32_t lut_base = ptx::smem_u32(&sm.lut16[0][lane & 15]);
+    const uint32_t lut_base = ptx::smem_u32(&sm.lut32[0][lane]);
     const uint32_t a32 = ptx::smem_u32(sm.rpl.a32[slot] + cbase);           // 32-bit shared addresses of this lane's tables
     const uint32_t bcs = ptx::smem_u32(sm.rpl.bcs32[slot][sgn] + cbase);
     const uint32_t ost_s = ptx::smem_u32(ost) + lane * 64;
@@ -273,9 +274,9 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                 // saturate to [-128, 127] while packing; the table entry of -128 holds the value of -127 (the reference's clip)
                 const uint32_t z = ptx::pack_sat_s8((x0 + b4.x) >> p.out_shift, (x1 + b4.y) >> p.out_shift, (x2 + b4.z) >> p.out_shift,
                                                     (x3 + b4.w) >> p.out_shift);
-                // word (idx, lane & 15) of the replicated table: 32-bit shared address = base + idx * 64
-                const uint32_t u0 = ptx::lds_u32(lut_base + ((z & 0xFFu) << 6)), u1 = ptx::lds_u32(lut_base + ((z >> 2) & 0x3FC0u));
-                const uint32_t u2 = ptx::lds_u32(lut_base + ((z >> 10) & 0x3FC0u)), u3 = ptx::lds_u32(lut_base + ((z >> 18) & 0x3FC0u));
+                // word (idx, lane) of the replicated table: 32-bit shared address = base + idx * 128
+                const uint32_t u0 = ptx::lds_u32(lut_base + ((z & 0xFFu) << 7)), u1 = ptx::lds_u32(lut_base + ((z >> 1) & 0x7F80u));
+                const uint32_t u2 = ptx::lds_u32(lut_base + ((z >> 9) & 0x7F80u)), u3 = ptx::lds_u32(lut_base + ((z >> 17) & 0x7F80u));
                 const uint32_t w = __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
                 racc = __dp4a((int)w, *reinterpret_cast<const int32_t *>(dt + col), racc);
                 outw[q4] = w;
@@ -470,9 +471,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (EPI == EPI_GELU && p.act_lut && e < 256) sm.act_lut[e] = p.act_lut[e == 0x80 ? 0x81 : e];   // saturating pack yields -128 where the reference clips to -127
         if (EPI == EPI_HEAD && p.exp_lut && e < 256) sm.exp_lut[e] = p.exp_lut[e];
         if (EPI == EPI_GELU && RPL && p.act_lut) {
-            for (int i = e; i < 256 * 16; i += GEMM_EPI_THREADS) {
-                const int idx = i >> 4;
-                sm.lut16[idx][i & 15] = (uint32_t)(uint8_t)p.act_lut[idx == 0x80 ? 0x81 : idx];
+            for (int i = e; i < 256 * 32; i += GEMM_EPI_THREADS) {
+                const int idx = i >> 5;
+                sm.lut32[idx][i & 31] = (uint32_t)(uint8_t)p.act_lut[idx == 0x80 ? 0x81 : idx];
             }
         }
     }
