@@ -22,7 +22,7 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 
 def kat():
-    ref = "/root/reference/d-eggs/include"
+    ref = os.path.join(os.environ.get("EGG_REFERENCE", "/root/reference"), "d-eggs", "include")
     src = os.path.join(ROOT, "oracle", "ref_kat.cpp")
     for mask in (15, 3):
         exe = "/tmp/ref_kat_mask%d" % mask
@@ -116,10 +116,10 @@ def generate(outdir):
 
 if __name__ == "__main__":
     if sys.argv[1] == "generate":
-        generate(sys.argv[2] if len(sys.argv) > 2 else os.path.join(ROOT, "gpurun_out", "golden"))
+        generate(sys.argv[2] if len(sys.argv) > 2 else os.path.join(ROOT, "golden_out"))
     elif sys.argv[1] == "kat":
         kat()
     elif sys.argv[1] == "deggs":
-        deggs(sys.argv[2] if len(sys.argv) > 2 else os.path.join(ROOT, "gpurun_out", "golden"))
+        deggs(sys.argv[2] if len(sys.argv) > 2 else os.path.join(ROOT, "golden_out"))
     else:
-        mgpu(sys.argv[2] if len(sys.argv) > 2 else os.path.join(ROOT, "gpurun_out", "golden"))
+        mgpu(sys.argv[2] if len(sys.argv) > 2 else os.path.join(ROOT, "golden_out"))
