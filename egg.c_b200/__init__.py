@@ -23,7 +23,7 @@ EXPORTS = [
     "egg_apply_update", "egg_generation_host", "egg_perturbed_projection", "egg_update_reconstruct",
     "egg_update_reconstruct_noalloc", "egg_scales_bytes", "egg_upload_scales", "egg_download_scales", "egg_set_overlay_steps",
     "egg_timer_start", "egg_timer_stop", "egg_profile_enable", "egg_profile_read", "egg_profile_name", "egg_launch_count",
-    "egg_wave_members", "egg_measure_int8_peak", "egg_generate", "egg_save_checkpoint", "egg_load_checkpoint", "egg_wire_fixed_bytes", "egg_wire_encode", "egg_wire_decode_header", "egg_wire_decode_body",
+    "egg_wave_members", "egg_measure_int8_peak", "egg_selftest_index_math", "egg_generate", "egg_save_checkpoint", "egg_load_checkpoint", "egg_wire_fixed_bytes", "egg_wire_encode", "egg_wire_decode_header", "egg_wire_decode_body",
     "egg_ternary_packed_size", "egg_ternary_pack", "egg_ternary_unpack", "egg_deggs_chunk_fitness", "egg_next_seed",
     "egg_gru_config_defaults", "egg_gru_model_bytes", "egg_gru_state_bytes", "egg_gru_create", "egg_gru_destroy",
     "egg_gru_upload_model", "egg_gru_download_model", "egg_gru_upload_states", "egg_gru_download_states", "egg_gru_set_dataset",
@@ -200,6 +200,14 @@ def gru_state_bytes(gcfg):
 
 def opt_state_bytes(cfg):
     return lib().egg_opt_state_bytes(C.byref(cfg))
+
+
+def selftest_index_math():
+    """Host-only check of the multiply-shift division shared by host and kernels (raises on a mismatch)."""
+    L = lib()
+    L.egg_selftest_index_math.argtypes = []
+    L.egg_selftest_index_math.restype = C.c_int
+    _check(L.egg_selftest_index_math())
 
 
 def scales_bytes(cfg):

@@ -1171,6 +1171,31 @@ extern "C" const char *egg_profile_name(int cls) {
     return (cls >= 0 && cls < EGG_PROF_N) ? names[cls] : "";
 }
 
+extern "C" int egg_selftest_index_math(void) {
+    uint64_t rng = 0x9E3779B97F4A7C15ull;
+    auto next = [&]() { rng ^= rng << 13; rng ^= rng >> 7; rng ^= rng << 17; return (int)(rng & 0x7FFFFFFFull); };
+    auto check = [&](int d) -> bool {
+        const FastDiv f = make_fastdiv(d);
+        const int top = 0x7FFFFFFF;
+        const long long fixed[] = {0, 1, d - 1, d, (long long)d + 1, 2ll * d - 1, top, top - 1, top - d, (long long)(top / d) * d, (long long)(top / d) * d - 1};
+        for (long long nn : fixed) {
+            if (nn < 0 || nn > top) continue;
+            const int n = (int)nn;
+            if (fast_div(n, f) != n / d || fast_mod(n, f) != n % d) { set_error("fast_div(%d, %d) = %d, expected %d", n, d, fast_div(n, f), n / d); return false; }
+        }
+        for (int i = 0; i < 64; i++) {
+            const int n = next();
+            if (fast_div(n, f) != n / d || fast_mod(n, f) != n % d) { set_error("fast_div(%d, %d) = %d, expected %d", n, d, fast_div(n, f), n / d); return false; }
+        }
+        return true;
+    };
+    for (int d = 1; d <= 4096; d++) if (!check(d)) return EGG_E_STATE;
+    for (int k = 12; k <= 30; k++) {
+        if (!check(1 << k) || !check((1 << k) - 1) || !check((1 << k) + 1)) return EGG_E_STATE;
+    }
+    return EGG_OK;
+}
+
 extern "C" int egg_measure_int8_peak(egg_ctx *c, int m, int n, int k, int iters, double *tops) {
     if (!c || !tops || m <= 0 || n <= 0 || k <= 0 || iters <= 0 || m % 256 || n % 256 || k % 128) { set_error("m, n must be multiples of 256, k of 128, iters positive"); return EGG_E_INVALID; }
     EGG_CUDA(cudaSetDevice(c->device));

@@ -146,8 +146,8 @@ inline FastDiv make_fastdiv(int d) {
     f.d = d;
     return f;
 }
-__device__ __forceinline__ int fast_div(int n, const FastDiv &f) { return (int)(((uint64_t)(uint32_t)n * f.mul) >> f.shift); }
-__device__ __forceinline__ int fast_mod(int n, const FastDiv &f) { return n - fast_div(n, f) * f.d; }
+__host__ __device__ __forceinline__ int fast_div(int n, const FastDiv &f) { return (int)(((uint64_t)(uint32_t)n * f.mul) >> f.shift); }
+__host__ __device__ __forceinline__ int fast_mod(int n, const FastDiv &f) { return n - fast_div(n, f) * f.d; }
 
 // One trainable parameter of the update sequence (mgpu.cu:1603-1643).
 struct ParamDesc {

@@ -391,6 +391,15 @@ int egg_wave_members(egg_ctx *ctx);
  */
 int egg_measure_int8_peak(egg_ctx *ctx, int m, int n, int k, int iters, double *tops);
 
+/*
+ * Host-side self test of the index arithmetic the kernels share with the host (no GPU needed): the
+ * multiply-shift division that replaces `/ SEQ_LEN`, `/ tiles`, `% HEAD_DIM` in the per-tile code is
+ * compared with C division for every divisor up to 4096 (and powers of two and their neighbours up to
+ * 2^30) on boundary and pseudo-random dividends below 2^31.  Returns EGG_OK or EGG_E_STATE with the
+ * first mismatch in egg_last_error().  No counterpart in the reference (it divides at run time).
+ */
+int egg_selftest_index_math(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -149,3 +149,9 @@ def test_newton_schulz_orthogonalises():
         # 5 cubic iterations from Frobenius normalisation move singular values toward 1 (not all the way)
         s = np.linalg.svd(y, compute_uv=False)
         assert s.max() < 1.3 and np.isfinite(g).all()
+
+
+def test_index_math_selftest_runs_on_the_host():
+    """FastDiv (the multiply-shift division of the per-tile index arithmetic) against C division, through the C ABI."""
+    pkg = load_pkg()
+    pkg.selftest_index_math()
