@@ -82,6 +82,7 @@ struct GemmParams {
     int rpl;                     // -1 forces the transposed evaluation epilogue (tests); otherwise chosen from seq_len
     // divisors of the per-tile index arithmetic (filled by launch_gemm)
     FastDiv fd_seq, fd_tiles_n, fd_third, fd_head;
+    int lut_stride;              // bytes between entries of the replicated GELU table (filled by launch_gemm)
 };
 
 template <int BN>
@@ -227,6 +228,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
     const int rc = row_ok ? r : (p.M - 1);
     const int mem = fast_div(rc, p.fd_seq);
     const uint32_t lut_base = ptx::smem_u32(&sm.lut32[0][lane]);
+    const uint32_t lut_stride = (uint32_t)p.lut_stride;       // 128 bytes per table entry, read from the parameters
     const uint32_t a32 = ptx::smem_u32(sm.rpl.a32[slot] + cbase);           // 32-bit shared addresses of this lane's tables
     const uint32_t bcs = ptx::smem_u32(sm.rpl.bcs32[slot][sgn] + cbase);
     const uint32_t ost_s = ptx::smem_u32(ost) + lane * 64;
@@ -275,8 +277,10 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                 const uint32_t z = ptx::pack_sat_s8((x0 + b4.x) >> p.out_shift, (x1 + b4.y) >> p.out_shift, (x2 + b4.z) >> p.out_shift,
                                                     (x3 + b4.w) >> p.out_shift);
                 // word (idx, lane) of the replicated table: 32-bit shared address = base + idx * 128
-                const uint32_t u0 = ptx::lds_u32(lut_base + ((z & 0xFFu) << 7)), u1 = ptx::lds_u32(lut_base + ((z >> 1) & 0x7F80u));
-                const uint32_t u2 = ptx::lds_u32(lut_base + ((z >> 9) & 0x7F80u)), u3 = ptx::lds_u32(lut_base + ((z >> 17) & 0x7F80u));
+                // one integer-pipe instruction to isolate each byte, then index * 128 + base as a multiply-add with a
+                // run-time multiplier (kept a multiply: that pipe has room, the integer pipe is the busy one)
+                const uint32_t u0 = ptx::lds_u32((z & 0xFFu) * lut_stride + lut_base), u1 = ptx::lds_u32(__byte_perm(z, 0, 0x4441) * lut_stride + lut_base);
+                const uint32_t u2 = ptx::lds_u32(__byte_perm(z, 0, 0x4442) * lut_stride + lut_base), u3 = ptx::lds_u32((z >> 24) * lut_stride + lut_base);
                 const uint32_t w = __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
                 racc = __dp4a((int)w, *reinterpret_cast<const int32_t *>(dt + col), racc);
                 outw[q4] = w;

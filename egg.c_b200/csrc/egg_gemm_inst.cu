@@ -134,6 +134,7 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
     p.fd_tiles_n = make_fastdiv(p.N / bn);
     p.fd_third = make_fastdiv(p.third);
     p.fd_head = make_fastdiv(p.head_dim);
+    p.lut_stride = 32 * 4;
     CUtensorMap ta, tb;
     int rc;
     if ((rc = make_tmap(&ta, A, (uint64_t)p.M, (uint64_t)p.K, GEMM_BM))) return rc;
