@@ -285,7 +285,7 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
         const int d = (j << 7) + (lane << 2);
-        uint32_t w = pack4(x[j][0], x[j][1], x[j][2], x[j][3]);
+        uint32_t w = ptx::pack_sat_s8(x[j][0], x[j][1], x[j][2], x[j][3]);      // |x| <= 127: the saturating pack is exact, two instructions
         *reinterpret_cast<uint32_t *>(p.x_out + (int64_t)r * H + d) = w;
         tot = __dp4a((int)__vabsss4(w), 0x01010101, tot);    // sum of |x|, four at a time
     }
