@@ -194,12 +194,12 @@ __device__ __forceinline__ int aln_quant(int val, float scale24) {
     return (xi + (1 << 23) + (xi >> 31)) >> 24;
 }
 
-// trunc(a / mn) as C integer division does, for |a| < 2^15 and 1 <= mn <= 127:
-// a*(1/mn) is off by < 0.003, exact quotients are pushed off the integer by a bias of
-// 0.004 (the nearest non-integer quotient is 1/127 away), then truncated by the conversion.
-__device__ __forceinline__ int div_small(int a, float rinv) {
-    float af = i2f_small(a);
-    return __float2int_rz(fmaf(af, rinv, copysignf(0.004f, af)));
+// trunc(a / mn) as C integer division does, for |a| < 2^15 and 1 <= mn <= 127, with rinv_up = (1/mn) * (1 + 2^-17):
+// the factor pushes every quotient away from zero by |q| * 7.6e-6 -- more than the float error of the product
+// (three roundings, < |q| * 1.8e-7), so an exact quotient k lands beyond k and truncates to k, and less than the
+// distance 1/mn from a non-integer quotient to the next integer (|q| * 7.8e-6 < 1/mn because |q| * mn = |a| < 2^15).
+__device__ __forceinline__ int div_small(int a, float rinv_up) {
+    return __float2int_rz(i2f_small(a) * rinv_up);
 }
 
 // [sat8(a), sat8(b), sat8(c), sat8(d)] as bytes 0..3 with the reference's clip to [-127, 127]
@@ -293,7 +293,7 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
     tot = warp_sum(tot);
     int mn = tot / H;
     if (!mn) mn = 1;
-    const float rinv = 1.0f / (float)mn;
+    const float rinv = (1.0f / (float)mn) * (1.0f + 0x1p-17f);
     int dot0 = 0, dot1 = 0, dot2 = 0;
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
