@@ -172,6 +172,12 @@ extern "C" int egg_config_validate(const egg_config *c, const char **why) {
     else if (c->rope_scale_bit < 1 || c->rope_scale_bit > 30) w = "rope_scale_bit out of range";
     else if (c->fixed_point < 0 || c->fixed_point > 7) w = "fixed_point out of range";
     else if (c->sigma_shift_vector < 0 || c->sigma_shift_vector > 16 || c->sigma_shift < 0 || c->sigma_shift > 16) w = "sigma shifts out of range";
+    if (!w) {
+        // the mean-abs norm divides x * (gain + noise delta) exactly only below 2^16 in magnitude
+        const int nmax = (c->device_gaussian ? 3 : 1) * c->device_mask;
+        const int gain_max = 127 + ((nmax * nmax) >> c->sigma_shift_vector);
+        if (127 * gain_max >= (1 << 16)) w = "sigma_shift_vector too small for this noise amplitude (perturbed norm gains exceed the exact range)";
+    }
     if (why) *why = w ? w : "";
     if (w) { set_error("invalid configuration: %s", w); return EGG_E_INVALID; }
     return EGG_OK;

@@ -194,10 +194,11 @@ __device__ __forceinline__ int aln_quant(int val, float scale24) {
     return (xi + (1 << 23) + (xi >> 31)) >> 24;
 }
 
-// trunc(a / mn) as C integer division does, for |a| < 2^15 and 1 <= mn <= 127, with rinv_up = (1/mn) * (1 + 2^-17):
+// trunc(a / mn) as C integer division does, for |a| < 2^16 and 1 <= mn <= 127, with rinv_up = (1/mn) * (1 + 2^-17):
 // the factor pushes every quotient away from zero by |q| * 7.6e-6 -- more than the float error of the product
 // (three roundings, < |q| * 1.8e-7), so an exact quotient k lands beyond k and truncates to k, and less than the
-// distance 1/mn from a non-integer quotient to the next integer (|q| * 7.8e-6 < 1/mn because |q| * mn = |a| < 2^15).
+// distance 1/mn from a non-integer quotient to the next integer (|q| * 7.8e-6 < 1/mn because |q| * mn = |a| < 2^16).
+// The configuration check bounds |x * gain| by 2^16 from the noise amplitude.
 __device__ __forceinline__ int div_small(int a, float rinv_up) {
     return __float2int_rz(i2f_small(a) * rinv_up);
 }
