@@ -126,6 +126,7 @@ def cpu_reference_run(steps, warmup, pairs=None, tokens=None):
             if i >= warmup:
                 vals.append(info["member_tokens_per_s"])
     return {"value": float(np.mean(vals)), "unit": UNIT, "cores": int(info["threads"]), "kind": "reference",
+            "ms_per_step": 1e3 * 2 * pairs * tokens / float(np.mean(vals)),
             "sample": "full_trained_egg.c forward_pass (GRU+MLP int8 model at its compiled-in H=512 L=4), %d pairs x %d tokens "
                       "= %d member-tokens per step, one OpenMP task per pair" % (pairs, tokens, 2 * pairs * tokens)}
 
@@ -138,7 +139,7 @@ def run_reference_arm(args, rank):
         print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/ref_cpu_gru is not built"}))
         return
     line = {"metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8/int32",
+            "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8/int32",
             "data": "synthetic", "impl": "reference", "config": {"workload": WORKLOAD, "note": "reference CPU path: " + res["sample"]},
             "cpu_baseline": res, "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
