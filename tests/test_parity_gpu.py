@@ -67,11 +67,13 @@ def test_eval_waves_and_chunks_are_consistent():
     ctx.close()
 
 
-def test_eval_partial_tiles_with_256_wide_projections():
+@pytest.mark.parametrize("hidden", [256, 384])
+def test_eval_partial_tiles_with_256_wide_projections(hidden):
     """Waves whose row count is not a multiple of the 128-row tile, on a model wide enough for the 256-column tiles
-    (residual boxes fetched by the copy engine, output boxes clipped at the last row, row-per-lane head)."""
+    (residual boxes fetched by the copy engine, output boxes clipped at the last row, row-per-lane head); hidden 384
+    takes the 128-column tiles for the residual and QKV projections."""
     O = load_oracle()
-    kw = dict(hidden_dim=256, n_layers=2, seq_len=32, population_size=44, device_mask=3)
+    kw = dict(hidden_dim=hidden, n_layers=2, seq_len=32, population_size=44, device_mask=3)
     cfg, ocfg, model, data = make_case(kw, data_len=30000, model_kind="random")
     want = O.eval_losses(ocfg, model, data, 64, SEED + 9, 0, 44)
     ctx = _ctx(cfg, wave=10)       # 320 rows per wave = 2.5 tiles; the last wave has 4 members = 1 tile
