@@ -467,18 +467,24 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// the same product started from a zero accumulator: the outputs are written, not read, so no register has to be
+// cleared first
+__device__ __forceinline__ void mma_s8_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
 constexpr int ATT_KP = 80;   // K row pitch in shared memory (bytes): conflict-free fragment loads
 
 // scores of one 16-query x 32-key block: c[nt][0..3] for the four 8-key n-tiles
 __device__ __forceinline__ void att_scores(int (&c)[4][4], const uint32_t (&qa)[2][4], const int8_t *Ks, int kb, int g, int q) {
 #pragma unroll
     for (int nt = 0; nt < 4; nt++) {
-        c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0;
         const int8_t *kp = Ks + (kb * 32 + nt * 8 + g) * ATT_KP + 4 * q;
-#pragma unroll
-        for (int ks = 0; ks < 2; ks++)
-            mma_s8(c[nt], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], *reinterpret_cast<const uint32_t *>(kp + 32 * ks),
-                   *reinterpret_cast<const uint32_t *>(kp + 32 * ks + 16));
+        mma_s8_first(c[nt], qa[0][0], qa[0][1], qa[0][2], qa[0][3], *reinterpret_cast<const uint32_t *>(kp), *reinterpret_cast<const uint32_t *>(kp + 16));
+        mma_s8(c[nt], qa[1][0], qa[1][1], qa[1][2], qa[1][3], *reinterpret_cast<const uint32_t *>(kp + 32), *reinterpret_cast<const uint32_t *>(kp + 48));
     }
 }
 
