@@ -1,14 +1,21 @@
 #!/usr/bin/env python
 """Benchmark of the EGGROLL population-evaluation path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c4|c5slice]
 
-One "step" is one ES generation of the Int8NativeFormer benchmark configuration
-(4 layers, H=512, 8 heads, MLP 4H, seq 256, vocab 256, 40 960 antithetic members per
-GPU, DEVICE_MASK=3, ES-AdamW): population evaluation, pair fitness, fitness exchange
-(NCCL all-gather when N > 1) and update reconstruction + optimiser step.  The metric
-is the reference's own "tok/s": POPULATION_SIZE * SEQ_LEN / generation seconds
-(member-token evaluations per second), aggregated over all GPUs.
+Default workload `c2`: one "step" is one ES generation of the Int8NativeFormer benchmark configuration
+(4 layers, H=512, 8 heads, MLP 4H, seq 256, vocab 256, 40 960 antithetic members per GPU, DEVICE_MASK=3,
+ES-AdamW): population evaluation, pair fitness, fitness exchange (NCCL all-gather when N > 1) and update
+reconstruction + optimiser step.  The metric is the reference's own "tok/s": POPULATION_SIZE * SEQ_LEN /
+generation seconds (member-token evaluations per second), aggregated over all GPUs.
+
+Other workloads (single GPU, same JSON contract, named in config.workload):
+  c3       isolated perturbed projection, W 4096 x 4096, 4096 members x 64 tokens (rows are member-tokens)
+  c4       isolated update reconstruction of a 4096 x 4096 weight from 32 768 pairs of int8 fitness, followed by an
+           ES-AdamW step and a Muon step (value: pair-weights reconstructed per second is not the headline metric,
+           so the line reports member-token-equivalents = pairs*2 per step second and the tensor roofline)
+  c5slice  d-eggs-scale shapes (12 layers, H 1024, seq 512, ternary weights, Muon): a slice of the 262 144-member
+           population is evaluated, the update runs over all 131 072 pairs
 
 Prints ONE JSON line on rank 0.  `--impl reference` times the reference's CPU trainer
 (full_trained_egg.c, built into oracle/_ref/ref_cpu_gru) on the host cores instead.
@@ -17,11 +24,11 @@ import argparse
 import importlib.util
 import json
 import os
+import struct
 import subprocess
 import sys
 import tempfile
-import threading
-import time
+import zlib
 
 import numpy as np
 
@@ -31,9 +38,11 @@ UNIT = "member-tokens/s"
 WORKLOAD = ("Int8NativeFormer one ES-AdamW generation: L=4 H=512 heads=8 MLP=4H seq=256 vocab=256, "
             "40960 antithetic members per GPU, rank-1 noise mask 3")
 C2 = dict(hidden_dim=512, head_dim=64, n_layers=4, seq_len=256, vocab_size=256, device_mask=3)
+C5 = dict(hidden_dim=1024, head_dim=64, n_layers=12, seq_len=512, vocab_size=256, device_mask=15)
 POP_PER_GPU = 40960
 DATA_LEN = 64 << 20
 LR = 0.05
+SEED0 = 0x00C0FFEE
 
 
 def _load(name, path, search=None):
@@ -49,6 +58,36 @@ def _load(name, path, search=None):
 def load_pkg():
     d = os.path.join(ROOT, "egg.c_b200")
     return _load("egg_c_b200", os.path.join(d, "__init__.py"), [d])
+
+
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def load_peaks():
+    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peaks = json.load(open(pk)) if os.path.exists(pk) else {}
+    src = "measured" if peaks else "fallback"
+    # no int8 figure is measured on this pool: int8 dense peak taken as 2x the measured sustained bf16 GEMM throughput
+    return {"hbm": peaks.get("hbm_gbs", 6650.0), "tensor": 2.0 * peaks.get("bf16_tflops_sustained", 1400.0), "src": src,
+            "tensor_source": "2 x bf16_tflops_sustained of %s MEASURED_PEAKS (no int8 entry); int8 ops" % src,
+            "hbm_source": "hbm_gbs of %s MEASURED_PEAKS" % src}
+
+
+def load_traffic():
+    """DRAM bytes per launch from the committed ncu captures (profiles/ncu_dram_traffic.json), per row."""
+    p = os.path.join(ROOT, "profiles", "ncu_dram_traffic.json")
+    if not os.path.exists(p):
+        return {}, None
+    j = json.load(open(p))
+    rows = float(j["rows_per_captured_launch"])
+    per_row = {k: (v["read"] + v["write"]) / rows for k, v in j["bytes_per_launch"].items()}
+    src = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of a %d-row launch (profiles/ncu_dram_traffic.json, captured at "
+           "commit %s), scaled by rows per launch; not re-measured by this run" % (int(rows), j["taken_at_commit"]))
+    return per_row, src
 
 
 # ----------------------------------------------------------------------------- clocks
@@ -100,50 +139,82 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- reference arm (CPU)
-def cpu_reference_run(steps, warmup, pairs=None, tokens=None):
-    """Times the reference's own CPU trainer functions (full_trained_egg.c: forward_pass x2 per pair,
-    compiled unmodified into oracle/_ref/ref_cpu_gru) on all host cores, on a bounded sample."""
+def cpu_reference_run(steps, warmup, tokens=None):
+    """Times the reference's own CPU trainer (full_trained_egg.c compiled unmodified into oracle/_ref/ref_cpu_gru) on
+    all host cores: one generation of its whole population (64 pairs -> forward_pass x2 per pair, then its 25
+    update_matrix calls) on a bounded number of tokens per member (the reference runs 4096)."""
     exe = os.path.join(ROOT, "oracle", "_ref", "ref_cpu_gru")
     if not os.path.exists(exe):
         return None
-    pkg = load_pkg()
+    load_pkg()
     from egg_c_b200 import synth
     sizes = json.loads(subprocess.run([exe, "--sizes"], check=True, capture_output=True, text=True).stdout)
-    cores = os.cpu_count() or 1
-    pairs = pairs or min(sizes["population_size"] // 2, max(1, cores))
-    tokens = tokens or 1024
+    cores = host_cores()
+    pairs = sizes["population_size"] // 2             # the whole population: only then does the driver run the update
+    tokens = tokens or max(64, min(1024, 16 * cores))  # about 10-20 s per step at ~5 ms per member-token and core
     model = synth.uniform_int8(0, sizes["model_bytes"])
     data = synth.zipf_bytes(1, 1 << 20)
-    vals = []
+    env = dict(os.environ, OMP_NUM_THREADS=str(cores))    # torch.distributed.run exports OMP_NUM_THREADS=1
+    vals, info = [], None
     with tempfile.TemporaryDirectory() as td:
         fin, fout = os.path.join(td, "in.bin"), os.path.join(td, "out.bin")
         with open(fin, "wb") as f:
-            f.write(np.uint32(0x00C0FFEE).tobytes()); f.write(np.int64(len(data)).tobytes())
+            f.write(np.uint32(SEED0).tobytes()); f.write(np.int64(len(data)).tobytes())
             f.write(model.tobytes()); f.write(data.tobytes())
         for i in range(warmup + steps):
-            r = subprocess.run([exe, fin, fout, str(pairs), str(tokens)], check=True, capture_output=True, text=True)
+            r = subprocess.run([exe, fin, fout, str(pairs), str(tokens)], check=True, capture_output=True, text=True, env=env)
             info = json.loads(r.stdout.strip().splitlines()[-1])
             if i >= warmup:
                 vals.append(info["member_tokens_per_s"])
     return {"value": float(np.mean(vals)), "unit": UNIT, "cores": int(info["threads"]), "kind": "reference",
             "ms_per_step": 1e3 * 2 * pairs * tokens / float(np.mean(vals)),
-            "sample": "full_trained_egg.c forward_pass (GRU+MLP int8 model at its compiled-in H=512 L=4), %d pairs x %d tokens "
-                      "= %d member-tokens per step, one OpenMP task per pair" % (pairs, tokens, 2 * pairs * tokens)}
+            "eval_s": info["eval_s"], "update_s": info["update_s"],
+            "sample": "full_trained_egg.c (GRU+MLP int8 model at its compiled-in H=512 L=4, population 128): one generation = "
+                      "forward_pass of all 64 pairs x 2 members on %d tokens (the reference's SEQ_LEN is 4096) + its 25 update_matrix "
+                      "calls = %d member-tokens per step, one OpenMP task per pair, %d threads" % (tokens, 2 * pairs * tokens, int(info["threads"]))}
 
 
 def run_reference_arm(args, rank):
     if rank != 0:
         return
-    res = cpu_reference_run(args.steps, max(args.warmup, 0))
+    res = cpu_reference_run(min(args.steps, 3), min(max(args.warmup, 0), 1))
     if res is None:
         print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/ref_cpu_gru is not built"}))
         return
-    line = {"metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+    line = {"metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": min(args.steps, 3),
+            "warmup": min(max(args.warmup, 0), 1),
             "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8/int32",
             "data": "synthetic", "impl": "reference", "config": {"workload": WORKLOAD, "note": "reference CPU path: " + res["sample"]},
             "cpu_baseline": res, "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line))
+
+
+def reference_gpu_kernels_run(members=1024):
+    """Member-tokens/s of the reference's own train_sequence_kernel (mgpu.cu:847, built unmodified for sm_100a into
+    oracle/_ref/ref_mgpu_c2) on `members` members of the same configuration on the same GPU: CUDA events inside the
+    harness around its launches."""
+    exe = os.path.join(ROOT, "oracle", "_ref", "ref_mgpu_c2")
+    if not os.path.exists(exe):
+        return {"value": None, "unit": UNIT, "sample": "oracle/_ref/ref_mgpu_c2 is not built"}
+    pkg = load_pkg()
+    from egg_c_b200 import synth
+    cfg = pkg.default_config(population_size=40960, **C2)
+    model = synth.random_model(cfg, 0, "uniform")
+    data = synth.zipf_bytes(1, 1 << 22)
+    with tempfile.TemporaryDirectory() as td:
+        fin, fout = os.path.join(td, "in.bin"), os.path.join(td, "out.bin")
+        with open(fin, "wb") as f:
+            f.write(struct.pack("<IIqqiifiii", 0x46524745, SEED0, 256, len(data), 0, members, 0.0, 0, 0, 0))
+            f.write(struct.pack("<6i", C2["hidden_dim"], C2["n_layers"], C2["seq_len"], 40960, C2["device_mask"], 0))
+            f.write(model.tobytes()); f.write(data.tobytes())
+        r = subprocess.run([exe, fin, fout], capture_output=True, text=True, timeout=600)
+        if r.returncode != 0:
+            return {"value": None, "unit": UNIT, "sample": "harness failed: " + (r.stderr or r.stdout)[-200:]}
+        info = json.loads(r.stdout.strip().splitlines()[-1])
+    return {"value": members * C2["seq_len"] / (info["eval_ms"] / 1e3), "unit": UNIT, "eval_ms": info["eval_ms"],
+            "sample": "train_sequence_kernel of the reference (one block per member, dp4a) on %d members x %d tokens, "
+                      "same model configuration, same GPU; evaluation only" % (members, C2["seq_len"])}
 
 
 def gru_model_run(pkg, synth, device, tokens=512, reps=2):
@@ -155,17 +226,151 @@ def gru_model_run(pkg, synth, device, tokens=512, reps=2):
     ctx = pkg.GruContext(gcfg, device)
     ctx.upload_model(synth.uniform_int8(0, pkg.gru_model_bytes(gcfg)))
     ctx.set_dataset(synth.zipf_bytes(1, 1 << 20))
-    ctx.generation(0x00C0FFEE, 0, 32, True)                    # warm-up: graph capture
+    ctx.generation(SEED0, 0, 32, True)                    # warm-up: graph capture
     n0 = ctx.launch_count()
     t0 = time.perf_counter()
     for r in range(reps):
-        ctx.generation(0x00C0FFEE + 1 + r, (r + 1) * gcfg.seq_len, tokens, True)
+        ctx.generation(SEED0 + 1 + r, (r + 1) * gcfg.seq_len, tokens, True)
     dt = (time.perf_counter() - t0) / reps
     launches = (ctx.launch_count() - n0) // reps
     ctx.close()
     return {"value": gcfg.population_size * tokens / dt, "unit": UNIT, "ms_per_generation_sample": dt * 1e3,
             "sample": "%d members x %d tokens per generation (the reference runs 4096 tokens), update included" % (gcfg.population_size, tokens),
             "gpu_launches": int(launches), "timing": "wall clock around the blocking call"}
+
+
+def projection_ops_per_member_token(H, L, V):
+    return 2.0 * (8 * H * H + 12 * H * H * L + H * V)
+
+
+def c5_sample_run(pkg, synth, device, members, peaks, mma_loop_tops, steps=2):
+    """d-eggs-scale shapes on one GPU: `members` members of the 262 144-member population evaluated (the evaluation
+    is linear in the members), then the whole Muon update over all 131 072 pairs from a seeded ternary fitness vector.
+    Gives the two times that decide how a fixed population of 262 144 scales over 8 GPUs: evaluation shards, the
+    update is replicated."""
+    pop = 262144
+    cfg = pkg.default_config(population_size=pop, use_muon=1, **C5)
+    ctx = pkg.Context(cfg, device, members)
+    ctx.upload_model(synth.random_model(cfg, 0, "ternary"))
+    ctx.set_dataset(synth.zipf_bytes(1, 1 << 24))
+    rng = np.random.default_rng(5)
+    ctx.write_fitness(rng.integers(-1, 2, pop // 2).astype(np.int32), 0)
+    S = cfg.seq_len
+    ctx.eval_chunk(42, 0, 0, members)
+    ctx.apply_update(42, 0.5)
+    ctx.sync()
+    ctx.profile_enable(True)
+    ctx.profile_read()
+    ev, up = [], []
+    for i in range(steps):
+        ctx.timer_start(); ctx.eval_chunk(43 + i, (1 + i) * S, 0, members); ev.append(ctx.timer_stop())
+        ctx.timer_start(); ctx.apply_update(43 + i, 0.5); up.append(ctx.timer_stop())
+    prof = ctx.profile_read()
+    ctx.profile_enable(False)
+    ctx.close()
+    eval_ms, upd_ms = float(np.mean(ev)), float(np.mean(up))
+    gemm_ms = sum(prof[k][0] for k in prof if k.startswith("gemm_")) / steps
+    ops = projection_ops_per_member_token(cfg.hidden_dim, cfg.n_layers, cfg.vocab_size) * members * S
+    tops = ops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else None
+    per_gpu_members = pop // 8
+    t_eval_8 = eval_ms * per_gpu_members / members
+    t_eval_1 = eval_ms * pop / members
+    return {"workload": "12 layers, H 1024, 16 heads, seq 512, ternary weight values, Muon; %d of 262144 members evaluated, update over "
+                        "all 131072 pairs" % members,
+            "eval_member_tokens_per_s": members * S / (eval_ms / 1e3), "eval_ms": eval_ms, "update_ms": upd_ms,
+            "newton_schulz_and_apply_ms": prof.get("muon", (0.0, 0))[0] / steps,
+            "update_gemm_ms": prof.get("update_gemm", (0.0, 0))[0] / steps,
+            "update_operands_ms": prof.get("update_operands", (0.0, 0))[0] / steps,
+            "projection_tops": tops, "projection_frac_of_peak": (tops / peaks["tensor"]) if tops else None,
+            "projection_frac_of_mma_loop": (tops / mma_loop_tops) if (tops and mma_loop_tops) else None,
+            "implied_generation_ms": {"1_gpu": t_eval_1 + upd_ms, "8_gpus": t_eval_8 + upd_ms},
+            "implied_8gpu_efficiency_fixed_population": (t_eval_1 + upd_ms) / (8.0 * (t_eval_8 + upd_ms)),
+            "implied_8gpu_eval_share": t_eval_8 / (t_eval_8 + upd_ms),
+            "kernels_ms": {k: v[0] / steps for k, v in prof.items() if v[1] > 0}}
+
+
+# ----------------------------------------------------------------------------- isolated workloads (one GPU)
+def run_c3(args, pkg, synth, torch, real_stdout, peaks):
+    """Isolated perturbed projection at the size BASELINE names: y = clip((x.W + ((x.b) a ns >> 7)) >> 8)."""
+    K = N = 4096
+    rpm, members = 64, 4096
+    rows = rpm * members
+    cfg = pkg.default_config(device_mask=3)
+    ctx = pkg.Context(cfg, 0, 2)
+    g = torch.Generator(device="cuda"); g.manual_seed(3)
+    x = torch.empty((rows, K), dtype=torch.int8, device="cuda")
+    for r0 in range(0, rows, 16384):
+        x[r0:r0 + 16384] = torch.clamp(torch.round(torch.randn((16384, K), generator=g, device="cuda") * 32.0), -127, 127).to(torch.int8)
+    w = synth.uniform_int8(0, K * N)
+    d_w = torch.from_numpy(w).cuda()
+    y = torch.zeros((rows, N), dtype=torch.int8, device="cuda")
+    x_host = torch.empty((rows, K), dtype=torch.int8).pin_memory(); x_host.copy_(x)
+    y_host = torch.empty((rows, N), dtype=torch.int8).pin_memory()
+    torch.cuda.synchronize()
+
+    def step(host):
+        if host:
+            ctx.perturbed_projection(x_host.numpy(), w, y_host.numpy(), rows, K, N, rpm, 7, 200, 201, 7, 8)
+        else:
+            ctx.perturbed_projection(x.data_ptr(), d_w.data_ptr(), y.data_ptr(), rows, K, N, rpm, 7, 200, 201, 7, 8, on_device=True)
+
+    n_warm = max(args.warmup, 3)
+    for _ in range(n_warm):
+        step(False)
+    l0 = ctx.launch_count()
+    sampler = ClockSampler(0); sampler.start()
+    ctx.timer_start()
+    for _ in range(args.steps):
+        step(False)
+    ms = ctx.timer_stop() / args.steps
+    clocks = sampler.stop()
+    launches = ctx.launch_count() - l0
+    step(True)
+    ctx.timer_start()
+    for _ in range(args.steps):
+        step(True)
+    ms_e2e = ctx.timer_stop() / args.steps
+    ops = 2.0 * rows * K * N
+    achieved = ops / (ms / 1e3) / 1e12
+    line = {"metric": METRIC, "value": rows / (ms / 1e3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": n_warm, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8/int32", "data": "synthetic",
+            "config": {"workload": "c3: isolated perturbed int8 projection, W 4096x4096, 4096 members x 64 tokens = 262144 rows, noise in [-3,3], "
+                                   ">>8 and clip; the step includes the weight transpose, the pair noise table and the row dots x.b",
+                       "l2_policy": "inputs larger than L2 (x 1 GiB, y 1 GiB)"},
+            "e2e": {"value": rows / (ms_e2e / 1e3), "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": int(rows * K + K * N),
+                    "d2h_bytes_per_step": int(rows * N)},
+            "gpu_launches": int(launches),
+            "roofline": {"kernel": "gemm_i8_kernel<EPI_CLIP8> (whole call: transpose + noise + dots + GEMM)", "bound": "tensor", "achieved": achieved,
+                         "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": achieved / peaks["tensor"], "traffic": None,
+                         "peak_source": peaks["tensor_source"]},
+            "clocks": clocks, "cpu_baseline": None}
+    real_stdout.write(json.dumps(line) + "\n"); real_stdout.flush()
+    ctx.close()
+
+
+def run_c4(args, pkg, synth, torch, real_stdout, peaks):
+    raise SystemExit("workload c4 needs the isolated matrix-update entry point")
+
+
+def run_c5slice(args, pkg, synth, torch, real_stdout, peaks):
+    members = 2048
+    ctx0 = pkg.Context(pkg.default_config(**C2), 0, 2)
+    mma = ctx0.measure_int8_peak(16384, 2048, 2048, 20)
+    ctx0.close()
+    sampler = ClockSampler(0); sampler.start()
+    r = c5_sample_run(pkg, synth, 0, members, peaks, mma, steps=max(1, args.steps))
+    clocks = sampler.stop()
+    S = C5["seq_len"]
+    gen_ms = r["eval_ms"] + r["update_ms"]
+    line = {"metric": METRIC, "value": members * S / (gen_ms / 1e3), "unit": UNIT, "n_gpus": 1, "steps": max(1, args.steps), "warmup": 1,
+            "ms_per_step": gen_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8/int32", "data": "synthetic",
+            "config": {"workload": "c5slice: " + r["workload"], "l2_policy": "inputs larger than L2"},
+            "e2e": None, "gpu_launches": None,
+            "roofline": {"kernel": "gemm_i8_kernel (all projection epilogues)", "bound": "tensor", "achieved": r["projection_tops"],
+                         "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": r["projection_frac_of_peak"], "traffic": None,
+                         "peak_source": peaks["tensor_source"]},
+            "c5_sample": r, "clocks": clocks, "cpu_baseline": None}
+    real_stdout.write(json.dumps(line) + "\n"); real_stdout.flush()
 
 
 # ----------------------------------------------------------------------------- our arm
@@ -175,8 +380,11 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5slice"])
     ap.add_argument("--pop", type=int, default=POP_PER_GPU, help="members per GPU (benchmark value: 40960)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the extra legs of the default line (recurrent model, reference GPU kernels, C5 sample)")
+    ap.add_argument("--two-kernel-norm", action="store_true", help="A/B: take the two-kernel form of the adaptive normalisations (int32 pre-activations + requantisation kernels)")
     ap.add_argument("--wave", type=int, default=0, help="members per internal wave (0: the library's default)")
     ap.add_argument("--small", action="store_true", help="profiling-sized run: 1024 members, one warm-up step, no end-to-end / CPU legs")
     args = ap.parse_args()
@@ -187,7 +395,7 @@ def main():
         run_reference_arm(args, rank)
         return
     if args.small:
-        args.pop, args.no_cpu_baseline = 1024, True
+        args.pop, args.no_cpu_baseline, args.no_extras = 1024, True, True
 
     # libraries (NCCL's version banner, for one) may write to stdout: keep fd 1 for the single JSON line
     real_stdout = os.fdopen(os.dup(1), "w")
@@ -198,6 +406,18 @@ def main():
     from egg_c_b200 import synth
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a B200: the library has no CPU path")
+    peaks = load_peaks()
+    if args.workload != "c2":
+        if world > 1:
+            if rank == 0:
+                raise SystemExit("workload %s is a single-GPU measurement" % args.workload)
+            return
+        if args.workload == "c3":
+            return run_c3(args, pkg, synth, torch, real_stdout, peaks)
+        if args.workload == "c4":
+            return run_c4(args, pkg, synth, torch, real_stdout, peaks)
+        return run_c5slice(args, pkg, synth, torch, real_stdout, peaks)
+
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
@@ -208,6 +428,9 @@ def main():
     pop = args.pop * world                       # weak scaling: fixed members per GPU
     cfg = pkg.default_config(population_size=pop, **C2)
     ctx = pkg.Context(cfg, local_rank, args.wave)
+    if args.two_kernel_norm:
+        ctx.set_fused_epilogues(False)
+    fused_active = ctx.fused_epilogues_active()
     model = synth.random_model(cfg, 0, "uniform")
     ctx.upload_model(model)
     data_np = synth.zipf_bytes(1, DATA_LEN)
@@ -235,15 +458,14 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    seed0 = 0x00C0FFEE
     step_no = [0]
 
     def one_step(host_io):
         s = step_no[0]
         step_no[0] += 1
         if host_io:
-            return ctx.generation_host(data_host, s, seed0 + s, LR, losses_host)
-        return ctx.generation_host(None, s, seed0 + s, LR, None)
+            return ctx.generation_host(data_host, s, SEED0 + s, LR, losses_host)
+        return ctx.generation_host(None, s, SEED0 + s, LR, None)
 
     # ---- kernel-resident timing (inputs already in HBM) ----
     n_warm = args.warmup if args.small else max(args.warmup, 3)
@@ -281,6 +503,16 @@ def main():
         barrier()
     e2e_value = pop * cfg.seq_len / (ms_e2e / 1e3)
 
+    # ---- replicas: every rank must hold byte-identical weights and optimiser state after the same generations ----
+    crc_model = zlib.crc32(ctx.download_model().tobytes())
+    crc_opt = zlib.crc32(ctx.download_opt_state().tobytes())
+    replicas_identical = None
+    if dist:
+        t = torch.tensor([crc_model, crc_opt], dtype=torch.int64, device="cuda")
+        allc = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(allc, t)
+        replicas_identical = all(bool(torch.equal(a, allc[0])) for a in allc)
+
     # ---- roofline of the dominant kernel class ----
     H, L, S, V = cfg.hidden_dim, cfg.n_layers, cfg.seq_len, cfg.vocab_size
     rows_per_step = per * S
@@ -295,22 +527,9 @@ def main():
         "rowwise": 6.0 * H * rows_per_step * (2 * L + 2),
         "aqn": 15.0 * H * rows_per_step * L,
     }
-    # DRAM bytes (read + write) per row of one launch, from the ncu captures summarised under profiles/ (262 144-row
-    # launches of the same kernels; traffic grows in proportion to the rows of a launch)
-    ncu_traffic_per_row = {"attention": (404.110e6 + 116.544e6) / 262144, "rowwise": (543.130e6 + 249.417e6) / 262144,
-                           "aqn": (1613.772e6 + 384.940e6) / 262144,
-                           "gemm_gelu": (143.689e6 + 484.641e6) / 262144, "gemm_qkv": (142.191e6 + 1560.224e6) / 262144,
-                           "gemm_pre32": (675.062e6 + 494.890e6) / 262144}
-    peaks = {}
-    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(pk):
-        peaks = json.load(open(pk))
-    hbm_peak = peaks.get("hbm_gbs", 6650.0)
-    # no int8 figure is measured on this pool: int8 dense peak taken as 2x the measured sustained bf16 GEMM throughput
-    tensor_peak = 2.0 * peaks.get("bf16_tflops_sustained", 1400.0)
-    peak_src = "measured" if peaks else "fallback"
+    traffic_per_row, traffic_src = load_traffic()
+    hbm_peak, tensor_peak = peaks["hbm"], peaks["tensor"]
     rows_per_launch = min(ctx.wave_members(), per) * S
-    traffic_src = "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 262144-row launch (profiles/), scaled by rows per launch"
 
     def class_roofline(k):
         t_ms, n_launch = prof[k]
@@ -320,8 +539,10 @@ def main():
         else:
             achieved = hbm_bytes[k] * args.steps / (t_ms / 1e3) / 1e9
             r = {"kernel": k, "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak}
+            if r["frac"] > 1.0:
+                r["note"] = "above the DRAM copy figure: part of this kernel's bytes are served from L2"
         r["avg_launch_ms"] = t_ms / max(1, n_launch)
-        r["traffic"] = ncu_traffic_per_row[k] * rows_per_launch if k in ncu_traffic_per_row else None
+        r["traffic"] = traffic_per_row[k] * rows_per_launch if k in traffic_per_row else None
         return r
 
     per_class = [class_roofline(k) for k in prof if prof[k][1] > 0 and (k in gemm_ops or k in hbm_bytes)]
@@ -332,33 +553,6 @@ def main():
     gemm_launches = sum(prof[k][1] for k in gemm_keys)
     others = [k for k in hbm_bytes if k in prof and prof[k][1] > 0]
     top_other = max(others, key=lambda k: prof[k][0]) if others else None
-    if gemm_keys and (top_other is None or gemm_ms >= prof[top_other][0]):
-        achieved = sum(gemm_ops[k] for k in gemm_keys) * args.steps / (gemm_ms / 1e3) / 1e12
-        known = [k for k in gemm_keys if k in ncu_traffic_per_row]
-        roof = {"kernel": "gemm_i8_kernel (all projection epilogues)", "bound": "tensor", "achieved": achieved, "peak": tensor_peak,
-                "unit": "TFLOP/s", "frac": achieved / tensor_peak,
-                "traffic": (sum(ncu_traffic_per_row[k] * rows_per_launch * prof[k][1] for k in known) / max(1, sum(prof[k][1] for k in known)))
-                if known else None,
-                "peak_source": "2 x bf16_tflops_sustained of %s MEASURED_PEAKS (no int8 entry); int8 ops" % peak_src,
-                "avg_launch_ms": gemm_ms / max(1, gemm_launches), "share_of_step": None,
-                "traffic_source": traffic_src + "; launch-weighted mean over the GELU / residual / QKV instantiations"}
-    else:
-        roof = class_roofline(top_other)
-        roof["peak_source"] = "hbm_gbs of %s MEASURED_PEAKS" % peak_src
-        roof["traffic_source"] = traffic_src
-    total_prof = sum(v[0] for v in prof.values()) or 1.0
-    kernel_share = {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps, "share": v[0] / total_prof}
-                    for k, v in prof.items() if v[1] > 0}
-    roof["share_of_step"] = (gemm_ms if roof["bound"] == "tensor" else prof[top_other][0]) / total_prof
-    gemm_total_ms = sum(prof[k][0] for k in gemm_ops if k in prof)
-    gemm_tops = sum(gemm_ops.values()) * args.steps / (gemm_total_ms / 1e3) / 1e12 if gemm_total_ms > 0 else None
-
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        try:
-            cpu = cpu_reference_run(1, 0)
-        except Exception as e:   # the baseline is reported, never allowed to break the bench line
-            cpu = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference", "sample": "failed: %s" % e}
 
     # what the GEMM's own TMA + tcgen05 loop sustains on this GPU with the accumulators dropped (operands in L2)
     mma_loop_tops = None
@@ -368,12 +562,54 @@ def main():
         except Exception:
             mma_loop_tops = None
 
-    gru = None
-    if rank == 0 and world == 1 and not args.small:
+    if gemm_keys and (top_other is None or gemm_ms >= prof[top_other][0]):
+        achieved = sum(gemm_ops[k] for k in gemm_keys) * args.steps / (gemm_ms / 1e3) / 1e12
+        known = [k for k in gemm_keys if k in traffic_per_row]
+        roof = {"kernel": "gemm_i8_kernel (all projection epilogues)", "bound": "tensor", "achieved": achieved, "peak": tensor_peak,
+                "unit": "TFLOP/s", "frac": achieved / tensor_peak,
+                "frac_of_mma_loop_measured": (achieved / mma_loop_tops) if mma_loop_tops else None,
+                "mma_loop_tops_measured": mma_loop_tops,
+                "traffic": (sum(traffic_per_row[k] * rows_per_launch * prof[k][1] for k in known) / max(1, sum(prof[k][1] for k in known)))
+                if known else None,
+                "peak_source": peaks["tensor_source"],
+                "avg_launch_ms": gemm_ms / max(1, gemm_launches), "share_of_step": None,
+                "traffic_source": (traffic_src + "; launch-weighted mean over the projection instantiations") if traffic_src else None}
+    else:
+        roof = class_roofline(top_other)
+        roof["peak_source"] = peaks["hbm_source"]
+        roof["traffic_source"] = traffic_src
+    total_prof = sum(v[0] for v in prof.values()) or 1.0
+    kernel_share = {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps, "share": v[0] / total_prof}
+                    for k, v in prof.items() if v[1] > 0}
+    roof["share_of_step"] = (gemm_ms if roof["bound"] == "tensor" else prof[top_other][0]) / total_prof
+    gemm_total_ms = sum(prof[k][0] for k in gemm_ops if k in prof)
+    gemm_tops = sum(gemm_ops.values()) * args.steps / (gemm_total_ms / 1e3) / 1e12 if gemm_total_ms > 0 else None
+    step_tops = sum(gemm_ops.values()) / (ms_per_step / 1e3) / 1e12
+
+    wave_members = ctx.wave_members()
+    ctx.close()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            cpu = cpu_reference_run(1, 0)
+        except Exception as e:   # the baseline is reported, never allowed to break the bench line
+            cpu = {"value": None, "unit": UNIT, "cores": host_cores(), "kind": "reference", "sample": "failed: %s" % e}
+
+    gru = ref_gpu = c5 = None
+    if rank == 0 and world == 1 and not args.no_extras:
         try:
             gru = gru_model_run(pkg, synth, local_rank)
         except Exception as e:
             gru = {"value": None, "unit": UNIT, "sample": "failed: %s" % e}
+        try:
+            ref_gpu = reference_gpu_kernels_run()
+        except Exception as e:
+            ref_gpu = {"value": None, "unit": UNIT, "sample": "failed: %s" % e}
+        try:
+            c5 = c5_sample_run(pkg, synth, local_rank, 512, peaks, mma_loop_tops)
+        except Exception as e:
+            c5 = {"workload": "failed: %s" % e}
 
     if rank == 0:
         line = {
@@ -381,7 +617,8 @@ def main():
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8/int32",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "population_size": pop, "members_per_gpu": per, "seq_len": S, "hidden_dim": H,
-                       "n_layers": L, "wave_members": ctx.wave_members(), "dataset_bytes": DATA_LEN,
+                       "n_layers": L, "wave_members": wave_members, "dataset_bytes": DATA_LEN,
+                       "adaptive_norms": "fused into the projection epilogues (row-owning kernels)" if fused_active else "two-kernel form",
                        "l2_policy": "inputs larger than L2: each wave streams > 2 GB of activations, dataset 64 MiB",
                        "parallelism": "population sharded, pair-aligned; one NCCL all-gather of fitness per generation"},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": int(DATA_LEN),
@@ -391,15 +628,19 @@ def main():
             "rooflines_by_class": per_class,
             "projection_gemms": {"tops": gemm_tops, "frac_of_peak": (gemm_tops / tensor_peak) if gemm_tops else None, "peak": tensor_peak,
                                  "mma_loop_tops_measured": mma_loop_tops,
-                                 "frac_of_mma_loop": (gemm_tops / mma_loop_tops) if (gemm_tops and mma_loop_tops) else None},
+                                 "frac_of_mma_loop": (gemm_tops / mma_loop_tops) if (gemm_tops and mma_loop_tops) else None,
+                                 "whole_step_tops": step_tops, "whole_step_frac_of_peak": step_tops / tensor_peak},
             "kernels": kernel_share,
             "clocks": clocks,
+            "replicas_identical": replicas_identical,
+            "replica_crc32": {"model": crc_model, "optimizer_state": crc_opt},
             "cpu_baseline": cpu,
             "gru_model_gpu": gru,
+            "reference_gpu_kernels": ref_gpu,
+            "c5_sample": c5,
         }
         real_stdout.write(json.dumps(line) + "\n")
         real_stdout.flush()
-    ctx.close()
     if dist:
         dist.destroy_process_group()
 

@@ -2,6 +2,7 @@
 // evaluation pipeline, fitness, NCCL exchange, update reconstruction + optimiser.
 // "mgpu.cu" = full_cuda_train_transformer_adam_mgpu.cu of the reference.
 #include "egg_kernels.cuh"
+#include "egg_gemm_fused.cuh"
 
 #include <string>
 #include <sys/stat.h>
@@ -107,6 +108,8 @@ struct egg_ctx {
     MuonWs muon = {nullptr, nullptr, nullptr, nullptr};
     unsigned long long *d_updates = nullptr;
     int *d_err = nullptr;
+    // row-owning projections with the adaptive normalisations fused (default wherever the shapes allow)
+    bool fused_on = true;
     // measurement
     cudaEvent_t t0 = nullptr, t1 = nullptr;
     bool prof_on = false;
@@ -313,7 +316,7 @@ extern "C" void egg_ctx_destroy(egg_ctx *c) {
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
     void *ptrs[] = {c->d_model, c->d_opt, c->d_shadow, c->d_exp_lut, c->d_rope_lut, c->d_rope_t, c->d_act_lut, c->d_data, c->d_loss, c->d_fit,
-                    c->d_x, c->d_h, c->d_u, c->d_q, c->d_k, c->d_v, c->d_ao, c->d_pre, c->d_xb, c->d_xb2, c->d_rowmax,
+                    c->d_x, c->d_h, c->d_u, c->d_q, c->d_ao, c->d_pre, c->d_xb, c->d_xb2, c->d_rowmax,
                     c->d_rowmax3, c->d_xbo, c->d_wave_loss, c->d_segs, c->d_nt, c->d_na, c->d_nb, c->muon.x, c->muon.g,
                     c->muon.y, c->muon.norm2, c->d_updates, c->d_err, c->d_scales, c->d_ch_in, c->d_ch_out};
     for (void *p : ptrs) if (p) cudaFree(p);
@@ -323,6 +326,8 @@ extern "C" void egg_ctx_destroy(egg_ctx *c) {
     if (c->stream) cudaStreamDestroy(c->stream);
     delete c;
 }
+
+static int noalloc_scratch_address(int device, int8_t **out);
 
 extern "C" int egg_ctx_create(const egg_config *cfg, int device, int wave_members, egg_ctx **out) {
     if (!cfg || !out) { set_error("null argument"); return EGG_E_INVALID; }
@@ -337,6 +342,11 @@ extern "C" int egg_ctx_create(const egg_config *cfg, int device, int wave_member
     EGG_CUDA(cudaGetDeviceProperties(&prop, device));
     if (prop.major != 10) { set_error("this library is built for sm_100a only (device is sm_%d%d)", prop.major, prop.minor); return EGG_E_INVALID; }
     if ((rc = gemm_init())) return rc;
+    {   // resolve the built-in scratch buffer of egg_update_reconstruct_noalloc now (this device is current), so that
+        // the module that holds it is loaded here and that call itself stays a table lookup
+        int8_t *unused = nullptr;
+        if ((rc = noalloc_scratch_address(device, &unused))) return rc;
+    }
 
     egg_ctx *c = new egg_ctx();
     c->cfg = *cfg; c->device = device; c->num_sms = prop.multiProcessorCount;
@@ -407,7 +417,8 @@ extern "C" int egg_ctx_create(const egg_config *cfg, int device, int wave_member
     const int64_t R = (int64_t)wave_members * S;
     c->R = R;
     TRY(dev_alloc(&c->d_x, R * H)); TRY(dev_alloc(&c->d_h, R * H)); TRY(dev_alloc(&c->d_u, R * 4 * H));
-    TRY(dev_alloc(&c->d_q, R * H)); TRY(dev_alloc(&c->d_k, R * H)); TRY(dev_alloc(&c->d_v, R * H)); TRY(dev_alloc(&c->d_ao, R * H));
+    TRY(dev_alloc(&c->d_q, 3 * R * H)); c->d_k = c->d_q + R * H; c->d_v = c->d_q + 2 * R * H;   // one [3][R][H] block: q, k, v
+    TRY(dev_alloc(&c->d_ao, R * H));
     TRY(dev_alloc(&c->d_pre, R * 3 * H));
     TRY(dev_alloc(&c->d_xb, R * 3)); TRY(dev_alloc(&c->d_xb2, R)); TRY(dev_alloc(&c->d_rowmax, R)); TRY(dev_alloc(&c->d_rowmax3, R * 3));
     TRY(dev_alloc(&c->d_xbo, R)); TRY(dev_alloc(&c->d_wave_loss, wave_members));
@@ -609,6 +620,22 @@ extern "C" int egg_set_dataset(egg_ctx *c, const uint8_t *host_tokens, int64_t n
 
 // ---------------------------------------------------------------- evaluation
 
+static bool use_fused(const egg_ctx *c) {
+    return c->fused_on && fused_supported(c->cfg.hidden_dim, c->cfg.seq_len);
+}
+
+static FusedParams base_fused(egg_ctx *c, int M, int K, int parts) {
+    FusedParams f;
+    memset(&f, 0, sizeof(f));
+    f.M = M; f.H = c->cfg.hidden_dim; f.K = K; f.parts = parts; f.seq_len = c->cfg.seq_len;
+    f.nt = c->d_nt; f.nt_stride = c->nmap.stride; f.nt_c_off = -1;
+    f.rank1_shift = c->cfg.fixed_point + c->cfg.sigma_shift;
+    f.rope_t = c->d_rope_t; f.head_dim = c->cfg.head_dim; f.rope_bit = c->cfg.rope_scale_bit;
+    f.part_rows = c->R;
+    f.err = c->d_err;
+    return f;
+}
+
 static GemmParams base_gemm(egg_ctx *c, int M, int N, int K) {
     GemmParams g;
     memset(&g, 0, sizeof(g));
@@ -648,6 +675,13 @@ static int run_mlp(egg_ctx *c, int M, const MlpOff &mo, int nt_base, const int8_
     int rc = PROF(EGG_PROF_GEMM_GELU, launch_gemm(c->stream, EPI_GELU, c->d_h, up_t, g, c->num_sms));
     if (rc) return rc;
     if (c->scales_on && (rc = scaled_dot1(c, M, c->d_u, 4, nt_base + mo.dn_b, ov_dn_row, c->d_xb2, 1))) return rc;
+    if (use_fused(c)) {
+        // down projection + residual + bias, adaptive layer normalise in the epilogue: x is rewritten in place
+        FusedParams f = base_fused(c, M, 4 * H, 1);
+        f.nt_a_off = nt_base + mo.dn_a; f.nt_c_off = nt_base + mo.bdn_d;
+        f.xb = c->d_xb2; f.xb_stride = 1; f.out_shift = c->cfg.shift_mlp_down; f.bias = dn_bias;
+        return PROF(EGG_PROF_GEMM_PRE32, launch_gemm_fused(c->stream, FUSED_RES, c->d_u, dn_t, c->d_x, c->d_x, f, c->num_sms));
+    }
     GemmParams d = base_gemm(c, M, H, 4 * H);
     d.nt_a_off = nt_base + mo.dn_a; d.nt_c_off = nt_base + mo.bdn_d;
     d.xb = c->d_xb2; d.xb_stride = 1; d.out_shift = c->cfg.shift_mlp_down; d.bias = dn_bias; d.resid = c->d_x; d.out32 = c->d_pre;
@@ -701,37 +735,53 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
         const int nb = nm.layer0 + l * nm.layer_stride;
         const LayerOff &lo = nm.layer_rel;
         const int8_t *shl = sh + c->so.layer0 + (int64_t)l * c->so.layer_stride;
-        // ALN of the previous block -> x ; LN1 -> h ; Σ h·b for q,k,v (mgpu.cu:770-776)
+        // ALN of the previous block -> x (already done by the producing projection on the row-owning path) ; LN1 -> h ;
+        // Σ h·b for q,k,v (mgpu.cu:770-776)
+        const bool fused = use_fused(c);
+        const int row_mode = fused ? 2 : 1;
         RowParams ra = base_row(c, M);
         ra.nt_w_m = nb + lo.ln1.w_m; ra.nt_b_m = nb + lo.ln1.b_m;
         ra.ndots = 3; ra.nt_dot[0] = nb + lo.qkv_b; ra.nt_dot[1] = nb + lo.qkv_b + H; ra.nt_dot[2] = nb + lo.qkv_b + 2 * H;
-        if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, ra, 1)))) return rc;
+        if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, ra, row_mode)))) return rc;
         const int64_t lH = (int64_t)l * H;
         if (sc) {
             const int64_t ovq[3] = {SL.w_q_row + lH, SL.w_k_row + lH, SL.w_v_row + lH};
             if ((rc = scaled_dots(c, M, c->d_h, 1, 3, ra.nt_dot, ovq, c->d_xb, 3))) return rc;
         }
-        // fused Q|K|V projection + RoPE (mgpu.cu:779-784)
-        GemmParams gq = base_gemm(c, M, 3 * H, H);
-        gq.nt_a_off = nb + lo.qkv_a; gq.xb = c->d_xb; gq.xb_stride = 3; gq.out32 = c->d_pre; gq.rowstat = c->d_rowmax3; gq.third = H;
-        if ((rc = PROF(EGG_PROF_GEMM_QKV, launch_gemm(st, EPI_QKV, c->d_h, shl + c->so.qkv, gq, c->num_sms)))) return rc;
-        AqnParams aq; aq.M = M; aq.H = H; aq.pre3 = c->d_pre; aq.rowmax3 = c->d_rowmax3; aq.q = c->d_q; aq.k = c->d_k; aq.v = c->d_v;
-        if ((rc = PROF(EGG_PROF_AQN, launch_aqn(st, aq)))) return rc;
+        if (fused) {
+            // Q|K|V projection + RoPE + adaptive_qkv_normalize in one kernel (mgpu.cu:779-784): int8 q, k, v
+            FusedParams fq = base_fused(c, M, H, 3);
+            fq.nt_a_off = nb + lo.qkv_a; fq.xb = c->d_xb; fq.xb_stride = 3;
+            if ((rc = PROF(EGG_PROF_GEMM_QKV, launch_gemm_fused(st, FUSED_QKV, c->d_h, shl + c->so.qkv, c->d_q, nullptr, fq, c->num_sms)))) return rc;
+        } else {
+            // fused Q|K|V projection + RoPE (mgpu.cu:779-784)
+            GemmParams gq = base_gemm(c, M, 3 * H, H);
+            gq.nt_a_off = nb + lo.qkv_a; gq.xb = c->d_xb; gq.xb_stride = 3; gq.out32 = c->d_pre; gq.rowstat = c->d_rowmax3; gq.third = H;
+            if ((rc = PROF(EGG_PROF_GEMM_QKV, launch_gemm(st, EPI_QKV, c->d_h, shl + c->so.qkv, gq, c->num_sms)))) return rc;
+            AqnParams aq; aq.M = M; aq.H = H; aq.pre3 = c->d_pre; aq.rowmax3 = c->d_rowmax3; aq.q = c->d_q; aq.k = c->d_k; aq.v = c->d_v;
+            if ((rc = PROF(EGG_PROF_AQN, launch_aqn(st, aq)))) return rc;
+        }
         AttnParams ap; ap.members = members; ap.H = H; ap.head_dim = cf.head_dim; ap.seq_len = S; ap.shift_attn = cf.shift_attn;
         ap.q = c->d_q; ap.k = c->d_k; ap.v = c->d_v; ap.ao = c->d_ao; ap.exp_lut = c->d_exp_lut; ap.nt = c->d_nt;
         ap.nt_stride = nm.stride; ap.nt_o_b = nb + lo.o_b; ap.xbo = c->d_xbo;
         if ((rc = PROF(EGG_PROF_ATTENTION, launch_attention(st, ap)))) return rc;
         if (sc && (rc = scaled_dot1(c, M, c->d_ao, 1, nb + lo.o_b, SL.w_o_row + lH, c->d_xbo, 1))) return rc;
         // output projection + residual (mgpu.cu:828-830)
-        GemmParams go = base_gemm(c, M, H, H);
-        go.nt_a_off = nb + lo.o_a; go.xb = c->d_xbo; go.xb_stride = 1; go.out_shift = cf.shift_out; go.resid = c->d_x;
-        go.out32 = c->d_pre; go.rowstat = c->d_rowmax;
-        if ((rc = PROF(EGG_PROF_GEMM_PRE32, launch_gemm(st, EPI_PRE32, c->d_ao, shl + c->so.o, go, c->num_sms)))) return rc;
+        if (fused) {
+            FusedParams fo = base_fused(c, M, H, 1);
+            fo.nt_a_off = nb + lo.o_a; fo.xb = c->d_xbo; fo.xb_stride = 1; fo.out_shift = cf.shift_out;
+            if ((rc = PROF(EGG_PROF_GEMM_PRE32, launch_gemm_fused(st, FUSED_RES, c->d_ao, shl + c->so.o, c->d_x, c->d_x, fo, c->num_sms)))) return rc;
+        } else {
+            GemmParams go = base_gemm(c, M, H, H);
+            go.nt_a_off = nb + lo.o_a; go.xb = c->d_xbo; go.xb_stride = 1; go.out_shift = cf.shift_out; go.resid = c->d_x;
+            go.out32 = c->d_pre; go.rowstat = c->d_rowmax;
+            if ((rc = PROF(EGG_PROF_GEMM_PRE32, launch_gemm(st, EPI_PRE32, c->d_ao, shl + c->so.o, go, c->num_sms)))) return rc;
+        }
         // ALN -> x ; LN2 -> h ; Σ h·b_up
         RowParams rb = base_row(c, M);
         rb.nt_w_m = nb + lo.ln2.w_m; rb.nt_b_m = nb + lo.ln2.b_m;
         rb.ndots = 1; rb.nt_dot[0] = nb + lo.mlp.up_b;
-        if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, rb, 1)))) return rc;
+        if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, rb, row_mode)))) return rc;
         if (sc && (rc = scaled_dot1(c, M, c->d_h, 1, nb + lo.mlp.up_b, SL.w_up_row + lH, c->d_xb, 3))) return rc;
         if ((rc = run_mlp(c, M, lo.mlp, nb, shl + c->so.up, mdl + L.mlp_bias_up + (int64_t)l * 4 * H, shl + c->so.dn,
                           mdl + L.mlp_bias_down + (int64_t)l * H, SL.w_down_row + 4 * lH))) return rc;
@@ -740,7 +790,7 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
     RowParams rf = base_row(c, M);
     rf.nt_w_m = nm.ln_f.w_m; rf.nt_b_m = nm.ln_f.b_m;
     rf.ndots = 1; rf.nt_dot[0] = nm.emb_b;
-    if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, rf, 1)))) return rc;
+    if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, rf, use_fused(c) ? 2 : 1)))) return rc;
     if (sc && (rc = scaled_dot1(c, M, c->d_h, 1, nm.emb_b, SL.embedding_col, c->d_xb, 3))) return rc;
     GemmParams gh = base_gemm(c, M, V, H);
     gh.nt_a_off = nm.head_a; gh.xb = c->d_xb; gh.xb_stride = 3; gh.out_shift = cf.shift_logit;
@@ -1097,6 +1147,18 @@ extern "C" int egg_update_reconstruct(egg_ctx *c, const int32_t *fitness, int pa
 static __device__ __align__(256) int8_t g_noalloc_scratch[EGG_NOALLOC_SCRATCH_BYTES];
 static int8_t *g_noalloc_ptr[64] = {};     // device address of the array, per device ordinal
 
+// Device address of the array on `device`, which must be the current device: looked up once per device and cached.
+static int noalloc_scratch_address(int device, int8_t **out) {
+    if (device < 0 || device >= 64) { set_error("device ordinal out of range"); return EGG_E_INVALID; }
+    if (!g_noalloc_ptr[device]) {
+        void *ptr = nullptr;
+        EGG_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        g_noalloc_ptr[device] = static_cast<int8_t *>(ptr);
+    }
+    *out = g_noalloc_ptr[device];
+    return EGG_OK;
+}
+
 extern "C" int egg_update_reconstruct_noalloc(egg_ctx *c, const int32_t *d_fitness, int pairs, int rows_k, int cols_n, int off_a,
                                               int off_b, int seed_base, uint32_t step_seed, int split, int32_t *d_vote_out) {
     if (!c || !d_fitness || !d_vote_out) { set_error("null argument"); return EGG_E_INVALID; }
@@ -1111,14 +1173,10 @@ extern "C" int egg_update_reconstruct_noalloc(egg_ctx *c, const int32_t *d_fitne
     }
     const int amax = c->cfg.device_gaussian ? 3 * c->cfg.device_mask : c->cfg.device_mask;
     if (split && 16 * amax > 127) { set_error("noise magnitude %d does not fit the two-digit operand split", amax); return EGG_E_INVALID; }
-    if (c->device < 0 || c->device >= 64) { set_error("device ordinal out of range"); return EGG_E_INVALID; }
     EGG_CUDA(cudaSetDevice(c->device));
-    if (!g_noalloc_ptr[c->device]) {       // set-up, once per device, with that device current
-        void *ptr = nullptr;
-        EGG_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
-        g_noalloc_ptr[c->device] = static_cast<int8_t *>(ptr);
-    }
-    int8_t *na = g_noalloc_ptr[c->device];
+    int8_t *na = nullptr;                  // set-up happened in egg_ctx_create on this device; this is the cached address
+    int rc0 = noalloc_scratch_address(c->device, &na);
+    if (rc0) return rc0;
     int8_t *nb = na + (int64_t)cols_n * ktot;           // cols_n*ktot is a multiple of 128*128: stays 256-byte aligned
     int rc = launch_update_operands(c->stream, na, nb, d_fitness, pairs, kp, rows_k, cols_n, off_a, off_b, seed_base, step_seed,
                                     c->cfg.device_mask, c->cfg.device_gaussian, split ? 1 : 0);
@@ -1231,6 +1289,14 @@ extern "C" int egg_measure_int8_peak(egg_ctx *c, int m, int n, int k, int iters,
     cleanup();
     return check_dev_err(c);
 }
+
+extern "C" int egg_set_fused_epilogues(egg_ctx *c, int enable) {
+    if (!c) { set_error("null context"); return EGG_E_INVALID; }
+    c->fused_on = enable != 0;
+    return EGG_OK;
+}
+
+extern "C" int egg_fused_epilogues_active(egg_ctx *c) { return (c && use_fused(c)) ? 1 : 0; }
 
 extern "C" int64_t egg_launch_count(egg_ctx *c) { return c ? c->launches : 0; }
 extern "C" int egg_wave_members(egg_ctx *c) { return c ? c->wave_members : 0; }

@@ -162,6 +162,24 @@ struct ParamDesc {
     int64_t ov_in, ov_out;   // AdaptiveScales offsets of the overlays over the input index (or the vector) and the output index
 };
 
+// ---------------------------------------------------------------- adaptive requantisation
+// adaptive_layer_normalize / adaptive_qkv_normalize (egg_adaptive_normalize.h:10-103):
+//   scale = 127.0f / (float)(max + 1e-9f);  out = clamp((int)roundf((float)v * scale), -127, 127)
+__device__ __forceinline__ float aln_scale(int layer_max) { return 127.0f / (float)(layer_max + 1e-9f); }
+__device__ __forceinline__ float aln_scale24(int layer_max) { return aln_scale(layer_max) * 16777216.0f; }    // exact: a power of two
+// clamp((int)roundf((float)v * scale), -127, 127) for |v| <= max, in fixed point: |v| * (scale * 2^24) is the same
+// float product scaled by a power of two (|x| <= 127 * (1 + 2^-23), so x * 2^24 < 2^31), its truncation to an integer
+// keeps every bit that decides the rounding (for |x| >= 1 the product has at most 23 fraction bits; below 1 only
+// "is it >= 0.5" matters, which truncation preserves), and round-half-away-from-zero becomes (xi + 2^23) >> 24.
+// The result cannot leave [-127, 127], so the reference's clamp needs no instruction.
+// The float product and its truncation are symmetric in the sign of v, so the sign is carried through: for a negative
+// truncated product xi = -a, -((a + 2^23) >> 24) == (xi + 2^23 - 1) >> 24 (the arithmetic shift floors), which is the
+// positive formula plus the sign word xi >> 31.
+__device__ __forceinline__ int aln_quant(int val, float scale24) {
+    const int xi = __float2int_rz(__int2float_rn(val) * scale24);
+    return (xi + (1 << 23) + (xi >> 31)) >> 24;
+}
+
 // ---------------------------------------------------------------- errors
 void set_error(const char *fmt, ...);
 

@@ -1,5 +1,6 @@
 // Instantiations and host launcher of the tcgen05 int8 GEMM.
 #include "egg_kernels.cuh"
+#include "egg_gemm_fused.cuh"
 
 #include <cudaTypedefs.h>
 
@@ -45,6 +46,10 @@ int gemm_init() {
     if ((rc = set_attr_both<EPI_MUON_M>())) return rc;
     if ((rc = set_attr_both<EPI_VOTE>())) return rc;
     if ((rc = set_attr<256, EPI_NULL>())) return rc;
+    EGG_CUDA(cudaFuncSetAttribute(gemm_fused_kernel<256, FUSED_QKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_smem_bytes<256>()));
+    EGG_CUDA(cudaFuncSetAttribute(gemm_fused_kernel<256, FUSED_RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_smem_bytes<256>()));
+    EGG_CUDA(cudaFuncSetAttribute(gemm_fused_kernel<128, FUSED_QKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_smem_bytes<128>()));
+    EGG_CUDA(cudaFuncSetAttribute(gemm_fused_kernel<128, FUSED_RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_smem_bytes<128>()));
     return EGG_OK;
 }
 
@@ -87,6 +92,56 @@ static int make_tmap_out8(CUtensorMap *m, const void *ptr, uint64_t rows, uint64
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (int8 output) failed (%d) rows=%llu cols=%llu", (int)r, (unsigned long long)rows, (unsigned long long)cols); return EGG_E_CUDA; }
+    return EGG_OK;
+}
+
+// [rows][cols] int8 row-major moved as box_cols-column x 32-row boxes: 64-byte rows swizzled (64-byte pattern), 32-byte
+// rows stored densely
+static int make_tmap_box8(CUtensorMap *m, const void *ptr, uint64_t rows, uint64_t cols, uint32_t box_cols) {
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (cols & 15) || (box_cols != 64 && box_cols != 32)) {
+        set_error("int8 box map unsupported (ptr %p, cols %llu, box %u)", ptr, (unsigned long long)cols, box_cols);
+        return EGG_E_INVALID;
+    }
+    cuuint64_t gdim[2] = {cols, rows};
+    cuuint64_t gstride[1] = {cols};
+    cuuint32_t box[2] = {box_cols, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), gdim, gstride, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (int8 boxes) failed (%d) rows=%llu cols=%llu", (int)r, (unsigned long long)rows, (unsigned long long)cols); return EGG_E_CUDA; }
+    return EGG_OK;
+}
+
+int launch_gemm_fused(cudaStream_t st, int mode, const int8_t *A, const int8_t *B, int8_t *out, const int8_t *resid,
+                      const FusedParams &p_in, int num_sms) {
+    FusedParams p = p_in;
+    if (!g_encode) { set_error("gemm_init() was not called"); return EGG_E_STATE; }
+    if (p.M <= 0 || p.M % GEMM_BM || p.seq_len % GEMM_BM || p.H % 128 || p.H > FUSED_MAX_H || p.K % 16 || p.parts < 1 ||
+        (mode == FUSED_RES && (p.parts != 1 || !resid)) || (mode != FUSED_QKV && mode != FUSED_RES)) {
+        set_error("unsupported row-owning GEMM shape M=%d H=%d K=%d parts=%d seq_len=%d", p.M, p.H, p.K, p.parts, p.seq_len);
+        return EGG_E_INVALID;
+    }
+    const int bn = (p.H % 256 == 0) ? 256 : 128;
+    p.fd_head = make_fastdiv(p.head_dim > 0 ? p.head_dim : 64);
+    CUtensorMap ta, tb, to, tr;
+    int rc;
+    if ((rc = make_tmap(&ta, A, (uint64_t)p.M, (uint64_t)p.K, GEMM_BM))) return rc;
+    if ((rc = make_tmap(&tb, B, (uint64_t)p.parts * p.H, (uint64_t)p.K, (uint32_t)bn))) return rc;
+    const uint64_t out_rows = p.parts > 1 ? (uint64_t)p.parts * (uint64_t)p.part_rows : (uint64_t)p.M;
+    if ((rc = make_tmap_box8(&to, out, out_rows, (uint64_t)p.H, (uint32_t)bn / 4))) return rc;
+    tr = to;
+    if (mode == FUSED_RES && (rc = make_tmap_box8(&tr, resid, (uint64_t)p.M, (uint64_t)p.H, (uint32_t)bn / 4))) return rc;
+    const int units = (p.M / GEMM_BM) * p.parts;
+    const int grid = units < num_sms ? units : num_sms;
+    if (bn == 256) {
+        if (mode == FUSED_QKV) gemm_fused_kernel<256, FUSED_QKV><<<grid, GEMM_THREADS, fused_smem_bytes<256>(), st>>>(ta, tb, to, tr, p);
+        else gemm_fused_kernel<256, FUSED_RES><<<grid, GEMM_THREADS, fused_smem_bytes<256>(), st>>>(ta, tb, to, tr, p);
+    } else {
+        if (mode == FUSED_QKV) gemm_fused_kernel<128, FUSED_QKV><<<grid, GEMM_THREADS, fused_smem_bytes<128>(), st>>>(ta, tb, to, tr, p);
+        else gemm_fused_kernel<128, FUSED_RES><<<grid, GEMM_THREADS, fused_smem_bytes<128>(), st>>>(ta, tb, to, tr, p);
+    }
+    EGG_CUDA(cudaGetLastError());
     return EGG_OK;
 }
 

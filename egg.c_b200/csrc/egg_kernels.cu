@@ -177,23 +177,6 @@ __device__ __forceinline__ float roundf_small(float x) {
 // integer value of a float that holds an integer, |f| < 2^22
 __device__ __forceinline__ int f2i_exact(float f) { return __float_as_int(f + kMagic) - kMagicBits; }
 
-// adaptive_layer_normalize / adaptive_qkv_normalize (egg_adaptive_normalize.h:10-103):
-//   scale = 127.0f / (float)(max + 1e-9f);  out = clamp((int)roundf((float)v * scale), -127, 127)
-__device__ __forceinline__ float aln_scale(int layer_max) { return 127.0f / (float)(layer_max + 1e-9f); }
-__device__ __forceinline__ float aln_scale24(int layer_max) { return aln_scale(layer_max) * 16777216.0f; }    // exact: a power of two
-// clamp((int)roundf((float)v * scale), -127, 127) for |v| <= max, in fixed point: |v| * (scale * 2^24) is the same
-// float product scaled by a power of two (|x| <= 127 * (1 + 2^-23), so x * 2^24 < 2^31), its truncation to an integer
-// keeps every bit that decides the rounding (for |x| >= 1 the product has at most 23 fraction bits; below 1 only
-// "is it >= 0.5" matters, which truncation preserves), and round-half-away-from-zero becomes (xi + 2^23) >> 24.
-// The result cannot leave [-127, 127], so the reference's clamp needs no instruction.
-// The float product and its truncation are symmetric in the sign of v, so the sign is carried through: for a negative
-// truncated product xi = -a, -((a + 2^23) >> 24) == (xi + 2^23 - 1) >> 24 (the arithmetic shift floors), which is the
-// positive formula plus the sign word xi >> 31.
-__device__ __forceinline__ int aln_quant(int val, float scale24) {
-    const int xi = __float2int_rz(__int2float_rn(val) * scale24);
-    return (xi + (1 << 23) + (xi >> 31)) >> 24;
-}
-
 // trunc(a / mn) as C integer division does, for |a| < 2^16 and 1 <= mn <= 127, with rinv_up = (1/mn) * (1 + 2^-17):
 // the factor pushes every quotient away from zero by |q| * 7.6e-6 -- more than the float error of the product
 // (three roundings, < |q| * 1.8e-7), so an exact quotient k lands beyond k and truncates to k, and less than the
@@ -270,6 +253,13 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
                 x[j][i] = clip8((int)byte_of(e4, i) + (int)byte_of(eb4, i) + (int)byte_of(dl4, i) + perturb);
             }
         }
+    } else if (MODE == 2) {
+        // the residual stream was requantised by the projection that produced it: only read it
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+            const uint32_t w = *reinterpret_cast<const uint32_t *>(p.x_out + (int64_t)r * H + (j << 7) + (lane << 2));
+            x[j][0] = ptx::sx_byte0(w); x[j][1] = ptx::sx_byte1(w); x[j][2] = ptx::sx_byte2(w); x[j][3] = (int)w >> 24;
+        }
     } else {
         int4 v[NJ];
 #pragma unroll
@@ -287,7 +277,7 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
     for (int j = 0; j < NJ; j++) {
         const int d = (j << 7) + (lane << 2);
         uint32_t w = ptx::pack_sat_s8(x[j][0], x[j][1], x[j][2], x[j][3]);      // |x| <= 127: the saturating pack is exact, two instructions
-        *reinterpret_cast<uint32_t *>(p.x_out + (int64_t)r * H + d) = w;
+        if (MODE != 2) *reinterpret_cast<uint32_t *>(p.x_out + (int64_t)r * H + d) = w;
         tot = __dp4a((int)__vabsss4(w), 0x01010101, tot);    // sum of |x|, four at a time
     }
     // mean-abs norm with perturbed gain / bias (mgpu.cu:646-678): y = clip((x*w')/mn + b')
@@ -343,7 +333,7 @@ static int launch_rowwise_nj(cudaStream_t st, const RowParams &p) {
 int launch_rowwise(cudaStream_t st, const RowParams &p_in, int mode) {
     RowParams p = p_in;
     p.fd_seq = make_fastdiv(p.seq_len);
-    return mode == 0 ? launch_rowwise_nj<0>(st, p) : launch_rowwise_nj<1>(st, p);
+    return mode == 0 ? launch_rowwise_nj<0>(st, p) : (mode == 1 ? launch_rowwise_nj<1>(st, p) : launch_rowwise_nj<2>(st, p));
 }
 
 // Row dots under adaptive-noise overlays (d-eggs/include/model/layers.cuh:250, 272-280, 339-341, 396):

@@ -50,13 +50,13 @@ struct RowParams {
     int M, H, seq_len;
     FastDiv fd_seq;              // seq_len as a multiply-shift divisor (filled by launch_rowwise)
     const int8_t *nt; int64_t nt_stride;
-    // source: embedding (mode 0) or adaptive layer normalise of pre32 (mode 1)
+    // source: embedding (mode 0), adaptive layer normalise of pre32 (mode 1), or the finished int8 stream (mode 2)
     const uint8_t *dataset; int64_t data_len, start_idx, data_stride; int pop_base, use_same_data;
     const int8_t *emb_packed; const int8_t *emb_bias; int vocab;
     int nt_emb_a, nt_emb_b, nt_emb_bias_d, emb_shift;
     const int8_t *ov_emb_row, *ov_emb_col;   // adaptive-noise overlays of the embedding ([vocab], [H]) or null
     const int32_t *pre32; int32_t *rowmax;
-    // residual stream out
+    // residual stream out (modes 0, 1); in mode 2 the residual stream is final already and is only read, from x_out
     int8_t *x_out;
     // mean-abs norm (apply_standard_norm, mgpu.cu:646-678)
     int nt_w_m, nt_b_m;          // perturbed gain / bias tables (int16 [2][H])
@@ -119,6 +119,14 @@ int launch_generate(cudaStream_t st, const GenParams &p);
 // ---- weights ----------------------------------------------------------------
 // packed [K/4][N][4] -> K-major shadow [N][K]
 int launch_unpack_transpose(cudaStream_t st, const int8_t *packed, int8_t *shadow, int rows_k, int cols_n);
+
+// ---- row-owning GEMM with the adaptive normalisation fused (egg_gemm_fused.cuh) -----
+struct FusedParams;
+// mode: FUSED_QKV (out = [3][part_rows][H] int8: q, k, v) or FUSED_RES (out = x [M][H] int8, resid = x, may alias out)
+int launch_gemm_fused(cudaStream_t st, int mode, const int8_t *A, const int8_t *B, int8_t *out, const int8_t *resid,
+                      const FusedParams &p, int num_sms);
+// whether the row-owning kernels can run a configuration (whole tiles inside one member, a row fits tensor memory)
+inline bool fused_supported(int hidden, int seq_len) { return seq_len % 128 == 0 && hidden % 128 == 0 && hidden <= 512; }
 
 // ---- GEMM -------------------------------------------------------------------
 // A: [M][K] int8 row-major, B: [N][K] int8 row-major (both device pointers).

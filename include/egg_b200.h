@@ -249,8 +249,8 @@ int egg_update_reconstruct(egg_ctx *ctx, const int32_t *fitness, int pairs,
  * split = 1 selects the two-digit operand form for int8 fitness (needs
  * 16 * noise magnitude <= 127).  Nothing is read back to check the promise.
  *
- * The first call on a device looks up the buffer's device address; make that first
- * call outside any stream capture.  All calls share the buffer and it keeps the last
+ * The buffer's device address is looked up once per device, in egg_ctx_create (with
+ * that device current); create the context outside any stream capture.  All calls share the buffer and it keeps the last
  * call's operands; every call rewrites the whole region it uses (zero padding
  * included), so nothing has to be cleared, but two calls that overlap on the GPU
  * (different contexts or streams on one device) race on it.
@@ -382,6 +382,17 @@ const char *egg_profile_name(int cls);
 int64_t egg_launch_count(egg_ctx *ctx);
 /* Members evaluated per internal wave (chosen at creation). */
 int egg_wave_members(egg_ctx *ctx);
+/*
+ * The projections that feed an adaptive normalisation (Q/K/V -> adaptive_qkv_normalize, O and MLP-down ->
+ * adaptive_layer_normalize; egg_adaptive_normalize.h:10-103, called at mgpu.cu:782-784, 756, 830) run as
+ * row-owning kernels that keep a whole output row in tensor memory and write the requantised int8 row
+ * directly, whenever hidden_dim <= 512 and seq_len % 128 == 0; other shapes take the two-kernel form
+ * (int32 pre-activations + row maxima, then a requantisation kernel).  Both forms give identical bytes.
+ * enable = 0 forces the two-kernel form (for A/B timing and for tests that compare the two); no counterpart
+ * in the reference.  egg_fused_epilogues_active tells which form this context's evaluations take.
+ */
+int egg_set_fused_epilogues(egg_ctx *ctx, int enable);
+int egg_fused_epilogues_active(egg_ctx *ctx);
 /*
  * Measures what the tensor-core loop of the projection GEMM sustains by itself on this GPU: the same
  * kernel (TMA loads, tcgen05.mma kind::i8, two TMEM accumulator stages) with an epilogue that drops the

@@ -892,21 +892,72 @@ uint64_t oracle_update_scaled(const egg_config *c, int8_t *model, void *opt_stat
 void oracle_projection(const egg_config *cfg, const int8_t *x, const int8_t *w_packed, int8_t *y, int64_t rows,
                        int K, int N, int rows_per_member, uint32_t seed, int off_a, int off_b, int rank1_shift,
                        int out_shift) {
+    /* the packed [K/4][N][4] weights once as [N][K] so that the inner sums run over contiguous bytes; the noise
+     * vectors of a pair once per row (they are functions of the pair only) */
+    int8_t *wt = (int8_t *)malloc((size_t)K * N);
+    for (int n = 0; n < N; n++)
+        for (int k = 0; k < K; k++) wt[(int64_t)n * K + k] = (int8_t)wq(w_packed, k, n, N);
+#pragma omp parallel
+    {
+        int8_t *nb = (int8_t *)malloc((size_t)K), *na = (int8_t *)malloc((size_t)N);
+#pragma omp for schedule(static)
+        for (int64_t r = 0; r < rows; r++) {
+            int64_t member = r / rows_per_member;
+            uint32_t s = seed + (uint32_t)(member / 2);
+            int ns = (member % 2 == 0) ? 1 : -1;
+            const int8_t *xr = x + r * K;
+            for (int k = 0; k < K; k++) nb[k] = (int8_t)oracle_noise(cfg, s + (uint32_t)off_b, (uint32_t)k);
+            for (int n = 0; n < N; n++) na[n] = (int8_t)oracle_noise(cfg, s + (uint32_t)off_a, (uint32_t)n);
+            int32_t xb = 0;
+            for (int k = 0; k < K; k++) xb += (int32_t)xr[k] * nb[k];
+            for (int n = 0; n < N; n++) {
+                const int8_t *wn = wt + (int64_t)n * K;
+                int32_t acc = 0;
+                for (int k = 0; k < K; k++) acc += (int32_t)xr[k] * wn[k];
+                acc += ((xb * (int32_t)na[n]) * ns) >> rank1_shift;
+                y[r * N + n] = (int8_t)clip8(acc >> out_shift);
+            }
+        }
+        free(nb); free(na);
+    }
+    free(wt);
+}
+
+/* Votes of selected output columns n of one matrix (mgpu.cu:1085-1098): out[i][k] = Σ_p f_p · A_p[n_i] · B_p[k].
+ * The whole vote matrix of a 4096 x 4096 weight with 32 768 pairs is 5.5e11 terms; a sample of columns is what a
+ * CPU can check. */
+void oracle_vote_columns(const egg_config *cfg, const int32_t *fitness, int pairs, int rows_k, int off_a, int off_b,
+                         int seed_base, uint32_t step_seed, const int32_t *n_list, int n_count, int32_t *out) {
+    int8_t *B = (int8_t *)malloc((size_t)pairs * rows_k);
+    int32_t *FA = (int32_t *)malloc(sizeof(int32_t) * (size_t)pairs * n_count);
 #pragma omp parallel for schedule(static)
-    for (int64_t r = 0; r < rows; r++) {
-        int64_t member = r / rows_per_member;
-        uint32_t s = seed + (uint32_t)(member / 2);
-        int ns = (member % 2 == 0) ? 1 : -1;
-        const int8_t *xr = x + r * K;
-        int32_t xb = 0;
-        for (int k = 0; k < K; k++) xb += (int32_t)xr[k] * oracle_noise(cfg, s + (uint32_t)off_b, (uint32_t)k);
-        for (int n = 0; n < N; n++) {
-            int32_t acc = 0;
-            for (int k = 0; k < K; k++) acc += (int32_t)xr[k] * wq(w_packed, k, n, N);
-            acc += ((xb * oracle_noise(cfg, s + (uint32_t)off_a, (uint32_t)n)) * ns) >> rank1_shift;
-            y[r * N + n] = (int8_t)clip8(acc >> out_shift);
+    for (int p = 0; p < pairs; p++) {
+        uint32_t s = step_seed + (uint32_t)p + (uint32_t)seed_base;
+        for (int k = 0; k < rows_k; k++) B[(int64_t)p * rows_k + k] = (int8_t)oracle_noise(cfg, s + (uint32_t)off_b, (uint32_t)k);
+        for (int i = 0; i < n_count; i++) FA[(int64_t)p * n_count + i] = fitness[p] * oracle_noise(cfg, s + (uint32_t)off_a, (uint32_t)n_list[i]);
+    }
+#pragma omp parallel for schedule(static)
+    for (int i = 0; i < n_count; i++) {
+        int32_t *o = out + (int64_t)i * rows_k;
+        for (int k = 0; k < rows_k; k++) o[k] = 0;
+        for (int p = 0; p < pairs; p++) {
+            int32_t fa = FA[(int64_t)p * n_count + i];
+            if (!fa) continue;
+            const int8_t *b = B + (int64_t)p * rows_k;
+            for (int k = 0; k < rows_k; k++) o[k] += fa * b[k];
         }
     }
+    free(B); free(FA);
+}
+
+/* ES-AdamW on an array of elements from their votes (update_matrix_adam_kernel's tail, mgpu.cu:1100-1110):
+ * state = AdamParam{m, v, acc} per element; returns the number of weights that changed. */
+uint64_t oracle_adam_from_votes(const egg_config *cfg, int8_t *w, float *state, const int32_t *vote, int64_t count, float lr,
+                                int fma_mode) {
+    uint64_t changed = 0;
+    for (int64_t j = 0; j < count; j++)
+        changed += (uint64_t)oracle_adam_step(cfg, &state[3 * j], &state[3 * j + 1], &state[3 * j + 2], &w[j], -(float)vote[j], lr, fma_mode);
+    return changed;
 }
 
 /* ------------------------------------------------- d-eggs per-chunk fitness */

@@ -100,6 +100,14 @@ void oracle_projection(const egg_config *cfg, const int8_t *x, const int8_t *w_p
                        int8_t *y, int64_t rows, int k_dim, int n_dim, int rows_per_member,
                        uint32_t seed, int off_a, int off_b, int rank1_shift, int out_shift);
 
+/* votes of selected output columns: out[n_count][rows_k], out[i][k] = Σ_p f_p A_p[n_list[i]] B_p[k] (mgpu.cu:1085-1098) */
+void oracle_vote_columns(const egg_config *cfg, const int32_t *fitness, int pairs, int rows_k, int off_a, int off_b,
+                         int seed_base, uint32_t step_seed, const int32_t *n_list, int n_count, int32_t *out);
+
+/* ES-AdamW over `count` elements from their votes; state = {m, v, acc} per element (mgpu.cu:1040-1064, 1100-1110) */
+uint64_t oracle_adam_from_votes(const egg_config *cfg, int8_t *w, float *state, const int32_t *vote, int64_t count, float lr,
+                                int fma_mode);
+
 /* --- d-eggs worker host fitness (d-eggs/src/worker.cu:635-687). Parity unpinned: the reference
  * has this code inline in main(), it cannot be called; restated by reading. --- */
 void oracle_deggs_chunk_fitness(const int32_t *losses, int count, int mean_filter, double exponent, int adaptive,

@@ -87,8 +87,6 @@ def lib():
         L.oracle_repack_matrix.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int]
         L.oracle_eval.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                                   C.c_uint32, C.c_int, C.c_int, C.c_void_p]
-        L.oracle_eval_trace.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
-                                        C.c_uint32, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         L.oracle_fitness.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         L.oracle_generate.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_uint32, C.c_float, C.c_float, C.c_float]
         L.oracle_update.restype = C.c_uint64
@@ -97,6 +95,10 @@ def lib():
         L.oracle_update_scaled.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_float, C.c_int, C.c_void_p]
         L.oracle_vote_matrix.argtypes = [cfgp, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                          C.c_int, C.c_uint32, C.c_void_p]
+        L.oracle_vote_columns.argtypes = [cfgp, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_void_p,
+                                          C.c_int, C.c_void_p]
+        L.oracle_adam_from_votes.restype = C.c_uint64
+        L.oracle_adam_from_votes.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_int]
         L.oracle_newton_schulz.argtypes = [C.c_void_p, C.c_int, C.c_int]
         L.oracle_projection.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int,
                                         C.c_int, C.c_uint32, C.c_int, C.c_int, C.c_int, C.c_int]
@@ -160,15 +162,6 @@ def eval_losses(cfg, model, dataset, start_idx, step_seed, pop_offset, count, sc
     return out
 
 
-def eval_trace(cfg, model, dataset, start_idx, step_seed, member, scales=None):
-    x = np.zeros((cfg.seq_len, 3 + 2 * cfg.n_layers, cfg.hidden_dim), np.int8)
-    lg = np.zeros((cfg.seq_len, cfg.vocab_size), np.int32)
-    loss = np.zeros(1, np.int32)
-    lib().oracle_eval_trace(C.byref(cfg), _p(model), _p(scales), _p(dataset), len(dataset), start_idx,
-                            step_seed & 0xFFFFFFFF, member, _p(x), _p(lg), _p(loss))
-    return x, lg, int(loss[0])
-
-
 def fitness(losses):
     f = np.zeros(len(losses) // 2, np.int32)
     lib().oracle_fitness(_p(np.ascontiguousarray(losses, np.int32)), _p(f), len(f))
@@ -198,6 +191,22 @@ def vote_matrix(cfg, fit, rows_k, cols_n, off_a, off_b, seed_base, step_seed):
     lib().oracle_vote_matrix(C.byref(cfg), _p(fit), len(fit), rows_k, cols_n, off_a, off_b, seed_base,
                              step_seed & 0xFFFFFFFF, _p(v))
     return v
+
+
+def vote_columns(cfg, fit, rows_k, off_a, off_b, seed_base, step_seed, n_list):
+    """Votes of the output columns n_list of one matrix: array [len(n_list)][rows_k]."""
+    fit = np.ascontiguousarray(fit, np.int32)
+    n_list = np.ascontiguousarray(n_list, np.int32)
+    out = np.zeros((len(n_list), rows_k), np.int32)
+    lib().oracle_vote_columns(C.byref(cfg), _p(fit), len(fit), rows_k, off_a, off_b, seed_base, step_seed & 0xFFFFFFFF,
+                              _p(n_list), len(n_list), _p(out))
+    return out
+
+
+def adam_from_votes(cfg, w, state, vote, lr, fma_mode=FMA_NVCC):
+    """In place on w (int8) and state (float32 [n][3]); returns the number of changed weights."""
+    vote = np.ascontiguousarray(vote, np.int32)
+    return int(lib().oracle_adam_from_votes(C.byref(cfg), _p(w), _p(state), _p(vote), vote.size, C.c_float(lr), fma_mode))
 
 
 def newton_schulz(x):

@@ -74,3 +74,29 @@ def test_gru_against_reference_cpu_trainer_run_here():
     assert (r["states"] == ref["states"]).all()
     assert (r["model"] == ref["model"]).all()
     assert (r["model"] != model0).any()
+
+
+def test_gru_full_generation_matches_reference_golden():
+    """One whole generation of full_trained_egg.c at its compiled-in size -- 128 members x 4096 tokens, fitness, the
+    25 threshold-vote matrix updates (full_trained_egg.c:527-577) -- against what the reference's own code produced
+    on the CPU (tests/golden/ref_cpu_gru_full.npz, written by tests/golden/make_golden.py gru; minutes of CPU time,
+    hence a committed fixture)."""
+    import os
+    import zlib
+    from common import ROOT
+    pkg, O = load_pkg(), load_oracle()
+    from egg_c_b200 import synth
+    g = np.load(os.path.join(ROOT, "tests", "golden", "ref_cpu_gru_full.npz"))
+    ocfg = O.make_gru_config()
+    model0 = synth.uniform_int8(0, O.gru_model_bytes(ocfg))
+    data = synth.zipf_bytes(1, 1 << 20)
+    r = _run_generations(pkg, O, {}, ocfg.seq_len, 1, model0, data, [(SEED, 0)], check_oracle=False)
+    losses, fit = r["gens"][0]
+    assert (losses == g["losses"]).all(), "%d of 128 losses differ" % (losses != g["losses"]).sum()
+    assert (fit == g["fitness"]).all()
+    changed = np.nonzero(r["model"] != model0)[0]
+    assert len(changed) == int(g["changed_count"]) and len(changed) > 0
+    assert (changed[:4096] == g["changed_idx"]).all() and (r["model"][changed[:4096]] == g["changed_val"]).all()
+    assert zlib.crc32(r["model"].tobytes()) == int(g["model_crc"])
+    assert (r["states"][:2048] == g["states_head"]).all()
+    assert zlib.crc32(r["states"].tobytes()) == int(g["states_crc"])

@@ -2,6 +2,7 @@
 against the reference's own protocol.h / ternary_pack.h outputs and against the oracle."""
 import json
 import os
+import sys
 
 import numpy as np
 import pytest
@@ -78,3 +79,36 @@ def test_seed_chain_is_the_reference_hash():
     for s, i, h in KAT["hash_rng"]:
         assert pkg.next_seed(s, i) == h
     assert pkg.next_seed(42, 1) == O.hash_rng(42, 1)
+
+
+def test_chunk_fitness_matches_reference_worker_lines():
+    """The library and the oracle against d-eggs/src/worker.cu:635-687 itself: those lines, cut by line range and
+    compiled unmodified into oracle/_ref/ref_worker_fitness, produced tests/golden/ref_worker_fitness.json
+    (tests/golden/make_golden.py worker); where the binary is present it is also run live on fresh vectors."""
+    import json
+    import subprocess
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    import make_golden
+    pkg, O = load_pkg(), load_oracle()
+    gold = json.load(open(os.path.join(ROOT, "tests", "golden", "ref_worker_fitness.json")))
+    vectors = make_golden.worker_vectors()
+    assert len(gold["cases"]) == 4 * len(vectors)
+    for case in gold["cases"]:
+        losses = vectors[case["vector"]]
+        bits = np.unpackbits(np.array(case["fitness_packed"], np.uint8))[:2 * case["pairs"]].reshape(-1, 2)
+        want = (bits[:, 0] * 2 + bits[:, 1]).astype(np.int32) - 1
+        for impl in (pkg, O):
+            got, sl = impl.deggs_chunk_fitness(losses, case["mean_filter"], 1.2, case["adaptive"], 0.1)
+            assert sl == case["sum_loss"]
+            assert (got == want).all(), (case["vector"], case["mean_filter"], case["adaptive"])
+    exe = os.path.join(ROOT, "oracle", "_ref", "ref_worker_fitness")
+    if os.path.exists(exe):
+        rng = np.random.default_rng(123)
+        for n in (2, 6, 1000, 4096):
+            losses = rng.integers(-50000, 50000, n).astype(np.int32)
+            for mf in (0, 1):
+                for ad in (0, 1):
+                    r = subprocess.run([exe, str(mf), str(ad)], input=" ".join(str(int(x)) for x in losses), capture_output=True, text=True, check=True)
+                    o = json.loads(r.stdout)
+                    got, sl = pkg.deggs_chunk_fitness(losses, mf, 1.2, ad, 0.1)
+                    assert sl == o["sum_loss"] and got.tolist() == o["fitness"]
