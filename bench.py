@@ -349,7 +349,74 @@ def run_c3(args, pkg, synth, torch, real_stdout, peaks):
 
 
 def run_c4(args, pkg, synth, torch, real_stdout, peaks):
-    raise SystemExit("workload c4 needs the isolated matrix-update entry point")
+    """Isolated update of a 4096 x 4096 weight from 65 536 members (32 768 pairs, int8 rank-normalised fitness, noise in
+    [-3, 3] regenerated from the counter hash): one step = the whole ES-AdamW update (operands, vote GEMM, element step)
+    followed by the whole Muon update (operands, vote GEMM, momentum, 5 Newton-Schulz iterations, quantised apply)."""
+    R = Cn = 4096
+    pairs = 32768
+    cfg = pkg.default_config(device_mask=3, population_size=2 * pairs, use_muon=1)
+    ctx = pkg.Context(cfg, 0, 2)
+    rng = np.random.RandomState(2)
+    rank = np.argsort(np.argsort(rng.randn(pairs)))
+    fit = np.clip(np.round(rank / (pairs - 1) * 254.0 - 127.0), -127, 127).astype(np.int32)
+    w0 = synth.uniform_int8(0, R * Cn)
+    d_w = torch.from_numpy(w0.copy()).cuda()
+    d_adam = torch.zeros(R * Cn * 3, dtype=torch.float32, device="cuda")
+    d_muon = torch.zeros(R * Cn * 2, dtype=torch.float32, device="cuda")
+    d_fit = torch.from_numpy(fit).cuda()
+    fit_host = torch.from_numpy(fit).pin_memory()
+    torch.cuda.synchronize()
+    seed = [2]
+
+    def step(host):
+        if host:
+            d_fit.copy_(fit_host, non_blocking=False)
+        seed[0] += 1
+        n1 = ctx.update_matrix(d_w.data_ptr(), d_adam.data_ptr(), R, Cn, 402, 403, 1000, d_fit.data_ptr(), pairs, seed[0], LR, optimizer=0, split=True)
+        n2 = ctx.update_matrix(d_w.data_ptr(), d_muon.data_ptr(), R, Cn, 402, 403, 1000, d_fit.data_ptr(), pairs, seed[0], LR, optimizer=1, split=True)
+        return n1 + n2
+
+    n_warm = max(args.warmup, 3)
+    for _ in range(n_warm):
+        step(False)
+    l0 = ctx.launch_count()
+    ctx.profile_enable(True); ctx.profile_read()
+    sampler = ClockSampler(0); sampler.start()
+    ctx.timer_start()
+    for _ in range(args.steps):
+        step(False)
+    ms = ctx.timer_stop() / args.steps
+    clocks = sampler.stop()
+    prof = ctx.profile_read(); ctx.profile_enable(False)
+    launches = ctx.launch_count() - l0
+    ctx.timer_start()
+    for _ in range(args.steps):
+        step(True)
+    ms_e2e = ctx.timer_stop() / args.steps
+    k = {n: v[0] / args.steps for n, v in prof.items() if v[1] > 0}
+    vote_ops = 2.0 * R * Cn * pairs                         # algorithmic ops of ONE reconstruction (two per step)
+    gemm_ms = k.get("update_gemm", 0.0) / 2.0
+    achieved = vote_ops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else None
+    ns_flop = 5.0 * 2 * 2 * float(R) * R * Cn                # 5 iterations x (Gram + product), 2*K*K*L flop each
+    line = {"metric": "member_updates_per_sec", "value": 2 * pairs / (ms / 1e3), "unit": "members/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": n_warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8/int32 votes, fp32 optimiser", "data": "synthetic",
+            "config": {"workload": "c4: isolated update of a 4096x4096 weight, 65536 members = 32768 pairs, int8 rank-normalised fitness (two-digit "
+                                   "operand split: executed contraction 65536), noise in [-3,3]; step = ES-AdamW update + Muon update (5 Newton-Schulz)",
+                       "l2_policy": "operands (2 x 268 MB) and votes (64 MiB) exceed L2 together"},
+            "e2e": {"value": 2 * pairs / (ms_e2e / 1e3), "unit": "members/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": int(pairs * 4),
+                    "d2h_bytes_per_step": 16},
+            "gpu_launches": int(launches),
+            "roofline": {"kernel": "gemm_i8_kernel<EPI_VOTE> (vote reconstruction)", "bound": "tensor", "achieved": achieved, "peak": peaks["tensor"],
+                         "unit": "TFLOP/s", "frac": (achieved / peaks["tensor"]) if achieved else None, "traffic": None,
+                         "peak_source": peaks["tensor_source"],
+                         "note": "algorithmic ops 2*4096*4096*32768 per reconstruction; the operand split executes twice that"},
+            "kernels_ms_per_step": k,
+            "newton_schulz": {"ms": k.get("muon", 0.0), "tflops_fp32": ns_flop / (k["muon"] / 1e3) / 1e12 if k.get("muon") else None,
+                              "note": "5 iterations of G = X X^T, X <- 0.5 (3I - G) X in fp32 FFMA, plus normalise and quantised apply"},
+            "clocks": clocks, "cpu_baseline": None}
+    real_stdout.write(json.dumps(line) + "\n"); real_stdout.flush()
+    ctx.close()
 
 
 def run_c5slice(args, pkg, synth, torch, real_stdout, peaks):

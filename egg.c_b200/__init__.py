@@ -20,7 +20,7 @@ EXPORTS = [
     "egg_ctx_destroy", "egg_last_error", "egg_sync", "egg_upload_model", "egg_download_model", "egg_upload_opt_state",
     "egg_download_opt_state", "egg_set_dataset", "egg_eval_chunk", "egg_read_losses", "egg_compute_fitness_pairs",
     "egg_write_fitness", "egg_read_fitness", "egg_nccl_unique_id", "egg_comm_init", "egg_allgather_fitness",
-    "egg_apply_update", "egg_generation_host", "egg_perturbed_projection", "egg_update_reconstruct",
+    "egg_apply_update", "egg_generation_host", "egg_perturbed_projection", "egg_update_reconstruct", "egg_update_matrix",
     "egg_update_reconstruct_noalloc", "egg_scales_bytes", "egg_upload_scales", "egg_download_scales", "egg_set_overlay_steps",
     "egg_timer_start", "egg_timer_stop", "egg_profile_enable", "egg_profile_read", "egg_profile_name", "egg_launch_count",
     "egg_wave_members", "egg_set_fused_epilogues", "egg_fused_epilogues_active", "egg_measure_int8_peak", "egg_selftest_index_math", "egg_generate", "egg_save_checkpoint", "egg_load_checkpoint", "egg_wire_fixed_bytes", "egg_wire_encode", "egg_wire_decode_header", "egg_wire_decode_body",
@@ -28,8 +28,10 @@ EXPORTS = [
     "egg_gru_config_defaults", "egg_gru_model_bytes", "egg_gru_state_bytes", "egg_gru_create", "egg_gru_destroy",
     "egg_gru_upload_model", "egg_gru_download_model", "egg_gru_upload_states", "egg_gru_download_states", "egg_gru_set_dataset",
     "egg_gru_generation", "egg_gru_launch_count",
+    "egg_learning_rate", "egg_worker_options_defaults", "egg_worker_run", "egg_worker_engine_from_ctx", "egg_get_config",
+    "egg_log_open", "egg_log_record", "egg_log_close",
 ]
-EGG_PROF_N = 15
+EGG_PROF_N = 16
 
 
 class EggConfig(C.Structure):
@@ -55,6 +57,32 @@ class WireMsg(C.Structure):
     """struct egg_wire_msg."""
     _fields_ = [("opcode", C.c_int32), ("payload_size", C.c_uint32), ("seed", C.c_uint64), ("last_step", C.c_uint64),
                 ("data_position", C.c_uint64), ("updates_count", C.c_uint64), ("sum_loss", C.c_int64)]
+
+
+EVAL_CHUNK_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_uint32, C.c_int64, C.c_int, C.c_int, C.POINTER(C.c_int32))
+APPLY_UPDATE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_uint32, C.c_float, C.c_float, C.POINTER(C.c_uint64))
+GENERATE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int64, C.c_uint32, C.c_char_p, C.c_int)
+BEFORE_RESULT_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int64, C.c_int)
+
+
+class WorkerEngine(C.Structure):
+    """Mirror of struct egg_worker_engine."""
+    _fields_ = [("self", C.c_void_p), ("eval_chunk", EVAL_CHUNK_FN), ("apply_update", APPLY_UPDATE_FN), ("generate", GENERATE_FN)]
+
+
+class WorkerOptions(C.Structure):
+    """Mirror of struct egg_worker_options."""
+    _fields_ = [("host", C.c_char * 64), ("port", C.c_int), ("population_size", C.c_int), ("chunk_size", C.c_int),
+                ("initial_seed", C.c_uint64), ("wait_sleep_ms", C.c_int), ("recv_timeout_ms", C.c_int), ("generate_every", C.c_int),
+                ("mean_filter", C.c_int), ("mean_exponent", C.c_double), ("adaptive_threshold", C.c_int), ("threshold_alpha", C.c_double),
+                ("stop_at_step", C.c_int64), ("max_requests", C.c_int64), ("stop_flag", C.POINTER(C.c_int)),
+                ("before_result", BEFORE_RESULT_FN), ("hook_self", C.c_void_p)]
+
+
+class WorkerStats(C.Structure):
+    """Mirror of struct egg_worker_stats."""
+    _fields_ = [(n, C.c_uint64) for n in ("requests", "chunks_done", "updates_applied", "waits", "results_dropped", "bytes_sent",
+                                          "bytes_received", "final_step", "final_seed")]
 
 
 class EggError(RuntimeError):
@@ -134,6 +162,8 @@ def lib():
         L.egg_perturbed_projection.argtypes = [vp, vp, vp, vp, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_int,
                                                C.c_int, C.c_int, C.c_int, C.c_int]
         L.egg_update_reconstruct.argtypes = [vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint32, vp, C.c_int]
+        L.egg_update_matrix.argtypes = [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, C.c_int, C.c_uint32, C.c_float, C.c_int,
+                                        C.c_int, P(C.c_uint64)]
         L.egg_update_reconstruct_noalloc.argtypes = [vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_int, vp]
         L.egg_timer_start.argtypes = [vp]
         L.egg_timer_stop.argtypes = [vp, P(C.c_float)]
@@ -146,6 +176,17 @@ def lib():
         L.egg_wave_members.argtypes = [vp]
         L.egg_set_fused_epilogues.argtypes = [vp, C.c_int]
         L.egg_fused_epilogues_active.argtypes = [vp]
+        L.egg_learning_rate.argtypes = [C.c_int64]
+        L.egg_learning_rate.restype = C.c_float
+        L.egg_worker_options_defaults.argtypes = [P(WorkerOptions)]
+        L.egg_worker_options_defaults.restype = None
+        L.egg_worker_run.argtypes = [P(WorkerOptions), P(WorkerEngine), P(WorkerStats)]
+        L.egg_worker_engine_from_ctx.argtypes = [vp, P(WorkerEngine)]
+        L.egg_get_config.argtypes = [vp, P(EggConfig)]
+        L.egg_log_open.argtypes = [C.c_char_p, P(EggConfig), C.c_int, C.c_uint64, P(vp)]
+        L.egg_log_record.argtypes = [vp, C.c_int64, C.c_double, C.c_uint64, C.c_float]
+        L.egg_log_close.argtypes = [vp]
+        L.egg_log_close.restype = None
         L.egg_wire_fixed_bytes.argtypes = [C.c_int]
         L.egg_wire_encode.argtypes = [P(WireMsg), vp, C.c_int]
         L.egg_wire_decode_header.argtypes = [vp, P(C.c_int), P(C.c_uint32)]
@@ -352,6 +393,15 @@ class Context:
                                             step_seed & 0xFFFFFFFF, _ptr(vote_out), 1 if on_device else 0))
 
 
+    def update_matrix(self, d_w_packed, d_opt_state, rows_k, cols_n, off_a, off_b, seed_base, d_fitness, pairs, step_seed, lr,
+                      optimizer=0, split=False):
+        """Device pointers; one AdamW (optimizer 0) or Muon (1) update of one matrix in place. Returns the number of changed weights."""
+        n = C.c_uint64(0)
+        _check(lib().egg_update_matrix(self._h, _ptr(d_w_packed), _ptr(d_opt_state), rows_k, cols_n, off_a, off_b, seed_base,
+                                       _ptr(d_fitness), pairs, step_seed & 0xFFFFFFFF, C.c_float(lr), optimizer, 1 if split else 0,
+                                       C.byref(n)))
+        return n.value
+
     def update_reconstruct_noalloc(self, d_fitness, pairs, rows_k, cols_n, off_a, off_b, seed_base, step_seed, split, d_vote_out):
         """Device pointers in and out; uses the library's built-in operand buffer, allocates nothing."""
         _check(lib().egg_update_reconstruct_noalloc(self._h, _ptr(d_fitness), pairs, rows_k, cols_n, off_a, off_b, seed_base,
@@ -442,6 +492,50 @@ def deggs_chunk_fitness(losses, mean_filter=1, exponent=1.2, adaptive=1, alpha=0
 
 def next_seed(seed, step):
     return lib().egg_next_seed(seed & 0xFFFFFFFF, step)
+
+
+def learning_rate(step):
+    return float(lib().egg_learning_rate(step))
+
+
+def worker_options(**kw):
+    o = WorkerOptions()
+    lib().egg_worker_options_defaults(C.byref(o))
+    for k, v in kw.items():
+        if k == "host":
+            v = v.encode()
+        setattr(o, k, v)
+    return o
+
+
+def worker_run(options, engine):
+    """Runs the d-eggs worker loop until one of its stop conditions; returns (return code, WorkerStats).  The call
+    releases the GIL, so several workers can run in threads of one process; callbacks of a Python engine take it back."""
+    st = WorkerStats()
+    rc = lib().egg_worker_run(C.byref(options), C.byref(engine), C.byref(st))
+    return rc, st
+
+
+def worker_engine_from_ctx(ctx):
+    e = WorkerEngine()
+    _check(lib().egg_worker_engine_from_ctx(ctx._h, C.byref(e)))
+    return e
+
+
+class RunLog:
+    """The reference's plain-text run log (header block + Step,RelTime,Loss,Updates,LR rows); no remote posting."""
+
+    def __init__(self, path, cfg, num_gpus=1, vram_bytes_per_gpu=0):
+        self._h = C.c_void_p()
+        _check(lib().egg_log_open(path.encode(), C.byref(cfg), num_gpus, vram_bytes_per_gpu, C.byref(self._h)))
+
+    def record(self, step, loss, updates, lr):
+        _check(lib().egg_log_record(self._h, step, float(loss), int(updates), C.c_float(lr)))
+
+    def close(self):
+        if self._h:
+            lib().egg_log_close(self._h)
+            self._h = C.c_void_p()
 
 
 class GruContext:

@@ -104,6 +104,7 @@ struct egg_ctx {
     int8_t *d_nt = nullptr;
     // update scratch
     int8_t *d_na = nullptr, *d_nb = nullptr;
+    int32_t *d_votes = nullptr;         // partial vote matrices of the matrix being updated: [splits][rows*cols]
     int kp = 0;
     MuonWs muon = {nullptr, nullptr, nullptr, nullptr};
     unsigned long long *d_updates = nullptr;
@@ -317,7 +318,7 @@ extern "C" void egg_ctx_destroy(egg_ctx *c) {
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
     void *ptrs[] = {c->d_model, c->d_opt, c->d_shadow, c->d_exp_lut, c->d_rope_lut, c->d_rope_t, c->d_act_lut, c->d_data, c->d_loss, c->d_fit,
                     c->d_x, c->d_h, c->d_u, c->d_q, c->d_ao, c->d_pre, c->d_xb, c->d_xb2, c->d_rowmax,
-                    c->d_rowmax3, c->d_xbo, c->d_wave_loss, c->d_segs, c->d_nt, c->d_na, c->d_nb, c->muon.x, c->muon.g,
+                    c->d_rowmax3, c->d_xbo, c->d_wave_loss, c->d_segs, c->d_nt, c->d_na, c->d_nb, c->d_votes, c->muon.x, c->muon.g,
                     c->muon.y, c->muon.norm2, c->d_updates, c->d_err, c->d_scales, c->d_ch_in, c->d_ch_out};
     for (void *p : ptrs) if (p) cudaFree(p);
     for (cudaEvent_t e : c->prof_ev) cudaEventDestroy(e);
@@ -427,6 +428,15 @@ extern "C" int egg_ctx_create(const egg_config *cfg, int device, int wave_member
     // update scratch
     c->kp = (int)(((POP / 2) + 127) / 128 * 128);
     TRY(dev_alloc(&c->d_na, 4 * H * (int64_t)c->kp)); TRY(dev_alloc(&c->d_nb, 4 * H * (int64_t)c->kp));
+    {
+        int64_t vmax = 0;
+        for (const ParamDesc &d : c->params) {
+            if (!d.rows_k) continue;
+            const int64_t n = (int64_t)d.rows_k * d.cols_n * vote_gemm_splits(d.rows_k, d.cols_n, c->kp, c->num_sms);
+            if (n > vmax) vmax = n;
+        }
+        TRY(dev_alloc(&c->d_votes, vmax));
+    }
     if (cfg->use_muon) {
         TRY(dev_alloc(&c->muon.x, 4 * H * H)); TRY(dev_alloc(&c->muon.y, 4 * H * H)); TRY(dev_alloc(&c->muon.g, H * H));
         TRY(dev_alloc(&c->muon.norm2, 1));
@@ -928,33 +938,57 @@ extern "C" int egg_allgather_fitness(egg_ctx *c) {
 
 // ---------------------------------------------------------------- update
 
-static int update_matrix(egg_ctx *c, const ParamDesc &d, uint32_t step_seed, float lr) {
+// One matrix: operands -> vote GEMM (pair index split over the GPU) -> optimiser step from the votes.
+// Shared by the model update and by the isolated entry point; all pointers are device pointers.
+struct MatrixUpdate {
+    int8_t *w_packed; float *opt;
+    int rows_k, cols_n, off_a, off_b, seed_base;
+    const int32_t *fit; int pairs, kp, operand_split;
+    int8_t *na, *nb; int32_t *votes;
+    float lr; int muon;
+    uint8_t *ch_in, *ch_out;
+};
+
+static int run_matrix_update(egg_ctx *c, const MatrixUpdate &u, uint32_t step_seed) {
     const egg_config &cf = c->cfg;
-    const int pairs = cf.population_size / 2;
-    int rc = PROF(EGG_PROF_UPD_OPERANDS, launch_update_operands(c->stream, c->d_na, c->d_nb, c->d_fit, pairs, c->kp, d.rows_k, d.cols_n, d.off_a, d.off_b,
-                                    d.seed_base, step_seed, cf.device_mask, cf.device_gaussian, 0));
+    int rc = PROF(EGG_PROF_UPD_OPERANDS, launch_update_operands(c->stream, u.na, u.nb, u.fit, u.pairs, u.kp, u.rows_k, u.cols_n, u.off_a, u.off_b,
+                                    u.seed_base, step_seed, cf.device_mask, cf.device_gaussian, u.operand_split));
     if (rc) return rc;
+    const int ktot = u.operand_split ? 2 * u.kp : u.kp;
+    const int splits = vote_gemm_splits(u.rows_k, u.cols_n, ktot, c->num_sms);
     GemmParams g;
     memset(&g, 0, sizeof(g));
-    g.M = d.cols_n; g.N = d.rows_k; g.K = c->kp; g.seq_len = 1 << 20;
-    g.w_packed = c->d_model + d.model_off;
-    g.opt = reinterpret_cast<float *>(c->d_opt + d.opt_off);
-    g.lr = lr * d.lr_scale; g.beta1 = cf.adam_beta1; g.beta2 = cf.adam_beta2; g.eps = cf.adam_eps; g.wd = cf.adam_weight_decay;
-    g.mu = cf.muon_momentum; g.total_updates = c->d_updates; g.err = c->d_err;
-    if (!d.muon) {
-        if (c->scales_on) { g.ch_in = c->d_ch_in; g.ch_out = c->d_ch_out; }
-        if ((rc = PROF(EGG_PROF_UPD_GEMM, launch_gemm(c->stream, EPI_ADAM, c->d_na, c->d_nb, g, c->num_sms)))) return rc;
-        if (!c->scales_on) return EGG_OK;
-        // UPDATE_OVERLAY of the input-index and the output-index overlay (worker.cu:445-455)
-        if ((rc = PROF(EGG_PROF_OVERLAY, launch_overlay_step(c->stream, c->d_scales + d.ov_in, c->d_ch_in, d.rows_k, c->ov_inc, c->ov_dec)))) return rc;
-        return PROF(EGG_PROF_OVERLAY, launch_overlay_step(c->stream, c->d_scales + d.ov_out, c->d_ch_out, d.cols_n, c->ov_inc, c->ov_dec));
-    }
-    g.m_rowmajor = c->muon.x;
-    if ((rc = PROF(EGG_PROF_UPD_GEMM, launch_gemm(c->stream, EPI_MUON_M, c->d_na, c->d_nb, g, c->num_sms)))) return rc;
-    if ((rc = PROFN(EGG_PROF_MUON, 12, launch_newton_schulz(c->stream, c->muon, d.rows_k, d.cols_n)))) return rc;
+    g.M = u.cols_n; g.N = u.rows_k; g.K = ktot; g.seq_len = 1 << 20;
+    g.vote_out = u.votes; g.k_splits = splits; g.split_stride = (int64_t)u.rows_k * u.cols_n; g.err = c->d_err;
+    if ((rc = PROF(EGG_PROF_UPD_GEMM, launch_gemm(c->stream, EPI_VOTE, u.na, u.nb, g, c->num_sms)))) return rc;
+    VoteApplyParams a;
+    memset(&a, 0, sizeof(a));
+    a.w_packed = u.w_packed; a.opt = u.opt; a.votes = u.votes; a.nsplits = splits; a.split_stride = g.split_stride;
+    a.rows_k = u.rows_k; a.cols_n = u.cols_n;
+    a.lr = u.lr; a.beta1 = cf.adam_beta1; a.beta2 = cf.adam_beta2; a.eps = cf.adam_eps; a.wd = cf.adam_weight_decay; a.mu = cf.muon_momentum;
+    a.total_updates = c->d_updates; a.ch_in = u.ch_in; a.ch_out = u.ch_out;
+    if (!u.muon) return PROF(EGG_PROF_UPD_APPLY, launch_adam_from_votes(c->stream, a));
+    a.m_rowmajor = c->muon.x;
+    if ((rc = PROF(EGG_PROF_UPD_APPLY, launch_muon_m_from_votes(c->stream, a)))) return rc;
+    if ((rc = PROFN(EGG_PROF_MUON, 12, launch_newton_schulz(c->stream, c->muon, u.rows_k, u.cols_n)))) return rc;
     ProfScope ps_apply(c, EGG_PROF_MUON);
-    return launch_muon_apply(c->stream, c->d_model + d.model_off, reinterpret_cast<float *>(c->d_opt + d.opt_off), c->muon.x,
-                             d.rows_k, d.cols_n, lr * cf.muon_lr_scale, cf.adam_weight_decay, c->d_updates);
+    return launch_muon_apply(c->stream, u.w_packed, u.opt, c->muon.x, u.rows_k, u.cols_n, u.lr * cf.muon_lr_scale, cf.adam_weight_decay, c->d_updates);
+}
+
+static int update_matrix(egg_ctx *c, const ParamDesc &d, uint32_t step_seed, float lr) {
+    MatrixUpdate u;
+    memset(&u, 0, sizeof(u));
+    u.w_packed = c->d_model + d.model_off; u.opt = reinterpret_cast<float *>(c->d_opt + d.opt_off);
+    u.rows_k = d.rows_k; u.cols_n = d.cols_n; u.off_a = d.off_a; u.off_b = d.off_b; u.seed_base = d.seed_base;
+    u.fit = c->d_fit; u.pairs = c->cfg.population_size / 2; u.kp = c->kp; u.operand_split = 0;
+    u.na = c->d_na; u.nb = c->d_nb; u.votes = c->d_votes;
+    u.lr = lr * d.lr_scale; u.muon = d.muon;
+    if (!d.muon && c->scales_on) { u.ch_in = c->d_ch_in; u.ch_out = c->d_ch_out; }
+    int rc = run_matrix_update(c, u, step_seed);
+    if (rc || d.muon || !c->scales_on) return rc;
+    // UPDATE_OVERLAY of the input-index and the output-index overlay (worker.cu:445-455)
+    if ((rc = PROF(EGG_PROF_OVERLAY, launch_overlay_step(c->stream, c->d_scales + d.ov_in, c->d_ch_in, d.rows_k, c->ov_inc, c->ov_dec)))) return rc;
+    return PROF(EGG_PROF_OVERLAY, launch_overlay_step(c->stream, c->d_scales + d.ov_out, c->d_ch_out, d.cols_n, c->ov_inc, c->ov_dec));
 }
 
 static int apply_update_async(egg_ctx *c, uint32_t step_seed, float lr) {
@@ -1140,6 +1174,57 @@ extern "C" int egg_update_reconstruct(egg_ctx *c, const int32_t *fitness, int pa
     return check_dev_err(c);
 }
 
+// ---------------------------------------------------------------- isolated matrix update
+
+extern "C" int egg_update_matrix(egg_ctx *c, int8_t *d_w_packed, void *d_opt_state, int rows_k, int cols_n, int off_a, int off_b,
+                                 int seed_base, const int32_t *d_fitness, int pairs, uint32_t step_seed, float lr, int optimizer,
+                                 int split, uint64_t *total_updates) {
+    if (!c || !d_w_packed || !d_opt_state || !d_fitness) { set_error("null argument"); return EGG_E_INVALID; }
+    if (pairs <= 0 || rows_k % 128 || cols_n % 128 || rows_k <= 0 || cols_n <= 0 || (optimizer != 0 && optimizer != 1)) {
+        set_error("matrix update shape or optimiser unsupported"); return EGG_E_INVALID;
+    }
+    const int amax = c->cfg.device_gaussian ? 3 * c->cfg.device_mask : c->cfg.device_mask;
+    if (split && 16 * amax > 127) { set_error("noise magnitude %d does not fit the two-digit operand split", amax); return EGG_E_INVALID; }
+    EGG_CUDA(cudaSetDevice(c->device));
+    cudaStream_t st = c->stream;
+    const int kp = (pairs + 127) / 128 * 128;
+    const int ktot = split ? 2 * kp : kp;
+    const int splits = vote_gemm_splits(rows_k, cols_n, ktot, c->num_sms);
+    MatrixUpdate u;
+    memset(&u, 0, sizeof(u));
+    MuonWs saved = c->muon, ws = {nullptr, nullptr, nullptr, nullptr};
+    int rc = EGG_OK;
+    auto cleanup = [&]() {
+        cudaStreamSynchronize(st);
+        if (u.na) cudaFree(u.na); if (u.nb) cudaFree(u.nb); if (u.votes) cudaFree(u.votes);
+        if (ws.x) cudaFree(ws.x); if (ws.y) cudaFree(ws.y); if (ws.g) cudaFree(ws.g); if (ws.norm2) cudaFree(ws.norm2);
+        c->muon = saved;
+    };
+#define UTRY(e) do { rc = (e); if (rc) { cleanup(); return rc; } } while (0)
+    UTRY(dev_alloc(&u.na, (int64_t)cols_n * ktot)); UTRY(dev_alloc(&u.nb, (int64_t)rows_k * ktot));
+    UTRY(dev_alloc(&u.votes, (int64_t)rows_k * cols_n * splits));
+    if (optimizer == 1) {
+        const int kmin = rows_k < cols_n ? rows_k : cols_n;
+        UTRY(dev_alloc(&ws.x, (int64_t)rows_k * cols_n)); UTRY(dev_alloc(&ws.y, (int64_t)rows_k * cols_n));
+        UTRY(dev_alloc(&ws.g, (int64_t)kmin * kmin)); UTRY(dev_alloc(&ws.norm2, 1));
+        c->muon = ws;
+    }
+    u.w_packed = d_w_packed; u.opt = static_cast<float *>(d_opt_state);
+    u.rows_k = rows_k; u.cols_n = cols_n; u.off_a = off_a; u.off_b = off_b; u.seed_base = seed_base;
+    u.fit = d_fitness; u.pairs = pairs; u.kp = kp; u.operand_split = split ? 1 : 0;
+    u.lr = lr; u.muon = optimizer;
+    cudaError_t e = cudaMemsetAsync(c->d_updates, 0, sizeof(unsigned long long), st);
+    if (e != cudaSuccess) { set_error("cudaMemsetAsync: %s", cudaGetErrorString(e)); cleanup(); return EGG_E_CUDA; }
+    UTRY(run_matrix_update(c, u, step_seed));
+    unsigned long long n = 0;
+    e = cudaMemcpyAsync(&n, c->d_updates, sizeof(n), cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) { set_error("cudaMemcpyAsync: %s", cudaGetErrorString(e)); cleanup(); return EGG_E_CUDA; }
+#undef UTRY
+    cleanup();
+    if (total_updates) *total_updates = n;
+    return check_dev_err(c);
+}
+
 // ---------------------------------------------------------------- allocation-free reconstruct
 
 // Operand scratch of egg_update_reconstruct_noalloc: part of the library image, one copy per GPU.
@@ -1231,7 +1316,7 @@ extern "C" int egg_profile_read(egg_ctx *c, float *ms, int64_t *launches) {
 extern "C" const char *egg_profile_name(int cls) {
     static const char *names[EGG_PROF_N] = {"noise_fill", "rowwise", "gemm_gelu", "gemm_pre32", "gemm_qkv", "gemm_head", "aqn",
                                             "attention", "fitness", "update_operands", "update_gemm", "update_vector", "muon",
-                                            "transpose", "overlay"};
+                                            "transpose", "overlay", "update_apply"};
     return (cls >= 0 && cls < EGG_PROF_N) ? names[cls] : "";
 }
 
@@ -1297,6 +1382,12 @@ extern "C" int egg_set_fused_epilogues(egg_ctx *c, int enable) {
 }
 
 extern "C" int egg_fused_epilogues_active(egg_ctx *c) { return (c && use_fused(c)) ? 1 : 0; }
+
+extern "C" int egg_get_config(egg_ctx *c, egg_config *out) {
+    if (!c || !out) { set_error("null argument"); return EGG_E_INVALID; }
+    *out = c->cfg;
+    return EGG_OK;
+}
 
 extern "C" int64_t egg_launch_count(egg_ctx *c) { return c ? c->launches : 0; }
 extern "C" int egg_wave_members(egg_ctx *c) { return c ? c->wave_members : 0; }

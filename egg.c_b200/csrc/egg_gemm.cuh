@@ -30,9 +30,8 @@ enum GemmEpi {
     EPI_PRE32 = 2,   // pre = resid + ((acc+r1)>>s) + b + vn                    -> int32 + row abs-max
     EPI_QKV = 3,     // rope(acc + r1) for q,k ; acc + r1 for v                 -> int32 + row abs-max per q/k/v
     EPI_HEAD = 4,    // logits = (acc+r1)>>s ; integer cross-entropy            -> loss[member] +=
-    EPI_ADAM = 5,    // vote tile -> ES-AdamW step on packed weights
-    EPI_MUON_M = 6,  // vote tile -> m = mu*m + vote ; row-major copy of m
-    EPI_VOTE = 7,    // vote tile -> int32 votes in packed index order
+    EPI_VOTE = 7,    // vote tile -> int32 votes in packed index order; with k_splits > 1 every split of the contraction
+                     // writes its own partial vote matrix (integer sums: any split adds up exactly)
     EPI_NULL = 8,    // accumulators are dropped: the loop of TMA loads and tcgen05 MMAs alone (peak measurement)
 };
 
@@ -69,14 +68,10 @@ struct GemmParams {
     int use_same_data;
     int softmax_scale_bit;
     int32_t *loss;               // [wave members] +=
-    // ---- update epilogues: GEMM M = cols_n (output dim), GEMM N = rows_k (input dim) ----
-    int8_t *w_packed;            // [rows_k/4][cols_n][4]
-    float *opt;                  // AdamParam{m,v,acc} or MuonParam{m,acc} per packed index
-    float *m_rowmajor;           // EPI_MUON_M: [rows_k][cols_n]
-    float lr, beta1, beta2, eps, wd, mu;
-    unsigned long long *total_updates;
-    uint8_t *ch_in, *ch_out;     // EPI_ADAM: set to 1 for every input index k / output index n with a changed weight (or null)
-    int32_t *vote_out;
+    // ---- vote epilogue: GEMM M = cols_n (output dim), GEMM N = rows_k (input dim), K = pairs ----
+    int32_t *vote_out;           // [k_splits][rows_k * cols_n] in packed index order
+    int k_splits;                // parts the contraction is cut into (0 or 1: none)
+    int64_t split_stride;        // elements between the partial vote matrices
     // ---- device error record ----
     int *err;
     int rpl;                     // -1 forces the transposed evaluation epilogue (tests); otherwise chosen from seq_len
@@ -453,8 +448,12 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_n = p.N / BN;
     const int tiles_m = (p.M + GEMM_BM - 1) / GEMM_BM;
-    const int num_tiles = tiles_m * tiles_n;
     const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
+    // the vote GEMM may cut its contraction (the pair index) into k_splits parts: work item = (split, tile)
+    const int k_splits = (EPI == EPI_VOTE && p.k_splits > 1) ? p.k_splits : 1;
+    const int kb_per = (num_kb + k_splits - 1) / k_splits;
+    const int mn_tiles = tiles_m * tiles_n;
+    const int num_tiles = mn_tiles * k_splits;
     constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
     constexpr uint32_t STAGE_BYTES = GEMM_BM * GEMM_BK + BN * GEMM_BK;
 
@@ -494,8 +493,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                int tm_ = fast_div(tile, p.fd_tiles_n), m0 = tm_ * GEMM_BM, n0 = (tile - tm_ * tiles_n) * BN;
-                for (int kb = 0; kb < num_kb; kb++, it++) {
+                const int split = (k_splits > 1) ? tile / mn_tiles : 0, mn = tile - split * mn_tiles;
+                int tm_ = fast_div(mn, p.fd_tiles_n), m0 = tm_ * GEMM_BM, n0 = (mn - tm_ * tiles_n) * BN;
+                const int kb0 = split * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+                for (int kb = kb0; kb < kb1; kb++, it++) {
                     int s = it % GEMM_STAGES;
                     uint32_t ph = (it / GEMM_STAGES) & 1;
                     if (!ptx::mbar_wait(&sm.empty[s], ph ^ 1) || sm.abort_flag) { gemm_fail(p, &sm.abort_flag, DEV_TIMEOUT_EMPTY); ok = false; break; }
@@ -521,7 +522,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 if (!ptx::mbar_wait(&sm.tmem_empty[as], aph ^ 1) || sm.abort_flag) { gemm_fail(p, &sm.abort_flag, DEV_TIMEOUT_TMEM_EMPTY); ok = false; break; }
                 ptx::tc_fence_after();
                 uint32_t d_tmem = tmem_base + (uint32_t)(as * BN);
-                for (int kb = 0; kb < num_kb; kb++, it++) {
+                const int split = (k_splits > 1) ? tile / mn_tiles : 0;
+                const int kb0 = split * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+                for (int kb = kb0; kb < kb1; kb++, it++) {
                     int s = it % GEMM_STAGES;
                     uint32_t ph = (it / GEMM_STAGES) & 1;
                     if (!ptx::mbar_wait(&sm.full[s], ph) || sm.abort_flag) { gemm_fail(p, &sm.abort_flag, DEV_TIMEOUT_FULL); ok = false; break; }
@@ -531,7 +534,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                     for (int k = 0; k < GEMM_BK / 32; k++) {
                         // +32 bytes along K inside the swizzle row = +2 in the 16-byte address field
-                        ptx::mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        ptx::mma_i8(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     }
                     ptx::mma_commit(&sm.empty[s]);
                 }
@@ -554,7 +557,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tcount++) {
             const int as = tcount & 1;
             const uint32_t aph = (tcount >> 1) & 1;
-            const int tm_ = fast_div(tile, p.fd_tiles_n), m0 = tm_ * GEMM_BM, n0 = (tile - tm_ * tiles_n) * BN;
+            const int split = (k_splits > 1) ? tile / mn_tiles : 0, mn = tile - split * mn_tiles;
+            const int tm_ = fast_div(mn, p.fd_tiles_n), m0 = tm_ * GEMM_BM, n0 = (mn - tm_ * tiles_n) * BN;
             const int r = m0 + row_in_tile;
             const bool row_ok = r < p.M;
 
@@ -820,10 +824,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             } else if (EPI == EPI_NULL) {
                 // nothing: the accumulator stage is released right away
             } else {
-                // ---------------- update epilogues: row r = output column n, tile columns = input index k ----------------
+                // ---------------- vote epilogue: row r = output column n, tile columns = input index k ----------------
                 const int n = r;
                 const int cols_n = p.M;
-                int changes = 0;
+                int32_t *vout = p.vote_out + (int64_t)split * p.split_stride;
                 for (int c = 0; c < COLS_PER; c += 32) {
                     uint32_t v[32];
                     ptx::tmem_ld32(taddr + c, v);
@@ -833,47 +837,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                     for (int q = 0; q < 8; q++) {
                         const int64_t word = (int64_t)((k0 >> 2) + q) * cols_n + n;
-                        const int64_t idx = word * 4;
-                        if (EPI == EPI_VOTE) {
-                            *reinterpret_cast<int4 *>(p.vote_out + idx) = make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                        } else if (EPI == EPI_ADAM) {
-                            uint32_t wword = *reinterpret_cast<const uint32_t *>(p.w_packed + idx);
-                            float4 *st = reinterpret_cast<float4 *>(p.opt + idx * 3);
-                            float4 s0 = st[0], s1 = st[1], s2 = st[2];
-                            float f[12] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w, s2.x, s2.y, s2.z, s2.w};
-                            uint32_t neww = 0;
-#pragma unroll
-                            for (int j = 0; j < 4; j++) {
-                                int w = (int)(int8_t)(wword >> (8 * j));
-                                float g = -(float)(int)v[4 * q + j];
-                                const int ch = adam_apply(f[3 * j], f[3 * j + 1], f[3 * j + 2], w, g, p.lr, p.beta1, p.beta2, p.eps, p.wd);
-                                changes += ch;
-                                if (ch && p.ch_in) { p.ch_in[k0 + 4 * q + j] = 1; p.ch_out[n] = 1; }   // adam.cuh:77-83
-                                neww |= (uint32_t)(w & 0xFF) << (8 * j);
-                            }
-                            *reinterpret_cast<uint32_t *>(p.w_packed + idx) = neww;
-                            st[0] = make_float4(f[0], f[1], f[2], f[3]);
-                            st[1] = make_float4(f[4], f[5], f[6], f[7]);
-                            st[2] = make_float4(f[8], f[9], f[10], f[11]);
-                        } else if (EPI == EPI_MUON_M) {
-                            float4 *st = reinterpret_cast<float4 *>(p.opt + idx * 2);
-                            float4 s0 = st[0], s1 = st[1];     // m0 acc0 m1 acc1 | m2 acc2 m3 acc3
-                            s0.x = __fmaf_rn(p.mu, s0.x, (float)(int)v[4 * q]);   // m = mu*m + vote, muon_internal.cuh:45-47
-                            s0.z = __fmaf_rn(p.mu, s0.z, (float)(int)v[4 * q + 1]);
-                            s1.x = __fmaf_rn(p.mu, s1.x, (float)(int)v[4 * q + 2]);
-                            s1.z = __fmaf_rn(p.mu, s1.z, (float)(int)v[4 * q + 3]);
-                            st[0] = s0; st[1] = s1;
-                            const int k = k0 + 4 * q;
-                            p.m_rowmajor[(int64_t)k * cols_n + n] = s0.x;        // gather, muon_internal.cuh:53-74
-                            p.m_rowmajor[(int64_t)(k + 1) * cols_n + n] = s0.z;
-                            p.m_rowmajor[(int64_t)(k + 2) * cols_n + n] = s1.x;
-                            p.m_rowmajor[(int64_t)(k + 3) * cols_n + n] = s1.z;
-                        }
+                        *reinterpret_cast<int4 *>(vout + word * 4) = make_int4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                     }
-                }
-                if (EPI == EPI_ADAM) {
-                    for (int off = 16; off > 0; off >>= 1) changes += __shfl_down_sync(0xFFFFFFFFu, changes, off);
-                    if (lane == 0 && changes > 0) atomicAdd(p.total_updates, (unsigned long long)changes);
                 }
             }
             // release the accumulator stage

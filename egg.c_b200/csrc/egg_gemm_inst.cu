@@ -42,8 +42,6 @@ int gemm_init() {
     if ((rc = set_attr_both<EPI_QKV, 1>())) return rc;
     if ((rc = set_attr<256, EPI_HEAD>())) return rc;
     if ((rc = set_attr<256, EPI_HEAD, 1>())) return rc;
-    if ((rc = set_attr_both<EPI_ADAM>())) return rc;
-    if ((rc = set_attr_both<EPI_MUON_M>())) return rc;
     if ((rc = set_attr_both<EPI_VOTE>())) return rc;
     if ((rc = set_attr<256, EPI_NULL>())) return rc;
     EGG_CUDA(cudaFuncSetAttribute(gemm_fused_kernel<256, FUSED_QKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_smem_bytes<256>()));
@@ -147,7 +145,7 @@ int launch_gemm_fused(cudaStream_t st, int mode, const int8_t *A, const int8_t *
 
 template <int BN, int EPI, int RPL = 0>
 static int launch_one(cudaStream_t st, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to, const GemmParams &p, int num_sms) {
-    int tiles = ((p.M + GEMM_BM - 1) / GEMM_BM) * (p.N / BN);
+    int tiles = ((p.M + GEMM_BM - 1) / GEMM_BM) * (p.N / BN) * ((EPI == EPI_VOTE && p.k_splits > 1) ? p.k_splits : 1);
     int grid = tiles < num_sms ? tiles : num_sms;
     CUtensorMap tr = ta;       // residual bytes as 64-column x 32-row boxes (row-per-lane residual projections with BN = 256 only)
     if (EPI == EPI_PRE32 && RPL && BN == 256) {
@@ -185,6 +183,12 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
         const bool rpl = p.seq_len % 32 == 0 && p.rpl >= 0 && epi != EPI_CLIP8;
         if (max_slots > (rpl ? GEMM_RPL_SLOTS : GEMM_MAX_SLOTS)) { set_error("seq_len %d too small for the epilogue tables", p.seq_len); return EGG_E_INVALID; }
     }
+    if (epi == EPI_VOTE && p.k_splits > 1) {
+        // every split must own at least one k-block: the kernel cuts ceil(num_kb / k_splits) blocks per split
+        const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
+        const int kb_per = (num_kb + p.k_splits - 1) / p.k_splits;
+        if ((num_kb + kb_per - 1) / kb_per != p.k_splits) { set_error("k_splits %d leaves an empty split of %d k-blocks", p.k_splits, num_kb); return EGG_E_INVALID; }
+    }
     p.fd_seq = make_fastdiv(p.seq_len);
     p.fd_tiles_n = make_fastdiv(p.N / bn);
     p.fd_third = make_fastdiv(p.third);
@@ -209,8 +213,6 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
         case EPI_HEAD:
             if (p.seq_len % 32 == 0 && p.rpl >= 0) return launch_one<256, EPI_HEAD, 1>(st, ta, tb, to, p, num_sms);
             return launch_one<256, EPI_HEAD>(st, ta, tb, to, p, num_sms);
-        case EPI_ADAM: return launch_bn<EPI_ADAM>(st, bn, ta, tb, to, p, num_sms);
-        case EPI_MUON_M: return launch_bn<EPI_MUON_M>(st, bn, ta, tb, to, p, num_sms);
         case EPI_VOTE: return launch_bn<EPI_VOTE>(st, bn, ta, tb, to, p, num_sms);
         case EPI_NULL: return launch_one<256, EPI_NULL>(st, ta, tb, to, p, num_sms);
     }

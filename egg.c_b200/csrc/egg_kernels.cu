@@ -755,27 +755,35 @@ int launch_fitness(cudaStream_t st, const int32_t *loss, int32_t *fit, int pairs
 // =========================================================================
 // update operands: the two noise matrices of vote = Σ_p f_p a_p b_p^T, pair index contiguous
 // =========================================================================
-__global__ void update_operands_kernel(int8_t *na, int8_t *nb, const int32_t *fit, int pairs, int kp, int rows_k, int cols_n,
+__global__ void __launch_bounds__(256) update_operands_kernel(int8_t *na, int8_t *nb, const int32_t *fit, int pairs, int kp, int rows_k, int cols_n,
                                        int off_a, int off_b, int seed_base, uint32_t step_seed, int mask, int gaussian, int split) {
     const int row = blockIdx.y;                 // 0..cols_n-1 -> NA, cols_n.. -> NB
     const int ktot = split ? 2 * kp : kp;
-    for (int pp = blockIdx.x * blockDim.x + threadIdx.x; pp < ktot; pp += gridDim.x * blockDim.x) {
+    // four consecutive pair slots per thread (kp is a multiple of 128): one word store
+    for (int pp = (blockIdx.x * blockDim.x + threadIdx.x) * 4; pp < ktot; pp += gridDim.x * blockDim.x * 4) {
         const int hi = pp >= kp;
-        const int pidx = hi ? pp - kp : pp;
-        int val = 0;
-        if (pidx < pairs) {
-            const uint32_t s = step_seed + (uint32_t)pidx + (uint32_t)seed_base;    // mgpu.cu:1095
-            if (row < cols_n) {
-                int f = fit[pidx];
-                if (split) { int f1 = f >> 4, f0 = f - (f1 << 4); f = hi ? f1 : f0; }
-                val = f * noise_from_hash(s + (uint32_t)off_a, (uint32_t)row, mask, gaussian);
-            } else {
-                val = noise_from_hash(s + (uint32_t)off_b, (uint32_t)(row - cols_n), mask, gaussian);
-                if (hi) val *= 16;
+        const int pidx0 = hi ? pp - kp : pp;
+        int val[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int pidx = pidx0 + j;
+            int v = 0;
+            if (pidx < pairs) {
+                const uint32_t s = step_seed + (uint32_t)pidx + (uint32_t)seed_base;    // mgpu.cu:1095
+                if (row < cols_n) {
+                    int f = fit[pidx];
+                    if (split) { int f1 = f >> 4, f0 = f - (f1 << 4); f = hi ? f1 : f0; }
+                    v = f ? f * noise_from_hash(s + (uint32_t)off_a, (uint32_t)row, mask, gaussian) : 0;
+                } else {
+                    v = noise_from_hash(s + (uint32_t)off_b, (uint32_t)(row - cols_n), mask, gaussian);
+                    if (hi) v *= 16;
+                }
             }
+            val[j] = v;
         }
-        if (row < cols_n) na[(int64_t)row * ktot + pp] = (int8_t)val;
-        else nb[(int64_t)(row - cols_n) * ktot + pp] = (int8_t)val;
+        const uint32_t w = pack4(val[0], val[1], val[2], val[3]);
+        if (row < cols_n) *reinterpret_cast<uint32_t *>(na + (int64_t)row * ktot + pp) = w;
+        else *reinterpret_cast<uint32_t *>(nb + (int64_t)(row - cols_n) * ktot + pp) = w;
     }
 }
 
@@ -783,9 +791,99 @@ int launch_update_operands(cudaStream_t st, int8_t *na, int8_t *nb, const int32_
                            int cols_n, int off_a, int off_b, int seed_base, uint32_t step_seed, int mask, int gaussian,
                            int split) {
     int ktot = split ? 2 * kp : kp;
-    int gx = (ktot + 255) / 256; if (gx > 32) gx = 32;
+    int gx = (ktot / 4 + 255) / 256; if (gx > 32) gx = 32;
     dim3 grid((unsigned)gx, (unsigned)(rows_k + cols_n));
     update_operands_kernel<<<grid, 256, 0, st>>>(na, nb, fit, pairs, kp, rows_k, cols_n, off_a, off_b, seed_base, step_seed, mask, gaussian, split);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
+
+int vote_gemm_splits(int rows_k, int cols_n, int kp, int num_sms) {
+    const int bn = (rows_k % 256 == 0) ? 256 : 128;
+    const int tiles = ((cols_n + GEMM_BM - 1) / GEMM_BM) * (rows_k / bn);
+    const int num_kb = (kp + GEMM_BK - 1) / GEMM_BK;
+    int want = (2 * num_sms + tiles - 1) / tiles;
+    if (want > num_kb) want = num_kb;
+    if (want > 64) want = 64;
+    if (want < 1) want = 1;
+    const int kb_per = (num_kb + want - 1) / want;
+    return (num_kb + kb_per - 1) / kb_per;
+}
+
+// =========================================================================
+// optimiser step from the vote matrices: one thread per packed word (4 weights of one output column)
+// =========================================================================
+__device__ __forceinline__ int4 sum_votes(const VoteApplyParams &p, int64_t word) {
+    int4 v = *reinterpret_cast<const int4 *>(p.votes + word * 4);
+    for (int s = 1; s < p.nsplits; s++) {
+        const int4 u = *reinterpret_cast<const int4 *>(p.votes + (int64_t)s * p.split_stride + word * 4);
+        v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+    }
+    return v;
+}
+
+__global__ void __launch_bounds__(256) adam_from_votes_kernel(const VoteApplyParams p) {
+    const int64_t word = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t words = (int64_t)(p.rows_k >> 2) * p.cols_n;
+    int changes = 0;
+    if (word < words) {
+        const int4 vt = sum_votes(p, word);
+        const int vote[4] = {vt.x, vt.y, vt.z, vt.w};
+        const int64_t idx = word * 4;
+        const uint32_t wword = *reinterpret_cast<const uint32_t *>(p.w_packed + idx);
+        float4 *st = reinterpret_cast<float4 *>(p.opt + idx * 3);
+        const float4 s0 = st[0], s1 = st[1], s2 = st[2];
+        float f[12] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w, s2.x, s2.y, s2.z, s2.w};
+        uint32_t neww = 0;
+        const int n = (int)(word % p.cols_n), k0 = (int)(word / p.cols_n) * 4;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            int w = (int)(int8_t)(wword >> (8 * j));
+            const float g = -(float)vote[j];
+            const int ch = adam_apply(f[3 * j], f[3 * j + 1], f[3 * j + 2], w, g, p.lr, p.beta1, p.beta2, p.eps, p.wd);
+            changes += ch;
+            if (ch && p.ch_in) { p.ch_in[k0 + j] = 1; p.ch_out[n] = 1; }      // adam.cuh:77-83
+            neww |= (uint32_t)(w & 0xFF) << (8 * j);
+        }
+        *reinterpret_cast<uint32_t *>(p.w_packed + idx) = neww;
+        st[0] = make_float4(f[0], f[1], f[2], f[3]);
+        st[1] = make_float4(f[4], f[5], f[6], f[7]);
+        st[2] = make_float4(f[8], f[9], f[10], f[11]);
+    }
+    changes = warp_sum(changes);
+    if ((threadIdx.x & 31) == 0 && changes > 0) atomicAdd(p.total_updates, (unsigned long long)changes);
+}
+
+__global__ void __launch_bounds__(256) muon_m_from_votes_kernel(const VoteApplyParams p) {
+    const int64_t word = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t words = (int64_t)(p.rows_k >> 2) * p.cols_n;
+    if (word >= words) return;
+    const int4 vt = sum_votes(p, word);
+    const int64_t idx = word * 4;
+    float4 *st = reinterpret_cast<float4 *>(p.opt + idx * 2);
+    float4 s0 = st[0], s1 = st[1];     // m0 acc0 m1 acc1 | m2 acc2 m3 acc3
+    s0.x = __fmaf_rn(p.mu, s0.x, (float)vt.x);   // m = mu*m + vote, muon_internal.cuh:45-47
+    s0.z = __fmaf_rn(p.mu, s0.z, (float)vt.y);
+    s1.x = __fmaf_rn(p.mu, s1.x, (float)vt.z);
+    s1.z = __fmaf_rn(p.mu, s1.z, (float)vt.w);
+    st[0] = s0; st[1] = s1;
+    const int n = (int)(word % p.cols_n);
+    const int64_t k = (word / p.cols_n) * 4;
+    p.m_rowmajor[k * p.cols_n + n] = s0.x;        // gather, muon_internal.cuh:53-74
+    p.m_rowmajor[(k + 1) * p.cols_n + n] = s0.z;
+    p.m_rowmajor[(k + 2) * p.cols_n + n] = s1.x;
+    p.m_rowmajor[(k + 3) * p.cols_n + n] = s1.z;
+}
+
+int launch_adam_from_votes(cudaStream_t st, const VoteApplyParams &p) {
+    const int64_t words = (int64_t)(p.rows_k >> 2) * p.cols_n;
+    adam_from_votes_kernel<<<(unsigned)((words + 255) / 256), 256, 0, st>>>(p);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
+int launch_muon_m_from_votes(cudaStream_t st, const VoteApplyParams &p) {
+    const int64_t words = (int64_t)(p.rows_k >> 2) * p.cols_n;
+    muon_m_from_votes_kernel<<<(unsigned)((words + 255) / 256), 256, 0, st>>>(p);
     EGG_CUDA(cudaGetLastError());
     return EGG_OK;
 }

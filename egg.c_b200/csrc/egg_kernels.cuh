@@ -142,6 +142,25 @@ int launch_update_operands(cudaStream_t st, int8_t *na, int8_t *nb, const int32_
                            int cols_n, int off_a, int off_b, int seed_base, uint32_t step_seed, int mask, int gaussian,
                            int split);
 
+// Splits of the pair index for the vote GEMM of a rows_k x cols_n matrix over kp (padded) pairs: enough work items to
+// fill the GPU twice over, never an empty split.
+int vote_gemm_splits(int rows_k, int cols_n, int kp, int num_sms);
+
+// Optimiser step of one matrix from its (partial) vote matrices, element order = the packed weight layout.
+struct VoteApplyParams {
+    int8_t *w_packed;            // [rows_k/4][cols_n][4]
+    float *opt;                  // AdamParam{m,v,acc} (AdamW) or MuonParam{m,acc} (Muon momentum) per packed index
+    const int32_t *votes;        // [nsplits][rows_k * cols_n]
+    int nsplits; int64_t split_stride;
+    int rows_k, cols_n;
+    float lr, beta1, beta2, eps, wd, mu;
+    unsigned long long *total_updates;
+    uint8_t *ch_in, *ch_out;     // AdamW: set to 1 for every input index k / output index n with a changed weight (or null)
+    float *m_rowmajor;           // Muon: [rows_k][cols_n] copy of the new momentum
+};
+int launch_adam_from_votes(cudaStream_t st, const VoteApplyParams &p);        // ES-AdamW (mgpu.cu:1040-1064, 1100-1110)
+int launch_muon_m_from_votes(cudaStream_t st, const VoteApplyParams &p);      // m = mu*m + vote, gather (muon_internal.cuh:15-74)
+
 struct VecUpdParams {
     int8_t *v; float *opt; int len; int off_a, off_b, seed_base; const int32_t *fit; int pairs;
     uint32_t step_seed; float lr, beta1, beta2, eps, wd; int mask, gaussian; unsigned long long *total_updates;

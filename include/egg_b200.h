@@ -232,6 +232,25 @@ int egg_update_reconstruct(egg_ctx *ctx, const int32_t *fitness, int pairs,
                            uint32_t step_seed, int32_t *vote_out, int on_device);
 
 /*
+ * One whole update of one weight matrix outside any model (≙ one launch of update_matrix_adam_kernel,
+ * mgpu.cu:1067-1111, with its argument list: W, optimiser state, rows, cols, off_A, off_B, seed_base,
+ * fitnesses, step_seed, lr — or, with optimizer = 1, the Muon sequence of mgpu.cu:1587-1595:
+ * muon_momentum_update_kernel, gather, perform_newton_schulz, muon_apply_update_kernel,
+ * muon_internal.cuh:15-342).  d_w_packed is the matrix in the reference's [rows_k/4][cols_n][4] layout,
+ * d_opt_state its AdamParam{m,v,acc} (optimizer 0, 12 bytes per weight) or MuonParam{m,acc}
+ * (optimizer 1, 8 bytes per weight) array in the same index order; both are updated in place.
+ * d_fitness holds `pairs` int32 values; split = 1 takes the two-digit operand form for fitness
+ * beyond ternary (|f| <= 127; needs 16 * noise magnitude <= 127).  All pointers are DEVICE pointers.
+ * Hyper-parameters (betas, eps, weight decay, Muon momentum and lr scale, noise mask) come from the
+ * context's configuration.  *total_updates = number of weights that changed.  Allocates its scratch
+ * (operands, partial votes, Newton-Schulz workspace) per call and blocks until done.
+ */
+int egg_update_matrix(egg_ctx *ctx, int8_t *d_w_packed, void *d_opt_state, int rows_k, int cols_n,
+                      int off_a, int off_b, int seed_base, const int32_t *d_fitness, int pairs,
+                      uint32_t step_seed, float learning_rate, int optimizer, int split,
+                      uint64_t *total_updates);
+
+/*
  * Allocation-free variant of egg_update_reconstruct.  It has no counterpart in the
  * reference.  It exists for callers that must not allocate device memory while they
  * run: a d-eggs style worker that was handed a fixed memory budget at start-up, code
@@ -343,6 +362,78 @@ int egg_deggs_chunk_fitness(const int32_t *losses, int count, int mean_filter, d
 /* ≙ seed = hash_rng(seed, step) after every update (worker.cu:542, coordinator.cpp:406). */
 uint32_t egg_next_seed(uint32_t seed, uint64_t step);
 
+/* ≙ get_learning_rate (d-eggs/include/utils/training.h:5-9): 0.5 below step 100, 0.25 below 200, then 0.125. */
+float egg_learning_rate(int64_t step);
+
+/*
+ * The worker loop of d-eggs/src/worker.cu:390-717 against an unmodified coordinator
+ * (d-eggs/src/coordinator.cpp) over d-eggs/include/protocol.h.  Per iteration: JOB_REQUEST(seed,
+ * last_step); the answer is either the packed fitness of the whole population for the worker's step
+ * (-> apply_update with the learning rate of that step, step = answer's step, seed = hash_rng(seed, step);
+ * worker.cu:416-547), a wait (data_position == -1 -> sleep, worker.cu:550-554), or a chunk
+ * (data_position = first member -> eval_chunk of chunk_size members at start index step * SEQ_LEN, the
+ * per-chunk fitness filter, ternary pack, RESULT with the update count of the last update and the loss
+ * sum; worker.cu:557-713).  Every `generate_every` steps the worker that gets chunk 0 sends a sampled
+ * continuation as LOG_MESSAGE when the engine can generate.
+ *
+ * The GPU work is behind three callbacks so that the same loop runs on an egg_ctx
+ * (egg_worker_engine_from_ctx) and, in tests, on host-side fakes.  Callbacks return 0 or a negative
+ * EGG_E_* code, which ends the loop and is returned.  The loop also ends when the coordinator closes the
+ * connection or stays silent for recv_timeout_ms (EGG_E_STATE), when *stop_flag becomes non-zero, at
+ * stop_at_step, or after max_requests requests (both -1: never).
+ */
+typedef struct egg_worker_engine {
+    void *self;
+    /* losses[count] of members [pop_offset, pop_offset + count) for (seed, step); chunk-relative order */
+    int (*eval_chunk)(void *self, uint32_t seed, int64_t step, int pop_offset, int count, int32_t *losses);
+    /* one optimiser step from the fitness of all pairs; lr_bias is what the reference passes for emb_bias */
+    int (*apply_update)(void *self, const int32_t *fitness, int pairs, uint32_t seed, float lr, float lr_bias, uint64_t *updates);
+    /* optional: writes up to cap bytes of text for the coordinator's console, returns their number */
+    int (*generate)(void *self, int64_t step, uint32_t seed, char *text, int cap);
+} egg_worker_engine;
+
+typedef struct egg_worker_options {
+    char host[64];               /* dotted IPv4 address of the coordinator (default 127.0.0.1) */
+    int port;                    /* coordinator.cpp:26 listens on 12345 */
+    int population_size, chunk_size;     /* POPULATION_SIZE, CHUNK_SIZE of d-eggs/include/config.h:14-46 */
+    uint64_t initial_seed;       /* 42, worker.cu:386 */
+    int wait_sleep_ms;           /* 100, worker.cu:552 */
+    int recv_timeout_ms;         /* give up on a silent coordinator after this long */
+    int generate_every;          /* 5, worker.cu:564; 0: never */
+    int mean_filter; double mean_exponent; int adaptive_threshold; double threshold_alpha;   /* config.h:212-224 */
+    int64_t stop_at_step, max_requests;
+    const volatile int *stop_flag;       /* polled once per iteration (the reference's SIGINT flag, worker.cu:244) or NULL */
+    /* test hook, called before a RESULT is sent: a non-zero return drops that result (a worker that went silent) */
+    int (*before_result)(void *hook_self, int64_t step, int chunk_index);
+    void *hook_self;
+} egg_worker_options;
+
+typedef struct egg_worker_stats {
+    uint64_t requests, chunks_done, updates_applied, waits, results_dropped;
+    uint64_t bytes_sent, bytes_received;
+    uint64_t final_step, final_seed;
+} egg_worker_stats;
+
+void egg_worker_options_defaults(egg_worker_options *opts);
+int egg_worker_run(const egg_worker_options *opts, const egg_worker_engine *engine, egg_worker_stats *stats);
+/* Binds the callbacks to a context of this library (evaluation through egg_eval_chunk + egg_read_losses,
+ * updates through egg_write_fitness + egg_apply_update). */
+int egg_worker_engine_from_ctx(egg_ctx *ctx, egg_worker_engine *out);
+/* The configuration a context was created with. */
+int egg_get_config(egg_ctx *ctx, egg_config *out);
+
+/* ---- run log (≙ egg_disk_log.h / d-eggs/include/utils/log.h) ------------------ */
+/*
+ * The reference's plain-text run log: a header block with the configuration (egg_disk_log.h:111-138),
+ * the column line "Step,RelTime,Loss,Updates,LR" (:139) and one row per step (:222), appended to `path`.
+ * The reference also posts every run and step to a third-party tracking service through curl
+ * (:177-198, 238-261); that part is left out on purpose: this library opens no network connection here.
+ */
+typedef struct egg_log egg_log;
+int egg_log_open(const char *path, const egg_config *cfg, int num_gpus, uint64_t vram_bytes_per_gpu, egg_log **out);
+int egg_log_record(egg_log *log, int64_t step, double loss, uint64_t updates, float learning_rate);
+void egg_log_close(egg_log *log);
+
 /* ---- measurement ------------------------------------------------------ */
 /*
  * The reference times a generation with clock_gettime around its launches
@@ -370,6 +461,7 @@ enum {
     EGG_PROF_MUON,          /* Newton–Schulz + apply                                  */
     EGG_PROF_TRANSPOSE,     /* packed -> K-major weight shadows                       */
     EGG_PROF_OVERLAY,       /* adaptive-noise: scaled row dots, overlay steps          */
+    EGG_PROF_UPD_APPLY,     /* optimiser step of a matrix from its vote matrices      */
     EGG_PROF_N
 };
 /* enable != 0: every launch is bracketed by events (a few microseconds each). */

@@ -98,6 +98,22 @@ def run_ref_mgpu(tag, model, dataset, step_seed, start_idx, pop_offset, count, l
     return out
 
 
+def assert_losses_match_racy_reference(tag, model, dataset, step_seed, start_idx, pop_offset, ours, ref_losses, max_bad=None):
+    """Compares losses with the reference kernels' while tolerating the reference's own data race: its
+    train_sequence_kernel calls adaptive_qkv_normalize three times back to back on one shared scratch array with no
+    barrier between one call's reads and the next call's writes (egg_adaptive_normalize.h:29-41, mgpu.cu:782-784), and
+    at hidden 512 about one member in four thousand comes out differently from run to run.  A member that differs must
+    equal the reference re-run on its pair alone; returns the list of such members."""
+    bad = np.nonzero(ours != ref_losses)[0]
+    limit = max_bad if max_bad is not None else max(2, len(ours) // 500)
+    assert len(bad) <= limit, "%d of %d losses differ from the reference kernels" % (len(bad), len(ours))
+    for pr in sorted(set((pop_offset + int(m)) // 2 for m in bad)):
+        alone = run_ref_mgpu(tag, model, dataset, step_seed, start_idx, 2 * pr, 2)["losses"]
+        mine = ours[2 * pr - pop_offset:2 * pr - pop_offset + 2]
+        assert (mine == alone).all(), "pair %d: %s here, %s by the reference run on the pair alone" % (pr, mine, alone)
+    return bad.tolist()
+
+
 def deggs_binary(tag):
     p = os.path.join(ROOT, "oracle", "_ref", "ref_deggs_" + tag)
     return p if os.path.exists(p) else None

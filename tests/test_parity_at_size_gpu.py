@@ -9,7 +9,7 @@
 import numpy as np
 import pytest
 
-from common import REF_CONFIGS, cfg_pair, load_oracle, load_pkg, make_case, ref_binary, run_ref_mgpu
+from common import REF_CONFIGS, assert_losses_match_racy_reference, cfg_pair, load_oracle, load_pkg, make_case, ref_binary, run_ref_mgpu
 
 pytestmark = pytest.mark.gpu
 
@@ -18,7 +18,15 @@ SEED = 0x00C0FFEE
 
 def test_whole_benchmark_generation_matches_reference_kernels():
     """full_cuda_train_transformer_adam_mgpu.cu:1506-1688 at POPULATION_SIZE 40960: evaluation of every member, host
-    fitness, the whole LAUNCH_ADAM_* list.  Integer results and fp32 state must be bit-identical."""
+    fitness, the whole LAUNCH_ADAM_* list.
+
+    The reference's train_sequence_kernel is not deterministic at this size: two runs of it on identical inputs differ
+    in a handful of the 40 960 losses (its three back-to-back adaptive_qkv_normalize calls share one scratch array with
+    no barrier between one call's reads and the next call's writes, egg_adaptive_normalize.h:29-41 called at
+    mgpu.cu:782-784).  So: every loss must equal the reference's, except that a member whose loss differs must equal
+    the reference re-run on that pair alone (where its race does not show) -- and there may only be a few of them.
+    The update is then compared on the reference's own fitness vector, so that its raced losses cannot leak into the
+    comparison: update count, weights and fp32 AdamW state bit-identical."""
     if not ref_binary("c2"):
         pytest.skip("oracle/_ref/ref_mgpu_c2 not built")
     pkg = load_pkg()
@@ -32,14 +40,21 @@ def test_whole_benchmark_generation_matches_reference_kernels():
     ctx = pkg.Context(cfg, 0, 0)
     ctx.upload_model(model)
     ctx.set_dataset(data)
-    losses = np.zeros(pop, np.int32)
-    n_gpu = ctx.generation_host(None, 1, SEED, lr, losses)
+    ctx.eval_chunk(SEED, 256, 0, pop)
+    losses = ctx.read_losses(0, pop)
+    ctx.compute_fitness_pairs(0, pop // 2)
     fit = ctx.read_fitness(0, pop // 2)
+    ref = run_ref_mgpu("c2", model, data, SEED, 256, 0, pop, lr=lr, do_update=True)
+    bad = assert_losses_match_racy_reference("c2", model, data, SEED, 256, 0, losses, ref["losses"], max_bad=64)
+    bad_pairs = sorted(set(int(m) // 2 for m in bad))
+    print("members where the reference's full-population run differs from its own single-pair run:", bad)
+    same = np.ones(pop // 2, bool)
+    same[bad_pairs] = False
+    assert (fit[same] == ref["fitness"][same]).all()
+    ctx.write_fitness(ref["fitness"], 0)
+    n_gpu = ctx.apply_update(SEED, lr)
     got_model, got_opt = ctx.download_model(), ctx.download_opt_state()
     ctx.close()
-    ref = run_ref_mgpu("c2", model, data, SEED, 256, 0, pop, lr=lr, do_update=True)
-    assert (losses == ref["losses"]).all(), "%d of %d losses differ" % ((losses != ref["losses"]).sum(), pop)
-    assert (fit == ref["fitness"]).all()
     assert n_gpu == ref["updates"] and n_gpu > 0
     assert (got_model == ref["model"]).all(), "%d weights differ" % (got_model != ref["model"]).sum()
     assert (got_opt == ref["opt"]).all(), "fp32 AdamW state is not bit-identical to the reference kernels"
@@ -159,4 +174,104 @@ def test_isolated_vote_reconstruction_at_benchmark_size_sample():
         ctx.update_reconstruct(d_f.data_ptr(), pairs, R, Cn, 402, 403, 1000, 2, out.data_ptr(), on_device=True)
         parts.append(out)
     assert torch.equal(parts[0] + parts[1], votes)
+    ctx.close()
+
+
+def _packed_index(k, n, cols_n):
+    return ((k >> 2) * cols_n + n) * 4 + (k & 3)
+
+
+@pytest.mark.parametrize("int8fit", [False, True])
+def test_isolated_matrix_update_adamw_matches_oracle(int8fit):
+    """egg_update_matrix (one launch of update_matrix_adam_kernel, mgpu.cu:1067-1111): two chained ES-AdamW steps of a
+    256 x 384 matrix from 1000 pairs, ternary and int8 fitness; weights, fp32 state and the change count bit-exact."""
+    import torch
+    pkg, O = load_pkg(), load_oracle()
+    cfg, ocfg = cfg_pair(device_mask=3, population_size=2000)
+    R, Cn, pairs = 256, 384, 1000
+    rng = np.random.default_rng(21)
+    w = rng.integers(-127, 128, R * Cn).astype(np.int8)
+    st = np.zeros((R * Cn, 3), np.float32)
+    d_w, d_st = torch.from_numpy(w.copy()).cuda(), torch.zeros(R * Cn * 3, dtype=torch.float32, device="cuda")
+    ctx = pkg.Context(cfg, 0, 2)
+    for step in range(2):
+        fit = (rng.integers(-127, 128, pairs) if int8fit else rng.integers(-1, 2, pairs)).astype(np.int32)
+        d_fit = torch.from_numpy(fit).cuda()
+        torch.cuda.synchronize()
+        n_gpu = ctx.update_matrix(d_w.data_ptr(), d_st.data_ptr(), R, Cn, 402, 403, 1000, d_fit.data_ptr(), pairs, 5 + step, 0.7,
+                                  optimizer=0, split=int8fit)
+        votes = O.vote_matrix(ocfg, fit, R, Cn, 402, 403, 1000, 5 + step)
+        n_orc = O.adam_from_votes(ocfg, w, st, votes, 0.7)
+        assert n_gpu == n_orc
+        assert (d_w.cpu().numpy() == w).all(), "step %d: %d weights differ" % (step, (d_w.cpu().numpy() != w).sum())
+        assert (d_st.cpu().numpy().view(np.uint32) == st.reshape(-1).view(np.uint32)).all(), "fp32 AdamW state not bit-identical"
+    ctx.close()
+
+
+def test_isolated_matrix_update_muon_matches_oracle():
+    """egg_update_matrix with the Muon sequence (muon_internal.cuh:15-342) on a 512 x 1024 matrix from 300 pairs: momentum
+    exact, accumulator within 1e-5 relative of the oracle's double-accumulating Newton-Schulz."""
+    import torch
+    pkg, O = load_pkg(), load_oracle()
+    cfg, ocfg = cfg_pair(device_mask=3, population_size=600, use_muon=1)
+    R, Cn, pairs = 512, 1024, 300
+    rng = np.random.default_rng(22)
+    w = rng.integers(-127, 128, R * Cn).astype(np.int8)
+    fit = rng.integers(-1, 2, pairs).astype(np.int32)
+    d_w, d_st = torch.from_numpy(w.copy()).cuda(), torch.zeros(R * Cn * 2, dtype=torch.float32, device="cuda")
+    d_fit = torch.from_numpy(fit).cuda()
+    ctx = pkg.Context(cfg, 0, 2)
+    torch.cuda.synchronize()
+    lr = 0.5
+    ctx.update_matrix(d_w.data_ptr(), d_st.data_ptr(), R, Cn, 400, 401, 2000, d_fit.data_ptr(), pairs, 9, lr, optimizer=1)
+    st = d_st.cpu().numpy().reshape(-1, 2)
+    votes = O.vote_matrix(ocfg, fit, R, Cn, 400, 401, 2000, 9).astype(np.float32)          # from zero state: m = votes
+    assert (st[:, 0] == votes).all()
+    idx = np.arange(R * Cn)
+    n_of, k_of = (idx >> 2) % Cn, ((idx >> 2) // Cn) * 4 + (idx & 3)
+    m_rowmajor = np.zeros((R, Cn), np.float32)
+    m_rowmajor[k_of, n_of] = votes
+    u = O.newton_schulz(m_rowmajor)[k_of, n_of].astype(np.float64)
+    acc_want = -lr * (u + 0.01 * w.astype(np.float64))
+    wrapped = np.abs(acc_want) >= 1.0                                                      # the quantised step subtracts 1 there
+    err = np.abs(st[:, 1].astype(np.float64) - acc_want)[~wrapped]
+    tol = 1e-5 * np.abs(acc_want[~wrapped]) + 2e-6
+    assert (err <= tol).all(), "max err %g over %d elements" % (err.max(), (~wrapped).sum())
+    ctx.close()
+
+
+def test_isolated_matrix_update_at_benchmark_size_sample():
+    """4096 x 4096 weight, 32 768 pairs of int8 rank-normalised fitness, one ES-AdamW step from zero state: the weights and
+    fp32 state of 64 sampled output columns against the oracle (votes of those columns, then the element step)."""
+    import torch
+    pkg, O = load_pkg(), load_oracle()
+    from egg_c_b200 import synth
+    cfg, ocfg = cfg_pair(device_mask=3, population_size=65536)
+    R = Cn = 4096
+    pairs = 32768
+    rng = np.random.RandomState(2)
+    rank = np.argsort(np.argsort(rng.randn(pairs)))
+    fit = np.clip(np.round(rank / (pairs - 1) * 254.0 - 127.0), -127, 127).astype(np.int32)
+    w0 = synth.uniform_int8(0, R * Cn)
+    d_w = torch.from_numpy(w0.copy()).cuda()
+    d_st = torch.zeros(R * Cn * 3, dtype=torch.float32, device="cuda")
+    d_fit = torch.from_numpy(fit).cuda()
+    ctx = pkg.Context(cfg, 0, 2)
+    torch.cuda.synchronize()
+    lr = 2.5           # |m/sqrt(v)| = 0.1/sqrt(0.05) ~ 0.447 after the first step: lr above 2.24 makes weights flip at once
+    n_gpu = ctx.update_matrix(d_w.data_ptr(), d_st.data_ptr(), R, Cn, 402, 403, 1000, d_fit.data_ptr(), pairs, 2, lr, optimizer=0, split=True)
+    assert n_gpu > 0
+    w1 = d_w.cpu().numpy()
+    st1 = d_st.cpu().numpy().reshape(-1, 3)
+    assert int((w1 != w0).sum()) == n_gpu
+    n_list = np.unique(np.concatenate([[0, Cn - 1], np.random.default_rng(8).integers(0, Cn, 62)])).astype(np.int32)
+    votes = O.vote_columns(ocfg, fit, R, 402, 403, 1000, 2, n_list)
+    k = np.arange(R)
+    for i, n in enumerate(n_list):
+        idx = _packed_index(k, int(n), Cn)
+        w = w0[idx].copy()
+        st = np.zeros((R, 3), np.float32)
+        O.adam_from_votes(ocfg, w, st, votes[i], lr)
+        assert (w1[idx] == w).all(), "output column %d: %d weights differ" % (n, (w1[idx] != w).sum())
+        assert (st1[idx].view(np.uint32) == st.view(np.uint32)).all(), "output column %d: fp32 state differs" % n
     ctx.close()

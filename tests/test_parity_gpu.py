@@ -4,7 +4,7 @@ Integer results must be bit-exact; fp32 optimiser state within 1e-5 relative."""
 import numpy as np
 import pytest
 
-from common import REF_CONFIGS, cfg_pair, load_oracle, load_pkg, make_case, ref_binary, run_ref_mgpu
+from common import REF_CONFIGS, assert_losses_match_racy_reference, cfg_pair, load_oracle, load_pkg, make_case, ref_binary, run_ref_mgpu
 
 pytestmark = pytest.mark.gpu
 
@@ -202,7 +202,7 @@ def test_benchmark_config_sample_matches_reference_kernels():
         ctx.eval_chunk(SEED, 256, off, 64)
         got = ctx.read_losses(off, 64)
         ref = run_ref_mgpu("c2", model, data, SEED, 256, off, 64)
-        assert (got == ref["losses"]).all(), (off, got[:6], ref["losses"][:6])
+        assert_losses_match_racy_reference("c2", model, data, SEED, 256, off, got, ref["losses"])
     ctx.close()
     ctx2 = _ctx(cfg, wave=48)      # a wave size that leaves a ragged last wave
     ctx2.upload_model(model)
@@ -230,5 +230,5 @@ def test_deggs_scale_config_sample_matches_reference_kernels():
     ctx.eval_chunk(SEED, 512, off, 16)
     got = ctx.read_losses(off, 16)
     ref = run_ref_mgpu("c5", model, data, SEED, 512, off, 16)
-    assert (got == ref["losses"]).all(), (got[:6], ref["losses"][:6])
+    assert_losses_match_racy_reference("c5", model, data, SEED, 512, off, got, ref["losses"])
     ctx.close()
