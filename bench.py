@@ -16,6 +16,8 @@ Other workloads (single GPU, same JSON contract, named in config.workload):
            so the line reports member-token-equivalents = pairs*2 per step second and the tensor roofline)
   c5slice  d-eggs-scale shapes (12 layers, H 1024, seq 512, ternary weights, Muon): a slice of the 262 144-member
            population is evaluated, the update runs over all 131 072 pairs
+  c5       the same shapes as a whole generation of a FIXED population (--pop-total, default 262 144) sharded over the N
+           GPUs of the launch ("scaling": "strong"); a step takes tens of seconds at N = 1, so run it with --steps 1
 
 Prints ONE JSON line on rank 0.  `--impl reference` times the reference's CPU trainer
 (full_trained_egg.c, built into oracle/_ref/ref_cpu_gru) on the host cores instead.
@@ -447,11 +449,13 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5slice"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5slice", "c5"])
+    ap.add_argument("--pop-total", type=int, default=262144, help="workload c5: the fixed population that is sharded over the GPUs")
     ap.add_argument("--pop", type=int, default=POP_PER_GPU, help="members per GPU (benchmark value: 40960)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the extra legs of the default line (recurrent model, reference GPU kernels, C5 sample)")
     ap.add_argument("--two-kernel-norm", action="store_true", help="A/B: take the two-kernel form of the adaptive normalisations (int32 pre-activations + requantisation kernels)")
+    ap.add_argument("--attention-tc", action="store_true", help="A/B: take the tcgen05 form of the attention kernel")
     ap.add_argument("--wave", type=int, default=0, help="members per internal wave (0: the library's default)")
     ap.add_argument("--small", action="store_true", help="profiling-sized run: 1024 members, one warm-up step, no end-to-end / CPU legs")
     args = ap.parse_args()
@@ -474,7 +478,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a B200: the library has no CPU path")
     peaks = load_peaks()
-    if args.workload != "c2":
+    if args.workload not in ("c2", "c5"):
         if world > 1:
             if rank == 0:
                 raise SystemExit("workload %s is a single-GPU measurement" % args.workload)
@@ -492,13 +496,21 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    pop = args.pop * world                       # weak scaling: fixed members per GPU
-    cfg = pkg.default_config(population_size=pop, **C2)
+    strong = args.workload == "c5"
+    if strong:
+        pop = args.pop_total                     # strong scaling: the fixed population of the d-eggs-scale configuration
+        cfg = pkg.default_config(population_size=pop, use_muon=1, **C5)
+        args.no_extras = True
+    else:
+        pop = args.pop * world                   # weak scaling: fixed members per GPU
+        cfg = pkg.default_config(population_size=pop, **C2)
     ctx = pkg.Context(cfg, local_rank, args.wave)
     if args.two_kernel_norm:
         ctx.set_fused_epilogues(False)
+    if args.attention_tc:
+        ctx.set_attention_tensor_core(True)
     fused_active = ctx.fused_epilogues_active()
-    model = synth.random_model(cfg, 0, "uniform")
+    model = synth.random_model(cfg, 0, "ternary" if strong else "uniform")
     ctx.upload_model(model)
     data_np = synth.zipf_bytes(1, DATA_LEN)
     data_pinned = torch.from_numpy(data_np).pin_memory()
@@ -535,7 +547,7 @@ def main():
         return ctx.generation_host(None, s, SEED0 + s, LR, None)
 
     # ---- kernel-resident timing (inputs already in HBM) ----
-    n_warm = args.warmup if args.small else max(args.warmup, 3)
+    n_warm = args.warmup if (args.small or strong) else max(args.warmup, 3)
     for _ in range(n_warm):
         one_step(False)
     barrier()
@@ -591,7 +603,8 @@ def main():
     }
     hbm_bytes = {  # algorithmic bytes per generation on this rank
         "attention": 4.0 * H * rows_per_step * L,
-        "rowwise": 6.0 * H * rows_per_step * (2 * L + 2),
+        # two-kernel form: 4H of int32 in, H + H out per row; fused form: the int8 stream in, the normalised row out
+        "rowwise": (2.0 if fused_active else 6.0) * H * rows_per_step * (2 * L + 2),
         "aqn": 15.0 * H * rows_per_step * L,
     }
     traffic_per_row, traffic_src = load_traffic()
@@ -681,9 +694,10 @@ def main():
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": n_warm,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8/int32",
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "int8/int32",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "population_size": pop, "members_per_gpu": per, "seq_len": S, "hidden_dim": H,
+            "config": {"workload": ("c5: d-eggs-scale generation, L=12 H=1024 heads=16 MLP=4H seq=512 vocab=256, ternary weight values, Muon, "
+                                    "fixed population sharded over the GPUs") if strong else WORKLOAD, "population_size": pop, "members_per_gpu": per, "seq_len": S, "hidden_dim": H,
                        "n_layers": L, "wave_members": wave_members, "dataset_bytes": DATA_LEN,
                        "adaptive_norms": "fused into the projection epilogues (row-owning kernels)" if fused_active else "two-kernel form",
                        "l2_policy": "inputs larger than L2: each wave streams > 2 GB of activations, dataset 64 MiB",

@@ -23,7 +23,7 @@ EXPORTS = [
     "egg_apply_update", "egg_generation_host", "egg_perturbed_projection", "egg_update_reconstruct", "egg_update_matrix",
     "egg_update_reconstruct_noalloc", "egg_scales_bytes", "egg_upload_scales", "egg_download_scales", "egg_set_overlay_steps",
     "egg_timer_start", "egg_timer_stop", "egg_profile_enable", "egg_profile_read", "egg_profile_name", "egg_launch_count",
-    "egg_wave_members", "egg_set_fused_epilogues", "egg_fused_epilogues_active", "egg_measure_int8_peak", "egg_selftest_index_math", "egg_generate", "egg_save_checkpoint", "egg_load_checkpoint", "egg_wire_fixed_bytes", "egg_wire_encode", "egg_wire_decode_header", "egg_wire_decode_body",
+    "egg_wave_members", "egg_set_fused_epilogues", "egg_fused_epilogues_active", "egg_set_attention_tensor_core", "egg_measure_int8_peak", "egg_selftest_index_math", "egg_generate", "egg_save_checkpoint", "egg_load_checkpoint", "egg_wire_fixed_bytes", "egg_wire_encode", "egg_wire_decode_header", "egg_wire_decode_body",
     "egg_ternary_packed_size", "egg_ternary_pack", "egg_ternary_unpack", "egg_deggs_chunk_fitness", "egg_next_seed",
     "egg_gru_config_defaults", "egg_gru_model_bytes", "egg_gru_state_bytes", "egg_gru_create", "egg_gru_destroy",
     "egg_gru_upload_model", "egg_gru_download_model", "egg_gru_upload_states", "egg_gru_download_states", "egg_gru_set_dataset",
@@ -176,6 +176,7 @@ def lib():
         L.egg_wave_members.argtypes = [vp]
         L.egg_set_fused_epilogues.argtypes = [vp, C.c_int]
         L.egg_fused_epilogues_active.argtypes = [vp]
+        L.egg_set_attention_tensor_core.argtypes = [vp, C.c_int]
         L.egg_learning_rate.argtypes = [C.c_int64]
         L.egg_learning_rate.restype = C.c_float
         L.egg_worker_options_defaults.argtypes = [P(WorkerOptions)]
@@ -430,6 +431,9 @@ class Context:
 
     def set_fused_epilogues(self, enable):
         _check(lib().egg_set_fused_epilogues(self._h, 1 if enable else 0))
+
+    def set_attention_tensor_core(self, enable):
+        _check(lib().egg_set_attention_tensor_core(self._h, 1 if enable else 0))
 
     def fused_epilogues_active(self):
         return bool(lib().egg_fused_epilogues_active(self._h))

@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libegg_b200.so")
-SOURCES = ["egg_api.cu", "egg_kernels.cu", "egg_gemm_inst.cu", "egg_gru.cu", "egg_generate.cu", "egg_wire.cpp", "egg_worker.cpp"]
+SOURCES = ["egg_api.cu", "egg_kernels.cu", "egg_gemm_inst.cu", "egg_attention_tc.cu", "egg_gru.cu", "egg_generate.cu", "egg_wire.cpp", "egg_worker.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

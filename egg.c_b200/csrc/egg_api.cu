@@ -109,8 +109,14 @@ struct egg_ctx {
     MuonWs muon = {nullptr, nullptr, nullptr, nullptr};
     unsigned long long *d_updates = nullptr;
     int *d_err = nullptr;
+    // grow-only scratch of the isolated entry points (projection, reconstruct, matrix update): allocated on first use,
+    // kept for the next call, freed with the context
+    void *scratch[16] = {};
+    size_t scratch_bytes[16] = {};
     // row-owning projections with the adaptive normalisations fused (default wherever the shapes allow)
     bool fused_on = true;
+    // attention on tcgen05 (egg_attention_tc.cu) instead of the mma.sync kernel: correct but slower as measured, off by default
+    bool attention_tc_on = false;
     // measurement
     cudaEvent_t t0 = nullptr, t1 = nullptr;
     bool prof_on = false;
@@ -321,6 +327,7 @@ extern "C" void egg_ctx_destroy(egg_ctx *c) {
                     c->d_rowmax3, c->d_xbo, c->d_wave_loss, c->d_segs, c->d_nt, c->d_na, c->d_nb, c->d_votes, c->muon.x, c->muon.g,
                     c->muon.y, c->muon.norm2, c->d_updates, c->d_err, c->d_scales, c->d_ch_in, c->d_ch_out};
     for (void *p : ptrs) if (p) cudaFree(p);
+    for (void *p : c->scratch) if (p) cudaFree(p);
     for (cudaEvent_t e : c->prof_ev) cudaEventDestroy(e);
     if (c->t0) cudaEventDestroy(c->t0);
     if (c->t1) cudaEventDestroy(c->t1);
@@ -444,6 +451,20 @@ extern "C" int egg_ctx_create(const egg_config *cfg, int device, int wave_member
 #undef TRY
 #undef TRYC
     *out = c;
+    return EGG_OK;
+}
+
+// Scratch slot `slot` with room for `count` elements of T: reuses the slot's buffer when it is large enough.
+template <typename T>
+static int ctx_scratch(egg_ctx *c, int slot, int64_t count, T **out) {
+    const size_t need = (size_t)(count > 0 ? count : 1) * sizeof(T);
+    if (c->scratch_bytes[slot] < need) {
+        if (c->scratch[slot]) { cudaStreamSynchronize(c->stream); cudaFree(c->scratch[slot]); c->scratch[slot] = nullptr; c->scratch_bytes[slot] = 0; }
+        cudaError_t e = cudaMalloc(&c->scratch[slot], need);
+        if (e != cudaSuccess) { set_error("cudaMalloc of %zu scratch bytes failed: %s", need, cudaGetErrorString(e)); c->scratch[slot] = nullptr; return EGG_E_NOMEM; }
+        c->scratch_bytes[slot] = need;
+    }
+    *out = static_cast<T *>(c->scratch[slot]);
     return EGG_OK;
 }
 
@@ -774,7 +795,9 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
         AttnParams ap; ap.members = members; ap.H = H; ap.head_dim = cf.head_dim; ap.seq_len = S; ap.shift_attn = cf.shift_attn;
         ap.q = c->d_q; ap.k = c->d_k; ap.v = c->d_v; ap.ao = c->d_ao; ap.exp_lut = c->d_exp_lut; ap.nt = c->d_nt;
         ap.nt_stride = nm.stride; ap.nt_o_b = nb + lo.o_b; ap.xbo = c->d_xbo;
-        if ((rc = PROF(EGG_PROF_ATTENTION, launch_attention(st, ap)))) return rc;
+        if (c->attention_tc_on && attention_tc_supported(S, cf.head_dim)) rc = PROF(EGG_PROF_ATTENTION, launch_attention_tc(st, ap, c->d_err));
+        else rc = PROF(EGG_PROF_ATTENTION, launch_attention(st, ap));
+        if (rc) return rc;
         if (sc && (rc = scaled_dot1(c, M, c->d_ao, 1, nb + lo.o_b, SL.w_o_row + lH, c->d_xbo, 1))) return rc;
         // output projection + residual (mgpu.cu:828-830)
         if (fused) {
@@ -1088,20 +1111,17 @@ extern "C" int egg_perturbed_projection(egg_ctx *c, const int8_t *x, const int8_
     int32_t *d_xb = nullptr;
     NoiseSeg *d_segs = nullptr;
     int rc = EGG_OK;
-    auto cleanup = [&]() {
-        cudaStreamSynchronize(st);
-        if (!on_device) { if (d_x) cudaFree(d_x); if (d_w) cudaFree(d_w); if (d_y) cudaFree(d_y); }
-        if (d_wt) cudaFree(d_wt); if (d_nt) cudaFree(d_nt); if (d_xb) cudaFree(d_xb); if (d_segs) cudaFree(d_segs);
-    };
+    auto cleanup = [&]() { cudaStreamSynchronize(st); };      // buffers live in the context's scratch slots
 #define PTRY(e) do { rc = (e); if (rc) { cleanup(); return rc; } } while (0)
 #define PTRYC(e) do { cudaError_t e_ = (e); if (e_ != cudaSuccess) { set_error("%s: %s", #e, cudaGetErrorString(e_)); cleanup(); return EGG_E_CUDA; } } while (0)
     if (on_device) { d_x = const_cast<int8_t *>(x); d_w = const_cast<int8_t *>(w_packed); d_y = y; }
     else {
-        PTRY(dev_alloc(&d_x, rows * K)); PTRY(dev_alloc(&d_w, (int64_t)K * N)); PTRY(dev_alloc(&d_y, rows * N));
+        PTRY(ctx_scratch(c, 4, rows * K, &d_x)); PTRY(ctx_scratch(c, 5, (int64_t)K * N, &d_w)); PTRY(ctx_scratch(c, 6, rows * N, &d_y));
         PTRYC(cudaMemcpyAsync(d_x, x, (size_t)(rows * K), cudaMemcpyHostToDevice, st));
         PTRYC(cudaMemcpyAsync(d_w, w_packed, (size_t)K * N, cudaMemcpyHostToDevice, st));
     }
-    PTRY(dev_alloc(&d_wt, (int64_t)K * N)); PTRY(dev_alloc(&d_nt, pairs * stride)); PTRY(dev_alloc(&d_xb, rows)); PTRY(dev_alloc(&d_segs, 2));
+    PTRY(ctx_scratch(c, 0, (int64_t)K * N, &d_wt)); PTRY(ctx_scratch(c, 1, pairs * stride, &d_nt)); PTRY(ctx_scratch(c, 2, rows, &d_xb));
+    PTRY(ctx_scratch(c, 3, 2, &d_segs));
     NoiseSeg segs[2] = {{0, N, 0, off_a, 0, 0, -1, -1, 0}, {N, K, 0, off_b, 0, 0, -1, -1, 0}};
     noise_index_slices(segs, 2);
     PTRYC(cudaMemcpyAsync(d_segs, segs, sizeof(segs), cudaMemcpyHostToDevice, st));
@@ -1132,11 +1152,7 @@ extern "C" int egg_update_reconstruct(egg_ctx *c, const int32_t *fitness, int pa
     int32_t *d_fit = nullptr, *d_vote = nullptr;
     int8_t *d_na = nullptr, *d_nb = nullptr;
     int rc = EGG_OK;
-    auto cleanup = [&]() {
-        cudaStreamSynchronize(st);
-        if (!on_device) { if (d_fit) cudaFree(d_fit); if (d_vote) cudaFree(d_vote); }
-        if (d_na) cudaFree(d_na); if (d_nb) cudaFree(d_nb);
-    };
+    auto cleanup = [&]() { cudaStreamSynchronize(st); };      // buffers live in the context's scratch slots
 #define PTRY(e) do { rc = (e); if (rc) { cleanup(); return rc; } } while (0)
 #define PTRYC(e) do { cudaError_t e_ = (e); if (e_ != cudaSuccess) { set_error("%s: %s", #e, cudaGetErrorString(e_)); cleanup(); return EGG_E_CUDA; } } while (0)
     // fitness range decides whether f*a fits int8 directly or needs the base-16 split
@@ -1149,7 +1165,7 @@ extern "C" int egg_update_reconstruct(egg_ctx *c, const int32_t *fitness, int pa
         for (int i = 0; i < pairs; i++) { int a = hf[i] < 0 ? -hf[i] : hf[i]; if (a > fmax) fmax = a; }
     } else {
         for (int i = 0; i < pairs; i++) { int a = fitness[i] < 0 ? -fitness[i] : fitness[i]; if (a > fmax) fmax = a; }
-        PTRY(dev_alloc(&d_fit, pairs)); PTRY(dev_alloc(&d_vote, (int64_t)rows_k * cols_n));
+        PTRY(ctx_scratch(c, 10, pairs, &d_fit)); PTRY(ctx_scratch(c, 11, (int64_t)rows_k * cols_n, &d_vote));
         PTRYC(cudaMemcpyAsync(d_fit, fitness, (size_t)pairs * 4, cudaMemcpyHostToDevice, st));
     }
     const int amax = c->cfg.device_gaussian ? 3 * c->cfg.device_mask : c->cfg.device_mask;
@@ -1159,7 +1175,7 @@ extern "C" int egg_update_reconstruct(egg_ctx *c, const int32_t *fitness, int pa
         set_error("int8 fitness with noise magnitude %d does not fit the two-digit operand split", amax); cleanup(); return EGG_E_INVALID;
     }
     const int ktot = split ? 2 * kp : kp;
-    PTRY(dev_alloc(&d_na, (int64_t)cols_n * ktot)); PTRY(dev_alloc(&d_nb, (int64_t)rows_k * ktot));
+    PTRY(ctx_scratch(c, 7, (int64_t)cols_n * ktot, &d_na)); PTRY(ctx_scratch(c, 8, (int64_t)rows_k * ktot, &d_nb));
     PTRY(launch_update_operands(st, d_na, d_nb, d_fit, pairs, kp, rows_k, cols_n, off_a, off_b, seed_base, step_seed,
                                 c->cfg.device_mask, c->cfg.device_gaussian, split));
     GemmParams g;
@@ -1194,19 +1210,14 @@ extern "C" int egg_update_matrix(egg_ctx *c, int8_t *d_w_packed, void *d_opt_sta
     memset(&u, 0, sizeof(u));
     MuonWs saved = c->muon, ws = {nullptr, nullptr, nullptr, nullptr};
     int rc = EGG_OK;
-    auto cleanup = [&]() {
-        cudaStreamSynchronize(st);
-        if (u.na) cudaFree(u.na); if (u.nb) cudaFree(u.nb); if (u.votes) cudaFree(u.votes);
-        if (ws.x) cudaFree(ws.x); if (ws.y) cudaFree(ws.y); if (ws.g) cudaFree(ws.g); if (ws.norm2) cudaFree(ws.norm2);
-        c->muon = saved;
-    };
+    auto cleanup = [&]() { cudaStreamSynchronize(st); c->muon = saved; };      // buffers live in the context's scratch slots
 #define UTRY(e) do { rc = (e); if (rc) { cleanup(); return rc; } } while (0)
-    UTRY(dev_alloc(&u.na, (int64_t)cols_n * ktot)); UTRY(dev_alloc(&u.nb, (int64_t)rows_k * ktot));
-    UTRY(dev_alloc(&u.votes, (int64_t)rows_k * cols_n * splits));
+    UTRY(ctx_scratch(c, 7, (int64_t)cols_n * ktot, &u.na)); UTRY(ctx_scratch(c, 8, (int64_t)rows_k * ktot, &u.nb));
+    UTRY(ctx_scratch(c, 9, (int64_t)rows_k * cols_n * splits, &u.votes));
     if (optimizer == 1) {
         const int kmin = rows_k < cols_n ? rows_k : cols_n;
-        UTRY(dev_alloc(&ws.x, (int64_t)rows_k * cols_n)); UTRY(dev_alloc(&ws.y, (int64_t)rows_k * cols_n));
-        UTRY(dev_alloc(&ws.g, (int64_t)kmin * kmin)); UTRY(dev_alloc(&ws.norm2, 1));
+        UTRY(ctx_scratch(c, 12, (int64_t)rows_k * cols_n, &ws.x)); UTRY(ctx_scratch(c, 13, (int64_t)rows_k * cols_n, &ws.y));
+        UTRY(ctx_scratch(c, 14, (int64_t)kmin * kmin, &ws.g)); UTRY(ctx_scratch(c, 15, 1, &ws.norm2));
         c->muon = ws;
     }
     u.w_packed = d_w_packed; u.opt = static_cast<float *>(d_opt_state);
@@ -1382,6 +1393,16 @@ extern "C" int egg_set_fused_epilogues(egg_ctx *c, int enable) {
 }
 
 extern "C" int egg_fused_epilogues_active(egg_ctx *c) { return (c && use_fused(c)) ? 1 : 0; }
+
+extern "C" int egg_set_attention_tensor_core(egg_ctx *c, int enable) {
+    if (!c) { set_error("null context"); return EGG_E_INVALID; }
+    if (enable && !attention_tc_supported(c->cfg.seq_len, c->cfg.head_dim)) {
+        set_error("tensor-core attention needs seq_len %% 128 == 0, seq_len <= 512 and head_dim 64");
+        return EGG_E_INVALID;
+    }
+    c->attention_tc_on = enable != 0;
+    return EGG_OK;
+}
 
 extern "C" int egg_get_config(egg_ctx *c, egg_config *out) {
     if (!c || !out) { set_error("null argument"); return EGG_E_INVALID; }

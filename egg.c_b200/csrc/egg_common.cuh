@@ -179,6 +179,20 @@ __device__ __forceinline__ int aln_quant(int val, float scale24) {
     const int xi = __float2int_rz(__int2float_rn(val) * scale24);
     return (xi + (1 << 23) + (xi >> 31)) >> 24;
 }
+// The same value from the unscaled product p = (float)v * scale (|p| <= 127 * (1 + 2^-23)): round-half-away-from-zero is
+// trunc(p + copysign(c, p)) with c = 0.5 - 2^-25, the largest float below one half.  Take p = k + f >= 0 with integer k
+// and fraction f.  If f < 0.5, the largest such p is one ulp(p) >= 2^-25 below k + 0.5, so the exact sum p + c is at
+// least ulp(p) + 2^-25 below k + 1; the floats just below k + 1 are spaced ulp(p) (or ulp(p)/2 at a power of two) apart,
+// so the sum rounds to a float below k + 1 and truncates to k.  If f >= 0.5, the exact sum is k + 1 - 2^-25 or more;
+// for p >= 0.5 no float lies strictly between k + 1 - 2^-25 and k + 1 except at k = 0, f = 0.5, where the tie rounds to
+// the even mantissa 1.0: the sum rounds to k + 1 or above and truncates to k + 1 (f < 1 keeps it below k + 2).
+// Checked on every neighbour of every half-integer up to 127.5 and on 2*10^7 random products.
+// One logic operation and one float add in place of two shifts and a three-input add.
+__device__ __forceinline__ int aln_quant_f(int val, float scale) {
+    const float p = __int2float_rn(val) * scale;
+    const float c = __int_as_float(0x3EFFFFFF | (__float_as_int(p) & 0x80000000));
+    return __float2int_rz(p + c);
+}
 
 // ---------------------------------------------------------------- errors
 void set_error(const char *fmt, ...);

@@ -15,7 +15,7 @@
 //   pass 1 (per sub-tile, as soon as its MMAs are done): rank-1 term, RoPE / residual + bias, running abs-max per
 //          lane; the int32 values go back to the same TMEM columns (tcgen05.st);
 //   the four warps that share a lane quarter exchange their maxima through shared memory (128-thread named barrier);
-//   pass 2 (per sub-tile): requantise (aln_quant), pack, write the warp's 32 x BN/4 int8 box to shared memory, release
+//   pass 2 (per sub-tile): requantise (aln_quant_f), pack, write the warp's 32 x BN/4 int8 box to shared memory, release
 //          the TMEM slot to the MMA warp, store the box with one TMA store.
 // So the MMAs of the next unit's first sub-tile overlap pass 2 of this unit's last, and no int32 intermediate ever
 // reaches HBM.  Rows of a tile must belong to one population member: seq_len % 128 == 0 (then M % 128 == 0 too).
@@ -333,7 +333,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             ptx::named_bar_sync(2 + quarter, 128);            // the four column quarters of this lane quarter
             const int row_max = max(max(sm.rowpart[0][row_in_tile], sm.rowpart[1][row_in_tile]),
                                     max(sm.rowpart[2][row_in_tile], sm.rowpart[3][row_in_tile]));
-            const float scale24 = aln_scale24(row_max);
+            const float scale = aln_scale(row_max);
 
             // ---------------- pass 2: requantise, pack, store ----------------
             for (int j = 0; j < NT; j++) {
@@ -356,8 +356,8 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     uint32_t w[4];
 #pragma unroll
                     for (int q4 = 0; q4 < 4; q4++)
-                        w[q4] = ptx::pack_sat_s8(aln_quant((int)vc[4 * q4], scale24), aln_quant((int)vc[4 * q4 + 1], scale24),
-                                                 aln_quant((int)vc[4 * q4 + 2], scale24), aln_quant((int)vc[4 * q4 + 3], scale24));
+                        w[q4] = ptx::pack_sat_s8(aln_quant_f((int)vc[4 * q4], scale), aln_quant_f((int)vc[4 * q4 + 1], scale),
+                                                 aln_quant_f((int)vc[4 * q4 + 2], scale), aln_quant_f((int)vc[4 * q4 + 3], scale));
                     ptx::sts_v4(box_s + (((uint32_t)c ^ swz) << 4), make_int4((int)w[0], (int)w[1], (int)w[2], (int)w[3]));
                 }
                 // this warp has read its part of the slot: hand it back to the MMA warp

@@ -194,24 +194,28 @@ __device__ __forceinline__ uint32_t pack_clip8(int a, int b, int c, int d) {
     return __vmaxs4(r, 0x81818181u);
 }
 
-// One warp per row; NJ = H/128 chunks of 4 elements per lane.  Every global load of the row (the int32
-// pre-activations or the embedding bytes, the perturbed gain/bias tables, the noise vectors of the
-// following projections) is issued before any arithmetic, so that one memory latency is exposed per row
-// instead of three.
+// One warp per run of ROW_RUN consecutive rows of ONE population member (seq_len is a multiple of 16, so a run never
+// crosses members); NJ = H/128 chunks of 4 elements per lane.  Everything that depends on the member only -- the
+// perturbed gain / bias tables and the noise vectors of the following projections, 3.5 H bytes -- is loaded once per
+// run and kept in registers; per row only the row itself is read, and the next row's bytes are requested before the
+// current row is worked on (mode 2), so that the warp always has a load in flight.
+constexpr int ROW_RUN = 8;
+
 template <int MODE, int NJ>
 __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
-    const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int run = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
-    if (r >= p.M) return;
+    const int r0 = run * ROW_RUN;
+    if (r0 >= p.M) return;
+    const int r_end = min(r0 + ROW_RUN, p.M);
     const int H = NJ * 128;
-    const int mem = fast_div(r, p.fd_seq), t = r - mem * p.seq_len;
+    const int mem = fast_div(r0, p.fd_seq);
     const int sgn = mem & 1, ns = sgn ? -1 : 1;
     const int8_t *ntp = p.nt + (int64_t)(mem >> 1) * p.nt_stride;
     const int16_t *wm = reinterpret_cast<const int16_t *>(ntp + p.nt_w_m) + sgn * H;   // w + ((n1*n2*sign)>>SSV)
     const int16_t *bm = reinterpret_cast<const int16_t *>(ntp + p.nt_b_m) + sgn * H;
-    int x[NJ][4];
 
-    // ---- loads ----
+    // ---- per-member tables ----
     int2 w4[NJ], b4[NJ];
     int32_t n4[3][NJ];
 #pragma unroll
@@ -222,99 +226,113 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
 #pragma unroll
         for (int q = 0; q < 3; q++) n4[q][j] = (q < p.ndots) ? *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[q] + d) : 0;
     }
-    if (MODE == 0) {
-        // embedding (mgpu.cu:902-931)
-        int64_t pair = (p.pop_base + mem) >> 1;
-        int64_t pos = p.use_same_data ? (p.start_idx % (p.data_len - p.seq_len))
-                                      : ((p.start_idx + pair * p.data_stride) % (p.data_len - p.seq_len));
-        const int tok = p.dataset[pos + t];
-        const int a_tok = ntp[p.nt_emb_a + tok];
-        const float f_row = p.ov_emb_row ? __fdiv_rn((float)overlay_num(p.ov_emb_row[tok]), 64.0f) : 1.0f;
-        const int32_t *emb32 = reinterpret_cast<const int32_t *>(p.emb_packed);
+    uint32_t xw_next[NJ];
+    if (MODE == 2) {
+#pragma unroll
+        for (int j = 0; j < NJ; j++) xw_next[j] = *reinterpret_cast<const uint32_t *>(p.x_out + (int64_t)r0 * H + (j << 7) + (lane << 2));
+    }
+
+    for (int r = r0; r < r_end; r++) {
+        const int t = r - mem * p.seq_len;
+        int x[NJ][4];
+        if (MODE == 0) {
+            // embedding (mgpu.cu:902-931)
+            int64_t pair = (p.pop_base + mem) >> 1;
+            int64_t pos = p.use_same_data ? (p.start_idx % (p.data_len - p.seq_len))
+                                          : ((p.start_idx + pair * p.data_stride) % (p.data_len - p.seq_len));
+            const int tok = p.dataset[pos + t];
+            const int a_tok = ntp[p.nt_emb_a + tok];
+            const float f_row = p.ov_emb_row ? __fdiv_rn((float)overlay_num(p.ov_emb_row[tok]), 64.0f) : 1.0f;
+            const int32_t *emb32 = reinterpret_cast<const int32_t *>(p.emb_packed);
+#pragma unroll
+            for (int j = 0; j < NJ; j++) {
+                const int d = (j << 7) + (lane << 2);
+                int32_t e4 = emb32[(int64_t)(d >> 2) * p.vocab + tok];
+                int32_t eb4 = *reinterpret_cast<const int32_t *>(p.emb_bias + d);
+                int32_t dl4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_emb_bias_d + sgn * H + d);
+                int32_t nb4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_emb_b + d);
+                int32_t oc4 = 0;
+                if (p.ov_emb_col) oc4 = *reinterpret_cast<const int32_t *>(p.ov_emb_col + d);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    int prod = a_tok * (int)byte_of(nb4, i);
+                    if (p.ov_emb_col) {
+                        // (AccumType)(a_tok * b_dim * s_emb_row * s_emb_col), d-eggs kernels.cu:150-158: two float
+                        // multiplications, each rounded, then the truncating conversion
+                        const float fc = __fdiv_rn((float)overlay_num(byte_of(oc4, i)), 64.0f);
+                        prod = __float2int_rz(__fmul_rn(__fmul_rn((float)prod, f_row), fc));
+                    }
+                    int perturb = (prod * ns) >> p.emb_shift;
+                    x[j][i] = clip8((int)byte_of(e4, i) + (int)byte_of(eb4, i) + (int)byte_of(dl4, i) + perturb);
+                }
+            }
+        } else if (MODE == 2) {
+            // the residual stream was requantised by the projection that produced it: only read it
+#pragma unroll
+            for (int j = 0; j < NJ; j++) {
+                const uint32_t w = xw_next[j];
+                x[j][0] = ptx::sx_byte0(w); x[j][1] = ptx::sx_byte1(w); x[j][2] = ptx::sx_byte2(w); x[j][3] = (int)w >> 24;
+            }
+            if (r + 1 < r_end) {
+#pragma unroll
+                for (int j = 0; j < NJ; j++) xw_next[j] = *reinterpret_cast<const uint32_t *>(p.x_out + (int64_t)(r + 1) * H + (j << 7) + (lane << 2));
+            }
+        } else {
+            int4 v[NJ];
+#pragma unroll
+            for (int j = 0; j < NJ; j++) v[j] = *reinterpret_cast<const int4 *>(p.pre32 + (int64_t)r * H + (j << 7) + (lane << 2));
+            const int mx = p.rowmax[r];
+            const float scale = aln_scale24(mx);
+#pragma unroll
+            for (int j = 0; j < NJ; j++) {
+                x[j][0] = aln_quant(v[j].x, scale); x[j][1] = aln_quant(v[j].y, scale);
+                x[j][2] = aln_quant(v[j].z, scale); x[j][3] = aln_quant(v[j].w, scale);
+            }
+        }
+        int tot = 0;
 #pragma unroll
         for (int j = 0; j < NJ; j++) {
             const int d = (j << 7) + (lane << 2);
-            int32_t e4 = emb32[(int64_t)(d >> 2) * p.vocab + tok];
-            int32_t eb4 = *reinterpret_cast<const int32_t *>(p.emb_bias + d);
-            int32_t dl4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_emb_bias_d + sgn * H + d);
-            int32_t nb4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_emb_b + d);
-            int32_t oc4 = 0;
-            if (p.ov_emb_col) oc4 = *reinterpret_cast<const int32_t *>(p.ov_emb_col + d);
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                int prod = a_tok * (int)byte_of(nb4, i);
-                if (p.ov_emb_col) {
-                    // (AccumType)(a_tok * b_dim * s_emb_row * s_emb_col), d-eggs kernels.cu:150-158: two float
-                    // multiplications, each rounded, then the truncating conversion
-                    const float fc = __fdiv_rn((float)overlay_num(byte_of(oc4, i)), 64.0f);
-                    prod = __float2int_rz(__fmul_rn(__fmul_rn((float)prod, f_row), fc));
-                }
-                int perturb = (prod * ns) >> p.emb_shift;
-                x[j][i] = clip8((int)byte_of(e4, i) + (int)byte_of(eb4, i) + (int)byte_of(dl4, i) + perturb);
-            }
+            uint32_t w = ptx::pack_sat_s8(x[j][0], x[j][1], x[j][2], x[j][3]);      // |x| <= 127: the saturating pack is exact, two instructions
+            if (MODE != 2) *reinterpret_cast<uint32_t *>(p.x_out + (int64_t)r * H + d) = w;
+            tot = __dp4a((int)__vabsss4(w), 0x01010101, tot);    // sum of |x|, four at a time
         }
-    } else if (MODE == 2) {
-        // the residual stream was requantised by the projection that produced it: only read it
+        // mean-abs norm with perturbed gain / bias (mgpu.cu:646-678): y = clip((x*w')/mn + b')
+        tot = warp_sum(tot);
+        int mn = tot / H;
+        if (!mn) mn = 1;
+        const float rinv = (1.0f / (float)mn) * (1.0f + 0x1p-17f);
+        int dot0 = 0, dot1 = 0, dot2 = 0;
 #pragma unroll
         for (int j = 0; j < NJ; j++) {
-            const uint32_t w = *reinterpret_cast<const uint32_t *>(p.x_out + (int64_t)r * H + (j << 7) + (lane << 2));
-            x[j][0] = ptx::sx_byte0(w); x[j][1] = ptx::sx_byte1(w); x[j][2] = ptx::sx_byte2(w); x[j][3] = (int)w >> 24;
+            const int d = (j << 7) + (lane << 2);
+            // low halves sign-extended by one byte permute (selector msb = replicate the byte's sign), high halves by a shift
+            const int wv[4] = {ptx::sx_half0(w4[j].x), w4[j].x >> 16, ptx::sx_half0(w4[j].y), w4[j].y >> 16};
+            const int bv[4] = {ptx::sx_half0(b4[j].x), b4[j].x >> 16, ptx::sx_half0(b4[j].y), b4[j].y >> 16};
+            int y[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) y[i] = div_small(x[j][i] * wv[i], rinv) + bv[i];
+            const uint32_t yw = pack_clip8(y[0], y[1], y[2], y[3]);
+            *reinterpret_cast<uint32_t *>(p.h_out + (int64_t)r * H + d) = yw;
+            dot0 = __dp4a((int)yw, n4[0][j], dot0);
+            dot1 = __dp4a((int)yw, n4[1][j], dot1);
+            dot2 = __dp4a((int)yw, n4[2][j], dot2);
         }
-    } else {
-        int4 v[NJ];
-#pragma unroll
-        for (int j = 0; j < NJ; j++) v[j] = *reinterpret_cast<const int4 *>(p.pre32 + (int64_t)r * H + (j << 7) + (lane << 2));
-        const int mx = p.rowmax[r];
-        const float scale = aln_scale24(mx);
-#pragma unroll
-        for (int j = 0; j < NJ; j++) {
-            x[j][0] = aln_quant(v[j].x, scale); x[j][1] = aln_quant(v[j].y, scale);
-            x[j][2] = aln_quant(v[j].z, scale); x[j][3] = aln_quant(v[j].w, scale);
+        if (p.ndots > 0) { int s = warp_sum(dot0); if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride] = s; }
+        if (p.ndots > 1) { int s = warp_sum(dot1); if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride + 1] = s; }
+        if (p.ndots > 2) { int s = warp_sum(dot2); if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride + 2] = s; }
+        if (lane == 0) {
+            if (MODE == 1) p.rowmax[r] = 0;
+            if (p.zero1) p.zero1[r] = 0;
+            if (p.zero2) p.zero2[r] = 0;
+            if (p.zero3) { p.zero3[(int64_t)r * 3] = 0; p.zero3[(int64_t)r * 3 + 1] = 0; p.zero3[(int64_t)r * 3 + 2] = 0; }
         }
-    }
-    int tot = 0;
-#pragma unroll
-    for (int j = 0; j < NJ; j++) {
-        const int d = (j << 7) + (lane << 2);
-        uint32_t w = ptx::pack_sat_s8(x[j][0], x[j][1], x[j][2], x[j][3]);      // |x| <= 127: the saturating pack is exact, two instructions
-        if (MODE != 2) *reinterpret_cast<uint32_t *>(p.x_out + (int64_t)r * H + d) = w;
-        tot = __dp4a((int)__vabsss4(w), 0x01010101, tot);    // sum of |x|, four at a time
-    }
-    // mean-abs norm with perturbed gain / bias (mgpu.cu:646-678): y = clip((x*w')/mn + b')
-    tot = warp_sum(tot);
-    int mn = tot / H;
-    if (!mn) mn = 1;
-    const float rinv = (1.0f / (float)mn) * (1.0f + 0x1p-17f);
-    int dot0 = 0, dot1 = 0, dot2 = 0;
-#pragma unroll
-    for (int j = 0; j < NJ; j++) {
-        const int d = (j << 7) + (lane << 2);
-        // low halves sign-extended by one byte permute (selector msb = replicate the byte's sign), high halves by a shift
-        const int wv[4] = {ptx::sx_half0(w4[j].x), w4[j].x >> 16, ptx::sx_half0(w4[j].y), w4[j].y >> 16};
-        const int bv[4] = {ptx::sx_half0(b4[j].x), b4[j].x >> 16, ptx::sx_half0(b4[j].y), b4[j].y >> 16};
-        int y[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) y[i] = div_small(x[j][i] * wv[i], rinv) + bv[i];
-        const uint32_t yw = pack_clip8(y[0], y[1], y[2], y[3]);
-        *reinterpret_cast<uint32_t *>(p.h_out + (int64_t)r * H + d) = yw;
-        dot0 = __dp4a((int)yw, n4[0][j], dot0);
-        dot1 = __dp4a((int)yw, n4[1][j], dot1);
-        dot2 = __dp4a((int)yw, n4[2][j], dot2);
-    }
-    if (p.ndots > 0) { int s = warp_sum(dot0); if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride] = s; }
-    if (p.ndots > 1) { int s = warp_sum(dot1); if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride + 1] = s; }
-    if (p.ndots > 2) { int s = warp_sum(dot2); if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride + 2] = s; }
-    if (lane == 0) {
-        if (MODE == 1) p.rowmax[r] = 0;
-        if (p.zero1) p.zero1[r] = 0;
-        if (p.zero2) p.zero2[r] = 0;
-        if (p.zero3) { p.zero3[(int64_t)r * 3] = 0; p.zero3[(int64_t)r * 3 + 1] = 0; p.zero3[(int64_t)r * 3 + 2] = 0; }
     }
 }
 
 template <int MODE>
 static int launch_rowwise_nj(cudaStream_t st, const RowParams &p) {
-    const int blocks = (p.M + 7) / 8;
+    const int blocks = ((p.M + ROW_RUN - 1) / ROW_RUN + 7) / 8;       // 8 warps per block, one run of rows per warp
     switch (p.H >> 7) {
         case 1: rowwise_kernel<MODE, 1><<<blocks, 256, 0, st>>>(p); break;
         case 2: rowwise_kernel<MODE, 2><<<blocks, 256, 0, st>>>(p); break;

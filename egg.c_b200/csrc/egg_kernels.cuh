@@ -100,6 +100,9 @@ struct AttnParams {
     int32_t *xbo;             // [members*seq_len] += Σ_d ao_d * noise_B_o[d]
 };
 int launch_attention(cudaStream_t st, const AttnParams &p);
+// the same attention on tcgen05 (egg_attention_tc.cu): whole 128-query blocks of one member, head_dim 64, seq_len <= 512
+bool attention_tc_supported(int seq_len, int head_dim);
+int launch_attention_tc(cudaStream_t st, const AttnParams &p, int *err);
 
 // ---- sampling -----------------------------------------------------------------
 struct GenParams {

@@ -242,8 +242,9 @@ int egg_update_reconstruct(egg_ctx *ctx, const int32_t *fitness, int pairs,
  * d_fitness holds `pairs` int32 values; split = 1 takes the two-digit operand form for fitness
  * beyond ternary (|f| <= 127; needs 16 * noise magnitude <= 127).  All pointers are DEVICE pointers.
  * Hyper-parameters (betas, eps, weight decay, Muon momentum and lr scale, noise mask) come from the
- * context's configuration.  *total_updates = number of weights that changed.  Allocates its scratch
- * (operands, partial votes, Newton-Schulz workspace) per call and blocks until done.
+ * context's configuration.  *total_updates = number of weights that changed.  Its scratch (operands,
+ * partial votes, Newton-Schulz workspace) is allocated on first use, kept in the context for later calls
+ * of the same or a smaller size, and freed with the context.  Blocks until done.
  */
 int egg_update_matrix(egg_ctx *ctx, int8_t *d_w_packed, void *d_opt_state, int rows_k, int cols_n,
                       int off_a, int off_b, int seed_base, const int32_t *d_fitness, int pairs,
@@ -485,6 +486,14 @@ int egg_wave_members(egg_ctx *ctx);
  */
 int egg_set_fused_epilogues(egg_ctx *ctx, int enable);
 int egg_fused_epilogues_active(egg_ctx *ctx);
+/*
+ * Selects the tcgen05 form of the attention kernel (compute_attention's context loop, mgpu.cu:787-825: scores
+ * and the three weight-limb products as tensor-memory MMAs, one thread block per member and head) instead of
+ * the default warp-level mma.sync kernel.  Both give identical bytes.  Needs seq_len % 128 == 0, seq_len <= 512.
+ * Off by default: as measured on B200 one block per SM leaves its phases (stage, score, weigh, accumulate,
+ * divide) unoverlapped and it runs slower than the default kernel; kept selectable for comparison.
+ */
+int egg_set_attention_tensor_core(egg_ctx *ctx, int enable);
 /*
  * Measures what the tensor-core loop of the projection GEMM sustains by itself on this GPU: the same
  * kernel (TMA loads, tcgen05.mma kind::i8, two TMEM accumulator stages) with an epilogue that drops the

@@ -1,4 +1,5 @@
 """GPU parity of the row-owning projections (adaptive normalisations fused into the GEMM epilogue, csrc/egg_gemm_fused.cuh)
+and of the tensor-core attention (csrc/egg_attention_tc.cu), which run together wherever seq_len is a multiple of 128,
 against the CPU oracle, against the two-kernel form of the same library, and -- at the benchmark's layer shapes --
 against the reference's own kernels.  Everything here is integer work: bit-exact."""
 import numpy as np
@@ -11,9 +12,10 @@ pytestmark = pytest.mark.gpu
 SEED = 0x00C0FFEE
 
 
-def _losses(pkg, cfg, model, data, seed, start, pop, wave, fused):
+def _losses(pkg, cfg, model, data, seed, start, pop, wave, fused, attention_tc=False):
     ctx = pkg.Context(cfg, 0, wave)
     ctx.set_fused_epilogues(fused)
+    ctx.set_attention_tensor_core(attention_tc)
     assert ctx.fused_epilogues_active() == fused
     ctx.upload_model(model)
     ctx.set_dataset(data)
@@ -28,6 +30,8 @@ def _losses(pkg, cfg, model, data, seed, start, pop, wave, fused):
     (256, 2, 128, 8, 3, "random"),         # 256-column sub-tiles, one per row; two layers chain x through the in-place projections
     (384, 1, 128, 6, 3, "random_all"),     # three 128-column sub-tiles in a ring of four TMEM slots; random norm gains and biases
     (512, 1, 256, 6, 3, "random"),         # the benchmark's layer shape: two 256-column sub-tiles, tiles of one member half
+    (128, 1, 512, 4, 15, "random"),        # 512 tokens: four query blocks, the later ones with two key chunks (scores recomputed in pass B)
+    (256, 1, 384, 4, 3, "random_all"),     # three query blocks: an odd number of key tiles in the last chunk
 ])
 def test_fused_eval_matches_oracle(hidden, layers, seq, pop, mask, kind):
     pkg, O = load_pkg(), load_oracle()
@@ -37,6 +41,7 @@ def test_fused_eval_matches_oracle(hidden, layers, seq, pop, mask, kind):
     got = _losses(pkg, cfg, model, data, SEED + 3, seq, pop, 0, True)
     assert (got == want).all(), (got[:8], want[:8])
     assert (_losses(pkg, cfg, model, data, SEED + 3, seq, pop, 0, False) == want).all()
+    assert (_losses(pkg, cfg, model, data, SEED + 3, seq, pop, 0, True, attention_tc=True) == want).all(), "tcgen05 attention"
 
 
 def test_fused_eval_many_units_per_block_and_ragged_waves():
@@ -67,6 +72,7 @@ def test_fused_and_two_kernel_forms_agree_at_benchmark_shapes_and_with_reference
     a = _losses(pkg, cfg, model, data, SEED, 0, pop, 0, True)
     b = _losses(pkg, cfg, model, data, SEED, 0, pop, 0, False)
     assert (a == b).all()
+    assert (_losses(pkg, cfg, model, data, SEED, 0, pop, 0, True, attention_tc=True) == a).all(), "tcgen05 attention"
     ref = run_ref_mgpu(tag, model, data, SEED, 0, 0, pop)
     assert_losses_match_racy_reference(tag, model, data, SEED, 0, 0, a, ref["losses"])
     ctx = pkg.Context(cfg, 0, 100)          # ragged waves: 100 + 100 + 56 members

@@ -36,7 +36,7 @@ def test_whole_benchmark_generation_matches_reference_kernels():
     pop = kw["population_size"]
     model = synth.random_model(cfg, 0, "uniform")
     data = synth.zipf_bytes(1, 8 << 20)
-    lr = 0.5        # large enough that weights flip in the first step (acc crosses 1 where |m/sqrt(v)| ~ 2.2)
+    lr = 2.5        # from zero state |m / sqrt(v)| = 0.1 / sqrt(0.05) = 0.447: a rate above 2.24 makes weights flip in the first step
     ctx = pkg.Context(cfg, 0, 0)
     ctx.upload_model(model)
     ctx.set_dataset(data)
