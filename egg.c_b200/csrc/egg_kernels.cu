@@ -201,7 +201,7 @@ __device__ __forceinline__ uint32_t pack_clip8(int a, int b, int c, int d) {
 // current row is worked on (mode 2), so that the warp always has a load in flight.
 constexpr int ROW_RUN = 8;
 
-template <int MODE, int NJ>
+template <int MODE, int NJ, int NDOTS>
 __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
     const int run = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -215,16 +215,19 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
     const int16_t *wm = reinterpret_cast<const int16_t *>(ntp + p.nt_w_m) + sgn * H;   // w + ((n1*n2*sign)>>SSV)
     const int16_t *bm = reinterpret_cast<const int16_t *>(ntp + p.nt_b_m) + sgn * H;
 
-    // ---- per-member tables ----
-    int2 w4[NJ], b4[NJ];
-    int32_t n4[3][NJ];
+    // ---- per-member tables: gains and biases widened once per run, not once per row ----
+    int wv[NJ][4], bv[NJ][4];
+    int32_t n4[NDOTS][NJ];
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
         const int d = (j << 7) + (lane << 2);
-        w4[j] = *reinterpret_cast<const int2 *>(wm + d);
-        b4[j] = *reinterpret_cast<const int2 *>(bm + d);
+        const int2 w4 = *reinterpret_cast<const int2 *>(wm + d);
+        const int2 b4 = *reinterpret_cast<const int2 *>(bm + d);
+        // low halves sign-extended by one byte permute (selector msb = replicate the byte's sign), high halves by a shift
+        wv[j][0] = ptx::sx_half0(w4.x); wv[j][1] = w4.x >> 16; wv[j][2] = ptx::sx_half0(w4.y); wv[j][3] = w4.y >> 16;
+        bv[j][0] = ptx::sx_half0(b4.x); bv[j][1] = b4.x >> 16; bv[j][2] = ptx::sx_half0(b4.y); bv[j][3] = b4.y >> 16;
 #pragma unroll
-        for (int q = 0; q < 3; q++) n4[q][j] = (q < p.ndots) ? *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[q] + d) : 0;
+        for (int q = 0; q < NDOTS; q++) n4[q][j] = *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[q] + d);
     }
     uint32_t xw_next[NJ];
     if (MODE == 2) {
@@ -302,25 +305,25 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
         int mn = tot / H;
         if (!mn) mn = 1;
         const float rinv = (1.0f / (float)mn) * (1.0f + 0x1p-17f);
-        int dot0 = 0, dot1 = 0, dot2 = 0;
+        int dot[NDOTS];
+#pragma unroll
+        for (int q = 0; q < NDOTS; q++) dot[q] = 0;
 #pragma unroll
         for (int j = 0; j < NJ; j++) {
             const int d = (j << 7) + (lane << 2);
-            // low halves sign-extended by one byte permute (selector msb = replicate the byte's sign), high halves by a shift
-            const int wv[4] = {ptx::sx_half0(w4[j].x), w4[j].x >> 16, ptx::sx_half0(w4[j].y), w4[j].y >> 16};
-            const int bv[4] = {ptx::sx_half0(b4[j].x), b4[j].x >> 16, ptx::sx_half0(b4[j].y), b4[j].y >> 16};
             int y[4];
 #pragma unroll
-            for (int i = 0; i < 4; i++) y[i] = div_small(x[j][i] * wv[i], rinv) + bv[i];
+            for (int i = 0; i < 4; i++) y[i] = div_small(x[j][i] * wv[j][i], rinv) + bv[j][i];
             const uint32_t yw = pack_clip8(y[0], y[1], y[2], y[3]);
             *reinterpret_cast<uint32_t *>(p.h_out + (int64_t)r * H + d) = yw;
-            dot0 = __dp4a((int)yw, n4[0][j], dot0);
-            dot1 = __dp4a((int)yw, n4[1][j], dot1);
-            dot2 = __dp4a((int)yw, n4[2][j], dot2);
+#pragma unroll
+            for (int q = 0; q < NDOTS; q++) dot[q] = __dp4a((int)yw, n4[q][j], dot[q]);
         }
-        if (p.ndots > 0) { int s = warp_sum(dot0); if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride] = s; }
-        if (p.ndots > 1) { int s = warp_sum(dot1); if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride + 1] = s; }
-        if (p.ndots > 2) { int s = warp_sum(dot2); if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride + 2] = s; }
+#pragma unroll
+        for (int q = 0; q < NDOTS; q++) {
+            const int s = warp_sum(dot[q]);
+            if (lane == 0) p.xb_out[(int64_t)r * p.xb_stride + q] = s;
+        }
         if (lane == 0) {
             if (MODE == 1) p.rowmax[r] = 0;
             if (p.zero1) p.zero1[r] = 0;
@@ -330,18 +333,18 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
     }
 }
 
-template <int MODE>
+template <int MODE, int NDOTS>
 static int launch_rowwise_nj(cudaStream_t st, const RowParams &p) {
     const int blocks = ((p.M + ROW_RUN - 1) / ROW_RUN + 7) / 8;       // 8 warps per block, one run of rows per warp
     switch (p.H >> 7) {
-        case 1: rowwise_kernel<MODE, 1><<<blocks, 256, 0, st>>>(p); break;
-        case 2: rowwise_kernel<MODE, 2><<<blocks, 256, 0, st>>>(p); break;
-        case 3: rowwise_kernel<MODE, 3><<<blocks, 256, 0, st>>>(p); break;
-        case 4: rowwise_kernel<MODE, 4><<<blocks, 256, 0, st>>>(p); break;
-        case 5: rowwise_kernel<MODE, 5><<<blocks, 256, 0, st>>>(p); break;
-        case 6: rowwise_kernel<MODE, 6><<<blocks, 256, 0, st>>>(p); break;
-        case 7: rowwise_kernel<MODE, 7><<<blocks, 256, 0, st>>>(p); break;
-        case 8: rowwise_kernel<MODE, 8><<<blocks, 256, 0, st>>>(p); break;
+        case 1: rowwise_kernel<MODE, 1, NDOTS><<<blocks, 256, 0, st>>>(p); break;
+        case 2: rowwise_kernel<MODE, 2, NDOTS><<<blocks, 256, 0, st>>>(p); break;
+        case 3: rowwise_kernel<MODE, 3, NDOTS><<<blocks, 256, 0, st>>>(p); break;
+        case 4: rowwise_kernel<MODE, 4, NDOTS><<<blocks, 256, 0, st>>>(p); break;
+        case 5: rowwise_kernel<MODE, 5, NDOTS><<<blocks, 256, 0, st>>>(p); break;
+        case 6: rowwise_kernel<MODE, 6, NDOTS><<<blocks, 256, 0, st>>>(p); break;
+        case 7: rowwise_kernel<MODE, 7, NDOTS><<<blocks, 256, 0, st>>>(p); break;
+        case 8: rowwise_kernel<MODE, 8, NDOTS><<<blocks, 256, 0, st>>>(p); break;
         default: set_error("hidden_dim %d unsupported by the row-wise kernel", p.H); return EGG_E_INVALID;
     }
     EGG_CUDA(cudaGetLastError());
@@ -351,7 +354,9 @@ static int launch_rowwise_nj(cudaStream_t st, const RowParams &p) {
 int launch_rowwise(cudaStream_t st, const RowParams &p_in, int mode) {
     RowParams p = p_in;
     p.fd_seq = make_fastdiv(p.seq_len);
-    return mode == 0 ? launch_rowwise_nj<0>(st, p) : (mode == 1 ? launch_rowwise_nj<1>(st, p) : launch_rowwise_nj<2>(st, p));
+    if (p.ndots != 1 && p.ndots != 3) { set_error("row-wise kernel computes one or three row dots, not %d", p.ndots); return EGG_E_INVALID; }
+    if (p.ndots == 1) return mode == 0 ? launch_rowwise_nj<0, 1>(st, p) : (mode == 1 ? launch_rowwise_nj<1, 1>(st, p) : launch_rowwise_nj<2, 1>(st, p));
+    return mode == 0 ? launch_rowwise_nj<0, 3>(st, p) : (mode == 1 ? launch_rowwise_nj<1, 3>(st, p) : launch_rowwise_nj<2, 3>(st, p));
 }
 
 // Row dots under adaptive-noise overlays (d-eggs/include/model/layers.cuh:250, 272-280, 339-341, 396):
