@@ -752,7 +752,7 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
     RowParams r0 = base_row(c, M);
     r0.dataset = c->d_data; r0.data_len = c->data_len; r0.start_idx = start_idx; r0.data_stride = data_stride;
     r0.pop_base = pop_base; r0.use_same_data = cf.use_same_data;
-    r0.emb_packed = mdl + L.embedding; r0.emb_bias = mdl + L.emb_bias; r0.vocab = V;
+    r0.emb_rows = sh + c->so.emb; r0.emb_bias = mdl + L.emb_bias; r0.vocab = V;
     r0.nt_emb_a = nm.emb_a; r0.nt_emb_b = nm.emb_b; r0.nt_emb_bias_d = nm.emb_bias_d; r0.emb_shift = cf.fixed_point + cf.sigma_shift;
     r0.nt_w_m = nm.ln_init.w_m; r0.nt_b_m = nm.ln_init.b_m;
     r0.ndots = 1; r0.nt_dot[0] = nm.mlp_init.up_b;

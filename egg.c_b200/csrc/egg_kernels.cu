@@ -229,6 +229,21 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
 #pragma unroll
         for (int q = 0; q < NDOTS; q++) n4[q][j] = *reinterpret_cast<const int32_t *>(ntp + p.nt_dot[q] + d);
     }
+    // embedding mode: bias + bias-noise delta, the B-noise of the embedding's rank-1 term and the column overlays of the run's member
+    int emb_add[MODE == 0 ? NJ : 1][4];
+    int32_t emb_nb[MODE == 0 ? NJ : 1], emb_oc[MODE == 0 ? NJ : 1];
+    if (MODE == 0) {
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+            const int d = (j << 7) + (lane << 2);
+            const int32_t eb4 = *reinterpret_cast<const int32_t *>(p.emb_bias + d);
+            const int32_t dl4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_emb_bias_d + sgn * H + d);
+#pragma unroll
+            for (int i = 0; i < 4; i++) emb_add[j][i] = (int)byte_of(eb4, i) + (int)byte_of(dl4, i);
+            emb_nb[j] = *reinterpret_cast<const int32_t *>(ntp + p.nt_emb_b + d);
+            emb_oc[j] = p.ov_emb_col ? *reinterpret_cast<const int32_t *>(p.ov_emb_col + d) : 0;
+        }
+    }
     uint32_t xw_next[NJ];
     if (MODE == 2) {
 #pragma unroll
@@ -239,34 +254,30 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
         const int t = r - mem * p.seq_len;
         int x[NJ][4];
         if (MODE == 0) {
-            // embedding (mgpu.cu:902-931)
+            // embedding (mgpu.cu:902-931): the token's row comes from the token-major copy of the table ([V][H], the same
+            // K-major shadow the head projection multiplies with), 4 contiguous bytes per lane and chunk
             int64_t pair = (p.pop_base + mem) >> 1;
             int64_t pos = p.use_same_data ? (p.start_idx % (p.data_len - p.seq_len))
                                           : ((p.start_idx + pair * p.data_stride) % (p.data_len - p.seq_len));
             const int tok = p.dataset[pos + t];
             const int a_tok = ntp[p.nt_emb_a + tok];
             const float f_row = p.ov_emb_row ? __fdiv_rn((float)overlay_num(p.ov_emb_row[tok]), 64.0f) : 1.0f;
-            const int32_t *emb32 = reinterpret_cast<const int32_t *>(p.emb_packed);
+            const int8_t *erow = p.emb_rows + (int64_t)tok * H;
 #pragma unroll
             for (int j = 0; j < NJ; j++) {
                 const int d = (j << 7) + (lane << 2);
-                int32_t e4 = emb32[(int64_t)(d >> 2) * p.vocab + tok];
-                int32_t eb4 = *reinterpret_cast<const int32_t *>(p.emb_bias + d);
-                int32_t dl4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_emb_bias_d + sgn * H + d);
-                int32_t nb4 = *reinterpret_cast<const int32_t *>(ntp + p.nt_emb_b + d);
-                int32_t oc4 = 0;
-                if (p.ov_emb_col) oc4 = *reinterpret_cast<const int32_t *>(p.ov_emb_col + d);
+                const int32_t e4 = *reinterpret_cast<const int32_t *>(erow + d);
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    int prod = a_tok * (int)byte_of(nb4, i);
+                    int prod = a_tok * (int)byte_of(emb_nb[j], i);
                     if (p.ov_emb_col) {
                         // (AccumType)(a_tok * b_dim * s_emb_row * s_emb_col), d-eggs kernels.cu:150-158: two float
                         // multiplications, each rounded, then the truncating conversion
-                        const float fc = __fdiv_rn((float)overlay_num(byte_of(oc4, i)), 64.0f);
+                        const float fc = __fdiv_rn((float)overlay_num(byte_of(emb_oc[j], i)), 64.0f);
                         prod = __float2int_rz(__fmul_rn(__fmul_rn((float)prod, f_row), fc));
                     }
                     int perturb = (prod * ns) >> p.emb_shift;
-                    x[j][i] = clip8((int)byte_of(e4, i) + (int)byte_of(eb4, i) + (int)byte_of(dl4, i) + perturb);
+                    x[j][i] = clip8((int)byte_of(e4, i) + emb_add[j][i] + perturb);
                 }
             }
         } else if (MODE == 2) {
@@ -1011,6 +1022,83 @@ __global__ void __launch_bounds__(256) sgemm_strided_kernel(const float *A, int6
         }
 }
 
+// The same product for shapes that are multiples of 128 (every Muon matrix is): 128 x 128 tile, 16-deep steps, 256 threads
+// x (8 x 8) outputs, operands staged k-major in shared memory so that both micro-tile reads are 128-bit, the next step's
+// global loads in flight while the current one is multiplied.  Each output keeps ONE accumulator fed in ascending t by
+// fused multiply-adds, exactly as sgemm_strided_kernel does: the two kernels give identical bits.
+// a_kc / b_kc: the operand's contraction index is the contiguous one in memory (else its row / column index is).
+template <bool A_KC, bool B_KC>
+__global__ void __launch_bounds__(256, 2) sgemm128_kernel(const float *__restrict__ A, int64_t lda, const float *__restrict__ B, int64_t ldb,
+                                                       float *__restrict__ C, int Nn, int Kk, float alpha, int three_i_minus) {
+    __shared__ __align__(16) float sa[2][16][128 + 4], sb[2][16][128 + 4];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int i0 = blockIdx.y * 128, j0 = blockIdx.x * 128;
+    float acc[8][8];
+#pragma unroll
+    for (int u = 0; u < 8; u++)
+#pragma unroll
+        for (int w = 0; w < 8; w++) acc[u][w] = 0.0f;
+    // each thread moves two float4 per operand and step
+    float4 ra[2], rb[2];
+    auto gload = [&](int t0) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int e = tid + h * 256;                    // 0..511
+            if (A_KC) { const int i = e >> 2, t4 = (e & 3) * 4; ra[h] = *reinterpret_cast<const float4 *>(A + (int64_t)(i0 + i) * lda + t0 + t4); }
+            else { const int t = e >> 5, i4 = (e & 31) * 4; ra[h] = *reinterpret_cast<const float4 *>(A + (int64_t)(t0 + t) * lda + i0 + i4); }
+            if (B_KC) { const int j = e >> 2, t4 = (e & 3) * 4; rb[h] = *reinterpret_cast<const float4 *>(B + (int64_t)(j0 + j) * ldb + t0 + t4); }
+            else { const int t = e >> 5, j4 = (e & 31) * 4; rb[h] = *reinterpret_cast<const float4 *>(B + (int64_t)(t0 + t) * ldb + j0 + j4); }
+        }
+    };
+    auto sstore = [&](int buf) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int e = tid + h * 256;
+            if (A_KC) { const int i = e >> 2, t4 = (e & 3) * 4; sa[buf][t4][i] = ra[h].x; sa[buf][t4 + 1][i] = ra[h].y; sa[buf][t4 + 2][i] = ra[h].z; sa[buf][t4 + 3][i] = ra[h].w; }
+            else { const int t = e >> 5, i4 = (e & 31) * 4; *reinterpret_cast<float4 *>(&sa[buf][t][i4]) = ra[h]; }
+            if (B_KC) { const int j = e >> 2, t4 = (e & 3) * 4; sb[buf][t4][j] = rb[h].x; sb[buf][t4 + 1][j] = rb[h].y; sb[buf][t4 + 2][j] = rb[h].z; sb[buf][t4 + 3][j] = rb[h].w; }
+            else { const int t = e >> 5, j4 = (e & 31) * 4; *reinterpret_cast<float4 *>(&sb[buf][t][j4]) = rb[h]; }
+        }
+    };
+    gload(0);
+    sstore(0);
+    __syncthreads();
+    int buf = 0;
+    for (int t0 = 0; t0 < Kk; t0 += 16) {
+        if (t0 + 16 < Kk) gload(t0 + 16);
+#pragma unroll
+        for (int t = 0; t < 16; t++) {
+            const float4 a0 = *reinterpret_cast<const float4 *>(&sa[buf][t][ty * 8]), a1 = *reinterpret_cast<const float4 *>(&sa[buf][t][ty * 8 + 4]);
+            const float4 b0 = *reinterpret_cast<const float4 *>(&sb[buf][t][tx * 8]), b1 = *reinterpret_cast<const float4 *>(&sb[buf][t][tx * 8 + 4]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+#pragma unroll
+                for (int w = 0; w < 8; w++) acc[u][w] = fmaf(a[u], b[w], acc[u][w]);
+        }
+        if (t0 + 16 < Kk) {
+            sstore(buf ^ 1);
+            __syncthreads();
+            buf ^= 1;
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+        const int i = i0 + ty * 8 + u;
+        float o[8];
+#pragma unroll
+        for (int w = 0; w < 8; w++) {
+            const int j = j0 + tx * 8 + w;
+            float val = alpha * acc[u][w];
+            if (three_i_minus) val = (i == j) ? 3.0f - val : -val;     // muon_newton_schulz_term_kernel, muon_internal.cuh:91-109
+            o[w] = val;
+        }
+        *reinterpret_cast<float4 *>(C + (int64_t)i * Nn + j0 + tx * 8) = make_float4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<float4 *>(C + (int64_t)i * Nn + j0 + tx * 8 + 4) = make_float4(o[4], o[5], o[6], o[7]);
+    }
+}
+
 int launch_newton_schulz(cudaStream_t st, const MuonWs &ws, int rows, int cols) {
     const int64_t n = (int64_t)rows * cols;
     const bool use_rows = rows < cols;
@@ -1019,17 +1107,29 @@ int launch_newton_schulz(cudaStream_t st, const MuonWs &ws, int rows, int cols) 
     sumsq_kernel<<<256, 256, 0, st>>>(ws.x, n, ws.norm2);
     scale_by_norm_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ws.x, n, ws.norm2);
     float *x = ws.x, *y = ws.y;
+    const bool big = rows % 128 == 0 && cols % 128 == 0;       // every Muon matrix of a valid configuration
     for (int it = 0; it < 5; it++) {
-        dim3 gg((K + 63) / 64, (K + 63) / 64);
-        if (use_rows)   // G = X X^T : A(i,t)=X[i][t], B(t,j)=X[j][t]
-            sgemm_strided_kernel<<<gg, 256, 0, st>>>(x, cols, 1, x, 1, cols, ws.g, K, K, cols, 1.0f, 1);
-        else            // G = X^T X : A(i,t)=X[t][i], B(t,j)=X[t][j]
-            sgemm_strided_kernel<<<gg, 256, 0, st>>>(x, 1, cols, x, cols, 1, ws.g, K, K, rows, 1.0f, 1);
-        dim3 gy((cols + 63) / 64, (rows + 63) / 64);
-        if (use_rows)   // Y = 0.5 * B X
-            sgemm_strided_kernel<<<gy, 256, 0, st>>>(ws.g, K, 1, x, cols, 1, y, rows, cols, K, 0.5f, 0);
-        else            // Y = 0.5 * X B
-            sgemm_strided_kernel<<<gy, 256, 0, st>>>(x, cols, 1, ws.g, K, 1, y, rows, cols, K, 0.5f, 0);
+        if (big) {
+            dim3 gg(K / 128, K / 128), gy(cols / 128, rows / 128);
+            if (use_rows) {     // G = X X^T : A(i,t)=X[i][t], B(t,j)=X[j][t] ; Y = 0.5 * G' X
+                sgemm128_kernel<true, true><<<gg, 256, 0, st>>>(x, cols, x, cols, ws.g, K, cols, 1.0f, 1);
+                sgemm128_kernel<true, false><<<gy, 256, 0, st>>>(ws.g, K, x, cols, y, cols, K, 0.5f, 0);
+            } else {            // G = X^T X : A(i,t)=X[t][i], B(t,j)=X[t][j] ; Y = 0.5 * X G'
+                sgemm128_kernel<false, false><<<gg, 256, 0, st>>>(x, cols, x, cols, ws.g, K, rows, 1.0f, 1);
+                sgemm128_kernel<true, false><<<gy, 256, 0, st>>>(x, cols, ws.g, K, y, cols, K, 0.5f, 0);
+            }
+        } else {
+            dim3 gg((K + 63) / 64, (K + 63) / 64);
+            if (use_rows)   // G = X X^T : A(i,t)=X[i][t], B(t,j)=X[j][t]
+                sgemm_strided_kernel<<<gg, 256, 0, st>>>(x, cols, 1, x, 1, cols, ws.g, K, K, cols, 1.0f, 1);
+            else            // G = X^T X : A(i,t)=X[t][i], B(t,j)=X[t][j]
+                sgemm_strided_kernel<<<gg, 256, 0, st>>>(x, 1, cols, x, cols, 1, ws.g, K, K, rows, 1.0f, 1);
+            dim3 gy((cols + 63) / 64, (rows + 63) / 64);
+            if (use_rows)   // Y = 0.5 * B X
+                sgemm_strided_kernel<<<gy, 256, 0, st>>>(ws.g, K, 1, x, cols, 1, y, rows, cols, K, 0.5f, 0);
+            else            // Y = 0.5 * X B
+                sgemm_strided_kernel<<<gy, 256, 0, st>>>(x, cols, 1, ws.g, K, 1, y, rows, cols, K, 0.5f, 0);
+        }
         float *tmp = x; x = y; y = tmp;
     }
     // five swaps: the result lives in ws.y; copy back so callers always read ws.x

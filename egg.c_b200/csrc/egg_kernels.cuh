@@ -52,7 +52,8 @@ struct RowParams {
     const int8_t *nt; int64_t nt_stride;
     // source: embedding (mode 0), adaptive layer normalise of pre32 (mode 1), or the finished int8 stream (mode 2)
     const uint8_t *dataset; int64_t data_len, start_idx, data_stride; int pop_base, use_same_data;
-    const int8_t *emb_packed; const int8_t *emb_bias; int vocab;
+    const int8_t *emb_rows;      // token-major copy of the embedding, [vocab][H] (the K-major shadow of the tied head)
+    const int8_t *emb_bias; int vocab;
     int nt_emb_a, nt_emb_b, nt_emb_bias_d, emb_shift;
     const int8_t *ov_emb_row, *ov_emb_col;   // adaptive-noise overlays of the embedding ([vocab], [H]) or null
     const int32_t *pre32; int32_t *rowmax;
