@@ -207,6 +207,6 @@ void set_error(const char *fmt, ...);
     } while (0)
 
 // device-side error record: flag[0] = code (0 ok), flag[1] = where
-enum DevErr { DEV_OK = 0, DEV_TIMEOUT_FULL = 1, DEV_TIMEOUT_EMPTY = 2, DEV_TIMEOUT_TMEM_FULL = 3, DEV_TIMEOUT_TMEM_EMPTY = 4 };
+enum DevErr { DEV_OK = 0, DEV_TIMEOUT_FULL = 1, DEV_TIMEOUT_EMPTY = 2, DEV_TIMEOUT_TMEM_FULL = 3, DEV_TIMEOUT_TMEM_EMPTY = 4, DEV_TIMEOUT_PEER = 5 };
 
 }  // namespace egg

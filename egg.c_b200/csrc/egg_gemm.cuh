@@ -13,6 +13,13 @@
 #include "egg_common.cuh"
 #include "egg_ptx.cuh"
 
+// Additions of the evaluation epilogues issued as multiply-adds (define EGG_PLAIN_ADDS to compare against plain adds).
+#ifdef EGG_PLAIN_ADDS
+#define GEMM_FMA_ADDS 0
+#else
+#define GEMM_FMA_ADDS 1
+#endif
+
 namespace egg {
 
 constexpr int GEMM_BM = 128;
@@ -78,6 +85,7 @@ struct GemmParams {
     // divisors of the per-tile index arithmetic (filled by launch_gemm)
     FastDiv fd_seq, fd_tiles_n, fd_third, fd_head;
     int lut_stride;              // bytes between entries of the replicated GELU table (filled by launch_gemm)
+    int one;                     // 1 (filled by launch_gemm): the multiplier of additions issued as multiply-adds
 };
 
 template <int BN>
@@ -189,11 +197,13 @@ __device__ __forceinline__ void tab_store(const GemmParams &p, GemmSmem<BN> &sm,
     else *reinterpret_cast<int32_t *>(&sm.a_tab[sl][j]) = w.a;
     if ((EPI == EPI_GELU || EPI == EPI_PRE32) && RPL) {
         int vp[4], vn[4];
+        // GELU: shifted once more so that the sum joins the rank-1 product before its shift (see epilogue_rpl)
+        const int tsh = p.out_shift + ((EPI == EPI_GELU && GEMM_FMA_ADDS) ? p.rank1_shift : 0);
 #pragma unroll
         for (int b = 0; b < 4; b++) {
             const int bb = (int)(int8_t)(w.b >> (8 * b));
-            vp[b] = (bb + (int)(int8_t)(w.cp >> (8 * b))) << p.out_shift;
-            vn[b] = (bb + (int)(int8_t)(w.cn >> (8 * b))) << p.out_shift;
+            vp[b] = (bb + (int)(int8_t)(w.cp >> (8 * b))) << tsh;
+            vn[b] = (bb + (int)(int8_t)(w.cn >> (8 * b))) << tsh;
         }
         *reinterpret_cast<int4 *>(&sm.rpl.bcs32[sl][0][j]) = make_int4(vp[0], vp[1], vp[2], vp[3]);
         *reinterpret_cast<int4 *>(&sm.rpl.bcs32[sl][1][j]) = make_int4(vn[0], vn[1], vn[2], vn[3]);
@@ -261,10 +271,31 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
         for (int q4 = 0; q4 < 4; q4++) {
             const int col = 16 * c + 4 * q4;
             const int4 an = ptx::lds_v4(a32 + 4 * col);
-            int x0 = (int)vc[4 * q4] + ((xbs * an.x) >> p.rank1_shift);
-            int x1 = (int)vc[4 * q4 + 1] + ((xbs * an.y) >> p.rank1_shift);
-            int x2 = (int)vc[4 * q4 + 2] + ((xbs * an.z) >> p.rank1_shift);
-            int x3 = (int)vc[4 * q4 + 3] + ((xbs * an.w) >> p.rank1_shift);
+            int x0, x1, x2, x3;
+            if (EPI == EPI_GELU && GEMM_FMA_ADDS) {
+                // (((acc + r1) >> s) + b) with r1 = (xb*a) >> t  ==  (acc + ((xb*a + (b << (s+t))) >> t)) >> s.  The adds are issued
+                // as multiply-adds (the bias joins the rank-1 product, the accumulator is added with a run-time multiplier
+                // of 1): the integer pipe runs at half the rate of the multiply-add pipe and is the busy one here.
+                const int4 b4 = ptx::lds_v4(bcs + 4 * col);
+                x0 = ((xbs * an.x + b4.x) >> p.rank1_shift) * p.one + (int)vc[4 * q4];
+                x1 = ((xbs * an.y + b4.y) >> p.rank1_shift) * p.one + (int)vc[4 * q4 + 1];
+                x2 = ((xbs * an.z + b4.z) >> p.rank1_shift) * p.one + (int)vc[4 * q4 + 2];
+                x3 = ((xbs * an.w + b4.w) >> p.rank1_shift) * p.one + (int)vc[4 * q4 + 3];
+                // saturate to [-128, 127] while packing; the table entry of -128 holds the value of -127 (the reference's clip)
+                const uint32_t z = ptx::pack_sat_s8(x0 >> p.out_shift, x1 >> p.out_shift, x2 >> p.out_shift, x3 >> p.out_shift);
+                // word (idx, lane) of the replicated table: 32-bit shared address = base + idx * 128, one dot-product
+                // instruction per byte (the other three bytes meet a zero)
+                const uint32_t u0 = ptx::lds_u32(__dp4a(z, lut_stride, lut_base)), u1 = ptx::lds_u32(__dp4a(z, lut_stride << 8, lut_base));
+                const uint32_t u2 = ptx::lds_u32(__dp4a(z, lut_stride << 16, lut_base)), u3 = ptx::lds_u32(__dp4a(z, lut_stride << 24, lut_base));
+                const uint32_t w = __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
+                racc = __dp4a((int)w, *reinterpret_cast<const int32_t *>(dt + col), racc);
+                outw[q4] = w;
+                continue;
+            }
+            x0 = (int)vc[4 * q4] + ((xbs * an.x) >> p.rank1_shift);
+            x1 = (int)vc[4 * q4 + 1] + ((xbs * an.y) >> p.rank1_shift);
+            x2 = (int)vc[4 * q4 + 2] + ((xbs * an.z) >> p.rank1_shift);
+            x3 = (int)vc[4 * q4 + 3] + ((xbs * an.w) >> p.rank1_shift);
             if (EPI == EPI_GELU) {
                 // ((acc + r1) >> s) + b  ==  (acc + r1 + (b << s)) >> s
                 const int4 b4 = ptx::lds_v4(bcs + 4 * col);
@@ -272,8 +303,6 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                 const uint32_t z = ptx::pack_sat_s8((x0 + b4.x) >> p.out_shift, (x1 + b4.y) >> p.out_shift, (x2 + b4.z) >> p.out_shift,
                                                     (x3 + b4.w) >> p.out_shift);
                 // word (idx, lane) of the replicated table: 32-bit shared address = base + idx * 128
-                // one integer-pipe instruction to isolate each byte, then index * 128 + base as a multiply-add with a
-                // run-time multiplier (kept a multiply: that pipe has room, the integer pipe is the busy one)
                 const uint32_t u0 = ptx::lds_u32((z & 0xFFu) * lut_stride + lut_base), u1 = ptx::lds_u32(__byte_perm(z, 0, 0x4441) * lut_stride + lut_base);
                 const uint32_t u2 = ptx::lds_u32(__byte_perm(z, 0, 0x4442) * lut_stride + lut_base), u3 = ptx::lds_u32((z >> 24) * lut_stride + lut_base);
                 const uint32_t w = __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);

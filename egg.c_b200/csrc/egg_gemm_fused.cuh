@@ -30,7 +30,10 @@ namespace egg {
 enum FusedMode { FUSED_QKV = 0, FUSED_RES = 1 };
 
 struct FusedParams {
-    int M, H, K;                 // rows (multiple of 128), width of one part (multiple of BN, <= 512), contraction
+    int M, H, K;                 // rows (multiple of 128), width of one part, contraction
+    int cl;                      // thread blocks that share a unit (1 or 2, = the cluster size of the launch): each owns
+                                 // H/cl <= 512 columns of the unit's rows and the row maxima are exchanged through the
+                                 // peer's shared memory
     int parts;                   // 3 (q, k, v: B is [3H][K]) or 1
     int seq_len;                 // multiple of 128
     const int8_t *nt;            // per-pair noise table of this wave
@@ -40,6 +43,7 @@ struct FusedParams {
     const int32_t *xb;           // Σ_k a_k b_k per row and part: xb[r * xb_stride + part]
     int xb_stride;
     int rank1_shift, out_shift;
+    int one;                     // 1 (filled by launch_gemm_fused): the multiplier of additions issued as multiply-adds
     const int8_t *bias;          // FUSED_RES: [H] or null
     const int2 *rope_t;          // [head_dim/2][seq_len] (cos, sin)
     int head_dim, rope_bit;
@@ -61,6 +65,8 @@ struct FusedSmem {
     alignas(16) int32_t a32[2][FUSED_MAX_H];            // A-noise of the unit (double-buffered across units)
     alignas(16) int32_t bcs32[2][FUSED_MAX_H];          // (bias + bias-noise delta of the member's sign) << out_shift
     alignas(16) int32_t rowpart[4][GEMM_BM];            // per-row abs-max of each column quarter
+    alignas(16) int32_t peer_max[2][GEMM_BM];           // per-row abs-max of the peer block's columns (written by the peer)
+    alignas(8) uint64_t xbar[2];                        // arrival of the peer's maxima, one barrier per unit parity
     alignas(8) uint64_t full[GEMM_STAGES];
     uint64_t empty[GEMM_STAGES];
     uint64_t tmem_full[NS];
@@ -106,7 +112,11 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     constexpr uint32_t STAGE_BYTES = GEMM_BM * GEMM_BK + BN * GEMM_BK;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int NT = p.H / BN;                                        // sub-tiles per unit, 1..NS
+    const int HL = p.H / p.cl;                                      // columns of a part this block owns
+    const int crank = (int)blockIdx.x % p.cl;                       // rank in the cluster (clusters are consecutive blocks)
+    const int cofs = crank * HL;                                    // first of them
+    const int first_unit = (int)blockIdx.x / p.cl, unit_step = (int)gridDim.x / p.cl;      // both blocks of a pair walk the same units
+    const int NT = HL / BN;                                         // sub-tiles per unit, 1..NS
     const int num_units = (p.M / GEMM_BM) * p.parts;
     const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
 
@@ -115,6 +125,8 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         for (int a = 0; a < NS; a++) { ptx::mbar_init(&sm.tmem_full[a], 1); ptx::mbar_init(&sm.tmem_empty[a], GEMM_EPI_WARPS); }
         for (int w = 0; w < GEMM_EPI_WARPS; w++)
             for (int a = 0; a < NS; a++) ptx::mbar_init(&sm.rbar[w][a], 1);
+        ptx::mbar_init(&sm.xbar[0], GEMM_EPI_THREADS / 4);       // the peer's first column quarter: one arrival per row
+        ptx::mbar_init(&sm.xbar[1], GEMM_EPI_THREADS / 4);
         sm.abort_flag = 0;
         ptx::fence_barrier_init();
     }
@@ -125,6 +137,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
+    if (p.cl > 1) ptx::cluster_sync_all();          // the peer's barriers exist before anything arrives on them
     const uint32_t tmem_base = sm.tmem_base;
 
     if (warp == 0) {
@@ -133,11 +146,11 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             ptx::prefetch_tmap(&tmap_a);
             ptx::prefetch_tmap(&tmap_b);
             uint32_t it = 0;
-            for (int unit = blockIdx.x; unit < num_units && !sm.abort_flag; unit += gridDim.x) {
+            for (int unit = first_unit; unit < num_units && !sm.abort_flag; unit += unit_step) {
                 const int mt = unit / p.parts, part = unit - mt * p.parts;
                 const int m0 = mt * GEMM_BM;
                 for (int j = 0; j < NT; j++) {
-                    const int n0 = part * p.H + j * BN;
+                    const int n0 = part * p.H + cofs + j * BN;
                     for (int kb = 0; kb < num_kb; kb++, it++) {
                         const int s = it % GEMM_STAGES;
                         const uint32_t ph = (it / GEMM_STAGES) & 1;
@@ -160,7 +173,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (ptx::elect_one()) {
             constexpr uint32_t idesc = ptx::make_idesc_i8(GEMM_BM, BN);
             uint32_t it = 0, stc = 0;
-            for (int unit = blockIdx.x; unit < num_units && !sm.abort_flag; unit += gridDim.x) {
+            for (int unit = first_unit; unit < num_units && !sm.abort_flag; unit += unit_step) {
                 for (int j = 0; j < NT && !sm.abort_flag; j++, stc++) {
                     const int slot = stc % NS;
                     const uint32_t sph = (stc / NS) & 1;
@@ -192,7 +205,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const int quarter = warp & 3;              // TMEM lane quarter this warp may read
         const int cq = ew >> 2;                    // column quarter of every sub-tile
         const int row_in_tile = quarter * 32 + lane;
-        const int tab_items = p.H >> 2;            // one item = 4 consecutive columns
+        const int tab_items = HL >> 2;             // one item = 4 consecutive columns of this block's share
         const long long half_ulp = 1ll << (p.rope_bit - 1);
         // shared address of this lane's row inside a box, and the XOR that swizzles its 16-byte pieces (64-byte swizzle
         // for 64-byte rows; 32-byte rows are stored densely)
@@ -209,7 +222,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const int mt = unit / p.parts, part = unit - mt * p.parts;
             const int mem = (mt * GEMM_BM) / p.seq_len;
             const int8_t *base = p.nt + (int64_t)(mem >> 1) * p.nt_stride;
-            const int n = e << 2;
+            const int n = cofs + (e << 2);
             w.a = *reinterpret_cast<const int32_t *>(base + p.nt_a_off + part * p.H + n);
             w.b = 0; w.d = 0;
             if (MODE == FUSED_RES) {
@@ -224,7 +237,8 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             if (MODE == FUSED_RES) {
                 int v[4];
 #pragma unroll
-                for (int b = 0; b < 4; b++) v[b] = ((int)(int8_t)(w.b >> (8 * b)) + (int)(int8_t)(w.d >> (8 * b))) << p.out_shift;
+                for (int b = 0; b < 4; b++)      // pre-shifted so that the sum joins the rank-1 product before its shift
+                    v[b] = ((int)(int8_t)(w.b >> (8 * b)) + (int)(int8_t)(w.d >> (8 * b))) << (p.out_shift + (GEMM_FMA_ADDS ? p.rank1_shift : 0));
                 *reinterpret_cast<int4 *>(&sm.bcs32[buf][n]) = make_int4(v[0], v[1], v[2], v[3]);
             }
         };
@@ -232,11 +246,13 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const int m0 = (unit / p.parts) * GEMM_BM;
             for (int j = 0; j < NT; j++) {
                 ptx::mbar_arrive_expect_tx(&sm.rbar[ew][j], 32 * CW);
-                ptx::tma_load_2d(sm.box[ew][j], &tmap_r, &sm.rbar[ew][j], j * BN + cq * CW, m0 + quarter * 32);
+                ptx::tma_load_2d(sm.box[ew][j], &tmap_r, &sm.rbar[ew][j], cofs + j * BN + cq * CW, m0 + quarter * 32);
             }
         };
 
-        for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ucount++) {
+        const uint32_t peer_max_s = p.cl > 1 ? ptx::mapa_u32(ptx::smem_u32(&sm.peer_max[0][0]), (uint32_t)(crank ^ 1)) : 0u;
+        const uint32_t peer_bar_s = p.cl > 1 ? ptx::mapa_u32(ptx::smem_u32(&sm.xbar[0]), (uint32_t)(crank ^ 1)) : 0u;
+        for (int unit = first_unit; unit < num_units; unit += unit_step, ucount++) {
             const int mt = unit / p.parts, part = unit - mt * p.parts;
             const int m0 = mt * GEMM_BM;
             const int r = m0 + row_in_tile;
@@ -252,7 +268,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             // tables of this unit are published; everybody has left the previous unit
             ptx::named_bar_sync(1, GEMM_EPI_THREADS);
             const int xbs = sgn ? -pf_xb : pf_xb;
-            const int nunit = unit + gridDim.x;
+            const int nunit = unit + unit_step;
             have_nxt = false;
             if (nunit < num_units) {
                 have_nxt = tab_load(nunit, nxt);
@@ -275,7 +291,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 __syncwarp();                           // lanes leave the waits at different times; the TMEM accesses are warp-wide
                 ptx::tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(slot * BN + cq * CW);
-                const int col0 = j * BN + cq * CW;                     // column inside the part of this warp's first element
+                const int col0 = j * BN + cq * CW;                     // column inside this block's share of this warp's first element
                 uint32_t v[2][16];
                 ptx::tmem_ld16(taddr, v[0]);
 #pragma unroll
@@ -283,7 +299,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     int4 cs[4];
                     if (MODE == FUSED_QKV && do_rope) {
                         // the lanes of a warp are consecutive tokens of one member: every load below is one contiguous run
-                        const int pair0 = fast_mod(col0 + 16 * c, p.fd_head) >> 1;
+                        const int pair0 = fast_mod(cofs + col0 + 16 * c, p.fd_head) >> 1;
 #pragma unroll
                         for (int q4 = 0; q4 < 4; q4++) {
                             const int2 c0 = __ldg(rope + (int64_t)(pair0 + 2 * q4) * p.seq_len), c1 = __ldg(rope + (int64_t)(pair0 + 2 * q4 + 1) * p.seq_len);
@@ -302,11 +318,29 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     for (int q4 = 0; q4 < 4; q4++) {
                         const int col = col0 + 16 * c + 4 * q4;
                         const int4 an = ptx::lds_v4(a32_s + 4 * col);
-                        int x0 = (int)vc[4 * q4] + ((xbs * an.x) >> p.rank1_shift);
-                        int x1 = (int)vc[4 * q4 + 1] + ((xbs * an.y) >> p.rank1_shift);
-                        int x2 = (int)vc[4 * q4 + 2] + ((xbs * an.z) >> p.rank1_shift);
-                        int x3 = (int)vc[4 * q4 + 3] + ((xbs * an.w) >> p.rank1_shift);
-                        if (MODE == FUSED_RES) {
+                        int x0, x1, x2, x3;
+                        if (MODE == FUSED_RES && GEMM_FMA_ADDS) {
+                            // ((acc + r1 + (b << s)) >> s) + residual with r1 = (xb*a) >> t: the bias joins the rank-1 product
+                            // ((b << (s+t)) is a multiple of 2^t), the other adds are multiply-adds by a run-time 1 — the
+                            // integer pipe runs at half the rate of the multiply-add pipe and is the busy one here
+                            const int4 b4 = ptx::lds_v4(bcs_s + 4 * col);
+                            const int32_t rs = q4 == 0 ? rs4.x : (q4 == 1 ? rs4.y : (q4 == 2 ? rs4.z : rs4.w));
+                            x0 = ((((xbs * an.x + b4.x) >> p.rank1_shift) * p.one + (int)vc[4 * q4]) >> p.out_shift) * p.one + ptx::sx_byte0(rs);
+                            x1 = ((((xbs * an.y + b4.y) >> p.rank1_shift) * p.one + (int)vc[4 * q4 + 1]) >> p.out_shift) * p.one + ptx::sx_byte1(rs);
+                            x2 = ((((xbs * an.z + b4.z) >> p.rank1_shift) * p.one + (int)vc[4 * q4 + 2]) >> p.out_shift) * p.one + ptx::sx_byte2(rs);
+                            x3 = ((((xbs * an.w + b4.w) >> p.rank1_shift) * p.one + (int)vc[4 * q4 + 3]) >> p.out_shift) * p.one + (rs >> 24);
+                        } else if (GEMM_FMA_ADDS) {
+                            x0 = ((xbs * an.x) >> p.rank1_shift) * p.one + (int)vc[4 * q4];
+                            x1 = ((xbs * an.y) >> p.rank1_shift) * p.one + (int)vc[4 * q4 + 1];
+                            x2 = ((xbs * an.z) >> p.rank1_shift) * p.one + (int)vc[4 * q4 + 2];
+                            x3 = ((xbs * an.w) >> p.rank1_shift) * p.one + (int)vc[4 * q4 + 3];
+                        } else {
+                            x0 = (int)vc[4 * q4] + ((xbs * an.x) >> p.rank1_shift);
+                            x1 = (int)vc[4 * q4 + 1] + ((xbs * an.y) >> p.rank1_shift);
+                            x2 = (int)vc[4 * q4 + 2] + ((xbs * an.z) >> p.rank1_shift);
+                            x3 = (int)vc[4 * q4 + 3] + ((xbs * an.w) >> p.rank1_shift);
+                        }
+                        if (MODE == FUSED_RES && !GEMM_FMA_ADDS) {
                             const int4 b4 = ptx::lds_v4(bcs_s + 4 * col);
                             const int32_t rs = q4 == 0 ? rs4.x : (q4 == 1 ? rs4.y : (q4 == 2 ? rs4.z : rs4.w));
                             x0 = ptx::sx_byte0(rs) + ((x0 + b4.x) >> p.out_shift);
@@ -331,8 +365,23 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
             sm.rowpart[cq][row_in_tile] = max(rmx, -rmn);
             ptx::named_bar_sync(2 + quarter, 128);            // the four column quarters of this lane quarter
-            const int row_max = max(max(sm.rowpart[0][row_in_tile], sm.rowpart[1][row_in_tile]),
-                                    max(sm.rowpart[2][row_in_tile], sm.rowpart[3][row_in_tile]));
+            int row_max = max(max(sm.rowpart[0][row_in_tile], sm.rowpart[1][row_in_tile]),
+                              max(sm.rowpart[2][row_in_tile], sm.rowpart[3][row_in_tile]));
+            if (p.cl > 1) {
+                // the other half of the row lives in the peer block: its first column quarter writes the maximum of its
+                // columns into this block's peer_max and arrives (release, cluster scope) on this block's barrier, and
+                // vice versa.  Buffers and barriers alternate with the unit parity: the peer cannot get past this
+                // exchange of unit u+1 before this block has arrived for it, that is after it has read unit u's value.
+                if (cq == 0) {
+                    ptx::st_cluster_u32(peer_max_s + (uint32_t)(tb * GEMM_BM + row_in_tile) * 4u, (uint32_t)row_max);
+                    ptx::mbar_arrive_cluster(peer_bar_s + (uint32_t)tb * 8u);
+                }
+                if (!sm.abort_flag && !ptx::mbar_wait_cluster(&sm.xbar[tb], (uint32_t)(ucount >> 1) & 1u, 1000000000ull)) {
+                    sm.abort_flag = 1;
+                    if (p.err) atomicCAS(p.err, 0, DEV_TIMEOUT_PEER);
+                }
+                row_max = max(row_max, sm.peer_max[tb][row_in_tile]);
+            }
             const float scale = aln_scale(row_max);
 
             // ---------------- pass 2: requantise, pack, store ----------------
@@ -366,7 +415,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 __syncwarp();
                 if (lane == 0) {
                     ptx::mbar_arrive(&sm.tmem_empty[slot]);
-                    ptx::tma_store_2d(&tmap_o, sm.box[ew][j], j * BN + cq * CW, (int)(part * p.part_rows) + m0 + quarter * 32);
+                    ptx::tma_store_2d(&tmap_o, sm.box[ew][j], cofs + j * BN + cq * CW, (int)(part * p.part_rows) + m0 + quarter * 32);
                     ptx::tma_store_commit();
                 }
             }
@@ -392,6 +441,8 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, 512);
     }
+    // neither block of a pair retires while the other may still write its maxima into it
+    if (p.cl > 1) ptx::cluster_sync_all();
 }
 
 template <int BN>

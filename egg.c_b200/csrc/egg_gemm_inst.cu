@@ -111,17 +111,63 @@ static int make_tmap_box8(CUtensorMap *m, const void *ptr, uint64_t rows, uint64
     return EGG_OK;
 }
 
+// Blocks that share a unit of the row-owning GEMM: one up to 512 columns, a cluster of two above (0: unsupported width).
+int fused_cluster_size(int hidden) {
+    if (hidden <= 0 || hidden % 128) return 0;
+    if (hidden <= FUSED_MAX_H) return 1;
+    if (hidden <= 2 * FUSED_MAX_H && hidden % 256 == 0) return 2;
+    return 0;
+}
+
+template <int BN, int MODE>
+static int launch_fused_one(cudaStream_t st, const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to, const CUtensorMap &tr,
+                            const FusedParams &p, int units, int num_sms) {
+    auto kern = gemm_fused_kernel<BN, MODE>;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = fused_smem_bytes<BN>();
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    int groups = num_sms / p.cl;                     // resident blocks (pairs of blocks)
+    if (p.cl > 1) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)p.cl; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        // the pairs that can be resident at once (a GPC with an odd number of free SMs leaves one out): asked once
+        static int max_pairs = 0;
+        if (max_pairs == 0) {
+            cfg.gridDim = dim3((unsigned)(num_sms / p.cl * p.cl));
+            int n = 0;
+            EGG_CUDA(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+            if (n < 1) { set_error("no pair of blocks of the row-owning GEMM fits on the device"); return EGG_E_CUDA; }
+            max_pairs = n;
+        }
+        if (groups > max_pairs) groups = max_pairs;
+    }
+    if (groups > units) groups = units;
+    cfg.gridDim = dim3((unsigned)(groups * p.cl));
+    EGG_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, to, tr, p));
+    return EGG_OK;
+}
+
 int launch_gemm_fused(cudaStream_t st, int mode, const int8_t *A, const int8_t *B, int8_t *out, const int8_t *resid,
                       const FusedParams &p_in, int num_sms) {
     FusedParams p = p_in;
     if (!g_encode) { set_error("gemm_init() was not called"); return EGG_E_STATE; }
-    if (p.M <= 0 || p.M % GEMM_BM || p.seq_len % GEMM_BM || p.H % 128 || p.H > FUSED_MAX_H || p.K % 16 || p.parts < 1 ||
+    p.cl = fused_cluster_size(p.H);
+    if (p.M <= 0 || p.M % GEMM_BM || p.seq_len % GEMM_BM || p.cl == 0 || p.K % 16 || p.parts < 1 ||
         (mode == FUSED_RES && (p.parts != 1 || !resid)) || (mode != FUSED_QKV && mode != FUSED_RES)) {
         set_error("unsupported row-owning GEMM shape M=%d H=%d K=%d parts=%d seq_len=%d", p.M, p.H, p.K, p.parts, p.seq_len);
         return EGG_E_INVALID;
     }
-    const int bn = (p.H % 256 == 0) ? 256 : 128;
+    if (mode == FUSED_RES && p.out_shift + p.rank1_shift > 20) {     // (bias + noise) << (both shifts) joins a product below 2^30
+        set_error("shifts %d + %d too large for the pre-shifted bias table", p.out_shift, p.rank1_shift);
+        return EGG_E_INVALID;
+    }
+    const int hl = p.H / p.cl;                       // columns per block
+    const int bn = (hl % 256 == 0) ? 256 : 128;
     p.fd_head = make_fastdiv(p.head_dim > 0 ? p.head_dim : 64);
+    p.one = 1;
     CUtensorMap ta, tb, to, tr;
     int rc;
     if ((rc = make_tmap(&ta, A, (uint64_t)p.M, (uint64_t)p.K, GEMM_BM))) return rc;
@@ -131,16 +177,12 @@ int launch_gemm_fused(cudaStream_t st, int mode, const int8_t *A, const int8_t *
     tr = to;
     if (mode == FUSED_RES && (rc = make_tmap_box8(&tr, resid, (uint64_t)p.M, (uint64_t)p.H, (uint32_t)bn / 4))) return rc;
     const int units = (p.M / GEMM_BM) * p.parts;
-    const int grid = units < num_sms ? units : num_sms;
     if (bn == 256) {
-        if (mode == FUSED_QKV) gemm_fused_kernel<256, FUSED_QKV><<<grid, GEMM_THREADS, fused_smem_bytes<256>(), st>>>(ta, tb, to, tr, p);
-        else gemm_fused_kernel<256, FUSED_RES><<<grid, GEMM_THREADS, fused_smem_bytes<256>(), st>>>(ta, tb, to, tr, p);
-    } else {
-        if (mode == FUSED_QKV) gemm_fused_kernel<128, FUSED_QKV><<<grid, GEMM_THREADS, fused_smem_bytes<128>(), st>>>(ta, tb, to, tr, p);
-        else gemm_fused_kernel<128, FUSED_RES><<<grid, GEMM_THREADS, fused_smem_bytes<128>(), st>>>(ta, tb, to, tr, p);
+        if (mode == FUSED_QKV) return launch_fused_one<256, FUSED_QKV>(st, ta, tb, to, tr, p, units, num_sms);
+        return launch_fused_one<256, FUSED_RES>(st, ta, tb, to, tr, p, units, num_sms);
     }
-    EGG_CUDA(cudaGetLastError());
-    return EGG_OK;
+    if (mode == FUSED_QKV) return launch_fused_one<128, FUSED_QKV>(st, ta, tb, to, tr, p, units, num_sms);
+    return launch_fused_one<128, FUSED_RES>(st, ta, tb, to, tr, p, units, num_sms);
 }
 
 template <int BN, int EPI, int RPL = 0>
@@ -194,6 +236,11 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
     p.fd_third = make_fastdiv(p.third);
     p.fd_head = make_fastdiv(p.head_dim);
     p.lut_stride = 32 * 4;
+    p.one = 1;
+    if (epi == EPI_GELU && p.out_shift + p.rank1_shift > 20) {       // (bias + noise) << (both shifts) joins a product below 2^30
+        set_error("shifts %d + %d too large for the pre-shifted bias table", p.out_shift, p.rank1_shift);
+        return EGG_E_INVALID;
+    }
     CUtensorMap ta, tb;
     int rc;
     if ((rc = make_tmap(&ta, A, (uint64_t)p.M, (uint64_t)p.K, GEMM_BM))) return rc;

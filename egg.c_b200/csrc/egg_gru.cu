@@ -597,8 +597,11 @@ extern "C" int egg_gru_generation(egg_gru_ctx *c, uint32_t step_seed, int64_t st
     EGG_CUDA(cudaStreamSynchronize(st));       // hdr lives on this stack frame
     int per_step = 6 * cf.n_layers + 4, rc;
     if (!c->graph1) {
-        if ((rc = gru_capture(c, 1, &c->graph1, &per_step))) return rc;
-        if ((rc = gru_capture(c, 16, &c->graph16, &per_step))) return rc;
+        // both or neither: a lone single-step graph would make the next call skip the capture of the 16-step one
+        if ((rc = gru_capture(c, 1, &c->graph1, &per_step)) || (rc = gru_capture(c, 16, &c->graph16, &per_step))) {
+            gru_drop_graphs(c);
+            return rc;
+        }
     }
     int t = 0;
     for (; t + 16 <= tokens; t += 16) EGG_CUDA(cudaGraphLaunch(c->graph16, st));

@@ -500,6 +500,11 @@ __device__ __forceinline__ void mma_s8_first(int (&c)[4], uint32_t a0, uint32_t 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
+#ifdef EGG_ATT_EXACT_ALWAYS          // comparison build: the remainder test on every quotient
+constexpr bool ATT_EXACT_ALWAYS = true;
+#else
+constexpr bool ATT_EXACT_ALWAYS = false;
+#endif
 constexpr int ATT_KP = 80;   // K row pitch in shared memory (bytes): conflict-free fragment loads
 
 // scores of one 16-query x 32-key block: c[nt][0..3] for the four 8-key n-tiles
@@ -706,11 +711,25 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
         for (int dn = 0; dn < 8; dn++) {
             int o[4];
             if (small_limbs) {
-                // |Σw·v / Σw| <= 127 (a weighted mean of int8 values): the reference's clip cannot trigger
+                // |Σw·v / Σw| <= 127 (a weighted mean of int8 values): the reference's clip cannot trigger.
+                // The float estimate of the quotient is within 4e-5 of the real one (five roundings of 2^-24 relative on a
+                // value below 128), so its truncation is the answer unless it lies within 2e-4 of an integer; only then
+                // (about one group of four in twenty, and every single-key row) the exact remainder test runs.
+                bool near = false;
 #pragma unroll
-                for (int i = 0; i < 4; i++)
-                    o[i] = i < 2 ? att_div_small(acc[dn][0][i], acc[dn][1][i], acc[dn][2][i], tl0[0], tl0[1], tl0[2], rden0)
-                                 : att_div_small(acc[dn][0][i], acc[dn][1][i], acc[dn][2][i], tl1[0], tl1[1], tl1[2], rden1);
+                for (int i = 0; i < 4; i++) {
+                    const float fn = fmaf(__int2float_rn(acc[dn][2][i] * 128 + acc[dn][1][i]), 128.0f, __int2float_rn(acc[dn][0][i]));
+                    const float t = fn * (i < 2 ? rden0 : rden1);
+                    const float ri = __fadd_rn(__fadd_rn(t, 12582912.0f), -12582912.0f);      // nearest integer, |t| < 2^22
+                    near |= fabsf(t - ri) < 2e-4f;
+                    o[i] = __float2int_rz(t);
+                }
+                if (ATT_EXACT_ALWAYS || __any_sync(0xFFFFFFFFu, near)) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        o[i] = i < 2 ? att_div_small(acc[dn][0][i], acc[dn][1][i], acc[dn][2][i], tl0[0], tl0[1], tl0[2], rden0)
+                                     : att_div_small(acc[dn][0][i], acc[dn][1][i], acc[dn][2][i], tl1[0], tl1[1], tl1[2], rden1);
+                }
             } else {
 #pragma unroll
                 for (int i = 0; i < 4; i++)
@@ -789,44 +808,51 @@ int launch_fitness(cudaStream_t st, const int32_t *loss, int32_t *fit, int pairs
 // =========================================================================
 // update operands: the two noise matrices of vote = Σ_p f_p a_p b_p^T, pair index contiguous
 // =========================================================================
+constexpr int UPD_ROWS_PER_BLOCK = 8;     // operand rows one block writes: the pair seeds and fitness words are loaded once for all of them
+
 __global__ void __launch_bounds__(256) update_operands_kernel(int8_t *na, int8_t *nb, const int32_t *fit, int pairs, int kp, int rows_k, int cols_n,
                                        int off_a, int off_b, int seed_base, uint32_t step_seed, int mask, int gaussian, int split) {
-    const int row = blockIdx.y;                 // 0..cols_n-1 -> NA, cols_n.. -> NB
+    const int row0 = blockIdx.y * UPD_ROWS_PER_BLOCK;      // 0..cols_n-1 -> NA, cols_n.. -> NB (cols_n is a multiple of the group size)
     const int ktot = split ? 2 * kp : kp;
-    // four consecutive pair slots per thread (kp is a multiple of 128): one word store
+    const bool is_a = row0 < cols_n;
+    // four consecutive pair slots per thread (kp is a multiple of 128): one word store per row
     for (int pp = (blockIdx.x * blockDim.x + threadIdx.x) * 4; pp < ktot; pp += gridDim.x * blockDim.x * 4) {
         const int hi = pp >= kp;
         const int pidx0 = hi ? pp - kp : pp;
-        int val[4];
+        uint32_t seed[4];
+        int f[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int pidx = pidx0 + j;
-            int v = 0;
+            seed[j] = step_seed + (uint32_t)pidx + (uint32_t)seed_base + (uint32_t)(is_a ? off_a : off_b);    // mgpu.cu:1095
+            int fv = 0;
             if (pidx < pairs) {
-                const uint32_t s = step_seed + (uint32_t)pidx + (uint32_t)seed_base;    // mgpu.cu:1095
-                if (row < cols_n) {
-                    int f = fit[pidx];
-                    if (split) { int f1 = f >> 4, f0 = f - (f1 << 4); f = hi ? f1 : f0; }
-                    v = f ? f * noise_from_hash(s + (uint32_t)off_a, (uint32_t)row, mask, gaussian) : 0;
-                } else {
-                    v = noise_from_hash(s + (uint32_t)off_b, (uint32_t)(row - cols_n), mask, gaussian);
-                    if (hi) v *= 16;
-                }
+                fv = is_a ? fit[pidx] : (hi ? 16 : 1);
+                if (is_a && split) { const int f1 = fv >> 4, f0 = fv - (f1 << 4); fv = hi ? f1 : f0; }
             }
-            val[j] = v;
+            f[j] = fv;                                    // 0 for the padding beyond the last pair
         }
-        const uint32_t w = pack4(val[0], val[1], val[2], val[3]);
-        if (row < cols_n) *reinterpret_cast<uint32_t *>(na + (int64_t)row * ktot + pp) = w;
-        else *reinterpret_cast<uint32_t *>(nb + (int64_t)(row - cols_n) * ktot + pp) = w;
+#pragma unroll
+        for (int rr = 0; rr < UPD_ROWS_PER_BLOCK; rr++) {
+            const int row = row0 + rr;
+            const uint32_t idx = (uint32_t)(is_a ? row : row - cols_n);
+            int val[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) val[j] = f[j] ? f[j] * noise_from_hash(seed[j], idx, mask, gaussian) : 0;
+            const uint32_t w = pack4(val[0], val[1], val[2], val[3]);
+            if (is_a) *reinterpret_cast<uint32_t *>(na + (int64_t)row * ktot + pp) = w;
+            else *reinterpret_cast<uint32_t *>(nb + (int64_t)(row - cols_n) * ktot + pp) = w;
+        }
     }
 }
 
 int launch_update_operands(cudaStream_t st, int8_t *na, int8_t *nb, const int32_t *fit, int pairs, int kp, int rows_k,
                            int cols_n, int off_a, int off_b, int seed_base, uint32_t step_seed, int mask, int gaussian,
                            int split) {
+    if (rows_k % UPD_ROWS_PER_BLOCK || cols_n % UPD_ROWS_PER_BLOCK) { set_error("update operand rows must come in groups of %d", UPD_ROWS_PER_BLOCK); return EGG_E_INVALID; }
     int ktot = split ? 2 * kp : kp;
     int gx = (ktot / 4 + 255) / 256; if (gx > 32) gx = 32;
-    dim3 grid((unsigned)gx, (unsigned)(rows_k + cols_n));
+    dim3 grid((unsigned)gx, (unsigned)((rows_k + cols_n) / UPD_ROWS_PER_BLOCK));
     update_operands_kernel<<<grid, 256, 0, st>>>(na, nb, fit, pairs, kp, rows_k, cols_n, off_a, off_b, seed_base, step_seed, mask, gaussian, split);
     EGG_CUDA(cudaGetLastError());
     return EGG_OK;
@@ -928,10 +954,11 @@ int launch_muon_m_from_votes(cudaStream_t st, const VoteApplyParams &p) {
 __global__ void __launch_bounds__(256) update_vector_kernel(const VecUpdParams p) {
     const int idx = blockIdx.x;
     int vote = 0;
+    // no early-out on zero fitness: four pairs per trip keep eight independent hash chains in flight
+#pragma unroll 4
     for (int pr = threadIdx.x; pr < p.pairs; pr += blockDim.x) {
-        int f = p.fit[pr];
-        if (f == 0) continue;
-        uint32_t s = p.step_seed + (uint32_t)pr + (uint32_t)p.seed_base;
+        const int f = p.fit[pr];
+        const uint32_t s = p.step_seed + (uint32_t)pr + (uint32_t)p.seed_base;
         vote += f * noise_from_hash(s + (uint32_t)p.off_a, (uint32_t)idx, p.mask, p.gaussian) *
                 noise_from_hash(s + (uint32_t)p.off_b, (uint32_t)idx, p.mask, p.gaussian);
     }

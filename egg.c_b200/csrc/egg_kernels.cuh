@@ -130,7 +130,8 @@ struct FusedParams;
 int launch_gemm_fused(cudaStream_t st, int mode, const int8_t *A, const int8_t *B, int8_t *out, const int8_t *resid,
                       const FusedParams &p, int num_sms);
 // whether the row-owning kernels can run a configuration (whole tiles inside one member, a row fits tensor memory)
-inline bool fused_supported(int hidden, int seq_len) { return seq_len % 128 == 0 && hidden % 128 == 0 && hidden <= 512; }
+int fused_cluster_size(int hidden);       // blocks per unit of the row-owning GEMM, 0 when the width is unsupported
+inline bool fused_supported(int hidden, int seq_len) { return seq_len % 128 == 0 && fused_cluster_size(hidden) > 0; }
 
 // ---- GEMM -------------------------------------------------------------------
 // A: [M][K] int8 row-major, B: [N][K] int8 row-major (both device pointers).

@@ -32,6 +32,9 @@ def _losses(pkg, cfg, model, data, seed, start, pop, wave, fused, attention_tc=F
     (512, 1, 256, 6, 3, "random"),         # the benchmark's layer shape: two 256-column sub-tiles, tiles of one member half
     (128, 1, 512, 4, 15, "random"),        # 512 tokens: four query blocks, the later ones with two key chunks (scores recomputed in pass B)
     (256, 1, 384, 4, 3, "random_all"),     # three query blocks: an odd number of key tiles in the last chunk
+    (1024, 1, 128, 4, 3, "random_all"),    # a pair of thread blocks per row tile (2 x 512 columns), row maxima exchanged between them
+    (768, 1, 256, 4, 15, "random"),        # a pair with 3 x 128 columns each
+    (1024, 2, 256, 2, 3, "random"),        # pairs, two layers chained through the in-place projections
 ])
 def test_fused_eval_matches_oracle(hidden, layers, seq, pop, mask, kind):
     pkg, O = load_pkg(), load_oracle()
@@ -54,6 +57,19 @@ def test_fused_eval_many_units_per_block_and_ragged_waves():
     for wave in (0, 150):         # one wave of 400 members = 400 tiles (1200 Q/K/V units); then 150 + 150 + 100
         got = _losses(pkg, cfg, model, data, SEED + 11, 256, 400, wave, True)
         assert (got == want).all(), "wave %d: %d of 400 losses differ" % (wave, (got != want).sum())
+
+
+def test_paired_blocks_walk_many_units():
+    """H 1024: every 128-row tile is shared by a cluster of two thread blocks.  With 300 members there are more tiles
+    than pairs, so every pair walks several units (alternating exchange buffers and barrier phases); the row-owning
+    form must give the losses of the two-kernel form, whole and in ragged waves."""
+    pkg = load_pkg()
+    kw = dict(hidden_dim=1024, n_layers=2, seq_len=128, population_size=300, device_mask=3)
+    cfg, ocfg, model, data = make_case(kw, data_len=200000, model_kind="random")
+    want = _losses(pkg, cfg, model, data, SEED + 5, 128, 300, 0, False)
+    for wave in (0, 128):
+        got = _losses(pkg, cfg, model, data, SEED + 5, 128, 300, wave, True)
+        assert (got == want).all(), "wave %d: %d of 300 losses differ" % (wave, (got != want).sum())
 
 
 def test_fused_and_two_kernel_forms_agree_at_benchmark_shapes_and_with_reference_kernels():
