@@ -194,6 +194,17 @@ __device__ __forceinline__ uint32_t pack_clip8(int a, int b, int c, int d) {
     return __vmaxs4(r, 0x81818181u);
 }
 
+// (1/mn) * (1 + 2^-17) for mn = 1..127 (div_small's factor): the mean is the same for every lane of a row, so the
+// reciprocal is one constant-bank read instead of a division per row.  Compile-time IEEE single arithmetic, the same two
+// roundings as the expression it replaces.
+struct RinvTable { float v[128]; };
+constexpr RinvTable make_rinv_table() {
+    RinvTable t = {};
+    for (int mn = 1; mn < 128; mn++) t.v[mn] = (1.0f / (float)mn) * (1.0f + 0x1p-17f);
+    return t;
+}
+__constant__ RinvTable c_rinv_up = make_rinv_table();
+
 // One warp per run of ROW_RUN consecutive rows of ONE population member (seq_len is a multiple of 16, so a run never
 // crosses members); NJ = H/128 chunks of 4 elements per lane.  Everything that depends on the member only -- the
 // perturbed gain / bias tables and the noise vectors of the following projections, 3.5 H bytes -- is loaded once per
@@ -253,6 +264,7 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
     for (int r = r0; r < r_end; r++) {
         const int t = r - mem * p.seq_len;
         int x[NJ][4];
+        uint32_t xw_cur[MODE == 2 ? NJ : 1];
         if (MODE == 0) {
             // embedding (mgpu.cu:902-931): the token's row comes from the token-major copy of the table ([V][H], the same
             // K-major shadow the head projection multiplies with), 4 contiguous bytes per lane and chunk
@@ -285,6 +297,7 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
 #pragma unroll
             for (int j = 0; j < NJ; j++) {
                 const uint32_t w = xw_next[j];
+                xw_cur[j] = w;
                 x[j][0] = ptx::sx_byte0(w); x[j][1] = ptx::sx_byte1(w); x[j][2] = ptx::sx_byte2(w); x[j][3] = (int)w >> 24;
             }
             if (r + 1 < r_end) {
@@ -307,15 +320,20 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
 #pragma unroll
         for (int j = 0; j < NJ; j++) {
             const int d = (j << 7) + (lane << 2);
-            uint32_t w = ptx::pack_sat_s8(x[j][0], x[j][1], x[j][2], x[j][3]);      // |x| <= 127: the saturating pack is exact, two instructions
-            if (MODE != 2) *reinterpret_cast<uint32_t *>(p.x_out + (int64_t)r * H + d) = w;
+            uint32_t w;
+            if (MODE == 2) {
+                w = xw_cur[j];                                                       // the bytes as they were read
+            } else {
+                w = ptx::pack_sat_s8(x[j][0], x[j][1], x[j][2], x[j][3]);            // |x| <= 127: the saturating pack is exact, two instructions
+                *reinterpret_cast<uint32_t *>(p.x_out + (int64_t)r * H + d) = w;
+            }
             tot = __dp4a((int)__vabsss4(w), 0x01010101, tot);    // sum of |x|, four at a time
         }
         // mean-abs norm with perturbed gain / bias (mgpu.cu:646-678): y = clip((x*w')/mn + b')
         tot = warp_sum(tot);
         int mn = tot / H;
         if (!mn) mn = 1;
-        const float rinv = (1.0f / (float)mn) * (1.0f + 0x1p-17f);
+        const float rinv = c_rinv_up.v[mn];                     // mn <= 127: a mean of absolute values of int8
         int dot[NDOTS];
 #pragma unroll
         for (int q = 0; q < NDOTS; q++) dot[q] = 0;
@@ -324,7 +342,7 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
             const int d = (j << 7) + (lane << 2);
             int y[4];
 #pragma unroll
-            for (int i = 0; i < 4; i++) y[i] = div_small(x[j][i] * wv[j][i], rinv) + bv[j][i];
+            for (int i = 0; i < 4; i++) y[i] = div_small(x[j][i] * wv[j][i], rinv) * p.one + bv[j][i];   // the add as a multiply-add by a run-time 1: off the busier integer pipe
             const uint32_t yw = pack_clip8(y[0], y[1], y[2], y[3]);
             *reinterpret_cast<uint32_t *>(p.h_out + (int64_t)r * H + d) = yw;
 #pragma unroll
@@ -365,6 +383,7 @@ static int launch_rowwise_nj(cudaStream_t st, const RowParams &p) {
 int launch_rowwise(cudaStream_t st, const RowParams &p_in, int mode) {
     RowParams p = p_in;
     p.fd_seq = make_fastdiv(p.seq_len);
+    p.one = 1;
     if (p.ndots != 1 && p.ndots != 3) { set_error("row-wise kernel computes one or three row dots, not %d", p.ndots); return EGG_E_INVALID; }
     if (p.ndots == 1) return mode == 0 ? launch_rowwise_nj<0, 1>(st, p) : (mode == 1 ? launch_rowwise_nj<1, 1>(st, p) : launch_rowwise_nj<2, 1>(st, p));
     return mode == 0 ? launch_rowwise_nj<0, 3>(st, p) : (mode == 1 ? launch_rowwise_nj<1, 3>(st, p) : launch_rowwise_nj<2, 3>(st, p));
@@ -500,11 +519,6 @@ __device__ __forceinline__ void mma_s8_first(int (&c)[4], uint32_t a0, uint32_t 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
-#ifdef EGG_ATT_EXACT_ALWAYS          // comparison build: the remainder test on every quotient
-constexpr bool ATT_EXACT_ALWAYS = true;
-#else
-constexpr bool ATT_EXACT_ALWAYS = false;
-#endif
 constexpr int ATT_KP = 80;   // K row pitch in shared memory (bytes): conflict-free fragment loads
 
 // scores of one 16-query x 32-key block: c[nt][0..3] for the four 8-key n-tiles
@@ -711,25 +725,11 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
         for (int dn = 0; dn < 8; dn++) {
             int o[4];
             if (small_limbs) {
-                // |Σw·v / Σw| <= 127 (a weighted mean of int8 values): the reference's clip cannot trigger.
-                // The float estimate of the quotient is within 4e-5 of the real one (five roundings of 2^-24 relative on a
-                // value below 128), so its truncation is the answer unless it lies within 2e-4 of an integer; only then
-                // (about one group of four in twenty, and every single-key row) the exact remainder test runs.
-                bool near = false;
+                // |Σw·v / Σw| <= 127 (a weighted mean of int8 values): the reference's clip cannot trigger
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const float fn = fmaf(__int2float_rn(acc[dn][2][i] * 128 + acc[dn][1][i]), 128.0f, __int2float_rn(acc[dn][0][i]));
-                    const float t = fn * (i < 2 ? rden0 : rden1);
-                    const float ri = __fadd_rn(__fadd_rn(t, 12582912.0f), -12582912.0f);      // nearest integer, |t| < 2^22
-                    near |= fabsf(t - ri) < 2e-4f;
-                    o[i] = __float2int_rz(t);
-                }
-                if (ATT_EXACT_ALWAYS || __any_sync(0xFFFFFFFFu, near)) {
-#pragma unroll
-                    for (int i = 0; i < 4; i++)
-                        o[i] = i < 2 ? att_div_small(acc[dn][0][i], acc[dn][1][i], acc[dn][2][i], tl0[0], tl0[1], tl0[2], rden0)
-                                     : att_div_small(acc[dn][0][i], acc[dn][1][i], acc[dn][2][i], tl1[0], tl1[1], tl1[2], rden1);
-                }
+                for (int i = 0; i < 4; i++)
+                    o[i] = i < 2 ? att_div_small(acc[dn][0][i], acc[dn][1][i], acc[dn][2][i], tl0[0], tl0[1], tl0[2], rden0)
+                                 : att_div_small(acc[dn][0][i], acc[dn][1][i], acc[dn][2][i], tl1[0], tl1[1], tl1[2], rden1);
             } else {
 #pragma unroll
                 for (int i = 0; i < 4; i++)

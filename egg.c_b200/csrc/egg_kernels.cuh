@@ -68,6 +68,7 @@ struct RowParams {
     int32_t *zero1;      // [M]
     int32_t *zero2;      // [M]
     int32_t *zero3;      // [M][3]
+    int one;             // 1 (filled by launch_rowwise): the multiplier of additions issued as multiply-adds
 };
 int launch_rowwise(cudaStream_t st, const RowParams &p, int mode);
 
