@@ -194,6 +194,57 @@ __device__ __forceinline__ int aln_quant_f(int val, float scale) {
     return __float2int_rz(p + c);
 }
 
+// ---- exact float arithmetic without the conversion unit ----
+// The reference's requantisation is float math ((float)v * scale, roundf, int division);
+// the same values are produced here with adds against 1.5*2^23 on the ALU/FMA pipes,
+// because int<->float conversion instructions run at a small fraction of their rate.
+constexpr float kMagic = 12582912.0f;          // 1.5 * 2^23
+constexpr int kMagicBits = 0x4B400000;
+// (float)v for |v| < 2^22, exact
+__device__ __forceinline__ float i2f_small(int v) { return __int_as_float(kMagicBits + v) - kMagic; }
+// the same value through the conversion unit: used for a share of the conversions so that the otherwise idle unit
+// takes load off the integer/float pipes
+__device__ __forceinline__ float i2f_cvt(int v) { return __int2float_rn(v); }
+// roundf(x) (half away from zero) as a float, for |x| < 2^22: round-to-nearest-even by the
+// magic add, then the two tie cases that differ are corrected (x - rint(x) is exact).
+__device__ __forceinline__ float roundf_small(float x) {
+    float rf = (x + kMagic) - kMagic;
+    float d = x - rf;
+    if (d == 0.5f && x > 0.0f) rf += 1.0f;
+    if (d == -0.5f && x < 0.0f) rf -= 1.0f;
+    return rf;
+}
+// integer value of a float that holds an integer, |f| < 2^22
+__device__ __forceinline__ int f2i_exact(float f) { return __float_as_int(f + kMagic) - kMagicBits; }
+
+// trunc(a / mn) as C integer division does, for |a| < 2^16 and 1 <= mn <= 127, with rinv_up = (1/mn) * (1 + 2^-17):
+// the factor pushes every quotient away from zero by |q| * 7.6e-6 -- more than the float error of the product
+// (three roundings, < |q| * 1.8e-7), so an exact quotient k lands beyond k and truncates to k, and less than the
+// distance 1/mn from a non-integer quotient to the next integer (|q| * 7.8e-6 < 1/mn because |q| * mn = |a| < 2^16).
+// The configuration check bounds |x * gain| by 2^16 from the noise amplitude.
+__device__ __forceinline__ int div_small(int a, float rinv_up) {
+    return __float2int_rz(i2f_small(a) * rinv_up);
+}
+
+// [sat8(a), sat8(b), sat8(c), sat8(d)] as bytes 0..3 with the reference's clip to [-127, 127]
+__device__ __forceinline__ uint32_t pack_clip8(int a, int b, int c, int d) {
+    uint32_t hi, r;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(d), "r"(c));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(a), "r"(hi));
+    return __vmaxs4(r, 0x81818181u);
+}
+
+// (1/mn) * (1 + 2^-17) for mn = 1..127 (div_small's factor): the mean is the same for every lane of a row, so the
+// reciprocal is one constant-bank read instead of a division per row.  Compile-time IEEE single arithmetic, the same two
+// roundings as the expression it replaces.  One copy per translation unit.
+struct RinvTable { float v[128]; };
+constexpr RinvTable make_rinv_table() {
+    RinvTable t = {};
+    for (int mn = 1; mn < 128; mn++) t.v[mn] = (1.0f / (float)mn) * (1.0f + 0x1p-17f);
+    return t;
+}
+static __constant__ RinvTable c_rinv_up = make_rinv_table();
+
 // ---------------------------------------------------------------- errors
 void set_error(const char *fmt, ...);
 

@@ -27,7 +27,7 @@
 
 namespace egg {
 
-enum FusedMode { FUSED_QKV = 0, FUSED_RES = 1 };
+enum FusedMode { FUSED_QKV = 0, FUSED_RES = 1, FUSED_RES_LN = 2 };
 
 struct FusedParams {
     int M, H, K;                 // rows (multiple of 128), width of one part, contraction
@@ -49,7 +49,14 @@ struct FusedParams {
     int head_dim, rope_bit;
     int64_t part_rows;           // row distance between the parts in the output tensor map
     int *err;
-    FastDiv fd_head;
+    FastDiv fd_head, fd_h;       // head_dim and H as multiply-shift divisors (filled by launch_gemm_fused)
+    // FUSED_RES_LN: the mean-abs norm that follows the block (apply_standard_norm, mgpu.cu:646-678) and the row dots of
+    // the projections after it, computed from the requantised row while it is still in shared memory
+    int nt_w_m, nt_b_m;          // perturbed gain / bias tables (int16 [2][H]) in the noise table
+    int ndots, nt_dot[3];        // B-noise vectors of the following projections
+    int8_t *h_out;               // [M][H] normalised rows
+    int32_t *xb_out;             // [M][xb_out_stride] row dots, ADDED to (cleared by the caller)
+    int xb_out_stride;
 };
 
 constexpr int FUSED_MAX_H = 512;
@@ -66,7 +73,13 @@ struct FusedSmem {
     alignas(16) int32_t bcs32[2][FUSED_MAX_H];          // (bias + bias-noise delta of the member's sign) << out_shift
     alignas(16) int32_t rowpart[4][GEMM_BM];            // per-row abs-max of each column quarter
     alignas(16) int32_t peer_max[2][GEMM_BM];           // per-row abs-max of the peer block's columns (written by the peer)
+    alignas(16) int32_t rowsum[4][GEMM_BM];             // FUSED_RES_LN: per-row Σ|x| of each column quarter
+    alignas(16) int32_t peer_sum[2][GEMM_BM];           // ... and of the peer block's columns
+    alignas(16) int16_t ln_w[FUSED_MAX_H];              // FUSED_RES_LN: perturbed gains / biases of the unit's member
+    alignas(16) int16_t ln_b[FUSED_MAX_H];
+    alignas(16) int8_t ln_d[3][FUSED_MAX_H];            // B-noise of the following projections
     alignas(8) uint64_t xbar[2];                        // arrival of the peer's maxima, one barrier per unit parity
+    uint64_t xbar2[2];                                  // arrival of the peer's sums
     alignas(8) uint64_t full[GEMM_STAGES];
     uint64_t empty[GEMM_STAGES];
     uint64_t tmem_full[NS];
@@ -99,6 +112,8 @@ __device__ __forceinline__ void fused_wait(uint64_t *bar, uint32_t parity, volat
 
 // Words of the next unit's tables, loaded a unit ahead.
 struct FusedTabWords { int32_t a, b, d; };
+// One thread's share (4 columns) of the norm tables of a unit's member (FUSED_RES_LN).
+struct FusedLnWords { int2 w, b; int32_t d[3]; };
 
 template <int BN, int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -110,6 +125,8 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     constexpr int CW = BN / 4;                  // columns of a sub-tile that one epilogue warp owns
     constexpr int NCH = CW / 16;                // 16-column chunks per warp and sub-tile
     constexpr uint32_t STAGE_BYTES = GEMM_BM * GEMM_BK + BN * GEMM_BK;
+    constexpr bool RES = (MODE != FUSED_QKV);   // residual + bias projections (O, MLP down)
+    constexpr bool LN = (MODE == FUSED_RES_LN); // ... followed in the same epilogue by the next mean-abs norm
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int HL = p.H / p.cl;                                      // columns of a part this block owns
@@ -127,6 +144,8 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             for (int a = 0; a < NS; a++) ptx::mbar_init(&sm.rbar[w][a], 1);
         ptx::mbar_init(&sm.xbar[0], GEMM_EPI_THREADS / 4);       // the peer's first column quarter: one arrival per row
         ptx::mbar_init(&sm.xbar[1], GEMM_EPI_THREADS / 4);
+        ptx::mbar_init(&sm.xbar2[0], GEMM_EPI_THREADS / 4);
+        ptx::mbar_init(&sm.xbar2[1], GEMM_EPI_THREADS / 4);
         sm.abort_flag = 0;
         ptx::fence_barrier_init();
     }
@@ -225,7 +244,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const int n = cofs + (e << 2);
             w.a = *reinterpret_cast<const int32_t *>(base + p.nt_a_off + part * p.H + n);
             w.b = 0; w.d = 0;
-            if (MODE == FUSED_RES) {
+            if (RES) {
                 if (p.bias) w.b = *reinterpret_cast<const int32_t *>(p.bias + n);
                 if (p.nt_c_off >= 0) w.d = *reinterpret_cast<const int32_t *>(base + p.nt_c_off + (mem & 1) * p.H + n);
             }
@@ -234,7 +253,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         auto tab_store = [&](int buf, const FusedTabWords &w) {
             const int n = e << 2;
             *reinterpret_cast<int4 *>(&sm.a32[buf][n]) = make_int4((int)(int8_t)w.a, (int)(int8_t)(w.a >> 8), (int)(int8_t)(w.a >> 16), w.a >> 24);
-            if (MODE == FUSED_RES) {
+            if (RES) {
                 int v[4];
 #pragma unroll
                 for (int b = 0; b < 4; b++)      // pre-shifted so that the sum joins the rank-1 product before its shift
@@ -250,8 +269,26 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
         };
 
+        auto ln_load = [&](int mem, FusedLnWords &w) {      // threads e < tab_items: gains, biases and dot vectors of 4 columns
+            const int8_t *base = p.nt + (int64_t)(mem >> 1) * p.nt_stride;
+            const int n = cofs + (e << 2);
+            w.w = *reinterpret_cast<const int2 *>(reinterpret_cast<const int16_t *>(base + p.nt_w_m) + (mem & 1) * p.H + n);
+            w.b = *reinterpret_cast<const int2 *>(reinterpret_cast<const int16_t *>(base + p.nt_b_m) + (mem & 1) * p.H + n);
+#pragma unroll
+            for (int q = 0; q < 3; q++) w.d[q] = q < p.ndots ? *reinterpret_cast<const int32_t *>(base + p.nt_dot[q] + n) : 0;
+        };
+        auto ln_store = [&](const FusedLnWords &w) {
+            const int n = e << 2;
+            *reinterpret_cast<int2 *>(&sm.ln_w[n]) = w.w;
+            *reinterpret_cast<int2 *>(&sm.ln_b[n]) = w.b;
+#pragma unroll
+            for (int q = 0; q < 3; q++) *reinterpret_cast<int32_t *>(&sm.ln_d[q][n]) = w.d[q];
+        };
+
         const uint32_t peer_max_s = p.cl > 1 ? ptx::mapa_u32(ptx::smem_u32(&sm.peer_max[0][0]), (uint32_t)(crank ^ 1)) : 0u;
         const uint32_t peer_bar_s = p.cl > 1 ? ptx::mapa_u32(ptx::smem_u32(&sm.xbar[0]), (uint32_t)(crank ^ 1)) : 0u;
+        const uint32_t peer_sum_s = (LN && p.cl > 1) ? ptx::mapa_u32(ptx::smem_u32(&sm.peer_sum[0][0]), (uint32_t)(crank ^ 1)) : 0u;
+        const uint32_t peer_bar2_s = (LN && p.cl > 1) ? ptx::mapa_u32(ptx::smem_u32(&sm.xbar2[0]), (uint32_t)(crank ^ 1)) : 0u;
         for (int unit = first_unit; unit < num_units; unit += unit_step, ucount++) {
             const int mt = unit / p.parts, part = unit - mt * p.parts;
             const int m0 = mt * GEMM_BM;
@@ -263,7 +300,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 FusedTabWords w;
                 if (tab_load(unit, w)) tab_store(0, w);
                 pf_xb = p.xb[(int64_t)r * p.xb_stride + part];
-                if (MODE == FUSED_RES && lane == 0) resid_request(unit);
+                if (RES && lane == 0) resid_request(unit);
             }
             // tables of this unit are published; everybody has left the previous unit
             ptx::named_bar_sync(1, GEMM_EPI_THREADS);
@@ -275,6 +312,10 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 const int nmt = nunit / p.parts;
                 pf_xb = p.xb[(int64_t)(nmt * GEMM_BM + row_in_tile) * p.xb_stride + (nunit - nmt * p.parts)];
             }
+            // the norm tables of this unit's member: requested now, stored after pass 1 (nobody reads the previous unit's
+            // any more, and this unit's readers come after a 512-thread barrier)
+            FusedLnWords lnw;
+            if (LN && e < tab_items) ln_load(mem, lnw);
             const uint32_t a32_s = ptx::smem_u32(&sm.a32[tb][0]);
             const uint32_t bcs_s = ptx::smem_u32(&sm.bcs32[tb][0]);
             const bool do_rope = (MODE == FUSED_QKV) && part < 2;
@@ -287,7 +328,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 const int slot = st % NS;
                 fused_wait(&sm.tmem_full[slot], (st / NS) & 1, &sm.abort_flag, p.err, DEV_TIMEOUT_TMEM_FULL);
                 const uint32_t box_s = ptx::smem_u32(sm.box[ew][j]) + row_ofs;
-                if (MODE == FUSED_RES) fused_wait(&sm.rbar[ew][j], ucount & 1, &sm.abort_flag, p.err, DEV_TIMEOUT_FULL);
+                if (RES) fused_wait(&sm.rbar[ew][j], ucount & 1, &sm.abort_flag, p.err, DEV_TIMEOUT_FULL);
                 __syncwarp();                           // lanes leave the waits at different times; the TMEM accesses are warp-wide
                 ptx::tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(slot * BN + cq * CW);
@@ -307,7 +348,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         }
                     }
                     int4 rs4 = make_int4(0, 0, 0, 0);
-                    if (MODE == FUSED_RES) rs4 = ptx::lds_v4(box_s + (((uint32_t)c ^ swz) << 4));
+                    if (RES) rs4 = ptx::lds_v4(box_s + (((uint32_t)c ^ swz) << 4));
                     uint32_t *vc = v[c & 1];
                     ptx::tmem_ld_wait16(vc);
                     if (c + 1 < NCH) {
@@ -319,7 +360,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         const int col = col0 + 16 * c + 4 * q4;
                         const int4 an = ptx::lds_v4(a32_s + 4 * col);
                         int x0, x1, x2, x3;
-                        if (MODE == FUSED_RES && GEMM_FMA_ADDS) {
+                        if (RES && GEMM_FMA_ADDS) {
                             // ((acc + r1 + (b << s)) >> s) + residual with r1 = (xb*a) >> t: the bias joins the rank-1 product
                             // ((b << (s+t)) is a multiple of 2^t), the other adds are multiply-adds by a run-time 1 — the
                             // integer pipe runs at half the rate of the multiply-add pipe and is the busy one here
@@ -340,7 +381,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                             x2 = (int)vc[4 * q4 + 2] + ((xbs * an.z) >> p.rank1_shift);
                             x3 = (int)vc[4 * q4 + 3] + ((xbs * an.w) >> p.rank1_shift);
                         }
-                        if (MODE == FUSED_RES && !GEMM_FMA_ADDS) {
+                        if (RES && !GEMM_FMA_ADDS) {
                             const int4 b4 = ptx::lds_v4(bcs_s + 4 * col);
                             const int32_t rs = q4 == 0 ? rs4.x : (q4 == 1 ? rs4.y : (q4 == 2 ? rs4.z : rs4.w));
                             x0 = ptx::sx_byte0(rs) + ((x0 + b4.x) >> p.out_shift);
@@ -364,6 +405,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 ptx::tmem_st_wait();
             }
             sm.rowpart[cq][row_in_tile] = max(rmx, -rmn);
+            if (LN && e < tab_items) ln_store(lnw);
             ptx::named_bar_sync(2 + quarter, 128);            // the four column quarters of this lane quarter
             int row_max = max(max(sm.rowpart[0][row_in_tile], sm.rowpart[1][row_in_tile]),
                               max(sm.rowpart[2][row_in_tile], sm.rowpart[3][row_in_tile]));
@@ -385,6 +427,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const float scale = aln_scale(row_max);
 
             // ---------------- pass 2: requantise, pack, store ----------------
+            int tot = 0;                                      // FUSED_RES_LN: Σ|x| over this warp's columns of the row
             for (int j = 0; j < NT; j++) {
                 const uint32_t st = stc + (uint32_t)j;
                 const int slot = st % NS;
@@ -407,6 +450,10 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     for (int q4 = 0; q4 < 4; q4++)
                         w[q4] = ptx::pack_sat_s8(aln_quant_f((int)vc[4 * q4], scale), aln_quant_f((int)vc[4 * q4 + 1], scale),
                                                  aln_quant_f((int)vc[4 * q4 + 2], scale), aln_quant_f((int)vc[4 * q4 + 3], scale));
+                    if (LN) {
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; q4++) tot = __dp4a((int)__vabsss4(w[q4]), 0x01010101, tot);
+                    }
                     ptx::sts_v4(box_s + (((uint32_t)c ^ swz) << 4), make_int4((int)w[0], (int)w[1], (int)w[2], (int)w[3]));
                 }
                 // this warp has read its part of the slot: hand it back to the MMA warp
@@ -420,7 +467,64 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 }
             }
             stc += (uint32_t)NT;
-            if (MODE == FUSED_RES && lane == 0 && nunit < num_units) {
+            if (LN) {
+                // ---------------- the mean-abs norm of the finished row (apply_standard_norm, mgpu.cu:646-678) ----------------
+                // y = clip((x * w') / mean|x| + b'), and the dots of y with the B-noise of the projections that read it.  The
+                // row's bytes are still in this lane's boxes; TMEM has been handed back, so the next unit's MMAs run meanwhile.
+                sm.rowsum[cq][row_in_tile] = tot;
+                ptx::named_bar_sync(1, GEMM_EPI_THREADS);        // sums and norm tables of this unit are published
+                int total = sm.rowsum[0][row_in_tile] + sm.rowsum[1][row_in_tile] + sm.rowsum[2][row_in_tile] + sm.rowsum[3][row_in_tile];
+                if (p.cl > 1) {      // the peer block's half of the row: same exchange as for the maxima
+                    if (cq == 0) {
+                        ptx::st_cluster_u32(peer_sum_s + (uint32_t)(tb * GEMM_BM + row_in_tile) * 4u, (uint32_t)total);
+                        ptx::mbar_arrive_cluster(peer_bar2_s + (uint32_t)tb * 8u);
+                    }
+                    if (!sm.abort_flag && !ptx::mbar_wait_cluster(&sm.xbar2[tb], (uint32_t)(ucount >> 1) & 1u, 1000000000ull)) {
+                        sm.abort_flag = 1;
+                        if (p.err) atomicCAS(p.err, 0, DEV_TIMEOUT_PEER);
+                    }
+                    total += sm.peer_sum[tb][row_in_tile];
+                }
+                int mn = fast_div(total, p.fd_h);
+                if (!mn) mn = 1;
+                const float rinv = c_rinv_up.v[mn & 127];        // mn <= 127: a mean of absolute values of int8
+                const uint32_t lw_s = ptx::smem_u32(&sm.ln_w[0]), lb_s = ptx::smem_u32(&sm.ln_b[0]);
+                const uint32_t ld_s = ptx::smem_u32(&sm.ln_d[0][0]);
+                int8_t *hrow = p.h_out + (int64_t)r * p.H + cofs;
+                int dot0 = 0, dot1 = 0, dot2 = 0;
+                for (int j = 0; j < NT; j++) {
+                    const uint32_t box_s = ptx::smem_u32(sm.box[ew][j]) + row_ofs;
+#pragma unroll
+                    for (int c = 0; c < NCH; c++) {
+                        const int4 xw = ptx::lds_v4(box_s + (((uint32_t)c ^ swz) << 4));
+                        const int col = j * BN + cq * CW + 16 * c;
+                        uint32_t yw[4];
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; q4++) {
+                            const uint32_t xv = (uint32_t)(q4 == 0 ? xw.x : (q4 == 1 ? xw.y : (q4 == 2 ? xw.z : xw.w)));
+                            const int lc = col + 4 * q4;
+                            const int2 w2 = ptx::lds_v2(lw_s + 2u * (uint32_t)lc), b2 = ptx::lds_v2(lb_s + 2u * (uint32_t)lc);
+                            const int y0 = div_small(ptx::sx_byte0(xv) * ptx::sx_half0(w2.x), rinv) * p.one + ptx::sx_half0(b2.x);
+                            const int y1 = div_small(ptx::sx_byte1(xv) * (w2.x >> 16), rinv) * p.one + (b2.x >> 16);
+                            const int y2 = div_small(ptx::sx_byte2(xv) * ptx::sx_half0(w2.y), rinv) * p.one + ptx::sx_half0(b2.y);
+                            const int y3 = div_small(((int)xv >> 24) * (w2.y >> 16), rinv) * p.one + (b2.y >> 16);
+                            yw[q4] = pack_clip8(y0, y1, y2, y3);
+                            dot0 = __dp4a((int)yw[q4], (int)ptx::lds_u32(ld_s + (uint32_t)lc), dot0);
+                            if (p.ndots > 1) {
+                                dot1 = __dp4a((int)yw[q4], (int)ptx::lds_u32(ld_s + (uint32_t)(FUSED_MAX_H + lc)), dot1);
+                                dot2 = __dp4a((int)yw[q4], (int)ptx::lds_u32(ld_s + (uint32_t)(2 * FUSED_MAX_H + lc)), dot2);
+                            }
+                        }
+                        *reinterpret_cast<int4 *>(hrow + col) = make_int4((int)yw[0], (int)yw[1], (int)yw[2], (int)yw[3]);
+                    }
+                }
+                // every warp (and both blocks of a pair) adds its columns' share: integer sums, any order
+                int32_t *xo = p.xb_out + (int64_t)r * p.xb_out_stride;
+                atomicAdd(xo, dot0);
+                if (p.ndots > 1) { atomicAdd(xo + 1, dot1); atomicAdd(xo + 2, dot2); }
+                __syncwarp();          // all lanes have read their boxes before lane 0 lets the next residual bytes in
+            }
+            if (RES && lane == 0 && nunit < num_units) {
                 // the boxes are free once their stores have read them: fetch the next unit's residual bytes
                 ptx::tma_store_wait_read<0>();
                 resid_request(nunit);

@@ -48,6 +48,8 @@ int gemm_init() {
     EGG_CUDA(cudaFuncSetAttribute(gemm_fused_kernel<256, FUSED_RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_smem_bytes<256>()));
     EGG_CUDA(cudaFuncSetAttribute(gemm_fused_kernel<128, FUSED_QKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_smem_bytes<128>()));
     EGG_CUDA(cudaFuncSetAttribute(gemm_fused_kernel<128, FUSED_RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_smem_bytes<128>()));
+    EGG_CUDA(cudaFuncSetAttribute(gemm_fused_kernel<256, FUSED_RES_LN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_smem_bytes<256>()));
+    EGG_CUDA(cudaFuncSetAttribute(gemm_fused_kernel<128, FUSED_RES_LN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_smem_bytes<128>()));
     return EGG_OK;
 }
 
@@ -156,17 +158,19 @@ int launch_gemm_fused(cudaStream_t st, int mode, const int8_t *A, const int8_t *
     if (!g_encode) { set_error("gemm_init() was not called"); return EGG_E_STATE; }
     p.cl = fused_cluster_size(p.H);
     if (p.M <= 0 || p.M % GEMM_BM || p.seq_len % GEMM_BM || p.cl == 0 || p.K % 16 || p.parts < 1 ||
-        (mode == FUSED_RES && (p.parts != 1 || !resid)) || (mode != FUSED_QKV && mode != FUSED_RES)) {
+        (mode != FUSED_QKV && (p.parts != 1 || !resid)) || (mode != FUSED_QKV && mode != FUSED_RES && mode != FUSED_RES_LN) ||
+        (mode == FUSED_RES_LN && (!p.h_out || !p.xb_out || (p.ndots != 1 && p.ndots != 3)))) {
         set_error("unsupported row-owning GEMM shape M=%d H=%d K=%d parts=%d seq_len=%d", p.M, p.H, p.K, p.parts, p.seq_len);
         return EGG_E_INVALID;
     }
-    if (mode == FUSED_RES && p.out_shift + p.rank1_shift > 20) {     // (bias + noise) << (both shifts) joins a product below 2^30
+    if (mode != FUSED_QKV && p.out_shift + p.rank1_shift > 20) {     // (bias + noise) << (both shifts) joins a product below 2^30
         set_error("shifts %d + %d too large for the pre-shifted bias table", p.out_shift, p.rank1_shift);
         return EGG_E_INVALID;
     }
     const int hl = p.H / p.cl;                       // columns per block
     const int bn = (hl % 256 == 0) ? 256 : 128;
     p.fd_head = make_fastdiv(p.head_dim > 0 ? p.head_dim : 64);
+    p.fd_h = make_fastdiv(p.H);
     p.one = 1;
     CUtensorMap ta, tb, to, tr;
     int rc;
@@ -175,13 +179,15 @@ int launch_gemm_fused(cudaStream_t st, int mode, const int8_t *A, const int8_t *
     const uint64_t out_rows = p.parts > 1 ? (uint64_t)p.parts * (uint64_t)p.part_rows : (uint64_t)p.M;
     if ((rc = make_tmap_box8(&to, out, out_rows, (uint64_t)p.H, (uint32_t)bn / 4))) return rc;
     tr = to;
-    if (mode == FUSED_RES && (rc = make_tmap_box8(&tr, resid, (uint64_t)p.M, (uint64_t)p.H, (uint32_t)bn / 4))) return rc;
+    if (mode != FUSED_QKV && (rc = make_tmap_box8(&tr, resid, (uint64_t)p.M, (uint64_t)p.H, (uint32_t)bn / 4))) return rc;
     const int units = (p.M / GEMM_BM) * p.parts;
     if (bn == 256) {
         if (mode == FUSED_QKV) return launch_fused_one<256, FUSED_QKV>(st, ta, tb, to, tr, p, units, num_sms);
+        if (mode == FUSED_RES_LN) return launch_fused_one<256, FUSED_RES_LN>(st, ta, tb, to, tr, p, units, num_sms);
         return launch_fused_one<256, FUSED_RES>(st, ta, tb, to, tr, p, units, num_sms);
     }
     if (mode == FUSED_QKV) return launch_fused_one<128, FUSED_QKV>(st, ta, tb, to, tr, p, units, num_sms);
+    if (mode == FUSED_RES_LN) return launch_fused_one<128, FUSED_RES_LN>(st, ta, tb, to, tr, p, units, num_sms);
     return launch_fused_one<128, FUSED_RES>(st, ta, tb, to, tr, p, units, num_sms);
 }
 

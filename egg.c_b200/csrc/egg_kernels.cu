@@ -154,57 +154,6 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
     return (uint32_t)(a & 0xFF) | ((uint32_t)(b & 0xFF) << 8) | ((uint32_t)(c & 0xFF) << 16) | ((uint32_t)(d & 0xFF) << 24);
 }
 
-// ---- exact float arithmetic without the conversion unit ----
-// The reference's requantisation is float math ((float)v * scale, roundf, int division);
-// the same values are produced here with adds against 1.5*2^23 on the ALU/FMA pipes,
-// because int<->float conversion instructions run at a small fraction of their rate.
-constexpr float kMagic = 12582912.0f;          // 1.5 * 2^23
-constexpr int kMagicBits = 0x4B400000;
-// (float)v for |v| < 2^22, exact
-__device__ __forceinline__ float i2f_small(int v) { return __int_as_float(kMagicBits + v) - kMagic; }
-// the same value through the conversion unit: used for a share of the conversions so that the otherwise idle unit
-// takes load off the integer/float pipes
-__device__ __forceinline__ float i2f_cvt(int v) { return __int2float_rn(v); }
-// roundf(x) (half away from zero) as a float, for |x| < 2^22: round-to-nearest-even by the
-// magic add, then the two tie cases that differ are corrected (x - rint(x) is exact).
-__device__ __forceinline__ float roundf_small(float x) {
-    float rf = (x + kMagic) - kMagic;
-    float d = x - rf;
-    if (d == 0.5f && x > 0.0f) rf += 1.0f;
-    if (d == -0.5f && x < 0.0f) rf -= 1.0f;
-    return rf;
-}
-// integer value of a float that holds an integer, |f| < 2^22
-__device__ __forceinline__ int f2i_exact(float f) { return __float_as_int(f + kMagic) - kMagicBits; }
-
-// trunc(a / mn) as C integer division does, for |a| < 2^16 and 1 <= mn <= 127, with rinv_up = (1/mn) * (1 + 2^-17):
-// the factor pushes every quotient away from zero by |q| * 7.6e-6 -- more than the float error of the product
-// (three roundings, < |q| * 1.8e-7), so an exact quotient k lands beyond k and truncates to k, and less than the
-// distance 1/mn from a non-integer quotient to the next integer (|q| * 7.8e-6 < 1/mn because |q| * mn = |a| < 2^16).
-// The configuration check bounds |x * gain| by 2^16 from the noise amplitude.
-__device__ __forceinline__ int div_small(int a, float rinv_up) {
-    return __float2int_rz(i2f_small(a) * rinv_up);
-}
-
-// [sat8(a), sat8(b), sat8(c), sat8(d)] as bytes 0..3 with the reference's clip to [-127, 127]
-__device__ __forceinline__ uint32_t pack_clip8(int a, int b, int c, int d) {
-    uint32_t hi, r;
-    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(d), "r"(c));
-    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(a), "r"(hi));
-    return __vmaxs4(r, 0x81818181u);
-}
-
-// (1/mn) * (1 + 2^-17) for mn = 1..127 (div_small's factor): the mean is the same for every lane of a row, so the
-// reciprocal is one constant-bank read instead of a division per row.  Compile-time IEEE single arithmetic, the same two
-// roundings as the expression it replaces.
-struct RinvTable { float v[128]; };
-constexpr RinvTable make_rinv_table() {
-    RinvTable t = {};
-    for (int mn = 1; mn < 128; mn++) t.v[mn] = (1.0f / (float)mn) * (1.0f + 0x1p-17f);
-    return t;
-}
-__constant__ RinvTable c_rinv_up = make_rinv_table();
-
 // One warp per run of ROW_RUN consecutive rows of ONE population member (seq_len is a multiple of 16, so a run never
 // crosses members); NJ = H/128 chunks of 4 elements per lane.  Everything that depends on the member only -- the
 // perturbed gain / bias tables and the noise vectors of the following projections, 3.5 H bytes -- is loaded once per
@@ -808,10 +757,23 @@ int launch_fitness(cudaStream_t st, const int32_t *loss, int32_t *fit, int pairs
 // =========================================================================
 // update operands: the two noise matrices of vote = Σ_p f_p a_p b_p^T, pair index contiguous
 // =========================================================================
+// The update kernels are bound by the integer pipe (half the rate of the multiply-add pipe): the single-field noise
+// value's sign select and the seed additions are written as multiply-adds with run-time multipliers (constants would
+// be folded back into integer-pipe instructions).  hash_mix(seed + idx * 0x9e3779b9) == hash_rng(seed, idx).
+struct UpdMul { int one, two; };
+static inline UpdMul make_upd_mul() { UpdMul m; m.one = 1; m.two = 2; return m; }
+__device__ __forceinline__ uint32_t hash_mix(uint32_t x) {
+    x ^= x >> 16; x *= 0x85ebca6bu;
+    x ^= x >> 13; x *= 0xc2b2ae35u;
+    x ^= x >> 16;
+    return x;
+}
+
 constexpr int UPD_ROWS_PER_BLOCK = 8;     // operand rows one block writes: the pair seeds and fitness words are loaded once for all of them
 
+template <bool GAUSS>
 __global__ void __launch_bounds__(256) update_operands_kernel(int8_t *na, int8_t *nb, const int32_t *fit, int pairs, int kp, int rows_k, int cols_n,
-                                       int off_a, int off_b, int seed_base, uint32_t step_seed, int mask, int gaussian, int split) {
+                                       int off_a, int off_b, int seed_base, uint32_t step_seed, int mask, int split, const UpdMul um) {
     const int row0 = blockIdx.y * UPD_ROWS_PER_BLOCK;      // 0..cols_n-1 -> NA, cols_n.. -> NB (cols_n is a multiple of the group size)
     const int ktot = split ? 2 * kp : kp;
     const bool is_a = row0 < cols_n;
@@ -838,7 +800,15 @@ __global__ void __launch_bounds__(256) update_operands_kernel(int8_t *na, int8_t
             const uint32_t idx = (uint32_t)(is_a ? row : row - cols_n);
             int val[4];
 #pragma unroll
-            for (int j = 0; j < 4; j++) val[j] = f[j] ? f[j] * noise_from_hash(seed[j], idx, mask, gaussian) : 0;
+            for (int j = 0; j < 4; j++) {
+                if (GAUSS) {
+                    val[j] = f[j] * noise_from_hash(seed[j], idx, mask, 1);
+                } else {
+                    // f * noise_field(r, 0, 1, mask): magnitude (r >> 1) & mask, positive when bit 0 is set
+                    const uint32_t r = hash_mix(seed[j] * (uint32_t)um.one + idx * 0x9e3779b9u);
+                    val[j] = (f[j] * (int)((r >> 1) & (uint32_t)mask)) * ((int)(r & 1u) * um.two - 1);
+                }
+            }
             const uint32_t w = pack4(val[0], val[1], val[2], val[3]);
             if (is_a) *reinterpret_cast<uint32_t *>(na + (int64_t)row * ktot + pp) = w;
             else *reinterpret_cast<uint32_t *>(nb + (int64_t)(row - cols_n) * ktot + pp) = w;
@@ -853,7 +823,8 @@ int launch_update_operands(cudaStream_t st, int8_t *na, int8_t *nb, const int32_
     int ktot = split ? 2 * kp : kp;
     int gx = (ktot / 4 + 255) / 256; if (gx > 32) gx = 32;
     dim3 grid((unsigned)gx, (unsigned)((rows_k + cols_n) / UPD_ROWS_PER_BLOCK));
-    update_operands_kernel<<<grid, 256, 0, st>>>(na, nb, fit, pairs, kp, rows_k, cols_n, off_a, off_b, seed_base, step_seed, mask, gaussian, split);
+    if (gaussian) update_operands_kernel<true><<<grid, 256, 0, st>>>(na, nb, fit, pairs, kp, rows_k, cols_n, off_a, off_b, seed_base, step_seed, mask, split, make_upd_mul());
+    else update_operands_kernel<false><<<grid, 256, 0, st>>>(na, nb, fit, pairs, kp, rows_k, cols_n, off_a, off_b, seed_base, step_seed, mask, split, make_upd_mul());
     EGG_CUDA(cudaGetLastError());
     return EGG_OK;
 }
@@ -951,16 +922,36 @@ int launch_muon_m_from_votes(cudaStream_t st, const VoteApplyParams &p) {
 // =========================================================================
 // vector parameters (update_vector_adam_kernel, mgpu.cu:1114-1152): one block per element
 // =========================================================================
-__global__ void __launch_bounds__(256) update_vector_kernel(const VecUpdParams p) {
+template <bool FAST>
+__global__ void __launch_bounds__(256) update_vector_kernel(const VecUpdParams p, const UpdMul um) {
     const int idx = blockIdx.x;
     int vote = 0;
-    // no early-out on zero fitness: four pairs per trip keep eight independent hash chains in flight
+    if (!FAST) {
 #pragma unroll 4
-    for (int pr = threadIdx.x; pr < p.pairs; pr += blockDim.x) {
-        const int f = p.fit[pr];
-        const uint32_t s = p.step_seed + (uint32_t)pr + (uint32_t)p.seed_base;
-        vote += f * noise_from_hash(s + (uint32_t)p.off_a, (uint32_t)idx, p.mask, p.gaussian) *
-                noise_from_hash(s + (uint32_t)p.off_b, (uint32_t)idx, p.mask, p.gaussian);
+        for (int pr = threadIdx.x; pr < p.pairs; pr += blockDim.x) {
+            const int f = p.fit[pr];
+            const uint32_t s = p.step_seed + (uint32_t)pr + (uint32_t)p.seed_base;
+            vote += f * noise_from_hash(s + (uint32_t)p.off_a, (uint32_t)idx, p.mask, p.gaussian) *
+                    noise_from_hash(s + (uint32_t)p.off_b, (uint32_t)idx, p.mask, p.gaussian);
+        }
+    } else {
+        // f * na * nb with na, nb = ±((r >> 1) & mask), positive when bit 0 is set: the magnitudes are taken doubled
+        // (r & (mask << 1), no shift; every term is then 4x and the thread's sum is divided exactly afterwards, with
+        // |sum| < pairs/256 * 4 * 31^2 * |f| far inside int32), the sign of the product is + when the two bits agree.
+        // No early-out on zero fitness: four pairs per trip keep eight independent hash chains in flight.
+        const uint32_t base = p.step_seed + (uint32_t)p.seed_base + (uint32_t)idx * 0x9e3779b9u;
+        const uint32_t ca = base + (uint32_t)p.off_a, cb = base + (uint32_t)p.off_b;
+        const uint32_t m2 = (uint32_t)p.mask << 1;
+        int vote4 = 0;
+#pragma unroll 4
+        for (int pr = threadIdx.x; pr < p.pairs; pr += blockDim.x) {
+            const int f = p.fit[pr];
+            const uint32_t ra = hash_mix((uint32_t)pr * (uint32_t)um.one + ca), rb = hash_mix((uint32_t)pr * (uint32_t)um.one + cb);
+            const int mm = (int)(ra & m2) * (int)(rb & m2);
+            const int sg = 1 - (int)((ra ^ rb) & 1u) * um.two;
+            vote4 += (f * sg) * mm;
+        }
+        vote = vote4 >> 2;
     }
     __shared__ int s_part[8];
     vote = warp_sum(vote);
@@ -978,7 +969,10 @@ __global__ void __launch_bounds__(256) update_vector_kernel(const VecUpdParams p
     }
 }
 int launch_update_vector(cudaStream_t st, const VecUpdParams &p) {
-    update_vector_kernel<<<p.len, 256, 0, st>>>(p);
+    // the single-field form sums 4x terms per thread: (pairs/256) * 4 * mask^2 * 127 must stay inside int32
+    const bool fast = !p.gaussian && (int64_t)((p.pairs + 255) / 256) * 4 * p.mask * p.mask * 127 < (1ll << 31);
+    if (fast) update_vector_kernel<true><<<p.len, 256, 0, st>>>(p, make_upd_mul());
+    else update_vector_kernel<false><<<p.len, 256, 0, st>>>(p, make_upd_mul());
     EGG_CUDA(cudaGetLastError());
     return EGG_OK;
 }

@@ -479,8 +479,11 @@ int egg_wave_members(egg_ctx *ctx);
  * The projections that feed an adaptive normalisation (Q/K/V -> adaptive_qkv_normalize, O and MLP-down ->
  * adaptive_layer_normalize; egg_adaptive_normalize.h:10-103, called at mgpu.cu:782-784, 756, 830) run as
  * row-owning kernels that keep a whole output row in tensor memory and write the requantised int8 row
- * directly, whenever hidden_dim <= 512 and seq_len % 128 == 0; other shapes take the two-kernel form
- * (int32 pre-activations + row maxima, then a requantisation kernel).  Both forms give identical bytes.
+ * directly, whenever seq_len % 128 == 0 and hidden_dim is a multiple of 128 up to 512 (one thread block per
+ * 128-row tile) or a multiple of 256 up to 1024 (a cluster of two thread blocks per tile, each owning half of
+ * the columns and exchanging the row maxima through the other's shared memory); other shapes take the
+ * two-kernel form (int32 pre-activations + row maxima, then a requantisation kernel).  Both forms give
+ * identical bytes.
  * enable = 0 forces the two-kernel form (for A/B timing and for tests that compare the two); no counterpart
  * in the reference.  egg_fused_epilogues_active tells which form this context's evaluations take.
  */
