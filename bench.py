@@ -245,7 +245,7 @@ def projection_ops_per_member_token(H, L, V):
     return 2.0 * (8 * H * H + 12 * H * H * L + H * V)
 
 
-def c5_sample_run(pkg, synth, device, members, peaks, mma_loop_tops, steps=2, fused=True):
+def c5_sample_run(pkg, synth, device, members, peaks, mma_loop_tops, steps=2, fused=2):
     """d-eggs-scale shapes on one GPU: `members` members of the 262 144-member population evaluated (the evaluation
     is linear in the members), then the whole Muon update over all 131 072 pairs from a seeded ternary fitness vector.
     Gives the two times that decide how a fixed population of 262 144 scales over 8 GPUs: evaluation shards, the
@@ -253,7 +253,7 @@ def c5_sample_run(pkg, synth, device, members, peaks, mma_loop_tops, steps=2, fu
     pop = 262144
     cfg = pkg.default_config(population_size=pop, use_muon=1, **C5)
     ctx = pkg.Context(cfg, device, members)
-    ctx.set_fused_epilogues(fused)
+    ctx.set_fused_epilogues(fused)           # level: 0 two-kernel, 1 row-owning projections, 2 + norm inside MLP-down
     fused_active = ctx.fused_epilogues_active()
     ctx.upload_model(synth.random_model(cfg, 0, "ternary"))
     ctx.set_dataset(synth.zipf_bytes(1, 1 << 24))
@@ -281,7 +281,8 @@ def c5_sample_run(pkg, synth, device, members, peaks, mma_loop_tops, steps=2, fu
     t_eval_1 = eval_ms * pop / members
     return {"workload": "12 layers, H 1024, 16 heads, seq 512, ternary weight values, Muon; %d of 262144 members evaluated, update over "
                         "all 131072 pairs" % members,
-            "adaptive_norms": "fused into the projection epilogues (row-owning kernels on pairs of thread blocks)" if fused_active else "two-kernel form",
+            "adaptive_norms": {0: "two-kernel form", 1: "fused into the projection epilogues (row-owning kernels on pairs of thread blocks)",
+                               2: "fused into the projection epilogues (row-owning kernels on pairs of thread blocks), the next mean-abs norm inside MLP-down"}[fused_active],
             "eval_member_tokens_per_s": members * S / (eval_ms / 1e3), "eval_ms": eval_ms, "update_ms": upd_ms,
             "newton_schulz_and_apply_ms": prof.get("muon", (0.0, 0))[0] / steps,
             "update_gemm_ms": prof.get("update_gemm", (0.0, 0))[0] / steps,
@@ -430,7 +431,7 @@ def run_c5slice(args, pkg, synth, torch, real_stdout, peaks):
     mma = ctx0.measure_int8_peak(16384, 2048, 2048, 20)
     ctx0.close()
     sampler = ClockSampler(0); sampler.start()
-    r = c5_sample_run(pkg, synth, 0, members, peaks, mma, steps=max(1, args.steps), fused=not args.two_kernel_norm)
+    r = c5_sample_run(pkg, synth, 0, members, peaks, mma, steps=max(1, args.steps), fused=0 if args.two_kernel_norm else args.fused_level)
     clocks = sampler.stop()
     S = C5["seq_len"]
     gen_ms = r["eval_ms"] + r["update_ms"]
@@ -458,6 +459,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the extra legs of the default line (recurrent model, reference GPU kernels, C5 sample)")
     ap.add_argument("--two-kernel-norm", action="store_true", help="A/B: take the two-kernel form of the adaptive normalisations (int32 pre-activations + requantisation kernels)")
+    ap.add_argument("--fused-level", type=int, default=2, choices=[0, 1, 2],
+                    help="A/B: 0 two-kernel adaptive norms, 1 row-owning projections, 2 (default) also the next mean-abs norm inside the MLP-down epilogue")
     ap.add_argument("--attention-tc", action="store_true", help="A/B: take the tcgen05 form of the attention kernel")
     ap.add_argument("--wave", type=int, default=0, help="members per internal wave (0: the library's default)")
     ap.add_argument("--small", action="store_true", help="profiling-sized run: 1024 members, one warm-up step, no end-to-end / CPU legs")
@@ -508,8 +511,7 @@ def main():
         pop = args.pop * world                   # weak scaling: fixed members per GPU
         cfg = pkg.default_config(population_size=pop, **C2)
     ctx = pkg.Context(cfg, local_rank, args.wave)
-    if args.two_kernel_norm:
-        ctx.set_fused_epilogues(False)
+    ctx.set_fused_epilogues(0 if args.two_kernel_norm else args.fused_level)
     if args.attention_tc:
         ctx.set_attention_tensor_core(True)
     fused_active = ctx.fused_epilogues_active()
@@ -702,7 +704,8 @@ def main():
             "config": {"workload": ("c5: d-eggs-scale generation, L=12 H=1024 heads=16 MLP=4H seq=512 vocab=256, ternary weight values, Muon, "
                                     "fixed population sharded over the GPUs") if strong else WORKLOAD, "population_size": pop, "members_per_gpu": per, "seq_len": S, "hidden_dim": H,
                        "n_layers": L, "wave_members": wave_members, "dataset_bytes": DATA_LEN,
-                       "adaptive_norms": "fused into the projection epilogues (row-owning kernels)" if fused_active else "two-kernel form",
+                       "adaptive_norms": {0: "two-kernel form", 1: "fused into the projection epilogues (row-owning kernels)",
+                                          2: "fused into the projection epilogues (row-owning kernels), the next mean-abs norm inside MLP-down"}[fused_active],
                        "l2_policy": "inputs larger than L2: each wave streams > 2 GB of activations, dataset 64 MiB",
                        "parallelism": "population sharded, pair-aligned; one NCCL all-gather of fitness per generation"},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": int(DATA_LEN),

@@ -429,14 +429,17 @@ class Context:
     def launch_count(self):
         return lib().egg_launch_count(self._h)
 
-    def set_fused_epilogues(self, enable):
-        _check(lib().egg_set_fused_epilogues(self._h, 1 if enable else 0))
+    def set_fused_epilogues(self, level):
+        """0 / False: two-kernel adaptive norms; 1 / True: row-owning projections; 2 (the default of a new context):
+        also the next mean-abs norm inside the MLP-down epilogue."""
+        _check(lib().egg_set_fused_epilogues(self._h, int(level)))
 
     def set_attention_tensor_core(self, enable):
         _check(lib().egg_set_attention_tensor_core(self._h, 1 if enable else 0))
 
     def fused_epilogues_active(self):
-        return bool(lib().egg_fused_epilogues_active(self._h))
+        """The level in effect (0 when the configuration takes the two-kernel form)."""
+        return int(lib().egg_fused_epilogues_active(self._h))
 
     def wave_members(self):
         return lib().egg_wave_members(self._h)

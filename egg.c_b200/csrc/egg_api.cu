@@ -114,7 +114,7 @@ struct egg_ctx {
     void *scratch[16] = {};
     size_t scratch_bytes[16] = {};
     // row-owning projections with the adaptive normalisations fused (default wherever the shapes allow)
-    bool fused_on = true;
+    int fused_level = 2;      // 0: two-kernel adaptive norms; 1: row-owning projections; 2: + the next mean-abs norm inside MLP-down
     // attention on tcgen05 (egg_attention_tc.cu) instead of the mma.sync kernel: correct but slower as measured, off by default
     bool attention_tc_on = false;
     // measurement
@@ -652,7 +652,7 @@ extern "C" int egg_set_dataset(egg_ctx *c, const uint8_t *host_tokens, int64_t n
 // ---------------------------------------------------------------- evaluation
 
 static bool use_fused(const egg_ctx *c) {
-    return c->fused_on && fused_supported(c->cfg.hidden_dim, c->cfg.seq_len);
+    return c->fused_level > 0 && fused_supported(c->cfg.hidden_dim, c->cfg.seq_len);
 }
 
 static FusedParams base_fused(egg_ctx *c, int M, int K, int parts) {
@@ -697,8 +697,13 @@ static int scaled_dot1(egg_ctx *c, int M, const int8_t *x, int terms, int nt_dot
     return scaled_dots(c, M, x, terms, 1, &nt_dot, &ov_off, out, out_stride);
 }
 
+// The mean-abs norm that follows an MLP block (LN1 of the next layer or the final norm) and the row dots after it.
+struct NextNorm { int w_m, b_m, ndots, dot[3]; };
+
+// nn != null and *norm_done == true on return: the down projection's epilogue also wrote h = norm(x) and the dots.
 static int run_mlp(egg_ctx *c, int M, const MlpOff &mo, int nt_base, const int8_t *up_t, const int8_t *up_bias, const int8_t *dn_t,
-                   const int8_t *dn_bias, int64_t ov_dn_row) {
+                   const int8_t *dn_bias, int64_t ov_dn_row, const NextNorm *nn = nullptr, bool *norm_done = nullptr) {
+    if (norm_done) *norm_done = false;
     const int H = c->cfg.hidden_dim;
     GemmParams g = base_gemm(c, M, 4 * H, H);
     g.nt_a_off = nt_base + mo.up_a; g.nt_c_off = nt_base + mo.bup_d; g.nt_d_off = nt_base + mo.dn_b;
@@ -711,6 +716,15 @@ static int run_mlp(egg_ctx *c, int M, const MlpOff &mo, int nt_base, const int8_
         FusedParams f = base_fused(c, M, 4 * H, 1);
         f.nt_a_off = nt_base + mo.dn_a; f.nt_c_off = nt_base + mo.bdn_d;
         f.xb = c->d_xb2; f.xb_stride = 1; f.out_shift = c->cfg.shift_mlp_down; f.bias = dn_bias;
+        if (nn && c->fused_level > 1) {
+            // ... and the next mean-abs norm with its row dots (added to a cleared xb) while the row is still on chip
+            f.nt_w_m = nn->w_m; f.nt_b_m = nn->b_m; f.ndots = nn->ndots;
+            for (int q = 0; q < nn->ndots; q++) f.nt_dot[q] = nn->dot[q];
+            f.h_out = c->d_h; f.xb_out = c->d_xb; f.xb_out_stride = 3;
+            EGG_CUDA(cudaMemsetAsync(c->d_xb, 0, (size_t)M * 3 * sizeof(int32_t), c->stream));
+            if (norm_done) *norm_done = true;
+            return PROF(EGG_PROF_GEMM_PRE32, launch_gemm_fused(c->stream, FUSED_RES_LN, c->d_u, dn_t, c->d_x, c->d_x, f, c->num_sms));
+        }
         return PROF(EGG_PROF_GEMM_PRE32, launch_gemm_fused(c->stream, FUSED_RES, c->d_u, dn_t, c->d_x, c->d_x, f, c->num_sms));
     }
     GemmParams d = base_gemm(c, M, H, 4 * H);
@@ -759,8 +773,23 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
     if (sc) { r0.ov_emb_row = c->d_scales + SL.embedding_row; r0.ov_emb_col = c->d_scales + SL.embedding_col; }
     if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, r0, 0)))) return rc;
     if (sc && (rc = scaled_dot1(c, M, c->d_h, 1, nm.mlp_init.up_b, SL.w_emb_mlp_up_row, c->d_xb, 3))) return rc;
+    // the norm after every MLP block: LN1 of the next layer (three dots for q, k, v) or the final norm (one dot for the head)
+    auto next_norm = [&](int layer) {
+        NextNorm n;
+        memset(&n, 0, sizeof(n));
+        if (layer < cf.n_layers) {
+            const int nbl = nm.layer0 + layer * nm.layer_stride;
+            n.w_m = nbl + nm.layer_rel.ln1.w_m; n.b_m = nbl + nm.layer_rel.ln1.b_m; n.ndots = 3;
+            n.dot[0] = nbl + nm.layer_rel.qkv_b; n.dot[1] = n.dot[0] + H; n.dot[2] = n.dot[0] + 2 * H;
+        } else {
+            n.w_m = nm.ln_f.w_m; n.b_m = nm.ln_f.b_m; n.ndots = 1; n.dot[0] = nm.emb_b;
+        }
+        return n;
+    };
+    bool norm_done = false;
+    NextNorm nn = next_norm(0);
     if ((rc = run_mlp(c, M, nm.mlp_init, 0, sh + c->so.init_up, mdl + L.mlp_emb_bias_up, sh + c->so.init_dn, mdl + L.mlp_emb_bias_down,
-                      SL.w_emb_mlp_down_row))) return rc;
+                      SL.w_emb_mlp_down_row, &nn, &norm_done))) return rc;
 
     for (int l = 0; l < cf.n_layers; l++) {
         const int nb = nm.layer0 + l * nm.layer_stride;
@@ -773,7 +802,7 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
         RowParams ra = base_row(c, M);
         ra.nt_w_m = nb + lo.ln1.w_m; ra.nt_b_m = nb + lo.ln1.b_m;
         ra.ndots = 3; ra.nt_dot[0] = nb + lo.qkv_b; ra.nt_dot[1] = nb + lo.qkv_b + H; ra.nt_dot[2] = nb + lo.qkv_b + 2 * H;
-        if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, ra, row_mode)))) return rc;
+        if (!norm_done && (rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, ra, row_mode)))) return rc;
         const int64_t lH = (int64_t)l * H;
         if (sc) {
             const int64_t ovq[3] = {SL.w_q_row + lH, SL.w_k_row + lH, SL.w_v_row + lH};
@@ -816,14 +845,15 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
         rb.ndots = 1; rb.nt_dot[0] = nb + lo.mlp.up_b;
         if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, rb, row_mode)))) return rc;
         if (sc && (rc = scaled_dot1(c, M, c->d_h, 1, nb + lo.mlp.up_b, SL.w_up_row + lH, c->d_xb, 3))) return rc;
+        nn = next_norm(l + 1);
         if ((rc = run_mlp(c, M, lo.mlp, nb, shl + c->so.up, mdl + L.mlp_bias_up + (int64_t)l * 4 * H, shl + c->so.dn,
-                          mdl + L.mlp_bias_down + (int64_t)l * H, SL.w_down_row + 4 * lH))) return rc;
+                          mdl + L.mlp_bias_down + (int64_t)l * H, SL.w_down_row + 4 * lH, &nn, &norm_done))) return rc;
     }
     // final norm + tied-embedding head + cross-entropy (mgpu.cu:954-1024)
     RowParams rf = base_row(c, M);
     rf.nt_w_m = nm.ln_f.w_m; rf.nt_b_m = nm.ln_f.b_m;
     rf.ndots = 1; rf.nt_dot[0] = nm.emb_b;
-    if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, rf, use_fused(c) ? 2 : 1)))) return rc;
+    if (!norm_done && (rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, rf, use_fused(c) ? 2 : 1)))) return rc;
     if (sc && (rc = scaled_dot1(c, M, c->d_h, 1, nm.emb_b, SL.embedding_col, c->d_xb, 3))) return rc;
     GemmParams gh = base_gemm(c, M, V, H);
     gh.nt_a_off = nm.head_a; gh.xb = c->d_xb; gh.xb_stride = 3; gh.out_shift = cf.shift_logit;
@@ -1388,11 +1418,11 @@ extern "C" int egg_measure_int8_peak(egg_ctx *c, int m, int n, int k, int iters,
 
 extern "C" int egg_set_fused_epilogues(egg_ctx *c, int enable) {
     if (!c) { set_error("null context"); return EGG_E_INVALID; }
-    c->fused_on = enable != 0;
+    c->fused_level = enable <= 0 ? 0 : (enable == 1 ? 1 : 2);
     return EGG_OK;
 }
 
-extern "C" int egg_fused_epilogues_active(egg_ctx *c) { return (c && use_fused(c)) ? 1 : 0; }
+extern "C" int egg_fused_epilogues_active(egg_ctx *c) { return (c && use_fused(c)) ? c->fused_level : 0; }
 
 extern "C" int egg_set_attention_tensor_core(egg_ctx *c, int enable) {
     if (!c) { set_error("null context"); return EGG_E_INVALID; }

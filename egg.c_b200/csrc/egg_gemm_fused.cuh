@@ -73,11 +73,12 @@ struct FusedSmem {
     alignas(16) int32_t bcs32[2][FUSED_MAX_H];          // (bias + bias-noise delta of the member's sign) << out_shift
     alignas(16) int32_t rowpart[4][GEMM_BM];            // per-row abs-max of each column quarter
     alignas(16) int32_t peer_max[2][GEMM_BM];           // per-row abs-max of the peer block's columns (written by the peer)
-    alignas(16) int32_t rowsum[4][GEMM_BM];             // FUSED_RES_LN: per-row Σ|x| of each column quarter
+    alignas(16) uint16_t rowsum[4][GEMM_BM];            // FUSED_RES_LN: per-row Σ|x| of each column quarter (<= 127 * 128 columns)
     alignas(16) int32_t peer_sum[2][GEMM_BM];           // ... and of the peer block's columns
-    alignas(16) int16_t ln_w[FUSED_MAX_H];              // FUSED_RES_LN: perturbed gains / biases of the unit's member
-    alignas(16) int16_t ln_b[FUSED_MAX_H];
-    alignas(16) int8_t ln_d[3][FUSED_MAX_H];            // B-noise of the following projections
+    // FUSED_RES_LN, per group of 4 columns: the member's perturbed gains and biases {w0 w1 | w2 w3 | b0 b1 | b2 b3} (int16
+    // pairs), and the B-noise of the following projections {dot 0 | dot 1 | dot 2 | -} (four int8 each): one 16-byte read each
+    alignas(16) int4 ln_wb[FUSED_MAX_H / 4];
+    alignas(16) int4 ln_d4[FUSED_MAX_H / 4];
     alignas(8) uint64_t xbar[2];                        // arrival of the peer's maxima, one barrier per unit parity
     uint64_t xbar2[2];                                  // arrival of the peer's sums
     alignas(8) uint64_t full[GEMM_STAGES];
@@ -278,11 +279,8 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             for (int q = 0; q < 3; q++) w.d[q] = q < p.ndots ? *reinterpret_cast<const int32_t *>(base + p.nt_dot[q] + n) : 0;
         };
         auto ln_store = [&](const FusedLnWords &w) {
-            const int n = e << 2;
-            *reinterpret_cast<int2 *>(&sm.ln_w[n]) = w.w;
-            *reinterpret_cast<int2 *>(&sm.ln_b[n]) = w.b;
-#pragma unroll
-            for (int q = 0; q < 3; q++) *reinterpret_cast<int32_t *>(&sm.ln_d[q][n]) = w.d[q];
+            sm.ln_wb[e] = make_int4(w.w.x, w.w.y, w.b.x, w.b.y);
+            sm.ln_d4[e] = make_int4(w.d[0], w.d[1], w.d[2], 0);
         };
 
         const uint32_t peer_max_s = p.cl > 1 ? ptx::mapa_u32(ptx::smem_u32(&sm.peer_max[0][0]), (uint32_t)(crank ^ 1)) : 0u;
@@ -471,9 +469,9 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 // ---------------- the mean-abs norm of the finished row (apply_standard_norm, mgpu.cu:646-678) ----------------
                 // y = clip((x * w') / mean|x| + b'), and the dots of y with the B-noise of the projections that read it.  The
                 // row's bytes are still in this lane's boxes; TMEM has been handed back, so the next unit's MMAs run meanwhile.
-                sm.rowsum[cq][row_in_tile] = tot;
+                sm.rowsum[cq][row_in_tile] = (uint16_t)tot;
                 ptx::named_bar_sync(1, GEMM_EPI_THREADS);        // sums and norm tables of this unit are published
-                int total = sm.rowsum[0][row_in_tile] + sm.rowsum[1][row_in_tile] + sm.rowsum[2][row_in_tile] + sm.rowsum[3][row_in_tile];
+                int total = (int)sm.rowsum[0][row_in_tile] + (int)sm.rowsum[1][row_in_tile] + (int)sm.rowsum[2][row_in_tile] + (int)sm.rowsum[3][row_in_tile];
                 if (p.cl > 1) {      // the peer block's half of the row: same exchange as for the maxima
                     if (cq == 0) {
                         ptx::st_cluster_u32(peer_sum_s + (uint32_t)(tb * GEMM_BM + row_in_tile) * 4u, (uint32_t)total);
@@ -488,8 +486,7 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 int mn = fast_div(total, p.fd_h);
                 if (!mn) mn = 1;
                 const float rinv = c_rinv_up.v[mn & 127];        // mn <= 127: a mean of absolute values of int8
-                const uint32_t lw_s = ptx::smem_u32(&sm.ln_w[0]), lb_s = ptx::smem_u32(&sm.ln_b[0]);
-                const uint32_t ld_s = ptx::smem_u32(&sm.ln_d[0][0]);
+                const uint32_t lwb_s = ptx::smem_u32(&sm.ln_wb[0]), ld4_s = ptx::smem_u32(&sm.ln_d4[0]);
                 int8_t *hrow = p.h_out + (int64_t)r * p.H + cofs;
                 int dot0 = 0, dot1 = 0, dot2 = 0;
                 for (int j = 0; j < NT; j++) {
@@ -501,19 +498,23 @@ gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         uint32_t yw[4];
 #pragma unroll
                         for (int q4 = 0; q4 < 4; q4++) {
-                            const uint32_t xv = (uint32_t)(q4 == 0 ? xw.x : (q4 == 1 ? xw.y : (q4 == 2 ? xw.z : xw.w)));
-                            const int lc = col + 4 * q4;
-                            const int2 w2 = ptx::lds_v2(lw_s + 2u * (uint32_t)lc), b2 = ptx::lds_v2(lb_s + 2u * (uint32_t)lc);
-                            const int y0 = div_small(ptx::sx_byte0(xv) * ptx::sx_half0(w2.x), rinv) * p.one + ptx::sx_half0(b2.x);
-                            const int y1 = div_small(ptx::sx_byte1(xv) * (w2.x >> 16), rinv) * p.one + (b2.x >> 16);
-                            const int y2 = div_small(ptx::sx_byte2(xv) * ptx::sx_half0(w2.y), rinv) * p.one + ptx::sx_half0(b2.y);
-                            const int y3 = div_small(((int)xv >> 24) * (w2.y >> 16), rinv) * p.one + (b2.y >> 16);
+                            const int xv = q4 == 0 ? xw.x : (q4 == 1 ? xw.y : (q4 == 2 ? xw.z : xw.w));
+                            const uint32_t grp = (uint32_t)(col >> 2) + (uint32_t)q4;          // group of 4 columns
+                            const int4 wb = ptx::lds_v4(lwb_s + 16u * grp), d4 = ptx::lds_v4(ld4_s + 16u * grp);
+                            // x_i * w_i without widening either: a two-term dot product of the int16 pair with the word whose
+                            // other byte is masked to zero, started from the bit pattern of 1.5 * 2^23 (i2f_small's addend);
+                            // "+ b_i" the same way against a constant 1
+                            const float f0 = __int_as_float(__dp2a_lo(wb.x, xv & 0x000000FF, kMagicBits)) - kMagic;
+                            const float f1 = __int_as_float(__dp2a_lo(wb.x, xv & 0x0000FF00, kMagicBits)) - kMagic;
+                            const float f2 = __int_as_float(__dp2a_hi(wb.y, xv & 0x00FF0000, kMagicBits)) - kMagic;
+                            const float f3 = __int_as_float(__dp2a_hi(wb.y, xv & (int)0xFF000000, kMagicBits)) - kMagic;
+                            const int y0 = __dp2a_lo(wb.z, 0x00000001, __float2int_rz(f0 * rinv));
+                            const int y1 = __dp2a_lo(wb.z, 0x00000100, __float2int_rz(f1 * rinv));
+                            const int y2 = __dp2a_lo(wb.w, 0x00000001, __float2int_rz(f2 * rinv));
+                            const int y3 = __dp2a_lo(wb.w, 0x00000100, __float2int_rz(f3 * rinv));
                             yw[q4] = pack_clip8(y0, y1, y2, y3);
-                            dot0 = __dp4a((int)yw[q4], (int)ptx::lds_u32(ld_s + (uint32_t)lc), dot0);
-                            if (p.ndots > 1) {
-                                dot1 = __dp4a((int)yw[q4], (int)ptx::lds_u32(ld_s + (uint32_t)(FUSED_MAX_H + lc)), dot1);
-                                dot2 = __dp4a((int)yw[q4], (int)ptx::lds_u32(ld_s + (uint32_t)(2 * FUSED_MAX_H + lc)), dot2);
-                            }
+                            dot0 = __dp4a((int)yw[q4], d4.x, dot0);
+                            if (p.ndots > 1) { dot1 = __dp4a((int)yw[q4], d4.y, dot1); dot2 = __dp4a((int)yw[q4], d4.z, dot2); }
                         }
                         *reinterpret_cast<int4 *>(hrow + col) = make_int4((int)yw[0], (int)yw[1], (int)yw[2], (int)yw[3]);
                     }

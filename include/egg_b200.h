@@ -484,8 +484,12 @@ int egg_wave_members(egg_ctx *ctx);
  * the columns and exchanging the row maxima through the other's shared memory); other shapes take the
  * two-kernel form (int32 pre-activations + row maxima, then a requantisation kernel).  Both forms give
  * identical bytes.
- * enable = 0 forces the two-kernel form (for A/B timing and for tests that compare the two); no counterpart
- * in the reference.  egg_fused_epilogues_active tells which form this context's evaluations take.
+ * At level 2 (the default) the MLP-down projection's epilogue also runs the mean-abs norm that follows the
+ * block (apply_standard_norm, mgpu.cu:646-678: LN1 of the next layer or the final norm) and the row dots of the
+ * projections after it, so that row-wise kernel launch disappears.  enable = 1 keeps the row-owning projections
+ * without that, enable = 0 forces the two-kernel form (for A/B timing and for tests that compare the forms); no
+ * counterpart in the reference.  egg_fused_epilogues_active returns the level this context's evaluations take
+ * (0 when the configuration only allows the two-kernel form).
  */
 int egg_set_fused_epilogues(egg_ctx *ctx, int enable);
 int egg_fused_epilogues_active(egg_ctx *ctx);

@@ -14,9 +14,9 @@ SEED = 0x00C0FFEE
 
 def _losses(pkg, cfg, model, data, seed, start, pop, wave, fused, attention_tc=False):
     ctx = pkg.Context(cfg, 0, wave)
-    ctx.set_fused_epilogues(fused)
+    ctx.set_fused_epilogues(fused)          # False / True / 2: two-kernel, row-owning projections, + norm inside MLP-down
     ctx.set_attention_tensor_core(attention_tc)
-    assert ctx.fused_epilogues_active() == fused
+    assert ctx.fused_epilogues_active() == int(fused)
     ctx.upload_model(model)
     ctx.set_dataset(data)
     ctx.eval_chunk(seed, start, 0, pop)
@@ -43,6 +43,8 @@ def test_fused_eval_matches_oracle(hidden, layers, seq, pop, mask, kind):
     want = O.eval_losses(ocfg, model, data, seq, SEED + 3, 0, pop)
     got = _losses(pkg, cfg, model, data, SEED + 3, seq, pop, 0, True)
     assert (got == want).all(), (got[:8], want[:8])
+    got2 = _losses(pkg, cfg, model, data, SEED + 3, seq, pop, 0, 2)
+    assert (got2 == want).all(), ("norm inside the MLP-down epilogue", got2[:8], want[:8])
     assert (_losses(pkg, cfg, model, data, SEED + 3, seq, pop, 0, False) == want).all()
     assert (_losses(pkg, cfg, model, data, SEED + 3, seq, pop, 0, True, attention_tc=True) == want).all(), "tcgen05 attention"
 
@@ -55,8 +57,9 @@ def test_fused_eval_many_units_per_block_and_ragged_waves():
     cfg, ocfg, model, data = make_case(kw, data_len=200000, model_kind="random")
     want = O.eval_losses(ocfg, model, data, 256, SEED + 11, 0, 400)
     for wave in (0, 150):         # one wave of 400 members = 400 tiles (1200 Q/K/V units); then 150 + 150 + 100
-        got = _losses(pkg, cfg, model, data, SEED + 11, 256, 400, wave, True)
-        assert (got == want).all(), "wave %d: %d of 400 losses differ" % (wave, (got != want).sum())
+        for level in (1, 2):
+            got = _losses(pkg, cfg, model, data, SEED + 11, 256, 400, wave, level)
+            assert (got == want).all(), "wave %d level %d: %d of 400 losses differ" % (wave, level, (got != want).sum())
 
 
 def test_paired_blocks_walk_many_units():
@@ -68,8 +71,9 @@ def test_paired_blocks_walk_many_units():
     cfg, ocfg, model, data = make_case(kw, data_len=200000, model_kind="random")
     want = _losses(pkg, cfg, model, data, SEED + 5, 128, 300, 0, False)
     for wave in (0, 128):
-        got = _losses(pkg, cfg, model, data, SEED + 5, 128, 300, wave, True)
-        assert (got == want).all(), "wave %d: %d of 300 losses differ" % (wave, (got != want).sum())
+        for level in (1, 2):
+            got = _losses(pkg, cfg, model, data, SEED + 5, 128, 300, wave, level)
+            assert (got == want).all(), "wave %d level %d: %d of 300 losses differ" % (wave, level, (got != want).sum())
 
 
 def test_fused_and_two_kernel_forms_agree_at_benchmark_shapes_and_with_reference_kernels():
@@ -88,6 +92,7 @@ def test_fused_and_two_kernel_forms_agree_at_benchmark_shapes_and_with_reference
     a = _losses(pkg, cfg, model, data, SEED, 0, pop, 0, True)
     b = _losses(pkg, cfg, model, data, SEED, 0, pop, 0, False)
     assert (a == b).all()
+    assert (_losses(pkg, cfg, model, data, SEED, 0, pop, 0, 2) == a).all(), "norm inside the MLP-down epilogue"
     assert (_losses(pkg, cfg, model, data, SEED, 0, pop, 0, True, attention_tc=True) == a).all(), "tcgen05 attention"
     ref = run_ref_mgpu(tag, model, data, SEED, 0, 0, pop)
     assert_losses_match_racy_reference(tag, model, data, SEED, 0, 0, a, ref["losses"])
