@@ -609,7 +609,8 @@ def main():
     hbm_bytes = {  # algorithmic bytes per generation on this rank
         "attention": 4.0 * H * rows_per_step * L,
         # two-kernel form: 4H of int32 in, H + H out per row; fused form: the int8 stream in, the normalised row out
-        "rowwise": (2.0 if fused_active else 6.0) * H * rows_per_step * (2 * L + 2),
+        # (level 2: the norm after every MLP block runs inside the MLP-down epilogue, L + 1 launches per wave remain)
+        "rowwise": (2.0 if fused_active else 6.0) * H * rows_per_step * ((L + 1) if fused_active == 2 else (2 * L + 2)),
         "aqn": 15.0 * H * rows_per_step * L,
     }
     traffic_per_row, traffic_src = load_traffic()
