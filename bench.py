@@ -426,7 +426,7 @@ def run_c4(args, pkg, synth, torch, real_stdout, peaks):
 
 
 def run_c5slice(args, pkg, synth, torch, real_stdout, peaks):
-    members = 2048
+    members = 256 if args.small else 2048        # --small: a profiler-sized case (131 072 rows, activations still beyond L2)
     ctx0 = pkg.Context(pkg.default_config(**C2), 0, 2)
     mma = ctx0.measure_int8_peak(16384, 2048, 2048, 20)
     ctx0.close()

@@ -86,6 +86,7 @@ struct GemmParams {
     FastDiv fd_seq, fd_tiles_n, fd_third, fd_head;
     int lut_stride;              // bytes between entries of the replicated GELU table (filled by launch_gemm)
     int one;                     // 1 (filled by launch_gemm): the multiplier of additions issued as multiply-adds
+    int pow_t;                   // EPI_GELU: 2^rank1_shift when both shifts may be merged into one (0: keep two shifts)
 };
 
 template <int BN>
@@ -277,12 +278,24 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                 // as multiply-adds (the bias joins the rank-1 product, the accumulator is added with a run-time multiplier
                 // of 1): the integer pipe runs at half the rate of the multiply-add pipe and is the busy one here.
                 const int4 b4 = ptx::lds_v4(bcs + 4 * col);
-                x0 = ((xbs * an.x + b4.x) >> p.rank1_shift) * p.one + (int)vc[4 * q4];
-                x1 = ((xbs * an.y + b4.y) >> p.rank1_shift) * p.one + (int)vc[4 * q4 + 1];
-                x2 = ((xbs * an.z + b4.z) >> p.rank1_shift) * p.one + (int)vc[4 * q4 + 2];
-                x3 = ((xbs * an.w + b4.w) >> p.rank1_shift) * p.one + (int)vc[4 * q4 + 3];
-                // saturate to [-128, 127] while packing; the table entry of -128 holds the value of -127 (the reference's clip)
-                const uint32_t z = ptx::pack_sat_s8(x0 >> p.out_shift, x1 >> p.out_shift, x2 >> p.out_shift, x3 >> p.out_shift);
+                uint32_t z;
+                if (p.pow_t) {
+                    // floor((acc + floor(y / 2^t)) / 2^s) == floor((acc * 2^t + y) / 2^(s+t)): one multiply-add and one shift per
+                    // element; the launcher allows it only while acc * 2^t + y provably stays inside int32 (K <= 512 at t = 7)
+                    const int sh2 = p.rank1_shift + p.out_shift;
+                    x0 = (int)vc[4 * q4] * p.pow_t + (xbs * an.x + b4.x);
+                    x1 = (int)vc[4 * q4 + 1] * p.pow_t + (xbs * an.y + b4.y);
+                    x2 = (int)vc[4 * q4 + 2] * p.pow_t + (xbs * an.z + b4.z);
+                    x3 = (int)vc[4 * q4 + 3] * p.pow_t + (xbs * an.w + b4.w);
+                    z = ptx::pack_sat_s8(x0 >> sh2, x1 >> sh2, x2 >> sh2, x3 >> sh2);
+                } else {
+                    x0 = ((xbs * an.x + b4.x) >> p.rank1_shift) * p.one + (int)vc[4 * q4];
+                    x1 = ((xbs * an.y + b4.y) >> p.rank1_shift) * p.one + (int)vc[4 * q4 + 1];
+                    x2 = ((xbs * an.z + b4.z) >> p.rank1_shift) * p.one + (int)vc[4 * q4 + 2];
+                    x3 = ((xbs * an.w + b4.w) >> p.rank1_shift) * p.one + (int)vc[4 * q4 + 3];
+                    // saturate to [-128, 127] while packing; the table entry of -128 holds the value of -127 (the reference's clip)
+                    z = ptx::pack_sat_s8(x0 >> p.out_shift, x1 >> p.out_shift, x2 >> p.out_shift, x3 >> p.out_shift);
+                }
                 // word (idx, lane) of the replicated table: 32-bit shared address = base + idx * 128, one dot-product
                 // instruction per byte (the other three bytes meet a zero)
                 const uint32_t u0 = ptx::lds_u32(__dp4a(z, lut_stride, lut_base)), u1 = ptx::lds_u32(__dp4a(z, lut_stride << 8, lut_base));
