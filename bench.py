@@ -461,7 +461,8 @@ def main():
     ap.add_argument("--two-kernel-norm", action="store_true", help="A/B: take the two-kernel form of the adaptive normalisations (int32 pre-activations + requantisation kernels)")
     ap.add_argument("--fused-level", type=int, default=2, choices=[0, 1, 2],
                     help="A/B: 0 two-kernel adaptive norms, 1 row-owning projections, 2 (default) also the next mean-abs norm inside the MLP-down epilogue")
-    ap.add_argument("--attention-tc", action="store_true", help="A/B: take the tcgen05 form of the attention kernel")
+    ap.add_argument("--attention-tc", type=int, nargs="?", const=1, default=None, choices=[0, 1, 2],
+                    help="A/B: attention kernel: 0 mma.sync, 1 tcgen05 scores and sums, 2 mma.sync scores + tcgen05 sums (default: the library's)")
     ap.add_argument("--wave", type=int, default=0, help="members per internal wave (0: the library's default)")
     ap.add_argument("--small", action="store_true", help="profiling-sized run: 1024 members, one warm-up step, no end-to-end / CPU legs")
     args = ap.parse_args()
@@ -512,8 +513,8 @@ def main():
         cfg = pkg.default_config(population_size=pop, **C2)
     ctx = pkg.Context(cfg, local_rank, args.wave)
     ctx.set_fused_epilogues(0 if args.two_kernel_norm else args.fused_level)
-    if args.attention_tc:
-        ctx.set_attention_tensor_core(True)
+    if args.attention_tc is not None:
+        ctx.set_attention_tensor_core(args.attention_tc)
     fused_active = ctx.fused_epilogues_active()
     model = synth.random_model(cfg, 0, "ternary" if strong else "uniform")
     ctx.upload_model(model)

@@ -434,8 +434,10 @@ class Context:
         also the next mean-abs norm inside the MLP-down epilogue."""
         _check(lib().egg_set_fused_epilogues(self._h, int(level)))
 
-    def set_attention_tensor_core(self, enable):
-        _check(lib().egg_set_attention_tensor_core(self._h, 1 if enable else 0))
+    def set_attention_tensor_core(self, mode):
+        """0 / False: the mma.sync kernel; 1 / True: scores and weighted sums on tcgen05; 2: scores on mma.sync, weighted
+        sums on tcgen05 with the accumulators in tensor memory."""
+        _check(lib().egg_set_attention_tensor_core(self._h, int(mode)))
 
     def fused_epilogues_active(self):
         """The level in effect (0 when the configuration takes the two-kernel form)."""

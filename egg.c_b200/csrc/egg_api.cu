@@ -116,7 +116,7 @@ struct egg_ctx {
     // row-owning projections with the adaptive normalisations fused (default wherever the shapes allow)
     int fused_level = 2;      // 0: two-kernel adaptive norms; 1: row-owning projections; 2: + the next mean-abs norm inside MLP-down
     // attention on tcgen05 (egg_attention_tc.cu) instead of the mma.sync kernel: correct but slower as measured, off by default
-    bool attention_tc_on = false;
+    int attention_mode = 0;       // 0: mma.sync kernel; 1: tcgen05 scores and sums; 2: mma.sync scores, tcgen05 sums
     // measurement
     cudaEvent_t t0 = nullptr, t1 = nullptr;
     bool prof_on = false;
@@ -824,7 +824,8 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
         AttnParams ap; ap.members = members; ap.H = H; ap.head_dim = cf.head_dim; ap.seq_len = S; ap.shift_attn = cf.shift_attn;
         ap.q = c->d_q; ap.k = c->d_k; ap.v = c->d_v; ap.ao = c->d_ao; ap.exp_lut = c->d_exp_lut; ap.nt = c->d_nt;
         ap.nt_stride = nm.stride; ap.nt_o_b = nb + lo.o_b; ap.xbo = c->d_xbo;
-        if (c->attention_tc_on && attention_tc_supported(S, cf.head_dim)) rc = PROF(EGG_PROF_ATTENTION, launch_attention_tc(st, ap, c->d_err));
+        if (c->attention_mode == 1 && attention_tc_supported(S, cf.head_dim)) rc = PROF(EGG_PROF_ATTENTION, launch_attention_tc(st, ap, c->d_err));
+        else if (c->attention_mode == 2 && attention_tc_supported(S, cf.head_dim)) rc = PROF(EGG_PROF_ATTENTION, launch_attention_hy(st, ap, c->d_err));
         else rc = PROF(EGG_PROF_ATTENTION, launch_attention(st, ap));
         if (rc) return rc;
         if (sc && (rc = scaled_dot1(c, M, c->d_ao, 1, nb + lo.o_b, SL.w_o_row + lH, c->d_xbo, 1))) return rc;
@@ -1430,7 +1431,7 @@ extern "C" int egg_set_attention_tensor_core(egg_ctx *c, int enable) {
         set_error("tensor-core attention needs seq_len %% 128 == 0, seq_len <= 512 and head_dim 64");
         return EGG_E_INVALID;
     }
-    c->attention_tc_on = enable != 0;
+    c->attention_mode = enable < 0 ? 0 : (enable > 2 ? 2 : enable);
     return EGG_OK;
 }
 

@@ -396,7 +396,355 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const Attn
     }
 }
 
+
 bool attention_tc_supported(int seq_len, int head_dim) { return seq_len % 128 == 0 && seq_len <= 512 && head_dim == 64; }
+
+// =====================================================================================================================
+// Hybrid form: scores and weights per warp on mma.sync (as attention_kernel does), Σ wt·v on tcgen05.
+//
+// What bounds attention_kernel is not its tensor work but the 96 int32 accumulators every lane carries for Σ wt·v
+// (168 registers, 12 warps per SM, dependent MMA chains).  Here a worker warp still owns 16 queries and computes their
+// scores, maxima and three-limb weights with m16n8k32 MMAs exactly as before, but instead of multiplying the limbs with
+// V itself it writes them as int8 rows of three K-major operand tiles P_l[128 queries][128 keys] in shared memory
+// (8 bytes per row, limb and 32-key block: the key order inside a 32-key block is permuted so that the lane's eight
+// keys are adjacent; V^T is staged with the same permutation).  Warp 0 issues O_l += P_l V as tcgen05.mma kind::i8
+// (M = 128, N = 64, K = 32 per 32-key block) as soon as the eight workers have delivered a block; the accumulators live
+// in tensor memory (192 columns), so the workers run ahead with the next block while the tensor core works, need about
+// 100 registers, and two blocks of 288 threads fit on an SM.  The exact recombination and division are those of
+// attention_kernel.  One thread block per (member, head); needs seq_len % 128 == 0, head_dim 64.
+// Every wait is bounded; a timeout makes all later waits fall through.
+// =====================================================================================================================
+constexpr int AHY_WORKERS = 8;
+constexpr int AHY_THREADS = 32 * (1 + AHY_WORKERS);
+constexpr int AHY_KP = 80;              // K row pitch for the mma.sync B fragments (conflict-free)
+
+struct AhyBars {
+    uint64_t p_ready[4];                // the workers have written 32-key block sb of the current chunk (8 arrivals)
+    uint64_t p_free;                    // the MMAs that read the current chunk's operand tiles are done
+    uint64_t o_full;                    // all MMAs of a query block are done
+    uint64_t o_free;                    // the workers have read the accumulators (8 arrivals)
+    uint32_t tmem_base;
+    volatile int abort_flag;
+};
+struct AhyLayout { int vt, p, ks, lut, rsum, bars, total; };
+static AhyLayout ahy_layout(int S) {
+    AhyLayout L;
+    int o = 0;
+    L.vt = o; o += (S / 128) * 64 * 128;            // V^T operand tiles, one per 128 keys
+    L.p = o; o += 3 * 128 * 128;                    // three limb operand tiles of the current 128-key chunk
+    L.ks = o; o += S * AHY_KP;
+    L.lut = o; o += 256 * 4;
+    L.rsum = o; o += 2 * 3 * 128 * 4;               // limb sums of Σ wt per row, double-buffered over query blocks
+    L.bars = o; o += 128;
+    L.total = o + 1024;
+    return L;
+}
+
+__device__ __forceinline__ void mma_s8_sync(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_s8_sync_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+// scores of one 16-query x 32-key block: c[nt][0..3] for the four 8-key n-tiles (rows g and g+8, keys nt*8 + 2q, +1)
+__device__ __forceinline__ void ahy_scores(int (&c)[4][4], const uint32_t (&qa)[2][4], const int8_t *Ks, int kb, int g, int q) {
+#pragma unroll
+    for (int nt = 0; nt < 4; nt++) {
+        const int8_t *kp = Ks + (kb * 32 + nt * 8 + g) * AHY_KP + 4 * q;
+        mma_s8_sync_first(c[nt], qa[0][0], qa[0][1], qa[0][2], qa[0][3], *reinterpret_cast<const uint32_t *>(kp), *reinterpret_cast<const uint32_t *>(kp + 16));
+        mma_s8_sync(c[nt], qa[1][0], qa[1][1], qa[1][2], qa[1][3], *reinterpret_cast<const uint32_t *>(kp + 32), *reinterpret_cast<const uint32_t *>(kp + 48));
+    }
+}
+
+__global__ void __launch_bounds__(AHY_THREADS, 2) attention_hy_kernel(const AttnParams p, const AhyLayout L, int *err) {
+    extern __shared__ uint8_t ahy_raw[];
+    uint8_t *sm = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(ahy_raw) + 1023) & ~uintptr_t(1023));
+    AhyBars &bars = *reinterpret_cast<AhyBars *>(sm + L.bars);
+    const int8_t *Ks = reinterpret_cast<const int8_t *>(sm + L.ks);
+    uint32_t *lut3 = reinterpret_cast<uint32_t *>(sm + L.lut);
+    int32_t *rsum = reinterpret_cast<int32_t *>(sm + L.rsum);                 // [2][3][128]
+    const uint32_t vt_s = ptx::smem_u32(sm + L.vt), p_s = ptx::smem_u32(sm + L.p);
+
+    const int S = p.seq_len, H = p.H;
+    const int n_heads = H / 64;
+    const int mem = blockIdx.x / n_heads, hd = blockIdx.x % n_heads;
+    const int64_t base = (int64_t)mem * S;
+    const int col0 = hd * 64;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int NQ = S / 128;
+    const int sh = p.shift_attn;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 4; i++) ptx::mbar_init(&bars.p_ready[i], AHY_WORKERS);
+        ptx::mbar_init(&bars.p_free, 1);
+        ptx::mbar_init(&bars.o_full, 1);
+        ptx::mbar_init(&bars.o_free, AHY_WORKERS);
+        bars.abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    if (warp == 0) {
+        ptx::tmem_alloc(&bars.tmem_base, 256);
+        ptx::tmem_relinquish();
+    } else {
+        // ---- stage K (padded rows for the mma.sync fragments), V^T (tensor-core operand tiles, permuted keys), the table ----
+        const int tid = threadIdx.x - 32;                                     // 0..255
+        for (int i = tid; i < S * 4; i += 32 * AHY_WORKERS) {
+            const int row = i >> 2, ch = i & 3;
+            const int4 v = *reinterpret_cast<const int4 *>(p.k + (base + row) * H + col0 + ch * 16);
+            *reinterpret_cast<int4 *>(sm + L.ks + row * AHY_KP + ch * 16) = v;
+        }
+        // V: one item = two consecutive keys x 16 dims -> for every dim the two bytes, at the keys' permuted position
+        // (key 8nt + 2q + b of a 32-key block sits at byte 8q + 2nt + b of the block)
+        for (int i = tid; i < (S / 2) * 4; i += 32 * AHY_WORKERS) {
+            const int kp2 = i % (S / 2), dch = i / (S / 2);
+            const int key = 2 * kp2;
+            const int4 v0 = *reinterpret_cast<const int4 *>(p.v + (base + key) * H + col0 + dch * 16);
+            const int4 v1 = *reinterpret_cast<const int4 *>(p.v + (base + key + 1) * H + col0 + dch * 16);
+            const int k32 = key & 31;
+            const int pos = (key & ~31) + 8 * ((k32 & 7) >> 1) + 2 * (k32 >> 3);
+            const uint32_t tile = vt_s + (uint32_t)(pos >> 7) * 8192u;
+            const int pin = pos & 127;
+            const uint32_t *w0 = reinterpret_cast<const uint32_t *>(&v0), *w1 = reinterpret_cast<const uint32_t *>(&v1);
+#pragma unroll
+            for (int dq = 0; dq < 4; dq++) {
+                const uint32_t t0 = __byte_perm(w0[dq], w1[dq], 0x5140), t1 = __byte_perm(w0[dq], w1[dq], 0x7362);   // [a0 b0 a1 b1], [a2 b2 a3 b3]
+                const uint32_t pr[4] = {t0 & 0xFFFFu, t0 >> 16, t1 & 0xFFFFu, t1 >> 16};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int dim = dch * 16 + dq * 4 + j;
+                    const uint32_t a = sw128_addr(tile, dim, pin >> 4) + (uint32_t)(pin & 15);
+                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(a), "h"((unsigned short)pr[j]) : "memory");
+                }
+            }
+        }
+        {
+            const uint32_t w = (uint32_t)p.exp_lut[tid & 255];
+            lut3[tid & 255] = (w & 127u) | (((w >> 7) & 127u) << 8) | ((w >> 14) << 16);
+        }
+        ptx::fence_proxy_async();             // the V^T tiles are read by the tensor core
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = bars.tmem_base;
+
+    if (warp == 0) {
+        // ===================== MMA issuer =====================
+        if (ptx::elect_one()) {
+            constexpr uint32_t idesc = ptx::make_idesc_i8(128, 64);
+            uint32_t n_chunk = 0;
+            for (int qt = 0; qt < NQ && !bars.abort_flag; qt++) {
+                if (qt > 0) {        // the workers have read the previous block's accumulators
+                    atc_wait(&bars.o_free, (uint32_t)(qt - 1) & 1u, &bars.abort_flag, err, DEV_TIMEOUT_TMEM_EMPTY);
+                    ptx::tc_fence_after();
+                }
+                for (int ch = 0; ch <= qt && !bars.abort_flag; ch++, n_chunk++) {
+                    const uint64_t dv = ptx::make_smem_desc_sw128(vt_s + (uint32_t)ch * 8192u);
+                    for (int sb = 0; sb < 4 && !bars.abort_flag; sb++) {
+                        atc_wait(&bars.p_ready[sb], n_chunk & 1u, &bars.abort_flag, err, DEV_TIMEOUT_FULL);
+                        if (bars.abort_flag) break;
+                        ptx::tc_fence_after();
+#pragma unroll
+                        for (int l = 0; l < 3; l++) {
+                            const uint64_t dp = ptx::make_smem_desc_sw128(p_s + (uint32_t)l * 16384u);
+                            ptx::mma_i8(tmem_base + (uint32_t)(64 * l), dp + (uint64_t)(2 * sb), dv + (uint64_t)(2 * sb), idesc, (ch > 0 || sb > 0) ? 1u : 0u);
+                        }
+                    }
+                    if (!bars.abort_flag) ptx::mma_commit(&bars.p_free);
+                }
+                if (!bars.abort_flag) ptx::mma_commit(&bars.o_full);
+            }
+        }
+    } else {
+        // ===================== workers (8 warps) =====================
+        const int w = warp - 1;                     // 16 queries of every block: rows 16w .. 16w+15
+        const int quarter = warp & 3;               // tensor-memory lane quarter this warp may read
+        const int half = w >> 2;                    // which 32 of the 64 output dims it divides and stores
+        const int g = lane >> 2, q = lane & 3;
+        const int8_t *nbo = p.nt + (int64_t)(mem >> 1) * p.nt_stride + p.nt_o_b + col0 + half * 32;
+        const int4 nb4a = *reinterpret_cast<const int4 *>(nbo), nb4b = *reinterpret_cast<const int4 *>(nbo + 16);
+        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        uint32_t n_chunk = 0;
+
+        for (int qt = 0; qt < NQ; qt++) {
+            const int q0 = qt * 128 + 16 * w;
+            const int row0 = q0 + g, row1 = q0 + g + 8;
+            uint32_t qa[2][4];
+#pragma unroll
+            for (int ks = 0; ks < 2; ks++) {
+                const int8_t *qp0 = p.q + (base + row0) * H + col0 + 32 * ks + 4 * q;
+                const int8_t *qp1 = p.q + (base + row1) * H + col0 + 32 * ks + 4 * q;
+                qa[ks][0] = *reinterpret_cast<const uint32_t *>(qp0);
+                qa[ks][1] = *reinterpret_cast<const uint32_t *>(qp1);
+                qa[ks][2] = *reinterpret_cast<const uint32_t *>(qp0 + 16);
+                qa[ks][3] = *reinterpret_cast<const uint32_t *>(qp1 + 16);
+            }
+            const int last = (q0 + 15) / 32;          // the only key block of this warp that needs the causal mask
+
+            // ---- pass 1: row maxima over ctx <= t (mgpu.cu:795-802) ----
+            int mx0 = INT_MIN, mx1 = INT_MIN;
+            int c[4][4];
+            for (int kb = 0; kb < last; kb++) {
+                ahy_scores(c, qa, Ks, kb, g, q);
+#pragma unroll
+                for (int nt = 0; nt < 4; nt++) { mx0 = __vimax3_s32(mx0, c[nt][0], c[nt][1]); mx1 = __vimax3_s32(mx1, c[nt][2], c[nt][3]); }
+            }
+            ahy_scores(c, qa, Ks, last, g, q);
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+                const int key = last * 32 + nt * 8 + 2 * q;
+                if (key <= row0) mx0 = max(mx0, c[nt][0]);
+                if (key + 1 <= row0) mx0 = max(mx0, c[nt][1]);
+                if (key <= row1) mx1 = max(mx1, c[nt][2]);
+                if (key + 1 <= row1) mx1 = max(mx1, c[nt][3]);
+            }
+            mx0 = max(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 1)); mx0 = max(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 2));
+            mx1 = max(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 1)); mx1 = max(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 2));
+            const int mxs0 = mx0 >> sh, mxs1 = mx1 >> sh;
+
+            // ---- pass 2: weights as three limbs -> operand tiles; limb sums of Σ wt (mgpu.cu:810-824) ----
+            int tl0[3] = {0, 0, 0}, tl1[3] = {0, 0, 0};
+            const int tr0 = 16 * w + g, tr1 = tr0 + 8;                        // rows inside the 128-query operand tiles
+            for (int ch = 0; ch <= qt; ch++, n_chunk++) {
+                if (n_chunk > 0) {          // the previous chunk's MMAs still read the tiles
+                    atc_wait(&bars.p_free, (n_chunk - 1) & 1u, &bars.abort_flag, err, DEV_TIMEOUT_TMEM_FULL);
+                    __syncwarp();
+                }
+#pragma unroll 1
+                for (int sb = 0; sb < 4; sb++) {
+                    const int kb = ch * 4 + sb;
+                    uint32_t al[3][4];          // limb l: [0] row g keys of n-tiles 0,1; [1] row g+8; [2] row g n-tiles 2,3; [3] row g+8
+                    if (kb <= last) {
+                        ahy_scores(c, qa, Ks, kb, g, q);
+                        uint32_t wt[4][4];
+                        if (kb < last) {
+#pragma unroll
+                            for (int nt = 0; nt < 4; nt++) {
+                                wt[nt][0] = lut3[min(255, mxs0 - (c[nt][0] >> sh))];
+                                wt[nt][1] = lut3[min(255, mxs0 - (c[nt][1] >> sh))];
+                                wt[nt][2] = lut3[min(255, mxs1 - (c[nt][2] >> sh))];
+                                wt[nt][3] = lut3[min(255, mxs1 - (c[nt][3] >> sh))];
+                            }
+                        } else {
+#pragma unroll
+                            for (int nt = 0; nt < 4; nt++) {
+                                const int key = kb * 32 + nt * 8 + 2 * q;
+                                wt[nt][0] = (key <= row0) ? lut3[min(255u, (uint32_t)(mxs0 - (c[nt][0] >> sh)))] : 0u;
+                                wt[nt][1] = (key + 1 <= row0) ? lut3[min(255u, (uint32_t)(mxs0 - (c[nt][1] >> sh)))] : 0u;
+                                wt[nt][2] = (key <= row1) ? lut3[min(255u, (uint32_t)(mxs1 - (c[nt][2] >> sh)))] : 0u;
+                                wt[nt][3] = (key + 1 <= row1) ? lut3[min(255u, (uint32_t)(mxs1 - (c[nt][3] >> sh)))] : 0u;
+                            }
+                        }
+#pragma unroll
+                        for (int f = 0; f < 4; f++) {
+                            // 4 x 3 byte transpose of the four weights of word f (7 byte permutes)
+                            const int n0 = (f >> 1) * 2, i0 = (f & 1) * 2;
+                            const uint32_t wa = wt[n0][i0], wb = wt[n0][i0 + 1], wc = wt[n0 + 1][i0], wd = wt[n0 + 1][i0 + 1];
+                            const uint32_t t0 = __byte_perm(wa, wb, 0x5140), t1 = __byte_perm(wc, wd, 0x5140);
+                            const uint32_t t2 = __byte_perm(wa, wb, 0x7362), t3 = __byte_perm(wc, wd, 0x7362);
+                            al[0][f] = __byte_perm(t0, t1, 0x5410);
+                            al[1][f] = __byte_perm(t0, t1, 0x7632);
+                            al[2][f] = __byte_perm(t2, t3, 0x5410);
+                        }
+#pragma unroll
+                        for (int l = 0; l < 3; l++) {
+                            tl0[l] = __dp4a((int)al[l][0], 0x01010101, __dp4a((int)al[l][2], 0x01010101, tl0[l]));
+                            tl1[l] = __dp4a((int)al[l][1], 0x01010101, __dp4a((int)al[l][3], 0x01010101, tl1[l]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int l = 0; l < 3; l++)
+#pragma unroll
+                            for (int f = 0; f < 4; f++) al[l][f] = 0u;       // keys beyond this warp's queries: zero rows
+                    }
+                    // bytes 8q .. 8q+7 of the block (keys nt*8 + 2q + b at 8q + 2nt + b) of rows tr0 and tr1, one 8-byte store each
+                    const int piece = 2 * sb + (q >> 1);
+                    const uint32_t bo = (uint32_t)(q & 1) * 8u;
+#pragma unroll
+                    for (int l = 0; l < 3; l++) {
+                        const uint32_t tile = p_s + (uint32_t)l * 16384u;
+                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(sw128_addr(tile, tr0, piece) + bo), "r"(al[l][0]), "r"(al[l][2]) : "memory");
+                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(sw128_addr(tile, tr1, piece) + bo), "r"(al[l][1]), "r"(al[l][3]) : "memory");
+                    }
+                    ptx::fence_proxy_async();             // generic-proxy writes -> visible to the tensor core's reads
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&bars.p_ready[sb]);
+                }
+            }
+#pragma unroll
+            for (int l = 0; l < 3; l++) {                 // limb sums of Σ wt over the four lanes that share a row
+                tl0[l] += __shfl_xor_sync(0xFFFFFFFFu, tl0[l], 1); tl0[l] += __shfl_xor_sync(0xFFFFFFFFu, tl0[l], 2);
+                tl1[l] += __shfl_xor_sync(0xFFFFFFFFu, tl1[l], 1); tl1[l] += __shfl_xor_sync(0xFFFFFFFFu, tl1[l], 2);
+            }
+            int32_t *rs = rsum + (qt & 1) * 3 * 128;
+            if (q == 0) {
+#pragma unroll
+                for (int l = 0; l < 3; l++) { rs[l * 128 + tr0] = tl0[l]; rs[l * 128 + tr1] = tl1[l]; }
+            }
+            ptx::named_bar_sync(1, 32 * AHY_WORKERS);     // the sums of all 128 rows are in place
+
+            // ---- output: this lane's row of the block, 32 of its 64 dims ----
+            const int rowt = quarter * 32 + lane;
+            const int t = qt * 128 + rowt;
+            const int d0 = rs[rowt], d1 = rs[128 + rowt], d2 = rs[256 + rowt];
+            const uint32_t tot = (uint32_t)d0 + ((uint32_t)d1 << 7) + ((uint32_t)d2 << 14);
+            const float rden = 1.0f / (float)(tot ? tot : 1u);
+            const int e0 = tot ? d0 : 1, e1 = tot ? d1 : 0, e2 = tot ? d2 : 0;          // total_weight == 0 -> divide by 1 (mgpu.cu:818)
+            atc_wait(&bars.o_full, (uint32_t)qt & 1u, &bars.abort_flag, err, DEV_TIMEOUT_TMEM_FULL);
+            __syncwarp();
+            ptx::tc_fence_after();
+            int dot = 0;
+#pragma unroll
+            for (int rd = 0; rd < 2; rd++) {
+                uint32_t a0[16], a1[16], a2[16];
+                const uint32_t colb = (uint32_t)(half * 32 + rd * 16);
+                ptx::tmem_ld16(t_lane + colb, a0);
+                ptx::tmem_ld16(t_lane + 64u + colb, a1);
+                ptx::tmem_ld16(t_lane + 128u + colb, a2);
+                ptx::tmem_ld_wait16(a0); ptx::tmem_ld_wait16(a1); ptx::tmem_ld_wait16(a2);
+                uint32_t ow[4];
+                const int4 nb4 = rd == 0 ? nb4a : nb4b;
+#pragma unroll
+                for (int gg = 0; gg < 4; gg++) {
+                    int o[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) o[j] = atc_div((int)a0[4 * gg + j], (int)a1[4 * gg + j], (int)a2[4 * gg + j], e0, e1, e2, rden);
+                    ow[gg] = ptx::pack_sat_s8(o[0], o[1], o[2], o[3]);          // |o| <= 127: a weighted mean of int8 values
+                    const int nbw = gg == 0 ? nb4.x : (gg == 1 ? nb4.y : (gg == 2 ? nb4.z : nb4.w));
+                    dot = __dp4a((int)ow[gg], nbw, dot);
+                }
+                *reinterpret_cast<int4 *>(p.ao + (base + t) * H + col0 + half * 32 + rd * 16) = make_int4((int)ow[0], (int)ow[1], (int)ow[2], (int)ow[3]);
+            }
+            atomicAdd(&p.xbo[base + t], dot);              // the two warps of a row add their halves
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&bars.o_free);
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, 256);
+    }
+}
+
+int launch_attention_hy(cudaStream_t st, const AttnParams &p, int *err) {
+    if (!attention_tc_supported(p.seq_len, p.head_dim)) { set_error("tensor-core attention needs seq_len %% 128 == 0, seq_len <= 512, head_dim 64"); return EGG_E_INVALID; }
+    const AhyLayout L = ahy_layout(p.seq_len);
+    static int configured = 0;
+    if (L.total > configured) {
+        EGG_CUDA(cudaFuncSetAttribute(attention_hy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total));
+        configured = L.total;
+    }
+    const int blocks = p.members * (p.H / 64);
+    attention_hy_kernel<<<blocks, AHY_THREADS, L.total, st>>>(p, L, err);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
 
 int launch_attention_tc(cudaStream_t st, const AttnParams &p, int *err) {
     if (!attention_tc_supported(p.seq_len, p.head_dim)) { set_error("tensor-core attention needs seq_len %% 128 == 0, seq_len <= 512, head_dim 64"); return EGG_E_INVALID; }

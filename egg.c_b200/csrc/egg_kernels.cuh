@@ -105,6 +105,8 @@ int launch_attention(cudaStream_t st, const AttnParams &p);
 // the same attention on tcgen05 (egg_attention_tc.cu): whole 128-query blocks of one member, head_dim 64, seq_len <= 512
 bool attention_tc_supported(int seq_len, int head_dim);
 int launch_attention_tc(cudaStream_t st, const AttnParams &p, int *err);
+// scores on mma.sync per warp, Σ wt·v on tcgen05 with the accumulators in tensor memory (egg_attention_tc.cu)
+int launch_attention_hy(cudaStream_t st, const AttnParams &p, int *err);
 
 // ---- sampling -----------------------------------------------------------------
 struct GenParams {

@@ -47,6 +47,7 @@ def test_fused_eval_matches_oracle(hidden, layers, seq, pop, mask, kind):
     assert (got2 == want).all(), ("norm inside the MLP-down epilogue", got2[:8], want[:8])
     assert (_losses(pkg, cfg, model, data, SEED + 3, seq, pop, 0, False) == want).all()
     assert (_losses(pkg, cfg, model, data, SEED + 3, seq, pop, 0, True, attention_tc=True) == want).all(), "tcgen05 attention"
+    assert (_losses(pkg, cfg, model, data, SEED + 3, seq, pop, 0, True, attention_tc=2) == want).all(), "hybrid attention"
 
 
 def test_fused_eval_many_units_per_block_and_ragged_waves():
@@ -94,6 +95,7 @@ def test_fused_and_two_kernel_forms_agree_at_benchmark_shapes_and_with_reference
     assert (a == b).all()
     assert (_losses(pkg, cfg, model, data, SEED, 0, pop, 0, 2) == a).all(), "norm inside the MLP-down epilogue"
     assert (_losses(pkg, cfg, model, data, SEED, 0, pop, 0, True, attention_tc=True) == a).all(), "tcgen05 attention"
+    assert (_losses(pkg, cfg, model, data, SEED, 0, pop, 0, True, attention_tc=2) == a).all(), "hybrid attention"
     ref = run_ref_mgpu(tag, model, data, SEED, 0, 0, pop)
     assert_losses_match_racy_reference(tag, model, data, SEED, 0, 0, a, ref["losses"])
     ctx = pkg.Context(cfg, 0, 100)          # ragged waves: 100 + 100 + 56 members
