@@ -494,13 +494,16 @@ int egg_wave_members(egg_ctx *ctx);
 int egg_set_fused_epilogues(egg_ctx *ctx, int enable);
 int egg_fused_epilogues_active(egg_ctx *ctx);
 /*
- * Selects the tcgen05 form of the attention kernel (compute_attention's context loop, mgpu.cu:787-825: scores
- * and the three weight-limb products as tensor-memory MMAs, one thread block per member and head) instead of
- * the default warp-level mma.sync kernel.  Both give identical bytes.  Needs seq_len % 128 == 0, seq_len <= 512.
- * Off by default: as measured on B200 one block per SM leaves its phases (stage, score, weigh, accumulate,
- * divide) unoverlapped and it runs slower than the default kernel; kept selectable for comparison.
+ * Selects the attention kernel (compute_attention's context loop, mgpu.cu:787-825); all forms give identical
+ * bytes.  mode 0 (default): warp-level mma.sync kernel, accumulators in registers.  mode 1: scores and the three
+ * weight-limb products as tensor-memory MMAs (tcgen05), one thread block per member and head.  mode 2: scores,
+ * maxima and weights per warp on mma.sync, the weight-limb products on tcgen05 with the accumulators in tensor
+ * memory (two blocks per SM, the tensor core works on one 32-key block while the warps prepare the next).
+ * Modes 1 and 2 need seq_len % 128 == 0, seq_len <= 512, head_dim 64.  Off by default: as measured on B200 the
+ * per-pair weight arithmetic on the CUDA cores bounds all three, and the default kernel is the fastest
+ * (per 262 144 rows at seq_len 256: 0.57 ms, 1.02 ms, about 0.64 ms); kept selectable for comparison.
  */
-int egg_set_attention_tensor_core(egg_ctx *ctx, int enable);
+int egg_set_attention_tensor_core(egg_ctx *ctx, int mode);
 /*
  * Measures what the tensor-core loop of the projection GEMM sustains by itself on this GPU: the same
  * kernel (TMA loads, tcgen05.mma kind::i8, two TMEM accumulator stages) with an epilogue that drops the
