@@ -1128,28 +1128,30 @@ int launch_newton_schulz(cudaStream_t st, const MuonWs &ws, int rows, int cols) 
     sumsq_kernel<<<256, 256, 0, st>>>(ws.x, n, ws.norm2);
     scale_by_norm_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(ws.x, n, ws.norm2);
     float *x = ws.x, *y = ws.y;
-    const bool big = rows % 128 == 0 && cols % 128 == 0;       // every Muon matrix of a valid configuration
+    // 128 x 128 tiles where they fill the GPU (>= 120 tiles), else 64 x 64 tiles (four times as many blocks: a 1024 x 1024
+    // product is 64 big tiles on 148 SMs).  Both kernels feed every output's single accumulator in ascending contraction
+    // order, so the choice does not change a bit of the result.
+    const bool mult128 = rows % 128 == 0 && cols % 128 == 0;
+    const bool big_g = mult128 && (K / 128) * (K / 128) >= 120;
+    const bool big_y = mult128 && (cols / 128) * (rows / 128) >= 120;
     for (int it = 0; it < 5; it++) {
-        if (big) {
-            dim3 gg(K / 128, K / 128), gy(cols / 128, rows / 128);
-            if (use_rows) {     // G = X X^T : A(i,t)=X[i][t], B(t,j)=X[j][t] ; Y = 0.5 * G' X
-                sgemm128_kernel<true, true><<<gg, 256, 0, st>>>(x, cols, x, cols, ws.g, K, cols, 1.0f, 1);
-                sgemm128_kernel<true, false><<<gy, 256, 0, st>>>(ws.g, K, x, cols, y, cols, K, 0.5f, 0);
-            } else {            // G = X^T X : A(i,t)=X[t][i], B(t,j)=X[t][j] ; Y = 0.5 * X G'
-                sgemm128_kernel<false, false><<<gg, 256, 0, st>>>(x, cols, x, cols, ws.g, K, rows, 1.0f, 1);
-                sgemm128_kernel<true, false><<<gy, 256, 0, st>>>(x, cols, ws.g, K, y, cols, K, 0.5f, 0);
-            }
+        if (big_g) {
+            dim3 gg(K / 128, K / 128);
+            if (use_rows) sgemm128_kernel<true, true><<<gg, 256, 0, st>>>(x, cols, x, cols, ws.g, K, cols, 1.0f, 1);     // G = X X^T : A(i,t)=X[i][t], B(t,j)=X[j][t]
+            else sgemm128_kernel<false, false><<<gg, 256, 0, st>>>(x, cols, x, cols, ws.g, K, rows, 1.0f, 1);          // G = X^T X : A(i,t)=X[t][i], B(t,j)=X[t][j]
         } else {
             dim3 gg((K + 63) / 64, (K + 63) / 64);
-            if (use_rows)   // G = X X^T : A(i,t)=X[i][t], B(t,j)=X[j][t]
-                sgemm_strided_kernel<<<gg, 256, 0, st>>>(x, cols, 1, x, 1, cols, ws.g, K, K, cols, 1.0f, 1);
-            else            // G = X^T X : A(i,t)=X[t][i], B(t,j)=X[t][j]
-                sgemm_strided_kernel<<<gg, 256, 0, st>>>(x, 1, cols, x, cols, 1, ws.g, K, K, rows, 1.0f, 1);
+            if (use_rows) sgemm_strided_kernel<<<gg, 256, 0, st>>>(x, cols, 1, x, 1, cols, ws.g, K, K, cols, 1.0f, 1);
+            else sgemm_strided_kernel<<<gg, 256, 0, st>>>(x, 1, cols, x, cols, 1, ws.g, K, K, rows, 1.0f, 1);
+        }
+        if (big_y) {
+            dim3 gy(cols / 128, rows / 128);
+            if (use_rows) sgemm128_kernel<true, false><<<gy, 256, 0, st>>>(ws.g, K, x, cols, y, cols, K, 0.5f, 0);       // Y = 0.5 * G' X
+            else sgemm128_kernel<true, false><<<gy, 256, 0, st>>>(x, cols, ws.g, K, y, cols, K, 0.5f, 0);              // Y = 0.5 * X G'
+        } else {
             dim3 gy((cols + 63) / 64, (rows + 63) / 64);
-            if (use_rows)   // Y = 0.5 * B X
-                sgemm_strided_kernel<<<gy, 256, 0, st>>>(ws.g, K, 1, x, cols, 1, y, rows, cols, K, 0.5f, 0);
-            else            // Y = 0.5 * X B
-                sgemm_strided_kernel<<<gy, 256, 0, st>>>(x, cols, 1, ws.g, K, 1, y, rows, cols, K, 0.5f, 0);
+            if (use_rows) sgemm_strided_kernel<<<gy, 256, 0, st>>>(ws.g, K, 1, x, cols, 1, y, rows, cols, K, 0.5f, 0);
+            else sgemm_strided_kernel<<<gy, 256, 0, st>>>(x, cols, 1, ws.g, K, 1, y, rows, cols, K, 0.5f, 0);
         }
         float *tmp = x; x = y; y = tmp;
     }
