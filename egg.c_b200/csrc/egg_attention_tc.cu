@@ -735,10 +735,11 @@ __global__ void __launch_bounds__(AHY_THREADS, 2) attention_hy_kernel(const Attn
 int launch_attention_hy(cudaStream_t st, const AttnParams &p, int *err) {
     if (!attention_tc_supported(p.seq_len, p.head_dim)) { set_error("tensor-core attention needs seq_len %% 128 == 0, seq_len <= 512, head_dim 64"); return EGG_E_INVALID; }
     const AhyLayout L = ahy_layout(p.seq_len);
-    static int configured = 0;
-    if (L.total > configured) {
+    static int configured[EGG_MAX_DEVICES] = {};
+    const int dev = current_device_slot();
+    if (L.total > configured[dev]) {
         EGG_CUDA(cudaFuncSetAttribute(attention_hy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total));
-        configured = L.total;
+        configured[dev] = L.total;
     }
     const int blocks = p.members * (p.H / 64);
     attention_hy_kernel<<<blocks, AHY_THREADS, L.total, st>>>(p, L, err);
@@ -749,10 +750,11 @@ int launch_attention_hy(cudaStream_t st, const AttnParams &p, int *err) {
 int launch_attention_tc(cudaStream_t st, const AttnParams &p, int *err) {
     if (!attention_tc_supported(p.seq_len, p.head_dim)) { set_error("tensor-core attention needs seq_len %% 128 == 0, seq_len <= 512, head_dim 64"); return EGG_E_INVALID; }
     const AtcLayout L = atc_layout(p.seq_len);
-    static int configured = 0;
-    if (L.total > configured) {
+    static int configured[EGG_MAX_DEVICES] = {};
+    const int dev = current_device_slot();
+    if (L.total > configured[dev]) {
         EGG_CUDA(cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total));
-        configured = L.total;
+        configured[dev] = L.total;
     }
     const int blocks = p.members * (p.H / 64);
     attention_tc_kernel<<<blocks, ATC_THREADS, L.total, st>>>(p, L, err);

@@ -245,6 +245,15 @@ constexpr RinvTable make_rinv_table() {
 }
 static __constant__ RinvTable c_rinv_up = make_rinv_table();
 
+// Function attributes (dynamic shared-memory limits, cluster occupancy) belong to a device: caches of "already set" are
+// kept per device so that one process may hold contexts on several GPUs.
+constexpr int EGG_MAX_DEVICES = 64;
+inline int current_device_slot() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0) d = 0;
+    return d % EGG_MAX_DEVICES;
+}
+
 // ---------------------------------------------------------------- errors
 void set_error(const char *fmt, ...);
 

@@ -240,7 +240,6 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
     const uint32_t ost_s = ptx::smem_u32(ost) + lane * 64;
     const uint32_t ost1_s = ptx::smem_u32(ost1) + lane * 64;
     const int8_t *dt = sm.d_tab[slot] + cbase;
-    const int64_t gofs = (int64_t)rc * p.N + n0 + cbase;
     const int2 *rope = p.rope_t + (rc - mem * p.seq_len);                                // column of this token position
     constexpr bool do_rope = (EPI == EPI_QKV) && ROPE;      // Q and K column tiles; V passes through
     const long long half_ulp = 1ll << (p.rope_bit - 1);

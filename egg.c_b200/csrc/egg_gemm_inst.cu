@@ -136,7 +136,8 @@ static int launch_fused_one(cudaStream_t st, const CUtensorMap &ta, const CUtens
         attr[0].val.clusterDim.x = (unsigned)p.cl; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr; cfg.numAttrs = 1;
         // the pairs that can be resident at once (a GPC with an odd number of free SMs leaves one out): asked once
-        static int max_pairs = 0;
+        static int max_pairs_dev[EGG_MAX_DEVICES] = {};
+        int &max_pairs = max_pairs_dev[current_device_slot()];
         if (max_pairs == 0) {
             cfg.gridDim = dim3((unsigned)(num_sms / p.cl * p.cl));
             int n = 0;

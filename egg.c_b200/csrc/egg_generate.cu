@@ -236,10 +236,11 @@ __global__ void __launch_bounds__(GEN_THREADS, 1) generate_kernel(const GenParam
 }
 
 int launch_generate(cudaStream_t st, const GenParams &p) {
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[EGG_MAX_DEVICES] = {};
+    const int dev = current_device_slot();
+    if (!attr_set[dev]) {
         EGG_CUDA(cudaFuncSetAttribute(generate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(GenSmem)));
-        attr_set = true;
+        attr_set[dev] = true;
     }
     generate_kernel<<<1, GEN_THREADS, sizeof(GenSmem), st>>>(p);
     EGG_CUDA(cudaGetLastError());

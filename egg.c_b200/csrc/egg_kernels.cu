@@ -707,10 +707,11 @@ static size_t attention_smem_bytes(int S) {
 
 int launch_attention(cudaStream_t st, const AttnParams &p) {
     size_t smem = attention_smem_bytes(p.seq_len);
-    static size_t configured = 0;
-    if (smem > configured) {
+    static size_t configured[EGG_MAX_DEVICES] = {};
+    const int dev = current_device_slot();
+    if (smem > configured[dev]) {
         EGG_CUDA(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
+        configured[dev] = smem;
     }
     int blocks = p.members * (p.H / 64);
     attention_kernel<<<blocks, 128, smem, st>>>(p);
