@@ -160,9 +160,12 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
 // run and kept in registers; per row only the row itself is read, and the next row's bytes are requested before the
 // current row is worked on (mode 2), so that the warp always has a load in flight.
 constexpr int ROW_RUN = 8;
+#ifndef ROW_EMB_BLOCKS
+#define ROW_EMB_BLOCKS 2          // resident blocks asked for in embedding mode (its per-member tables are the widest)
+#endif
 
 template <int MODE, int NJ, int NDOTS>
-__global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
+__global__ void __launch_bounds__(256, MODE == 0 ? ROW_EMB_BLOCKS : 1) rowwise_kernel(const RowParams p) {
     const int run = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int r0 = run * ROW_RUN;
@@ -210,24 +213,48 @@ __global__ void __launch_bounds__(256) rowwise_kernel(const RowParams p) {
         for (int j = 0; j < NJ; j++) xw_next[j] = *reinterpret_cast<const uint32_t *>(p.x_out + (int64_t)r0 * H + (j << 7) + (lane << 2));
     }
 
-    for (int r = r0; r < r_end; r++) {
-        const int t = r - mem * p.seq_len;
+    // embedding mode: the run's tokens and their A-noise bytes are fetched up front (two dependent loads that would
+    // otherwise sit at the head of every row), and the embedding row of the next token is requested a row ahead
+    unsigned long long toks = 0, atoks = 0;          // one byte per row of the run (ROW_RUN = 8)
+    int32_t e4_next[MODE == 0 ? NJ : 1];
+    if (MODE == 0) {
+        static_assert(ROW_RUN == 8, "the run's tokens are packed into one 64-bit register");
+        const int64_t pair = (p.pop_base + mem) >> 1;
+        const int64_t pos = p.use_same_data ? (p.start_idx % (p.data_len - p.seq_len))
+                                            : ((p.start_idx + pair * p.data_stride) % (p.data_len - p.seq_len));
+        const uint8_t *tk = p.dataset + pos + (r0 - mem * p.seq_len);
+#pragma unroll
+        for (int i = 0; i < ROW_RUN; i++) {
+            const unsigned tok = (r0 + i < r_end) ? (unsigned)tk[i] : 0u;
+            toks |= (unsigned long long)tok << (8 * i);
+        }
+#pragma unroll
+        for (int i = 0; i < ROW_RUN; i++) atoks |= (unsigned long long)(uint8_t)ntp[p.nt_emb_a + (int)((toks >> (8 * i)) & 0xFF)] << (8 * i);
+#pragma unroll
+        for (int j = 0; j < NJ; j++) e4_next[j] = *reinterpret_cast<const int32_t *>(p.emb_rows + (int64_t)(toks & 0xFF) * H + (j << 7) + (lane << 2));
+    }
+
+    for (int ri = 0; ri < ROW_RUN; ri++) {
+        const int r = r0 + ri;
+        if (r >= r_end) break;
         int x[NJ][4];
         uint32_t xw_cur[MODE == 2 ? NJ : 1];
         if (MODE == 0) {
             // embedding (mgpu.cu:902-931): the token's row comes from the token-major copy of the table ([V][H], the same
             // K-major shadow the head projection multiplies with), 4 contiguous bytes per lane and chunk
-            int64_t pair = (p.pop_base + mem) >> 1;
-            int64_t pos = p.use_same_data ? (p.start_idx % (p.data_len - p.seq_len))
-                                          : ((p.start_idx + pair * p.data_stride) % (p.data_len - p.seq_len));
-            const int tok = p.dataset[pos + t];
-            const int a_tok = ntp[p.nt_emb_a + tok];
+            const int tok = (int)((toks >> (8 * ri)) & 0xFF);
+            const int a_tok = (int)(int8_t)((atoks >> (8 * ri)) & 0xFF);
             const float f_row = p.ov_emb_row ? __fdiv_rn((float)overlay_num(p.ov_emb_row[tok]), 64.0f) : 1.0f;
-            const int8_t *erow = p.emb_rows + (int64_t)tok * H;
+            int32_t e4c[NJ];
+#pragma unroll
+            for (int j = 0; j < NJ; j++) e4c[j] = e4_next[j];
+            if (ri + 1 < ROW_RUN && r + 1 < r_end) {
+#pragma unroll
+                for (int j = 0; j < NJ; j++) e4_next[j] = *reinterpret_cast<const int32_t *>(p.emb_rows + (int64_t)((toks >> (8 * (ri + 1))) & 0xFF) * H + (j << 7) + (lane << 2));
+            }
 #pragma unroll
             for (int j = 0; j < NJ; j++) {
-                const int d = (j << 7) + (lane << 2);
-                const int32_t e4 = *reinterpret_cast<const int32_t *>(erow + d);
+                const int32_t e4 = e4c[j];
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     int prod = a_tok * (int)byte_of(emb_nb[j], i);

@@ -62,3 +62,24 @@ def test_two_gpu_generation_matches_single_gpu():
         assert u == ups
         per = pop // 2
         assert lb == losses[rank * per:(rank + 1) * per].tobytes()
+
+
+def test_one_process_holds_contexts_on_two_gpus():
+    """Kernel attributes (dynamic shared-memory limits, cluster occupancy) are per device: a process that evaluates on
+    GPU 0 and then on GPU 1 must get the same losses from both, for the row-owning projections on one thread block
+    (H 256) and on pairs (H 1024), the default attention and the sampling kernel's attribute path."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    pkg = load_pkg()
+    for hidden, seq in ((256, 128), (1024, 128)):
+        kw = dict(hidden_dim=hidden, n_layers=1, seq_len=seq, population_size=8, device_mask=3)
+        cfg, ocfg, model, data = make_case(kw, data_len=40000, model_kind="random")
+        out = []
+        for dev in (0, 1):
+            ctx = pkg.Context(cfg, dev, 0)
+            ctx.upload_model(model)
+            ctx.set_dataset(data)
+            ctx.eval_chunk(SEED, seq, 0, 8)
+            out.append(ctx.read_losses(0, 8))
+            ctx.close()
+        assert (out[0] == out[1]).all(), (hidden, out)
