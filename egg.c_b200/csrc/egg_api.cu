@@ -107,6 +107,13 @@ struct egg_ctx {
     int32_t *d_votes = nullptr;         // partial vote matrices of the matrix being updated: [splits][rows*cols]
     int kp = 0;
     MuonWs muon = {nullptr, nullptr, nullptr, nullptr};
+    // Newton-Schulz of one matrix runs on a side stream while the main stream builds the next matrix's votes: two
+    // workspaces / streams take turns (a 1024-wide product is 64 tiles on 148 SMs, two at a time fill the GPU better)
+    MuonWs muon_alt = {nullptr, nullptr, nullptr, nullptr};
+    cudaStream_t side[2] = {nullptr, nullptr};
+    cudaEvent_t ev_m[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr};
+    bool side_used[2] = {false, false};
+    int muon_turn = 0;
     unsigned long long *d_updates = nullptr;
     int *d_err = nullptr;
     // grow-only scratch of the isolated entry points (projection, reconstruct, matrix update): allocated on first use,
@@ -132,8 +139,8 @@ struct egg_ctx {
 
 // Brackets one launch (or launch group) with events when profiling is on.
 struct ProfScope {
-    egg_ctx *c; int idx;
-    ProfScope(egg_ctx *ctx, int cls, int nlaunch = 1) : c(ctx), idx(-1) {
+    egg_ctx *c; int idx; cudaStream_t st;
+    ProfScope(egg_ctx *ctx, int cls, int nlaunch = 1, cudaStream_t stream = nullptr) : c(ctx), idx(-1), st(stream ? stream : ctx->stream) {
         c->launches += nlaunch;
         if (!c->prof_on) return;
         c->prof_launches[cls] += nlaunch;
@@ -146,9 +153,9 @@ struct ProfScope {
         c->prof_used += 2;
         c->prof_cls.resize(c->prof_used / 2);
         c->prof_cls[idx / 2] = cls;
-        cudaEventRecord(c->prof_ev[idx], c->stream);
+        cudaEventRecord(c->prof_ev[idx], st);
     }
-    ~ProfScope() { if (idx >= 0) cudaEventRecord(c->prof_ev[idx + 1], c->stream); }
+    ~ProfScope() { if (idx >= 0) cudaEventRecord(c->prof_ev[idx + 1], st); }
 };
 #define PROF(cls, call) [&]() { ProfScope ps_(c, cls); return (call); }()
 #define PROFN(cls, n, call) [&]() { ProfScope ps_(c, cls, n); return (call); }()
@@ -327,6 +334,13 @@ extern "C" void egg_ctx_destroy(egg_ctx *c) {
                     c->d_rowmax3, c->d_xbo, c->d_wave_loss, c->d_segs, c->d_nt, c->d_na, c->d_nb, c->d_votes, c->muon.x, c->muon.g,
                     c->muon.y, c->muon.norm2, c->d_updates, c->d_err, c->d_scales, c->d_ch_in, c->d_ch_out};
     for (void *p : ptrs) if (p) cudaFree(p);
+    void *alt[] = {c->muon_alt.x, c->muon_alt.g, c->muon_alt.y, c->muon_alt.norm2};
+    for (void *p : alt) if (p) cudaFree(p);
+    for (int b = 0; b < 2; b++) {
+        if (c->side[b]) { cudaStreamSynchronize(c->side[b]); cudaStreamDestroy(c->side[b]); }
+        if (c->ev_m[b]) cudaEventDestroy(c->ev_m[b]);
+        if (c->ev_done[b]) cudaEventDestroy(c->ev_done[b]);
+    }
     for (void *p : c->scratch) if (p) cudaFree(p);
     for (cudaEvent_t e : c->prof_ev) cudaEventDestroy(e);
     if (c->t0) cudaEventDestroy(c->t0);
@@ -412,9 +426,9 @@ extern "C" int egg_ctx_create(const egg_config *cfg, int device, int wave_member
         size_t free_b = 0, total_b = 0;
         TRYC(cudaMemGetInfo(&free_b, &total_b));
         int64_t budget = (int64_t)(free_b / 3);
-        if (budget > (24ll << 30)) budget = 24ll << 30;
+        if (budget > (48ll << 30)) budget = 48ll << 30;
         int64_t wm = budget / per_member;
-        wave_members = (int)(wm > 4096 ? 4096 : wm);
+        wave_members = (int)(wm > 8192 ? 8192 : wm);          // larger waves: fewer launch tails (about 1 % per doubling at H 512)
     }
     if (wave_members > POP) wave_members = (int)POP;
     wave_members &= ~1;
@@ -447,6 +461,13 @@ extern "C" int egg_ctx_create(const egg_config *cfg, int device, int wave_member
     if (cfg->use_muon) {
         TRY(dev_alloc(&c->muon.x, 4 * H * H)); TRY(dev_alloc(&c->muon.y, 4 * H * H)); TRY(dev_alloc(&c->muon.g, H * H));
         TRY(dev_alloc(&c->muon.norm2, 1));
+        TRY(dev_alloc(&c->muon_alt.x, 4 * H * H)); TRY(dev_alloc(&c->muon_alt.y, 4 * H * H)); TRY(dev_alloc(&c->muon_alt.g, H * H));
+        TRY(dev_alloc(&c->muon_alt.norm2, 1));
+        for (int b = 0; b < 2; b++) {
+            TRYC(cudaStreamCreateWithFlags(&c->side[b], cudaStreamNonBlocking));
+            TRYC(cudaEventCreateWithFlags(&c->ev_m[b], cudaEventDisableTiming));
+            TRYC(cudaEventCreateWithFlags(&c->ev_done[b], cudaEventDisableTiming));
+        }
     }
 #undef TRY
 #undef TRYC
@@ -1003,7 +1024,7 @@ struct MatrixUpdate {
     uint8_t *ch_in, *ch_out;
 };
 
-static int run_matrix_update(egg_ctx *c, const MatrixUpdate &u, uint32_t step_seed) {
+static int run_matrix_update(egg_ctx *c, const MatrixUpdate &u, uint32_t step_seed, bool overlap_muon = false) {
     const egg_config &cf = c->cfg;
     int rc = PROF(EGG_PROF_UPD_OPERANDS, launch_update_operands(c->stream, u.na, u.nb, u.fit, u.pairs, u.kp, u.rows_k, u.cols_n, u.off_a, u.off_b,
                                     u.seed_base, step_seed, cf.device_mask, cf.device_gaussian, u.operand_split));
@@ -1022,6 +1043,25 @@ static int run_matrix_update(egg_ctx *c, const MatrixUpdate &u, uint32_t step_se
     a.lr = u.lr; a.beta1 = cf.adam_beta1; a.beta2 = cf.adam_beta2; a.eps = cf.adam_eps; a.wd = cf.adam_weight_decay; a.mu = cf.muon_momentum;
     a.total_updates = c->d_updates; a.ch_in = u.ch_in; a.ch_out = u.ch_out;
     if (!u.muon) return PROF(EGG_PROF_UPD_APPLY, launch_adam_from_votes(c->stream, a));
+    if (overlap_muon && c->side[0] && c->muon_alt.x) {
+        // momentum on the main stream into workspace b (free once its previous matrix has been applied), then
+        // Newton-Schulz and the quantised apply of this matrix on side stream b
+        const int b = c->muon_turn++ & 1;
+        const MuonWs &ws = b ? c->muon_alt : c->muon;
+        if (c->side_used[b]) EGG_CUDA(cudaStreamWaitEvent(c->stream, c->ev_done[b], 0));
+        a.m_rowmajor = ws.x;
+        if ((rc = PROF(EGG_PROF_UPD_APPLY, launch_muon_m_from_votes(c->stream, a)))) return rc;
+        EGG_CUDA(cudaEventRecord(c->ev_m[b], c->stream));
+        EGG_CUDA(cudaStreamWaitEvent(c->side[b], c->ev_m[b], 0));
+        {
+            ProfScope ps_ns(c, EGG_PROF_MUON, 13, c->side[b]);
+            if ((rc = launch_newton_schulz(c->side[b], ws, u.rows_k, u.cols_n))) return rc;
+            if ((rc = launch_muon_apply(c->side[b], u.w_packed, u.opt, ws.x, u.rows_k, u.cols_n, u.lr * cf.muon_lr_scale, cf.adam_weight_decay, c->d_updates))) return rc;
+        }
+        EGG_CUDA(cudaEventRecord(c->ev_done[b], c->side[b]));
+        c->side_used[b] = true;
+        return EGG_OK;
+    }
     a.m_rowmajor = c->muon.x;
     if ((rc = PROF(EGG_PROF_UPD_APPLY, launch_muon_m_from_votes(c->stream, a)))) return rc;
     if ((rc = PROFN(EGG_PROF_MUON, 12, launch_newton_schulz(c->stream, c->muon, u.rows_k, u.cols_n)))) return rc;
@@ -1038,7 +1078,7 @@ static int update_matrix(egg_ctx *c, const ParamDesc &d, uint32_t step_seed, flo
     u.na = c->d_na; u.nb = c->d_nb; u.votes = c->d_votes;
     u.lr = lr * d.lr_scale; u.muon = d.muon;
     if (!d.muon && c->scales_on) { u.ch_in = c->d_ch_in; u.ch_out = c->d_ch_out; }
-    int rc = run_matrix_update(c, u, step_seed);
+    int rc = run_matrix_update(c, u, step_seed, true);
     if (rc || d.muon || !c->scales_on) return rc;
     // UPDATE_OVERLAY of the input-index and the output-index overlay (worker.cu:445-455)
     if ((rc = PROF(EGG_PROF_OVERLAY, launch_overlay_step(c->stream, c->d_scales + d.ov_in, c->d_ch_in, d.rows_k, c->ov_inc, c->ov_dec)))) return rc;
@@ -1065,6 +1105,9 @@ static int apply_update_async(egg_ctx *c, uint32_t step_seed, float lr) {
         }
         if (rc) return rc;
     }
+    // every matrix still on a side stream must be applied before its K-major shadow is rebuilt
+    for (int b = 0; b < 2; b++)
+        if (c->side_used[b]) { EGG_CUDA(cudaStreamWaitEvent(c->stream, c->ev_done[b], 0)); c->side_used[b] = false; }
     return refresh_shadows(c);
 }
 
