@@ -284,7 +284,8 @@ def c5_sample_run(pkg, synth, device, members, peaks, mma_loop_tops, steps=2, fu
             "adaptive_norms": {0: "two-kernel form", 1: "fused into the projection epilogues (row-owning kernels on pairs of thread blocks)",
                                2: "fused into the projection epilogues (row-owning kernels on pairs of thread blocks), the next mean-abs norm inside MLP-down"}[fused_active],
             "eval_member_tokens_per_s": members * S / (eval_ms / 1e3), "eval_ms": eval_ms, "update_ms": upd_ms,
-            "newton_schulz_and_apply_ms": prof.get("muon", (0.0, 0))[0] / steps,
+            # summed over the two side streams the matrices alternate on: two run at a time, so this exceeds its share of update_ms
+            "newton_schulz_and_apply_ms_summed_over_streams": prof.get("muon", (0.0, 0))[0] / steps,
             "update_gemm_ms": prof.get("update_gemm", (0.0, 0))[0] / steps,
             "update_operands_ms": prof.get("update_operands", (0.0, 0))[0] / steps,
             "projection_tops": tops, "projection_frac_of_peak": (tops / peaks["tensor"]) if tops else None,
