@@ -120,3 +120,36 @@ def test_overlays_against_oracle_other_width_and_switching_off():
     with pytest.raises(pkg.EggError):
         ctx.download_scales()
     ctx.close()
+
+
+@pytest.mark.parametrize("hidden,level", [(256, 2), (256, 1), (1024, 2)])
+def test_overlays_with_row_owning_projections_against_oracle(hidden, level):
+    """seq_len 128, so the row-owning projections (and at level 2 the norm inside MLP-down; at hidden_dim 1024 the pairs of
+    thread blocks) run under adaptive-noise overlays: scaled A vectors and bias deltas come from the noise table, the row
+    dots are recomputed with per-term truncation after the fused norm.  Two generations with updates against the oracle."""
+    pkg, O = load_pkg(), load_oracle()
+    kw = dict(hidden_dim=hidden, n_layers=2 if hidden < 1024 else 1, seq_len=128, population_size=8, device_mask=7)
+    cfg, ocfg, model0, data = make_case(kw, data_len=30000, model_kind="random_all", model_seed=5)
+    scales = deggs_initial_scales(pkg.scales_bytes(cfg), seed=7)
+    model, opt = model0.copy(), np.zeros(O.opt_bytes(ocfg), np.uint8)
+    oscales = scales.copy()
+    ctx = pkg.Context(cfg, 0, 0)
+    ctx.set_fused_epilogues(level)
+    assert ctx.fused_epilogues_active() == level
+    ctx.upload_model(model0)
+    ctx.upload_scales(scales)
+    ctx.set_dataset(data)
+    seed = 4321
+    for gen in range(2):
+        want = O.eval_losses(ocfg, model, data, 128 * gen, seed, 0, 8, scales=oscales)
+        ctx.eval_chunk(seed, 128 * gen, 0, 8)
+        got = ctx.read_losses(0, 8)
+        assert (got == want).all(), "losses of generation %d: %s vs %s" % (gen, got, want)
+        fit = O.fitness(want)
+        n_want = O.update_scaled(ocfg, model, opt, fit, seed, 0.5, oscales)
+        ctx.write_fitness(fit, 0)
+        assert ctx.apply_update(seed, 0.5) == n_want
+        assert (ctx.download_scales() == oscales).all()
+        assert (ctx.download_model() == model).all()
+        seed = pkg.next_seed(seed, gen + 1)
+    ctx.close()
