@@ -87,7 +87,8 @@ typedef struct egg_ctx egg_ctx;
 /*
  * One context per process per GPU (≙ struct GPUContext, mgpu.cu:1287-1302).
  * wave_members: how many population members are evaluated per internal wave
- * (activation scratch scales with it; 0 picks a default from free memory).
+ * (activation scratch scales with it: about 23 * hidden_dim + 40 bytes per member-token plus the pair's noise table;
+ * 0 picks a default: up to 8192 members, at most a third of the free memory and 48 GB).
  */
 int  egg_ctx_create(const egg_config *cfg, int device, int wave_members, egg_ctx **out);
 void egg_ctx_destroy(egg_ctx *ctx);
