@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the EGGROLL population-evaluation path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c4|c5slice]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c4|c5slice|c5|tok]
 
 Default workload `c2`: one "step" is one ES generation of the Int8NativeFormer benchmark configuration
 (4 layers, H=512, 8 heads, MLP 4H, seq 256, vocab 256, 40 960 antithetic members per GPU, DEVICE_MASK=3,
@@ -16,6 +16,8 @@ Other workloads (single GPU, same JSON contract, named in config.workload):
            so the line reports member-token-equivalents = pairs*2 per step second and the tensor roofline)
   c5slice  d-eggs-scale shapes (12 layers, H 1024, seq 512, ternary weights, Muon): a slice of the 262 144-member
            population is evaluated, the update runs over all 131 072 pairs
+  tok      the reference's tokenizer build at the benchmark shapes: vocabulary 8192 (--vocab), uint32 tokens, 8192 members
+           (--pop) per generation; the head takes two passes over 32 column tiles per row
   c5       the same shapes as a whole generation of a FIXED population (--pop-total, default 262 144) sharded over the N
            GPUs of the launch ("scaling": "strong"); a step takes tens of seconds at N = 1, so run it with --steps 1
 
@@ -447,6 +449,57 @@ def run_c5slice(args, pkg, synth, torch, real_stdout, peaks):
     real_stdout.write(json.dumps(line) + "\n"); real_stdout.flush()
 
 
+def run_tok(args, pkg, synth, torch, real_stdout, peaks):
+    """One ES-AdamW generation of the benchmark shapes with the tokenizer build's vocabulary (VOCAB_SIZE != 256:
+    uint32 tokens, embedding and tied head over V columns, two-pass cross-entropy)."""
+    V = args.vocab
+    pop = 1024 if args.small else (args.pop if args.pop != POP_PER_GPU else 8192)
+    kw = dict(C2); kw["vocab_size"] = V
+    cfg = pkg.default_config(population_size=pop, **kw)
+    ctx = pkg.Context(cfg, 0, args.wave)
+    ctx.set_fused_epilogues(args.fused_level)
+    ctx.upload_model(synth.random_model(cfg, 0, "uniform"))
+    data = synth.zipf_tokens(1, 1 << 22, V)
+    ctx.set_dataset(data)
+    S = cfg.seq_len
+    steps, warm = max(1, args.steps), max(1, args.warmup)
+    for i in range(warm):
+        ctx.eval_chunk(SEED0 + i, i * S, 0, pop); ctx.compute_fitness_pairs(0, pop // 2); ctx.apply_update(SEED0 + i, LR)
+    ctx.sync()
+    ctx.profile_enable(True); ctx.profile_read()
+    sampler = ClockSampler(0); sampler.start()
+    ev, up = [], []
+    for i in range(steps):
+        ctx.timer_start(); ctx.eval_chunk(SEED0 + warm + i, (warm + i) * S, 0, pop); ctx.compute_fitness_pairs(0, pop // 2); ev.append(ctx.timer_stop())
+        ctx.timer_start(); ctx.apply_update(SEED0 + warm + i, LR); up.append(ctx.timer_stop())
+    clocks = sampler.stop()
+    prof = ctx.profile_read()
+    ctx.profile_enable(False)
+    wave = ctx.wave_members()
+    ctx.close()
+    eval_ms, upd_ms = float(np.mean(ev)), float(np.mean(up))
+    gen_ms = eval_ms + upd_ms
+    kern = {k: v[0] / steps for k, v in prof.items() if v[1] > 0}
+    gemm_ms = sum(v for k, v in kern.items() if k.startswith("gemm_"))
+    ops = projection_ops_per_member_token(cfg.hidden_dim, cfg.n_layers, V) * pop * S
+    # the head's own stream: int32 logits written by the projection and read once by the cross-entropy pass
+    head_bytes = 2.0 * pop * S * V * 4
+    head_ms = kern.get("gemm_head", 0.0)
+    line = {"metric": METRIC, "value": pop * S / (gen_ms / 1e3), "unit": UNIT, "n_gpus": 1, "steps": steps, "warmup": warm,
+            "ms_per_step": gen_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8/int32", "data": "synthetic",
+            "config": {"workload": "tok: Int8NativeFormer generation with the tokenizer build's vocabulary: L=4 H=512 seq=256 vocab=%d, uint32 tokens, "
+                                   "%d members, rank-1 noise mask 3" % (V, pop), "wave_members": wave, "l2_policy": "inputs larger than L2"},
+            "e2e": None, "gpu_launches": None,
+            "roofline": {"kernel": "head projection (logits epilogue) + head_loss_kernel", "bound": "hbm", "achieved": head_bytes / (head_ms / 1e3) / 1e9 if head_ms else None,
+                         "peak": peaks["hbm"], "unit": "GB/s", "frac": (head_bytes / (head_ms / 1e3) / 1e9 / peaks["hbm"]) if head_ms else None,
+                         "traffic": None, "peak_source": peaks["hbm_source"],
+                         "algorithmic_bytes": "rows x vocab x 4 B written by the projection + the same read by the cross-entropy pass"},
+            "eval_ms": eval_ms, "update_ms": upd_ms, "head_ms": head_ms,
+            "projection_tops": ops / (gemm_ms / 1e3) / 1e12 if gemm_ms else None,
+            "kernels_ms": kern, "clocks": clocks, "cpu_baseline": None}
+    real_stdout.write(json.dumps(line) + "\n"); real_stdout.flush()
+
+
 # ----------------------------------------------------------------------------- our arm
 def main():
     ap = argparse.ArgumentParser()
@@ -454,7 +507,8 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5slice", "c5"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5slice", "c5", "tok"])
+    ap.add_argument("--vocab", type=int, default=8192, help="workload tok: vocabulary size (a multiple of 256)")
     ap.add_argument("--pop-total", type=int, default=262144, help="workload c5: the fixed population that is sharded over the GPUs")
     ap.add_argument("--pop", type=int, default=POP_PER_GPU, help="members per GPU (benchmark value: 40960)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -495,6 +549,8 @@ def main():
             return run_c3(args, pkg, synth, torch, real_stdout, peaks)
         if args.workload == "c4":
             return run_c4(args, pkg, synth, torch, real_stdout, peaks)
+        if args.workload == "tok":
+            return run_tok(args, pkg, synth, torch, real_stdout, peaks)
         return run_c5slice(args, pkg, synth, torch, real_stdout, peaks)
 
     dist = None

@@ -18,7 +18,7 @@ EGG_OK, EGG_E_INVALID, EGG_E_CUDA, EGG_E_NOMEM, EGG_E_TIMEOUT, EGG_E_NCCL, EGG_E
 EXPORTS = [
     "egg_config_defaults", "egg_config_validate", "egg_model_bytes", "egg_opt_state_bytes", "egg_ctx_create",
     "egg_ctx_destroy", "egg_last_error", "egg_sync", "egg_upload_model", "egg_download_model", "egg_upload_opt_state",
-    "egg_download_opt_state", "egg_set_dataset", "egg_eval_chunk", "egg_read_losses", "egg_compute_fitness_pairs",
+    "egg_download_opt_state", "egg_set_dataset", "egg_set_dataset_tokens", "egg_eval_chunk", "egg_read_losses", "egg_compute_fitness_pairs",
     "egg_write_fitness", "egg_read_fitness", "egg_nccl_unique_id", "egg_comm_init", "egg_allgather_fitness",
     "egg_apply_update", "egg_generation_host", "egg_perturbed_projection", "egg_update_reconstruct", "egg_update_matrix",
     "egg_update_reconstruct_noalloc", "egg_scales_bytes", "egg_upload_scales", "egg_download_scales", "egg_set_overlay_steps",
@@ -147,7 +147,7 @@ def lib():
         L.egg_last_error.restype = C.c_char_p
         L.egg_sync.argtypes = [vp]
         for f in (L.egg_upload_model, L.egg_download_model, L.egg_upload_opt_state, L.egg_download_opt_state, L.egg_set_dataset,
-                  L.egg_upload_scales, L.egg_download_scales):
+                  L.egg_set_dataset_tokens, L.egg_upload_scales, L.egg_download_scales):
             f.argtypes = [vp, vp, C.c_int64]
         L.egg_eval_chunk.argtypes = [vp, C.c_uint32, C.c_int64, C.c_int, C.c_int]
         L.egg_read_losses.argtypes = [vp, vp, C.c_int, C.c_int]
@@ -342,8 +342,13 @@ class Context:
         return t.value
 
     def set_dataset(self, tokens):
-        tokens = np.ascontiguousarray(tokens, np.uint8)
-        _check(lib().egg_set_dataset(self._h, _ptr(tokens), tokens.nbytes))
+        """Byte tokens at vocab_size 256; uint32 tokens (the reference's TokenType of its tokenizer build) otherwise."""
+        if self.cfg.vocab_size == 256:
+            tokens = np.ascontiguousarray(tokens, np.uint8)
+            _check(lib().egg_set_dataset(self._h, _ptr(tokens), len(tokens)))
+        else:
+            tokens = np.ascontiguousarray(tokens, np.uint32)
+            _check(lib().egg_set_dataset_tokens(self._h, _ptr(tokens), len(tokens)))
 
     def eval_chunk(self, step_seed, start_idx, pop_offset, count):
         _check(lib().egg_eval_chunk(self._h, step_seed & 0xFFFFFFFF, start_idx, pop_offset, count))
@@ -378,9 +383,11 @@ class Context:
         return n.value
 
     def generation_host(self, tokens, step, step_seed, lr, losses_out=None):
-        """tokens: pinned/pageable host uint8 array or None to keep the resident dataset."""
+        """tokens: pinned/pageable host array (uint8, or uint32 when vocab_size != 256) or None to keep the resident dataset."""
         n = C.c_uint64(0)
-        tp, tl = (None, 0) if tokens is None else (_ptr(tokens), tokens.nbytes)
+        if tokens is not None:
+            assert tokens.dtype == (np.uint8 if self.cfg.vocab_size == 256 else np.uint32), "token width does not match vocab_size"
+        tp, tl = (None, 0) if tokens is None else (_ptr(tokens), len(tokens))
         _check(lib().egg_generation_host(self._h, tp, tl, step, step_seed & 0xFFFFFFFF, C.c_float(lr), _ptr(losses_out), C.byref(n)))
         return n.value
 

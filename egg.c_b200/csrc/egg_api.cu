@@ -87,8 +87,10 @@ struct egg_ctx {
     int2 *d_rope_t = nullptr;           // the same (cos, sin) pairs, [head_dim/2][seq_len]: consecutive tokens are consecutive in memory
     int8_t *d_act_lut = nullptr;
     // dataset
-    uint8_t *d_data = nullptr;
-    int64_t data_len = 0, data_cap = 0;
+    uint8_t *d_data = nullptr;          // data_len tokens of tok_bytes bytes each
+    int64_t data_len = 0, data_cap = 0;  // data_cap in bytes
+    int tok_bytes = 1;                  // sizeof(TokenType), mgpu.cu:62-66: 1 at vocab_size 256, 4 otherwise
+    int32_t *d_logits = nullptr;        // [wave rows][vocab] int32 logits of the two-pass head (vocab_size != 256 only)
     // population buffers
     int32_t *d_loss = nullptr, *d_fit = nullptr;
     // wave scratch
@@ -182,7 +184,7 @@ extern "C" int egg_config_validate(const egg_config *c, const char **why) {
     else if (c->head_dim != 64) w = "head_dim must be 64";
     else if (c->n_layers < 1 || c->n_layers > 64) w = "n_layers out of range";
     else if (c->seq_len < 16 || c->seq_len % 16 || c->seq_len > 4096) w = "seq_len must be a multiple of 16 in [16,4096]";
-    else if (c->vocab_size != 256) w = "vocab_size must be 256 (byte tokens)";
+    else if (c->vocab_size < 256 || c->vocab_size > 65536 || c->vocab_size % 256) w = "vocab_size must be a multiple of 256 in [256,65536]";
     else if (c->population_size < 2 || c->population_size % 2) w = "population_size must be even";
     else if (c->device_mask < 0 || c->device_mask > 15) w = "device_mask must be in [0,15]";
     else if (c->softmax_scale_bit < 1 || c->softmax_scale_bit > 20) w = "softmax_scale_bit must be in [1,20] (three 7-bit weight limbs)";
@@ -331,7 +333,7 @@ extern "C" void egg_ctx_destroy(egg_ctx *c) {
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
     void *ptrs[] = {c->d_model, c->d_opt, c->d_shadow, c->d_exp_lut, c->d_rope_lut, c->d_rope_t, c->d_act_lut, c->d_data, c->d_loss, c->d_fit,
                     c->d_x, c->d_h, c->d_u, c->d_q, c->d_ao, c->d_pre, c->d_xb, c->d_xb2, c->d_rowmax,
-                    c->d_rowmax3, c->d_xbo, c->d_wave_loss, c->d_segs, c->d_nt, c->d_na, c->d_nb, c->d_votes, c->muon.x, c->muon.g,
+                    c->d_rowmax3, c->d_xbo, c->d_wave_loss, c->d_logits, c->d_segs, c->d_nt, c->d_na, c->d_nb, c->d_votes, c->muon.x, c->muon.g,
                     c->muon.y, c->muon.norm2, c->d_updates, c->d_err, c->d_scales, c->d_ch_in, c->d_ch_out};
     for (void *p : ptrs) if (p) cudaFree(p);
     void *alt[] = {c->muon_alt.x, c->muon_alt.g, c->muon_alt.y, c->muon_alt.norm2};
@@ -421,7 +423,10 @@ extern "C" int egg_ctx_create(const egg_config *cfg, int device, int wave_member
     TRYC(cudaMemcpy(c->d_segs, segs.data(), c->nsegs * sizeof(NoiseSeg), cudaMemcpyHostToDevice));
 
     // wave scratch: 23 H bytes + 36 bytes per row, noise table per pair
-    const int64_t per_member = S * (23 * H + 40) + c->nmap.stride / 2 + 8;
+    // (+ a row of int32 logits per token when the head takes two passes over a vocabulary wider than one tile)
+    c->tok_bytes = cfg->vocab_size == 256 ? 1 : 4;
+    const int64_t logit_bytes = cfg->vocab_size == 256 ? 0 : (int64_t)cfg->vocab_size * 4;
+    const int64_t per_member = S * (23 * H + 40 + logit_bytes) + c->nmap.stride / 2 + 8;
     if (wave_members <= 0) {
         size_t free_b = 0, total_b = 0;
         TRYC(cudaMemGetInfo(&free_b, &total_b));
@@ -444,11 +449,16 @@ extern "C" int egg_ctx_create(const egg_config *cfg, int device, int wave_member
     TRY(dev_alloc(&c->d_pre, R * 3 * H));
     TRY(dev_alloc(&c->d_xb, R * 3)); TRY(dev_alloc(&c->d_xb2, R)); TRY(dev_alloc(&c->d_rowmax, R)); TRY(dev_alloc(&c->d_rowmax3, R * 3));
     TRY(dev_alloc(&c->d_xbo, R)); TRY(dev_alloc(&c->d_wave_loss, wave_members));
+    if (logit_bytes) TRY(dev_alloc(&c->d_logits, R * cfg->vocab_size));
     TRY(dev_alloc(&c->d_nt, (int64_t)(wave_members / 2) * c->nmap.stride));
 
     // update scratch
     c->kp = (int)(((POP / 2) + 127) / 128 * 128);
-    TRY(dev_alloc(&c->d_na, 4 * H * (int64_t)c->kp)); TRY(dev_alloc(&c->d_nb, 4 * H * (int64_t)c->kp));
+    {
+        // the widest output / input dimension of any matrix: 4 H, or the vocabulary of the embedding when that is wider
+        const int64_t wide_n = 4 * H > cfg->vocab_size ? 4 * H : cfg->vocab_size;
+        TRY(dev_alloc(&c->d_na, wide_n * (int64_t)c->kp)); TRY(dev_alloc(&c->d_nb, 4 * H * (int64_t)c->kp));
+    }
     {
         int64_t vmax = 0;
         for (const ParamDesc &d : c->params) {
@@ -648,26 +658,48 @@ extern "C" int egg_set_overlay_steps(egg_ctx *c, int inc, int dec) {
     return EGG_OK;
 }
 
-static int set_dataset_async(egg_ctx *c, const uint8_t *host_tokens, int64_t n) {
+// host_tokens: n tokens of the configuration's TokenType (bytes, or uint32_t when vocab_size != 256)
+static int set_dataset_async(egg_ctx *c, const void *host_tokens, int64_t n) {
     if (n <= c->cfg.seq_len + 1) { set_error("dataset must be longer than seq_len+1"); return EGG_E_INVALID; }
-    if (n > c->data_cap) {
-        if (c->d_data) { EGG_CUDA(cudaStreamSynchronize(c->stream)); cudaFree(c->d_data); c->d_data = nullptr; }
-        int rc = dev_alloc(&c->d_data, n);
-        if (rc) return rc;
-        c->data_cap = n;
+    if (c->tok_bytes == 4) {
+        // a token outside the vocabulary would index past the embedding table (the reference reads whatever lies there)
+        const uint32_t *t = static_cast<const uint32_t *>(host_tokens);
+        const uint32_t V = (uint32_t)c->cfg.vocab_size;
+        for (int64_t i = 0; i < n; i++)
+            if (t[i] >= V) { set_error("token %u at position %lld is outside the vocabulary of %u", t[i], (long long)i, V); return EGG_E_INVALID; }
     }
-    EGG_CUDA(cudaMemcpyAsync(c->d_data, host_tokens, (size_t)n, cudaMemcpyHostToDevice, c->stream));
+    const int64_t bytes = n * c->tok_bytes;
+    if (bytes > c->data_cap) {
+        if (c->d_data) { EGG_CUDA(cudaStreamSynchronize(c->stream)); cudaFree(c->d_data); c->d_data = nullptr; }
+        int rc = dev_alloc(&c->d_data, bytes);
+        if (rc) return rc;
+        c->data_cap = bytes;
+    }
+    EGG_CUDA(cudaMemcpyAsync(c->d_data, host_tokens, (size_t)bytes, cudaMemcpyHostToDevice, c->stream));
     c->data_len = n;
     return EGG_OK;
 }
 
-extern "C" int egg_set_dataset(egg_ctx *c, const uint8_t *host_tokens, int64_t n_tokens) {
+static int set_dataset_checked(egg_ctx *c, const void *host_tokens, int64_t n_tokens, int width) {
     if (!c || !host_tokens) { set_error("null argument"); return EGG_E_INVALID; }
+    if (c->tok_bytes != width) {
+        set_error("vocab_size %d takes %s tokens: use %s", c->cfg.vocab_size, c->tok_bytes == 1 ? "byte" : "uint32_t",
+                  c->tok_bytes == 1 ? "egg_set_dataset" : "egg_set_dataset_tokens");
+        return EGG_E_INVALID;
+    }
     EGG_CUDA(cudaSetDevice(c->device));
     int rc = set_dataset_async(c, host_tokens, n_tokens);
     if (rc) return rc;
     EGG_CUDA(cudaStreamSynchronize(c->stream));
     return EGG_OK;
+}
+
+extern "C" int egg_set_dataset(egg_ctx *c, const uint8_t *host_tokens, int64_t n_tokens) {
+    return set_dataset_checked(c, host_tokens, n_tokens, 1);
+}
+
+extern "C" int egg_set_dataset_tokens(egg_ctx *c, const uint32_t *host_tokens, int64_t n_tokens) {
+    return set_dataset_checked(c, host_tokens, n_tokens, 4);
 }
 
 // ---------------------------------------------------------------- evaluation
@@ -786,7 +818,7 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
     // embedding + initial norm (mgpu.cu:902-934)
     RowParams r0 = base_row(c, M);
     r0.dataset = c->d_data; r0.data_len = c->data_len; r0.start_idx = start_idx; r0.data_stride = data_stride;
-    r0.pop_base = pop_base; r0.use_same_data = cf.use_same_data;
+    r0.pop_base = pop_base; r0.use_same_data = cf.use_same_data; r0.tok_wide = c->tok_bytes == 4;
     r0.emb_rows = sh + c->so.emb; r0.emb_bias = mdl + L.emb_bias; r0.vocab = V;
     r0.nt_emb_a = nm.emb_a; r0.nt_emb_b = nm.emb_b; r0.nt_emb_bias_d = nm.emb_bias_d; r0.emb_shift = cf.fixed_point + cf.sigma_shift;
     r0.nt_w_m = nm.ln_init.w_m; r0.nt_b_m = nm.ln_init.b_m;
@@ -881,7 +913,22 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
     gh.nt_a_off = nm.head_a; gh.xb = c->d_xb; gh.xb_stride = 3; gh.out_shift = cf.shift_logit;
     gh.dataset = c->d_data; gh.data_len = c->data_len; gh.start_idx = start_idx; gh.data_stride = data_stride; gh.pop_base = pop_base;
     gh.use_same_data = cf.use_same_data; gh.softmax_scale_bit = cf.softmax_scale_bit; gh.loss = c->d_wave_loss;
-    if ((rc = PROF(EGG_PROF_GEMM_HEAD, launch_gemm(st, EPI_HEAD, c->d_h, sh + c->so.emb, gh, c->num_sms)))) return rc;
+    if (V == 256) {
+        if ((rc = PROF(EGG_PROF_GEMM_HEAD, launch_gemm(st, EPI_HEAD, c->d_h, sh + c->so.emb, gh, c->num_sms)))) return rc;
+    } else {
+        // vocabulary wider than one tile (the reference's strided two-pass loop, mgpu.cu:969-1023): the projection runs once,
+        // leaving int32 logits and the row maxima; a row-wise pass then sums the exp table and picks the target logit
+        EGG_CUDA(cudaMemsetAsync(c->d_rowmax, 0x80, (size_t)M * 4, st));       // 0x80808080: below every logit
+        gh.out32 = c->d_logits; gh.rowstat = c->d_rowmax;
+        if ((rc = PROF(EGG_PROF_GEMM_HEAD, launch_gemm(st, EPI_LOGITS, c->d_h, sh + c->so.emb, gh, c->num_sms)))) return rc;
+        HeadLossParams hl;
+        memset(&hl, 0, sizeof(hl));
+        hl.M = M; hl.V = V; hl.seq_len = S; hl.logits = c->d_logits; hl.rowmax = c->d_rowmax; hl.exp_lut = c->d_exp_lut;
+        hl.dataset = reinterpret_cast<const uint32_t *>(c->d_data); hl.data_len = c->data_len; hl.start_idx = start_idx;
+        hl.data_stride = data_stride; hl.pop_base = pop_base; hl.use_same_data = cf.use_same_data;
+        hl.softmax_scale_bit = cf.softmax_scale_bit; hl.loss = c->d_wave_loss;
+        if ((rc = PROF(EGG_PROF_GEMM_HEAD, launch_head_loss(st, hl)))) return rc;
+    }
     EGG_CUDA(cudaMemcpyAsync(loss_dst, c->d_wave_loss, (size_t)members * 4, cudaMemcpyDeviceToDevice, st));
     return EGG_OK;
 }
@@ -940,6 +987,7 @@ extern "C" int egg_generate(egg_ctx *c, uint8_t *host_tokens, int seed_len, int 
     if (!c || !host_tokens) { set_error("null argument"); return EGG_E_INVALID; }
     if (!c->have_model) { set_error("upload a model first"); return EGG_E_STATE; }
     const egg_config &cf = c->cfg;
+    if (cf.vocab_size != 256) { set_error("sampling is built for byte tokens only (vocab_size 256)"); return EGG_E_INVALID; }
     const int total = seed_len + gen_len;
     if (seed_len < 1 || gen_len < 0 || total > cf.seq_len || total > 256) { set_error("need 1 <= seed_len and seed_len + gen_len <= min(seq_len, 256)"); return EGG_E_INVALID; }
     if (!(temp > 0.0f)) { set_error("temperature must be positive"); return EGG_E_INVALID; }
@@ -1124,7 +1172,7 @@ extern "C" int egg_apply_update(egg_ctx *c, uint32_t step_seed, float learning_r
     return check_dev_err(c);
 }
 
-extern "C" int egg_generation_host(egg_ctx *c, const uint8_t *host_tokens, int64_t n_tokens, int64_t step, uint32_t step_seed,
+extern "C" int egg_generation_host(egg_ctx *c, const void *host_tokens, int64_t n_tokens, int64_t step, uint32_t step_seed,
                                    float learning_rate, int32_t *host_losses, uint64_t *total_updates) {
     if (!c) { set_error("null context"); return EGG_E_INVALID; }
     if (!c->have_model) { set_error("upload a model first"); return EGG_E_STATE; }

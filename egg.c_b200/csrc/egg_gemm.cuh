@@ -37,6 +37,7 @@ enum GemmEpi {
     EPI_PRE32 = 2,   // pre = resid + ((acc+r1)>>s) + b + vn                    -> int32 + row abs-max
     EPI_QKV = 3,     // rope(acc + r1) for q,k ; acc + r1 for v                 -> int32 + row abs-max per q/k/v
     EPI_HEAD = 4,    // logits = (acc+r1)>>s ; integer cross-entropy            -> loss[member] +=
+    EPI_LOGITS = 5,  // logits = (acc+r1)>>s                                    -> int32 + row max (vocabularies wider than one tile)
     EPI_VOTE = 7,    // vote tile -> int32 votes in packed index order; with k_splits > 1 every split of the contraction
                      // writes its own partial vote matrix (integer sums: any split adds up exactly)
     EPI_NULL = 8,    // accumulators are dropped: the loop of TMA loads and tcgen05 MMAs alone (peak measurement)
@@ -59,7 +60,7 @@ struct GemmParams {
     // outputs
     int8_t *out8;                // [M,N]
     int32_t *out32;              // [M,N]
-    int32_t *rowstat;            // EPI_GELU: xb2[M] (+=); EPI_PRE32: rowmax[M]; EPI_QKV: rowmax[M][3]
+    int32_t *rowstat;            // EPI_GELU: xb2[M] (+=); EPI_PRE32: rowmax[M]; EPI_QKV: rowmax[M][3]; EPI_LOGITS: signed row max[M] (max=)
     const int8_t *resid;         // [M,N] int8 (EPI_PRE32)
     const int8_t *act_lut;       // 256
     const int32_t *exp_lut;      // 256
@@ -606,7 +607,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // ---- per-tile tables (evaluation epilogues): built here for a block's first tile, otherwise already
             // written at the end of the previous tile from words prefetched during its epilogue ----
             int first_pl = 0, slot = 0, sgn = 0;
-            if (EPI <= EPI_HEAD) {
+            if (EPI <= EPI_LOGITS) {
                 int last_row = min(m0 + GEMM_BM, p.M) - 1;
                 first_pl = fast_div(m0, p.fd_seq) >> 1;
                 int mem = fast_div(row_ok ? r : last_row, p.fd_seq);
@@ -626,7 +627,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             bool rok[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                if (EPI > EPI_HEAD || RPL) { rrow[i] = 0; xbs[i] = 0; slot_sgn[i] = 0; aux[i] = 0; rok[i] = false; continue; }
+                if (EPI > EPI_LOGITS || RPL) { rrow[i] = 0; xbs[i] = 0; slot_sgn[i] = 0; aux[i] = 0; rok[i] = false; continue; }
                 const int rr = m0 + quarter * 32 + i * 8 + lrow;
                 rok[i] = rr < p.M;
                 const int rc = rok[i] ? rr : (p.M - 1);
@@ -693,7 +694,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // words of the next tile's tables: in flight while this tile is computed
             TabWords nxt;
             bool have_nxt = false;
-            if (EPI <= EPI_HEAD) {
+            if (EPI <= EPI_LOGITS) {
                 const int ntile = tile + gridDim.x;
                 if (ntile < num_tiles) {
                     const int ntm = fast_div(ntile, p.fd_tiles_n), nm0 = ntm * GEMM_BM, nn0 = (ntile - ntm * tiles_n) * BN;
@@ -733,14 +734,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         ptx::tma_load_2d(sm.ostage1[ew], &tmap_r, &sm.rbar[ew], (ntile - ntm * tiles_n) * BN + cbase, ntm * GEMM_BM + quarter * 32);
                     }
                 }
-            } else if (EPI <= EPI_HEAD) {
+            } else if (EPI <= EPI_LOGITS) {
                 // ---------------- evaluation epilogues ----------------
                 // Accumulators leave TMEM one row per lane; they are transposed through shared memory so
                 // that 4 consecutive lanes own 16 consecutive columns of one row: every global access below
                 // is then a run of full 32-byte sectors, and the per-column tables are read as words.
                 int racc[4];                                        // running abs-max / dot / row max per row
 #pragma unroll
-                for (int i = 0; i < 4; i++) racc[i] = (EPI == EPI_HEAD) ? INT_MIN : 0;
+                for (int i = 0; i < 4; i++) racc[i] = (EPI == EPI_HEAD || EPI == EPI_LOGITS) ? INT_MIN : 0;
                 int rsum[4], rtgt[4];
 #pragma unroll
                 for (int i = 0; i < 4; i++) { rsum[i] = 0; rtgt[i] = 0; }
@@ -820,6 +821,11 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                 }
                                 racc[i] = max(racc[i], max(max(abs(v0), abs(v1)), max(abs(v2), abs(v3))));
                                 if (rok[i]) *reinterpret_cast<int4 *>(p.out32 + gofs) = make_int4(v0, v1, v2, v3);
+                            } else if (EPI == EPI_LOGITS) {
+                                // the head of a vocabulary wider than one tile (mgpu.cu:969-983): logits to memory, row max so far
+                                v0 >>= p.out_shift; v1 >>= p.out_shift; v2 >>= p.out_shift; v3 >>= p.out_shift;
+                                racc[i] = max(racc[i], max(max(v0, v1), max(v2, v3)));
+                                if (rok[i]) *reinterpret_cast<int4 *>(p.out32 + gofs) = make_int4(v0, v1, v2, v3);
                             } else if (EPI == EPI_HEAD) {
                                 // pass 0: row max of the logits; pass 1: Σ exp-LUT and the target logit (mgpu.cu:969-1023)
                                 const int l0 = v0 >> p.out_shift, l1 = v1 >> p.out_shift, l2 = v2 >> p.out_shift, l3 = v3 >> p.out_shift;
@@ -851,6 +857,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                             if (EPI == EPI_PRE32) atomicMax(&p.rowstat[rrow[i]], m);
                             else atomicMax(&p.rowstat[(int64_t)rrow[i] * 3 + fast_div(n0, p.fd_third)], m);
                         }
+                    } else if (EPI == EPI_LOGITS) {
+                        int m = racc[i];
+                        m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1)); m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
+                        if (pc == 0 && rok[i]) atomicMax(&p.rowstat[rrow[i]], m);
                     } else if (EPI == EPI_HEAD) {
                         int sm_ = rsum[i], tg = rtgt[i];          // the target column lives in exactly one lane: others hold 0
                         sm_ += __shfl_xor_sync(0xFFFFFFFFu, sm_, 1); sm_ += __shfl_xor_sync(0xFFFFFFFFu, sm_, 2);
@@ -896,7 +906,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 else if (EPI == EPI_PRE32) atomicMax(&p.rowstat[r], max(max(a0, a1), max(a2, a3)));
                 else if (EPI == EPI_QKV) atomicMax(&p.rowstat[(int64_t)r * 3 + fast_div(n0, p.fd_third)], max(max(a0, a1), max(a2, a3)));
             }
-            if (EPI <= EPI_HEAD && have_nxt) tab_store<BN, EPI, RPL>(p, sm, e, nxt);   // published by the next tile's barrier
+            if (EPI <= EPI_LOGITS && have_nxt) tab_store<BN, EPI, RPL>(p, sm, e, nxt);   // published by the next tile's barrier
         }
     }
 

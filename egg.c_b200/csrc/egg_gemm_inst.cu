@@ -42,6 +42,7 @@ int gemm_init() {
     if ((rc = set_attr_both<EPI_QKV, 1>())) return rc;
     if ((rc = set_attr<256, EPI_HEAD>())) return rc;
     if ((rc = set_attr<256, EPI_HEAD, 1>())) return rc;
+    if ((rc = set_attr<256, EPI_LOGITS>())) return rc;
     if ((rc = set_attr_both<EPI_VOTE>())) return rc;
     if ((rc = set_attr<256, EPI_NULL>())) return rc;
     EGG_CUDA(cudaFuncSetAttribute(gemm_fused_kernel<256, FUSED_QKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_smem_bytes<256>()));
@@ -226,10 +227,11 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
     int bn = (p.N % 256 == 0) ? 256 : 128;
     if (epi == EPI_QKV && (p.third % bn)) bn = 128;
     if (epi == EPI_QKV && (p.third % 128)) { set_error("hidden_dim must be a multiple of 128"); return EGG_E_INVALID; }
-    if (epi == EPI_HEAD && p.N != 256) { set_error("head GEMM needs vocab_size == 256"); return EGG_E_INVALID; }
-    if (epi <= EPI_HEAD) {
+    if (epi == EPI_HEAD && p.N != 256) { set_error("the one-tile head GEMM needs vocab_size == 256"); return EGG_E_INVALID; }
+    if (epi == EPI_LOGITS && p.N % 256) { set_error("the logits GEMM needs a vocabulary that is a multiple of 256"); return EGG_E_INVALID; }
+    if (epi <= EPI_LOGITS) {
         int max_slots = ((GEMM_BM - 1) / p.seq_len) / 2 + 2;
-        const bool rpl = p.seq_len % 32 == 0 && p.rpl >= 0 && epi != EPI_CLIP8;
+        const bool rpl = p.seq_len % 32 == 0 && p.rpl >= 0 && epi != EPI_CLIP8 && epi != EPI_LOGITS;
         if (max_slots > (rpl ? GEMM_RPL_SLOTS : GEMM_MAX_SLOTS)) { set_error("seq_len %d too small for the epilogue tables", p.seq_len); return EGG_E_INVALID; }
     }
     if (epi == EPI_VOTE && p.k_splits > 1) {
@@ -274,6 +276,7 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
         case EPI_HEAD:
             if (p.seq_len % 32 == 0 && p.rpl >= 0) return launch_one<256, EPI_HEAD, 1>(st, ta, tb, to, p, num_sms);
             return launch_one<256, EPI_HEAD>(st, ta, tb, to, p, num_sms);
+        case EPI_LOGITS: return launch_one<256, EPI_LOGITS>(st, ta, tb, to, p, num_sms);
         case EPI_VOTE: return launch_bn<EPI_VOTE>(st, bn, ta, tb, to, p, num_sms);
         case EPI_NULL: return launch_one<256, EPI_NULL>(st, ta, tb, to, p, num_sms);
     }

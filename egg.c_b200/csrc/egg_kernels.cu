@@ -164,7 +164,8 @@ constexpr int ROW_RUN = 8;
 #define ROW_EMB_BLOCKS 2          // resident blocks asked for in embedding mode (its per-member tables are the widest)
 #endif
 
-template <int MODE, int NJ, int NDOTS>
+// WIDE (embedding mode only): the dataset holds uint32_t tokens below 65536 (vocab_size != 256, mgpu.cu:58-66)
+template <int MODE, int NJ, int NDOTS, bool WIDE = false>
 __global__ void __launch_bounds__(256, MODE == 0 ? ROW_EMB_BLOCKS : 1) rowwise_kernel(const RowParams p) {
     const int run = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -216,22 +217,26 @@ __global__ void __launch_bounds__(256, MODE == 0 ? ROW_EMB_BLOCKS : 1) rowwise_k
     // embedding mode: the run's tokens and their A-noise bytes are fetched up front (two dependent loads that would
     // otherwise sit at the head of every row), and the embedding row of the next token is requested a row ahead
     unsigned long long toks = 0, atoks = 0;          // one byte per row of the run (ROW_RUN = 8)
+    unsigned long long toks_hi = 0;                  // WIDE: bits 8..15 of the run's tokens, packed the same way
+    auto tok_of = [&](int i) { return (int)((toks >> (8 * i)) & 0xFF) | (WIDE ? (int)((toks_hi >> (8 * i)) & 0xFF) << 8 : 0); };
     int32_t e4_next[MODE == 0 ? NJ : 1];
     if (MODE == 0) {
         static_assert(ROW_RUN == 8, "the run's tokens are packed into one 64-bit register");
         const int64_t pair = (p.pop_base + mem) >> 1;
         const int64_t pos = p.use_same_data ? (p.start_idx % (p.data_len - p.seq_len))
                                             : ((p.start_idx + pair * p.data_stride) % (p.data_len - p.seq_len));
-        const uint8_t *tk = p.dataset + pos + (r0 - mem * p.seq_len);
+        const int64_t tpos = pos + (r0 - mem * p.seq_len);
 #pragma unroll
         for (int i = 0; i < ROW_RUN; i++) {
-            const unsigned tok = (r0 + i < r_end) ? (unsigned)tk[i] : 0u;
-            toks |= (unsigned long long)tok << (8 * i);
+            unsigned tok = 0u;
+            if (r0 + i < r_end) tok = WIDE ? reinterpret_cast<const uint32_t *>(p.dataset)[tpos + i] : (unsigned)p.dataset[tpos + i];
+            toks |= (unsigned long long)(tok & 0xFF) << (8 * i);
+            if (WIDE) toks_hi |= (unsigned long long)((tok >> 8) & 0xFF) << (8 * i);
         }
 #pragma unroll
-        for (int i = 0; i < ROW_RUN; i++) atoks |= (unsigned long long)(uint8_t)ntp[p.nt_emb_a + (int)((toks >> (8 * i)) & 0xFF)] << (8 * i);
+        for (int i = 0; i < ROW_RUN; i++) atoks |= (unsigned long long)(uint8_t)ntp[p.nt_emb_a + tok_of(i)] << (8 * i);
 #pragma unroll
-        for (int j = 0; j < NJ; j++) e4_next[j] = *reinterpret_cast<const int32_t *>(p.emb_rows + (int64_t)(toks & 0xFF) * H + (j << 7) + (lane << 2));
+        for (int j = 0; j < NJ; j++) e4_next[j] = *reinterpret_cast<const int32_t *>(p.emb_rows + (int64_t)tok_of(0) * H + (j << 7) + (lane << 2));
     }
 
     for (int ri = 0; ri < ROW_RUN; ri++) {
@@ -242,7 +247,7 @@ __global__ void __launch_bounds__(256, MODE == 0 ? ROW_EMB_BLOCKS : 1) rowwise_k
         if (MODE == 0) {
             // embedding (mgpu.cu:902-931): the token's row comes from the token-major copy of the table ([V][H], the same
             // K-major shadow the head projection multiplies with), 4 contiguous bytes per lane and chunk
-            const int tok = (int)((toks >> (8 * ri)) & 0xFF);
+            const int tok = tok_of(ri);
             const int a_tok = (int)(int8_t)((atoks >> (8 * ri)) & 0xFF);
             const float f_row = p.ov_emb_row ? __fdiv_rn((float)overlay_num(p.ov_emb_row[tok]), 64.0f) : 1.0f;
             int32_t e4c[NJ];
@@ -250,7 +255,7 @@ __global__ void __launch_bounds__(256, MODE == 0 ? ROW_EMB_BLOCKS : 1) rowwise_k
             for (int j = 0; j < NJ; j++) e4c[j] = e4_next[j];
             if (ri + 1 < ROW_RUN && r + 1 < r_end) {
 #pragma unroll
-                for (int j = 0; j < NJ; j++) e4_next[j] = *reinterpret_cast<const int32_t *>(p.emb_rows + (int64_t)((toks >> (8 * (ri + 1))) & 0xFF) * H + (j << 7) + (lane << 2));
+                for (int j = 0; j < NJ; j++) e4_next[j] = *reinterpret_cast<const int32_t *>(p.emb_rows + (int64_t)tok_of(ri + 1) * H + (j << 7) + (lane << 2));
             }
 #pragma unroll
             for (int j = 0; j < NJ; j++) {
@@ -338,18 +343,18 @@ __global__ void __launch_bounds__(256, MODE == 0 ? ROW_EMB_BLOCKS : 1) rowwise_k
     }
 }
 
-template <int MODE, int NDOTS>
+template <int MODE, int NDOTS, bool WIDE = false>
 static int launch_rowwise_nj(cudaStream_t st, const RowParams &p) {
     const int blocks = ((p.M + ROW_RUN - 1) / ROW_RUN + 7) / 8;       // 8 warps per block, one run of rows per warp
     switch (p.H >> 7) {
-        case 1: rowwise_kernel<MODE, 1, NDOTS><<<blocks, 256, 0, st>>>(p); break;
-        case 2: rowwise_kernel<MODE, 2, NDOTS><<<blocks, 256, 0, st>>>(p); break;
-        case 3: rowwise_kernel<MODE, 3, NDOTS><<<blocks, 256, 0, st>>>(p); break;
-        case 4: rowwise_kernel<MODE, 4, NDOTS><<<blocks, 256, 0, st>>>(p); break;
-        case 5: rowwise_kernel<MODE, 5, NDOTS><<<blocks, 256, 0, st>>>(p); break;
-        case 6: rowwise_kernel<MODE, 6, NDOTS><<<blocks, 256, 0, st>>>(p); break;
-        case 7: rowwise_kernel<MODE, 7, NDOTS><<<blocks, 256, 0, st>>>(p); break;
-        case 8: rowwise_kernel<MODE, 8, NDOTS><<<blocks, 256, 0, st>>>(p); break;
+        case 1: rowwise_kernel<MODE, 1, NDOTS, WIDE><<<blocks, 256, 0, st>>>(p); break;
+        case 2: rowwise_kernel<MODE, 2, NDOTS, WIDE><<<blocks, 256, 0, st>>>(p); break;
+        case 3: rowwise_kernel<MODE, 3, NDOTS, WIDE><<<blocks, 256, 0, st>>>(p); break;
+        case 4: rowwise_kernel<MODE, 4, NDOTS, WIDE><<<blocks, 256, 0, st>>>(p); break;
+        case 5: rowwise_kernel<MODE, 5, NDOTS, WIDE><<<blocks, 256, 0, st>>>(p); break;
+        case 6: rowwise_kernel<MODE, 6, NDOTS, WIDE><<<blocks, 256, 0, st>>>(p); break;
+        case 7: rowwise_kernel<MODE, 7, NDOTS, WIDE><<<blocks, 256, 0, st>>>(p); break;
+        case 8: rowwise_kernel<MODE, 8, NDOTS, WIDE><<<blocks, 256, 0, st>>>(p); break;
         default: set_error("hidden_dim %d unsupported by the row-wise kernel", p.H); return EGG_E_INVALID;
     }
     EGG_CUDA(cudaGetLastError());
@@ -361,6 +366,10 @@ int launch_rowwise(cudaStream_t st, const RowParams &p_in, int mode) {
     p.fd_seq = make_fastdiv(p.seq_len);
     p.one = 1;
     if (p.ndots != 1 && p.ndots != 3) { set_error("row-wise kernel computes one or three row dots, not %d", p.ndots); return EGG_E_INVALID; }
+    if (mode == 0 && p.tok_wide) {
+        if (p.ndots != 1 || p.vocab > 65536) { set_error("wide-token embedding takes one row dot and a vocabulary of at most 65536"); return EGG_E_INVALID; }
+        return launch_rowwise_nj<0, 1, true>(st, p);
+    }
     if (p.ndots == 1) return mode == 0 ? launch_rowwise_nj<0, 1>(st, p) : (mode == 1 ? launch_rowwise_nj<1, 1>(st, p) : launch_rowwise_nj<2, 1>(st, p));
     return mode == 0 ? launch_rowwise_nj<0, 3>(st, p) : (mode == 1 ? launch_rowwise_nj<1, 3>(st, p) : launch_rowwise_nj<2, 3>(st, p));
 }
@@ -763,6 +772,48 @@ __global__ void unpack_transpose_kernel(const int32_t *packed, int8_t *shadow, i
 int launch_unpack_transpose(cudaStream_t st, const int8_t *packed, int8_t *shadow, int rows_k, int cols_n) {
     int64_t words = (int64_t)(rows_k >> 2) * cols_n;
     unpack_transpose_kernel<<<(unsigned)((words + 255) / 256), 256, 0, st>>>(reinterpret_cast<const int32_t *>(packed), shadow, rows_k, cols_n);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
+
+// =========================================================================
+// cross-entropy over stored logits: second pass of the head when the vocabulary is wider than one GEMM tile
+// (mgpu.cu:985-1023).  One warp per row: Σ exp-table[max - logit] in 64 bits, the target's logit, then
+// loss[member] += (log_sum >> 1) + max - target with log_sum = 16 * (floor(log2 Σ) - SOFTMAX_SCALE_BIT).
+// =========================================================================
+__global__ void __launch_bounds__(256) head_loss_kernel(const HeadLossParams p) {
+    __shared__ int32_t s_exp[256];
+    s_exp[threadIdx.x] = p.exp_lut[threadIdx.x];
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (r >= p.M) return;
+    const int mem = fast_div(r, p.fd_seq), t = r - mem * p.seq_len;
+    const int64_t pair = (p.pop_base + mem) >> 1;
+    const int64_t pos = p.use_same_data ? (p.start_idx % (p.data_len - p.seq_len))
+                                        : ((p.start_idx + pair * p.data_stride) % (p.data_len - p.seq_len));
+    const uint32_t target = p.dataset[pos + t + 1];
+    const int mx = p.rowmax[r];
+    const int4 *row = reinterpret_cast<const int4 *>(p.logits + (int64_t)r * p.V);
+    long long sum = 0;
+    for (int c = lane; c < (p.V >> 2); c += 32) {
+        const int4 l = __ldcs(row + c);            // read once
+        sum += (long long)s_exp[min(255, mx - l.x)] + s_exp[min(255, mx - l.y)] + s_exp[min(255, mx - l.z)] + s_exp[min(255, mx - l.w)];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+    if (lane == 0) {
+        const int tgt = target < (uint32_t)p.V ? p.logits[(int64_t)r * p.V + target] : 0;   // no column matches: s_target_logit stays 0
+        long long log_sum = 0;
+        if (sum > 0) log_sum = ((long long)(63 - __clzll(sum)) << 4) - ((long long)p.softmax_scale_bit << 4);   // shift ladder of mgpu.cu:1012-1019
+        atomicAdd(&p.loss[mem], (int)((log_sum >> 1) + mx - tgt));
+    }
+}
+int launch_head_loss(cudaStream_t st, const HeadLossParams &p_in) {
+    HeadLossParams p = p_in;
+    if (p.M <= 0 || p.V % 128 || p.V <= 0) { set_error("head loss: unsupported shape M=%d V=%d", p.M, p.V); return EGG_E_INVALID; }
+    p.fd_seq = make_fastdiv(p.seq_len);
+    head_loss_kernel<<<(p.M + 7) / 8, 256, 0, st>>>(p);
     EGG_CUDA(cudaGetLastError());
     return EGG_OK;
 }

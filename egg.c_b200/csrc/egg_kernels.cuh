@@ -52,6 +52,7 @@ struct RowParams {
     const int8_t *nt; int64_t nt_stride;
     // source: embedding (mode 0), adaptive layer normalise of pre32 (mode 1), or the finished int8 stream (mode 2)
     const uint8_t *dataset; int64_t data_len, start_idx, data_stride; int pop_base, use_same_data;
+    int tok_wide;                // 0: byte tokens; 1: dataset is a uint32_t array (vocab_size != 256), positions count tokens
     const int8_t *emb_rows;      // token-major copy of the embedding, [vocab][H] (the K-major shadow of the tied head)
     const int8_t *emb_bias; int vocab;
     int nt_emb_a, nt_emb_b, nt_emb_bias_d, emb_shift;
@@ -142,6 +143,18 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
 int gemm_init();   // resolves the driver entry point for tensor-map encoding, sets smem attributes
 
 // ---- fitness / update -------------------------------------------------------
+// Second pass of the head over int32 logits kept in memory (vocab_size != 256): see head_loss_kernel.
+struct HeadLossParams {
+    int M, V, seq_len;
+    FastDiv fd_seq;              // filled by launch_head_loss
+    const int32_t *logits;       // [M][V], after >> SHIFT_LOGIT
+    const int32_t *rowmax;       // [M] signed row maxima
+    const int32_t *exp_lut;      // 256
+    const uint32_t *dataset; int64_t data_len, start_idx, data_stride; int pop_base, use_same_data;
+    int softmax_scale_bit;
+    int32_t *loss;               // [wave members] +=
+};
+int launch_head_loss(cudaStream_t st, const HeadLossParams &p);
 int launch_fitness(cudaStream_t st, const int32_t *loss, int32_t *fit, int pairs);
 
 // operand generation for the update GEMM: NA[n][Kp] = f_p * noise(s_p+off_a, n), NB[k][Kp] = noise(s_p+off_b, k)

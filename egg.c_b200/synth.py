@@ -30,6 +30,17 @@ def zipf_bytes(seed, n, s=1.1):
     return np.minimum(np.searchsorted(cdf, u, side="right"), 255).astype(np.uint8)
 
 
+def zipf_tokens(seed, n, vocab, s=1.1):
+    """i.i.d. uint32 tokens for a vocabulary other than 256: P(rank r) ~ r^-s, token = a fixed permutation of the
+    rank (so that frequent tokens are spread over the whole index range, as a trained tokenizer's are)."""
+    p = np.arange(1, vocab + 1, dtype=np.float64) ** (-s)
+    cdf = np.cumsum(p / p.sum())
+    u = uniform01(seed, n)
+    rank = np.minimum(np.searchsorted(cdf, u, side="right"), vocab - 1)
+    perm = np.argsort(splitmix64(0x70CE75, vocab), kind="stable")
+    return perm[rank].astype(np.uint32)
+
+
 def uniform_int8(seed, n, lo=-127, hi=127):
     span = np.uint64(hi - lo + 1)
     return ((splitmix64(seed, n) % span).astype(np.int64) + lo).astype(np.int8)

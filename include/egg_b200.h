@@ -41,7 +41,7 @@ typedef struct egg_config {
     int32_t head_dim;            /* HEAD_DIM    (64)                                */
     int32_t n_layers;            /* N_LAYERS                                        */
     int32_t seq_len;             /* SEQ_LEN     (multiple of 16)                    */
-    int32_t vocab_size;          /* VOCAB_SIZE  (256: byte tokens)                  */
+    int32_t vocab_size;          /* VOCAB_SIZE  (256: byte tokens; else uint32_t)   */
     int32_t population_size;     /* POPULATION_SIZE (even)                          */
     int32_t fixed_point;         /* FIXED_POINT                                     */
     int32_t sigma_shift;         /* SIGMA_SHIFT                                     */
@@ -138,8 +138,17 @@ int egg_download_scales(egg_ctx *ctx, void *host_scales, int64_t nbytes);
 /* ADAPTIVE_NOISE_INC / ADAPTIVE_NOISE_DEC (d-eggs/include/config.h:231-236); defaults 5 and 1. */
 int egg_set_overlay_steps(egg_ctx *ctx, int inc, int dec);
 
-/* ≙ cudaMemcpy(d_dataset, ds.data, ds.length) (mgpu.cu:1466-1467). Byte tokens. */
+/* ≙ cudaMemcpy(d_dataset, ds.data, ds.length) (mgpu.cu:1466-1467). Byte tokens: vocab_size == 256 only. */
 int egg_set_dataset(egg_ctx *ctx, const uint8_t *host_tokens, int64_t n_tokens);
+/*
+ * The same for the reference's tokenizer build (VOCAB_SIZE != 256 makes TokenType uint32_t, mgpu.cu:58-66; the
+ * stream is its input.bin, mgpu.cu:1329-1339): vocab_size a multiple of 256 up to 65536, every token below
+ * vocab_size (checked here; EGG_E_INVALID otherwise).  Evaluation then embeds 32-bit tokens and takes the head in
+ * two passes over the vocabulary (row maximum, then the exp-table sum in 64 bits and the target logit,
+ * mgpu.cu:969-1023); update, fitness and the multi-GPU exchange are unchanged.  egg_generate and the d-eggs
+ * worker engine stay byte-token only.
+ */
+int egg_set_dataset_tokens(egg_ctx *ctx, const uint32_t *host_tokens, int64_t n_tokens);
 
 /* ---- evaluation -------------------------------------------------------- */
 /*
@@ -198,12 +207,13 @@ int egg_apply_update(egg_ctx *ctx, uint32_t step_seed, float learning_rate,
 
 /*
  * One whole generation through host buffers (≙ one iteration of the training
- * loop, mgpu.cu:1506-1688): uploads the dataset bytes if host_tokens != NULL,
+ * loop, mgpu.cu:1506-1688): uploads the dataset if host_tokens != NULL (n_tokens
+ * tokens: bytes at vocab_size 256, uint32_t otherwise),
  * evaluates this rank's slice of the population, computes fitness, exchanges
  * it when a communicator is attached, applies the update, copies this rank's
  * losses back.  host_losses may be NULL.
  */
-int egg_generation_host(egg_ctx *ctx, const uint8_t *host_tokens, int64_t n_tokens,
+int egg_generation_host(egg_ctx *ctx, const void *host_tokens, int64_t n_tokens,
                         int64_t step, uint32_t step_seed, float learning_rate,
                         int32_t *host_losses, uint64_t *total_updates);
 

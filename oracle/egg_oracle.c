@@ -480,6 +480,12 @@ static void attention_block(const eval_env *E, int l, int t, int8_t *x, int8_t *
     free(h); free(q8); free(ao); free(aq); free(ak); free(av);
 }
 
+/* TokenType (mgpu.cu:58-66): bytes when vocab_size == 256, uint32_t otherwise.  `dataset` points at the token
+ * array of either width; positions and data_len count tokens. */
+static inline int token_at(const egg_config *c, const uint8_t *dataset, int64_t i) {
+    return c->vocab_size == 256 ? (int)dataset[i] : (int)((const uint32_t *)dataset)[i];
+}
+
 /* One member, whole sequence (mgpu.cu:847-1029). */
 static int32_t eval_member(const eval_env *E, const uint8_t *dataset, int64_t data_len, int64_t start_idx,
                            uint32_t step_seed, int p_idx, int8_t *trace_x, int32_t *trace_logits) {
@@ -497,7 +503,7 @@ static int32_t eval_member(const eval_env *E, const uint8_t *dataset, int64_t da
     int64_t my_loss = 0;
 
     for (int t = 0; t < S; t++) {
-        int tok = dataset[stream_pos + t];
+        int tok = token_at(c, dataset, stream_pos + t);
         /* embedding, mgpu.cu:902-931 (+ d-eggs kernels.cu:134-156 factors) */
         uint32_t seed_emb = S0 + 0;
         for (int d = 0; d < H; d++) {
@@ -541,7 +547,7 @@ static int32_t eval_member(const eval_env *E, const uint8_t *dataset, int64_t da
         if (trace_logits) memcpy(trace_logits + (int64_t)t * V, lg, sizeof(int32_t) * (size_t)V);
         int64_t sum_ex = 0;
         for (int v = 0; v < V; v++) sum_ex += softmax_exp_lookup(E, lg[v] - mx);
-        int target = dataset[stream_pos + t + 1];
+        int target = token_at(c, dataset, stream_pos + t + 1);
         int64_t log_sum = 0;
         if (sum_ex > 0) {
             uint64_t xx = (uint64_t)sum_ex; int pos = 0;
@@ -551,7 +557,8 @@ static int32_t eval_member(const eval_env *E, const uint8_t *dataset, int64_t da
             if (xx >= 2) { pos += 1; }
             log_sum = (pos << 4) - (c->softmax_scale_bit << 4);
         }
-        my_loss += (log_sum >> 1) + mx - lg[target];
+        /* a target outside the vocabulary matches no column: the reference's s_target_logit stays 0 (mgpu.cu:989-1002) */
+        my_loss += (log_sum >> 1) + mx - ((target >= 0 && target < V) ? lg[target] : 0);
     }
     free(x); free(nf); free(kv); free(lg);
     return (int32_t)my_loss;

@@ -46,7 +46,9 @@ void oracle_init_model(const egg_config *cfg, int8_t *model, uint32_t seed);
 
 /* --- evaluation (mgpu.cu:847-1029; d-eggs/src/kernels.cu:90-298) ---
  * losses_out[i] is the loss of member pop_offset+i (always chunk-relative).
- * scales: AdaptiveScales bytes (d-eggs/include/model/definitions.h:92-142) or NULL. */
+ * scales: AdaptiveScales bytes (d-eggs/include/model/definitions.h:92-142) or NULL.
+ * dataset: data_len tokens of the reference's TokenType (mgpu.cu:58-66): one byte each when vocab_size == 256,
+ * uint32_t each otherwise (the pointer is then a uint32_t array passed as bytes). */
 void oracle_eval(const egg_config *cfg, const int8_t *model, const int8_t *scales,
                  const uint8_t *dataset, int64_t data_len, int64_t start_idx,
                  uint32_t step_seed, int pop_offset, int count, int32_t *losses_out);

@@ -156,6 +156,9 @@ def init_model(cfg, seed=42):
 
 
 def eval_losses(cfg, model, dataset, start_idx, step_seed, pop_offset, count, scales=None):
+    """dataset: uint8 tokens when cfg.vocab_size == 256, uint32 tokens otherwise (TokenType, mgpu.cu:58-66)."""
+    want = np.uint8 if cfg.vocab_size == 256 else np.uint32
+    assert dataset.dtype == want, "token width does not match vocab_size"
     out = np.zeros(count, np.int32)
     lib().oracle_eval(C.byref(cfg), _p(model), _p(scales), _p(dataset), len(dataset), start_idx,
                       step_seed & 0xFFFFFFFF, pop_offset, count, _p(out))

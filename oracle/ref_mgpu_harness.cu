@@ -6,7 +6,8 @@
 //
 //   ref_mgpu_<tag> <in.bin> <out.bin>
 //
-// in.bin : struct ref_case_header, TransformerModel bytes, [AdamModel bytes], dataset bytes
+// in.bin : struct ref_case_header, TransformerModel bytes, [AdamModel bytes], data_len tokens of the reference's
+//          TokenType (bytes at VOCAB_SIZE 256, uint32_t otherwise)
 // out.bin: int32 losses[count]; if do_update: int32 fitness[POP/2], uint64 total_updates,
 //          TransformerModel bytes, AdamModel bytes
 // stdout : one JSON line with the configuration and kernel timings.
@@ -20,13 +21,13 @@ struct ref_case_header {
     uint32_t magic;        // 0x46524745 "EGRF"
     uint32_t step_seed;
     int64_t start_idx;
-    int64_t data_len;
+    int64_t data_len;      // tokens
     int32_t pop_offset;
     int32_t count;
     float lr;
     int32_t do_update;     // needs pop_offset == 0 && count == POPULATION_SIZE
     int32_t has_opt;
-    int32_t reserved;
+    int32_t vocab_size;    // 0: not checked (cases written before the field had a meaning)
     int32_t cfg_check[6];  // hidden_dim, n_layers, seq_len, population_size, device_mask, use_muon
 };
 
@@ -50,12 +51,14 @@ int main(int argc, char **argv) {
         for (int i = 0; i < 6; i++)
             if (h.cfg_check[i] != want[i]) { fprintf(stderr, "ref harness: case was made for another configuration (field %d: %d vs compiled %d)\n", i, h.cfg_check[i], want[i]); return 3; }
     }
+    if (h.vocab_size != 0 && h.vocab_size != VOCAB_SIZE) { fprintf(stderr, "ref harness: case was made for vocab_size %d, compiled %d\n", h.vocab_size, VOCAB_SIZE); return 3; }
+    const size_t data_bytes = (size_t)h.data_len * sizeof(TokenType);
     TransformerModel *h_model = (TransformerModel *)calloc(1, sizeof(TransformerModel));
     AdamModel *h_opt = (AdamModel *)calloc(1, sizeof(AdamModel));
     if (fread(h_model, sizeof(TransformerModel), 1, f) != 1) die("short model");
     if (h.has_opt && fread(h_opt, sizeof(AdamModel), 1, f) != 1) die("short opt state");
-    uint8_t *h_data = (uint8_t *)malloc(h.data_len);
-    if (fread(h_data, 1, h.data_len, f) != (size_t)h.data_len) die("short dataset");
+    uint8_t *h_data = (uint8_t *)malloc(data_bytes);
+    if (fread(h_data, 1, data_bytes, f) != data_bytes) die("short dataset");
     fclose(f);
     if (h.count <= 0 || h.pop_offset < 0 || h.pop_offset + h.count > POPULATION_SIZE) die("bad population range");
     if (h.do_update && (h.pop_offset != 0 || h.count != POPULATION_SIZE)) die("update needs the whole population");
@@ -70,7 +73,7 @@ int main(int argc, char **argv) {
     TransformerModel *d_model; AdamModel *d_opt; TokenType *d_dataset; int32_t *d_loss, *d_fit; ActType *d_kv;
     CHECK_CUDA(cudaMalloc(&d_model, sizeof(TransformerModel)));
     CHECK_CUDA(cudaMalloc(&d_opt, sizeof(AdamModel)));
-    CHECK_CUDA(cudaMalloc(&d_dataset, h.data_len));
+    CHECK_CUDA(cudaMalloc(&d_dataset, data_bytes));
     CHECK_CUDA(cudaMalloc(&d_loss, POPULATION_SIZE * sizeof(int32_t)));
     CHECK_CUDA(cudaMalloc(&d_fit, (POPULATION_SIZE / 2) * sizeof(int32_t)));
     int batch_cap = h.count < POPULATION_BATCH_SIZE ? h.count : POPULATION_BATCH_SIZE;
@@ -78,7 +81,7 @@ int main(int argc, char **argv) {
     CHECK_CUDA(cudaMalloc(&d_kv, kv_size));
     CHECK_CUDA(cudaMemcpy(d_model, h_model, sizeof(TransformerModel), cudaMemcpyHostToDevice));
     CHECK_CUDA(cudaMemcpy(d_opt, h_opt, sizeof(AdamModel), cudaMemcpyHostToDevice));
-    CHECK_CUDA(cudaMemcpy(d_dataset, h_data, h.data_len, cudaMemcpyHostToDevice));
+    CHECK_CUDA(cudaMemcpy(d_dataset, h_data, data_bytes, cudaMemcpyHostToDevice));
     CHECK_CUDA(cudaMemset(d_loss, 0, POPULATION_SIZE * sizeof(int32_t)));
 
     cudaEvent_t e0, e1, e2; cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventCreate(&e2);

@@ -44,6 +44,9 @@ REF_CONFIGS = {
     "c5": dict(hidden_dim=1024, n_layers=12, seq_len=512, population_size=262144, device_mask=15),
     "muon_tiny": dict(hidden_dim=128, n_layers=1, seq_len=16, population_size=32, device_mask=15, use_muon=1),
     "muon_small": dict(hidden_dim=256, n_layers=2, seq_len=32, population_size=64, device_mask=3, use_muon=1),
+    # tokenizer variant: uint32 tokens, vocabulary other than 256 (mgpu.cu:58-66)
+    "tok_tiny": dict(hidden_dim=128, n_layers=1, seq_len=16, population_size=32, device_mask=15, vocab_size=1024),
+    "tok_small": dict(hidden_dim=256, n_layers=2, seq_len=32, population_size=64, device_mask=3, vocab_size=512),
 }
 
 
@@ -75,14 +78,15 @@ def run_ref_mgpu(tag, model, dataset, step_seed, start_idx, pop_offset, count, l
         fin, fout = os.path.join(td, "in.bin"), os.path.join(td, "out.bin")
         with open(fin, "wb") as f:
             f.write(struct.pack("<IIqqiifiii", 0x46524745, step_seed & 0xFFFFFFFF, start_idx, len(dataset), pop_offset, count,
-                                lr, 1 if do_update else 0, 1 if opt_state is not None else 0, 0))
+                                lr, 1 if do_update else 0, 1 if opt_state is not None else 0, sizes["vocab_size"]))
             kw = REF_CONFIGS[tag]
+            assert kw.get("vocab_size", 256) == sizes["vocab_size"]
             f.write(struct.pack("<6i", kw["hidden_dim"], kw["n_layers"], kw["seq_len"], kw["population_size"], kw["device_mask"],
                                 kw.get("use_muon", 0)))
             f.write(np.ascontiguousarray(model, np.int8).tobytes())
             if opt_state is not None:
                 f.write(np.ascontiguousarray(opt_state, np.uint8).tobytes())
-            f.write(np.ascontiguousarray(dataset, np.uint8).tobytes())
+            f.write(np.ascontiguousarray(dataset, np.uint8 if sizes["vocab_size"] == 256 else np.uint32).tobytes())
         r = subprocess.run([exe, fin, fout], capture_output=True, text=True, timeout=600)
         assert r.returncode == 0, r.stdout + r.stderr
         info = json.loads(r.stdout.strip().splitlines()[-1])
@@ -157,7 +161,7 @@ def deggs_initial_scales(n, seed=7):
 
 
 def make_case(kw, data_len=200000, data_seed=1, model_seed=0, model_kind="init"):
-    """Config pair, model bytes and a Zipf byte stream for a small case."""
+    """Config pair, model bytes and a Zipf token stream (bytes, or uint32 tokens when vocab_size != 256) for a small case."""
     pkg, orc = load_pkg(), load_oracle()
     cfg, ocfg = cfg_pair(**kw)
     from egg_c_b200 import synth
@@ -165,7 +169,8 @@ def make_case(kw, data_len=200000, data_seed=1, model_seed=0, model_kind="init")
         model = orc.init_model(ocfg, 42)            # the reference's own initialisation
     else:
         model = synth.random_model(cfg, model_seed, "uniform", gains_random=(model_kind == "random_all"))
-    data = synth.zipf_bytes(data_seed, data_len)
+    vocab = kw.get("vocab_size", 256)
+    data = synth.zipf_bytes(data_seed, data_len) if vocab == 256 else synth.zipf_tokens(data_seed, data_len, vocab)
     return cfg, ocfg, model, data
 
 

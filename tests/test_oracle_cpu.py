@@ -74,13 +74,45 @@ def test_library_exports_every_declared_symbol():
 def test_config_validation_messages():
     pkg = load_pkg()
     L = pkg.lib()
-    for kw in (dict(hidden_dim=100), dict(seq_len=8), dict(vocab_size=8192), dict(population_size=7), dict(head_dim=32)):
+    for kw in (dict(hidden_dim=100), dict(seq_len=8), dict(vocab_size=300), dict(vocab_size=128), dict(vocab_size=131072), dict(population_size=7), dict(head_dim=32)):
         cfg = pkg.default_config(**kw)
         why = C.c_char_p()
         assert L.egg_config_validate(C.byref(cfg), C.byref(why)) == pkg.EGG_E_INVALID
         assert why.value
     cfg = pkg.default_config()
     assert L.egg_config_validate(C.byref(cfg), None) == 0
+    for vocab in (512, 8192, 65536):          # the tokenizer build: any multiple of 256 that 16 bits can index
+        cfg = pkg.default_config(vocab_size=vocab)
+        assert L.egg_config_validate(C.byref(cfg), None) == 0
+
+
+def test_oracle_tokenizer_variant_reads_32_bit_tokens():
+    """vocab_size != 256 switches the token stream to uint32 (TokenType, mgpu.cu:58-66): the embedding table grows with
+    the vocabulary, a byte stream is refused, and stream positions count tokens rather than bytes."""
+    O = load_oracle()
+    kw = dict(hidden_dim=128, n_layers=1, seq_len=16, population_size=8, device_mask=15)
+    o256, o512 = O.make_config(**kw), O.make_config(vocab_size=512, **kw)
+    assert O.model_bytes(o512) - O.model_bytes(o256) == 256 * 128
+    m512 = O.init_model(o512, 42)
+    data = (np.arange(4000, dtype=np.uint32) * 2654435761 >> 7) % 512
+    a = O.eval_losses(o512, m512, data.astype(np.uint32), 0, 11, 0, 8)
+    b = O.eval_losses(o512, m512, data.astype(np.uint32), 0, 11, 0, 8)
+    assert (a == b).all() and (a > 0).all()
+    with pytest.raises(AssertionError):
+        O.eval_losses(o512, m512, data.astype(np.uint8), 0, 11, 0, 8)
+    # positions count tokens, not bytes: shifting the start by one token shifts by four bytes of the stream
+    c = O.eval_losses(o512, m512, data[1:].astype(np.uint32), 0, 11, 0, 8)
+    d = O.eval_losses(dict_same_data(O, o512), m512, data.astype(np.uint32), 1, 11, 0, 8)
+    e = O.eval_losses(dict_same_data(O, o512), m512, data[1:].astype(np.uint32), 0, 11, 0, 8)
+    assert (d == e).all() and c.shape == d.shape
+
+
+def dict_same_data(O, cfg):
+    """A copy of the oracle configuration with USE_SAME_DATA = 1 (every pair reads the same window)."""
+    import copy
+    c2 = copy.copy(cfg)
+    c2.use_same_data = 1
+    return c2
 
 
 def test_no_gpu_fails_loudly():
