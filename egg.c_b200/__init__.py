@@ -44,7 +44,7 @@ class EggConfig(C.Structure):
         "chunk_relative_loss")] + [
         ("softmax_exp_scale", C.c_double), ("adam_beta1", C.c_float), ("adam_beta2", C.c_float),
         ("adam_eps", C.c_float), ("adam_weight_decay", C.c_float), ("muon_momentum", C.c_float),
-        ("muon_lr_scale", C.c_float)]
+        ("muon_lr_scale", C.c_float), ("ntt_mode", C.c_int32)]
 
 
 class GruConfig(C.Structure):

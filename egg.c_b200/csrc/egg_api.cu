@@ -62,7 +62,7 @@ static int nccl_load() {
 
 using namespace egg;
 
-struct ShadowOff { int64_t init_up, init_dn, emb, layer0, layer_stride, qkv, o, up, dn; };
+struct ShadowOff { int64_t init_up, init_dn, emb, ntt, layer0, layer_stride, qkv, o, up, dn; };
 
 struct egg_ctx {
     egg_config cfg;
@@ -91,6 +91,7 @@ struct egg_ctx {
     int64_t data_len = 0, data_cap = 0;  // data_cap in bytes
     int tok_bytes = 1;                  // sizeof(TokenType), mgpu.cu:62-66: 1 at vocab_size 256, 4 otherwise
     int32_t *d_logits = nullptr;        // [wave rows][vocab] int32 logits of the two-pass head (vocab_size != 256 only)
+    int32_t *d_coef = nullptr;          // [wave pairs][seq_len] transformed-window coefficients (ntt_mode != 0 only)
     // population buffers
     int32_t *d_loss = nullptr, *d_fit = nullptr;
     // wave scratch
@@ -190,6 +191,10 @@ extern "C" int egg_config_validate(const egg_config *c, const char **why) {
     else if (c->softmax_scale_bit < 1 || c->softmax_scale_bit > 20) w = "softmax_scale_bit must be in [1,20] (three 7-bit weight limbs)";
     else if (c->rope_scale_bit < 1 || c->rope_scale_bit > 30) w = "rope_scale_bit out of range";
     else if (c->fixed_point < 0 || c->fixed_point > 7) w = "fixed_point out of range";
+    else if (c->ntt_mode < 0 || c->ntt_mode > 3) w = "ntt_mode must be 0, 1, 2 or 3";
+    else if (c->ntt_mode && ((c->seq_len & (c->seq_len - 1)) || c->seq_len > c->hidden_dim))
+        w = "ntt_mode needs a power-of-two seq_len no larger than hidden_dim (the reference transforms the window with one thread per hidden unit)";
+    else if (c->ntt_mode == 2 && c->seq_len > 256) w = "ntt_mode 2 (Fermat-257) needs seq_len <= 256";
     else if (c->sigma_shift_vector < 0 || c->sigma_shift_vector > 16 || c->sigma_shift < 0 || c->sigma_shift > 16) w = "sigma shifts out of range";
     if (!w) {
         // the mean-abs norm divides x * (gain + noise delta) exactly only below 2^16 in magnitude
@@ -208,7 +213,7 @@ static void build_params(const egg_config &c, const ModelLayout &L, const Shadow
     // optimiser-state offsets follow the field order of AdamModel (mgpu.cu:337-370)
     const int64_t H = c.hidden_dim, V = c.vocab_size, NL = c.n_layers;
     struct F { int64_t off, n; int hidden; };
-    F fields[] = {{L.embedding, V * H, 0}, {L.emb_bias, H, 0}, {L.ln_init, H, 0}, {L.ln_init_bias, H, 0},
+    F fields[] = {{L.embedding, V * H, 0}, {L.emb_bias, H, 0}, {L.ntt_emb, c.ntt_mode ? 3 * V * H : 0, 0}, {L.ln_init, H, 0}, {L.ln_init_bias, H, 0},
                   {L.w_emb_mlp_up, 4 * H * H, 1}, {L.mlp_emb_bias_up, 4 * H, 0}, {L.w_emb_mlp_down, 4 * H * H, 1},
                   {L.mlp_emb_bias_down, H, 0}, {L.ln_1, NL * H, 0}, {L.ln_1_bias, NL * H, 0}, {L.w_q, NL * H * H, 1},
                   {L.w_k, NL * H * H, 1}, {L.w_v, NL * H * H, 1}, {L.w_o, NL * H * H, 1}, {L.ln_2, NL * H, 0},
@@ -231,9 +236,9 @@ static void build_params(const egg_config &c, const ModelLayout &L, const Shadow
     const ScalesLayout S = scales_layout(c);
     // ov_in / ov_out: overlays over the input index k ("_row") and the output index n ("_col") as the worker passes
     // them (worker.cu:465-517); for the embedding these are embedding_col / embedding_row (worker.cu:499-519)
-    auto mat = [&](int64_t off, int rows, int cols, int a, int b, int base, int hidden, int64_t shadow, int64_t ov_in, int64_t ov_out) {
+    auto mat = [&](int64_t off, int rows, int cols, int a, int b, int base, int hidden, int64_t shadow, int64_t ov_in, int64_t ov_out, float sc = 1.0f) {
         ParamDesc d; d.model_off = off; d.opt_off = opt_of(off, nullptr); d.rows_k = rows; d.cols_n = cols; d.off_a = a; d.off_b = b;
-        d.seed_base = base; d.lr_scale = 1.0f; d.muon = hidden && c.use_muon; d.shadow_off = shadow; d.ov_in = ov_in; d.ov_out = ov_out;
+        d.seed_base = base; d.lr_scale = sc; d.muon = hidden && c.use_muon; d.shadow_off = shadow; d.ov_in = ov_in; d.ov_out = ov_out;
         out.push_back(d);
     };
     auto vec = [&](int64_t off, int len, int a, int b, int base, float sc, int64_t ov) {
@@ -267,6 +272,11 @@ static void build_params(const egg_config &c, const ModelLayout &L, const Shadow
     vec(L.mlp_emb_bias_down, h, 516, 517, 0, 1.0f, S.mlp_emb_bias_down);
     vec(L.emb_bias, h, 50, 51, 0, 0.1f, S.emb_bias);
     mat(L.embedding, h, (int)V, 0, 0 + h, 0, 0, so.emb, S.embedding_col, S.embedding_row);
+    // the three coefficient-byte tables of the transformed-window variant: AdamW at half the rate, seeds 600 / 610 / 620
+    // (mgpu.cu:168-170, 1645-1668); the adaptive-noise overlays have no entry for them
+    if (c.ntt_mode)
+        for (int k = 0; k < 3; k++)
+            mat(L.ntt_emb + k * V * H, h, (int)V, 600 + 10 * k, 600 + 10 * k + h, 0, 0, so.ntt + k * V * H, -1, -1, 0.5f);
 }
 
 static ShadowOff shadow_offsets(const egg_config &c, int64_t *total) {
@@ -275,6 +285,7 @@ static ShadowOff shadow_offsets(const egg_config &c, int64_t *total) {
     s.init_up = o; o += 4 * H * H;
     s.init_dn = o; o += 4 * H * H;
     s.emb = o; o += V * H;
+    s.ntt = o; o += c.ntt_mode ? 3 * V * H : 0;
     s.layer0 = o;
     s.qkv = 0; s.o = 3 * H * H; s.up = 4 * H * H; s.dn = 8 * H * H; s.layer_stride = 12 * H * H;
     o += c.n_layers * s.layer_stride;
@@ -333,7 +344,7 @@ extern "C" void egg_ctx_destroy(egg_ctx *c) {
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
     void *ptrs[] = {c->d_model, c->d_opt, c->d_shadow, c->d_exp_lut, c->d_rope_lut, c->d_rope_t, c->d_act_lut, c->d_data, c->d_loss, c->d_fit,
                     c->d_x, c->d_h, c->d_u, c->d_q, c->d_ao, c->d_pre, c->d_xb, c->d_xb2, c->d_rowmax,
-                    c->d_rowmax3, c->d_xbo, c->d_wave_loss, c->d_logits, c->d_segs, c->d_nt, c->d_na, c->d_nb, c->d_votes, c->muon.x, c->muon.g,
+                    c->d_rowmax3, c->d_xbo, c->d_wave_loss, c->d_logits, c->d_coef, c->d_segs, c->d_nt, c->d_na, c->d_nb, c->d_votes, c->muon.x, c->muon.g,
                     c->muon.y, c->muon.norm2, c->d_updates, c->d_err, c->d_scales, c->d_ch_in, c->d_ch_out};
     for (void *p : ptrs) if (p) cudaFree(p);
     void *alt[] = {c->muon_alt.x, c->muon_alt.g, c->muon_alt.y, c->muon_alt.norm2};
@@ -450,6 +461,7 @@ extern "C" int egg_ctx_create(const egg_config *cfg, int device, int wave_member
     TRY(dev_alloc(&c->d_xb, R * 3)); TRY(dev_alloc(&c->d_xb2, R)); TRY(dev_alloc(&c->d_rowmax, R)); TRY(dev_alloc(&c->d_rowmax3, R * 3));
     TRY(dev_alloc(&c->d_xbo, R)); TRY(dev_alloc(&c->d_wave_loss, wave_members));
     if (logit_bytes) TRY(dev_alloc(&c->d_logits, R * cfg->vocab_size));
+    if (cfg->ntt_mode) TRY(dev_alloc(&c->d_coef, (int64_t)(wave_members / 2) * S));
     TRY(dev_alloc(&c->d_nt, (int64_t)(wave_members / 2) * c->nmap.stride));
 
     // update scratch
@@ -635,6 +647,7 @@ extern "C" int egg_upload_scales(egg_ctx *c, const void *host_scales, int64_t nb
     if (!c) { set_error("null context"); return EGG_E_INVALID; }
     EGG_CUDA(cudaSetDevice(c->device));
     if (!host_scales) { EGG_CUDA(cudaStreamSynchronize(c->stream)); c->scales_on = false; return EGG_OK; }
+    if (c->cfg.ntt_mode) { set_error("adaptive-noise overlays are not built for ntt_mode != 0 (AdaptiveScales has no entry for the coefficient tables)"); return EGG_E_INVALID; }
     if (nbytes != c->SL.total) { set_error("overlays are %lld bytes, this configuration needs %lld", (long long)nbytes, (long long)c->SL.total); return EGG_E_INVALID; }
     EGG_CUDA(cudaMemcpyAsync(c->d_scales, host_scales, (size_t)nbytes, cudaMemcpyHostToDevice, c->stream));
     EGG_CUDA(cudaStreamSynchronize(c->stream));
@@ -645,6 +658,7 @@ extern "C" int egg_upload_scales(egg_ctx *c, const void *host_scales, int64_t nb
 extern "C" int egg_download_scales(egg_ctx *c, void *host_scales, int64_t nbytes) {
     if (!c || !host_scales) { set_error("null argument"); return EGG_E_INVALID; }
     if (!c->scales_on) { set_error("no overlays uploaded"); return EGG_E_STATE; }
+    if (c->cfg.ntt_mode) { set_error("adaptive-noise overlays are not built for ntt_mode != 0 (AdaptiveScales has no entry for the coefficient tables)"); return EGG_E_INVALID; }
     if (nbytes != c->SL.total) { set_error("overlays are %lld bytes, buffer is %lld", (long long)c->SL.total, (long long)nbytes); return EGG_E_INVALID; }
     EGG_CUDA(cudaSetDevice(c->device));
     EGG_CUDA(cudaMemcpyAsync(host_scales, c->d_scales, (size_t)nbytes, cudaMemcpyDeviceToHost, c->stream));
@@ -824,6 +838,16 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
     r0.nt_w_m = nm.ln_init.w_m; r0.nt_b_m = nm.ln_init.b_m;
     r0.ndots = 1; r0.nt_dot[0] = nm.mlp_init.up_b;
     if (sc) { r0.ov_emb_row = c->d_scales + SL.embedding_row; r0.ov_emb_col = c->d_scales + SL.embedding_col; }
+    if (cf.ntt_mode) {
+        // the pair's window, transformed once (mgpu.cu:877-887); its coefficients pick rows of three more tables
+        WindowParams wp;
+        memset(&wp, 0, sizeof(wp));
+        wp.mode = cf.ntt_mode; wp.seq_len = S; wp.pairs = members / 2; wp.dataset = c->d_data; wp.tok_wide = c->tok_bytes == 4;
+        wp.data_len = c->data_len; wp.start_idx = start_idx; wp.data_stride = data_stride; wp.pair_base = pop_base / 2;
+        wp.use_same_data = cf.use_same_data; wp.coef = c->d_coef;
+        if ((rc = PROF(EGG_PROF_ROWWISE, launch_window_transform(st, wp)))) return rc;
+        r0.ntt_coef = c->d_coef; r0.ntt_rows = sh + c->so.ntt;
+    }
     if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, r0, 0)))) return rc;
     if (sc && (rc = scaled_dot1(c, M, c->d_h, 1, nm.mlp_init.up_b, SL.w_emb_mlp_up_row, c->d_xb, 3))) return rc;
     // the norm after every MLP block: LN1 of the next layer (three dots for q, k, v) or the final norm (one dot for the head)
@@ -988,6 +1012,7 @@ extern "C" int egg_generate(egg_ctx *c, uint8_t *host_tokens, int seed_len, int 
     if (!c->have_model) { set_error("upload a model first"); return EGG_E_STATE; }
     const egg_config &cf = c->cfg;
     if (cf.vocab_size != 256) { set_error("sampling is built for byte tokens only (vocab_size 256)"); return EGG_E_INVALID; }
+    if (cf.ntt_mode) { set_error("sampling is not built for ntt_mode != 0"); return EGG_E_INVALID; }
     const int total = seed_len + gen_len;
     if (seed_len < 1 || gen_len < 0 || total > cf.seq_len || total > 256) { set_error("need 1 <= seed_len and seed_len + gen_len <= min(seq_len, 256)"); return EGG_E_INVALID; }
     if (!(temp > 0.0f)) { set_error("temperature must be positive"); return EGG_E_INVALID; }

@@ -38,7 +38,8 @@ __host__ __device__ __forceinline__ int clip8(int a) { return a > 127 ? 127 : (a
 // ---------------------------------------------------------------- model layout
 // Field order of TransformerModel (mgpu.cu:284-318); element offsets.
 struct ModelLayout {
-    int64_t embedding, emb_bias, ln_init, ln_init_bias, w_emb_mlp_up, mlp_emb_bias_up, w_emb_mlp_down,
+    int64_t embedding, emb_bias, ntt_emb /* ntt_emb1..3 in a row (mgpu.cu:288-293); empty when ntt_mode == 0 */, ln_init, ln_init_bias,
+        w_emb_mlp_up, mlp_emb_bias_up, w_emb_mlp_down,
         mlp_emb_bias_down, ln_1, ln_1_bias, w_q, w_k, w_v, w_o, ln_2, ln_2_bias, w_up, mlp_bias_up, w_down,
         mlp_bias_down, ln_f, ln_f_bias, total;
 };
@@ -48,6 +49,7 @@ inline ModelLayout model_layout(const egg_config &c) {
     int64_t H = c.hidden_dim, V = c.vocab_size, NL = c.n_layers, o = 0;
     L.embedding = o;         o += V * H;
     L.emb_bias = o;          o += H;
+    L.ntt_emb = o;           o += c.ntt_mode ? 3 * V * H : 0;
     L.ln_init = o;           o += H;
     L.ln_init_bias = o;      o += H;
     L.w_emb_mlp_up = o;      o += H * 4 * H;

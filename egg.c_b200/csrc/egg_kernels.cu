@@ -165,7 +165,9 @@ constexpr int ROW_RUN = 8;
 #endif
 
 // WIDE (embedding mode only): the dataset holds uint32_t tokens below 65536 (vocab_size != 256, mgpu.cu:58-66)
-template <int MODE, int NJ, int NDOTS, bool WIDE = false>
+// NTT (embedding mode only): bytes 1..3 of the row's transformed-window coefficient index three more tables whose
+// rows are added >> 2 each (NTT_MODE != 0, mgpu.cu:916-929)
+template <int MODE, int NJ, int NDOTS, bool WIDE = false, bool NTT = false>
 __global__ void __launch_bounds__(256, MODE == 0 ? ROW_EMB_BLOCKS : 1) rowwise_kernel(const RowParams p) {
     const int run = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -257,6 +259,22 @@ __global__ void __launch_bounds__(256, MODE == 0 ? ROW_EMB_BLOCKS : 1) rowwise_k
 #pragma unroll
                 for (int j = 0; j < NJ; j++) e4_next[j] = *reinterpret_cast<const int32_t *>(p.emb_rows + (int64_t)tok_of(ri + 1) * H + (j << 7) + (lane << 2));
             }
+            int ex[NTT ? NJ : 1][4];
+            if (NTT) {
+                const int cw = p.ntt_coef[(int64_t)(mem >> 1) * p.seq_len + (r - mem * p.seq_len)];
+#pragma unroll
+                for (int j = 0; j < NJ; j++) { ex[j][0] = 0; ex[j][1] = 0; ex[j][2] = 0; ex[j][3] = 0; }
+#pragma unroll
+                for (int k = 0; k < 3; k++) {
+                    const int8_t *nrow = p.ntt_rows + ((int64_t)k * p.vocab + ((cw >> (8 * (k + 1))) & 0xFF)) * H;
+#pragma unroll
+                    for (int j = 0; j < NJ; j++) {
+                        const int32_t w4 = *reinterpret_cast<const int32_t *>(nrow + (j << 7) + (lane << 2));
+#pragma unroll
+                        for (int i = 0; i < 4; i++) ex[j][i] += (int)byte_of(w4, i) >> 2;
+                    }
+                }
+            }
 #pragma unroll
             for (int j = 0; j < NJ; j++) {
                 const int32_t e4 = e4c[j];
@@ -270,7 +288,7 @@ __global__ void __launch_bounds__(256, MODE == 0 ? ROW_EMB_BLOCKS : 1) rowwise_k
                         prod = __float2int_rz(__fmul_rn(__fmul_rn((float)prod, f_row), fc));
                     }
                     int perturb = (prod * ns) >> p.emb_shift;
-                    x[j][i] = clip8((int)byte_of(e4, i) + emb_add[j][i] + perturb);
+                    x[j][i] = clip8((int)byte_of(e4, i) + emb_add[j][i] + perturb + (NTT ? ex[j][i] : 0));
                 }
             }
         } else if (MODE == 2) {
@@ -343,18 +361,18 @@ __global__ void __launch_bounds__(256, MODE == 0 ? ROW_EMB_BLOCKS : 1) rowwise_k
     }
 }
 
-template <int MODE, int NDOTS, bool WIDE = false>
+template <int MODE, int NDOTS, bool WIDE = false, bool NTT = false>
 static int launch_rowwise_nj(cudaStream_t st, const RowParams &p) {
     const int blocks = ((p.M + ROW_RUN - 1) / ROW_RUN + 7) / 8;       // 8 warps per block, one run of rows per warp
     switch (p.H >> 7) {
-        case 1: rowwise_kernel<MODE, 1, NDOTS, WIDE><<<blocks, 256, 0, st>>>(p); break;
-        case 2: rowwise_kernel<MODE, 2, NDOTS, WIDE><<<blocks, 256, 0, st>>>(p); break;
-        case 3: rowwise_kernel<MODE, 3, NDOTS, WIDE><<<blocks, 256, 0, st>>>(p); break;
-        case 4: rowwise_kernel<MODE, 4, NDOTS, WIDE><<<blocks, 256, 0, st>>>(p); break;
-        case 5: rowwise_kernel<MODE, 5, NDOTS, WIDE><<<blocks, 256, 0, st>>>(p); break;
-        case 6: rowwise_kernel<MODE, 6, NDOTS, WIDE><<<blocks, 256, 0, st>>>(p); break;
-        case 7: rowwise_kernel<MODE, 7, NDOTS, WIDE><<<blocks, 256, 0, st>>>(p); break;
-        case 8: rowwise_kernel<MODE, 8, NDOTS, WIDE><<<blocks, 256, 0, st>>>(p); break;
+        case 1: rowwise_kernel<MODE, 1, NDOTS, WIDE, NTT><<<blocks, 256, 0, st>>>(p); break;
+        case 2: rowwise_kernel<MODE, 2, NDOTS, WIDE, NTT><<<blocks, 256, 0, st>>>(p); break;
+        case 3: rowwise_kernel<MODE, 3, NDOTS, WIDE, NTT><<<blocks, 256, 0, st>>>(p); break;
+        case 4: rowwise_kernel<MODE, 4, NDOTS, WIDE, NTT><<<blocks, 256, 0, st>>>(p); break;
+        case 5: rowwise_kernel<MODE, 5, NDOTS, WIDE, NTT><<<blocks, 256, 0, st>>>(p); break;
+        case 6: rowwise_kernel<MODE, 6, NDOTS, WIDE, NTT><<<blocks, 256, 0, st>>>(p); break;
+        case 7: rowwise_kernel<MODE, 7, NDOTS, WIDE, NTT><<<blocks, 256, 0, st>>>(p); break;
+        case 8: rowwise_kernel<MODE, 8, NDOTS, WIDE, NTT><<<blocks, 256, 0, st>>>(p); break;
         default: set_error("hidden_dim %d unsupported by the row-wise kernel", p.H); return EGG_E_INVALID;
     }
     EGG_CUDA(cudaGetLastError());
@@ -366,8 +384,9 @@ int launch_rowwise(cudaStream_t st, const RowParams &p_in, int mode) {
     p.fd_seq = make_fastdiv(p.seq_len);
     p.one = 1;
     if (p.ndots != 1 && p.ndots != 3) { set_error("row-wise kernel computes one or three row dots, not %d", p.ndots); return EGG_E_INVALID; }
-    if (mode == 0 && p.tok_wide) {
-        if (p.ndots != 1 || p.vocab > 65536) { set_error("wide-token embedding takes one row dot and a vocabulary of at most 65536"); return EGG_E_INVALID; }
+    if (mode == 0 && (p.tok_wide || p.ntt_coef)) {
+        if (p.ndots != 1 || p.vocab > 65536) { set_error("wide-token / transformed-window embedding takes one row dot and a vocabulary of at most 65536"); return EGG_E_INVALID; }
+        if (p.ntt_coef) return p.tok_wide ? launch_rowwise_nj<0, 1, true, true>(st, p) : launch_rowwise_nj<0, 1, false, true>(st, p);
         return launch_rowwise_nj<0, 1, true>(st, p);
     }
     if (p.ndots == 1) return mode == 0 ? launch_rowwise_nj<0, 1>(st, p) : (mode == 1 ? launch_rowwise_nj<1, 1>(st, p) : launch_rowwise_nj<2, 1>(st, p));
@@ -772,6 +791,75 @@ __global__ void unpack_transpose_kernel(const int32_t *packed, int8_t *shadow, i
 int launch_unpack_transpose(cudaStream_t st, const int8_t *packed, int8_t *shadow, int rows_k, int cols_n) {
     int64_t words = (int64_t)(rows_k >> 2) * cols_n;
     unpack_transpose_kernel<<<(unsigned)((words + 255) / 256), 256, 0, st>>>(reinterpret_cast<const int32_t *>(packed), shadow, rows_k, cols_n);
+    EGG_CUDA(cudaGetLastError());
+    return EGG_OK;
+}
+
+// =========================================================================
+// transform of each pair's input window (NTT_MODE 1..3; egg_ntt.cuh, called mgpu.cu:877-887): one block per pair,
+// the window in shared memory.  Mode 1: Walsh-Hadamard butterflies (a, b) -> (a + b, a - b) over strides 1, 2, 4, ...
+// Modes 2 / 3: values reduced mod p = 257 / 65537, bit-reversal, then log2(len) decimation-in-time stages whose
+// twiddle is 3^(j * len / m) mod p -- the reference takes the root of the full-length transform whatever len is.
+// Both members of a pair read the same window, so the coefficients are kept per pair.
+// =========================================================================
+__device__ __forceinline__ uint32_t fermat_pow3(uint32_t prime, int k) {
+    k &= (int)(prime - 2);                 // prime - 1 is a power of two
+    unsigned long long r = 1, b = 3;
+    while (k > 0) {
+        if (k & 1) r = r * b % prime;
+        b = b * b % prime;
+        k >>= 1;
+    }
+    return (uint32_t)r;
+}
+
+__global__ void __launch_bounds__(512) window_transform_kernel(const WindowParams p) {
+    extern __shared__ int32_t s_win[];
+    const int S = p.seq_len, tid = threadIdx.x;
+    const int64_t pair = p.pair_base + blockIdx.x;
+    const int64_t pos = p.use_same_data ? (p.start_idx % (p.data_len - S)) : ((p.start_idx + pair * p.data_stride) % (p.data_len - S));
+    const uint32_t prime = p.mode == 2 ? 257u : 65537u;
+    for (int i = tid; i < S; i += blockDim.x) {
+        const uint32_t tok = p.tok_wide ? reinterpret_cast<const uint32_t *>(p.dataset)[pos + i] : (uint32_t)p.dataset[pos + i];
+        s_win[i] = p.mode == 1 ? (int32_t)tok : (int32_t)(tok % prime);
+    }
+    __syncthreads();
+    if (p.mode == 1) {
+        for (int stride = 1; stride < S; stride <<= 1) {
+            for (int t = tid; t < (S >> 1); t += blockDim.x) {
+                const int base = (t / stride) * 2 * stride + (t % stride);
+                const int32_t a = s_win[base], b = s_win[base + stride];
+                s_win[base] = a + b; s_win[base + stride] = a - b;
+            }
+            __syncthreads();
+        }
+    } else {
+        const int lg = 31 - __clz(S);
+        for (int i = tid; i < S; i += blockDim.x) {
+            const int rev = (int)(__brev((unsigned)i) >> (32 - lg));
+            if (i < rev) { const int32_t t = s_win[i]; s_win[i] = s_win[rev]; s_win[rev] = t; }
+        }
+        __syncthreads();
+        for (int s = 1; s <= lg; s++) {
+            const int m2 = 1 << (s - 1), w_step = S >> s;
+            for (int k = tid; k < (S >> 1); k += blockDim.x) {
+                const int j = k & (m2 - 1), i1 = ((k >> (s - 1)) << s) + j, i2 = i1 + m2;
+                const uint32_t wb = (uint32_t)((unsigned long long)fermat_pow3(prime, j * w_step) * (uint32_t)s_win[i2] % prime);
+                const uint32_t a = (uint32_t)s_win[i1];
+                s_win[i1] = (int32_t)((a + wb) % prime);
+                s_win[i2] = (int32_t)((a + prime - wb) % prime);
+            }
+            __syncthreads();
+        }
+    }
+    for (int i = tid; i < S; i += blockDim.x) p.coef[(int64_t)blockIdx.x * S + i] = s_win[i];
+}
+int launch_window_transform(cudaStream_t st, const WindowParams &p) {
+    if (p.mode < 1 || p.mode > 3 || p.seq_len < 2 || (p.seq_len & (p.seq_len - 1)) || p.seq_len > 8192 || p.pairs <= 0) {
+        set_error("window transform: mode %d, seq_len %d, %d pairs unsupported", p.mode, p.seq_len, p.pairs); return EGG_E_INVALID;
+    }
+    int threads = p.seq_len / 2 < 32 ? 32 : (p.seq_len / 2 > 512 ? 512 : p.seq_len / 2);
+    window_transform_kernel<<<p.pairs, threads, (size_t)p.seq_len * sizeof(int32_t), st>>>(p);
     EGG_CUDA(cudaGetLastError());
     return EGG_OK;
 }

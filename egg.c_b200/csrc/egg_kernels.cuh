@@ -57,6 +57,8 @@ struct RowParams {
     const int8_t *emb_bias; int vocab;
     int nt_emb_a, nt_emb_b, nt_emb_bias_d, emb_shift;
     const int8_t *ov_emb_row, *ov_emb_col;   // adaptive-noise overlays of the embedding ([vocab], [H]) or null
+    const int32_t *ntt_coef;     // transformed-window coefficients [wave pairs][seq_len] (ntt_mode != 0) or null
+    const int8_t *ntt_rows;      // token-major copies of ntt_emb1..3, [3][vocab][H]
     const int32_t *pre32; int32_t *rowmax;
     // residual stream out (modes 0, 1); in mode 2 the residual stream is final already and is only read, from x_out
     int8_t *x_out;
@@ -143,6 +145,13 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
 int gemm_init();   // resolves the driver entry point for tensor-map encoding, sets smem attributes
 
 // ---- fitness / update -------------------------------------------------------
+// Transform of every pair's input window (ntt_mode 1..3): see window_transform_kernel.
+struct WindowParams {
+    int mode, seq_len, pairs;
+    const uint8_t *dataset; int tok_wide; int64_t data_len, start_idx, data_stride; int pair_base, use_same_data;
+    int32_t *coef;               // [pairs][seq_len]
+};
+int launch_window_transform(cudaStream_t st, const WindowParams &p);
 // Second pass of the head over int32 logits kept in memory (vocab_size != 256): see head_loss_kernel.
 struct HeadLossParams {
     int M, V, seq_len;

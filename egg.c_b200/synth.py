@@ -75,6 +75,8 @@ def random_model(cfg, seed=0, kind="uniform", gains_random=False):
         H, V, L = cfg.hidden_dim, cfg.vocab_size, cfg.n_layers
         o = V * H
         m[o:o + H] = 0; o += H                       # emb_bias
+        if cfg.ntt_mode:
+            o += 3 * V * H                           # ntt_emb1..3
         m[o:o + H] = 16; o += H                      # ln_init
         m[o:o + H] = 0; o += H                       # ln_init_bias
         o += 4 * H * H

@@ -68,6 +68,10 @@ typedef struct egg_config {
     float   adam_weight_decay;   /* ADAM_WEIGHT_DECAY                               */
     float   muon_momentum;       /* MUON_MOMENTUM                                   */
     float   muon_lr_scale;       /* MUON_LR_SCALE                                   */
+    int32_t ntt_mode;            /* NTT_MODE (mgpu.cu:50-53, egg_ntt.cuh): 0 off; 1 Walsh-Hadamard, 2 Fermat-257,
+                                    3 Fermat-65537 transform of each member's input window, whose coefficient bytes
+                                    1..3 index three more embedding tables (ntt_emb1..3 in TransformerModel and
+                                    AdamModel).  Needs a power-of-two seq_len <= hidden_dim (mode 2: <= 256). */
 } egg_config;
 
 /* Defaults of full_cuda_train_transformer_adam_mgpu.cu:35-270. */

@@ -60,7 +60,8 @@ static inline int clip8(int64_t a) { return a > 127 ? 127 : (a < -127 ? -127 : (
 /* --------------------------------------------------------------- layout */
 
 typedef struct {
-    int64_t embedding, emb_bias, ln_init, ln_init_bias, w_emb_mlp_up, mlp_emb_bias_up,
+    int64_t embedding, emb_bias, ntt_emb /* three V*H tables in a row, present when ntt_mode != 0 */, ln_init, ln_init_bias,
+        w_emb_mlp_up, mlp_emb_bias_up,
         w_emb_mlp_down, mlp_emb_bias_down, ln_1, ln_1_bias, w_q, w_k, w_v, w_o, ln_2,
         ln_2_bias, w_up, mlp_bias_up, w_down, mlp_bias_down, ln_f, ln_f_bias, total;
 } model_layout;
@@ -70,6 +71,7 @@ static void layout_of(const egg_config *c, model_layout *L) {
     int64_t H = c->hidden_dim, V = c->vocab_size, NL = c->n_layers, o = 0;
     L->embedding = o;        o += V * H;
     L->emb_bias = o;         o += H;
+    L->ntt_emb = o;          o += c->ntt_mode ? 3 * V * H : 0;     /* ntt_emb1..3, mgpu.cu:288-293 */
     L->ln_init = o;          o += H;
     L->ln_init_bias = o;     o += H;
     L->w_emb_mlp_up = o;     o += H * 4 * H;
@@ -116,7 +118,8 @@ static int64_t opt_offset_of(const egg_config *c, const model_layout *L, int64_t
     /* walk the fields in order */
     int64_t H = c->hidden_dim, V = c->vocab_size, NL = c->n_layers;
     struct { int64_t o, n; int hidden; } f[] = {
-        {L->embedding, V * H, 0}, {L->emb_bias, H, 0}, {L->ln_init, H, 0}, {L->ln_init_bias, H, 0},
+        {L->embedding, V * H, 0}, {L->emb_bias, H, 0}, {L->ntt_emb, c->ntt_mode ? 3 * V * H : 0, 0},
+        {L->ln_init, H, 0}, {L->ln_init_bias, H, 0},
         {L->w_emb_mlp_up, 4 * H * H, 1}, {L->mlp_emb_bias_up, 4 * H, 0},
         {L->w_emb_mlp_down, 4 * H * H, 1}, {L->mlp_emb_bias_down, H, 0},
         {L->ln_1, NL * H, 0}, {L->ln_1_bias, NL * H, 0},
@@ -220,6 +223,8 @@ void oracle_init_model(const egg_config *cfg, int8_t *model, uint32_t seed) {
     memset(model, 0, (size_t)L.total);
 #define DRAW(n) for (int64_t i_ = 0; i_ < (n); i_++) tmp[i_] = (int8_t)oracle_gen_noise_host(cfg, &rng)
     DRAW(V * H); oracle_repack_matrix(model + L.embedding, tmp, (int)H, (int)V);
+    if (cfg->ntt_mode)          /* mgpu.cu:472-482 */
+        for (int k = 0; k < 3; k++) { DRAW(V * H); oracle_repack_matrix(model + L.ntt_emb + k * V * H, tmp, (int)H, (int)V); }
     for (int64_t i = 0; i < H; i++) { model[L.ln_init + i] = 16; }
     DRAW(4 * H * H); oracle_repack_matrix(model + L.w_emb_mlp_up, tmp, (int)H, (int)(4 * H));
     DRAW(4 * H * H); oracle_repack_matrix(model + L.w_emb_mlp_down, tmp, (int)(4 * H), (int)H);
@@ -486,6 +491,54 @@ static inline int token_at(const egg_config *c, const uint8_t *dataset, int64_t 
     return c->vocab_size == 256 ? (int)dataset[i] : (int)((const uint32_t *)dataset)[i];
 }
 
+/* ---- the optional transform of the input window (egg_ntt.cuh; NTT_MODE 1, 2, 3) ----
+ * The reference runs it with one thread per hidden unit; with seq_len <= hidden_dim (required here) every element
+ * is loaded and every butterfly of every stage is executed, which is what this serial form computes. */
+static int64_t fermat_p(int mode) { return mode == 2 ? 257 : 65537; }
+
+/* 3^k mod p by square-and-multiply with k taken mod p-1 (pow_omega257 / pow_omega65537, egg_ntt.cuh:187-201, 273-289) */
+static int64_t fermat_pow3(int mode, int k) {
+    int64_t p = fermat_p(mode), r = 1, b = 3;
+    k &= (int)(p - 2);          /* p-1 is a power of two: k mod (p-1) */
+    while (k > 0) { if (k & 1) r = r * b % p; b = b * b % p; k >>= 1; }
+    return r;
+}
+
+static void window_transform(const egg_config *c, int32_t *d, int len) {
+    int mode = c->ntt_mode;
+    if (mode == 1) {            /* Walsh-Hadamard, natural order (wht_transform_inplace, egg_ntt.cuh:105-122) */
+        for (int stride = 1; stride < len; stride <<= 1)
+            for (int t = 0; t < len / 2; t++) {
+                int base = (t / stride) * 2 * stride + t % stride;
+                int32_t a = d[base], b = d[base + stride];
+                d[base] = a + b; d[base + stride] = a - b;
+            }
+        return;
+    }
+    /* fermat_ntt_inplace + ntt_dit_inplace (egg_ntt.cuh:330-366, 420-428): reduce, bit-reverse, then log2(len)
+     * stages whose twiddle is 3^(j * len / m) -- the root of the full-length transform whatever len is */
+    int64_t p = fermat_p(mode);
+    int lg = 0; while ((1 << lg) < len) lg++;
+    for (int i = 0; i < len; i++) d[i] = (int32_t)(((int64_t)d[i] % p + p) % p);
+    for (int i = 0; i < len; i++) {
+        int rev = 0;
+        for (int b = 0; b < lg; b++) rev |= ((i >> b) & 1) << (lg - 1 - b);
+        if (i < rev) { int32_t t = d[i]; d[i] = d[rev]; d[rev] = t; }
+    }
+    for (int s = 1; s <= lg; s++) {
+        int m = 1 << s, m2 = m >> 1, w_step = len >> s;
+        for (int k = 0; k < len / 2; k++) {
+            int j = k % m2, i1 = (k / m2) * m + j, i2 = i1 + m2;
+            int64_t wb = fermat_pow3(mode, j * w_step) * d[i2] % p;
+            int64_t a = d[i1];
+            d[i1] = (int32_t)((a + wb) % p);
+            d[i2] = (int32_t)((a - wb + p) % p);
+        }
+    }
+}
+
+void oracle_window_transform(const egg_config *cfg, int32_t *data, int len) { window_transform(cfg, data, len); }
+
 /* One member, whole sequence (mgpu.cu:847-1029). */
 static int32_t eval_member(const eval_env *E, const uint8_t *dataset, int64_t data_len, int64_t start_idx,
                            uint32_t step_seed, int p_idx, int8_t *trace_x, int32_t *trace_logits) {
@@ -501,6 +554,12 @@ static int32_t eval_member(const eval_env *E, const uint8_t *dataset, int64_t da
     int8_t *kv = (int8_t *)calloc((size_t)NL * 2 * S * H, 1);
     int32_t *lg = (int32_t *)malloc(sizeof(int32_t) * (size_t)V);
     int64_t my_loss = 0;
+    int32_t *coef = NULL;
+    if (c->ntt_mode) {          /* mgpu.cu:877-887: the window's first seq_len tokens, transformed once */
+        coef = (int32_t *)malloc(sizeof(int32_t) * (size_t)S);
+        for (int t = 0; t < S; t++) coef[t] = token_at(c, dataset, stream_pos + t);
+        window_transform(c, coef, S);
+    }
 
     for (int t = 0; t < S; t++) {
         int tok = token_at(c, dataset, stream_pos + t);
@@ -517,7 +576,14 @@ static int32_t eval_member(const eval_env *E, const uint8_t *dataset, int64_t da
                 prod = (int32_t)((float)prod * adaptive_factor(E, SC->embedding_row, tok) *
                                  adaptive_factor(E, SC->embedding_col, d));
             int32_t perturb = (prod * ns) >> (c->fixed_point + c->sigma_shift);
-            x[d] = (int8_t)clip8(emb + ebias + chk + perturb);
+            int32_t extra = 0;
+            if (coef) {         /* bytes 1, 2, 3 of the coefficient index three more tables, each added >> 2 (mgpu.cu:916-929) */
+                for (int k = 0; k < 3; k++) {
+                    int nb = (coef[t] >> (8 * (k + 1))) & 0xFF;
+                    extra += M[L->ntt_emb + (int64_t)k * V * H + ((int64_t)(d >> 2) * V + nb) * 4 + (d & 3)] >> 2;
+                }
+            }
+            x[d] = (int8_t)clip8(emb + ebias + chk + perturb + extra);
         }
         const int nst = 3 + 2 * NL;
 #define STAGE(i, buf) do { if (trace_x) memcpy(trace_x + ((int64_t)t * nst + (i)) * H, (buf), (size_t)H); } while (0)
@@ -560,7 +626,7 @@ static int32_t eval_member(const eval_env *E, const uint8_t *dataset, int64_t da
         /* a target outside the vocabulary matches no column: the reference's s_target_logit stays 0 (mgpu.cu:989-1002) */
         my_loss += (log_sum >> 1) + mx - ((target >= 0 && target < V) ? lg[target] : 0);
     }
-    free(x); free(nf); free(kv); free(lg);
+    free(x); free(nf); free(kv); free(lg); free(coef);
     return (int32_t)my_loss;
 }
 
@@ -798,6 +864,12 @@ static int build_params(const egg_config *c, const model_layout *L, const scales
     MAT(L->w_emb_mlp_down, 4 * H, H, 512, 513, 0, 1, S->w_emb_mlp_down_row, S->w_emb_mlp_down_col);  VEC(L->mlp_emb_bias_down, H, 516, 517, 0, 1.0f, S->mlp_emb_bias_down);
     VEC(L->emb_bias, H, 50, 51, 0, 0.1f, S->emb_bias);
     MAT(L->embedding, H, V, 0, 0 + H, 0, 0, S->embedding_col, S->embedding_row);    /* always AdamW, mgpu.cu:1636-1643 */
+    if (c->ntt_mode) {          /* mgpu.cu:1645-1668: AdamW at half the learning rate, seeds 600 / 610 / 620 */
+        for (int k = 0; k < 3; k++) {
+            MAT(L->ntt_emb + (int64_t)k * V * H, H, V, 600 + 10 * k, 600 + 10 * k + H, 0, 0, -1, -1);
+            P[n - 1].lr_scale = 0.5f;
+        }
+    }
 #undef MAT
 #undef VEC
     return n;
@@ -821,7 +893,7 @@ uint64_t oracle_update_scaled(const egg_config *c, int8_t *model, void *opt_stat
                               uint32_t step_seed, float lr, int fma_mode, int8_t *scales) {
     model_layout L; layout_of(c, &L);
     scales_layout SL; scales_layout_of(c, &SL);
-    param_desc *P = (param_desc *)malloc(sizeof(param_desc) * (size_t)(c->n_layers * 12 + 16));
+    param_desc *P = (param_desc *)malloc(sizeof(param_desc) * (size_t)(c->n_layers * 12 + 20));
     int np = build_params(c, &L, &SL, P);
     int maxdim = 4 * c->hidden_dim > c->vocab_size ? 4 * c->hidden_dim : c->vocab_size;
     uint8_t *ch_in = (uint8_t *)malloc((size_t)maxdim), *ch_out = (uint8_t *)malloc((size_t)maxdim);
@@ -833,7 +905,7 @@ uint64_t oracle_update_scaled(const egg_config *c, int8_t *model, void *opt_stat
         int64_t field_off, within;
         {
             int64_t H = c->hidden_dim;
-            int64_t starts[] = {L.embedding, L.emb_bias, L.ln_init, L.ln_init_bias, L.w_emb_mlp_up,
+            int64_t starts[] = {L.embedding, L.emb_bias, L.ntt_emb, L.ln_init, L.ln_init_bias, L.w_emb_mlp_up,
                                 L.mlp_emb_bias_up, L.w_emb_mlp_down, L.mlp_emb_bias_down, L.ln_1, L.ln_1_bias,
                                 L.w_q, L.w_k, L.w_v, L.w_o, L.ln_2, L.ln_2_bias, L.w_up, L.mlp_bias_up,
                                 L.w_down, L.mlp_bias_down, L.ln_f, L.ln_f_bias};
@@ -862,7 +934,7 @@ uint64_t oracle_update_scaled(const egg_config *c, int8_t *model, void *opt_stat
                     else ch_in[j] = 1;
                 }
             }
-            if (scales) {   /* worker.cu:445-463: overlay of the input index, then of the output index */
+            if (scales && d->ov_in >= 0) {   /* worker.cu:445-463: overlay of the input index, then of the output index */
                 overlay_step(scales + d->ov_in, ch_in, d->rows ? d->rows : d->cols);
                 if (d->rows) overlay_step(scales + d->ov_out, ch_out, d->cols);
             }

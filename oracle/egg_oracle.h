@@ -53,6 +53,10 @@ void oracle_eval(const egg_config *cfg, const int8_t *model, const int8_t *scale
                  const uint8_t *dataset, int64_t data_len, int64_t start_idx,
                  uint32_t step_seed, int pop_offset, int count, int32_t *losses_out);
 
+/* the transform cfg->ntt_mode (1 Walsh-Hadamard, 2 Fermat-257, 3 Fermat-65537) applies to a member's input window
+ * before the embedding (ntt_transform_sequence, egg_ntt.cuh:446-455), in place on `len` values (a power of two) */
+void oracle_window_transform(const egg_config *cfg, int32_t *data, int len);
+
 /* per-token trace of one member for debugging/cross-checks: fills
  * stages[seq_len][3 + 2*n_layers][H] with the residual stream after the
  * embedding, after the initial MLP, after each layer's attention and MLP block,

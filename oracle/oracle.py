@@ -23,7 +23,7 @@ class EggConfig(C.Structure):
         "chunk_relative_loss")] + [
         ("softmax_exp_scale", C.c_double), ("adam_beta1", C.c_float), ("adam_beta2", C.c_float),
         ("adam_eps", C.c_float), ("adam_weight_decay", C.c_float), ("muon_momentum", C.c_float),
-        ("muon_lr_scale", C.c_float)]
+        ("muon_lr_scale", C.c_float), ("ntt_mode", C.c_int32)]
 
 
 class GruConfig(C.Structure):
@@ -49,7 +49,7 @@ def make_config(**kw):
              softmax_scale_bit=18, rope_scale_bit=20, device_mask=15, device_gaussian=0,
              host_mask=15, use_same_data=0, use_muon=0, chunk_relative_loss=0,
              softmax_exp_scale=6.0, adam_beta1=0.9, adam_beta2=0.95, adam_eps=1e-8,
-             adam_weight_decay=0.01, muon_momentum=0.85, muon_lr_scale=1.0)
+             adam_weight_decay=0.01, muon_momentum=0.85, muon_lr_scale=1.0, ntt_mode=0)
     for k in kw:
         if k not in d:
             raise KeyError(k)
@@ -88,6 +88,7 @@ def lib():
         L.oracle_eval.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                                   C.c_uint32, C.c_int, C.c_int, C.c_void_p]
         L.oracle_fitness.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+        L.oracle_window_transform.argtypes = [cfgp, C.c_void_p, C.c_int]
         L.oracle_generate.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_uint32, C.c_float, C.c_float, C.c_float]
         L.oracle_update.restype = C.c_uint64
         L.oracle_update.argtypes = [cfgp, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_float, C.c_int]
@@ -163,6 +164,13 @@ def eval_losses(cfg, model, dataset, start_idx, step_seed, pop_offset, count, sc
     lib().oracle_eval(C.byref(cfg), _p(model), _p(scales), _p(dataset), len(dataset), start_idx,
                       step_seed & 0xFFFFFFFF, pop_offset, count, _p(out))
     return out
+
+
+def window_transform(cfg, values):
+    """The ntt_mode transform of one input window (int32 in, int32 out)."""
+    d = np.ascontiguousarray(values, np.int32).copy()
+    lib().oracle_window_transform(C.byref(cfg), _p(d), len(d))
+    return d
 
 
 def fitness(losses):

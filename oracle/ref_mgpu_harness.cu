@@ -36,9 +36,9 @@ static void die(const char *m) { fprintf(stderr, "ref harness: %s\n", m); exit(2
 int main(int argc, char **argv) {
     if (argc == 2 && std::string(argv[1]) == "--sizes") {
         printf("{\"model_bytes\": %zu, \"opt_bytes\": %zu, \"hidden_dim\": %d, \"head_dim\": %d, \"n_layers\": %d, "
-               "\"seq_len\": %d, \"vocab_size\": %d, \"population_size\": %d, \"device_mask\": %d, \"use_muon\": %d}\n",
+               "\"seq_len\": %d, \"vocab_size\": %d, \"population_size\": %d, \"device_mask\": %d, \"use_muon\": %d, \"ntt_mode\": %d}\n",
                sizeof(TransformerModel), sizeof(AdamModel), HIDDEN_DIM, HEAD_DIM, N_LAYERS, SEQ_LEN, VOCAB_SIZE,
-               POPULATION_SIZE, DEVICE_MASK, USE_MUON);
+               POPULATION_SIZE, DEVICE_MASK, USE_MUON, NTT_MODE);
         return 0;
     }
     if (argc < 3) die("usage: ref_mgpu_<tag> in.bin out.bin | --sizes");
@@ -86,6 +86,9 @@ int main(int argc, char **argv) {
 
     cudaEvent_t e0, e1, e2; cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventCreate(&e2);
     size_t sm_size = 2 * HIDDEN_DIM + 512 + (4 * HIDDEN_DIM);
+#if NTT_MODE != 0
+    sm_size += SEQ_LEN * sizeof(int32_t);      // the transformed window (mgpu.cu:1512-1517)
+#endif
     const long step = 1;   // only gates the reference's debug printf
     cudaEventRecord(e0, stream);
     for (int off = h.pop_offset; off < h.pop_offset + h.count; off += batch_cap) {
@@ -132,8 +135,8 @@ int main(int argc, char **argv) {
         auto vec = [&](WeightType *v, AdamParam *st, int len, int a, int b, int base, float sc) {
             update_vector_adam_kernel<<<(len + 255) / 256, 256, 0, stream>>>(v, st, len, a, b, base, d_fit, seed, current_lr * sc);
         };
-        auto mat_adam = [&](WeightType *w, AdamParam *st, int rows, int cols, int a, int b, int base) {
-            update_matrix_adam_kernel<<<(rows * cols + 511) / 512, 512, 0, stream>>>(w, st, rows, cols, a, b, base, d_fit, seed, current_lr);
+        auto mat_adam = [&](WeightType *w, AdamParam *st, int rows, int cols, int a, int b, int base, float sc = 1.0f) {
+            update_matrix_adam_kernel<<<(rows * cols + 511) / 512, 512, 0, stream>>>(w, st, rows, cols, a, b, base, d_fit, seed, current_lr * sc);
         };
         auto mat = [&](WeightType *w, HIDDEN_OPT_TYPE *st, int rows, int cols, int a, int b, int base) {
 #if USE_MUON == 1
@@ -172,6 +175,11 @@ int main(int argc, char **argv) {
         vec(d_model->mlp_emb_bias_down, d_opt->mlp_emb_bias_down, H, SEED_OFF_EMB_MLP_BIAS_DOWN_A, SEED_OFF_EMB_MLP_BIAS_DOWN_B, 0, 1.0f);
         vec(d_model->emb_bias, d_opt->emb_bias, H, SEED_OFF_EMB_BIAS_A, SEED_OFF_EMB_BIAS_B, 0, 0.1f);
         mat_adam(d_model->embedding, d_opt->embedding, H, VOCAB_SIZE, SEED_OFF_EMB, SEED_OFF_EMB + H, 0);
+#if NTT_MODE != 0
+        mat_adam(d_model->ntt_emb1, d_opt->ntt_emb1, H, VOCAB_SIZE, SEED_OFF_NTT_EMB1, SEED_OFF_NTT_EMB1 + H, 0, 0.5f);
+        mat_adam(d_model->ntt_emb2, d_opt->ntt_emb2, H, VOCAB_SIZE, SEED_OFF_NTT_EMB2, SEED_OFF_NTT_EMB2 + H, 0, 0.5f);
+        mat_adam(d_model->ntt_emb3, d_opt->ntt_emb3, H, VOCAB_SIZE, SEED_OFF_NTT_EMB3, SEED_OFF_NTT_EMB3 + H, 0, 0.5f);
+#endif
         cudaEventRecord(e2, stream);
         CHECK_CUDA(cudaStreamSynchronize(stream));
         CHECK_CUDA(cudaGetLastError());

@@ -47,6 +47,10 @@ REF_CONFIGS = {
     # tokenizer variant: uint32 tokens, vocabulary other than 256 (mgpu.cu:58-66)
     "tok_tiny": dict(hidden_dim=128, n_layers=1, seq_len=16, population_size=32, device_mask=15, vocab_size=1024),
     "tok_small": dict(hidden_dim=256, n_layers=2, seq_len=32, population_size=64, device_mask=3, vocab_size=512),
+    # transformed-window variants (NTT_MODE 1 Walsh-Hadamard, 2 Fermat-257, 3 Fermat-65537)
+    "ntt1_tiny": dict(hidden_dim=128, n_layers=1, seq_len=16, population_size=32, device_mask=15, ntt_mode=1),
+    "ntt2_tiny": dict(hidden_dim=128, n_layers=1, seq_len=16, population_size=32, device_mask=15, ntt_mode=2),
+    "ntt3_small": dict(hidden_dim=256, n_layers=2, seq_len=32, population_size=64, device_mask=3, ntt_mode=3),
 }
 
 
@@ -80,7 +84,7 @@ def run_ref_mgpu(tag, model, dataset, step_seed, start_idx, pop_offset, count, l
             f.write(struct.pack("<IIqqiifiii", 0x46524745, step_seed & 0xFFFFFFFF, start_idx, len(dataset), pop_offset, count,
                                 lr, 1 if do_update else 0, 1 if opt_state is not None else 0, sizes["vocab_size"]))
             kw = REF_CONFIGS[tag]
-            assert kw.get("vocab_size", 256) == sizes["vocab_size"]
+            assert kw.get("vocab_size", 256) == sizes["vocab_size"] and kw.get("ntt_mode", 0) == sizes.get("ntt_mode", 0)
             f.write(struct.pack("<6i", kw["hidden_dim"], kw["n_layers"], kw["seq_len"], kw["population_size"], kw["device_mask"],
                                 kw.get("use_muon", 0)))
             f.write(np.ascontiguousarray(model, np.int8).tobytes())

@@ -4,7 +4,8 @@
                                                reference's egg_math.h / ternary_pack.h)
   python tests/golden/make_golden.py mgpu     (on a B200: runs oracle/_ref/ref_mgpu_*, the
                                                reference's own kernels, on seeded cases; the tok_* cases
-                                               are its tokenizer build, VOCAB_SIZE 1024 / 512, uint32 tokens)
+                                               are its tokenizer build, VOCAB_SIZE 1024 / 512, uint32 tokens;
+                                               the ntt* cases its NTT_MODE 1 / 2 / 3 builds)
   python tests/golden/make_golden.py deggs    (on a B200: runs oracle/_ref/ref_deggs_*, the d-eggs
                                                worker's kernels with adaptive-noise overlays)
   python tests/golden/make_golden.py muon     (on a B200: one Muon step of oracle/_ref/ref_mgpu_muon_*, the
@@ -52,7 +53,7 @@ def mgpu(outdir):
     from common import REF_CONFIGS, make_case, run_ref_mgpu
     os.makedirs(outdir, exist_ok=True)
     only = os.environ.get("EGG_GOLDEN_TAGS")       # e.g. "tok_tiny,tok_small": regenerate a subset
-    for tag in ("tiny", "small", "muon_tiny", "tok_tiny", "tok_small"):
+    for tag in ("tiny", "small", "muon_tiny", "tok_tiny", "tok_small", "ntt1_tiny", "ntt2_tiny", "ntt3_small"):
         if only and tag not in only.split(","):
             continue
         kw = REF_CONFIGS[tag]

@@ -12,7 +12,7 @@ GOLD = os.path.join(ROOT, "tests", "golden")
 STEPS, SEED, LR = 4, 0x00C0FFEE, 0.5
 
 
-@pytest.mark.parametrize("tag", ["tiny", "small", "muon_tiny", "tok_tiny", "tok_small"])
+@pytest.mark.parametrize("tag", ["tiny", "small", "muon_tiny", "tok_tiny", "tok_small", "ntt1_tiny", "ntt2_tiny", "ntt3_small"])
 def test_oracle_reproduces_reference_kernel_outputs(tag):
     path = os.path.join(GOLD, "ref_mgpu_%s.npz" % tag)
     g = np.load(path)

@@ -187,3 +187,42 @@ def test_index_math_selftest_runs_on_the_host():
     """FastDiv (the multiply-shift division of the per-tile index arithmetic) against C division, through the C ABI."""
     pkg = load_pkg()
     pkg.selftest_index_math()
+
+
+def test_oracle_window_transforms_against_their_definitions():
+    """ntt_mode 1 is the Walsh-Hadamard transform in natural order; modes 2 and 3 at their full lengths (256, 65536)
+    are number-theoretic transforms with root 3: X[k] = sum_n x[n] 3^(n k) mod p.  At shorter lengths the reference
+    keeps the full-length root in its twiddles (egg_ntt.cuh:349-362), so only the first stages agree with a true
+    transform; those lengths are pinned by the reference-kernel goldens instead."""
+    O = load_oracle()
+    rng = np.random.default_rng(3)
+    x = rng.integers(0, 256, 64).astype(np.int32)
+    h = np.array([[1]])
+    while h.shape[0] < 64:
+        h = np.block([[h, h], [h, -h]])
+    assert (O.window_transform(O.make_config(ntt_mode=1), x) == h @ x).all()
+    x = rng.integers(0, 256, 256).astype(np.int32)
+    n = np.arange(256)
+    pw = np.array([pow(3, int(e), 257) for e in range(256)], np.int64)
+    want = np.array([(x.astype(np.int64) * pw[(n * k) % 256]).sum() % 257 for k in range(256)])
+    assert (O.window_transform(O.make_config(ntt_mode=2), x) == want).all()
+    # mode 3 at a short length: every output stays below the prime and the transform is linear mod p
+    a, b = rng.integers(0, 65537, 32).astype(np.int32), rng.integers(0, 65537, 32).astype(np.int32)
+    c3 = O.make_config(ntt_mode=3)
+    ta, tb, tab = O.window_transform(c3, a), O.window_transform(c3, b), O.window_transform(c3, ((a.astype(np.int64) + b) % 65537).astype(np.int32))
+    assert ta.max() < 65537 and ta.min() >= 0
+    assert (((ta.astype(np.int64) + tb) % 65537) == tab).all()
+
+
+def test_ntt_mode_layout_and_validation():
+    pkg, O = load_pkg(), load_oracle()
+    kw = dict(hidden_dim=128, n_layers=1, seq_len=16)
+    for mode in (1, 2, 3):
+        cfg, ocfg = cfg_pair(ntt_mode=mode, **kw)
+        assert pkg.model_bytes(cfg) == O.model_bytes(ocfg) == O.model_bytes(O.make_config(**kw)) + 3 * 256 * 128
+        assert pkg.opt_state_bytes(cfg) == O.opt_bytes(ocfg) == O.opt_bytes(O.make_config(**kw)) + 3 * 256 * 128 * 12
+    L = pkg.lib()
+    for bad in (dict(ntt_mode=4), dict(ntt_mode=1, seq_len=48), dict(ntt_mode=1, seq_len=256, hidden_dim=128),
+                dict(ntt_mode=2, seq_len=512, hidden_dim=512)):
+        cfg = pkg.default_config(**bad)
+        assert L.egg_config_validate(C.byref(cfg), None) == pkg.EGG_E_INVALID, bad
