@@ -284,7 +284,8 @@ def c5_sample_run(pkg, synth, device, members, peaks, mma_loop_tops, steps=2, fu
     return {"workload": "12 layers, H 1024, 16 heads, seq 512, ternary weight values, Muon; %d of 262144 members evaluated, update over "
                         "all 131072 pairs" % members,
             "adaptive_norms": {0: "two-kernel form", 1: "fused into the projection epilogues (row-owning kernels on pairs of thread blocks)",
-                               2: "fused into the projection epilogues (row-owning kernels on pairs of thread blocks), the next mean-abs norm inside MLP-down"}[fused_active],
+                               2: "fused into the projection epilogues (row-owning kernels on pairs of thread blocks), the next mean-abs norm inside MLP-down",
+                               3: "fused into the projection epilogues (row-owning kernels on pairs of thread blocks), every mean-abs norm inside the projection before it"}[fused_active],
             "eval_member_tokens_per_s": members * S / (eval_ms / 1e3), "eval_ms": eval_ms, "update_ms": upd_ms,
             # summed over the two side streams the matrices alternate on: two run at a time, so this exceeds its share of update_ms
             "newton_schulz_and_apply_ms_summed_over_streams": prof.get("muon", (0.0, 0))[0] / steps,
@@ -514,7 +515,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the extra legs of the default line (recurrent model, reference GPU kernels, C5 sample)")
     ap.add_argument("--two-kernel-norm", action="store_true", help="A/B: take the two-kernel form of the adaptive normalisations (int32 pre-activations + requantisation kernels)")
-    ap.add_argument("--fused-level", type=int, default=2, choices=[0, 1, 2],
+    ap.add_argument("--fused-level", type=int, default=2, choices=[0, 1, 2, 3],
                     help="A/B: 0 two-kernel adaptive norms, 1 row-owning projections, 2 (default) also the next mean-abs norm inside the MLP-down epilogue")
     ap.add_argument("--attention-tc", type=int, nargs="?", const=1, default=None, choices=[0, 1, 2],
                     help="A/B: attention kernel: 0 mma.sync, 1 tcgen05 scores and sums, 2 mma.sync scores + tcgen05 sums (default: the library's)")
@@ -764,7 +765,8 @@ def main():
                                     "fixed population sharded over the GPUs") if strong else WORKLOAD, "population_size": pop, "members_per_gpu": per, "seq_len": S, "hidden_dim": H,
                        "n_layers": L, "wave_members": wave_members, "dataset_bytes": DATA_LEN,
                        "adaptive_norms": {0: "two-kernel form", 1: "fused into the projection epilogues (row-owning kernels)",
-                                          2: "fused into the projection epilogues (row-owning kernels), the next mean-abs norm inside MLP-down"}[fused_active],
+                                          2: "fused into the projection epilogues (row-owning kernels), the next mean-abs norm inside MLP-down",
+                                          3: "fused into the projection epilogues (row-owning kernels), every mean-abs norm inside the projection before it"}[fused_active],
                        "l2_policy": "inputs larger than L2: each wave streams > 2 GB of activations, dataset 64 MiB",
                        "parallelism": "population sharded, pair-aligned; one NCCL all-gather of fitness per generation"},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": int(DATA_LEN),

@@ -438,7 +438,7 @@ class Context:
 
     def set_fused_epilogues(self, level):
         """0 / False: two-kernel adaptive norms; 1 / True: row-owning projections; 2 (the default of a new context):
-        also the next mean-abs norm inside the MLP-down epilogue."""
+        also the next mean-abs norm inside the MLP-down epilogue; 3: LN2 inside the output projection as well (slower on B200)."""
         _check(lib().egg_set_fused_epilogues(self._h, int(level)))
 
     def set_attention_tensor_core(self, mode):

@@ -124,7 +124,8 @@ struct egg_ctx {
     void *scratch[16] = {};
     size_t scratch_bytes[16] = {};
     // row-owning projections with the adaptive normalisations fused (default wherever the shapes allow)
-    int fused_level = 2;      // 0: two-kernel adaptive norms; 1: row-owning projections; 2: + the next mean-abs norm inside MLP-down
+    int fused_level = 2;      // 0: two-kernel adaptive norms; 1: row-owning projections; 2: + the next mean-abs norm inside MLP-down;
+                              // 3: + LN2 inside the output projection (selectable, slower: that epilogue is not hidden behind its MMAs)
     // attention on tcgen05 (egg_attention_tc.cu) instead of the mma.sync kernel: correct but slower as measured, off by default
     int attention_mode = 0;       // 0: mma.sync kernel; 1: tcgen05 scores and sums; 2: mma.sync scores, tcgen05 sums
     // measurement
@@ -907,10 +908,21 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
         if (rc) return rc;
         if (sc && (rc = scaled_dot1(c, M, c->d_ao, 1, nb + lo.o_b, SL.w_o_row + lH, c->d_xbo, 1))) return rc;
         // output projection + residual (mgpu.cu:828-830)
+        bool ln2_done = false;
         if (fused) {
             FusedParams fo = base_fused(c, M, H, 1);
             fo.nt_a_off = nb + lo.o_a; fo.xb = c->d_xbo; fo.xb_stride = 1; fo.out_shift = cf.shift_out;
-            if ((rc = PROF(EGG_PROF_GEMM_PRE32, launch_gemm_fused(st, FUSED_RES, c->d_ao, shl + c->so.o, c->d_x, c->d_x, fo, c->num_sms)))) return rc;
+            if (c->fused_level > 2) {
+                // ... and LN2 with the row dot of the MLP's up projection while the row is still on chip; the accumulators the
+                // row-wise launch used to clear for the kernels that follow are cleared here instead
+                fo.nt_w_m = nb + lo.ln2.w_m; fo.nt_b_m = nb + lo.ln2.b_m; fo.ndots = 1; fo.nt_dot[0] = nb + lo.mlp.up_b;
+                fo.h_out = c->d_h; fo.xb_out = c->d_xb; fo.xb_out_stride = 3;
+                EGG_CUDA(cudaMemsetAsync(c->d_xb, 0, (size_t)M * 3 * sizeof(int32_t), st));
+                if ((rc = PROF(EGG_PROF_GEMM_PRE32, launch_gemm_fused(st, FUSED_RES_LN, c->d_ao, shl + c->so.o, c->d_x, c->d_x, fo, c->num_sms)))) return rc;
+                EGG_CUDA(cudaMemsetAsync(c->d_xb2, 0, (size_t)M * sizeof(int32_t), st));
+                EGG_CUDA(cudaMemsetAsync(c->d_xbo, 0, (size_t)M * sizeof(int32_t), st));
+                ln2_done = true;
+            } else if ((rc = PROF(EGG_PROF_GEMM_PRE32, launch_gemm_fused(st, FUSED_RES, c->d_ao, shl + c->so.o, c->d_x, c->d_x, fo, c->num_sms)))) return rc;
         } else {
             GemmParams go = base_gemm(c, M, H, H);
             go.nt_a_off = nb + lo.o_a; go.xb = c->d_xbo; go.xb_stride = 1; go.out_shift = cf.shift_out; go.resid = c->d_x;
@@ -921,7 +933,7 @@ static int eval_wave(egg_ctx *c, uint32_t step_seed, int64_t start_idx, int pop_
         RowParams rb = base_row(c, M);
         rb.nt_w_m = nb + lo.ln2.w_m; rb.nt_b_m = nb + lo.ln2.b_m;
         rb.ndots = 1; rb.nt_dot[0] = nb + lo.mlp.up_b;
-        if ((rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, rb, row_mode)))) return rc;
+        if (!ln2_done && (rc = PROF(EGG_PROF_ROWWISE, launch_rowwise(st, rb, row_mode)))) return rc;
         if (sc && (rc = scaled_dot1(c, M, c->d_h, 1, nb + lo.mlp.up_b, SL.w_up_row + lH, c->d_xb, 3))) return rc;
         nn = next_norm(l + 1);
         if ((rc = run_mlp(c, M, lo.mlp, nb, shl + c->so.up, mdl + L.mlp_bias_up + (int64_t)l * 4 * H, shl + c->so.dn,
@@ -1535,7 +1547,7 @@ extern "C" int egg_measure_int8_peak(egg_ctx *c, int m, int n, int k, int iters,
 
 extern "C" int egg_set_fused_epilogues(egg_ctx *c, int enable) {
     if (!c) { set_error("null context"); return EGG_E_INVALID; }
-    c->fused_level = enable <= 0 ? 0 : (enable == 1 ? 1 : 2);
+    c->fused_level = enable <= 0 ? 0 : (enable >= 3 ? 3 : enable);
     return EGG_OK;
 }
 

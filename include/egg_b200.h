@@ -501,8 +501,11 @@ int egg_wave_members(egg_ctx *ctx);
  * identical bytes.
  * At level 2 (the default) the MLP-down projection's epilogue also runs the mean-abs norm that follows the
  * block (apply_standard_norm, mgpu.cu:646-678: LN1 of the next layer or the final norm) and the row dots of the
- * projections after it, so that row-wise kernel launch disappears.  enable = 1 keeps the row-owning projections
- * without that, enable = 0 forces the two-kernel form (for A/B timing and for tests that compare the forms); no
+ * projections after it, so that row-wise kernel launch disappears.  Level 3 does the same for LN2 inside the
+ * output projection; it is selectable and tested but not the default: that projection's epilogue is not hidden
+ * behind its short contraction (K = hidden_dim), and the norm costs more there than as a kernel of its own
+ * (measured on B200: +15 ms in the projections against -12 ms of row-wise kernels per 40960-member generation).
+ * enable = 1 keeps the row-owning projections without either, enable = 0 forces the two-kernel form (for A/B timing and for tests that compare the forms); no
  * counterpart in the reference.  egg_fused_epilogues_active returns the level this context's evaluations take
  * (0 when the configuration only allows the two-kernel form).
  */

@@ -14,7 +14,7 @@ SEED = 0x00C0FFEE
 
 def _losses(pkg, cfg, model, data, seed, start, pop, wave, fused, attention_tc=False):
     ctx = pkg.Context(cfg, 0, wave)
-    ctx.set_fused_epilogues(fused)          # False / True / 2: two-kernel, row-owning projections, + norm inside MLP-down
+    ctx.set_fused_epilogues(fused)          # False / True / 2 / 3: two-kernel, row-owning projections, + norm inside MLP-down, + LN2 inside the O projection
     ctx.set_attention_tensor_core(attention_tc)
     assert ctx.fused_epilogues_active() == int(fused)
     ctx.upload_model(model)
@@ -45,6 +45,8 @@ def test_fused_eval_matches_oracle(hidden, layers, seq, pop, mask, kind):
     assert (got == want).all(), (got[:8], want[:8])
     got2 = _losses(pkg, cfg, model, data, SEED + 3, seq, pop, 0, 2)
     assert (got2 == want).all(), ("norm inside the MLP-down epilogue", got2[:8], want[:8])
+    got3 = _losses(pkg, cfg, model, data, SEED + 3, seq, pop, 0, 3)
+    assert (got3 == want).all(), ("LN2 inside the output projection as well", got3[:8], want[:8])
     assert (_losses(pkg, cfg, model, data, SEED + 3, seq, pop, 0, False) == want).all()
     assert (_losses(pkg, cfg, model, data, SEED + 3, seq, pop, 0, True, attention_tc=True) == want).all(), "tcgen05 attention"
     assert (_losses(pkg, cfg, model, data, SEED + 3, seq, pop, 0, True, attention_tc=2) == want).all(), "hybrid attention"
