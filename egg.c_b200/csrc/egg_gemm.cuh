@@ -244,7 +244,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
     const int2 *rope = p.rope_t + (rc - mem * p.seq_len);                                // column of this token position
     constexpr bool do_rope = (EPI == EPI_QKV) && ROPE;      // Q and K column tiles; V passes through
     const long long half_ulp = 1ll << (p.rope_bit - 1);
-    int racc = 0, rmx = 0, rmn = 0;
+    int racc = 0, rmx = (EPI == EPI_LOGITS) ? INT_MIN : 0, rmn = 0;      // EPI_LOGITS: the signed row maximum
     uint32_t v[2][16];
     ptx::tmem_ld16(taddr, v[0]);
 #pragma unroll
@@ -346,6 +346,10 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                 rmx = __vimax3_s32(__vimax3_s32(rmx, x0, x1), x2, x3);
                 rmn = __vimin3_s32(__vimin3_s32(rmn, x0, x1), x2, x3);
                 o4[q4] = make_int4(x0, x1, x2, x3);
+            } else if (EPI == EPI_LOGITS) {
+                x0 >>= p.out_shift; x1 >>= p.out_shift; x2 >>= p.out_shift; x3 >>= p.out_shift;
+                rmx = __vimax3_s32(__vimax3_s32(rmx, x0, x1), x2, x3);
+                o4[q4] = make_int4(x0, x1, x2, x3);
             }
         }
         if (EPI == EPI_GELU) {
@@ -360,7 +364,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
                 *reinterpret_cast<int4 *>(&ost[lane * 16 + 4 * c]) = make_int4(outw[0], outw[1], outw[2], outw[3]);
             }
         }
-        if (EPI == EPI_PRE32 || EPI == EPI_QKV) {
+        if (EPI == EPI_PRE32 || EPI == EPI_QKV || EPI == EPI_LOGITS) {
             // int32 results leave as one TMA store per warp and chunk: each lane writes its row's 64 bytes into a dense
             // 32 x 16 box (16-byte pieces XOR-swizzled with the row, the 64-byte pattern the tensor map expects, which
             // also makes the stores conflict-free); the copy engine does the coalescing and clips rows beyond M
@@ -368,7 +372,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
             // chunks ago (the same box) must have been read out, the previous one may still be draining (-3 % on that
             // projection).  The residual projections keep one box: with K = 2048 the copy engine and the shared-memory
             // port are the busy units, and a second store in flight made them 2.5 % slower on the same GPU.
-            constexpr bool TWO_BOXES = (EPI == EPI_QKV);
+            constexpr bool TWO_BOXES = (EPI == EPI_QKV || EPI == EPI_LOGITS);
             if (lane == 0) { if (TWO_BOXES) ptx::tma_store_wait_read<1>(); else ptx::tma_store_wait_read<0>(); }
             __syncwarp();
             const bool second = TWO_BOXES && (c & 1);
@@ -410,6 +414,7 @@ __device__ __forceinline__ void epilogue_rpl(const GemmParams &p, GemmSmem<BN> &
         __syncwarp();
     }
     if (EPI == EPI_PRE32 || EPI == EPI_QKV) racc = max(rmx, -rmn);
+    if (EPI == EPI_LOGITS) racc = rmx;
     // per-row partial of this column quarter; the quarters are combined after the end-of-tile barrier
     sm.rowpart[cbase / (BN / 4)][m0q + lane - (m0q & ~(GEMM_BM - 1))] = racc;
 }
@@ -903,7 +908,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 const int a0 = sm.rowpart[0][row_in_tile], a1 = sm.rowpart[1][row_in_tile], a2 = sm.rowpart[2][row_in_tile],
                           a3 = sm.rowpart[3][row_in_tile];
                 if (EPI == EPI_GELU) atomicAdd(&p.rowstat[r], a0 + a1 + a2 + a3);
-                else if (EPI == EPI_PRE32) atomicMax(&p.rowstat[r], max(max(a0, a1), max(a2, a3)));
+                else if (EPI == EPI_PRE32 || EPI == EPI_LOGITS) atomicMax(&p.rowstat[r], max(max(a0, a1), max(a2, a3)));
                 else if (EPI == EPI_QKV) atomicMax(&p.rowstat[(int64_t)r * 3 + fast_div(n0, p.fd_third)], max(max(a0, a1), max(a2, a3)));
             }
             if (EPI <= EPI_LOGITS && have_nxt) tab_store<BN, EPI, RPL>(p, sm, e, nxt);   // published by the next tile's barrier
@@ -911,7 +916,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
 
     // output boxes still being copied out of shared memory must land before the block retires
-    if (RPL && (EPI == EPI_PRE32 || EPI == EPI_QKV || EPI == EPI_GELU) && warp >= 2 && lane == 0) ptx::tma_store_wait_all<0>();
+    if (RPL && (EPI == EPI_PRE32 || EPI == EPI_QKV || EPI == EPI_GELU || EPI == EPI_LOGITS) && warp >= 2 && lane == 0) ptx::tma_store_wait_all<0>();
     __syncwarp();
     ptx::tc_fence_before();
     __syncthreads();

@@ -43,6 +43,7 @@ int gemm_init() {
     if ((rc = set_attr<256, EPI_HEAD>())) return rc;
     if ((rc = set_attr<256, EPI_HEAD, 1>())) return rc;
     if ((rc = set_attr<256, EPI_LOGITS>())) return rc;
+    if ((rc = set_attr<256, EPI_LOGITS, 1>())) return rc;
     if ((rc = set_attr_both<EPI_VOTE>())) return rc;
     if ((rc = set_attr<256, EPI_NULL>())) return rc;
     EGG_CUDA(cudaFuncSetAttribute(gemm_fused_kernel<256, FUSED_QKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fused_smem_bytes<256>()));
@@ -231,7 +232,7 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
     if (epi == EPI_LOGITS && p.N % 256) { set_error("the logits GEMM needs a vocabulary that is a multiple of 256"); return EGG_E_INVALID; }
     if (epi <= EPI_LOGITS) {
         int max_slots = ((GEMM_BM - 1) / p.seq_len) / 2 + 2;
-        const bool rpl = p.seq_len % 32 == 0 && p.rpl >= 0 && epi != EPI_CLIP8 && epi != EPI_LOGITS;
+        const bool rpl = p.seq_len % 32 == 0 && p.rpl >= 0 && epi != EPI_CLIP8;
         if (max_slots > (rpl ? GEMM_RPL_SLOTS : GEMM_MAX_SLOTS)) { set_error("seq_len %d too small for the epilogue tables", p.seq_len); return EGG_E_INVALID; }
     }
     if (epi == EPI_VOTE && p.k_splits > 1) {
@@ -262,7 +263,7 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
     if ((rc = make_tmap(&ta, A, (uint64_t)p.M, (uint64_t)p.K, GEMM_BM))) return rc;
     if ((rc = make_tmap(&tb, B, (uint64_t)p.N, (uint64_t)p.K, (uint32_t)bn))) return rc;
     CUtensorMap to = ta;       // only the row-per-lane int32 epilogues store through a tensor map
-    if ((epi == EPI_PRE32 || epi == EPI_QKV) && p.seq_len % 32 == 0 && p.rpl >= 0) {
+    if ((epi == EPI_PRE32 || epi == EPI_QKV || epi == EPI_LOGITS) && p.seq_len % 32 == 0 && p.rpl >= 0) {
         if ((rc = make_tmap_out(&to, p.out32, (uint64_t)p.M, (uint64_t)p.N))) return rc;
     }
     if (epi == EPI_GELU && bn == 256 && p.seq_len % 32 == 0 && p.rpl >= 0) {
@@ -276,7 +277,9 @@ int launch_gemm(cudaStream_t st, int epi, const int8_t *A, const int8_t *B, cons
         case EPI_HEAD:
             if (p.seq_len % 32 == 0 && p.rpl >= 0) return launch_one<256, EPI_HEAD, 1>(st, ta, tb, to, p, num_sms);
             return launch_one<256, EPI_HEAD>(st, ta, tb, to, p, num_sms);
-        case EPI_LOGITS: return launch_one<256, EPI_LOGITS>(st, ta, tb, to, p, num_sms);
+        case EPI_LOGITS:
+            if (p.seq_len % 32 == 0 && p.rpl >= 0) return launch_one<256, EPI_LOGITS, 1>(st, ta, tb, to, p, num_sms);
+            return launch_one<256, EPI_LOGITS>(st, ta, tb, to, p, num_sms);
         case EPI_VOTE: return launch_bn<EPI_VOTE>(st, bn, ta, tb, to, p, num_sms);
         case EPI_NULL: return launch_one<256, EPI_NULL>(st, ta, tb, to, p, num_sms);
     }
