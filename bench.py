@@ -519,6 +519,7 @@ def main():
                     help="A/B: 0 two-kernel adaptive norms, 1 row-owning projections, 2 (default) also the next mean-abs norm inside the MLP-down epilogue")
     ap.add_argument("--attention-tc", type=int, nargs="?", const=1, default=None, choices=[0, 1, 2],
                     help="A/B: attention kernel: 0 mma.sync, 1 tcgen05 scores and sums, 2 mma.sync scores + tcgen05 sums (default: the library's)")
+    ap.add_argument("--replicated-update", action="store_true", help="N > 1: repeat the whole update on every GPU as the reference does (default: shard it by matrix)")
     ap.add_argument("--wave", type=int, default=0, help="members per internal wave (0: the library's default)")
     ap.add_argument("--small", action="store_true", help="profiling-sized run: 1024 members, one warm-up step, no end-to-end / CPU legs")
     args = ap.parse_args()
@@ -587,6 +588,8 @@ def main():
         ident = [pkg.nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ident, src=0)
         ctx.comm_init(ident[0], rank, world)
+        if not args.replicated_update:
+            ctx.set_update_sharding(True)      # every matrix stepped by one rank, new weights broadcast over NVLink
 
     def barrier():
         ctx.sync()
@@ -646,7 +649,8 @@ def main():
         barrier()
     e2e_value = pop * cfg.seq_len / (ms_e2e / 1e3)
 
-    # ---- replicas: every rank must hold byte-identical weights and optimiser state after the same generations ----
+    # ---- replicas: every rank must hold byte-identical weights and optimiser state after the same generations
+    # (with the sharded update download_opt_state first collects every matrix's state from its owner) ----
     crc_model = zlib.crc32(ctx.download_model().tobytes())
     crc_opt = zlib.crc32(ctx.download_opt_state().tobytes())
     replicas_identical = None
@@ -768,7 +772,9 @@ def main():
                                           2: "fused into the projection epilogues (row-owning kernels), the next mean-abs norm inside MLP-down",
                                           3: "fused into the projection epilogues (row-owning kernels), every mean-abs norm inside the projection before it"}[fused_active],
                        "l2_policy": "inputs larger than L2: each wave streams > 2 GB of activations, dataset 64 MiB",
-                       "parallelism": "population sharded, pair-aligned; one NCCL all-gather of fitness per generation"},
+                       "parallelism": ("population sharded, pair-aligned; one NCCL all-gather of fitness per generation; " +
+                                       ("update replicated on every GPU" if (world == 1 or args.replicated_update) else
+                                        "update sharded by matrix, new weights by grouped ncclBroadcast"))},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": int(DATA_LEN),
                     "d2h_bytes_per_step": int(per * 4 + 8)},
             "gpu_launches": int(launches),

@@ -19,7 +19,7 @@ EXPORTS = [
     "egg_config_defaults", "egg_config_validate", "egg_model_bytes", "egg_opt_state_bytes", "egg_ctx_create",
     "egg_ctx_destroy", "egg_last_error", "egg_sync", "egg_upload_model", "egg_download_model", "egg_upload_opt_state",
     "egg_download_opt_state", "egg_set_dataset", "egg_set_dataset_tokens", "egg_eval_chunk", "egg_read_losses", "egg_compute_fitness_pairs",
-    "egg_write_fitness", "egg_read_fitness", "egg_nccl_unique_id", "egg_comm_init", "egg_allgather_fitness",
+    "egg_write_fitness", "egg_read_fitness", "egg_nccl_unique_id", "egg_comm_init", "egg_allgather_fitness", "egg_set_update_sharding",
     "egg_apply_update", "egg_generation_host", "egg_perturbed_projection", "egg_update_reconstruct", "egg_update_matrix",
     "egg_update_reconstruct_noalloc", "egg_scales_bytes", "egg_upload_scales", "egg_download_scales", "egg_set_overlay_steps",
     "egg_timer_start", "egg_timer_stop", "egg_profile_enable", "egg_profile_read", "egg_profile_name", "egg_launch_count",
@@ -157,6 +157,7 @@ def lib():
         L.egg_nccl_unique_id.argtypes = [vp]
         L.egg_comm_init.argtypes = [vp, vp, C.c_int, C.c_int]
         L.egg_allgather_fitness.argtypes = [vp]
+        L.egg_set_update_sharding.argtypes = [vp, C.c_int]
         L.egg_apply_update.argtypes = [vp, C.c_uint32, C.c_float, P(C.c_uint64)]
         L.egg_generation_host.argtypes = [vp, vp, C.c_int64, C.c_int64, C.c_uint32, C.c_float, vp, P(C.c_uint64)]
         L.egg_perturbed_projection.argtypes = [vp, vp, vp, vp, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_int,
@@ -373,6 +374,10 @@ class Context:
     def comm_init(self, id128, rank, world):
         buf = (C.c_char * 128).from_buffer_copy(bytes(id128))
         _check(lib().egg_comm_init(self._h, buf, rank, world))
+
+    def set_update_sharding(self, enable=True):
+        """Each parameter is updated by one rank and broadcast (needs comm_init); download_opt_state becomes a collective."""
+        _check(lib().egg_set_update_sharding(self._h, 1 if enable else 0))
 
     def allgather_fitness(self):
         _check(lib().egg_allgather_fitness(self._h))

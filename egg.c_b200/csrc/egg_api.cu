@@ -13,6 +13,7 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <algorithm>
 #include <vector>
 
 #include <nccl.h>
@@ -35,6 +36,11 @@ struct NcclApi {
     ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
+    // sharded update only
+    ncclResult_t (*Broadcast)(const void *, void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
 };
 static NcclApi g_nccl;
 static int nccl_load() {
@@ -51,6 +57,10 @@ static int nccl_load() {
     *(void **)&g_nccl.AllGather = dlsym(g_nccl.h, "ncclAllGather");
     *(void **)&g_nccl.CommDestroy = dlsym(g_nccl.h, "ncclCommDestroy");
     *(void **)&g_nccl.GetErrorString = dlsym(g_nccl.h, "ncclGetErrorString");
+    *(void **)&g_nccl.Broadcast = dlsym(g_nccl.h, "ncclBroadcast");
+    *(void **)&g_nccl.AllReduce = dlsym(g_nccl.h, "ncclAllReduce");
+    *(void **)&g_nccl.GroupStart = dlsym(g_nccl.h, "ncclGroupStart");
+    *(void **)&g_nccl.GroupEnd = dlsym(g_nccl.h, "ncclGroupEnd");
     if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllGather || !g_nccl.CommDestroy) {
         set_error("NCCL library lacks required symbols");
         return EGG_E_NCCL;
@@ -139,6 +149,10 @@ struct egg_ctx {
     // multi-GPU
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1;
+    // sharded update: every parameter is reconstructed and stepped by one rank (owner[i] for params[i]) and its new int8
+    // weights are broadcast.  The optimiser state of a parameter is current on its owner only.
+    bool shard_update = false;
+    std::vector<int> owner;
 };
 
 // Brackets one launch (or launch group) with events when profiling is on.
@@ -571,10 +585,18 @@ extern "C" int egg_upload_opt_state(egg_ctx *c, const void *host_state, int64_t 
     return EGG_OK;
 }
 
+static bool update_is_sharded(const egg_ctx *c);
+static int broadcast_params(egg_ctx *c, bool opt_state);
+
 extern "C" int egg_download_opt_state(egg_ctx *c, void *host_state, int64_t nbytes) {
     if (!c || !host_state) { set_error("null argument"); return EGG_E_INVALID; }
     if (nbytes != c->opt_bytes) { set_error("optimiser state is %lld bytes", (long long)c->opt_bytes); return EGG_E_INVALID; }
     EGG_CUDA(cudaSetDevice(c->device));
+    if (update_is_sharded(c)) {
+        // every parameter's state is current on its owner only: collect it first (a collective: every rank calls this)
+        int rc = broadcast_params(c, true);
+        if (rc) return rc;
+    }
     EGG_CUDA(cudaMemcpyAsync(host_state, c->d_opt, (size_t)nbytes, cudaMemcpyDeviceToHost, c->stream));
     EGG_CUDA(cudaStreamSynchronize(c->stream));
     return EGG_OK;
@@ -1084,6 +1106,32 @@ extern "C" int egg_comm_init(egg_ctx *c, const void *id128, int rank, int world)
     return EGG_OK;
 }
 
+extern "C" int egg_set_update_sharding(egg_ctx *c, int enable) {
+    if (!c) { set_error("null context"); return EGG_E_INVALID; }
+    if (!enable) { c->shard_update = false; return EGG_OK; }
+    if (!c->comm || c->world < 2) { set_error("update sharding needs a communicator over at least two ranks"); return EGG_E_STATE; }
+    // owners: parameters in order of decreasing cost, each to the rank with the least work so far; the same
+    // deterministic walk on every rank.  Cost ~ weights for a matrix (tensor-core vote GEMM); a vector element costs
+    // about 300 matrix elements (its votes are hashed and summed pair by pair on the ordinary cores).
+    auto cost = [&](size_t i) {
+        const ParamDesc &d = c->params[i];
+        return d.rows_k ? (int64_t)d.rows_k * d.cols_n : (int64_t)d.cols_n * 300;
+    };
+    std::vector<size_t> order(c->params.size());
+    for (size_t i = 0; i < order.size(); i++) order[i] = i;
+    std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return cost(a) > cost(b); });
+    std::vector<int64_t> load(c->world, 0);
+    c->owner.assign(c->params.size(), 0);
+    for (size_t i : order) {
+        int best = 0;
+        for (int r = 1; r < c->world; r++) if (load[r] < load[best]) best = r;
+        c->owner[i] = best;
+        load[best] += cost(i);
+    }
+    c->shard_update = true;
+    return EGG_OK;
+}
+
 extern "C" int egg_allgather_fitness(egg_ctx *c) {
     if (!c) { set_error("null context"); return EGG_E_INVALID; }
     if (c->world == 1) return EGG_OK;
@@ -1170,10 +1218,35 @@ static int update_matrix(egg_ctx *c, const ParamDesc &d, uint32_t step_seed, flo
     return PROF(EGG_PROF_OVERLAY, launch_overlay_step(c->stream, c->d_scales + d.ov_out, c->d_ch_out, d.cols_n, c->ov_inc, c->ov_dec));
 }
 
+static bool update_is_sharded(const egg_ctx *c) { return c->shard_update && c->comm && c->world > 1 && !c->scales_on; }
+
+// One grouped broadcast per parameter from its owner: of the int8 weights, or of the optimiser state.
+static int broadcast_params(egg_ctx *c, bool opt_state) {
+    if (!g_nccl.Broadcast || !g_nccl.GroupStart || !g_nccl.GroupEnd) { set_error("this NCCL build lacks ncclBroadcast / group calls"); return EGG_E_NCCL; }
+    ncclResult_t r = g_nccl.GroupStart();
+    for (size_t i = 0; r == ncclSuccess && i < c->params.size(); i++) {
+        const ParamDesc &d = c->params[i];
+        const size_t n = d.rows_k ? (size_t)d.rows_k * d.cols_n : (size_t)d.cols_n;
+        if (opt_state) {
+            void *p = c->d_opt + d.opt_off;
+            r = g_nccl.Broadcast(p, p, n * (d.muon ? 8 : 12), ncclInt8, c->owner[i], c->comm, c->stream);
+        } else {
+            void *p = c->d_model + d.model_off;
+            r = g_nccl.Broadcast(p, p, n, ncclInt8, c->owner[i], c->comm, c->stream);
+        }
+    }
+    ncclResult_t e = g_nccl.GroupEnd();
+    if (r != ncclSuccess || e != ncclSuccess) { set_error("ncclBroadcast of the sharded update failed (%d / %d)", (int)r, (int)e); return EGG_E_NCCL; }
+    return EGG_OK;
+}
+
 static int apply_update_async(egg_ctx *c, uint32_t step_seed, float lr) {
     const egg_config &cf = c->cfg;
     EGG_CUDA(cudaMemsetAsync(c->d_updates, 0, sizeof(unsigned long long), c->stream));
-    for (const ParamDesc &d : c->params) {
+    const bool sharded = update_is_sharded(c);
+    for (size_t i = 0; i < c->params.size(); i++) {
+        const ParamDesc &d = c->params[i];
+        if (sharded && c->owner[i] != c->rank) continue;       // another rank steps this parameter and sends the result
         int rc;
         if (d.rows_k) {
             rc = update_matrix(c, d, step_seed, lr);
@@ -1193,6 +1266,14 @@ static int apply_update_async(egg_ctx *c, uint32_t step_seed, float lr) {
     // every matrix still on a side stream must be applied before its K-major shadow is rebuilt
     for (int b = 0; b < 2; b++)
         if (c->side_used[b]) { EGG_CUDA(cudaStreamWaitEvent(c->stream, c->ev_done[b], 0)); c->side_used[b] = false; }
+    if (sharded) {
+        // the new weights travel from their owners; the owners' change counts add up to the generation's
+        int rc = broadcast_params(c, false);
+        if (rc) return rc;
+        if (!g_nccl.AllReduce) { set_error("this NCCL build lacks ncclAllReduce"); return EGG_E_NCCL; }
+        ncclResult_t r = g_nccl.AllReduce(c->d_updates, c->d_updates, 1, ncclUint64, ncclSum, c->comm, c->stream);
+        if (r != ncclSuccess) { set_error("ncclAllReduce of the update count failed (%d)", (int)r); return EGG_E_NCCL; }
+    }
     return refresh_shadows(c);
 }
 

@@ -199,6 +199,18 @@ int egg_comm_init(egg_ctx *ctx, const void *id128, int rank, int world);
  */
 int egg_allgather_fitness(egg_ctx *ctx);
 
+/*
+ * Shards the update over the ranks of the communicator (no counterpart in the reference, which repeats the whole
+ * update on every GPU, mgpu.cu:1573-1668): every parameter is reconstructed and stepped by ONE rank -- parameters
+ * are dealt in order of decreasing cost to the least loaded rank -- and its new int8 weights reach the others by one
+ * grouped ncclBroadcast per generation; the change counts are summed with ncclAllReduce.  The weights are identical
+ * on every rank afterwards, as without sharding.  The optimiser state of a parameter is current on its owner only:
+ * egg_download_opt_state (and egg_save_checkpoint through it) first collects it, which makes them collective calls
+ * while sharding is on.  Not combined with adaptive-noise overlays (the update then runs replicated as before).
+ * Call after egg_comm_init; enable = 0 switches back.
+ */
+int egg_set_update_sharding(egg_ctx *ctx, int enable);
+
 /* ---- update ------------------------------------------------------------ */
 /*
  * ≙ the LAUNCH_ADAM_MATRIX / LAUNCH_ADAM_VECTOR sequence (mgpu.cu:1573-1668):

@@ -16,16 +16,19 @@ KW = dict(hidden_dim=256, n_layers=2, seq_len=32, population_size=64, device_mas
 SEED, LR, STEPS = 4242, 0.5, 3
 
 
-def _rank_main(rank, world, ident, q):
+def _rank_main(rank, world, ident, q, kw=None, shard=False):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     pkg = load_pkg()
-    cfg, ocfg, model, data = make_case(KW, data_len=40000)
+    kw = kw or KW
+    cfg, ocfg, model, data = make_case(kw, data_len=40000)
     ctx = pkg.Context(cfg, rank, 0)
     ctx.upload_model(model)
     ctx.set_dataset(data)
     ctx.comm_init(ident, rank, world)
-    per = KW["population_size"] // world
+    if shard:
+        ctx.set_update_sharding(True)
+    per = kw["population_size"] // world
     losses = np.zeros(per, np.int32)
     ups = []
     for step in range(STEPS):
@@ -62,6 +65,42 @@ def test_two_gpu_generation_matches_single_gpu():
         assert u == ups
         per = pop // 2
         assert lb == losses[rank * per:(rank + 1) * per].tobytes()
+
+
+@pytest.mark.parametrize("muon", [0, 1])
+def test_sharded_update_matches_replicated_update(muon):
+    """Every matrix updated by one rank and broadcast (egg_set_update_sharding): weights, change counts and the
+    collected optimiser state must equal the single-GPU generation's byte for byte (AdamW), and with Muon too, where
+    each matrix's Newton-Schulz runs on its owner with the same kernels as on one GPU."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    pkg = load_pkg()
+    kw = dict(KW, use_muon=muon)
+    cfg, ocfg, model, data = make_case(kw, data_len=40000)
+    ctx = pkg.Context(cfg, 0, 0)
+    ctx.upload_model(model)
+    ctx.set_dataset(data)
+    pop = kw["population_size"]
+    losses = np.zeros(pop, np.int32)
+    ups = [ctx.generation_host(None, step, SEED + step, LR, losses) for step in range(STEPS)]
+    want_m, want_o = ctx.download_model().tobytes(), ctx.download_opt_state().tobytes()
+    with pytest.raises(pkg.EggError):
+        ctx.set_update_sharding(True)            # no communicator
+    ctx.close()
+    ident = pkg.nccl_unique_id()
+    mpc = mp.get_context("spawn")
+    q = mpc.Queue()
+    procs = [mpc.Process(target=_rank_main, args=(r, 2, ident, q, kw, True)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, mb, ob, lb, u in got:
+        assert mb == want_m, "rank %d: weights diverged from the single-GPU generation" % rank
+        assert ob == want_o, "rank %d: collected optimiser state differs" % rank
+        assert u == ups
 
 
 def test_one_process_holds_contexts_on_two_gpus():
