@@ -19,7 +19,7 @@ EXPORTS = [
     "egg_config_defaults", "egg_config_validate", "egg_model_bytes", "egg_opt_state_bytes", "egg_ctx_create",
     "egg_ctx_destroy", "egg_last_error", "egg_sync", "egg_upload_model", "egg_download_model", "egg_upload_opt_state",
     "egg_download_opt_state", "egg_set_dataset", "egg_set_dataset_tokens", "egg_eval_chunk", "egg_read_losses", "egg_compute_fitness_pairs",
-    "egg_write_fitness", "egg_read_fitness", "egg_nccl_unique_id", "egg_comm_init", "egg_allgather_fitness", "egg_set_update_sharding",
+    "egg_write_fitness", "egg_read_fitness", "egg_nccl_unique_id", "egg_comm_init", "egg_allgather_fitness", "egg_set_update_sharding", "egg_update_owner_plan",
     "egg_apply_update", "egg_generation_host", "egg_perturbed_projection", "egg_update_reconstruct", "egg_update_matrix",
     "egg_update_reconstruct_noalloc", "egg_scales_bytes", "egg_upload_scales", "egg_download_scales", "egg_set_overlay_steps",
     "egg_timer_start", "egg_timer_stop", "egg_profile_enable", "egg_profile_read", "egg_profile_name", "egg_launch_count",
@@ -158,6 +158,7 @@ def lib():
         L.egg_comm_init.argtypes = [vp, vp, C.c_int, C.c_int]
         L.egg_allgather_fitness.argtypes = [vp]
         L.egg_set_update_sharding.argtypes = [vp, C.c_int]
+        L.egg_update_owner_plan.argtypes = [vp, C.c_int, vp, vp, C.c_int]
         L.egg_apply_update.argtypes = [vp, C.c_uint32, C.c_float, P(C.c_uint64)]
         L.egg_generation_host.argtypes = [vp, vp, C.c_int64, C.c_int64, C.c_uint32, C.c_float, vp, P(C.c_uint64)]
         L.egg_perturbed_projection.argtypes = [vp, vp, vp, vp, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_int,
@@ -219,6 +220,15 @@ def default_config(**kw):
             raise KeyError(k)
         setattr(cfg, k, v)
     return cfg
+
+
+def update_owner_plan(cfg, world):
+    """(owners, costs) of every parameter as the sharded update deals them over `world` ranks (no GPU needed)."""
+    n = lib().egg_update_owner_plan(C.byref(cfg), world, None, None, 0)
+    _check(min(n, 0))
+    owners, costs = np.zeros(n, np.int32), np.zeros(n, np.int64)
+    _check(min(lib().egg_update_owner_plan(C.byref(cfg), world, _ptr(owners), _ptr(costs), n), 0))
+    return owners, costs
 
 
 def model_bytes(cfg):

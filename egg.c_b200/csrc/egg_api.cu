@@ -1106,28 +1106,46 @@ extern "C" int egg_comm_init(egg_ctx *c, const void *id128, int rank, int world)
     return EGG_OK;
 }
 
+// owners: parameters in order of decreasing cost, each to the rank with the least work so far; the same
+// deterministic walk on every rank.  Cost ~ weights for a matrix (tensor-core vote GEMM); a vector element costs
+// about 300 matrix elements (its votes are hashed and summed pair by pair on the ordinary cores).
+static int64_t update_cost(const ParamDesc &d) { return d.rows_k ? (int64_t)d.rows_k * d.cols_n : (int64_t)d.cols_n * 300; }
+static void plan_owners(const std::vector<ParamDesc> &params, int world, std::vector<int> &owner) {
+    std::vector<size_t> order(params.size());
+    for (size_t i = 0; i < order.size(); i++) order[i] = i;
+    std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return update_cost(params[a]) > update_cost(params[b]); });
+    std::vector<int64_t> load(world, 0);
+    owner.assign(params.size(), 0);
+    for (size_t i : order) {
+        int best = 0;
+        for (int r = 1; r < world; r++) if (load[r] < load[best]) best = r;
+        owner[i] = best;
+        load[best] += update_cost(params[i]);
+    }
+}
+
+extern "C" int egg_update_owner_plan(const egg_config *cfg, int world, int32_t *owner_out, int64_t *cost_out, int cap) {
+    if (!cfg || world < 1) { set_error("bad arguments"); return EGG_E_INVALID; }
+    int rc = egg_config_validate(cfg, nullptr);
+    if (rc) return rc;
+    const ModelLayout L = model_layout(*cfg);
+    const ShadowOff so = shadow_offsets(*cfg, nullptr);
+    std::vector<ParamDesc> params;
+    build_params(*cfg, L, so, params, nullptr);
+    std::vector<int> owner;
+    plan_owners(params, world, owner);
+    for (size_t i = 0; i < params.size() && (int)i < cap; i++) {
+        if (owner_out) owner_out[i] = owner[i];
+        if (cost_out) cost_out[i] = update_cost(params[i]);
+    }
+    return (int)params.size();
+}
+
 extern "C" int egg_set_update_sharding(egg_ctx *c, int enable) {
     if (!c) { set_error("null context"); return EGG_E_INVALID; }
     if (!enable) { c->shard_update = false; return EGG_OK; }
     if (!c->comm || c->world < 2) { set_error("update sharding needs a communicator over at least two ranks"); return EGG_E_STATE; }
-    // owners: parameters in order of decreasing cost, each to the rank with the least work so far; the same
-    // deterministic walk on every rank.  Cost ~ weights for a matrix (tensor-core vote GEMM); a vector element costs
-    // about 300 matrix elements (its votes are hashed and summed pair by pair on the ordinary cores).
-    auto cost = [&](size_t i) {
-        const ParamDesc &d = c->params[i];
-        return d.rows_k ? (int64_t)d.rows_k * d.cols_n : (int64_t)d.cols_n * 300;
-    };
-    std::vector<size_t> order(c->params.size());
-    for (size_t i = 0; i < order.size(); i++) order[i] = i;
-    std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return cost(a) > cost(b); });
-    std::vector<int64_t> load(c->world, 0);
-    c->owner.assign(c->params.size(), 0);
-    for (size_t i : order) {
-        int best = 0;
-        for (int r = 1; r < c->world; r++) if (load[r] < load[best]) best = r;
-        c->owner[i] = best;
-        load[best] += cost(i);
-    }
+    plan_owners(c->params, c->world, c->owner);
     c->shard_update = true;
     return EGG_OK;
 }

@@ -77,3 +77,21 @@ def test_slices_are_pair_aligned_and_cover_population():
         assert all(seen[i][0] + seen[i][1] == seen[i + 1][0] for i in range(world - 1))
     with pytest.raises(ValueError):
         sharding.member_slice(0, 4, 36)
+
+
+def test_sharded_update_owner_plan_is_balanced_and_complete():
+    """Every parameter has exactly one owner, every rank gets work, and the heaviest rank carries at most one largest
+    parameter more than an even split (greedy longest-processing-time bound), at the benchmark and the d-eggs shapes."""
+    pkg = load_pkg()
+    for kw in (dict(hidden_dim=512, n_layers=4, seq_len=256), dict(hidden_dim=1024, n_layers=12, seq_len=512, use_muon=1),
+               dict(hidden_dim=128, n_layers=1, seq_len=16, vocab_size=1024, ntt_mode=1)):
+        cfg = pkg.default_config(**kw)
+        for world in (1, 2, 4, 8):
+            owners, costs = pkg.update_owner_plan(cfg, world)
+            assert len(owners) == 12 * cfg.n_layers + 10 + (3 if cfg.ntt_mode else 0)
+            assert owners.min() >= 0 and owners.max() < world
+            load = np.bincount(owners, weights=costs, minlength=world)
+            assert (load > 0).all()
+            assert load.max() <= costs.sum() / world + costs.max()
+            again, _ = pkg.update_owner_plan(cfg, world)
+            assert (again == owners).all()
