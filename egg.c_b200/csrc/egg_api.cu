@@ -199,7 +199,7 @@ extern "C" int egg_config_validate(const egg_config *c, const char **why) {
     if (c->hidden_dim < 128 || c->hidden_dim > 1024 || c->hidden_dim % 128) w = "hidden_dim must be a multiple of 128 in [128,1024]";
     else if (c->head_dim != 64) w = "head_dim must be 64";
     else if (c->n_layers < 1 || c->n_layers > 64) w = "n_layers out of range";
-    else if (c->seq_len < 16 || c->seq_len % 16 || c->seq_len > 4096) w = "seq_len must be a multiple of 16 in [16,4096]";
+    else if (c->seq_len < 16 || c->seq_len % 16 || c->seq_len > 1024) w = "seq_len must be a multiple of 16 in [16,1024] (a head's K and V stay in shared memory for the whole attention block)";
     else if (c->vocab_size < 256 || c->vocab_size > 65536 || c->vocab_size % 256) w = "vocab_size must be a multiple of 256 in [256,65536]";
     else if (c->population_size < 2 || c->population_size % 2) w = "population_size must be even";
     else if (c->device_mask < 0 || c->device_mask > 15) w = "device_mask must be in [0,15]";

@@ -40,7 +40,7 @@ typedef struct egg_config {
     int32_t hidden_dim;          /* HIDDEN_DIM  (multiple of 128, <= 1024)         */
     int32_t head_dim;            /* HEAD_DIM    (64)                                */
     int32_t n_layers;            /* N_LAYERS                                        */
-    int32_t seq_len;             /* SEQ_LEN     (multiple of 16)                    */
+    int32_t seq_len;             /* SEQ_LEN     (multiple of 16, <= 1024)           */
     int32_t vocab_size;          /* VOCAB_SIZE  (256: byte tokens; else uint32_t)   */
     int32_t population_size;     /* POPULATION_SIZE (even)                          */
     int32_t fixed_point;         /* FIXED_POINT                                     */

@@ -74,7 +74,7 @@ def test_library_exports_every_declared_symbol():
 def test_config_validation_messages():
     pkg = load_pkg()
     L = pkg.lib()
-    for kw in (dict(hidden_dim=100), dict(seq_len=8), dict(vocab_size=300), dict(vocab_size=128), dict(vocab_size=131072), dict(population_size=7), dict(head_dim=32)):
+    for kw in (dict(hidden_dim=100), dict(seq_len=8), dict(seq_len=2048), dict(vocab_size=300), dict(vocab_size=128), dict(vocab_size=131072), dict(population_size=7), dict(head_dim=32)):
         cfg = pkg.default_config(**kw)
         why = C.c_char_p()
         assert L.egg_config_validate(C.byref(cfg), C.byref(why)) == pkg.EGG_E_INVALID

@@ -51,6 +51,24 @@ def test_eval_losses_match_oracle_and_reference(tag):
     ctx.close()
 
 
+def test_eval_longest_sequence():
+    """seq_len 1024, the longest the configuration check admits: a head's K and V fill 150 KB of shared memory, the
+    limb sums leave the 23-bit range of the short-sequence division path, the causal loop runs 32 key blocks."""
+    O = load_oracle()
+    kw = dict(hidden_dim=128, n_layers=1, seq_len=1024, population_size=4, device_mask=15)
+    cfg, ocfg, model, data = make_case(kw, data_len=30000, model_kind="random")
+    want = O.eval_losses(ocfg, model, data, 5, SEED + 9, 0, 4)
+    for fused in (2, 0):
+        ctx = _ctx(cfg)
+        ctx.set_fused_epilogues(fused)
+        ctx.upload_model(model)
+        ctx.set_dataset(data)
+        ctx.eval_chunk(SEED + 9, 5, 0, 4)
+        got = ctx.read_losses(0, 4)
+        assert (got == want).all(), (fused, got, want)
+        ctx.close()
+
+
 def test_eval_waves_and_chunks_are_consistent():
     """Small waves, an odd number of waves, chunked calls and a later start index give the same losses."""
     O = load_oracle()
