@@ -670,6 +670,7 @@ extern "C" int egg_upload_scales(egg_ctx *c, const void *host_scales, int64_t nb
     if (!c) { set_error("null context"); return EGG_E_INVALID; }
     EGG_CUDA(cudaSetDevice(c->device));
     if (!host_scales) { EGG_CUDA(cudaStreamSynchronize(c->stream)); c->scales_on = false; return EGG_OK; }
+    if (c->shard_update) { set_error("adaptive-noise overlays are not combined with the sharded update: switch it off first (egg_set_update_sharding(ctx, 0))"); return EGG_E_STATE; }
     if (c->cfg.ntt_mode) { set_error("adaptive-noise overlays are not built for ntt_mode != 0 (AdaptiveScales has no entry for the coefficient tables)"); return EGG_E_INVALID; }
     if (nbytes != c->SL.total) { set_error("overlays are %lld bytes, this configuration needs %lld", (long long)nbytes, (long long)c->SL.total); return EGG_E_INVALID; }
     EGG_CUDA(cudaMemcpyAsync(c->d_scales, host_scales, (size_t)nbytes, cudaMemcpyHostToDevice, c->stream));
@@ -681,6 +682,7 @@ extern "C" int egg_upload_scales(egg_ctx *c, const void *host_scales, int64_t nb
 extern "C" int egg_download_scales(egg_ctx *c, void *host_scales, int64_t nbytes) {
     if (!c || !host_scales) { set_error("null argument"); return EGG_E_INVALID; }
     if (!c->scales_on) { set_error("no overlays uploaded"); return EGG_E_STATE; }
+    if (c->shard_update) { set_error("adaptive-noise overlays are not combined with the sharded update: switch it off first (egg_set_update_sharding(ctx, 0))"); return EGG_E_STATE; }
     if (c->cfg.ntt_mode) { set_error("adaptive-noise overlays are not built for ntt_mode != 0 (AdaptiveScales has no entry for the coefficient tables)"); return EGG_E_INVALID; }
     if (nbytes != c->SL.total) { set_error("overlays are %lld bytes, buffer is %lld", (long long)c->SL.total, (long long)nbytes); return EGG_E_INVALID; }
     EGG_CUDA(cudaSetDevice(c->device));
@@ -702,8 +704,14 @@ static int set_dataset_async(egg_ctx *c, const void *host_tokens, int64_t n) {
         // a token outside the vocabulary would index past the embedding table (the reference reads whatever lies there)
         const uint32_t *t = static_cast<const uint32_t *>(host_tokens);
         const uint32_t V = (uint32_t)c->cfg.vocab_size;
-        for (int64_t i = 0; i < n; i++)
-            if (t[i] >= V) { set_error("token %u at position %lld is outside the vocabulary of %u", t[i], (long long)i, V); return EGG_E_INVALID; }
+        uint32_t top = 0;
+        for (int64_t i = 0; i < n; i++) top = t[i] > top ? t[i] : top;      // one vectorisable pass; the position only if it fails
+        if (top >= V) {
+            int64_t i = 0;
+            while (t[i] < V) i++;
+            set_error("token %u at position %lld is outside the vocabulary of %u", t[i], (long long)i, V);
+            return EGG_E_INVALID;
+        }
     }
     const int64_t bytes = n * c->tok_bytes;
     if (bytes > c->data_cap) {
@@ -1143,8 +1151,19 @@ extern "C" int egg_update_owner_plan(const egg_config *cfg, int world, int32_t *
 
 extern "C" int egg_set_update_sharding(egg_ctx *c, int enable) {
     if (!c) { set_error("null context"); return EGG_E_INVALID; }
-    if (!enable) { c->shard_update = false; return EGG_OK; }
+    if (!enable) {
+        // back to the replicated update: every rank needs every parameter's current state first (a collective)
+        if (update_is_sharded(c)) {
+            EGG_CUDA(cudaSetDevice(c->device));
+            int rc = broadcast_params(c, true);
+            if (rc) return rc;
+            EGG_CUDA(cudaStreamSynchronize(c->stream));
+        }
+        c->shard_update = false;
+        return EGG_OK;
+    }
     if (!c->comm || c->world < 2) { set_error("update sharding needs a communicator over at least two ranks"); return EGG_E_STATE; }
+    if (c->scales_on) { set_error("update sharding is not combined with adaptive-noise overlays"); return EGG_E_STATE; }
     plan_owners(c->params, c->world, c->owner);
     c->shard_update = true;
     return EGG_OK;

@@ -206,8 +206,9 @@ int egg_allgather_fitness(egg_ctx *ctx);
  * grouped ncclBroadcast per generation; the change counts are summed with ncclAllReduce.  The weights are identical
  * on every rank afterwards, as without sharding.  The optimiser state of a parameter is current on its owner only:
  * egg_download_opt_state (and egg_save_checkpoint through it) first collects it, which makes them collective calls
- * while sharding is on.  Not combined with adaptive-noise overlays (the update then runs replicated as before).
- * Call after egg_comm_init; enable = 0 switches back.
+ * while sharding is on.  Not combined with adaptive-noise overlays (either call refuses while the other is on).
+ * Call after egg_comm_init; enable = 0 switches back and, being the moment every rank needs every state again, is
+ * a collective call too.
  */
 int egg_set_update_sharding(egg_ctx *ctx, int enable);
 /* The owner (rank) and the cost weight of every parameter, in the library's update order, as the sharded update deals

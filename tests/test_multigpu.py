@@ -33,6 +33,11 @@ def _rank_main(rank, world, ident, q, kw=None, shard=False):
     ups = []
     for step in range(STEPS):
         ups.append(ctx.generation_host(None, step, SEED + step, LR, losses))
+    if shard:
+        # back to the replicated update: the switch collects every parameter's state, so one more generation on
+        # every rank must continue exactly where the owners left off
+        ctx.set_update_sharding(False)
+        ups.append(ctx.generation_host(None, STEPS, SEED + STEPS, LR, losses))
     q.put((rank, ctx.download_model().tobytes(), ctx.download_opt_state().tobytes(), losses.tobytes(), ups))
     ctx.close()
 
@@ -82,7 +87,7 @@ def test_sharded_update_matches_replicated_update(muon):
     ctx.set_dataset(data)
     pop = kw["population_size"]
     losses = np.zeros(pop, np.int32)
-    ups = [ctx.generation_host(None, step, SEED + step, LR, losses) for step in range(STEPS)]
+    ups = [ctx.generation_host(None, step, SEED + step, LR, losses) for step in range(STEPS + 1)]
     want_m, want_o = ctx.download_model().tobytes(), ctx.download_opt_state().tobytes()
     with pytest.raises(pkg.EggError):
         ctx.set_update_sharding(True)            # no communicator
