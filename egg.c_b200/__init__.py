@@ -158,7 +158,7 @@ def lib():
         L.egg_comm_init.argtypes = [vp, vp, C.c_int, C.c_int]
         L.egg_allgather_fitness.argtypes = [vp]
         L.egg_set_update_sharding.argtypes = [vp, C.c_int]
-        L.egg_update_owner_plan.argtypes = [vp, C.c_int, vp, vp, C.c_int]
+        L.egg_update_owner_plan.argtypes = [vp, C.c_int, vp, vp, vp, vp, C.c_int]
         L.egg_apply_update.argtypes = [vp, C.c_uint32, C.c_float, P(C.c_uint64)]
         L.egg_generation_host.argtypes = [vp, vp, C.c_int64, C.c_int64, C.c_uint32, C.c_float, vp, P(C.c_uint64)]
         L.egg_perturbed_projection.argtypes = [vp, vp, vp, vp, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_uint32, C.c_int,
@@ -222,13 +222,14 @@ def default_config(**kw):
     return cfg
 
 
-def update_owner_plan(cfg, world):
-    """(owners, costs) of every parameter as the sharded update deals them over `world` ranks (no GPU needed)."""
-    n = lib().egg_update_owner_plan(C.byref(cfg), world, None, None, 0)
+def update_owner_plan(cfg, world, spans=False):
+    """(owners, costs) of every parameter as the sharded update deals them over `world` ranks (no GPU needed); with
+    spans=True also the byte offset inside the model and the number of weights of every parameter."""
+    n = lib().egg_update_owner_plan(C.byref(cfg), world, None, None, None, None, 0)
     _check(min(n, 0))
-    owners, costs = np.zeros(n, np.int32), np.zeros(n, np.int64)
-    _check(min(lib().egg_update_owner_plan(C.byref(cfg), world, _ptr(owners), _ptr(costs), n), 0))
-    return owners, costs
+    owners, costs, offs, lens = np.zeros(n, np.int32), np.zeros(n, np.int64), np.zeros(n, np.int64), np.zeros(n, np.int64)
+    _check(min(lib().egg_update_owner_plan(C.byref(cfg), world, _ptr(owners), _ptr(costs), _ptr(offs), _ptr(lens), n), 0))
+    return (owners, costs, offs, lens) if spans else (owners, costs)
 
 
 def model_bytes(cfg):

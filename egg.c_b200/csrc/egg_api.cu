@@ -1132,7 +1132,8 @@ static void plan_owners(const std::vector<ParamDesc> &params, int world, std::ve
     }
 }
 
-extern "C" int egg_update_owner_plan(const egg_config *cfg, int world, int32_t *owner_out, int64_t *cost_out, int cap) {
+extern "C" int egg_update_owner_plan(const egg_config *cfg, int world, int32_t *owner_out, int64_t *cost_out, int64_t *model_off_out,
+                                     int64_t *weights_out, int cap) {
     if (!cfg || world < 1) { set_error("bad arguments"); return EGG_E_INVALID; }
     int rc = egg_config_validate(cfg, nullptr);
     if (rc) return rc;
@@ -1145,6 +1146,8 @@ extern "C" int egg_update_owner_plan(const egg_config *cfg, int world, int32_t *
     for (size_t i = 0; i < params.size() && (int)i < cap; i++) {
         if (owner_out) owner_out[i] = owner[i];
         if (cost_out) cost_out[i] = update_cost(params[i]);
+        if (model_off_out) model_off_out[i] = params[i].model_off;
+        if (weights_out) weights_out[i] = params[i].rows_k ? (int64_t)params[i].rows_k * params[i].cols_n : (int64_t)params[i].cols_n;
     }
     return (int)params.size();
 }

@@ -211,10 +211,11 @@ int egg_allgather_fitness(egg_ctx *ctx);
  * a collective call too.
  */
 int egg_set_update_sharding(egg_ctx *ctx, int enable);
-/* The owner (rank) and the cost weight of every parameter, in the library's update order, as the sharded update deals
- * them for `world` ranks; needs no GPU.  Writes at most `cap` entries to each non-NULL array, returns the number of
- * parameters (or a negative error). */
-int egg_update_owner_plan(const egg_config *cfg, int world, int32_t *owner_out, int64_t *cost_out, int cap);
+/* The owner (rank), the cost weight, the byte offset inside TransformerModel and the number of int8 weights of every
+ * parameter, in the library's update order, as the sharded update deals them for `world` ranks; needs no GPU.  Writes
+ * at most `cap` entries to each non-NULL array, returns the number of parameters (or a negative error). */
+int egg_update_owner_plan(const egg_config *cfg, int world, int32_t *owner_out, int64_t *cost_out, int64_t *model_off_out,
+                          int64_t *weights_out, int cap);
 
 /* ---- update ------------------------------------------------------------ */
 /*
