@@ -455,12 +455,12 @@ def run_tok(args, pkg, synth, torch, real_stdout, peaks):
     uint32 tokens, embedding and tied head over V columns, two-pass cross-entropy)."""
     V = args.vocab
     pop = 1024 if args.small else (args.pop if args.pop != POP_PER_GPU else 8192)
-    kw = dict(C2); kw["vocab_size"] = V
+    kw = dict(C2); kw["vocab_size"] = V; kw["ntt_mode"] = args.ntt_mode
     cfg = pkg.default_config(population_size=pop, **kw)
     ctx = pkg.Context(cfg, 0, args.wave)
     ctx.set_fused_epilogues(args.fused_level)
     ctx.upload_model(synth.random_model(cfg, 0, "uniform"))
-    data = synth.zipf_tokens(1, 1 << 22, V)
+    data = synth.zipf_tokens(1, 1 << 22, V) if V != 256 else synth.zipf_bytes(1, 1 << 22)
     ctx.set_dataset(data)
     S = cfg.seq_len
     steps, warm = max(1, args.steps), max(1, args.warmup)
@@ -489,7 +489,8 @@ def run_tok(args, pkg, synth, torch, real_stdout, peaks):
     line = {"metric": METRIC, "value": pop * S / (gen_ms / 1e3), "unit": UNIT, "n_gpus": 1, "steps": steps, "warmup": warm,
             "ms_per_step": gen_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8/int32", "data": "synthetic",
             "config": {"workload": "tok: Int8NativeFormer generation with the tokenizer build's vocabulary: L=4 H=512 seq=256 vocab=%d, uint32 tokens, "
-                                   "%d members, rank-1 noise mask 3" % (V, pop), "wave_members": wave, "l2_policy": "inputs larger than L2"},
+                                   "%d members, rank-1 noise mask 3%s" % (V, pop, (", transformed-window variant NTT_MODE %d" % args.ntt_mode) if args.ntt_mode else ""),
+                       "wave_members": wave, "l2_policy": "inputs larger than L2"},
             "e2e": None, "gpu_launches": None,
             "roofline": {"kernel": "head projection (logits epilogue) + head_loss_kernel", "bound": "hbm", "achieved": head_bytes / (head_ms / 1e3) / 1e9 if head_ms else None,
                          "peak": peaks["hbm"], "unit": "GB/s", "frac": (head_bytes / (head_ms / 1e3) / 1e9 / peaks["hbm"]) if head_ms else None,
@@ -510,6 +511,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5slice", "c5", "tok"])
     ap.add_argument("--vocab", type=int, default=8192, help="workload tok: vocabulary size (a multiple of 256)")
+    ap.add_argument("--ntt-mode", type=int, default=0, choices=[0, 1, 2, 3], help="workload tok: the reference's NTT_MODE (transformed input window, three more embedding tables)")
     ap.add_argument("--pop-total", type=int, default=262144, help="workload c5: the fixed population that is sharded over the GPUs")
     ap.add_argument("--pop", type=int, default=POP_PER_GPU, help="members per GPU (benchmark value: 40960)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
