@@ -71,6 +71,17 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(pkg.EXPORTS)
 
 
+def test_header_is_plain_c():
+    """The boundary is a C ABI: the header must compile as C99 on its own (no C++ in the signatures)."""
+    import shutil
+    import subprocess
+    if not shutil.which("gcc"):
+        pytest.skip("no gcc")
+    r = subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-fsyntax-only", "-x", "c", os.path.join(ROOT, "include", "egg_b200.h")],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
 def test_config_validation_messages():
     pkg = load_pkg()
     L = pkg.lib()
